@@ -1,0 +1,75 @@
+/* C ABI of libnexrt_b200: every launcher returns a cudaError_t as int (0 == success), takes raw
+ * device pointers and a stream handle, allocates nothing and is safe to call while the stream
+ * is being captured into a CUDA graph.  Same calling convention as the reference's per-kernel
+ * `extern "C" int NexN25Pro…Launch(ptrs…, stream)` entry points (e.g. nex_n2_5_pro/kernels/
+ * full_attn/nex_n2_5_pro_o_proj_reduce_ctypes.cu:299), but one library and run-time geometry.
+ */
+#pragma once
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One LL packet channel (see ll.cuh).  Mirrored field by field in parallel/channel.py. */
+typedef struct NexrtLLChannel {
+    unsigned long long* local;    /* this rank's inbox: [2 halves][world][slots] 8-byte packets */
+    unsigned long long* mc;       /* multicast alias of every rank's inbox, or NULL */
+    unsigned long long* peer[8];  /* unicast address of each rank's inbox (peer[rank] == local) */
+    const unsigned int* seq;      /* call sequence base, advanced by the last kernel of a step */
+    int* status;                  /* sticky failure word, 0 == healthy */
+    int world;
+    int rank;
+    unsigned int slots;           /* packets per (half, source rank) */
+    unsigned int reserved;
+    unsigned long long budget_ns; /* longest time one wait may take */
+} NexrtLLChannel;
+
+int nexrt_set_pdl(int enabled);
+int nexrt_version(void);
+
+/* step plumbing */
+int nexrt_embed_gather(const void* embed, const void* ctl, void* x, void* status, int H, int vocab, int M, void* stream);
+int nexrt_step_end(void* ctl, void* seq, unsigned int n_sites, void* mirror_host, void* mirror_gen, int words, void* stream);
+int nexrt_residual_add(void* x, const void* y, int n, void* stream);
+
+/* gated delta net */
+int nexrt_gdn_front(const void* x, const void* in_ln, const void* front_w, const void* front_s, const void* ba_w, const void* conv_w,
+                    const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv, void* z, void* beta, void* g, int H,
+                    int R, int C, int nv, int M, int conv_ring_len, float eps, int n_cta, void* stream);
+int nexrt_gdn_core(const void* qkv, const void* beta, const void* g, const void* ctl, void* state_ring, void* out, int nqk, int nv, int M,
+                   int state_ring_len, int C, void* stream);
+
+/* gated full attention */
+int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void* s, const void* ctl, void* q_raw, void* gate, void* k_raw,
+                     void* v_cache, int H, int hd, int nq, int ngate, int kvh, int M, int cache_len, float eps, int n_cta, void* stream);
+size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M);
+int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
+                      const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out, int hd, int nq,
+                      int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int cp_size, int cp_rank,
+                      const NexrtLLChannel* ch, unsigned int site, void* stream);
+
+/* output projection + all-reduce + residual.  mode 0: plain fp32 input; 1: GDN gated RMSNorm of
+ * (in, z); 2: context-parallel merge of the partials waiting in `cp` followed by * sigmoid(gate). */
+int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, const void* w, const void* s, void* x, int H, int K, int M,
+                          int mode, float eps, int hd, const NexrtLLChannel* ch, unsigned int site, const NexrtLLChannel* cp,
+                          unsigned int cp_site, int n_cta, void* stream);
+
+/* mixture of experts */
+int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket, int H, int E,
+                     int topk, int M, float eps, int n_cta, void* stream);
+int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, const void* wts, void* h, int H,
+                 int I, int S, int M, float eps, int shared_expert, int n_cta, void* stream);
+int nexrt_moe_l2_allreduce(const void* h, const void* ids, const void* w2, const void* w2_s, void* x, int H, int I, int S, int M,
+                           const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
+
+/* LM head, distributed top-k, sampler, accept / commit */
+int nexrt_lmhead_sample(const void* x, const void* final_ln, const void* w, void* logits_out, void* cand, void* ticket, const void* sampling,
+                        void* ctl, void* export_buf, int H, int V_local, int vocab_base, int M, float eps, int mode, int arg,
+                        const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
+int nexrt_sample_logits(const void* logits, const void* sampling, void* ctl, int V, int position_base, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,355 @@
+// Gated full attention for 1..8 token rows: projection front and split-KV decode.
+//
+//   attn_front  : input RMSNorm -> block-scaled FP8 GEMV of the (query|gate) per head, k and v
+//                 rows; v is appended to the bf16 cache at positions C..C+M-1.
+//   attn_decode : per-head q/k RMSNorm (1+w) + partial NeoX RoPE in the prologue, append of the
+//                 new k rows, split-KV online-softmax decode with a staircase causal mask over the
+//                 M rows, and an in-kernel combine by the last CTA to finish (ticket), which
+//                 also applies ctx * sigmoid(gate).
+//
+// One pair of kernels replaces the reference's QkvGroupSplitKKernel + NormRopeFusedKernel +
+// wgmma_fd4_mega (nex_n2_5_pro/kernels/full_attn/nex_n2_5_pro_qkv_proj_ctypes.cu:71-152,
+// …norm_rope_ctypes.cu:83-173, …attn_fd4_wgmma_ctypes.cu:120-401) and their M=4 / M=8 and
+// context-parallel variants.  There is no software grid barrier: the combine is done by
+// whichever CTA takes the last ticket, so no CTA ever waits on another.
+//
+// Context parallel mode: the committed prefix [0, C) is cut into cp_size equal windows, the
+// last rank of the group also takes the M new rows, every rank attends with the q heads of
+// the whole group, and instead of the final context the kernel emits per-row partials
+// (locally normalised context + log2-domain LSE) which it sends to the rank that owns each head.
+#include "api.h"
+#include "gemv.cuh"
+#include "ll.cuh"
+
+namespace nexrt {
+
+struct AttnFrontArgs {
+    const __nv_bfloat16* x;
+    const float* in_ln;
+    const uint8_t* w;        // [R][H]
+    const float* s;          // [R/128][H/128]
+    const int* ctl;
+    float* q_raw;            // [M][nq][hd]
+    float* gate;             // [M][ngate][hd]
+    float* k_raw;            // [M][kvh][hd]
+    __nv_bfloat16* v_cache;  // [kvh][cache_len][hd]
+    int H, hd, nq, ngate, kvh, M, cache_len;
+    float eps;
+};
+
+// Row order of the weight: nq "query" heads; when ngate == nq each query head is followed by its
+// gate head (checkpoint order query|gate per head), otherwise (context-parallel front) all nq
+// query heads come first and the ngate gate heads after them; then k heads, then v heads.
+template <int MB>
+__global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int R = (a.nq + a.ngate + 2 * a.kvh) * a.hd;
+    int t0, t1;
+    cta_range(R / 2, blockIdx.x, gridDim.x, &t0, &t1);
+    if (t1 > t0) prefetch_l2_range(a.w + static_cast<size_t>(t0) * 2 * a.H, static_cast<size_t>(t1 - t0) * 2 * a.H);
+    pdl_wait();
+    const int C0 = a.ctl[kCtlCommittedLen];
+    const int KB = a.H / kScaleBlock;
+    const bool interleaved = a.ngate == a.nq;
+    for (int m0 = 0; m0 < a.M; m0 += MB) {
+        const int mb = min(MB, a.M - m0);
+        if (m0) __syncthreads();
+        stage_rmsnorm<16>(smem, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
+        for (int t = t0 + warp; t < t1; t += nwarps) {
+            const int r = t * 2;
+            const uint8_t* w[2] = {a.w + static_cast<size_t>(r) * a.H, a.w + static_cast<size_t>(r + 1) * a.H};
+            const float* s[2] = {a.s + (r / kScaleBlock) * KB, a.s + ((r + 1) / kScaleBlock) * KB};
+            float acc[2][MB];
+            gemv_fp8<MB, 2, 32>(w, s, a.H, smem, lane, acc);
+            if (lane < 2) {
+                const int row = r + lane;
+                const int head = row / a.hd, d = row % a.hd;
+                for (int m = 0; m < mb; ++m) {
+                    const float v = lane == 0 ? acc[0][m] : acc[1][m];
+                    const int mm = m0 + m;
+                    if (head < a.nq + a.ngate) {
+                        int qh, is_gate;
+                        if (interleaved) { qh = head >> 1; is_gate = head & 1; }
+                        else { is_gate = head >= a.nq; qh = is_gate ? head - a.nq : head; }
+                        if (is_gate) a.gate[(static_cast<size_t>(mm) * a.ngate + qh) * a.hd + d] = v;
+                        else a.q_raw[(static_cast<size_t>(mm) * a.nq + qh) * a.hd + d] = v;
+                    } else if (head < a.nq + a.ngate + a.kvh) {
+                        a.k_raw[(static_cast<size_t>(mm) * a.kvh + (head - a.nq - a.ngate)) * a.hd + d] = v;
+                    } else {
+                        const int kv = head - a.nq - a.ngate - a.kvh;
+                        a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+struct AttnDecodeArgs {
+    const float* q_raw;       // [M][nq][hd]
+    const float* gate;        // [M][ngate][hd]
+    const float* k_raw;       // [M][kvh][hd]
+    const float* qn;          // [hd] 1 + w
+    const float* kn;          // [hd]
+    const float* inv_freq;    // [rotary/2]
+    const int* ctl;
+    __nv_bfloat16* k_cache;   // [kvh][cache_len][hd]
+    const __nv_bfloat16* v_cache;
+    float* ws_acc;            // [kvh][n_splits][rows][hd]
+    float* ws_ml;             // [kvh][n_splits][rows][2]
+    int* ticket;              // [kvh]
+    float* out;               // [M][ngate*hd]   ctx * sigmoid(gate)      (cp_size == 1)
+    int nq, ngate, kvh, M, cache_len, rotary, n_splits;
+    float eps;
+    // context parallel
+    int cp_size, cp_rank;     // window of the prefix this rank attends
+    LLChannel ch;             // partial exchange inside the cp group (world == cp_size)
+    unsigned int site;
+};
+
+constexpr int kRowsPerPass = 4;
+constexpr int kMinKeysPerSplit = 32;
+
+template <int HD>
+__global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
+    constexpr int EL = HD / 32;  // elements per lane
+    extern __shared__ __align__(16) float smem[];
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int NW = 8;
+    const int kv = blockIdx.y, split = blockIdx.x;
+    const int G = a.nq / a.kvh;             // q heads attending one kv head
+    const int rows = a.M * G;               // row index = m * G + head_in_group
+    pdl_wait();
+    const int C0 = a.ctl[kCtlCommittedLen];
+    // key window of this rank: [win_lo, win_hi) of positions, new rows included on the last cp rank
+    int win_lo = 0, win_hi = C0 + a.M;
+    if (a.cp_size > 1) {
+        const int share = C0 / a.cp_size;
+        win_lo = a.cp_rank * share;
+        win_hi = (a.cp_rank == a.cp_size - 1) ? C0 + a.M : (a.cp_rank + 1) * share;
+    }
+    const int n_keys = win_hi - win_lo;
+    int n_active = min(a.n_splits, (n_keys + kMinKeysPerSplit - 1) / kMinKeysPerSplit);
+    if (n_active < 1) n_active = 1;
+    if (split >= n_active) return;
+    const int per = (n_keys + n_active - 1) / n_active;
+    const int lo = win_lo + split * per, hi = min(win_hi, lo + per);
+
+    float* q_s = smem;                                   // [rows][HD]  normalised, roped, pre-scaled
+    float* k_s = q_s + static_cast<size_t>(rows) * HD;   // [M][HD]     normalised, roped, bf16 rounded
+    float* part = k_s + static_cast<size_t>(a.M) * HD;   // [NW][kRowsPerPass][HD + 2]
+    const float qscale = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;
+    const int half = a.rotary / 2;
+    // ---- prologue: q and new-k normalisation + RoPE, one warp per vector
+    for (int v = warp; v < rows + a.M; v += NW) {
+        const bool is_q = v < rows;
+        const int m = is_q ? v / G : v - rows;
+        const float* src = is_q ? a.q_raw + (static_cast<size_t>(m) * a.nq + kv * G + (v % G)) * HD
+                                : a.k_raw + (static_cast<size_t>(m) * a.kvh + kv) * HD;
+        float* dst = is_q ? q_s + static_cast<size_t>(v) * HD : k_s + static_cast<size_t>(m) * HD;
+        const float* gam = is_q ? a.qn : a.kn;
+        float e[EL], ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < EL; ++i) { e[i] = src[lane + 32 * i]; ss = fmaf(e[i], e[i], ss); }
+        const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(HD) + a.eps);
+#pragma unroll
+        for (int i = 0; i < EL; ++i) dst[lane + 32 * i] = e[i] * inv * gam[lane + 32 * i];
+        __syncwarp();
+        const float pos = static_cast<float>(C0 + m);
+        float rot[2] = {0.f, 0.f};
+        int ri[2] = {-1, -1};
+        for (int i = lane, c = 0; i < a.rotary; i += 32, ++c) {
+            const int f = i < half ? i : i - half;
+            float sn, cs;
+            sincosf(pos * a.inv_freq[f], &sn, &cs);
+            const float self = dst[i], other = i < half ? -dst[i + half] : dst[i - half];
+            rot[c] = self * cs + other * sn;
+            ri[c] = i;
+        }
+        __syncwarp();
+        for (int c = 0; c < 2; ++c)
+            if (ri[c] >= 0) dst[ri[c]] = rot[c];
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < EL; ++i) {
+            const float val = dst[lane + 32 * i];
+            dst[lane + 32 * i] = is_q ? val * qscale : bf16_round(val);
+        }
+        if (!is_q && split == 0) {
+            // every rank keeps the full cache: the new k rows are appended by split 0
+#pragma unroll
+            for (int i = 0; i < EL; ++i)
+                a.k_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + m) * HD + lane + 32 * i] = __float2bfloat16_rn(dst[lane + 32 * i]);
+        }
+    }
+    __syncthreads();
+
+    const __nv_bfloat16* kc = a.k_cache + static_cast<size_t>(kv) * a.cache_len * HD;
+    const __nv_bfloat16* vc = a.v_cache + static_cast<size_t>(kv) * a.cache_len * HD;
+    float* wsa = a.ws_acc + (static_cast<size_t>(kv) * a.n_splits + split) * rows * HD;
+    float* wsm = a.ws_ml + (static_cast<size_t>(kv) * a.n_splits + split) * rows * 2;
+
+    for (int r0 = 0; r0 < rows; r0 += kRowsPerPass) {
+        const int nr = min(kRowsPerPass, rows - r0);
+        float q[kRowsPerPass][EL], acc[kRowsPerPass][EL], mx[kRowsPerPass], l[kRowsPerPass];
+        int limit[kRowsPerPass];
+#pragma unroll
+        for (int r = 0; r < kRowsPerPass; ++r) {
+            const int rr = min(r0 + r, rows - 1);
+#pragma unroll
+            for (int i = 0; i < EL; ++i) { q[r][i] = q_s[static_cast<size_t>(rr) * HD + lane * EL + i]; acc[r][i] = 0.f; }
+            mx[r] = -INFINITY; l[r] = 0.f;
+            limit[r] = (r < nr) ? C0 + rr / G : -1;   // last visible position of the row
+        }
+        for (int p = lo + warp; p < hi; p += NW) {
+            float kf[EL], vf[EL];
+            if (p < C0) {
+                if (EL == 8) {
+                    unpack8_bf16(*reinterpret_cast<const uint4*>(kc + static_cast<size_t>(p) * HD + lane * 8), kf);
+                } else {
+                    const uint2 u = *reinterpret_cast<const uint2*>(kc + static_cast<size_t>(p) * HD + lane * 4);
+                    kf[0] = __uint_as_float(u.x << 16); kf[1] = __uint_as_float(u.x & 0xffff0000u);
+                    kf[2] = __uint_as_float(u.y << 16); kf[3] = __uint_as_float(u.y & 0xffff0000u);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < EL; ++i) kf[i] = k_s[static_cast<size_t>(p - C0) * HD + lane * EL + i];
+            }
+            if (EL == 8) {
+                unpack8_bf16(*reinterpret_cast<const uint4*>(vc + static_cast<size_t>(p) * HD + lane * 8), vf);
+            } else {
+                const uint2 u = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(p) * HD + lane * 4);
+                vf[0] = __uint_as_float(u.x << 16); vf[1] = __uint_as_float(u.x & 0xffff0000u);
+                vf[2] = __uint_as_float(u.y << 16); vf[3] = __uint_as_float(u.y & 0xffff0000u);
+            }
+#pragma unroll
+            for (int r = 0; r < kRowsPerPass; ++r) {
+                float sdot = 0.f;
+#pragma unroll
+                for (int i = 0; i < EL; ++i) sdot = fmaf(q[r][i], kf[i], sdot);
+                sdot = warp_sum(sdot);
+                if (p <= limit[r]) {
+                    const float nm = fmaxf(mx[r], sdot);
+                    const float corr = exp2f(mx[r] - nm), pw = exp2f(sdot - nm);
+                    l[r] = l[r] * corr + pw;
+#pragma unroll
+                    for (int i = 0; i < EL; ++i) acc[r][i] = fmaf(pw, vf[i], acc[r][i] * corr);
+                    mx[r] = nm;
+                }
+            }
+        }
+        // ---- merge the 8 warps of the CTA
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kRowsPerPass; ++r) {
+            float* pr = part + (static_cast<size_t>(warp) * kRowsPerPass + r) * (HD + 2);
+#pragma unroll
+            for (int i = 0; i < EL; ++i) pr[lane * EL + i] = acc[r][i];
+            if (lane == 0) { pr[HD] = mx[r]; pr[HD + 1] = l[r]; }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nr * HD; idx += blockDim.x) {
+            const int r = idx / HD, d = idx % HD;
+            float M_ = -INFINITY;
+            for (int w = 0; w < NW; ++w) M_ = fmaxf(M_, part[(static_cast<size_t>(w) * kRowsPerPass + r) * (HD + 2) + HD]);
+            float L_ = 0.f, A_ = 0.f;
+            for (int w = 0; w < NW; ++w) {
+                const float* pr = part + (static_cast<size_t>(w) * kRowsPerPass + r) * (HD + 2);
+                const float sc = pr[HD] == -INFINITY ? 0.f : exp2f(pr[HD] - M_);
+                L_ = fmaf(pr[HD + 1], sc, L_);
+                A_ = fmaf(pr[d], sc, A_);
+            }
+            wsa[static_cast<size_t>(r0 + r) * HD + d] = A_;
+            if (d == 0) { wsm[(r0 + r) * 2] = M_; wsm[(r0 + r) * 2 + 1] = L_; }
+        }
+        __syncthreads();
+    }
+
+    // ---- ticket: the last CTA of this kv head to arrive combines all splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_active - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
+    const float* base_ml = a.ws_ml + static_cast<size_t>(kv) * a.n_splits * rows * 2;
+    LLCall call;
+    if (a.cp_size > 1) call = ll_begin(a.ch, a.site);
+    for (int idx = threadIdx.x; idx < rows * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx % HD;
+        float M_ = -INFINITY;
+        for (int s = 0; s < n_active; ++s) M_ = fmaxf(M_, __ldcg(base_ml + (static_cast<size_t>(s) * rows + r) * 2));
+        float L_ = 0.f, A_ = 0.f;
+        for (int s = 0; s < n_active; ++s) {
+            const float ms = __ldcg(base_ml + (static_cast<size_t>(s) * rows + r) * 2);
+            const float sc = ms == -INFINITY ? 0.f : exp2f(ms - M_);
+            L_ = fmaf(__ldcg(base_ml + (static_cast<size_t>(s) * rows + r) * 2 + 1), sc, L_);
+            A_ = fmaf(__ldcg(base_acc + (static_cast<size_t>(s) * rows + r) * HD + d), sc, A_);
+        }
+        const int m = r / G, hg = r % G;   // head inside the kv group
+        const float ctx = L_ > 0.f ? A_ / L_ : 0.f;
+        if (a.cp_size == 1) {
+            const int head = kv * G + hg;
+            const float gt = a.gate[(static_cast<size_t>(m) * a.ngate + head) * HD + d];
+            a.out[(static_cast<size_t>(m) * a.ngate + head) * HD + d] = ctx * sigmoid_f(gt);
+        } else {
+            // head hg of the group belongs to cp rank hg / ngate; slot layout at the owner:
+            // [m][local head][HD + 1] with the LSE in the last slot
+            const int owner = hg / a.ngate, lh = hg % a.ngate;
+            const unsigned int slot = (static_cast<unsigned int>(m) * a.ngate + lh) * (HD + 1) + d;
+            const float lse = L_ > 0.f ? M_ + log2f(L_) : -INFINITY;
+            ll_send(a.ch, call, owner, slot, __float_as_uint(ctx));
+            if (d == 0) ll_send(a.ch, call, owner, slot - d + HD, __float_as_uint(lse));
+        }
+    }
+    if (threadIdx.x == 0) a.ticket[kv] = 0;
+}
+
+}  // namespace nexrt
+
+using namespace nexrt;
+
+extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void* s, const void* ctl, void* q_raw, void* gate,
+                                void* k_raw, void* v_cache, int H, int hd, int nq, int ngate, int kvh, int M, int cache_len, float eps,
+                                int n_cta, void* stream) {
+    if (M < 1 || M > kMaxRows || H % 512 || (hd != 128 && hd != 256)) return cudaErrorInvalidValue;
+    AttnFrontArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(in_ln), static_cast<const uint8_t*>(w),
+                    static_cast<const float*>(s), static_cast<const int*>(ctl), static_cast<float*>(q_raw), static_cast<float*>(gate),
+                    static_cast<float*>(k_raw), static_cast<__nv_bfloat16*>(v_cache), H, hd, nq, ngate, kvh, M, cache_len, eps};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M == 1) return launch(attn_front_kernel<1>, dim3(n_cta), dim3(512), sizeof(float) * H, st, a);
+    return launch(attn_front_kernel<4>, dim3(n_cta), dim3(512), sizeof(float) * 4 * H, st, a);
+}
+
+extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
+    const size_t rows = static_cast<size_t>(M) * (nq / kvh);
+    return sizeof(float) * (rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPass * (hd + 2));
+}
+
+extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
+                                 const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out,
+                                 int hd, int nq, int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int cp_size,
+                                 int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream) {
+    if (M < 1 || M > kMaxRows || nq % kvh || rotary > 64 || rotary % 2) return cudaErrorInvalidValue;
+    if (cp_size > 1 && ch == nullptr) return cudaErrorInvalidValue;
+    AttnDecodeArgs a{};
+    a.q_raw = static_cast<const float*>(q_raw); a.gate = static_cast<const float*>(gate); a.k_raw = static_cast<const float*>(k_raw);
+    a.qn = static_cast<const float*>(qn); a.kn = static_cast<const float*>(kn); a.inv_freq = static_cast<const float*>(inv_freq);
+    a.ctl = static_cast<const int*>(ctl); a.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+    a.v_cache = static_cast<const __nv_bfloat16*>(v_cache); a.ws_acc = static_cast<float*>(ws_acc); a.ws_ml = static_cast<float*>(ws_ml);
+    a.ticket = static_cast<int*>(ticket); a.out = static_cast<float*>(out);
+    a.nq = nq; a.ngate = ngate; a.kvh = kvh; a.M = M; a.cache_len = cache_len; a.rotary = rotary; a.n_splits = n_splits; a.eps = eps;
+    a.cp_size = cp_size; a.cp_rank = cp_rank; a.site = site;
+    if (ch) a.ch = *ch;
+    const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (hd == 256) return launch(attn_decode_kernel<256>, dim3(n_splits, kvh), dim3(256), smem, st, a);
+    if (hd == 128) return launch(attn_decode_kernel<128>, dim3(n_splits, kvh), dim3(256), smem, st, a);
+    return cudaErrorInvalidValue;
+}

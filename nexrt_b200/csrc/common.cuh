@@ -1,0 +1,182 @@
+// Shared device helpers for the sm_100a decode kernels: FP8 decode, warp reductions, bounded
+// waits on %globaltimer, programmatic dependent launch (PDL) and the launch wrapper.
+//
+// Counterpart of the reference's nex_n2_5_pro/kernels/common/{pdl.cuh,oproj_common.cuh}; the
+// geometry here is a run-time argument, not constexpr, so one binary serves every
+// tensor-parallel width and the shrunk test geometry.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace nexrt {
+
+constexpr int kScaleBlock = 128;   // edge of one FP8 scale block
+constexpr int kMaxRows = 8;        // most token rows one step carries (M=1 decode, 4 MTP, 8 DFlash)
+constexpr int kMaxWorld = 8;
+
+// Sticky status codes written into a status word by any kernel that gives up.
+enum Status : int {
+    kStatusOk = 0,
+    kStatusReduceTimeout = 1,   // a peer's packet did not arrive inside the wait budget
+    kStatusNonFinite = 2,       // sampler saw a non-finite winning logit
+    kStatusBadConfig = 3,       // sampler configuration out of range
+    kStatusCpTimeout = 4,       // context-parallel partial did not arrive
+    kStatusBadToken = 5,        // token id outside the vocabulary
+    kStatusPipeTimeout = 6,     // an mbarrier / TMA / tensor-core completion did not arrive
+};
+
+// Control block shared by all three decode modes (int32[32]).  Python mirror: runtime/control.py.
+enum Ctl : int {
+    kCtlCommittedLen = 0,   // tokens whose state is committed == position of row 0
+    kCtlStatus = 1,         // sticky OR of failure bits, 0 == healthy
+    kCtlCommitCount = 2,    // tokens committed by the last step
+    kCtlPending = 3,        // next row-0 token (sampled by the last step)
+    kCtlIds = 4,            // [8] ids of the rows of the next step; ids[0] == pending
+    kCtlEmitted = 12,       // [8] tokens emitted by the last step
+    kCtlRows = 20,          // live rows of the step (1, 4 or 8)
+    kCtlForcedCommit = 21,  // >0: commit exactly this many tokens (fixed-acceptance benchmarking)
+    kCtlStepEpoch = 22,     // steps executed
+    kCtlAccepted = 23,      // drafts accepted by the last step
+    kCtlEos = 24,           // end-of-sequence id or -1
+    kCtlStopPos = 25,       // index in emitted[] of the first EOS, or -1
+    kCtlFlags = 26,
+    kCtlForcedSeed = 27,    // seed of the forced-commit schedule (0: constant forced_commit)
+    kCtlForcedMean10 = 28,  // mean accepted length x10 of the seeded schedule
+    kCtlWords = 32,
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---- FP8 e4m3 -> fp32 ---------------------------------------------------------------------
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
+    __half2 h = *reinterpret_cast<__half2*>(&h2);
+    return __half22float2(h);
+}
+
+__device__ __forceinline__ void e4m3x4_to_float4(uint32_t w, float* f) {
+    float2 a = e4m3x2_to_float2(static_cast<uint16_t>(w & 0xffffu));
+    float2 b = e4m3x2_to_float2(static_cast<uint16_t>(w >> 16));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+// 16 fp8 weights (one uint4) dotted with 16 fp32 activations.
+__device__ __forceinline__ float dot16_fp8(const uint4& w, const float* __restrict__ x) {
+    float f[4], acc = 0.f;
+    e4m3x4_to_float4(w.x, f); acc = fmaf(f[0], x[0], acc); acc = fmaf(f[1], x[1], acc); acc = fmaf(f[2], x[2], acc); acc = fmaf(f[3], x[3], acc);
+    e4m3x4_to_float4(w.y, f); acc = fmaf(f[0], x[4], acc); acc = fmaf(f[1], x[5], acc); acc = fmaf(f[2], x[6], acc); acc = fmaf(f[3], x[7], acc);
+    e4m3x4_to_float4(w.z, f); acc = fmaf(f[0], x[8], acc); acc = fmaf(f[1], x[9], acc); acc = fmaf(f[2], x[10], acc); acc = fmaf(f[3], x[11], acc);
+    e4m3x4_to_float4(w.w, f); acc = fmaf(f[0], x[12], acc); acc = fmaf(f[1], x[13], acc); acc = fmaf(f[2], x[14], acc); acc = fmaf(f[3], x[15], acc);
+    return acc;
+}
+
+__device__ __forceinline__ void unpack16_fp8(const uint4& w, float* f) {
+    e4m3x4_to_float4(w.x, f);
+    e4m3x4_to_float4(w.y, f + 4);
+    e4m3x4_to_float4(w.z, f + 8);
+    e4m3x4_to_float4(w.w, f + 12);
+}
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& w, float* f) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(u[i] << 16);
+        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
+// Streaming 16-byte weight load: read-only path, do not keep in L1.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// Pull a byte range towards L2 with the whole CTA (used in the window before the dependency
+// wait, where a kernel may touch only constant weights).
+__device__ __forceinline__ void prefetch_l2_range(const void* base, size_t bytes) {
+    const char* p = static_cast<const char*>(base);
+    for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < bytes; off += static_cast<size_t>(blockDim.x) * 128)
+        prefetch_l2(p + off);
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------------
+// Everything a kernel does before pdl_wait() may overlap the tail of the previous kernel in
+// the stream and must therefore touch only data that no kernel of the step writes (weights).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// Block-wide sum for blockDim.x <= 1024; `red` is 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+}  // namespace nexrt
+
+// ---- host side --------------------------------------------------------------------------------
+namespace nexrt {
+
+// Process-wide switch: launch with the programmatic-stream-serialisation attribute.
+int& pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  Args... args) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
+}  // namespace nexrt

@@ -1,0 +1,155 @@
+// Mixer output projection fused with the tensor-parallel all-reduce and the residual add.
+//
+//   x[m] += all_reduce_sum_over_ranks( W_out[:, local] @ f(in[m]) )
+//
+// One kernel does: the input transform f (identity for attention, per-head gated RMSNorm *
+// silu(z) for the gated delta net, or the context-parallel LSE merge * sigmoid(gate)), the
+// block-scaled FP8 GEMV of this rank's column slice, the in-kernel all-reduce over NVSwitch
+// (one 8-byte self-tagged packet per value, published with `multimem.st` or peer stores, summed
+// in rank order), and the bf16 residual update.  Every rank ends with a bitwise identical
+// residual stream, which is also the "all-gather" that feeds the next projection.
+//
+// Replaces the reference's LinearFinalOProjFusedPushKernel (nex_n2_5_pro/kernels/linear_attn/
+// nex_n2_5_pro_linear_final_o_proj_ctypes.cu:51-259), OProjFusedPushKernel and
+// WholeVectorReduceKernel (…full_attn/nex_n2_5_pro_o_proj_reduce_ctypes.cu:51-289), the CP tail
+// (…cp_tail_ctypes.cu:117-211) and the M=4/M=8 o_proj kernels (…m4_attn_oproj_fused_ctypes.cu,
+// …m8_attn_oproj_ctypes.cu, …m4_gdn_oproj_fused_ctypes.cu, …m8_gdn_oproj_ctypes.cu).
+#include "api.h"
+#include "epilogue.cuh"
+#include "gemv.cuh"
+#include "ll.cuh"
+
+namespace nexrt {
+
+struct OProjArgs {
+    const float* in;        // [M][K]
+    const float* z;         // mode 1: [M][K]; mode 2: gate [M][K]
+    const float* gnorm_w;   // mode 1: [hd]
+    const uint8_t* w;       // [H][K] fp8
+    const float* s;         // [H/128][K/128]
+    __nv_bfloat16* x;       // [M][H] residual stream (read-modify-write)
+    int H, K, M, mode, hd;
+    float eps;
+    LLChannel ch;
+    unsigned int site;
+    LLChannel cp;           // mode 2: partial inbox of the context-parallel group
+    unsigned int cp_site;
+};
+
+template <int MB, int LPR>
+__global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    constexpr int GP = 32 / LPR;                 // row pairs a warp works on at once
+    const int sub = lane % LPR, grp = lane / LPR;
+    int r0, r1;
+    cta_range(a.H / 2, blockIdx.x, gridDim.x, &r0, &r1);   // in row pairs
+    const int nrows = (r1 - r0) * 2, row0 = r0 * 2;
+    if (nrows) prefetch_l2_range(a.w + static_cast<size_t>(row0) * a.K, static_cast<size_t>(nrows) * a.K);
+    float* xs = smem;                                       // [MB][K]
+    float* res = smem + static_cast<size_t>(MB) * a.K;      // [kMaxRows][nrows]
+    const int KB = a.K / kScaleBlock;
+    pdl_wait();
+    LLCall cpcall;
+    if (a.mode == 2) cpcall = ll_begin(a.cp, a.cp_site);
+    for (int m0 = 0; m0 < a.M; m0 += MB) {
+        const int mb = min(MB, a.M - m0);
+        if (m0) __syncthreads();
+        if (a.mode == 0) {
+            for (int idx = threadIdx.x; idx < mb * a.K; idx += blockDim.x) {
+                const int m = idx / a.K, k = idx % a.K;
+                xs[m * a.K + perm16(k, a.K)] = a.in[static_cast<size_t>(m0 + m) * a.K + k];
+            }
+        } else if (a.mode == 1) {
+            // gated RMSNorm per 128-wide head: gnorm_w * o * rsqrt(mean o^2 + eps) * silu(z)
+            const int heads = a.K / 128;
+            for (int v = warp; v < mb * heads; v += nwarps) {
+                const int m = v / heads, h = v % heads;
+                const size_t base = static_cast<size_t>(m0 + m) * a.K + h * 128 + lane * 4;
+                const float4 o = *reinterpret_cast<const float4*>(a.in + base);
+                const float4 zz = *reinterpret_cast<const float4*>(a.z + base);
+                const float4 gw = *reinterpret_cast<const float4*>(a.gnorm_w + lane * 4);
+                const float inv = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) / 128.f + a.eps);
+                const int k = h * 128 + lane * 4;
+                float* d = xs + m * a.K + perm16(k, a.K);
+                d[0] = gw.x * o.x * inv * silu_f(zz.x);
+                d[1] = gw.y * o.y * inv * silu_f(zz.y);
+                d[2] = gw.z * o.z * inv * silu_f(zz.z);
+                d[3] = gw.w * o.w * inv * silu_f(zz.w);
+            }
+        } else {
+            // context-parallel merge: for every (row, local head, dim) combine the partial contexts
+            // of the cp ranks with their log2-domain LSE weights, then gate.
+            const int hd = a.hd, heads = a.K / hd;
+            for (int idx = threadIdx.x; idx < mb * a.K; idx += blockDim.x) {
+                const int m = idx / a.K, k = idx % a.K, lh = k / hd, d = k % hd;
+                const unsigned int base = (static_cast<unsigned int>(m0 + m) * heads + lh) * (hd + 1);
+                float lse[kMaxWorld], ctx[kMaxWorld], mx = -INFINITY;
+                for (int sr = 0; sr < a.cp.world; ++sr) {
+                    unsigned int pl, pc;
+                    ll_wait(a.cp, cpcall, sr, base + hd, &pl, kStatusCpTimeout);
+                    ll_wait(a.cp, cpcall, sr, base + d, &pc, kStatusCpTimeout);
+                    lse[sr] = __uint_as_float(pl);
+                    ctx[sr] = __uint_as_float(pc);
+                    mx = fmaxf(mx, lse[sr]);
+                }
+                float num = 0.f, den = 0.f;
+                for (int sr = 0; sr < a.cp.world; ++sr) {
+                    const float wgt = lse[sr] == -INFINITY ? 0.f : exp2f(lse[sr] - mx);
+                    num = fmaf(wgt, ctx[sr], num);
+                    den += wgt;
+                }
+                const float gt = a.z[static_cast<size_t>(m0 + m) * a.K + k];
+                xs[m * a.K + perm16(k, a.K)] = (den > 0.f ? num / den : 0.f) * sigmoid_f(gt);
+            }
+        }
+        __syncthreads();
+        for (int tb = r0 + warp * GP; tb < r1; tb += nwarps * GP) {
+            const int t = min(tb + grp, r1 - 1);
+            const int r = t * 2;
+            const uint8_t* w[2] = {a.w + static_cast<size_t>(r) * a.K, a.w + static_cast<size_t>(r + 1) * a.K};
+            const float* s[2] = {a.s + (r / kScaleBlock) * KB, a.s + ((r + 1) / kScaleBlock) * KB};
+            float acc[2][MB];
+            gemv_fp8<MB, 2, LPR>(w, s, a.K, xs, sub, acc);
+            if (sub < 2 && tb + grp < r1) {
+                for (int m = 0; m < mb; ++m) res[(m0 + m) * nrows + (r - row0) + sub] = sub == 0 ? acc[0][m] : acc[1][m];
+            }
+        }
+    }
+    __syncthreads();
+    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
+}
+
+}  // namespace nexrt
+
+using namespace nexrt;
+
+extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, const void* w, const void* s, void* x, int H, int K,
+                                     int M, int mode, float eps, int hd, const NexrtLLChannel* ch, unsigned int site,
+                                     const NexrtLLChannel* cp, unsigned int cp_site, int n_cta, void* stream) {
+    if (M < 1 || M > kMaxRows || K % 128 || H % 2 || ch == nullptr || mode < 0 || mode > 2) return cudaErrorInvalidValue;
+    if (mode == 2 && (cp == nullptr || hd <= 0 || K % hd)) return cudaErrorInvalidValue;
+    if (ch->world > 1 && ch->slots < static_cast<unsigned int>(kMaxRows) * H) return cudaErrorInvalidValue;
+    OProjArgs a{};
+    a.in = static_cast<const float*>(in); a.z = static_cast<const float*>(z); a.gnorm_w = static_cast<const float*>(gnorm_w);
+    a.w = static_cast<const uint8_t*>(w); a.s = static_cast<const float*>(s); a.x = static_cast<__nv_bfloat16*>(x);
+    a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.eps = eps; a.ch = *ch; a.site = site;
+    if (cp) { a.cp = *cp; a.cp_site = cp_site; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int mb = M == 1 ? 1 : 4;
+    const int max_rows = ((H / 2 + n_cta - 1) / n_cta) * 2;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * K + static_cast<size_t>(kMaxRows) * max_rows);
+    const int lpr = K % 512 == 0 ? 32 : K % 256 == 0 ? 16 : 8;
+    dim3 g(n_cta), b(512);
+#define NEXRT_OPROJ(MB_, LPR_) return launch(oproj_allreduce_kernel<MB_, LPR_>, g, b, smem, st, a)
+    if (mb == 1) {
+        if (lpr == 32) NEXRT_OPROJ(1, 32);
+        if (lpr == 16) NEXRT_OPROJ(1, 16);
+        NEXRT_OPROJ(1, 8);
+    }
+    if (lpr == 32) NEXRT_OPROJ(4, 32);
+    if (lpr == 16) NEXRT_OPROJ(4, 16);
+    NEXRT_OPROJ(4, 8);
+#undef NEXRT_OPROJ
+}

@@ -1,0 +1,219 @@
+"""Plain fp32 PyTorch oracle of the hybrid stack (runs on CPU, single process, no collectives).
+
+This is the correctness reference every CUDA kernel is compared against and the timed CPU
+baseline.  It restates the math of the reference's own torch references:
+GDN ``nex_n2_5_pro/gdn.py:257-289``, gated attention ``nex_n2_5_pro/attn.py:96-137``, MoE with
+shared expert ``nex_n2_5_pro/moe.py:76-108`` and the final norm + LM head
+``nex_n2_5_pro/head.py:268-280`` - for an arbitrary :class:`ModelConfig` and for all heads
+at once (what a tensor-parallel group computes together).
+
+Rounding contract shared with the kernels: the residual stream and the KV cache are bf16,
+everything else (projections, conv history, recurrent state, logits) is fp32.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..config import ModelConfig
+from ..quant import dequantize_blockwise
+from ..weights import PFX, _scale_key
+
+L2_EPS = 1e-6
+
+
+def _deq(ckpt, name):
+    return dequantize_blockwise(ckpt[name + ".weight"], ckpt[_scale_key(ckpt.keys(), name + ".weight_scale_inv")])
+
+
+def rms_norm(x: torch.Tensor, gamma_plus_one: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * gamma_plus_one
+
+
+def partial_rope(x: torch.Tensor, pos: int, rotary_dim: int, theta: float) -> torch.Tensor:
+    """NeoX-style rotation of the first ``rotary_dim`` dims (reference attn.py:108-119)."""
+    half = rotary_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+    ang = float(pos) * inv
+    cos, sin = torch.cos(ang).repeat(2), torch.sin(ang).repeat(2)
+    rot = x[..., :rotary_dim]
+    rotated = torch.cat([-rot[..., half:], rot[..., :half]], -1)
+    return torch.cat([rot * cos + rotated * sin, x[..., rotary_dim:]], -1)
+
+
+def l2_norm(x: torch.Tensor) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + L2_EPS)
+
+
+class RefLayerState:
+    __slots__ = ("k", "v", "conv", "state")
+
+    def __init__(self):
+        self.k: List[torch.Tensor] = []
+        self.v: List[torch.Tensor] = []
+        self.conv: Optional[torch.Tensor] = None  # [C, 3] last three pre-conv rows
+        self.state: Optional[torch.Tensor] = None  # [nv, Dk, Dv]
+
+
+class RefModel:
+    """Token-at-a-time fp32 reference over an HF-named checkpoint dict."""
+
+    def __init__(self, cfg: ModelConfig, ckpt: Dict[str, torch.Tensor]):
+        self.cfg = cfg
+        c = cfg
+        self.embed = ckpt[PFX + "embed_tokens.weight"].float()
+        self.final_ln = 1.0 + ckpt[PFX + "norm.weight"].float()
+        self.lm_head = ckpt["lm_head.weight"].float()
+        self.layers = []
+        for L in range(c.n_layers):
+            p = f"{PFX}layers.{L}."
+            w = {
+                "in_ln": 1.0 + ckpt[p + "input_layernorm.weight"].float(),
+                "post_ln": 1.0 + ckpt[p + "post_attention_layernorm.weight"].float(),
+            }
+            if c.layer_types[L] == "linear":
+                a = p + "linear_attn."
+                w.update(
+                    kind="linear",
+                    qkv=_deq(ckpt, a + "in_proj_qkv"),
+                    z=_deq(ckpt, a + "in_proj_z"),
+                    out=_deq(ckpt, a + "out_proj"),
+                    b=ckpt[a + "in_proj_b.weight"].float(),
+                    a=ckpt[a + "in_proj_a.weight"].float(),
+                    conv=ckpt[a + "conv1d.weight"].float().reshape(-1, c.conv_kernel),
+                    A_log=ckpt[a + "A_log"].float(),
+                    dt_bias=ckpt[a + "dt_bias"].float(),
+                    gnorm=ckpt[a + "norm.weight"].float(),
+                )
+            else:
+                a = p + "self_attn."
+                w.update(
+                    kind="full",
+                    q=_deq(ckpt, a + "q_proj"),
+                    k=_deq(ckpt, a + "k_proj"),
+                    v=_deq(ckpt, a + "v_proj"),
+                    o=_deq(ckpt, a + "o_proj"),
+                    qn=1.0 + ckpt[a + "q_norm.weight"].float(),
+                    kn=1.0 + ckpt[a + "k_norm.weight"].float(),
+                )
+            m = p + "mlp."
+            w["router"] = ckpt[m + "gate.weight"].float()
+            w["sgate"] = ckpt[m + "shared_expert_gate.weight"].float().reshape(-1)
+            names = [f"experts.{e}." for e in range(c.n_experts)] + ["shared_expert."]
+            w["w1"] = [_deq(ckpt, m + n + "gate_proj") for n in names]
+            w["w3"] = [_deq(ckpt, m + n + "up_proj") for n in names]
+            w["w2"] = [_deq(ckpt, m + n + "down_proj") for n in names]
+            self.layers.append(w)
+        self.reset()
+
+    def reset(self):
+        self.pos = 0
+        self.states = [RefLayerState() for _ in range(self.cfg.n_layers)]
+
+    # ---- blocks ----------------------------------------------------------------------------
+    def _gdn(self, w, st: RefLayerState, x: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        D, nqk, nv = c.gdn_dim, c.gdn_qk_heads, c.gdn_v_heads
+        xn = rms_norm(x, w["in_ln"], c.rms_eps)
+        mixed = w["qkv"] @ xn
+        z = w["z"] @ xn
+        if st.conv is None:
+            st.conv = torch.zeros(mixed.numel(), c.conv_kernel - 1)
+            st.state = torch.zeros(nv, D, D)
+        window = torch.cat([st.conv, mixed[:, None]], 1)
+        st.conv = window[:, 1:].clone()
+        qkv = F.silu((window * w["conv"]).sum(1))
+        beta = torch.sigmoid(w["b"] @ xn)
+        g = -torch.exp(w["A_log"]) * F.softplus(w["a"] @ xn + w["dt_bias"])
+        rep = nv // nqk
+        q = l2_norm(qkv[: nqk * D].reshape(nqk, D)).repeat_interleave(rep, 0) * D**-0.5
+        k = l2_norm(qkv[nqk * D : 2 * nqk * D].reshape(nqk, D)).repeat_interleave(rep, 0)
+        v = qkv[2 * nqk * D :].reshape(nv, D)
+        s = st.state * torch.exp(g).view(nv, 1, 1)
+        kv = (s * k.unsqueeze(-1)).sum(-2)
+        s = s + k.unsqueeze(-1) * ((v - kv) * beta.view(nv, 1)).unsqueeze(-2)
+        st.state = s
+        out = (s * q.unsqueeze(-1)).sum(-2)
+        on = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + c.rms_eps)
+        core = (w["gnorm"] * on * F.silu(z.reshape(nv, D))).reshape(-1)
+        return w["out"] @ core
+
+    def _attn(self, w, st: RefLayerState, x: torch.Tensor, pos: int) -> torch.Tensor:
+        c = self.cfg
+        hd, nq, nkv = c.head_dim, c.n_q_heads, c.n_kv_heads
+        xn = rms_norm(x, w["in_ln"], c.rms_eps)
+        qg = (w["q"] @ xn).reshape(nq, 2 * hd)
+        q, gate = qg[:, :hd], qg[:, hd:]
+        k = (w["k"] @ xn).reshape(nkv, hd)
+        v = (w["v"] @ xn).reshape(nkv, hd)
+        q = partial_rope(rms_norm(q, w["qn"], c.rms_eps), pos, c.rotary_dim, c.rope_theta)
+        k = partial_rope(rms_norm(k, w["kn"], c.rms_eps), pos, c.rotary_dim, c.rope_theta)
+        st.k.append(k.to(torch.bfloat16).float())
+        st.v.append(v.to(torch.bfloat16).float())
+        K = torch.stack(st.k, 1)  # [nkv, S, hd]
+        V = torch.stack(st.v, 1)
+        rep = nq // nkv
+        scores = torch.einsum("hd,hsd->hs", q, K.repeat_interleave(rep, 0)) * hd**-0.5
+        ctx = torch.einsum("hs,hsd->hd", torch.softmax(scores, -1), V.repeat_interleave(rep, 0))
+        gated = (ctx * torch.sigmoid(gate)).reshape(-1)
+        return w["o"] @ gated
+
+    def _moe(self, w, x: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        xn = rms_norm(x, w["post_ln"], c.rms_eps)
+        probs = torch.softmax(w["router"] @ xn, -1)
+        tw, te = probs.topk(c.top_k)
+        tw = tw / tw.sum()
+        y = torch.zeros(c.hidden)
+        for wt, e in zip(tw.tolist(), te.tolist()):
+            h = F.silu(w["w1"][e] @ xn) * (w["w3"][e] @ xn)
+            y += wt * (w["w2"][e] @ h)
+        E = c.n_experts
+        h = F.silu(w["w1"][E] @ xn) * (w["w3"][E] @ xn)
+        y += torch.sigmoid(w["sgate"] @ xn) * (w["w2"][E] @ h)
+        return y
+
+    # ---- one token -------------------------------------------------------------------------
+    @torch.inference_mode()
+    def step(self, token: int, return_hidden: bool = False) -> torch.Tensor:
+        """Consume ``token`` at the current position, return fp32 logits ``[vocab]``."""
+        c = self.cfg
+        x = self.embed[token].to(torch.bfloat16)
+        for L, w in enumerate(self.layers):
+            st = self.states[L]
+            y = self._gdn(w, st, x) if w["kind"] == "linear" else self._attn(w, st, x, self.pos)
+            x = (x.float() + y).to(torch.bfloat16)
+            x = (x.float() + self._moe(w, x)).to(torch.bfloat16)
+        self.pos += 1
+        if return_hidden:
+            return x
+        return self.lm_head @ rms_norm(x, self.final_ln, c.rms_eps)
+
+    @torch.inference_mode()
+    def prefill(self, ids) -> torch.Tensor:
+        logits = None
+        for t in ids:
+            logits = self.step(int(t))
+        return logits
+
+    @torch.inference_mode()
+    def greedy(self, prompt, n_new: int):
+        """Greedy decode: returns (tokens, list of logits that produced them)."""
+        logits = self.prefill(prompt)
+        toks, all_logits = [], []
+        for _ in range(n_new):
+            all_logits.append(logits)
+            t = int(torch.argmax(logits))
+            toks.append(t)
+            logits = self.step(t)
+        return toks, all_logits
+
+
+def synthetic_prompt(vocab: int, length: int, seed: int = 1) -> List[int]:
+    """Uniform-random token ids (the benchmark prompts)."""
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (length,), generator=gen).tolist()
