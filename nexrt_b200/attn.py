@@ -1,0 +1,75 @@
+"""Gated full-attention layer block (non-CP and context-parallel arms).
+
+Counterpart of the reference's ``FullAttn`` (``nex_n2_5_pro/attn.py:261-512``) and ``FullAttnCP``
+(``nex_n2_5_pro/attn_cp.py:76-367``).  Three launches per layer: projection front (v appended to
+the cache), split-KV decode (q/k norm + RoPE in its prologue, combine by the last CTA), and the
+out-projection fused with the all-reduce and the residual.  In the context-parallel arm the
+front also projects the q heads of the other ranks that share this rank's kv head (the
+reference's duplicate-Q weights, ``attn.py:220-257``), the decode kernel attends only this
+rank's window of the prefix and sends per-head partials to their owners, and the LSE merge runs
+in the prologue of the out-projection kernel.
+
+The bf16 KV cache is ``[kv_heads_local][cache_len][head_dim]`` for K and for V, pre-allocated for
+the whole context (``attn.py:71-75,305-306``); ``cache_len`` may be shrunk for tests.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .ops.lib import check, ptr
+from .runtime.context import StepContext
+
+
+class FullAttn:
+    def __init__(self, ctx: StepContext, w: dict, cache_len: Optional[int] = None, cp_w: Optional[dict] = None):
+        self.ctx, self.w, self.cp_w = ctx, w, cp_w
+        cfg, spec, dev = ctx.cfg, ctx.spec, ctx.device
+        self.cache_len = cache_len or cfg.cache_len
+        shape = (spec.kv_heads, self.cache_len, cfg.head_dim)
+        self.k_cache = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+        self.v_cache = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+
+    def reset(self) -> None:
+        pass  # rows beyond committed_len are never read
+
+    def forward(self, M: int = 1, cp: bool = False) -> None:
+        c, lib = self.ctx, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
+        use_cp = cp and c.cp_channel is not None and self.cp_w is not None
+        w = self.cp_w if use_cp else self.w
+        nq = spec.q_heads * (spec.cp_size if use_cp else 1)
+        check(
+            lib.nexrt_attn_front(
+                ptr(c.x), ptr(self.w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(c.ctl), ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw),
+                ptr(self.v_cache), cfg.hidden, cfg.head_dim, nq, spec.q_heads, spec.kv_heads, M, self.cache_len, cfg.rms_eps, c.n_cta, st,
+            ),
+            "attn_front",
+        )
+        cp_site = c.next_site() if use_cp else 0
+        check(
+            lib.nexrt_attn_decode(
+                ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw), ptr(self.w["qn"]), ptr(self.w["kn"]), ptr(c.inv_freq), ptr(c.ctl), ptr(self.k_cache),
+                ptr(self.v_cache), ptr(c.ws_acc), ptr(c.ws_ml), ptr(c.attn_ticket), ptr(c.attn_out), cfg.head_dim, nq, spec.q_heads,
+                spec.kv_heads, M, self.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, spec.cp_size if use_cp else 1,
+                spec.cp_rank if use_cp else 0, c.cp_channel.ref if use_cp else None, cp_site, st,
+            ),
+            "attn_decode",
+        )
+        n_cta = min(c.n_cta, cfg.hidden // 32)
+        check(
+            lib.nexrt_oproj_allreduce(
+                ptr(c.attn_out), ptr(c.gate), None, ptr(self.w["out_w"]), ptr(self.w["out_s"]), ptr(c.x), cfg.hidden, spec.attn_local, M,
+                2 if use_cp else 0, cfg.rms_eps, cfg.head_dim, c.channel.ref, c.next_site(), c.cp_channel.ref if use_cp else None, cp_site,
+                n_cta, st,
+            ),
+            "attn_oproj_allreduce",
+        )
+
+    def load_kv(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Install ``k, v [kv_heads_local][S][head_dim]`` (already normalised and rotated)."""
+        S = k.shape[1]
+        self.k_cache[:, :S] = k.to(self.k_cache)
+        self.v_cache[:, :S] = v.to(self.v_cache)

@@ -70,6 +70,16 @@ int nexrt_lmhead_sample(const void* x, const void* final_ln, const void* w, void
                         const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
 int nexrt_sample_logits(const void* logits, const void* sampling, void* ctl, int V, int position_base, void* stream);
 
+/* host runtime (host_runtime.cu) */
+int nexrt_ipc_alloc(size_t bytes, void** ptr);
+int nexrt_ipc_get_handle(void* ptr, void* handle64);
+int nexrt_ipc_open(const void* handle64, void** ptr);
+int nexrt_ipc_close(void* ptr);
+int nexrt_ipc_free(void* ptr);
+int nexrt_host_mapped_alloc(size_t bytes, void** host, void** dev);
+int nexrt_host_mapped_free(void* host);
+int nexrt_host_wait_flag(const volatile int* flag, int want, double timeout_s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,307 @@
+"""Batch-1 decode engine: owns the blocks of every layer, the captured whole-step CUDA graphs and
+the generate loop.
+
+API of the reference's ``DecodeEngine`` (``nex_n2_5_pro/decode_engine.py:87-399``):
+``DecodeEngine(rank, world, dev, cp, ext)``, ``load_prefill``, ``step`` / ``step_cp``, ``capture``,
+``generate`` (one-step look-ahead queueing, tokens read from the host mirror), ``status_max``.
+What differs: any tensor-parallel width 1/2/4/8; the step carries ``M`` token rows (1 for plain
+decode, 4 / 8 for the speculative verifiers and for the engine's own chunked prefill) through the
+same kernels; 6 kernel nodes per layer + 3 per step instead of 7-8 + 6, every node launched with
+programmatic dependent launch so its weight prefetch overlaps the previous node's tail.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .attn import FullAttn
+from .config import ModelConfig, ShardSpec, active_config
+from .ctl_mirror import CtlMirror
+from .gdn import Gdn
+from .head import MODE_COMMIT, Head
+from .moe import Moe
+from .ops.lib import check, ptr
+from .runtime.context import StepContext
+from .runtime.control import CTL_WORDS, Ctl, decode_ctl
+
+CP_THRESHOLD = int(os.environ.get("NEXRT_CP_THRESHOLD", str(48 * 1024)))  # reference decode_engine.py:63-66
+WARMUP_STEPS = 3
+
+
+class DecodeEngine:
+    def __init__(
+        self,
+        rank: int = 0,
+        world: int = 1,
+        dev: Optional[torch.device] = None,
+        cp: bool = False,
+        ext: Optional[Dict] = None,
+        *,
+        cfg: Optional[ModelConfig] = None,
+        group=None,
+        max_rows: int = 1,
+        cache_len: Optional[int] = None,
+        budget_ms: Optional[float] = None,
+    ):
+        """``ext`` is the per-rank model dict in kernel layout (``weights.shard_model`` or
+        ``weights.random_rank_model``); the reference uses the same argument to alias tensors that
+        already live on the device (``decode_engine.py:87-92``)."""
+        if ext is None:
+            raise ValueError("DecodeEngine needs the per-rank model dict (ext=weights.shard_model(...))")
+        self.cfg = cfg or active_config()
+        self.rank, self.world = rank, world
+        self.dev = dev or torch.device("cuda", torch.cuda.current_device())
+        self.spec = ShardSpec(self.cfg, world, rank)
+        self.group = group
+        self.max_rows = max_rows
+        self.cp = bool(cp) and self.spec.cp_size > 1
+        self.ctx = StepContext(self.cfg, self.spec, self.dev, group=group, budget_ms=budget_ms, cp=self.cp)
+        state_ring = max(2, max_rows + 1)
+        conv_ring = 16
+        self.mixers: List = []
+        self.moes: List[Moe] = []
+        for layer, lw in enumerate(ext["layers"]):
+            mw = lw["mixer"]
+            if mw["kind"] == "linear":
+                self.mixers.append(Gdn(self.ctx, mw, state_ring=state_ring, conv_ring=conv_ring))
+            else:
+                self.mixers.append(FullAttn(self.ctx, mw, cache_len=cache_len, cp_w=lw.get("mixer_cp") if self.cp else None))
+            self.moes.append(Moe(self.ctx, lw["moe"]))
+        self.head = Head(self.ctx, ext["head"])
+        self.embed = ext["head"]["embed"]
+        self.mirror = CtlMirror(self.dev, CTL_WORDS)
+        self.graphs: Dict = {}
+        self._n_sites: Dict = {}
+        if world > 1:
+            dist.barrier(group=group)
+
+    # ---- state --------------------------------------------------------------------------------
+    def reset(self, first_token: int = 0, committed_len: int = 0) -> None:
+        """Start a new sequence: clear rings and the control block (collective when world > 1)."""
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for m in self.mixers:
+            m.reset()
+        c = self.ctx
+        c.ctl.zero_()
+        c.ctl[Ctl.EOS] = -1
+        c.ctl[Ctl.STOP_POS] = -1
+        c.ctl[Ctl.COMMITTED_LEN] = committed_len
+        c.ctl[Ctl.PENDING] = first_token
+        c.ctl[Ctl.IDS] = first_token
+        c.channel.reset()
+        if c.cp_channel is not None:
+            c.cp_channel.buf.tensor.zero_()
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def set_rows(self, ids: Sequence[int]) -> None:
+        """Host write of the row ids of the next step (eager use and tests)."""
+        t = torch.tensor(list(ids), dtype=torch.int32, device=self.dev)
+        self.ctx.ctl[Ctl.IDS : Ctl.IDS + len(ids)] = t
+
+    def set_forced_commit(self, count: int = 0, seed: int = 0, mean10: int = 0) -> None:
+        c = self.ctx.ctl
+        c[Ctl.FORCED_COMMIT], c[Ctl.FORCED_SEED], c[Ctl.FORCED_MEAN10] = count, seed, mean10
+
+    def read_ctl(self) -> dict:
+        return decode_ctl(self.ctx.ctl.tolist())
+
+    @property
+    def slot(self):
+        """The reference's ``slot = [token, S]`` view of the control block."""
+        w = self.ctx.ctl.tolist()
+        return [w[Ctl.PENDING], w[Ctl.COMMITTED_LEN]]
+
+    # ---- one step -----------------------------------------------------------------------------
+    def step(self, M: int = 1, cp: bool = False, head_mode: int = MODE_COMMIT, end: bool = True) -> None:
+        """Launch one whole step on the current stream: embed, every layer, head, step end."""
+        c = self.ctx
+        c.begin_step()
+        check(c.lib.nexrt_embed_gather(ptr(self.embed), ptr(c.ctl), ptr(c.x), ptr(c.status), self.cfg.hidden, self.cfg.vocab, M, c.stream()), "embed")
+        for mixer, moe in zip(self.mixers, self.moes):
+            if isinstance(mixer, FullAttn):
+                mixer.forward(M, cp=cp)
+            else:
+                mixer.forward(M)
+            moe.forward(M)
+        self.head.forward(M, mode=head_mode)
+        if end:
+            self.step_end()
+
+    def step_cp(self, M: int = 1) -> None:
+        self.step(M, cp=True)
+
+    def step_end(self) -> None:
+        c = self.ctx
+        check(
+            c.lib.nexrt_step_end(ptr(c.ctl), ptr(c.seq), c.site, self.mirror.dev_ptr, ptr(self.mirror.gen_dev), CTL_WORDS, c.stream()),
+            "step_end",
+        )
+
+    def status_max(self) -> int:
+        """Largest status word over the ranks (reference decode_engine.py:296-306)."""
+        s = self.ctx.ctl[Ctl.STATUS : Ctl.STATUS + 1].clone()
+        if self.world > 1:
+            dist.all_reduce(s, op=dist.ReduceOp.MAX, group=self.group)
+        return int(s.item())
+
+    # ---- graphs -------------------------------------------------------------------------------
+    def capture(self, M: int = 1, cp: bool = False, warmup: int = WARMUP_STEPS):
+        """Warm up, then capture one whole step into a CUDA graph (reference
+        decode_engine.py:308-324).  The control block is restored afterwards so the capture leaves
+        the sequence where it was."""
+        key = (M, bool(cp))
+        if key in self.graphs:
+            return self.graphs[key]
+        saved = self._snapshot()
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.step(M, cp=cp)
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            self.step(M, cp=cp)
+        self._restore(saved)
+        self.graphs[key] = g
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        return g
+
+    def _snapshot(self):
+        torch.cuda.synchronize(self.dev)
+        snap = {"ctl": self.ctx.ctl.clone(), "gdn": []}
+        C = int(snap["ctl"][Ctl.COMMITTED_LEN])
+        for m in self.mixers:
+            if isinstance(m, Gdn):
+                snap["gdn"].append((m.conv_ring.clone(), m.state_ring[C % m.state_ring_len].clone()))
+        return snap
+
+    def _restore(self, snap) -> None:
+        torch.cuda.synchronize(self.dev)
+        C = int(snap["ctl"][Ctl.COMMITTED_LEN])
+        it = iter(snap["gdn"])
+        for m in self.mixers:
+            if isinstance(m, Gdn):
+                conv, st = next(it)
+                m.conv_ring.copy_(conv)
+                m.state_ring[C % m.state_ring_len].copy_(st)
+        self.ctx.ctl.copy_(snap["ctl"])
+        self.mirror.resync()
+        torch.cuda.synchronize(self.dev)
+
+    # ---- generate -----------------------------------------------------------------------------
+    def generate(
+        self,
+        g_noncp=None,
+        g_cp=None,
+        max_new: int = 16,
+        eos: Optional[int] = None,
+        cp_threshold: int = CP_THRESHOLD,
+        on_tokens: Optional[Callable[[List[int]], None]] = None,
+    ) -> List[int]:
+        """Greedy / sampled decode of up to ``max_new`` tokens by graph replay.
+
+        Step k+1 is queued before step k's token is read from the host mirror, so the GPU never
+        idles on the host; EOS is therefore learned one step late and the extra replay is simply
+        not reported (reference decode_engine.py:326-399).  A token of -1 means a failed step.
+        """
+        g_noncp = g_noncp or self.capture(1, cp=False)
+        if self.cp and g_cp is None:
+            g_cp = self.capture(1, cp=True)
+        self.mirror.resync()
+        S = int(self.ctx.ctl[Ctl.COMMITTED_LEN].item())
+        budget = self._kv_budget()
+        out: List[int] = []
+
+        def launch(pos: int) -> int:
+            (g_cp if (g_cp is not None and pos >= cp_threshold) else g_noncp).replay()
+            return self.mirror.next_gen()
+
+        pending = [launch(S)]
+        queued = 1
+        while pending:
+            if queued < max_new and S + queued < budget:
+                pending.append(launch(S + queued))
+                queued += 1
+            words = self.mirror.wait(pending.pop(0))
+            tok = words[Ctl.EMITTED]
+            if tok < 0 or words[Ctl.STATUS] != 0:
+                for gen in pending:
+                    self.mirror.wait(gen)
+                raise RuntimeError(f"decode step failed: status {words[Ctl.STATUS]}")
+            out.append(tok)
+            if on_tokens:
+                on_tokens([tok])
+            if eos is not None and tok == eos:
+                for gen in pending:
+                    self.mirror.wait(gen)
+                break
+        return out
+
+    def _kv_budget(self) -> int:
+        lens = [m.cache_len for m in self.mixers if isinstance(m, FullAttn)]
+        return min(lens) if lens else 1 << 30
+
+    # ---- prefill ------------------------------------------------------------------------------
+    def prefill(self, ids: Sequence[int], chunk: int = 8, sample: bool = True) -> int:
+        """The engine's own chunked prefill: consume ``ids`` from an empty state and leave the
+        first generated token pending.  This arm runs the multi-row step kernels ``chunk`` rows at
+        a time with a forced full commit, so the state it leaves is the decode path's own."""
+        if self.max_rows < min(chunk, len(ids)) and len(ids) > 1:
+            chunk = self.max_rows
+        ids = list(int(t) for t in ids)
+        self.reset(first_token=ids[0])
+        pos = 0
+        while pos < len(ids):
+            n = min(chunk, len(ids) - pos)
+            self.set_rows(ids[pos : pos + n])
+            self.set_forced_commit(n)
+            g = self.graphs.get((n, False))
+            if g is not None:
+                g.replay()
+            else:
+                self.step(n)
+            pos += n
+        self.set_forced_commit(0)
+        torch.cuda.synchronize(self.dev)
+        self.mirror.resync()
+        return int(self.ctx.ctl[Ctl.PENDING].item())
+
+    def load_prefill(self, state: Dict) -> None:
+        """Install a saved prefill state ``{L, first_token, layers{idx: {kind, k_cache, v_cache |
+        conv_state, recurrent_state}}}`` (reference decode_engine.py:204-233, file format of
+        sglang_prefill/extract_state.py:260-281).  Tensors hold this rank's heads."""
+        L = int(state["L"])
+        self.reset(first_token=int(state["first_token"]), committed_len=L)
+        for idx, m in enumerate(self.mixers):
+            st = state["layers"][idx]
+            if isinstance(m, FullAttn):
+                m.load_kv(st["k_cache"].to(self.dev), st["v_cache"].to(self.dev))
+            else:
+                m.load_state(L, st["conv_state"].to(self.dev), st["recurrent_state"].to(self.dev))
+        torch.cuda.synchronize(self.dev)
+
+    def export_state(self) -> Dict:
+        """Inverse of :meth:`load_prefill` at the current committed length."""
+        w = self.ctx.ctl.tolist()
+        L = w[Ctl.COMMITTED_LEN]
+        layers = {}
+        for idx, m in enumerate(self.mixers):
+            if isinstance(m, FullAttn):
+                layers[idx] = {"kind": "full", "k_cache": m.k_cache[:, :L].clone(), "v_cache": m.v_cache[:, :L].clone()}
+            else:
+                conv, st = m.export_state(L)
+                layers[idx] = {"kind": "linear", "conv_state": conv.clone(), "recurrent_state": st.clone()}
+        return {"rank": self.rank, "tp": self.world, "L": L, "first_token": w[Ctl.PENDING], "layers": layers}

@@ -1,0 +1,47 @@
+"""Mixture-of-experts block: router + top-k, expert gate/up, expert down fused with the all-reduce.
+
+Counterpart of the reference's ``Moe`` (``nex_n2_5_pro/moe.py:220-426``): 512 routed experts,
+top-10 with renormalised softmax weights, one shared expert gated by ``sigmoid(gate . x)``,
+intermediate-parallel sharding (every rank holds all experts, ``inter / tp`` columns of each).
+Three launches instead of four (router GEMV and top-k are one kernel) and the raw weight mode
+only: the post-attention RMSNorm multiplier is applied to the activation in the kernels, so
+checkpoint tensors are used as stored (the reference's folded mode re-quantises every expert,
+``moe.py:127-171``).
+"""
+
+from __future__ import annotations
+
+from .ops.lib import check, ptr
+from .runtime.context import StepContext
+
+
+class Moe:
+    def __init__(self, ctx: StepContext, w: dict):
+        self.ctx, self.w = ctx, w
+
+    def forward(self, M: int = 1) -> None:
+        c, w, lib = self.ctx, self.w, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
+        S = cfg.top_k + 1
+        check(
+            lib.nexrt_moe_router(
+                ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w"]), ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_ticket),
+                cfg.hidden, cfg.n_experts, cfg.top_k, M, cfg.rms_eps, c.n_cta, st,
+            ),
+            "moe_router",
+        )
+        check(
+            lib.nexrt_moe_l1(
+                ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_h), cfg.hidden,
+                spec.inter, S, M, cfg.rms_eps, cfg.n_experts, c.n_cta, st,
+            ),
+            "moe_l1",
+        )
+        n_cta = min(c.n_cta, cfg.hidden // 32)
+        check(
+            lib.nexrt_moe_l2_allreduce(
+                ptr(c.moe_h), ptr(c.moe_ids), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), cfg.hidden, spec.inter, S, M, c.channel.ref,
+                c.next_site(), n_cta, st,
+            ),
+            "moe_l2_allreduce",
+        )

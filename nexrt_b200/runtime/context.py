@@ -1,0 +1,90 @@
+"""Per-engine launch context: control block, residual rows, LL channel, scratch and site counting.
+
+The reference allocates these per block object and wires them together in
+``DecodeEngine.__init__`` (``nex_n2_5_pro/decode_engine.py:87-202``); here one context owns the
+buffers every block of an engine shares, so a 60-layer stack carries one set of scratch.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig, ShardSpec
+from ..ops import lib as L
+from ..parallel.channel import LLChannel
+from .control import CTL_WORDS, Ctl
+
+MAX_ROWS = 8
+MAX_TOPK = 28
+
+
+class StepContext:
+    def __init__(self, cfg: ModelConfig, spec: ShardSpec, device: torch.device, group=None, budget_ms=None, cp: bool = False):
+        self.cfg, self.spec, self.device, self.group = cfg, spec, device, group
+        self.lib = L.load()
+        self.tp, self.rank = spec.tp, spec.rank
+        props = torch.cuda.get_device_properties(device)
+        self.n_cta = props.multi_processor_count
+        H = cfg.hidden
+        i32, f32, bf = torch.int32, torch.float32, torch.bfloat16
+        z = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=device)
+        self.ctl = z(CTL_WORDS, dtype=i32)
+        self.ctl[Ctl.EOS] = -1
+        self.ctl[Ctl.STOP_POS] = -1
+        self.x = z(MAX_ROWS, H, dtype=bf)
+        self.seq = torch.ones(1, dtype=i32, device=device)
+        self.status = self.ctl[Ctl.STATUS : Ctl.STATUS + 1]
+        kw = {} if budget_ms is None else {"budget_ms": budget_ms}
+        self.channel = LLChannel(device, spec.tp, spec.rank, MAX_ROWS * H, group=group, seq=self.seq, status=self.status, **kw)
+        self.cp_channel = None
+        if cp and spec.cp_size > 1:
+            slots = MAX_ROWS * spec.q_heads * (cfg.head_dim + 1)
+            self.cp_channel = LLChannel(
+                device, spec.tp, spec.rank, slots, group=group, seq=self.seq, status=self.status, members=spec.cp_group, **kw
+            )
+        # gated delta net scratch
+        self.gdn_qkv = z(MAX_ROWS, max(spec.gdn_qkv_rows, 1))
+        self.gdn_z = z(MAX_ROWS, max(spec.gdn_local, 1))
+        self.gdn_beta = z(MAX_ROWS, max(spec.gdn_v, 1))
+        self.gdn_g = z(MAX_ROWS, max(spec.gdn_v, 1))
+        self.gdn_out = z(MAX_ROWS, max(spec.gdn_local, 1))
+        # attention scratch (sized for the context-parallel front: every q head of the kv group)
+        hd = cfg.head_dim
+        nq_max = spec.q_heads * (spec.cp_size if cp else 1)
+        self.q_raw = z(MAX_ROWS, nq_max, hd)
+        self.gate = z(MAX_ROWS, spec.q_heads, hd)
+        self.k_raw = z(MAX_ROWS, spec.kv_heads, hd)
+        self.attn_out = z(MAX_ROWS, spec.q_heads * hd)
+        self.n_splits = max(1, self.n_cta // spec.kv_heads)
+        rows_max = MAX_ROWS * (nq_max // spec.kv_heads)
+        self.ws_acc = z(spec.kv_heads, self.n_splits, rows_max, hd)
+        self.ws_ml = z(spec.kv_heads, self.n_splits, rows_max, 2)
+        self.attn_ticket = z(spec.kv_heads, dtype=i32)
+        half = cfg.rotary_dim // 2
+        self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rotary_dim, 2, dtype=f32) / cfg.rotary_dim))).to(device)
+        assert self.inv_freq.numel() == half
+        # mixture of experts scratch
+        S = cfg.top_k + 1
+        self.moe_logits = z(MAX_ROWS, cfg.n_experts + 1)
+        self.moe_ids = z(MAX_ROWS, S, dtype=i32)
+        self.moe_wts = z(MAX_ROWS, S)
+        self.moe_h = z(MAX_ROWS, S, spec.inter)
+        self.moe_ticket = z(1, dtype=i32)
+        # head scratch
+        self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)
+        self.head_ticket = z(1, dtype=i32)
+        self.head_export = z(MAX_ROWS, 64, dtype=i32)
+        self.sampling = z(8, dtype=torch.int64)
+        self.site = 0
+
+    # ---- site counting: one index per launch that touches an LL channel -----------------------
+    def begin_step(self) -> None:
+        self.site = 0
+
+    def next_site(self) -> int:
+        s = self.site
+        self.site += 1
+        return s
+
+    def stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream

@@ -1,0 +1,96 @@
+"""Single-GPU end-to-end numerics: the CUDA engine against the fp32 CPU oracle on the shrunk
+hybrid stack (one GDN layer, one gated-attention layer, MoE with shared expert, FP8 block-scaled
+weights) - the reference's tier-B/D strategy (block mains print relL2 against a torch reference,
+nex_n2_5_pro/gdn.py:327-408) reduced to a geometry that needs no checkpoint."""
+
+import pytest
+import torch
+
+from nexrt_b200.models.reference import RefModel, synthetic_prompt
+from nexrt_b200.testing import gather_logits, make_engine, shrunk_checkpoint
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+@pytest.fixture(scope="module")
+def setup():
+    cfg, ckpt = shrunk_checkpoint(0)
+    ref = RefModel(cfg, ckpt)
+    eng = make_engine(cfg, ckpt, max_rows=8)
+    eng.head.enable_logits()
+    return cfg, ref, eng
+
+
+def test_single_row_steps_match_oracle(setup):
+    cfg, ref, eng = setup
+    prompt = synthetic_prompt(cfg.vocab, 24, seed=1)
+    ref.reset()
+    eng.reset(first_token=prompt[0])
+    worst = 0.0
+    for t, tok in enumerate(prompt):
+        eng.set_rows([tok])
+        eng.set_forced_commit(1)
+        eng.step(1)
+        got = gather_logits(eng, 1)[0]
+        want = ref.step(tok)
+        worst = max(worst, rel_l2(got, want))
+        assert int(got.argmax()) == int(want.argmax()) or (want.max() - want[int(got.argmax())]) < 0.05
+    assert worst < 2e-2, worst
+    ctl = eng.read_ctl()
+    assert ctl["committed_len"] == len(prompt) and ctl["status"] == 0
+
+
+@pytest.mark.parametrize("rows", [4, 8])
+def test_multi_row_step_matches_sequential(setup, rows):
+    cfg, ref, eng = setup
+    prompt = synthetic_prompt(cfg.vocab, 3 * rows, seed=2)
+    ref.reset()
+    want = torch.stack([ref.step(t) for t in prompt])
+    eng.reset(first_token=prompt[0])
+    got = []
+    for i in range(0, len(prompt), rows):
+        eng.set_rows(prompt[i : i + rows])
+        eng.set_forced_commit(rows)
+        eng.step(rows)
+        got.append(gather_logits(eng, rows))
+    got = torch.cat(got)
+    assert rel_l2(got, want) < 2e-2
+    assert eng.read_ctl()["committed_len"] == len(prompt)
+
+
+def test_greedy_decode_config1(setup):
+    """BASELINE config 1 shape: random prompt, greedy decode, logits checked against fp32."""
+    cfg, ref, eng = setup
+    prompt = synthetic_prompt(cfg.vocab, 64, seed=1)
+    ref.reset()
+    toks_ref, logits_ref = ref.greedy(prompt, 8)
+    first = eng.prefill(prompt, chunk=8)
+    assert first == toks_ref[0]
+    out = eng.generate(max_new=7)
+    near_tie = 0
+    for i, (a, b) in enumerate(zip([first] + out, toks_ref)):
+        if a != b:
+            lg = logits_ref[i]
+            assert lg.max() - lg[a] < 0.05, (i, a, b)
+            near_tie += 1
+            break
+    assert near_tie <= 1
+
+
+def test_graph_replay_equals_eager(setup):
+    cfg, ref, eng = setup
+    prompt = synthetic_prompt(cfg.vocab, 16, seed=3)
+    first = eng.prefill(prompt, chunk=8)
+    state = eng.export_state()
+    eager = []
+    for _ in range(6):
+        eng.step(1)
+        eager.append(eng.read_ctl()["emitted"][0])
+    eng.load_prefill(state)
+    assert eng.read_ctl()["pending"] == first
+    graphed = eng.generate(max_new=6)
+    assert graphed == eager

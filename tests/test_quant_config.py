@@ -1,0 +1,95 @@
+"""Host-only checks of the quantiser, geometry, sharding and checkpoint layout."""
+
+import pytest
+import torch
+
+from nexrt_b200.config import ShardSpec, full_config, shrunk_config
+from nexrt_b200.quant import FP8_MAX, act_quant, dequantize_blockwise, fold_requant, quantize_blockwise
+from nexrt_b200.weights import load_checkpoint, normalise_scale_names, random_checkpoint, save_checkpoint, shard_model
+
+
+def test_block_quant_roundtrip_error():
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(256, 384, generator=g) * 0.02
+    q, s = quantize_blockwise(w)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (2, 3)
+    back = dequantize_blockwise(q, s)
+    assert float((back - w).abs().max()) <= float(w.abs().max()) / 16 + 1e-9
+    assert float(q.float().abs().max()) <= FP8_MAX
+
+
+def test_block_quant_ragged_edges():
+    w = torch.randn(130, 200)
+    q, s = quantize_blockwise(w)
+    assert q.shape == w.shape and s.shape == (2, 2)
+    assert torch.isfinite(dequantize_blockwise(q, s)).all()
+
+
+def test_fold_requant_matches_dequant_times_gamma():
+    w = torch.randn(128, 256) * 0.02
+    q, s = quantize_blockwise(w)
+    gamma = 1.0 + 0.1 * torch.randn(256)
+    q2, s2 = fold_requant(q, s, gamma)
+    want = dequantize_blockwise(q, s) * gamma
+    got = dequantize_blockwise(q2, s2)
+    assert float((got - want).norm() / want.norm()) < 0.05
+
+
+def test_act_quant_shapes():
+    x = torch.randn(3, 512)
+    q, s = act_quant(x)
+    assert q.shape == (3, 512) and s.shape == (3, 4)
+    with pytest.raises(ValueError):
+        act_quant(torch.randn(2, 100))
+
+
+def test_full_geometry_matches_reference_constants():
+    c = full_config()
+    assert (c.hidden, c.vocab, c.n_layers) == (4096, 248320, 60)
+    assert c.n_full == 15 and c.n_linear == 45
+    assert c.layer_types[3] == "full" and c.layer_types[0] == "linear"
+    assert c.cache_len == 256 * 1024 + 1024
+    s = ShardSpec(c, 8, 5)
+    assert (s.q_heads, s.kv_heads, s.kv_head0, s.cp_size, s.cp_rank) == (4, 1, 1, 4, 1)
+    assert s.gdn_front_rows == 2560 and s.attn_front_rows == 2560 and s.inter == 128 and s.vocab == 31040
+    assert s.cp_group == (4, 5, 6, 7)
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_shard_spec_parametric(tp):
+    c = full_config()
+    total_q = sum(ShardSpec(c, tp, r).q_heads for r in range(tp))
+    assert total_q == c.n_q_heads
+    assert ShardSpec(c, tp, 0).inter * tp == c.moe_inter
+    assert c.truncated(4).n_layers == 4
+
+
+def test_shrunk_config_limits():
+    c = shrunk_config()
+    assert c.supports_tp(2) and not c.supports_tp(4)
+    with pytest.raises(ValueError):
+        ShardSpec(c, 3, 0)
+
+
+def test_checkpoint_roundtrip_and_sharding(tmp_path):
+    cfg = shrunk_config()
+    ck = random_checkpoint(cfg, 0)
+    save_checkpoint(ck, cfg, tmp_path)
+    back = load_checkpoint(cfg, tmp_path)
+    assert set(back) == set(ck)
+    for k in ck:
+        assert torch.equal(back[k].view(torch.uint8) if back[k].dtype == torch.float8_e4m3fn else back[k],
+                           ck[k].view(torch.uint8) if ck[k].dtype == torch.float8_e4m3fn else ck[k])
+    # the other checkpoint spelling of the scale tensors is accepted
+    alias = {k[: -len("_inv")] if k.endswith("weight_scale_inv") else k: v for k, v in ck.items()}
+    m_alias = shard_model(alias, cfg, 2, 1, "cpu")
+    m = shard_model(ck, cfg, 2, 1, "cpu")
+    assert torch.equal(m["layers"][0]["mixer"]["front_s"], m_alias["layers"][0]["mixer"]["front_s"])
+    assert set(normalise_scale_names(alias)) == set(ck)
+    # shards tile the global tensors
+    s0, s1 = shard_model(ck, cfg, 2, 0, "cpu"), m
+    o = ck["model.language_model.layers.1.self_attn.o_proj.weight"].view(torch.uint8)
+    got = torch.cat([s0["layers"][1]["mixer"]["out_w"].view(torch.uint8), s1["layers"][1]["mixer"]["out_w"].view(torch.uint8)], 1)
+    assert torch.equal(got, o)
+    assert s0["layers"][0]["moe"]["w13"].shape == (cfg.n_experts + 1, 2 * 128, cfg.hidden)
+    assert s0["head"]["lm_head"].shape == (cfg.vocab // 2, cfg.hidden)
