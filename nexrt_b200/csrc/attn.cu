@@ -42,14 +42,15 @@ struct AttnFrontArgs {
 // query heads come first and the ngate gate heads after them; then k heads, then v heads.
 template <int MB>
 __global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
+    constexpr int NR = MB == 1 ? 4 : 2;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int R = (a.nq + a.ngate + 2 * a.kvh) * a.hd;
     int t0, t1;
-    cta_range(R / 2, blockIdx.x, gridDim.x, &t0, &t1);
-    if (t1 > t0) prefetch_l2_range(a.w + static_cast<size_t>(t0) * 2 * a.H, static_cast<size_t>(t1 - t0) * 2 * a.H);
+    cta_range(R / NR, blockIdx.x, gridDim.x, &t0, &t1);
+    if (t1 > t0) prefetch_l2_range(a.w + static_cast<size_t>(t0) * NR * a.H, static_cast<size_t>(t1 - t0) * NR * a.H);
     pdl_wait();
     const int C0 = a.ctl[kCtlCommittedLen];
     const int KB = a.H / kScaleBlock;
@@ -59,16 +60,26 @@ __global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
         if (m0) __syncthreads();
         stage_rmsnorm<16>(smem, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
         for (int t = t0 + warp; t < t1; t += nwarps) {
-            const int r = t * 2;
-            const uint8_t* w[2] = {a.w + static_cast<size_t>(r) * a.H, a.w + static_cast<size_t>(r + 1) * a.H};
-            const float* s[2] = {a.s + (r / kScaleBlock) * KB, a.s + ((r + 1) / kScaleBlock) * KB};
-            float acc[2][MB];
-            gemv_fp8<MB, 2, 32>(w, s, a.H, smem, lane, acc);
-            if (lane < 2) {
+            const int r = t * NR;
+            const uint8_t* w[NR];
+            const float* s[NR];
+#pragma unroll
+            for (int n = 0; n < NR; ++n) {
+                w[n] = a.w + static_cast<size_t>(r + n) * a.H;
+                s[n] = a.s + ((r + n) / kScaleBlock) * KB;
+            }
+            float acc[NR][MB];
+            gemv_fp8<MB, NR, 32>(w, s, a.H, smem, lane, acc);
+            if (lane < NR) {
                 const int row = r + lane;
                 const int head = row / a.hd, d = row % a.hd;
-                for (int m = 0; m < mb; ++m) {
-                    const float v = lane == 0 ? acc[0][m] : acc[1][m];
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    if (m >= mb) break;
+                    float v = acc[0][m];
+#pragma unroll
+                    for (int n = 1; n < NR; ++n)
+                        if (lane == n) v = acc[n][m];
                     const int mm = m0 + m;
                     if (head < a.nq + a.ngate) {
                         int qh, is_gate;
@@ -279,19 +290,50 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     __threadfence();
     const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
     const float* base_ml = a.ws_ml + static_cast<size_t>(kv) * a.n_splits * rows * 2;
-    LLCall call;
+    LLCall call{0u, 0u};
     if (a.cp_size > 1) call = ll_begin(a.ch, a.site);
+    // stage the (max, sum) pairs, turn them into per-(row, split) scales, then stream the partials
+    float* sc = smem;                                        // [rows][n_active] scale of each split
+    float* sl = sc + static_cast<size_t>(rows) * n_active;   // [rows][n_active] l, then [rows] totals
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * n_active; idx += blockDim.x) {
+        const int r = idx / n_active, sp = idx % n_active;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(base_ml + (static_cast<size_t>(sp) * rows + r) * 2));
+        sc[idx] = ml.x;
+        sl[idx] = ml.y;
+    }
+    __syncthreads();
+    float* rowM = sl + static_cast<size_t>(rows) * n_active;  // [rows] max
+    float* rowL = rowM + rows;                                // [rows] total sum
+    for (int r = warp; r < rows; r += NW) {
+        float mxv = -INFINITY;
+        for (int sp = lane; sp < n_active; sp += 32) mxv = fmaxf(mxv, sc[r * n_active + sp]);
+        mxv = warp_max(mxv);
+        float lsum = 0.f;
+        for (int sp = lane; sp < n_active; sp += 32) {
+            const float m_ = sc[r * n_active + sp];
+            const float w_ = m_ == -INFINITY ? 0.f : exp2f(m_ - mxv);
+            sc[r * n_active + sp] = w_;
+            lsum = fmaf(sl[r * n_active + sp], w_, lsum);
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) { rowM[r] = mxv; rowL[r] = lsum; }
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < rows * HD; idx += blockDim.x) {
         const int r = idx / HD, d = idx % HD;
-        float M_ = -INFINITY;
-        for (int s = 0; s < n_active; ++s) M_ = fmaxf(M_, __ldcg(base_ml + (static_cast<size_t>(s) * rows + r) * 2));
-        float L_ = 0.f, A_ = 0.f;
-        for (int s = 0; s < n_active; ++s) {
-            const float ms = __ldcg(base_ml + (static_cast<size_t>(s) * rows + r) * 2);
-            const float sc = ms == -INFINITY ? 0.f : exp2f(ms - M_);
-            L_ = fmaf(__ldcg(base_ml + (static_cast<size_t>(s) * rows + r) * 2 + 1), sc, L_);
-            A_ = fmaf(__ldcg(base_acc + (static_cast<size_t>(s) * rows + r) * HD + d), sc, A_);
+        const float* pa = base_acc + static_cast<size_t>(r) * HD + d;
+        const size_t stride = static_cast<size_t>(rows) * HD;
+        float A_ = 0.f;
+        int sp = 0;
+        for (; sp + 4 <= n_active; sp += 4) {
+            const float a0 = __ldcg(pa + sp * stride), a1 = __ldcg(pa + (sp + 1) * stride);
+            const float a2 = __ldcg(pa + (sp + 2) * stride), a3 = __ldcg(pa + (sp + 3) * stride);
+            const float* w_ = sc + r * n_active + sp;
+            A_ = fmaf(a0, w_[0], A_); A_ = fmaf(a1, w_[1], A_); A_ = fmaf(a2, w_[2], A_); A_ = fmaf(a3, w_[3], A_);
         }
+        for (; sp < n_active; ++sp) A_ = fmaf(__ldcg(pa + sp * stride), sc[r * n_active + sp], A_);
+        const float L_ = rowL[r], M_ = rowM[r];
         const int m = r / G, hg = r % G;   // head inside the kv group
         const float ctx = L_ > 0.f ? A_ / L_ : 0.f;
         if (a.cp_size == 1) {
@@ -305,7 +347,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             const unsigned int slot = (static_cast<unsigned int>(m) * a.ngate + lh) * (HD + 1) + d;
             const float lse = L_ > 0.f ? M_ + log2f(L_) : -INFINITY;
             ll_send(a.ch, call, owner, slot, __float_as_uint(ctx));
-            if (d == 0) ll_send(a.ch, call, owner, slot - d + HD, __float_as_uint(lse));
+            if (d == 0) ll_send(a.ch, call, owner, slot + HD, __float_as_uint(lse));
         }
     }
     if (threadIdx.x == 0) a.ticket[kv] = 0;
@@ -329,7 +371,10 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
 
 extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
     const size_t rows = static_cast<size_t>(M) * (nq / kvh);
-    return sizeof(float) * (rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPass * (hd + 2));
+    const size_t main_floats = rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPass * (hd + 2);
+    const size_t n_sm = 160;  // upper bound of splits per kv head
+    const size_t combine_floats = rows * n_sm * 2 + 2 * rows;
+    return sizeof(float) * (main_floats > combine_floats ? main_floats : combine_floats);
 }
 
 extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
@@ -338,6 +383,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
                                  int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream) {
     if (M < 1 || M > kMaxRows || nq % kvh || rotary > 64 || rotary % 2) return cudaErrorInvalidValue;
     if (cp_size > 1 && ch == nullptr) return cudaErrorInvalidValue;
+    if (n_splits > 160) return cudaErrorInvalidValue;
     AttnDecodeArgs a{};
     a.q_raw = static_cast<const float*>(q_raw); a.gate = static_cast<const float*>(gate); a.k_raw = static_cast<const float*>(k_raw);
     a.qn = static_cast<const float*>(qn); a.kn = static_cast<const float*>(kn); a.inv_freq = static_cast<const float*>(inv_freq);

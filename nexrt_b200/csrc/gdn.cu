@@ -40,16 +40,17 @@ struct GdnFrontArgs {
 
 template <int MB>
 __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
+    constexpr int NR = MB == 1 ? 4 : 2;   // fp8 rows a warp streams together
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    // tasks: nv (b,a) pairs first, then R/2 pairs of fp8 rows
-    const int n_tasks = a.nv + a.R / 2;
+    // tasks: nv (b,a) pairs first, then R/NR groups of fp8 rows
+    const int n_tasks = a.nv + a.R / NR;
     int t0, t1;
     cta_range(n_tasks, blockIdx.x, gridDim.x, &t0, &t1);
     {
-        const int r0 = max(t0 - a.nv, 0) * 2, r1 = max(t1 - a.nv, 0) * 2;
+        const int r0 = max(t0 - a.nv, 0) * NR, r1 = max(t1 - a.nv, 0) * NR;
         if (r1 > r0) prefetch_l2_range(a.front_w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(r1 - r0) * a.H);
     }
     pdl_wait();
@@ -60,8 +61,8 @@ __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
         if (m0) __syncthreads();
         stage_rmsnorm<16>(smem, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
         for (int t = t0 + warp; t < t1; t += nwarps) {
-            float acc[2][MB];
             if (t < a.nv) {
+                float acc[2][MB];
                 const __nv_bfloat16* w[2] = {a.ba_w + static_cast<size_t>(t) * a.H, a.ba_w + static_cast<size_t>(a.nv + t) * a.H};
                 gemv_bf16<MB, 2, 16>(w, a.H, smem, lane, acc);
                 if (lane == 0) {
@@ -72,15 +73,26 @@ __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
                     }
                 }
             } else {
-                const int r = (t - a.nv) * 2;
-                const uint8_t* w[2] = {a.front_w + static_cast<size_t>(r) * a.H, a.front_w + static_cast<size_t>(r + 1) * a.H};
-                const float* s[2] = {a.front_s + (r / kScaleBlock) * KB, a.front_s + ((r + 1) / kScaleBlock) * KB};
-                gemv_fp8<MB, 2, 32>(w, s, a.H, smem, lane, acc);
-                if (lane < 2) {
+                float acc[NR][MB];
+                const int r = (t - a.nv) * NR;
+                const uint8_t* w[NR];
+                const float* s[NR];
+#pragma unroll
+                for (int n = 0; n < NR; ++n) {
+                    w[n] = a.front_w + static_cast<size_t>(r + n) * a.H;
+                    s[n] = a.front_s + ((r + n) / kScaleBlock) * KB;
+                }
+                gemv_fp8<MB, NR, 32>(w, s, a.H, smem, lane, acc);
+                if (lane < NR) {
                     const int row = r + lane;
                     float pre[MB];
 #pragma unroll
-                    for (int m = 0; m < MB; ++m) pre[m] = lane == 0 ? acc[0][m] : acc[1][m];
+                    for (int m = 0; m < MB; ++m) {
+                        pre[m] = acc[0][m];
+#pragma unroll
+                        for (int n = 1; n < NR; ++n)
+                            if (lane == n) pre[m] = acc[n][m];
+                    }
                     if (row < a.C) {
                         const float4 cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
                         const int ring = a.conv_ring_len;
@@ -157,7 +169,7 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
                                const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv,
                                void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, float eps, int n_cta,
                                void* stream) {
-    if (M < 1 || M > kMaxRows || H % 512 || R % 2 || C % 2 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
+    if (M < 1 || M > kMaxRows || H % 512 || R % 4 || C % 4 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
     GdnFrontArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(in_ln), static_cast<const uint8_t*>(front_w),
                    static_cast<const float*>(front_s), static_cast<const __nv_bfloat16*>(ba_w), static_cast<const float*>(conv_w),
                    static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), static_cast<const int*>(ctl),

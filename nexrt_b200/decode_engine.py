@@ -210,6 +210,7 @@ class DecodeEngine:
         eos: Optional[int] = None,
         cp_threshold: int = CP_THRESHOLD,
         on_tokens: Optional[Callable[[List[int]], None]] = None,
+        host_inputs: Optional[torch.Tensor] = None,
     ) -> List[int]:
         """Greedy / sampled decode of up to ``max_new`` tokens by graph replay.
 
@@ -226,6 +227,8 @@ class DecodeEngine:
         out: List[int] = []
 
         def launch(pos: int) -> int:
+            if host_inputs is not None:  # per-step upload of the request's sampling words (pinned host memory)
+                self.ctx.sampling.copy_(host_inputs, non_blocking=True)
             (g_cp if (g_cp is not None and pos >= cp_threshold) else g_noncp).replay()
             return self.mirror.next_gen()
 

@@ -1,0 +1,52 @@
+"""Run a few eager decode steps of a random-init model at a chosen context length without a real
+prefill (the committed length is simply set, the KV cache holds zeros): a timing fixture for
+profilers, like the reference's ``slot[1]`` override (``nex_n2_5_pro/decode_engine.py:687-723``).
+
+    python -m nexrt_b200.utils.profile_step --layers 4 --ctx 1024 --steps 3 --rows 1
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+
+import torch
+
+
+def main() -> None:
+    p = argparse.ArgumentParser()
+    p.add_argument("--layers", type=int, default=4)
+    p.add_argument("--ctx", type=int, default=1024)
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--rows", type=int, default=1)
+    p.add_argument("--shrunk", action="store_true")
+    p.add_argument("--graph", action="store_true", help="time captured-graph replays and print us/step")
+    a = p.parse_args()
+    from ..config import full_config, shrunk_config
+    from ..decode_engine import DecodeEngine
+    from ..runtime.control import Ctl
+    from ..weights import random_rank_model
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = shrunk_config() if a.shrunk else full_config().truncated(a.layers)
+    model = random_rank_model(cfg, 1, 0, dev)
+    eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, max_rows=max(a.rows, 1), cache_len=a.ctx + 64 * a.rows + 1024)
+    eng.reset(first_token=1, committed_len=a.ctx)
+    eng.set_rows(list(range(1, a.rows + 1)))
+    eng.set_forced_commit(a.rows)
+    if a.graph:
+        from .bench import bench_graph
+
+        g = eng.capture(a.rows)
+        r = bench_graph(g, a.steps, warmup=5, device=dev)
+        print(f"rows={a.rows} ctx={a.ctx} layers={cfg.n_layers}: {r['ms_per_replay'] * 1e3:.1f} us/step")
+    else:
+        for _ in range(a.steps):
+            eng.step(a.rows)
+        torch.cuda.synchronize()
+    print("status", int(eng.ctx.ctl[Ctl.STATUS]))
+
+
+if __name__ == "__main__":
+    main()

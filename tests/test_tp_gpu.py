@@ -1,0 +1,30 @@
+"""Tensor-parallel engine on 2 GPUs as child processes (torchrun, NCCL bootstrap, in-kernel LL
+all-reduce over symmetric memory), with NVSwitch multicast and with plain peer stores."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world, env_extra, port):
+    env = dict(os.environ, **env_extra)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "tp_worker.py")]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+
+
+@pytest.mark.parametrize("mode", ["auto", "peer-stores"])
+def test_tp2_matches_oracle(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    extra = {"NEXRT_WAIT_BUDGET_MS": "5000"}
+    if mode == "peer-stores":
+        extra.update(NEXRT_NO_MULTICAST="1", NCCL_NVLS_ENABLE="0")
+    r = _run(2, extra, 29611 if mode == "auto" else 29612)
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -1,0 +1,88 @@
+"""Child process of the multi-GPU tests: one rank of a tensor-parallel engine over the shrunk
+model, checked against the fp32 CPU oracle.  Launched by torchrun from test_tp_gpu.py."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from nexrt_b200.models.reference import RefModel, synthetic_prompt  # noqa: E402
+from nexrt_b200.testing import make_engine, shrunk_checkpoint  # noqa: E402
+
+
+def rel_l2(a, b):
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg, ckpt = shrunk_checkpoint(0)
+    ref = RefModel(cfg, ckpt)
+    eng = make_engine(cfg, ckpt, rank=rank, world=world, device=dev, max_rows=8)
+    eng.head.enable_logits()
+    V = cfg.vocab // world
+    sl = slice(rank * V, (rank + 1) * V)
+    print(f"[rank {rank}] symm={eng.ctx.channel.buf.backend} multicast={eng.ctx.channel.multicast}", flush=True)
+
+    # single-row steps
+    prompt = synthetic_prompt(cfg.vocab, 12, seed=1)
+    ref.reset()
+    eng.reset(first_token=prompt[0])
+    for tok in prompt:
+        eng.set_rows([tok])
+        eng.set_forced_commit(1)
+        eng.step(1)
+        torch.cuda.synchronize()
+        got = eng.head.logits[0].float().cpu()
+        want = ref.step(tok)[sl]
+        assert rel_l2(got, want) < 2e-2, rel_l2(got, want)
+    assert eng.status_max() == 0
+    # the residual stream is bitwise identical on every rank
+    xs = [torch.empty_like(eng.ctx.x) for _ in range(world)]
+    dist.all_gather(xs, eng.ctx.x)
+    assert all(torch.equal(xs[0].view(torch.int16), t.view(torch.int16)) for t in xs)
+
+    # multi-row steps
+    for rows in (4, 8):
+        p2 = synthetic_prompt(cfg.vocab, 2 * rows, seed=5)
+        ref.reset()
+        want = torch.stack([ref.step(t) for t in p2])[:, sl]
+        eng.reset(first_token=p2[0])
+        got = []
+        for i in range(0, len(p2), rows):
+            eng.set_rows(p2[i : i + rows])
+            eng.set_forced_commit(rows)
+            eng.step(rows)
+            torch.cuda.synchronize()
+            got.append(eng.head.logits[:rows].float().cpu())
+        assert rel_l2(torch.cat(got), want) < 2e-2
+
+    # prefill + captured-graph generate: every rank emits the same stream, equal to the oracle's
+    prompt = synthetic_prompt(cfg.vocab, 32, seed=1)
+    ref.reset()
+    toks_ref, logits_ref = ref.greedy(prompt, 8)
+    first = eng.prefill(prompt, chunk=8)
+    out = [first] + eng.generate(max_new=7)
+    t = torch.tensor(out, device=dev)
+    allt = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(allt, t)
+    assert all(torch.equal(allt[0], u) for u in allt), allt
+    for i, (a, b) in enumerate(zip(out, toks_ref)):
+        if a != b:
+            assert logits_ref[i].max() - logits_ref[i][a] < 0.05, (i, a, b)
+            break
+    assert eng.status_max() == 0
+    dist.barrier()
+    if rank == 0:
+        print("TP_WORKER_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
