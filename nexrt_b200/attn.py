@@ -58,7 +58,7 @@ class FullAttn:
             ),
             "attn_decode",
         )
-        n_cta = min(c.n_cta, cfg.hidden // 32)
+        n_cta = c.n_cta
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.attn_out), ptr(c.gate), None, ptr(self.w["out_w"]), ptr(self.w["out_s"]), ptr(c.x), cfg.hidden, spec.attn_local, M,

@@ -59,10 +59,10 @@ int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, co
 /* mixture of experts */
 int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket, int H, int E,
                      int topk, int M, float eps, int n_cta, void* stream);
-int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, const void* wts, void* h, int H,
-                 int I, int S, int M, float eps, int shared_expert, int n_cta, void* stream);
-int nexrt_moe_l2_allreduce(const void* h, const void* ids, const void* w2, const void* w2_s, void* x, int H, int I, int S, int M,
-                           const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
+int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I, int S, int M,
+                 float eps, int shared_expert, int n_cta, void* stream);
+int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I, int S,
+                           int M, const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
 
 /* LM head, distributed top-k, sampler, accept / commit */
 int nexrt_lmhead_sample(const void* x, const void* final_ln, const void* w, void* logits_out, void* cand, void* ticket, const void* sampling,

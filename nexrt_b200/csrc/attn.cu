@@ -19,6 +19,7 @@
 // (locally normalised context + log2-domain LSE) which it sends to the rank that owns each head.
 #include "api.h"
 #include "gemv.cuh"
+#include "gemv_cta.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -42,58 +43,42 @@ struct AttnFrontArgs {
 // query heads come first and the ngate gate heads after them; then k heads, then v heads.
 template <int MB>
 __global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
-    constexpr int NR = MB == 1 ? 4 : 2;
+    constexpr int U = MB == 1 ? 8 : 4;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int R = (a.nq + a.ngate + 2 * a.kvh) * a.hd;
-    int t0, t1;
-    cta_range(R / NR, blockIdx.x, gridDim.x, &t0, &t1);
-    if (t1 > t0) prefetch_l2_range(a.w + static_cast<size_t>(t0) * NR * a.H, static_cast<size_t>(t1 - t0) * NR * a.H);
+    int r0, r1;
+    cta_range(R, blockIdx.x, gridDim.x, &r0, &r1);
+    const int nrows = r1 - r0;
+    if (nrows) prefetch_l2_range(a.w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(nrows) * a.H);
+    const GemvGeom gf = gemv_geom(a.H / 16, blockDim.x);
+    float* xs = smem;
+    float* part = xs + static_cast<size_t>(MB) * a.H;
     pdl_wait();
     const int C0 = a.ctl[kCtlCommittedLen];
-    const int KB = a.H / kScaleBlock;
     const bool interleaved = a.ngate == a.nq;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm<16>(smem, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
-        for (int t = t0 + warp; t < t1; t += nwarps) {
-            const int r = t * NR;
-            const uint8_t* w[NR];
-            const float* s[NR];
-#pragma unroll
-            for (int n = 0; n < NR; ++n) {
-                w[n] = a.w + static_cast<size_t>(r + n) * a.H;
-                s[n] = a.s + ((r + n) / kScaleBlock) * KB;
-            }
-            float acc[NR][MB];
-            gemv_fp8<MB, NR, 32>(w, s, a.H, smem, lane, acc);
-            if (lane < NR) {
-                const int row = r + lane;
-                const int head = row / a.hd, d = row % a.hd;
-#pragma unroll
-                for (int m = 0; m < MB; ++m) {
-                    if (m >= mb) break;
-                    float v = acc[0][m];
-#pragma unroll
-                    for (int n = 1; n < NR; ++n)
-                        if (lane == n) v = acc[n][m];
-                    const int mm = m0 + m;
-                    if (head < a.nq + a.ngate) {
-                        int qh, is_gate;
-                        if (interleaved) { qh = head >> 1; is_gate = head & 1; }
-                        else { is_gate = head >= a.nq; qh = is_gate ? head - a.nq : head; }
-                        if (is_gate) a.gate[(static_cast<size_t>(mm) * a.ngate + qh) * a.hd + d] = v;
-                        else a.q_raw[(static_cast<size_t>(mm) * a.nq + qh) * a.hd + d] = v;
-                    } else if (head < a.nq + a.ngate + a.kvh) {
-                        a.k_raw[(static_cast<size_t>(mm) * a.kvh + (head - a.nq - a.ngate)) * a.hd + d] = v;
-                    } else {
-                        const int kv = head - a.nq - a.ngate - a.kvh;
-                        a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
-                    }
-                }
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
+        gemv_cta<MB, U>(PlainFp8{a.w, a.s, a.H}, r0, nrows, xs, a.H, part);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
+            const int rl = idx / mb, m = idx % mb, row = r0 + rl, mm = m0 + m;
+            const float v = gemv_result(part, rl, m, MB, gf.wpr);
+            const int head = row / a.hd, d = row % a.hd;
+            if (head < a.nq + a.ngate) {
+                int qh, is_gate;
+                if (interleaved) { qh = head >> 1; is_gate = head & 1; }
+                else { is_gate = head >= a.nq; qh = is_gate ? head - a.nq : head; }
+                if (is_gate) a.gate[(static_cast<size_t>(mm) * a.ngate + qh) * a.hd + d] = v;
+                else a.q_raw[(static_cast<size_t>(mm) * a.nq + qh) * a.hd + d] = v;
+            } else if (head < a.nq + a.ngate + a.kvh) {
+                a.k_raw[(static_cast<size_t>(mm) * a.kvh + (head - a.nq - a.ngate)) * a.hd + d] = v;
+            } else {
+                const int kv = head - a.nq - a.ngate - a.kvh;
+                a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
             }
         }
     }
@@ -360,13 +345,16 @@ using namespace nexrt;
 extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void* s, const void* ctl, void* q_raw, void* gate,
                                 void* k_raw, void* v_cache, int H, int hd, int nq, int ngate, int kvh, int M, int cache_len, float eps,
                                 int n_cta, void* stream) {
-    if (M < 1 || M > kMaxRows || H % 512 || (hd != 128 && hd != 256)) return cudaErrorInvalidValue;
+    if (M < 1 || M > kMaxRows || H % 256 || (hd != 128 && hd != 256)) return cudaErrorInvalidValue;
     AttnFrontArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(in_ln), static_cast<const uint8_t*>(w),
                     static_cast<const float*>(s), static_cast<const int*>(ctl), static_cast<float*>(q_raw), static_cast<float*>(gate),
                     static_cast<float*>(k_raw), static_cast<__nv_bfloat16*>(v_cache), H, hd, nq, ngate, kvh, M, cache_len, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (M == 1) return launch(attn_front_kernel<1>, dim3(n_cta), dim3(512), sizeof(float) * H, st, a);
-    return launch(attn_front_kernel<4>, dim3(n_cta), dim3(512), sizeof(float) * 4 * H, st, a);
+    const int mb = M == 1 ? 1 : 4;
+    const int R = (nq + ngate + 2 * kvh) * hd;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats((R + n_cta - 1) / n_cta, mb, gemv_geom(H / 16, 512)));
+    if (M == 1) return launch(attn_front_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
+    return launch(attn_front_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
 }
 
 extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {

@@ -16,6 +16,7 @@
 // in place, so rejected rows need no rollback.
 #include "api.h"
 #include "gemv.cuh"
+#include "gemv_cta.cuh"
 
 namespace nexrt {
 
@@ -40,81 +41,64 @@ struct GdnFrontArgs {
 
 template <int MB>
 __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
-    constexpr int NR = MB == 1 ? 4 : 2;   // fp8 rows a warp streams together
+    constexpr int U = MB == 1 ? 8 : 4;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    // tasks: nv (b,a) pairs first, then R/NR groups of fp8 rows
-    const int n_tasks = a.nv + a.R / NR;
-    int t0, t1;
-    cta_range(n_tasks, blockIdx.x, gridDim.x, &t0, &t1);
-    {
-        const int r0 = max(t0 - a.nv, 0) * NR, r1 = max(t1 - a.nv, 0) * NR;
-        if (r1 > r0) prefetch_l2_range(a.front_w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(r1 - r0) * a.H);
-    }
+    int r0, r1, b0, b1;
+    cta_range(a.R, blockIdx.x, gridDim.x, &r0, &r1);
+    cta_range(2 * a.nv, blockIdx.x, gridDim.x, &b0, &b1);
+    const int nrows = r1 - r0, nba = b1 - b0;
+    if (nrows) prefetch_l2_range(a.front_w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(nrows) * a.H);
+    const GemvGeom gf = gemv_geom(a.H / 16, blockDim.x), gb = gemv_geom(a.H / 8, blockDim.x);
+    float* xs = smem;                                                   // [MB][H]
+    float* part = xs + static_cast<size_t>(MB) * a.H;                   // fp8 rows
+    float* part_ba = part + gemv_part_floats((a.R + gridDim.x - 1) / gridDim.x, MB, gf);
     pdl_wait();
     const int C0 = a.ctl[kCtlCommittedLen];
-    const int KB = a.H / kScaleBlock;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm<16>(smem, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
-        for (int t = t0 + warp; t < t1; t += nwarps) {
-            if (t < a.nv) {
-                float acc[2][MB];
-                const __nv_bfloat16* w[2] = {a.ba_w + static_cast<size_t>(t) * a.H, a.ba_w + static_cast<size_t>(a.nv + t) * a.H};
-                gemv_bf16<MB, 2, 16>(w, a.H, smem, lane, acc);
-                if (lane == 0) {
-                    const float A = -__expf(a.a_log[t]), dt = a.dt_bias[t];
-                    for (int m = 0; m < mb; ++m) {
-                        a.beta[(m0 + m) * a.nv + t] = sigmoid_f(acc[0][m]);
-                        a.g[(m0 + m) * a.nv + t] = A * softplus_f(acc[1][m] + dt);
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
+        gemv_cta<MB, U>(PlainFp8{a.front_w, a.front_s, a.H}, r0, nrows, xs, a.H, part);
+        if (nba) gemv_cta<MB, 2>(PlainBf16{a.ba_w, a.H}, b0, nba, xs, a.H, part_ba);
+        __syncthreads();
+        for (int rl = threadIdx.x; rl < nrows; rl += blockDim.x) {
+            const int row = r0 + rl;
+            float pre[MB];
+#pragma unroll
+            for (int m = 0; m < MB; ++m) pre[m] = gemv_result(part, rl, m, MB, gf.wpr);
+            if (row < a.C) {
+                const float4 cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
+                const int ring = a.conv_ring_len;
+                for (int m = 0; m < mb; ++m) {
+                    const int p = C0 + m0 + m;
+                    a.conv_ring[static_cast<size_t>(p % ring) * a.C + row] = pre[m];
+                }
+                for (int m = 0; m < mb; ++m) {
+                    const int p = C0 + m0 + m;
+                    // taps at positions p-3..p; slots of positions before the sequence start hold zero
+                    float h[3];
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) {
+                        const int mm = m - 3 + j;
+                        h[j] = (mm >= 0) ? pre[mm < 0 ? 0 : mm] : a.conv_ring[static_cast<size_t>((p - 3 + j + ring) % ring) * a.C + row];
                     }
+                    const float v = fmaf(cw.x, h[0], fmaf(cw.y, h[1], fmaf(cw.z, h[2], cw.w * pre[m])));
+                    a.qkv[static_cast<size_t>(m0 + m) * a.C + row] = silu_f(v);
                 }
             } else {
-                float acc[NR][MB];
-                const int r = (t - a.nv) * NR;
-                const uint8_t* w[NR];
-                const float* s[NR];
-#pragma unroll
-                for (int n = 0; n < NR; ++n) {
-                    w[n] = a.front_w + static_cast<size_t>(r + n) * a.H;
-                    s[n] = a.front_s + ((r + n) / kScaleBlock) * KB;
-                }
-                gemv_fp8<MB, NR, 32>(w, s, a.H, smem, lane, acc);
-                if (lane < NR) {
-                    const int row = r + lane;
-                    float pre[MB];
-#pragma unroll
-                    for (int m = 0; m < MB; ++m) {
-                        pre[m] = acc[0][m];
-#pragma unroll
-                        for (int n = 1; n < NR; ++n)
-                            if (lane == n) pre[m] = acc[n][m];
-                    }
-                    if (row < a.C) {
-                        const float4 cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
-                        const int ring = a.conv_ring_len;
-                        for (int m = 0; m < mb; ++m) {
-                            const int p = C0 + m0 + m;
-                            a.conv_ring[static_cast<size_t>(p % ring) * a.C + row] = pre[m];
-                        }
-                        for (int m = 0; m < mb; ++m) {
-                            const int p = C0 + m0 + m;
-                            // taps at positions p-3..p; slots of positions before the sequence start hold zero
-                            float h[3];
-#pragma unroll
-                            for (int j = 0; j < 3; ++j) {
-                                const int mm = m - 3 + j;
-                                h[j] = (mm >= 0) ? pre[mm < 0 ? 0 : mm] : a.conv_ring[static_cast<size_t>((p - 3 + j + ring) % ring) * a.C + row];
-                            }
-                            const float v = fmaf(cw.x, h[0], fmaf(cw.y, h[1], fmaf(cw.z, h[2], cw.w * pre[m])));
-                            a.qkv[static_cast<size_t>(m0 + m) * a.C + row] = silu_f(v);
-                        }
-                    } else {
-                        for (int m = 0; m < mb; ++m) a.z[static_cast<size_t>(m0 + m) * (a.R - a.C) + (row - a.C)] = pre[m];
-                    }
+                for (int m = 0; m < mb; ++m) a.z[static_cast<size_t>(m0 + m) * (a.R - a.C) + (row - a.C)] = pre[m];
+            }
+        }
+        for (int rl = threadIdx.x; rl < nba; rl += blockDim.x) {
+            const int row = b0 + rl;     // [0, nv): b rows, [nv, 2nv): a rows
+            for (int m = 0; m < mb; ++m) {
+                const float v = gemv_result(part_ba, rl, m, MB, gb.wpr);
+                if (row < a.nv) a.beta[(m0 + m) * a.nv + row] = sigmoid_f(v);
+                else {
+                    const int h = row - a.nv;
+                    a.g[(m0 + m) * a.nv + h] = -__expf(a.a_log[h]) * softplus_f(v + a.dt_bias[h]);
                 }
             }
         }
@@ -169,15 +153,18 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
                                const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv,
                                void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, float eps, int n_cta,
                                void* stream) {
-    if (M < 1 || M > kMaxRows || H % 512 || R % 4 || C % 4 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
+    if (M < 1 || M > kMaxRows || H % 256 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
     GdnFrontArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(in_ln), static_cast<const uint8_t*>(front_w),
                    static_cast<const float*>(front_s), static_cast<const __nv_bfloat16*>(ba_w), static_cast<const float*>(conv_w),
                    static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), static_cast<const int*>(ctl),
                    static_cast<float*>(conv_ring), static_cast<float*>(qkv), static_cast<float*>(z), static_cast<float*>(beta),
                    static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (M == 1) return launch(gdn_front_kernel<1>, dim3(n_cta), dim3(512), sizeof(float) * H, st, a);
-    return launch(gdn_front_kernel<4>, dim3(n_cta), dim3(512), sizeof(float) * 4 * H, st, a);
+    const int mb = M == 1 ? 1 : 4;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats((R + n_cta - 1) / n_cta, mb, gemv_geom(H / 16, 512)) +
+                                         gemv_part_floats((2 * nv + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, 512)));
+    if (M == 1) return launch(gdn_front_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
+    return launch(gdn_front_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
 }
 
 extern "C" int nexrt_gdn_core(const void* qkv, const void* beta, const void* g, const void* ctl, void* state_ring, void* out, int nqk, int nv,

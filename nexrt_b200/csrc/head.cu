@@ -18,6 +18,7 @@
 // plain integer max picks the largest logit and, on ties, the lowest token id.
 #include "api.h"
 #include "gemv.cuh"
+#include "gemv_cta.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -212,31 +213,30 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     cta_range(a.V_local, blockIdx.x, gridDim.x, &v0, &v1);
     const int nv = v1 - v0, nv_max = (a.V_local + gridDim.x - 1) / gridDim.x;
     if (nv) prefetch_l2_range(a.w + static_cast<size_t>(v0) * a.H, static_cast<size_t>(nv) * a.H * 2);
+    constexpr int kTile = 256;                                                          // rows per GEMV tile
+    const GemvGeom gg = gemv_geom(a.H / 8, blockDim.x);
     float* xs = smem;                                                                   // [MB][H]
-    unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem + static_cast<size_t>(MB) * a.H);   // [MB][nv_max]
+    float* part = xs + static_cast<size_t>(MB) * a.H;                                   // [kTile][wpr][MB]
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(part + gemv_part_floats(kTile, MB, gg));   // [MB][nv_max]
     pdl_wait();
     const SamplingCfg cfg = read_sampling(a.sampling);
     const int K = a.mode == 2 ? 1 : cfg.top_k;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm<8>(xs, a.x + static_cast<size_t>(m0) * a.H, a.final_ln, mb, a.H, a.eps, red);
-        for (int t = warp * 2; t < nv; t += nwarps * 2) {
-            const int ra = v0 + t, rb = min(v0 + t + 1, v1 - 1);
-            const __nv_bfloat16* w[2] = {a.w + static_cast<size_t>(ra) * a.H, a.w + static_cast<size_t>(rb) * a.H};
-            float acc[2][MB];
-            gemv_bf16<MB, 2, 8>(w, a.H, xs, lane, acc);
-            if (lane == 0)
-                for (int m = 0; m < mb; ++m) {
-                    keys[m * nv_max + t] = make_key(acc[0][m], a.vocab_base + ra);
-                    if (rb != ra) keys[m * nv_max + t + 1] = make_key(acc[1][m], a.vocab_base + rb);
-                    if (a.logits_out) {
-                        a.logits_out[static_cast<size_t>(m0 + m) * a.V_local + ra] = acc[0][m];
-                        if (rb != ra) a.logits_out[static_cast<size_t>(m0 + m) * a.V_local + rb] = acc[1][m];
-                    }
-                }
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.final_ln, mb, a.H, a.eps, red);
+        for (int t0 = 0; t0 < nv; t0 += kTile) {
+            const int nt = min(kTile, nv - t0);
+            gemv_cta<MB, (MB == 1 ? 8 : 4)>(PlainBf16{a.w, a.H}, v0 + t0, nt, xs, a.H, part);
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < nt * mb; idx += blockDim.x) {
+                const int rl = idx / mb, m = idx % mb, row = v0 + t0 + rl;
+                const float v = gemv_result(part, rl, m, MB, gg.wpr);
+                keys[m * nv_max + t0 + rl] = make_key(v, a.vocab_base + row);
+                if (a.logits_out) a.logits_out[static_cast<size_t>(m0 + m) * a.V_local + row] = v;
+            }
+            __syncthreads();
         }
-        __syncthreads();
         // per-CTA top-K of each row: warp m owns row m
         if (warp < mb) {
             unsigned long long* kr = keys + warp * nv_max;
@@ -400,7 +400,8 @@ extern "C" int nexrt_lmhead_sample(const void* x, const void* final_ln, const vo
     a.H = H; a.V_local = V_local; a.vocab_base = vocab_base; a.M = M; a.eps = eps; a.mode = mode; a.arg = arg; a.ch = *ch; a.site = site;
     const int mb = M == 1 ? 1 : 4;
     const int nv_max = (V_local + n_cta - 1) / n_cta;
-    const size_t smem = sizeof(float) * static_cast<size_t>(mb) * H + sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, 512))) +
+                        sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (mb == 1) return launch(lmhead_sample_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
     return launch(lmhead_sample_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);

@@ -18,6 +18,7 @@
 #include "api.h"
 #include "epilogue.cuh"
 #include "gemv.cuh"
+#include "gemv_cta.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -37,30 +38,30 @@ struct RouterArgs {
 
 template <int MB>
 __global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
+    constexpr int U = MB == 1 ? 4 : 2;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_last;
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int rows = a.E + 1, pairs = (rows + 1) / 2;
-    int t0, t1;
-    cta_range(pairs, blockIdx.x, gridDim.x, &t0, &t1);
-    if (t1 > t0) prefetch_l2_range(a.w + static_cast<size_t>(t0) * 2 * a.H, static_cast<size_t>(min(t1 * 2, rows) - t0 * 2) * a.H * 2);
+    const int rows = a.E + 1;
+    int r0, r1;
+    cta_range(rows, blockIdx.x, gridDim.x, &r0, &r1);
+    const int nrows = r1 - r0;
+    if (nrows) prefetch_l2_range(a.w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(nrows) * a.H * 2);
+    const GemvGeom gg = gemv_geom(a.H / 8, blockDim.x);
+    float* xs = smem;
+    float* part = xs + static_cast<size_t>(MB) * a.H;
     pdl_wait();
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm<8>(smem, a.x + static_cast<size_t>(m0) * a.H, a.post_ln, mb, a.H, a.eps, red);
-        for (int t = t0 + warp; t < t1; t += nwarps) {
-            const int ra = t * 2, rb = min(t * 2 + 1, rows - 1);
-            const __nv_bfloat16* w[2] = {a.w + static_cast<size_t>(ra) * a.H, a.w + static_cast<size_t>(rb) * a.H};
-            float acc[2][MB];
-            gemv_bf16<MB, 2, 8>(w, a.H, smem, lane, acc);
-            if (lane == 0)
-                for (int m = 0; m < mb; ++m) {
-                    a.logits[static_cast<size_t>(m0 + m) * rows + ra] = acc[0][m];
-                    if (rb != ra) a.logits[static_cast<size_t>(m0 + m) * rows + rb] = acc[1][m];
-                }
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.post_ln, mb, a.H, a.eps, red);
+        gemv_cta<MB, U>(PlainBf16{a.w, a.H}, r0, nrows, xs, a.H, part);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
+            const int rl = idx / mb, m = idx % mb;
+            a.logits[static_cast<size_t>(m0 + m) * rows + r0 + rl] = gemv_result(part, rl, m, MB, gg.wpr);
         }
     }
     __threadfence();
@@ -121,8 +122,7 @@ struct MoeL1Args {
     const uint8_t* w13;     // [E+1][2I][H]: gate rows then up rows
     const float* w13_s;     // [E+1][2I/128][H/128]
     const int* ids;         // [M][S]
-    const float* wts;       // [M][S]
-    float* h;               // [M][S][I]
+    float* gu;              // [M][S][2I] raw gate | up projections
     int H, I, S, M;
     float eps;
     int shared_expert;      // index whose weights may be prefetched before the dependency wait
@@ -131,36 +131,38 @@ struct MoeL1Args {
 __global__ void __launch_bounds__(512, 1) moe_l1_kernel(MoeL1Args a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
+    __shared__ int s_ids[16];
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int per_row = a.S * a.I, total = a.M * per_row;
-    int t0, t1;
-    cta_range(total, blockIdx.x, gridDim.x, &t0, &t1);
-    const size_t expert_bytes = static_cast<size_t>(2) * a.I * a.H;
-    {   // the shared expert is known before routing: pull this CTA's share of it towards L2
-        const size_t share = expert_bytes / gridDim.x;
-        prefetch_l2_range(a.w13 + a.shared_expert * expert_bytes + blockIdx.x * share, share);
+    const int I2 = 2 * a.I, vrows = a.S * I2;
+    int v0, v1;
+    cta_range(vrows, blockIdx.x, gridDim.x, &v0, &v1);
+    const int nrows = v1 - v0;
+    const size_t expert_bytes = static_cast<size_t>(I2) * a.H;
+    {   // the shared expert (last slot) is known before routing: pull this CTA's rows of it towards L2
+        const int s0 = max(v0, (a.S - 1) * I2), s1 = v1;
+        if (s1 > s0) prefetch_l2_range(a.w13 + a.shared_expert * expert_bytes + static_cast<size_t>(s0 - (a.S - 1) * I2) * a.H,
+                                       static_cast<size_t>(s1 - s0) * a.H);
     }
+    const GemvGeom gg = gemv_geom(a.H / 16, blockDim.x);
+    float* xs = smem;                 // [H]
+    float* part = xs + a.H;
     pdl_wait();
-    stage_rmsnorm<16>(smem, a.x, a.post_ln, a.M, a.H, a.eps, red);
-    const int KB = a.H / kScaleBlock;
-    for (int t = t0 + warp; t < t1; t += nwarps) {
-        const int m = t / per_row, s_ = (t % per_row) / a.I, i = t % a.I;
-        const int e = a.ids[m * a.S + s_];
-        const uint8_t* base = a.w13 + e * expert_bytes;
-        const uint8_t* w[2] = {base + static_cast<size_t>(i) * a.H, base + static_cast<size_t>(a.I + i) * a.H};
-        const float* sb = a.w13_s + static_cast<size_t>(e) * (2 * a.I / kScaleBlock) * KB;
-        const float* s[2] = {sb + (i / kScaleBlock) * KB, sb + ((a.I + i) / kScaleBlock) * KB};
-        float acc[2][1];
-        gemv_fp8<1, 2, 32>(w, s, a.H, smem + static_cast<size_t>(m) * a.H, lane, acc);
-        if (lane == 0) a.h[t] = silu_f(acc[0][0]) * acc[1][0] * a.wts[m * a.S + s_];
+    for (int m = 0; m < a.M; ++m) {
+        if (m) __syncthreads();
+        if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m) * a.H, a.post_ln, 1, a.H, a.eps, red);
+        gemv_cta<1, 8>(ExpertUp{a.w13, a.w13_s, s_ids, a.H, I2}, v0, nrows, xs, a.H, part);
+        __syncthreads();
+        for (int rl = threadIdx.x; rl < nrows; rl += blockDim.x)
+            a.gu[static_cast<size_t>(m) * vrows + v0 + rl] = gemv_result(part, rl, 0, 1, gg.wpr);
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 struct MoeL2Args {
-    const float* h;         // [M][S][I] (route weight already folded in)
+    const float* gu;        // [M][S][2I] raw gate | up projections
     const int* ids;         // [M][S]
+    const float* wts;       // [M][S] route weights (shared-expert gate last)
     const uint8_t* w2;      // [E+1][H][I]
     const float* w2_s;      // [E+1][H/128][I/128]
     __nv_bfloat16* x;
@@ -173,51 +175,28 @@ __global__ void __launch_bounds__(512, 1) moe_l2_allreduce_kernel(MoeL2Args a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_ids[16];
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    int r0, r1;
-    cta_range(a.H / 2, blockIdx.x, gridDim.x, &r0, &r1);
-    const int nrows = (r1 - r0) * 2, row0 = r0 * 2;
-    const int VK = a.S * a.I, q = VK >> 4, cps = a.I >> 4;   // virtual row, its 16-byte chunks, chunks per slot
-    float* hs = smem;               // [VK] quad-major
-    float* res = smem + VK;         // [kMaxRows][nrows]
-    const size_t expert_elems = static_cast<size_t>(a.H) * a.I;
-    const int SB = a.I / kScaleBlock;
+    int row0, row1;
+    cta_range(a.H, blockIdx.x, gridDim.x, &row0, &row1);
+    const int nrows = row1 - row0, max_rows = (a.H + gridDim.x - 1) / gridDim.x;
+    const int VK = a.S * a.I;
+    const GemvGeom gg = gemv_geom(VK / 16, blockDim.x);
+    float* hs = smem;                                        // [VK]
+    float* part = hs + VK;
+    float* res = part + gemv_part_floats(max_rows, 1, gg);   // [kMaxRows][nrows]
     pdl_wait();
     for (int m = 0; m < a.M; ++m) {
         if (m) __syncthreads();
-        for (int k = threadIdx.x; k < VK; k += blockDim.x) hs[perm16(k, VK)] = a.h[static_cast<size_t>(m) * VK + k];
+        // h = silu(gate) * up * route weight
+        for (int k = threadIdx.x; k < VK; k += blockDim.x) {
+            const int sl = k / a.I, i = k % a.I;
+            const float* g = a.gu + (static_cast<size_t>(m) * a.S + sl) * 2 * a.I;
+            hs[k] = silu_f(g[i]) * g[a.I + i] * a.wts[m * a.S + sl];
+        }
         if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
         __syncthreads();
-        for (int t = r0 + warp; t < r1; t += nwarps) {
-            const int r = t * 2;
-            float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll 2
-            for (int c = lane; c < q; c += 32) {
-                const int slot = c / cps, kc = c % cps;
-                const int e = s_ids[slot];
-                const uint8_t* wp = a.w2 + e * expert_elems + static_cast<size_t>(r) * a.I + kc * 16;
-                const uint4 w0 = ld_stream16(wp), w1 = ld_stream16(wp + a.I);
-                const float* sp = a.w2_s + (static_cast<size_t>(e) * (a.H / kScaleBlock) + r / kScaleBlock) * SB + (kc >> 3);
-                const float sc0 = __ldg(sp), sc1 = __ldg(sp + (((r + 1) / kScaleBlock) - (r / kScaleBlock)) * SB);
-                float p0 = 0.f, p1 = 0.f, f0[4], f1[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 xv = *reinterpret_cast<const float4*>(hs + ((j * q + c) << 2));
-                    e4m3x4_to_float4(j == 0 ? w0.x : j == 1 ? w0.y : j == 2 ? w0.z : w0.w, f0);
-                    e4m3x4_to_float4(j == 0 ? w1.x : j == 1 ? w1.y : j == 2 ? w1.z : w1.w, f1);
-                    p0 = fmaf(f0[0], xv.x, p0); p0 = fmaf(f0[1], xv.y, p0); p0 = fmaf(f0[2], xv.z, p0); p0 = fmaf(f0[3], xv.w, p0);
-                    p1 = fmaf(f1[0], xv.x, p1); p1 = fmaf(f1[1], xv.y, p1); p1 = fmaf(f1[2], xv.z, p1); p1 = fmaf(f1[3], xv.w, p1);
-                }
-                acc0 = fmaf(p0, sc0, acc0);
-                acc1 = fmaf(p1, sc1, acc1);
-            }
-            acc0 = warp_sum(acc0);
-            acc1 = warp_sum(acc1);
-            if (lane == 0) {
-                res[m * nrows + (r - row0)] = acc0;
-                res[m * nrows + (r - row0) + 1] = acc1;
-            }
-        }
+        gemv_cta<1, 8>(ExpertDown{a.w2, a.w2_s, s_ids, a.H, a.I}, row0, nrows, hs, VK, part);
+        __syncthreads();
+        for (int rl = threadIdx.x; rl < nrows; rl += blockDim.x) res[m * nrows + rl] = gemv_result(part, rl, 0, 1, gg.wpr);
     }
     __syncthreads();
     allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
@@ -233,27 +212,32 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
     RouterArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const __nv_bfloat16*>(w),
                  static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), static_cast<int*>(ticket), H, E, topk, M, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(512), sizeof(float) * H, st, a);
-    return launch(moe_router_kernel<4>, dim3(n_cta), dim3(512), sizeof(float) * 4 * H, st, a);
+    const int mb = M == 1 ? 1 : 4;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats((E + 1 + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, 512)));
+    if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
+    return launch(moe_router_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
 }
 
-extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, const void* wts, void* h,
-                            int H, int I, int S, int M, float eps, int shared_expert, int n_cta, void* stream) {
-    if (M < 1 || M > kMaxRows || H % 512 || I % 128 || S > 16) return cudaErrorInvalidValue;
+extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I,
+                            int S, int M, float eps, int shared_expert, int n_cta, void* stream) {
+    if (M < 1 || M > kMaxRows || H % 256 || I % 128 || S > 16) return cudaErrorInvalidValue;
     MoeL1Args a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const uint8_t*>(w13),
-                static_cast<const float*>(w13_s), static_cast<const int*>(ids), static_cast<const float*>(wts), static_cast<float*>(h),
-                H, I, S, M, eps, shared_expert};
-    return launch(moe_l1_kernel, dim3(n_cta), dim3(512), sizeof(float) * M * H, static_cast<cudaStream_t>(stream), a);
+                static_cast<const float*>(w13_s), static_cast<const int*>(ids), static_cast<float*>(gu), H, I, S, M, eps, shared_expert};
+    const int vrows = S * 2 * I;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(H) + gemv_part_floats((vrows + n_cta - 1) / n_cta, 1, gemv_geom(H / 16, 512)));
+    return launch(moe_l1_kernel, dim3(n_cta), dim3(512), smem, static_cast<cudaStream_t>(stream), a);
 }
 
-extern "C" int nexrt_moe_l2_allreduce(const void* h, const void* ids, const void* w2, const void* w2_s, void* x, int H, int I, int S, int M,
-                                      const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream) {
-    if (M < 1 || M > kMaxRows || I % 128 || S > 16 || H % 2 || ch == nullptr) return cudaErrorInvalidValue;
+extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I,
+                                      int S, int M, const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream) {
+    if (M < 1 || M > kMaxRows || I % 128 || S > 16 || ch == nullptr) return cudaErrorInvalidValue;
     if (ch->world > 1 && ch->slots < static_cast<unsigned int>(kMaxRows) * H) return cudaErrorInvalidValue;
     MoeL2Args a{};
-    a.h = static_cast<const float*>(h); a.ids = static_cast<const int*>(ids); a.w2 = static_cast<const uint8_t*>(w2);
-    a.w2_s = static_cast<const float*>(w2_s); a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = I; a.S = S; a.M = M; a.ch = *ch; a.site = site;
-    const int max_rows = ((H / 2 + n_cta - 1) / n_cta) * 2;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(S) * I + static_cast<size_t>(kMaxRows) * max_rows);
+    a.gu = static_cast<const float*>(gu); a.ids = static_cast<const int*>(ids); a.wts = static_cast<const float*>(wts);
+    a.w2 = static_cast<const uint8_t*>(w2); a.w2_s = static_cast<const float*>(w2_s); a.x = static_cast<__nv_bfloat16*>(x);
+    a.H = H; a.I = I; a.S = S; a.M = M; a.ch = *ch; a.site = site;
+    const int max_rows = (H + n_cta - 1) / n_cta;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(S) * I + gemv_part_floats(max_rows, 1, gemv_geom(S * I / 16, 512)) +
+                                         static_cast<size_t>(kMaxRows) * max_rows);
     return launch(moe_l2_allreduce_kernel, dim3(n_cta), dim3(512), smem, static_cast<cudaStream_t>(stream), a);
 }

@@ -17,6 +17,7 @@
 #include "api.h"
 #include "epilogue.cuh"
 #include "gemv.cuh"
+#include "gemv_cta.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -36,31 +37,28 @@ struct OProjArgs {
     unsigned int cp_site;
 };
 
-template <int MB, int LPR>
+template <int MB>
 __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
+    constexpr int U = MB == 1 ? 8 : 4;
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    constexpr int GP = 32 / LPR;                 // row pairs a warp works on at once
-    const int sub = lane % LPR, grp = lane / LPR;
-    int r0, r1;
-    cta_range(a.H / 2, blockIdx.x, gridDim.x, &r0, &r1);   // in row pairs
-    const int nrows = (r1 - r0) * 2, row0 = r0 * 2;
+    int row0, row1;
+    cta_range(a.H, blockIdx.x, gridDim.x, &row0, &row1);
+    const int nrows = row1 - row0, max_rows = (a.H + gridDim.x - 1) / gridDim.x;
     if (nrows) prefetch_l2_range(a.w + static_cast<size_t>(row0) * a.K, static_cast<size_t>(nrows) * a.K);
-    float* xs = smem;                                       // [MB][K]
-    float* res = smem + static_cast<size_t>(MB) * a.K;      // [kMaxRows][nrows]
-    const int KB = a.K / kScaleBlock;
+    const GemvGeom gg = gemv_geom(a.K / 16, blockDim.x);
+    float* xs = smem;                                        // [MB][K]
+    float* part = xs + static_cast<size_t>(MB) * a.K;        // [max_rows][wpr][MB]
+    float* res = part + gemv_part_floats(max_rows, MB, gg);  // [kMaxRows][nrows]
     pdl_wait();
-    LLCall cpcall;
+    LLCall cpcall{0u, 0u};
     if (a.mode == 2) cpcall = ll_begin(a.cp, a.cp_site);
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
         if (a.mode == 0) {
-            for (int idx = threadIdx.x; idx < mb * a.K; idx += blockDim.x) {
-                const int m = idx / a.K, k = idx % a.K;
-                xs[m * a.K + perm16(k, a.K)] = a.in[static_cast<size_t>(m0 + m) * a.K + k];
-            }
+            for (int idx = threadIdx.x; idx < mb * a.K; idx += blockDim.x) xs[idx] = a.in[static_cast<size_t>(m0) * a.K + idx];
         } else if (a.mode == 1) {
             // gated RMSNorm per 128-wide head: gnorm_w * o * rsqrt(mean o^2 + eps) * silu(z)
             const int heads = a.K / 128;
@@ -71,12 +69,12 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
                 const float4 zz = *reinterpret_cast<const float4*>(a.z + base);
                 const float4 gw = *reinterpret_cast<const float4*>(a.gnorm_w + lane * 4);
                 const float inv = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) / 128.f + a.eps);
-                const int k = h * 128 + lane * 4;
-                float* d = xs + m * a.K + perm16(k, a.K);
-                d[0] = gw.x * o.x * inv * silu_f(zz.x);
-                d[1] = gw.y * o.y * inv * silu_f(zz.y);
-                d[2] = gw.z * o.z * inv * silu_f(zz.z);
-                d[3] = gw.w * o.w * inv * silu_f(zz.w);
+                float4 r;
+                r.x = gw.x * o.x * inv * silu_f(zz.x);
+                r.y = gw.y * o.y * inv * silu_f(zz.y);
+                r.z = gw.z * o.z * inv * silu_f(zz.z);
+                r.w = gw.w * o.w * inv * silu_f(zz.w);
+                *reinterpret_cast<float4*>(xs + m * a.K + h * 128 + lane * 4) = r;
             }
         } else {
             // context-parallel merge: for every (row, local head, dim) combine the partial contexts
@@ -101,20 +99,15 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
                     den += wgt;
                 }
                 const float gt = a.z[static_cast<size_t>(m0 + m) * a.K + k];
-                xs[m * a.K + perm16(k, a.K)] = (den > 0.f ? num / den : 0.f) * sigmoid_f(gt);
+                xs[m * a.K + k] = (den > 0.f ? num / den : 0.f) * sigmoid_f(gt);
             }
         }
         __syncthreads();
-        for (int tb = r0 + warp * GP; tb < r1; tb += nwarps * GP) {
-            const int t = min(tb + grp, r1 - 1);
-            const int r = t * 2;
-            const uint8_t* w[2] = {a.w + static_cast<size_t>(r) * a.K, a.w + static_cast<size_t>(r + 1) * a.K};
-            const float* s[2] = {a.s + (r / kScaleBlock) * KB, a.s + ((r + 1) / kScaleBlock) * KB};
-            float acc[2][MB];
-            gemv_fp8<MB, 2, LPR>(w, s, a.K, xs, sub, acc);
-            if (sub < 2 && tb + grp < r1) {
-                for (int m = 0; m < mb; ++m) res[(m0 + m) * nrows + (r - row0) + sub] = sub == 0 ? acc[0][m] : acc[1][m];
-            }
+        gemv_cta<MB, U>(PlainFp8{a.w, a.s, a.K}, row0, nrows, xs, a.K, part);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
+            const int rl = idx / mb, m = idx % mb;
+            res[(m0 + m) * nrows + rl] = gemv_result(part, rl, m, MB, gg.wpr);
         }
     }
     __syncthreads();
@@ -138,18 +131,10 @@ extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* 
     if (cp) { a.cp = *cp; a.cp_site = cp_site; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int mb = M == 1 ? 1 : 4;
-    const int max_rows = ((H / 2 + n_cta - 1) / n_cta) * 2;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * K + static_cast<size_t>(kMaxRows) * max_rows);
-    const int lpr = K % 512 == 0 ? 32 : K % 256 == 0 ? 16 : 8;
+    const int max_rows = (H + n_cta - 1) / n_cta;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * K + gemv_part_floats(max_rows, mb, gemv_geom(K / 16, 512)) +
+                                         static_cast<size_t>(kMaxRows) * max_rows);
     dim3 g(n_cta), b(512);
-#define NEXRT_OPROJ(MB_, LPR_) return launch(oproj_allreduce_kernel<MB_, LPR_>, g, b, smem, st, a)
-    if (mb == 1) {
-        if (lpr == 32) NEXRT_OPROJ(1, 32);
-        if (lpr == 16) NEXRT_OPROJ(1, 16);
-        NEXRT_OPROJ(1, 8);
-    }
-    if (lpr == 32) NEXRT_OPROJ(4, 32);
-    if (lpr == 16) NEXRT_OPROJ(4, 16);
-    NEXRT_OPROJ(4, 8);
-#undef NEXRT_OPROJ
+    if (mb == 1) return launch(oproj_allreduce_kernel<1>, g, b, smem, st, a);
+    return launch(oproj_allreduce_kernel<4>, g, b, smem, st, a);
 }

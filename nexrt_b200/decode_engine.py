@@ -46,6 +46,7 @@ class DecodeEngine:
         max_rows: int = 1,
         cache_len: Optional[int] = None,
         budget_ms: Optional[float] = None,
+        shape_tp: Optional[int] = None,
     ):
         """``ext`` is the per-rank model dict in kernel layout (``weights.shard_model`` or
         ``weights.random_rank_model``); the reference uses the same argument to alias tensors that
@@ -55,11 +56,13 @@ class DecodeEngine:
         self.cfg = cfg or active_config()
         self.rank, self.world = rank, world
         self.dev = dev or torch.device("cuda", torch.cuda.current_device())
-        self.spec = ShardSpec(self.cfg, world, rank)
+        # shape_tp: run alone with the shard shapes of one rank of a shape_tp-wide group (profiling)
+        self.spec = ShardSpec(self.cfg, shape_tp or world, rank)
         self.group = group
         self.max_rows = max_rows
         self.cp = bool(cp) and self.spec.cp_size > 1
-        self.ctx = StepContext(self.cfg, self.spec, self.dev, group=group, budget_ms=budget_ms, cp=self.cp)
+        self.ctx = StepContext(self.cfg, self.spec, self.dev, group=group, budget_ms=budget_ms, cp=self.cp,
+                               comm_world=world, comm_rank=rank)
         state_ring = max(2, max_rows + 1)
         conv_ring = 16
         self.mixers: List = []

@@ -46,7 +46,7 @@ class Gdn:
             ),
             "gdn_core",
         )
-        n_cta = min(c.n_cta, cfg.hidden // 32)
+        n_cta = c.n_cta
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.gdn_out), ptr(c.gdn_z), ptr(w["gnorm_w"]), ptr(w["out_w"]), ptr(w["out_s"]), ptr(c.x), cfg.hidden, spec.gdn_local,

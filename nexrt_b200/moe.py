@@ -32,16 +32,15 @@ class Moe:
         )
         check(
             lib.nexrt_moe_l1(
-                ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_h), cfg.hidden,
-                spec.inter, S, M, cfg.rms_eps, cfg.n_experts, c.n_cta, st,
+                ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_gu), cfg.hidden, spec.inter, S, M,
+                cfg.rms_eps, cfg.n_experts, c.n_cta, st,
             ),
             "moe_l1",
         )
-        n_cta = min(c.n_cta, cfg.hidden // 32)
         check(
             lib.nexrt_moe_l2_allreduce(
-                ptr(c.moe_h), ptr(c.moe_ids), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), cfg.hidden, spec.inter, S, M, c.channel.ref,
-                c.next_site(), n_cta, st,
+                ptr(c.moe_gu), ptr(c.moe_ids), ptr(c.moe_wts), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), cfg.hidden, spec.inter, S, M,
+                c.channel.ref, c.next_site(), c.n_cta, st,
             ),
             "moe_l2_allreduce",
         )

@@ -50,8 +50,8 @@ _PROTOTYPES = {
     "nexrt_attn_decode": [vp] * 13 + [ci] * 8 + [cf, ci, ci, CH, cu, vp],
     "nexrt_oproj_allreduce": [vp] * 6 + [ci] * 4 + [cf, ci, CH, cu, CH, cu, ci, vp],
     "nexrt_moe_router": [vp] * 7 + [ci] * 4 + [cf, ci, vp],
-    "nexrt_moe_l1": [vp] * 7 + [ci] * 4 + [cf, ci, ci, vp],
-    "nexrt_moe_l2_allreduce": [vp] * 5 + [ci] * 4 + [CH, cu, ci, vp],
+    "nexrt_moe_l1": [vp] * 6 + [ci] * 4 + [cf, ci, ci, vp],
+    "nexrt_moe_l2_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, ci, vp],
     "nexrt_lmhead_sample": [vp] * 9 + [ci] * 4 + [cf, ci, ci, CH, cu, ci, vp],
     "nexrt_sample_logits": [vp, vp, vp, ci, ci, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],

@@ -19,10 +19,14 @@ MAX_TOPK = 28
 
 
 class StepContext:
-    def __init__(self, cfg: ModelConfig, spec: ShardSpec, device: torch.device, group=None, budget_ms=None, cp: bool = False):
+    def __init__(self, cfg: ModelConfig, spec: ShardSpec, device: torch.device, group=None, budget_ms=None, cp: bool = False,
+                 comm_world=None, comm_rank=None):
         self.cfg, self.spec, self.device, self.group = cfg, spec, device, group
         self.lib = L.load()
         self.tp, self.rank = spec.tp, spec.rank
+        # shapes may be those of one rank of a wider group while running alone (profiling fixture)
+        cw = spec.tp if comm_world is None else comm_world
+        cr = spec.rank if comm_rank is None else comm_rank
         props = torch.cuda.get_device_properties(device)
         self.n_cta = props.multi_processor_count
         H = cfg.hidden
@@ -35,9 +39,9 @@ class StepContext:
         self.seq = torch.ones(1, dtype=i32, device=device)
         self.status = self.ctl[Ctl.STATUS : Ctl.STATUS + 1]
         kw = {} if budget_ms is None else {"budget_ms": budget_ms}
-        self.channel = LLChannel(device, spec.tp, spec.rank, MAX_ROWS * H, group=group, seq=self.seq, status=self.status, **kw)
+        self.channel = LLChannel(device, cw, cr, MAX_ROWS * H, group=group, seq=self.seq, status=self.status, **kw)
         self.cp_channel = None
-        if cp and spec.cp_size > 1:
+        if cp and spec.cp_size > 1 and cw == spec.tp:
             slots = MAX_ROWS * spec.q_heads * (cfg.head_dim + 1)
             self.cp_channel = LLChannel(
                 device, spec.tp, spec.rank, slots, group=group, seq=self.seq, status=self.status, members=spec.cp_group, **kw
@@ -68,7 +72,7 @@ class StepContext:
         self.moe_logits = z(MAX_ROWS, cfg.n_experts + 1)
         self.moe_ids = z(MAX_ROWS, S, dtype=i32)
         self.moe_wts = z(MAX_ROWS, S)
-        self.moe_h = z(MAX_ROWS, S, spec.inter)
+        self.moe_gu = z(MAX_ROWS, S, 2 * spec.inter)
         self.moe_ticket = z(1, dtype=i32)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)

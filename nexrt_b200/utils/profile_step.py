@@ -20,6 +20,7 @@ def main() -> None:
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--rows", type=int, default=1)
     p.add_argument("--shrunk", action="store_true")
+    p.add_argument("--tp", type=int, default=1, help="use the shard shapes of one rank of a tp-wide group (no communication)")
     p.add_argument("--graph", action="store_true", help="time captured-graph replays and print us/step")
     a = p.parse_args()
     from ..config import full_config, shrunk_config
@@ -30,8 +31,8 @@ def main() -> None:
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     cfg = shrunk_config() if a.shrunk else full_config().truncated(a.layers)
-    model = random_rank_model(cfg, 1, 0, dev)
-    eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, max_rows=max(a.rows, 1), cache_len=a.ctx + 64 * a.rows + 1024)
+    model = random_rank_model(cfg, a.tp, 0, dev)
+    eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, shape_tp=a.tp, max_rows=max(a.rows, 1), cache_len=a.ctx + 64 * a.rows + 1024)
     eng.reset(first_token=1, committed_len=a.ctx)
     eng.set_rows(list(range(1, a.rows + 1)))
     eng.set_forced_commit(a.rows)
