@@ -28,6 +28,9 @@ typedef struct NexrtLLChannel {
 
 int nexrt_set_pdl(int enabled);
 int nexrt_version(void);
+int nexrt_set_gemv_threads(int threads);
+int nexrt_set_event_ring(void* ring);  /* 8 x u64 device words: phase timestamps of the GDN front kernel, NULL = off */
+int nexrt_set_gemv_mode(int mode);   /* 0: CUDA-core GEMV, 1: tensor-core GEMV (default) */
 
 /* step plumbing */
 int nexrt_embed_gather(const void* embed, const void* ctl, void* x, void* status, int H, int vocab, int M, void* stream);

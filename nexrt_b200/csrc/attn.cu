@@ -20,6 +20,7 @@
 #include "api.h"
 #include "gemv.cuh"
 #include "gemv_cta.cuh"
+#include "mma_gemv.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -38,6 +39,23 @@ struct AttnFrontArgs {
     float eps;
 };
 
+// Scatter one projected value: query / gate rows to scratch, k rows to scratch, v rows to the cache.
+__device__ __forceinline__ void attn_front_row(const AttnFrontArgs& a, int row, int mm, float v, int C0, bool interleaved) {
+    const int head = row / a.hd, d = row % a.hd;
+    if (head < a.nq + a.ngate) {
+        int qh, is_gate;
+        if (interleaved) { qh = head >> 1; is_gate = head & 1; }
+        else { is_gate = head >= a.nq; qh = is_gate ? head - a.nq : head; }
+        if (is_gate) a.gate[(static_cast<size_t>(mm) * a.ngate + qh) * a.hd + d] = v;
+        else a.q_raw[(static_cast<size_t>(mm) * a.nq + qh) * a.hd + d] = v;
+    } else if (head < a.nq + a.ngate + a.kvh) {
+        a.k_raw[(static_cast<size_t>(mm) * a.kvh + (head - a.nq - a.ngate)) * a.hd + d] = v;
+    } else {
+        const int kv = head - a.nq - a.ngate - a.kvh;
+        a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
+    }
+}
+
 // Row order of the weight: nq "query" heads; when ngate == nq each query head is followed by its
 // gate head (checkpoint order query|gate per head), otherwise (context-parallel front) all nq
 // query heads come first and the ngate gate heads after them; then k heads, then v heads.
@@ -55,31 +73,57 @@ __global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
     const GemvGeom gf = gemv_geom(a.H / 16, blockDim.x);
     float* xs = smem;
     float* part = xs + static_cast<size_t>(MB) * a.H;
+    float* gs = part + gemv_part_floats((R + gridDim.x - 1) / gridDim.x, MB, gf);   // [H] norm multiplier
+    GemvCta<MB, U, PlainFp8> gemv(PlainFp8{a.w, a.s, a.H}, r0, nrows, a.H);
+    gemv.preload();
+    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.in_ln[i];
     pdl_wait();
     const int C0 = a.ctl[kCtlCommittedLen];
     const bool interleaved = a.ngate == a.nq;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
-        gemv_cta<MB, U>(PlainFp8{a.w, a.s, a.H}, r0, nrows, xs, a.H, part);
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
+        if (m0 == 0) gemv.run(xs, part);
+        else gemv_cta<MB, U>(PlainFp8{a.w, a.s, a.H}, r0, nrows, xs, a.H, part);
         __syncthreads();
         for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
-            const int rl = idx / mb, m = idx % mb, row = r0 + rl, mm = m0 + m;
-            const float v = gemv_result(part, rl, m, MB, gf.wpr);
-            const int head = row / a.hd, d = row % a.hd;
-            if (head < a.nq + a.ngate) {
-                int qh, is_gate;
-                if (interleaved) { qh = head >> 1; is_gate = head & 1; }
-                else { is_gate = head >= a.nq; qh = is_gate ? head - a.nq : head; }
-                if (is_gate) a.gate[(static_cast<size_t>(mm) * a.ngate + qh) * a.hd + d] = v;
-                else a.q_raw[(static_cast<size_t>(mm) * a.nq + qh) * a.hd + d] = v;
-            } else if (head < a.nq + a.ngate + a.kvh) {
-                a.k_raw[(static_cast<size_t>(mm) * a.kvh + (head - a.nq - a.ngate)) * a.hd + d] = v;
-            } else {
-                const int kv = head - a.nq - a.ngate - a.kvh;
-                a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
-            }
+            const int rl = idx / mb, m = idx % mb;
+            attn_front_row(a, r0 + rl, m0 + m, gemv_result(part, rl, m, MB, gf.wpr), C0, interleaved);
+        }
+    }
+}
+
+// Tensor-core form: one CTA per 16 weight rows, 8 warps split K (see mma_gemv.cuh).
+template <int MP>
+__global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a) {
+    constexpr int TERMS = MP <= 2 ? 3 : 2, NB = 8, KS = 8;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5;
+    const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
+    float* tiles = smem;                                              // [KS][16][8]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(tiles + KS * 128);       // [MP*TERMS][H]
+    const MmaPlain src{a.w, a.s, a.H};
+    MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
+    mw.preload(src);
+    RowNorm<4> norm;
+    norm.preload_gamma(a.in_ln, a.H);
+    pdl_wait();
+    const int C0 = a.ctl[kCtlCommittedLen];
+    const bool interleaved = a.ngate == a.nq;
+    for (int m0 = 0; m0 < a.M; m0 += MP) {
+        const int mb = min(MP, a.M - m0);
+        if (m0) { __syncthreads(); mw.preloaded = false; }
+        norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
+        float d[4];
+        mw.run(src, xq, a.H, mb * TERMS, d);
+        mw.store(tiles + warp * 128, d);
+        __syncthreads();
+        if (threadIdx.x < kRowsPerGroup * mb) {
+            const int rl = threadIdx.x % kRowsPerGroup, m = threadIdx.x / kRowsPerGroup;
+            attn_front_row(a, row0 + rl, m0 + m, mma_result<TERMS>(tiles, 0, KS, rl, m, kSplitDescale), C0, interleaved);
         }
     }
 }
@@ -350,11 +394,19 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
                     static_cast<const float*>(s), static_cast<const int*>(ctl), static_cast<float*>(q_raw), static_cast<float*>(gate),
                     static_cast<float*>(k_raw), static_cast<__nv_bfloat16*>(v_cache), H, hd, nq, ngate, kvh, M, cache_len, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int mb = M == 1 ? 1 : 4;
     const int R = (nq + ngate + 2 * kvh) * hd;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats((R + n_cta - 1) / n_cta, mb, gemv_geom(H / 16, 512)));
-    if (M == 1) return launch(attn_front_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
-    return launch(attn_front_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
+    if (gemv_mode() == 1 && H % 512 == 0 && H <= 4096) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = mp <= 2 ? 3 : 2;
+        const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(mp) * terms * H;
+        dim3 g(R / 16), b(256);
+        if (mp == 1) return launch(attn_front_mma_kernel<1>, g, b, smem_mma, st, a);
+        if (mp == 2) return launch(attn_front_mma_kernel<2>, g, b, smem_mma, st, a);
+        return launch(attn_front_mma_kernel<4>, g, b, smem_mma, st, a);
+    }
+    const int mb = M == 1 ? 1 : 4;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb + 1) * H + gemv_part_floats((R + n_cta - 1) / n_cta, mb, gemv_geom(H / 16, gemv_threads())));
+    if (M == 1) return launch(attn_front_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+    return launch(attn_front_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }
 
 extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {

@@ -17,6 +17,7 @@
 #include "api.h"
 #include "gemv.cuh"
 #include "gemv_cta.cuh"
+#include "mma_gemv.cuh"
 
 namespace nexrt {
 
@@ -37,7 +38,43 @@ struct GdnFrontArgs {
     float* g;                    // [M][nv]
     int H, R, C, nv, M, conv_ring_len;
     float eps;
+    unsigned long long* events;  // optional in-kernel event ring: CTA 0 records %globaltimer at phase boundaries
 };
+
+// Per-row tail of the front: history-ring write, causal conv1d(4) + SiLU for the q|k|v rows, plain
+// store for the z rows.  pre[m] is the projection of row `row` for token row m0 + m.
+template <int MB>
+__device__ __forceinline__ void gdn_front_row(const GdnFrontArgs& a, int row, const float (&pre)[MB], int m0, int mb, int C0, const float4& cw) {
+    if (row < a.C) {
+        const int ring = a.conv_ring_len;
+        for (int m = 0; m < mb; ++m) {
+            const int p = C0 + m0 + m;
+            a.conv_ring[static_cast<size_t>(p % ring) * a.C + row] = pre[m];
+        }
+        for (int m = 0; m < mb; ++m) {
+            const int p = C0 + m0 + m;
+            // taps at positions p-3..p; slots of positions before the sequence start hold zero
+            float h[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const int mm = m - 3 + j;
+                h[j] = (mm >= 0) ? pre[mm < 0 ? 0 : mm] : a.conv_ring[static_cast<size_t>((p - 3 + j + ring) % ring) * a.C + row];
+            }
+            const float v = fmaf(cw.x, h[0], fmaf(cw.y, h[1], fmaf(cw.z, h[2], cw.w * pre[m])));
+            a.qkv[static_cast<size_t>(m0 + m) * a.C + row] = silu_f(v);
+        }
+    } else {
+        for (int m = 0; m < mb; ++m) a.z[static_cast<size_t>(m0 + m) * (a.R - a.C) + (row - a.C)] = pre[m];
+    }
+}
+
+__device__ __forceinline__ void gdn_ba_row(const GdnFrontArgs& a, int row, float v, int mm) {
+    if (row < a.nv) a.beta[mm * a.nv + row] = sigmoid_f(v);
+    else {
+        const int h = row - a.nv;
+        a.g[mm * a.nv + h] = -__expf(a.a_log[h]) * softplus_f(v + a.dt_bias[h]);
+    }
+}
 
 template <int MB>
 __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
@@ -54,54 +91,90 @@ __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
     float* xs = smem;                                                   // [MB][H]
     float* part = xs + static_cast<size_t>(MB) * a.H;                   // fp8 rows
     float* part_ba = part + gemv_part_floats((a.R + gridDim.x - 1) / gridDim.x, MB, gf);
+    float* gs = part_ba + gemv_part_floats((2 * a.nv + gridDim.x - 1) / gridDim.x, MB, gb);   // [H] norm multiplier
+    GemvCta<MB, U, PlainFp8> gemv(PlainFp8{a.front_w, a.front_s, a.H}, r0, nrows, a.H);
+    gemv.preload();
+    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.in_ln[i];
+    if (nrows) prefetch_l2_range(a.conv_w + static_cast<size_t>(r0) * 4, static_cast<size_t>(nrows) * 16);
     pdl_wait();
     const int C0 = a.ctl[kCtlCommittedLen];
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.in_ln, mb, a.H, a.eps, red);
-        gemv_cta<MB, U>(PlainFp8{a.front_w, a.front_s, a.H}, r0, nrows, xs, a.H, part);
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
+        if (m0 == 0) gemv.run(xs, part);
+        else gemv_cta<MB, U>(PlainFp8{a.front_w, a.front_s, a.H}, r0, nrows, xs, a.H, part);
         if (nba) gemv_cta<MB, 2>(PlainBf16{a.ba_w, a.H}, b0, nba, xs, a.H, part_ba);
         __syncthreads();
         for (int rl = threadIdx.x; rl < nrows; rl += blockDim.x) {
-            const int row = r0 + rl;
             float pre[MB];
 #pragma unroll
             for (int m = 0; m < MB; ++m) pre[m] = gemv_result(part, rl, m, MB, gf.wpr);
-            if (row < a.C) {
-                const float4 cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
-                const int ring = a.conv_ring_len;
-                for (int m = 0; m < mb; ++m) {
-                    const int p = C0 + m0 + m;
-                    a.conv_ring[static_cast<size_t>(p % ring) * a.C + row] = pre[m];
-                }
-                for (int m = 0; m < mb; ++m) {
-                    const int p = C0 + m0 + m;
-                    // taps at positions p-3..p; slots of positions before the sequence start hold zero
-                    float h[3];
+            float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r0 + rl < a.C) cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(r0 + rl) * 4);
+            gdn_front_row<MB>(a, r0 + rl, pre, m0, mb, C0, cw);
+        }
+        for (int rl = threadIdx.x; rl < nba; rl += blockDim.x)
+            for (int m = 0; m < mb; ++m) gdn_ba_row(a, b0 + rl, gemv_result(part_ba, rl, m, MB, gb.wpr), m0 + m);
+    }
+}
+
+// Tensor-core form of the front: one CTA per 16 weight rows, the 8 warps split K, FP8 weights go
+// from global memory to registers to mma.m16n8k32 against the exact e4m3 split of the normalised
+// activation.  MP token rows per pass (1, 2 or 4).  The first 2*nv CTAs also do one b/a row each.
+#define NEXRT_EVENT(i) do { if (a.events != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.events[i] = globaltimer_ns(); } while (0)
+
+template <int MP>
+__global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
+    constexpr int TERMS = MP <= 2 ? 3 : 2, NB = 8, KS = 8;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    NEXRT_EVENT(0);
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5;
+    const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
+    const int ba_row = static_cast<int>(blockIdx.x) < 2 * a.nv ? static_cast<int>(blockIdx.x) : -1;
+    const GemvGeom gb = gemv_geom(a.H / 8, blockDim.x);
+    float* xs = smem;                                                      // [MP][H]
+    float* gs = xs + static_cast<size_t>(MP) * a.H;                        // [H]
+    float* tiles = gs + a.H;                                               // [KS][16][8]
+    float* part_ba = tiles + KS * 128;                                     // [wpr][MP]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(part_ba + gemv_part_floats(1, MP, gb));   // [MP*TERMS][H]
+    const MmaPlain src{a.front_w, a.front_s, a.H};
+    MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
+    mw.preload(src);
+    NEXRT_EVENT(1);
+    RowNorm<4> norm;
+    norm.preload_gamma(a.in_ln, a.H);
+    float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (threadIdx.x < kRowsPerGroup && row0 + static_cast<int>(threadIdx.x) < a.C)
+        cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row0 + threadIdx.x) * 4);
+    NEXRT_EVENT(2);
+    pdl_wait();
+    NEXRT_EVENT(3);
+    const int C0 = a.ctl[kCtlCommittedLen];
+    for (int m0 = 0; m0 < a.M; m0 += MP) {
+        const int mb = min(MP, a.M - m0);
+        if (m0) { __syncthreads(); mw.preloaded = false; }
+        norm.template run<TERMS>(xq, ba_row >= 0 ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
+        NEXRT_EVENT(4);
+        float d[4];
+        mw.run(src, xq, a.H, mb * TERMS, d);
+        mw.store(tiles + warp * 128, d);
+        NEXRT_EVENT(5);
+        if (ba_row >= 0) gemv_cta<MP, 2>(PlainBf16{a.ba_w, a.H}, ba_row, 1, xs, a.H, part_ba);
+        __syncthreads();
+        NEXRT_EVENT(7);
+        if (threadIdx.x < kRowsPerGroup) {
+            float pre[MP];
 #pragma unroll
-                    for (int j = 0; j < 3; ++j) {
-                        const int mm = m - 3 + j;
-                        h[j] = (mm >= 0) ? pre[mm < 0 ? 0 : mm] : a.conv_ring[static_cast<size_t>((p - 3 + j + ring) % ring) * a.C + row];
-                    }
-                    const float v = fmaf(cw.x, h[0], fmaf(cw.y, h[1], fmaf(cw.z, h[2], cw.w * pre[m])));
-                    a.qkv[static_cast<size_t>(m0 + m) * a.C + row] = silu_f(v);
-                }
-            } else {
-                for (int m = 0; m < mb; ++m) a.z[static_cast<size_t>(m0 + m) * (a.R - a.C) + (row - a.C)] = pre[m];
-            }
+            for (int m = 0; m < MP; ++m) pre[m] = m < mb ? mma_result<TERMS>(tiles, 0, KS, threadIdx.x, m, kSplitDescale) : 0.f;
+            gdn_front_row<MP>(a, row0 + threadIdx.x, pre, m0, mb, C0, cw);
+        } else if (ba_row >= 0 && threadIdx.x >= 32 && threadIdx.x < 32 + mb) {
+            const int m = threadIdx.x - 32;
+            gdn_ba_row(a, ba_row, gemv_result(part_ba, 0, m, MP, gb.wpr), m0 + m);
         }
-        for (int rl = threadIdx.x; rl < nba; rl += blockDim.x) {
-            const int row = b0 + rl;     // [0, nv): b rows, [nv, 2nv): a rows
-            for (int m = 0; m < mb; ++m) {
-                const float v = gemv_result(part_ba, rl, m, MB, gb.wpr);
-                if (row < a.nv) a.beta[(m0 + m) * a.nv + row] = sigmoid_f(v);
-                else {
-                    const int h = row - a.nv;
-                    a.g[(m0 + m) * a.nv + h] = -__expf(a.a_log[h]) * softplus_f(v + a.dt_bias[h]);
-                }
-            }
-        }
+        NEXRT_EVENT(6);
     }
 }
 
@@ -149,6 +222,13 @@ __global__ void __launch_bounds__(256) gdn_core_kernel(GdnCoreArgs a) {
 
 using namespace nexrt;
 
+static unsigned long long* g_events = nullptr;
+// Optional event ring (8 x u64 device memory) filled by CTA 0 of the tensor-core front kernel.
+extern "C" int nexrt_set_event_ring(void* ring) {
+    g_events = static_cast<unsigned long long*>(ring);
+    return 0;
+}
+
 extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* front_w, const void* front_s, const void* ba_w,
                                const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv,
                                void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, float eps, int n_cta,
@@ -158,13 +238,22 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
                    static_cast<const float*>(front_s), static_cast<const __nv_bfloat16*>(ba_w), static_cast<const float*>(conv_w),
                    static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), static_cast<const int*>(ctl),
                    static_cast<float*>(conv_ring), static_cast<float*>(qkv), static_cast<float*>(z), static_cast<float*>(beta),
-                   static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, eps};
+                   static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, eps, g_events};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gemv_mode() == 1 && R % 16 == 0 && H % 512 == 0 && H <= 4096 && R / 16 >= 2 * nv) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = mp <= 2 ? 3 : 2;
+        const size_t smem = sizeof(float) * (static_cast<size_t>(mp + 1) * H + 8 * 128 + gemv_part_floats(1, mp, gemv_geom(H / 8, 256))) +
+                            static_cast<size_t>(mp) * terms * H;
+        dim3 g(R / 16), b(256);
+        if (mp == 1) return launch(gdn_front_mma_kernel<1>, g, b, smem, st, a);
+        if (mp == 2) return launch(gdn_front_mma_kernel<2>, g, b, smem, st, a);
+        return launch(gdn_front_mma_kernel<4>, g, b, smem, st, a);
+    }
     const int mb = M == 1 ? 1 : 4;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats((R + n_cta - 1) / n_cta, mb, gemv_geom(H / 16, 512)) +
-                                         gemv_part_floats((2 * nv + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, 512)));
-    if (M == 1) return launch(gdn_front_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
-    return launch(gdn_front_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb + 1) * H + gemv_part_floats((R + n_cta - 1) / n_cta, mb, gemv_geom(H / 16, gemv_threads())) +
+                                         gemv_part_floats((2 * nv + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, gemv_threads())));
+    if (M == 1) return launch(gdn_front_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+    return launch(gdn_front_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }
 
 extern "C" int nexrt_gdn_core(const void* qkv, const void* beta, const void* g, const void* ctl, void* state_ring, void* out, int nqk, int nv,

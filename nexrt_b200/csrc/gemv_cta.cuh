@@ -19,6 +19,17 @@
 
 namespace nexrt {
 
+// Threads per CTA of every GEMV-type kernel.  256 threads at <= 128 registers let the CTAs of two
+// consecutive kernels share an SM, which is what makes the early weight preload of the next
+// kernel overlap the tail of the current one under programmatic dependent launch.
+// (Kernels are compiled for up to 512 threads at <= 128 registers; the launch width is a run-time
+// setting so both shapes can be measured.)
+int& gemv_threads_ref();
+inline int gemv_threads() { return gemv_threads_ref(); }
+// 0: CUDA-core GEMV kernels, 1: tensor-core (mma) GEMV kernels where the shape allows.
+int& gemv_mode_ref();
+inline int gemv_mode() { return gemv_mode_ref(); }
+
 // ---- row sources ------------------------------------------------------------------------------
 // at(chunk) fixes the thread's chunk; ptr(r)/scale(r) then address row r of the CTA's range.
 
@@ -98,105 +109,140 @@ __device__ __forceinline__ void unpack_chunk(const uint4& v, float* f) {
     else unpack8_bf16(v, f);
 }
 
+// The GEMV as an object so that its first batch of weight loads can be issued BEFORE the
+// programmatic-dependency wait (weights are constants, so they may be fetched while the previous
+// kernel of the stream is still running) and consumed after the activation has been staged.
+//
+//   GemvCta<MB, U, Src> g(src, row0, nrows, Kx);   g.preload();   pdl_wait();   ... stage xs ...
+//   g.run(xs, part);   __syncthreads();   gemv_result(part, ...)
+//
 // xs: shared memory [MB][Kx] fp32 in natural order (Kx = chunks * EPL).  Rows [row0, row0+nrows).
-// part: shared memory [nrows][wpr][MB].  Caller must __syncthreads() before reading `part`.
+// part: shared memory [nrows][wpr][MB].
 template <int MB, int U, typename Src>
-__device__ __forceinline__ void gemv_cta(Src src, int row0, int nrows, const float* __restrict__ xs, int Kx, float* __restrict__ part) {
-    constexpr int EPL = Src::EPL;
-    const GemvGeom g = gemv_geom(Kx / EPL, blockDim.x);
-    const int tid = threadIdx.x, rsub = tid / g.tpr, kc = tid % g.tpr, lane = tid & 31;
-    const bool row_thread = rsub < g.rpp;
-    const int wir = g.tpr >= 32 ? kc >> 5 : 0;
-    for (int kb = 0; kb < g.kblocks; ++kb) {
-        const int chunk = kb * g.tpr + kc;
-        const bool live = row_thread && chunk < g.chunks;
-        float xr[MB][EPL];
-        if (live) {
-            src.at(chunk);
+struct GemvCta {
+    static constexpr int EPL = Src::EPL;
+    Src src;
+    GemvGeom g;
+    int row0, nrows, Kx, rsub, kc, lane, wir, jn;
+    bool row_thread, preloaded;
+    uint4 wv[U];
+    float sc[U];
+
+    __device__ __forceinline__ GemvCta(const Src& s, int r0, int nr, int kx) : src(s), row0(r0), nrows(nr), Kx(kx) {
+        g = gemv_geom(Kx / EPL, blockDim.x);
+        const int tid = threadIdx.x;
+        rsub = tid / g.tpr; kc = tid % g.tpr; lane = tid & 31;
+        row_thread = rsub < g.rpp;
+        wir = g.tpr >= 32 ? kc >> 5 : 0;
+        jn = (nrows + g.rpp - 1) / g.rpp;
+        preloaded = false;
+    }
+
+    __device__ __forceinline__ void load_batch(int j0, bool live) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int rl = (j0 + u) * g.rpp + rsub;
+            const bool ok = live && rl < nrows;
+            const int r = row0 + (ok ? rl : 0);
+            wv[u] = ok ? ld_stream16(src.ptr(r)) : make_uint4(0u, 0u, 0u, 0u);
+            sc[u] = ok ? src.scale(r) : 0.f;
+        }
+    }
+
+    // Issue the loads of the first batch (k-block 0).  Only for row sources that do not depend on
+    // data produced by earlier kernels of the step.
+    __device__ __forceinline__ void preload() {
+        const bool live = row_thread && kc < g.chunks;
+        src.at(live ? kc : 0);
+        load_batch(0, live);
+        preloaded = true;
+    }
+
+    __device__ __forceinline__ void run(const float* __restrict__ xs, float* __restrict__ part) {
+        for (int kb = 0; kb < g.kblocks; ++kb) {
+            const int chunk = kb * g.tpr + kc;
+            const bool live = row_thread && chunk < g.chunks;
+            float xr[MB][EPL];
+            if (!(preloaded && kb == 0)) src.at(live ? chunk : 0);
 #pragma unroll
             for (int m = 0; m < MB; ++m)
 #pragma unroll
                 for (int e = 0; e < EPL; e += 4) {
-                    const float4 v = *reinterpret_cast<const float4*>(xs + static_cast<size_t>(m) * Kx + chunk * EPL + e);
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (live) v = *reinterpret_cast<const float4*>(xs + static_cast<size_t>(m) * Kx + chunk * EPL + e);
                     xr[m][e] = v.x; xr[m][e + 1] = v.y; xr[m][e + 2] = v.z; xr[m][e + 3] = v.w;
                 }
-        } else {
-            src.at(0);
-#pragma unroll
-            for (int m = 0; m < MB; ++m)
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) xr[m][e] = 0.f;
-        }
-        for (int j0 = 0; j0 * g.rpp < nrows; j0 += U) {
-            uint4 wv[U];
-            float sc[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int rl = (j0 + u) * g.rpp + rsub;
-                const bool ok = live && rl < nrows;
-                const int r = row0 + (ok ? rl : 0);
-                wv[u] = ok ? ld_stream16(src.ptr(r)) : make_uint4(0u, 0u, 0u, 0u);
-                sc[u] = ok ? src.scale(r) : 0.f;
-            }
-            float acc[MB][U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                float wf[EPL];
-                unpack_chunk<EPL>(wv[u], wf);
-#pragma unroll
-                for (int m = 0; m < MB; ++m) {
-                    float a = 0.f;
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) a = fmaf(wf[e], xr[m][e], a);
-                    acc[m][u] = a * sc[u];
-                }
-            }
-            if (g.tpr >= 32) {
-                // transpose-reduce: U values per lane -> lane l ends with the warp total of value
-                // index sel(l); 2U-ish shuffles instead of 5U
-#pragma unroll
-                for (int m = 0; m < MB; ++m) {
-                    int sel = 0;
-#pragma unroll
-                    for (int w = U / 2, o = 16; w >= 1; w >>= 1, o >>= 1) {
-                        const bool hi = (lane & o) != 0;
-#pragma unroll
-                        for (int i = 0; i < w; ++i) {
-                            const float send = hi ? acc[m][i] : acc[m][i + w];
-                            const float keep = hi ? acc[m][i + w] : acc[m][i];
-                            acc[m][i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-                        }
-                        if (hi) sel += w;
-                    }
-#pragma unroll
-                    for (int o = 16 / U; o >= 1; o >>= 1) acc[m][0] += __shfl_xor_sync(0xffffffffu, acc[m][0], o);
-                    // lanes whose low bits are zero write: one writer per value index
-                    constexpr int kLow = 32 / U;
-                    if ((lane & (kLow - 1)) == 0) {
-                        const int rl = (j0 + sel) * g.rpp + rsub;
-                        if (row_thread && rl < nrows) {
-                            float* p = part + (static_cast<size_t>(rl) * g.wpr + wir) * MB + m;
-                            *p = (kb == 0 ? 0.f : *p) + acc[m][0];
-                        }
-                    }
-                }
-            } else {
+            for (int j0 = 0; j0 < jn; j0 += U) {
+                if (!(preloaded && kb == 0 && j0 == 0)) load_batch(j0, live);
+                float acc[MB][U];
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int rl = (j0 + u) * g.rpp + rsub;
+                    float wf[EPL];
+                    unpack_chunk<EPL>(wv[u], wf);
 #pragma unroll
                     for (int m = 0; m < MB; ++m) {
-                        float a = acc[m][u];
-                        for (int o = g.tpr >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                        if (kc == 0 && row_thread && rl < nrows) {
-                            float* p = part + (static_cast<size_t>(rl) * g.wpr + wir) * MB + m;
-                            *p = (kb == 0 ? 0.f : *p) + a;
+                        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                        for (int e = 0; e < EPL; e += 2) {
+                            a0 = fmaf(wf[e], xr[m][e], a0);
+                            a1 = fmaf(wf[e + 1], xr[m][e + 1], a1);
+                        }
+                        acc[m][u] = (a0 + a1) * sc[u];
+                    }
+                }
+                if (g.tpr >= 32) {
+                    // transpose-reduce: U values per lane -> lane l ends with the warp total of value
+                    // index sel(l); about 2U shuffles instead of 5U
+#pragma unroll
+                    for (int m = 0; m < MB; ++m) {
+                        int sel = 0;
+#pragma unroll
+                        for (int w = U / 2, o = 16; w >= 1; w >>= 1, o >>= 1) {
+                            const bool hi = (lane & o) != 0;
+#pragma unroll
+                            for (int i = 0; i < w; ++i) {
+                                const float send = hi ? acc[m][i] : acc[m][i + w];
+                                const float keep = hi ? acc[m][i + w] : acc[m][i];
+                                acc[m][i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                            }
+                            if (hi) sel += w;
+                        }
+#pragma unroll
+                        for (int o = 16 / U; o >= 1; o >>= 1) acc[m][0] += __shfl_xor_sync(0xffffffffu, acc[m][0], o);
+                        constexpr int kLow = 32 / U;   // lanes whose low bits are zero write: one writer per value
+                        if ((lane & (kLow - 1)) == 0) {
+                            const int rl = (j0 + sel) * g.rpp + rsub;
+                            if (row_thread && rl < nrows) {
+                                float* p = part + (static_cast<size_t>(rl) * g.wpr + wir) * MB + m;
+                                *p = (kb == 0 ? 0.f : *p) + acc[m][0];
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int rl = (j0 + u) * g.rpp + rsub;
+#pragma unroll
+                        for (int m = 0; m < MB; ++m) {
+                            float a = acc[m][u];
+                            for (int o = g.tpr >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                            if (kc == 0 && row_thread && rl < nrows) {
+                                float* p = part + (static_cast<size_t>(rl) * g.wpr + wir) * MB + m;
+                                *p = (kb == 0 ? 0.f : *p) + a;
+                            }
                         }
                     }
                 }
             }
         }
     }
+};
+
+// One-shot form (no early preload).
+template <int MB, int U, typename Src>
+__device__ __forceinline__ void gemv_cta(Src src, int row0, int nrows, const float* __restrict__ xs, int Kx, float* __restrict__ part) {
+    GemvCta<MB, U, Src> g(src, row0, nrows, Kx);
+    g.run(xs, part);
 }
 
 // Fixed-order sum of the partials of (row_local, m).
@@ -207,7 +253,8 @@ __device__ __forceinline__ float gemv_result(const float* part, int row_local, i
     return v;
 }
 
-// Stage rmsnorm(x) * gamma of `rows` bf16 rows into shared memory in natural order.
+// Stage rmsnorm(x) * gamma of `rows` bf16 rows into shared memory in natural order (gamma may
+// point at shared memory that was filled before the dependency wait).
 __device__ __forceinline__ void stage_rmsnorm_plain(float* xs, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, int rows,
                                                     int H, float eps, float* red) {
     for (int r = 0; r < rows; ++r) {

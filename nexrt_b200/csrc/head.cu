@@ -218,16 +218,21 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     float* xs = smem;                                                                   // [MB][H]
     float* part = xs + static_cast<size_t>(MB) * a.H;                                   // [kTile][wpr][MB]
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(part + gemv_part_floats(kTile, MB, gg));   // [MB][nv_max]
+    float* gs = reinterpret_cast<float*>(keys + static_cast<size_t>(MB) * nv_max);                                // [H] norm multiplier
+    GemvCta<MB, (MB == 1 ? 8 : 4), PlainBf16> gemv0(PlainBf16{a.w, a.H}, v0, min(kTile, nv), a.H);
+    gemv0.preload();
+    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.final_ln[i];
     pdl_wait();
     const SamplingCfg cfg = read_sampling(a.sampling);
     const int K = a.mode == 2 ? 1 : cfg.top_k;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.final_ln, mb, a.H, a.eps, red);
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
         for (int t0 = 0; t0 < nv; t0 += kTile) {
             const int nt = min(kTile, nv - t0);
-            gemv_cta<MB, (MB == 1 ? 8 : 4)>(PlainBf16{a.w, a.H}, v0 + t0, nt, xs, a.H, part);
+            if (m0 == 0 && t0 == 0) gemv0.run(xs, part);
+            else gemv_cta<MB, (MB == 1 ? 8 : 4)>(PlainBf16{a.w, a.H}, v0 + t0, nt, xs, a.H, part);
             __syncthreads();
             for (int idx = threadIdx.x; idx < nt * mb; idx += blockDim.x) {
                 const int rl = idx / mb, m = idx % mb, row = v0 + t0 + rl;
@@ -400,11 +405,11 @@ extern "C" int nexrt_lmhead_sample(const void* x, const void* final_ln, const vo
     a.H = H; a.V_local = V_local; a.vocab_base = vocab_base; a.M = M; a.eps = eps; a.mode = mode; a.arg = arg; a.ch = *ch; a.site = site;
     const int mb = M == 1 ? 1 : 4;
     const int nv_max = (V_local + n_cta - 1) / n_cta;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, 512))) +
-                        sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, gemv_threads()))) +
+                        sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max + sizeof(float) * H;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (mb == 1) return launch(lmhead_sample_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
-    return launch(lmhead_sample_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
+    if (mb == 1) return launch(lmhead_sample_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+    return launch(lmhead_sample_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }
 
 extern "C" int nexrt_sample_logits(const void* logits, const void* sampling, void* ctl, int V, int position_base, void* stream) {

@@ -19,6 +19,7 @@
 #include "epilogue.cuh"
 #include "gemv.cuh"
 #include "gemv_cta.cuh"
+#include "mma_gemv.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -52,12 +53,17 @@ __global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
     const GemvGeom gg = gemv_geom(a.H / 8, blockDim.x);
     float* xs = smem;
     float* part = xs + static_cast<size_t>(MB) * a.H;
+    float* gs = part + gemv_part_floats((rows + gridDim.x - 1) / gridDim.x, MB, gg);   // [H] norm multiplier
+    GemvCta<MB, U, PlainBf16> gemv(PlainBf16{a.w, a.H}, r0, nrows, a.H);
+    gemv.preload();
+    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.post_ln[i];
     pdl_wait();
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, a.post_ln, mb, a.H, a.eps, red);
-        gemv_cta<MB, U>(PlainBf16{a.w, a.H}, r0, nrows, xs, a.H, part);
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
+        if (m0 == 0) gemv.run(xs, part);
+        else gemv_cta<MB, U>(PlainBf16{a.w, a.H}, r0, nrows, xs, a.H, part);
         __syncthreads();
         for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
             const int rl = idx / mb, m = idx % mb;
@@ -146,11 +152,13 @@ __global__ void __launch_bounds__(512, 1) moe_l1_kernel(MoeL1Args a) {
     const GemvGeom gg = gemv_geom(a.H / 16, blockDim.x);
     float* xs = smem;                 // [H]
     float* part = xs + a.H;
+    float* gs = part + gemv_part_floats((vrows + gridDim.x - 1) / gridDim.x, 1, gg);   // [H] norm multiplier
+    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.post_ln[i];
     pdl_wait();
     for (int m = 0; m < a.M; ++m) {
         if (m) __syncthreads();
         if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m) * a.H, a.post_ln, 1, a.H, a.eps, red);
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m) * a.H, gs, 1, a.H, a.eps, red);
         gemv_cta<1, 8>(ExpertUp{a.w13, a.w13_s, s_ids, a.H, I2}, v0, nrows, xs, a.H, part);
         __syncthreads();
         for (int rl = threadIdx.x; rl < nrows; rl += blockDim.x)
@@ -202,6 +210,87 @@ __global__ void __launch_bounds__(512, 1) moe_l2_allreduce_kernel(MoeL2Args a) {
     allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
 }
 
+// ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
+// Expert gate/up: one CTA per 16 virtual rows (slot, i), the 8 warps split K = H.
+__global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
+    constexpr int TERMS = 3, NB = 8, KS = 8;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    __shared__ int s_ids[16];
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5;
+    const int I2 = 2 * a.I, vrows = a.S * I2;
+    const int v0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
+    float* tiles = smem;                                             // [KS][16][8]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(tiles + KS * 128);      // [TERMS][H]
+    const bool shared_rows = v0 >= (a.S - 1) * I2;                   // the shared expert is known before routing
+    if (threadIdx.x == 0) s_ids[a.S - 1] = a.shared_expert;
+    __syncthreads();
+    const MmaExpertUp src{a.w13, a.w13_s, s_ids, a.H, I2};
+    MmaWarp<NB, MmaExpertUp> mw(v0, warp, KS, nwin);
+    if (shared_rows) mw.preload(src);
+    RowNorm<4> norm;
+    norm.preload_gamma(a.post_ln, a.H);
+    pdl_wait();
+    for (int m = 0; m < a.M; ++m) {
+        if (m) { __syncthreads(); mw.preloaded = false; }
+        if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
+        norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m) * a.H, 1, a.H, a.eps, red);
+        float d[4];
+        mw.run(src, xq, a.H, TERMS, d);
+        mw.store(tiles + warp * 128, d);
+        __syncthreads();
+        if (threadIdx.x < kRowsPerGroup)
+            a.gu[static_cast<size_t>(m) * vrows + v0 + threadIdx.x] = mma_result<TERMS>(tiles, 0, KS, threadIdx.x, 0, kSplitDescale);
+    }
+}
+
+// Expert down + all-reduce + residual: one CTA per 16 output rows, warps split the virtual K = S x I.
+__global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args a) {
+    constexpr int TERMS = 3, NB = 4;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    __shared__ float descale[1];
+    __shared__ int s_ids[16];
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int row0 = blockIdx.x * kRowsPerGroup;
+    const int VK = a.S * a.I, nwin = VK / kWin;
+    const int KS = min(nwarps, nwin);
+    float* hs = smem;                                                // [VK]
+    float* tiles = hs + VK;                                          // [8][16][8]
+    float* res = tiles + 8 * 128;                                    // [kMaxRows][16]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(res + kMaxRows * kRowsPerGroup);   // [TERMS][VK]
+    const MmaExpertDown src{a.w2, a.w2_s, s_ids, a.H, a.I};
+    pdl_wait();
+    for (int m = 0; m < a.M; ++m) {
+        if (m) __syncthreads();
+        if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
+        __syncthreads();
+        MmaWarp<NB, MmaExpertDown> mw(row0, warp, KS, warp < KS ? nwin : 0);
+        mw.preload(src);                                             // weights stream while h is being built
+        // h = silu(gate) * up * route weight
+#pragma unroll 2
+        for (int k = threadIdx.x * 4; k < VK; k += blockDim.x * 4) {
+            const int sl = k / a.I, i = k % a.I;
+            const float* g = a.gu + (static_cast<size_t>(m) * a.S + sl) * 2 * a.I;
+            const float4 gt = *reinterpret_cast<const float4*>(g + i), up = *reinterpret_cast<const float4*>(g + a.I + i);
+            const float wt = a.wts[m * a.S + sl];
+            *reinterpret_cast<float4*>(hs + k) =
+                make_float4(silu_f(gt.x) * up.x * wt, silu_f(gt.y) * up.y * wt, silu_f(gt.z) * up.z * wt, silu_f(gt.w) * up.w * wt);
+        }
+        __syncthreads();
+        act_split<TERMS>(xq, hs, 1, VK, red, descale);
+        float d[4];
+        mw.run(src, xq, VK, TERMS, d);
+        if (warp < KS) mw.store(tiles + warp * 128, d);
+        __syncthreads();
+        if (threadIdx.x < kRowsPerGroup) res[m * kRowsPerGroup + threadIdx.x] = mma_result<TERMS>(tiles, 0, KS, threadIdx.x, 0, descale[0]);
+    }
+    __syncthreads();
+    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x);
+}
+
 }  // namespace nexrt
 
 using namespace nexrt;
@@ -213,9 +302,9 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
                  static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), static_cast<int*>(ticket), H, E, topk, M, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int mb = M == 1 ? 1 : 4;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats((E + 1 + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, 512)));
-    if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(512), smem, st, a);
-    return launch(moe_router_kernel<4>, dim3(n_cta), dim3(512), smem, st, a);
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb + 1) * H + gemv_part_floats((E + 1 + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, gemv_threads())));
+    if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+    return launch(moe_router_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }
 
 extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I,
@@ -224,8 +313,12 @@ extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13,
     MoeL1Args a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const uint8_t*>(w13),
                 static_cast<const float*>(w13_s), static_cast<const int*>(ids), static_cast<float*>(gu), H, I, S, M, eps, shared_expert};
     const int vrows = S * 2 * I;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(H) + gemv_part_floats((vrows + n_cta - 1) / n_cta, 1, gemv_geom(H / 16, 512)));
-    return launch(moe_l1_kernel, dim3(n_cta), dim3(512), smem, static_cast<cudaStream_t>(stream), a);
+    if (gemv_mode() == 1 && H % 512 == 0 && H <= 4096) {
+        const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H;
+        return launch(moe_l1_mma_kernel, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
+    }
+    const size_t smem = sizeof(float) * (static_cast<size_t>(2) * H + gemv_part_floats((vrows + n_cta - 1) / n_cta, 1, gemv_geom(H / 16, gemv_threads())));
+    return launch(moe_l1_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
 }
 
 extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I,
@@ -236,8 +329,13 @@ extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const voi
     a.gu = static_cast<const float*>(gu); a.ids = static_cast<const int*>(ids); a.wts = static_cast<const float*>(wts);
     a.w2 = static_cast<const uint8_t*>(w2); a.w2_s = static_cast<const float*>(w2_s); a.x = static_cast<__nv_bfloat16*>(x);
     a.H = H; a.I = I; a.S = S; a.M = M; a.ch = *ch; a.site = site;
+    if (gemv_mode() == 1 && H % 16 == 0) {
+        const size_t VK = static_cast<size_t>(S) * I;
+        const size_t smem_mma = sizeof(float) * (VK + 8 * 128 + kMaxRows * 16) + 3 * VK;
+        return launch(moe_l2_allreduce_mma_kernel, dim3(H / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
+    }
     const int max_rows = (H + n_cta - 1) / n_cta;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(S) * I + gemv_part_floats(max_rows, 1, gemv_geom(S * I / 16, 512)) +
+    const size_t smem = sizeof(float) * (static_cast<size_t>(S) * I + gemv_part_floats(max_rows, 1, gemv_geom(S * I / 16, gemv_threads())) +
                                          static_cast<size_t>(kMaxRows) * max_rows);
-    return launch(moe_l2_allreduce_kernel, dim3(n_cta), dim3(512), smem, static_cast<cudaStream_t>(stream), a);
+    return launch(moe_l2_allreduce_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
 }

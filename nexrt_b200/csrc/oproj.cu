@@ -18,6 +18,7 @@
 #include "epilogue.cuh"
 #include "gemv.cuh"
 #include "gemv_cta.cuh"
+#include "mma_gemv.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -51,6 +52,8 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
     float* xs = smem;                                        // [MB][K]
     float* part = xs + static_cast<size_t>(MB) * a.K;        // [max_rows][wpr][MB]
     float* res = part + gemv_part_floats(max_rows, MB, gg);  // [kMaxRows][nrows]
+    GemvCta<MB, U, PlainFp8> gemv(PlainFp8{a.w, a.s, a.K}, row0, nrows, a.K);
+    gemv.preload();
     pdl_wait();
     LLCall cpcall{0u, 0u};
     if (a.mode == 2) cpcall = ll_begin(a.cp, a.cp_site);
@@ -103,7 +106,8 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
             }
         }
         __syncthreads();
-        gemv_cta<MB, U>(PlainFp8{a.w, a.s, a.K}, row0, nrows, xs, a.K, part);
+        if (m0 == 0) gemv.run(xs, part);
+        else gemv_cta<MB, U>(PlainFp8{a.w, a.s, a.K}, row0, nrows, xs, a.K, part);
         __syncthreads();
         for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
             const int rl = idx / mb, m = idx % mb;
@@ -112,6 +116,89 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
     }
     __syncthreads();
     allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
+}
+
+// Tensor-core form: one CTA per 16 output rows, the 8 warps split K (see mma_gemv.cuh); the CTA
+// that computed the rows reduces them across the ranks and updates the residual.
+template <int MP>
+__global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a) {
+    constexpr int TERMS = MP <= 2 ? 3 : 2, NB = 8;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    __shared__ float descale[MP];
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.K / kWin;
+    const int KS = min(nwarps, nwin);                                   // warps that share the K range
+    float* xs = smem;                                                   // [MP][K]
+    float* tiles = xs + static_cast<size_t>(MP) * a.K;                  // [KS][16][8]
+    float* res = tiles + 8 * 128;                                       // [kMaxRows][16]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(res + kMaxRows * kRowsPerGroup);   // [MP*TERMS][K]
+    const MmaPlain src{a.w, a.s, a.K};
+    MmaWarp<NB, MmaPlain> mw(row0, warp, KS, warp < KS ? nwin : 0);
+    mw.preload(src);
+    pdl_wait();
+    LLCall cpcall{0u, 0u};
+    if (a.mode == 2) cpcall = ll_begin(a.cp, a.cp_site);
+    for (int m0 = 0; m0 < a.M; m0 += MP) {
+        const int mb = min(MP, a.M - m0);
+        if (m0) { __syncthreads(); mw.preloaded = false; }
+        if (a.mode == 0) {
+            for (int idx = threadIdx.x * 4; idx < mb * a.K; idx += blockDim.x * 4)
+                *reinterpret_cast<float4*>(xs + idx) = *reinterpret_cast<const float4*>(a.in + static_cast<size_t>(m0) * a.K + idx);
+        } else if (a.mode == 1) {
+            const int heads = a.K / 128;
+            const float4 gw = *reinterpret_cast<const float4*>(a.gnorm_w + lane * 4);
+            for (int v = warp; v < mb * heads; v += nwarps) {
+                const int m = v / heads, h = v % heads;
+                const size_t base = static_cast<size_t>(m0 + m) * a.K + h * 128 + lane * 4;
+                const float4 o = *reinterpret_cast<const float4*>(a.in + base);
+                const float4 zz = *reinterpret_cast<const float4*>(a.z + base);
+                const float inv = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) / 128.f + a.eps);
+                float4 r;
+                r.x = gw.x * o.x * inv * silu_f(zz.x);
+                r.y = gw.y * o.y * inv * silu_f(zz.y);
+                r.z = gw.z * o.z * inv * silu_f(zz.z);
+                r.w = gw.w * o.w * inv * silu_f(zz.w);
+                *reinterpret_cast<float4*>(xs + m * a.K + h * 128 + lane * 4) = r;
+            }
+        } else {
+            const int hd = a.hd, heads = a.K / hd;
+            for (int idx = threadIdx.x; idx < mb * a.K; idx += blockDim.x) {
+                const int m = idx / a.K, k = idx % a.K, lh = k / hd, d = k % hd;
+                const unsigned int base = (static_cast<unsigned int>(m0 + m) * heads + lh) * (hd + 1);
+                float lse[kMaxWorld], ctx[kMaxWorld], mx = -INFINITY;
+                for (int sr = 0; sr < a.cp.world; ++sr) {
+                    unsigned int pl, pc;
+                    ll_wait(a.cp, cpcall, sr, base + hd, &pl, kStatusCpTimeout);
+                    ll_wait(a.cp, cpcall, sr, base + d, &pc, kStatusCpTimeout);
+                    lse[sr] = __uint_as_float(pl);
+                    ctx[sr] = __uint_as_float(pc);
+                    mx = fmaxf(mx, lse[sr]);
+                }
+                float num = 0.f, den = 0.f;
+                for (int sr = 0; sr < a.cp.world; ++sr) {
+                    const float wgt = lse[sr] == -INFINITY ? 0.f : exp2f(lse[sr] - mx);
+                    num = fmaf(wgt, ctx[sr], num);
+                    den += wgt;
+                }
+                const float gt = a.z[static_cast<size_t>(m0 + m) * a.K + k];
+                xs[m * a.K + k] = (den > 0.f ? num / den : 0.f) * sigmoid_f(gt);
+            }
+        }
+        __syncthreads();
+        act_split<TERMS>(xq, xs, mb, a.K, red, descale);
+        float d[4];
+        mw.run(src, xq, a.K, mb * TERMS, d);
+        if (warp < KS) mw.store(tiles + warp * 128, d);
+        __syncthreads();
+        if (threadIdx.x < kRowsPerGroup * mb) {
+            const int rl = threadIdx.x % kRowsPerGroup, m = threadIdx.x / kRowsPerGroup;
+            res[(m0 + m) * kRowsPerGroup + rl] = mma_result<TERMS>(tiles, 0, KS, rl, m, descale[m]);
+        }
+    }
+    __syncthreads();
+    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x);
 }
 
 }  // namespace nexrt
@@ -130,11 +217,19 @@ extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* 
     a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.eps = eps; a.ch = *ch; a.site = site;
     if (cp) { a.cp = *cp; a.cp_site = cp_site; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gemv_mode() == 1 && H % 16 == 0 && K % 64 == 0) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = mp <= 2 ? 3 : 2;
+        const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * K + 8 * 128 + kMaxRows * 16) + static_cast<size_t>(mp) * terms * K;
+        dim3 g(H / 16), b(256);
+        if (mp == 1) return launch(oproj_allreduce_mma_kernel<1>, g, b, smem_mma, st, a);
+        if (mp == 2) return launch(oproj_allreduce_mma_kernel<2>, g, b, smem_mma, st, a);
+        return launch(oproj_allreduce_mma_kernel<4>, g, b, smem_mma, st, a);
+    }
     const int mb = M == 1 ? 1 : 4;
     const int max_rows = (H + n_cta - 1) / n_cta;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * K + gemv_part_floats(max_rows, mb, gemv_geom(K / 16, 512)) +
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * K + gemv_part_floats(max_rows, mb, gemv_geom(K / 16, gemv_threads())) +
                                          static_cast<size_t>(kMaxRows) * max_rows);
-    dim3 g(n_cta), b(512);
+    dim3 g(n_cta), b(gemv_threads());
     if (mb == 1) return launch(oproj_allreduce_kernel<1>, g, b, smem, st, a);
     return launch(oproj_allreduce_kernel<4>, g, b, smem, st, a);
 }

@@ -7,8 +7,19 @@
 // ResidualAddKernel (…util/nex_n2_5_pro_residual_add_ctypes.cu:30-43).
 #include "api.h"
 #include "common.cuh"
+#include "gemv_cta.cuh"
 
 namespace nexrt {
+
+int& gemv_threads_ref() {
+    static int threads = 512;
+    return threads;
+}
+
+int& gemv_mode_ref() {
+    static int mode = 1;
+    return mode;
+}
 
 int& pdl_enabled() {
     static int enabled = 1;
@@ -70,6 +81,15 @@ extern "C" int nexrt_set_pdl(int enabled) {
     return 0;
 }
 extern "C" int nexrt_version(void) { return 100; }
+extern "C" int nexrt_set_gemv_mode(int mode) {
+    gemv_mode_ref() = mode ? 1 : 0;
+    return 0;
+}
+extern "C" int nexrt_set_gemv_threads(int threads) {
+    if (threads != 256 && threads != 512) return cudaErrorInvalidValue;
+    gemv_threads_ref() = threads;
+    return 0;
+}
 
 extern "C" int nexrt_embed_gather(const void* embed, const void* ctl, void* x, void* status, int H, int vocab, int M, void* stream) {
     if (M < 1 || M > kMaxRows || H % 8) return cudaErrorInvalidValue;

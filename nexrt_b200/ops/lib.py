@@ -41,6 +41,9 @@ CH = POINTER(LLChannelStruct)
 _PROTOTYPES = {
     "nexrt_set_pdl": [ci],
     "nexrt_version": [],
+    "nexrt_set_gemv_threads": [ci],
+    "nexrt_set_event_ring": [vp],
+    "nexrt_set_gemv_mode": [ci],
     "nexrt_embed_gather": [vp, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_step_end": [vp, vp, cu, vp, vp, ci, vp],
     "nexrt_residual_add": [vp, vp, ci, vp],

@@ -22,12 +22,20 @@ def main() -> None:
     p.add_argument("--shrunk", action="store_true")
     p.add_argument("--tp", type=int, default=1, help="use the shard shapes of one rank of a tp-wide group (no communication)")
     p.add_argument("--graph", action="store_true", help="time captured-graph replays and print us/step")
+    p.add_argument("--no-pdl", action="store_true")
+    p.add_argument("--threads", type=int, default=0)
     a = p.parse_args()
     from ..config import full_config, shrunk_config
     from ..decode_engine import DecodeEngine
     from ..runtime.control import Ctl
     from ..weights import random_rank_model
 
+    from ..ops import lib as L
+
+    if a.no_pdl:
+        L.load().nexrt_set_pdl(0)
+    if a.threads:
+        L.load().nexrt_set_gemv_threads(a.threads)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     cfg = shrunk_config() if a.shrunk else full_config().truncated(a.layers)
