@@ -97,14 +97,14 @@ __global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
 // Tensor-core form: one CTA per 16 weight rows, 8 warps split K (see mma_gemv.cuh).
 template <int MP>
 __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a) {
-    constexpr int TERMS = MP <= 2 ? 3 : 2, NB = 8, KS = 8;
+    constexpr int TERMS = MmaShape<MP>::TERMS, NT = MmaShape<MP>::NT, TILE = MmaShape<MP>::TILE, NB = 8, KS = 8;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
     float* tiles = smem;                                              // [KS][16][8]
-    uint8_t* xq = reinterpret_cast<uint8_t*>(tiles + KS * 128);       // [MP*TERMS][H]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(tiles + KS * TILE);       // [MP*TERMS][H]
     const MmaPlain src{a.w, a.s, a.H};
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
     mw.preload(src);
@@ -117,13 +117,13 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
         const int mb = min(MP, a.M - m0);
         if (m0) { __syncthreads(); mw.preloaded = false; }
         norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
-        float d[4];
-        mw.run(src, xq, a.H, mb * TERMS, d);
-        mw.store(tiles + warp * 128, d);
+        float d[NT][4];
+        mw.template run<NT>(src, xq, a.H, mb * TERMS, d);
+        mw.template store<NT>(tiles + warp * TILE, d);
         __syncthreads();
         if (threadIdx.x < kRowsPerGroup * mb) {
             const int rl = threadIdx.x % kRowsPerGroup, m = threadIdx.x / kRowsPerGroup;
-            attn_front_row(a, row0 + rl, m0 + m, mma_result<TERMS>(tiles, 0, KS, rl, m, kSplitDescale), C0, interleaved);
+            attn_front_row(a, row0 + rl, m0 + m, mma_result<TERMS, NT>(tiles, KS, rl, m, kSplitDescale), C0, interleaved);
         }
     }
 }
@@ -395,9 +395,9 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
                     static_cast<float*>(k_raw), static_cast<__nv_bfloat16*>(v_cache), H, hd, nq, ngate, kvh, M, cache_len, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int R = (nq + ngate + 2 * kvh) * hd;
-    if (gemv_mode() == 1 && H % 512 == 0 && H <= 4096) {
-        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = mp <= 2 ? 3 : 2;
-        const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(mp) * terms * H;
+    if ((gemv_mode() & 1) && H % 512 == 0 && H <= 4096) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
+        const size_t smem_mma = sizeof(float) * 8 * 256 + static_cast<size_t>(mp) * terms * H;
         dim3 g(R / 16), b(256);
         if (mp == 1) return launch(attn_front_mma_kernel<1>, g, b, smem_mma, st, a);
         if (mp == 2) return launch(attn_front_mma_kernel<2>, g, b, smem_mma, st, a);

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
 
 template <int MP>
 __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
-    constexpr int TERMS = MP <= 2 ? 3 : 2, NB = 8, KS = 8;
+    constexpr int TERMS = MmaShape<MP>::TERMS, NT = MmaShape<MP>::NT, TILE = MmaShape<MP>::TILE, NB = 8, KS = 8;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     NEXRT_EVENT(0);
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     float* xs = smem;                                                      // [MP][H]
     float* gs = xs + static_cast<size_t>(MP) * a.H;                        // [H]
     float* tiles = gs + a.H;                                               // [KS][16][8]
-    float* part_ba = tiles + KS * 128;                                     // [wpr][MP]
+    float* part_ba = tiles + KS * TILE;                                     // [wpr][MP]
     uint8_t* xq = reinterpret_cast<uint8_t*>(part_ba + gemv_part_floats(1, MP, gb));   // [MP*TERMS][H]
     const MmaPlain src{a.front_w, a.front_s, a.H};
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
@@ -158,9 +158,9 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         if (m0) { __syncthreads(); mw.preloaded = false; }
         norm.template run<TERMS>(xq, ba_row >= 0 ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
         NEXRT_EVENT(4);
-        float d[4];
-        mw.run(src, xq, a.H, mb * TERMS, d);
-        mw.store(tiles + warp * 128, d);
+        float d[NT][4];
+        mw.template run<NT>(src, xq, a.H, mb * TERMS, d);
+        mw.template store<NT>(tiles + warp * TILE, d);
         NEXRT_EVENT(5);
         if (ba_row >= 0) gemv_cta<MP, 2>(PlainBf16{a.ba_w, a.H}, ba_row, 1, xs, a.H, part_ba);
         __syncthreads();
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         if (threadIdx.x < kRowsPerGroup) {
             float pre[MP];
 #pragma unroll
-            for (int m = 0; m < MP; ++m) pre[m] = m < mb ? mma_result<TERMS>(tiles, 0, KS, threadIdx.x, m, kSplitDescale) : 0.f;
+            for (int m = 0; m < MP; ++m) pre[m] = m < mb ? mma_result<TERMS, NT>(tiles, KS, threadIdx.x, m, kSplitDescale) : 0.f;
             gdn_front_row<MP>(a, row0 + threadIdx.x, pre, m0, mb, C0, cw);
         } else if (ba_row >= 0 && threadIdx.x >= 32 && threadIdx.x < 32 + mb) {
             const int m = threadIdx.x - 32;
@@ -240,9 +240,9 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
                    static_cast<float*>(conv_ring), static_cast<float*>(qkv), static_cast<float*>(z), static_cast<float*>(beta),
                    static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, eps, g_events};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (gemv_mode() == 1 && R % 16 == 0 && H % 512 == 0 && H <= 4096 && R / 16 >= 2 * nv) {
-        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = mp <= 2 ? 3 : 2;
-        const size_t smem = sizeof(float) * (static_cast<size_t>(mp + 1) * H + 8 * 128 + gemv_part_floats(1, mp, gemv_geom(H / 8, 256))) +
+    if ((gemv_mode() & 1) && R % 16 == 0 && H % 512 == 0 && H <= 4096 && R / 16 >= 2 * nv) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
+        const size_t smem = sizeof(float) * (static_cast<size_t>(mp + 1) * H + 8 * 256 + gemv_part_floats(1, mp, gemv_geom(H / 8, 256))) +
                             static_cast<size_t>(mp) * terms * H;
         dim3 g(R / 16), b(256);
         if (mp == 1) return launch(gdn_front_mma_kernel<1>, g, b, smem, st, a);

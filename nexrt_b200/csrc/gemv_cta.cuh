@@ -26,7 +26,8 @@ namespace nexrt {
 // setting so both shapes can be measured.)
 int& gemv_threads_ref();
 inline int gemv_threads() { return gemv_threads_ref(); }
-// 0: CUDA-core GEMV kernels, 1: tensor-core (mma) GEMV kernels where the shape allows.
+// Bit mask of the kernels that use the tensor-core GEMV where the shape allows (1: projection
+// fronts, 2: out-projection, 4: expert gate/up, 8: expert down); 0 selects the CUDA-core kernels.
 int& gemv_mode_ref();
 inline int gemv_mode() { return gemv_mode_ref(); }
 

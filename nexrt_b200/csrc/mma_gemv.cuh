@@ -5,8 +5,8 @@
 // weight bytes go from global memory to registers and straight into the tensor cores, which do
 // the decode and the multiply-accumulate in fp32.  FP8 x FP8 needs an FP8 activation, so the
 // activation is split exactly into a sum of e4m3 terms,
-//     x * 2^ex = t1 + t2 + t3,   t1 = e4m3(x'), t2 = e4m3(x' - t1), t3 = e4m3(x' - t1 - t2),
-// (relative error 2^-12, better than bf16), and the terms occupy separate columns of the N=8
+//     x' = t1 + t2 / 16 + t3 / 256,   t1 = e4m3(x'), t2 = e4m3(16 (x' - t1)), t3 = e4m3(16 (16 (x' - t1) - t2)),
+// (relative error 2^-12, better than bf16; the factor 16 keeps every term in e4m3's normal range), and the terms occupy separate columns of the N=8
 // operand: D[16 rows][8] += W[16][32] * T[32][8].  The per-128x128-block weight scale multiplies
 // the fp32 partial of each 64-byte k-window (`acc += scale * partial`, the arithmetic of the
 // reference's CUDA-core kernels, e.g. nex_n2_5_pro/kernels/full_attn/
@@ -47,6 +47,8 @@ __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
 // absolute resolution; saturation of the first term is absorbed by the later terms.
 constexpr float kSplitScale = 2.0f;
 constexpr float kSplitDescale = 0.5f;
+constexpr float kTermStep = 16.0f;        // scale between consecutive split terms
+constexpr float kTermInv = 1.0f / 16.0f;
 
 // e4m3 split of 4 values at once: TERMS packed words (byte i of word t = term t of value i).
 template <int TERMS>
@@ -58,8 +60,11 @@ __device__ __forceinline__ void split4(float (&r)[4], uint32_t (&out)[TERMS]) {
         asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(r[3]), "f"(r[2]));
         out[term] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
         if (term + 1 < TERMS) {
+            // the residual is re-scaled by 16 so that every term uses the normal range of e4m3
+            // (min normal 2^-6) instead of dying in its subnormals: x' = t1 + t2 / 16 + t3 / 256
             const float2 a = e4m3x2_to_float2(lo), b = e4m3x2_to_float2(hi);
-            r[0] -= a.x; r[1] -= a.y; r[2] -= b.x; r[3] -= b.y;
+            r[0] = (r[0] - a.x) * kTermStep; r[1] = (r[1] - a.y) * kTermStep;
+            r[2] = (r[2] - b.x) * kTermStep; r[3] = (r[3] - b.y) * kTermStep;
         }
     }
 }
@@ -285,43 +290,58 @@ struct MmaWarp {
     // Only for sources that do not depend on data written by earlier kernels of the step.
     __device__ __forceinline__ void preload(const Src& src) { load(src, w0); preloaded = true; }
 
-    // xq: shared memory [ncols][Kx] byte planes; columns >= ncols are zero.
-    __device__ __forceinline__ void run(const Src& src, const uint8_t* xq, int Kx, int ncols, float (&d)[4]) {
-        d[0] = d[1] = d[2] = d[3] = 0.f;
+    // xq: shared memory [ncols][Kx] byte planes; columns >= ncols are zero.  NT n-tiles of 8 columns.
+    template <int NT>
+    __device__ __forceinline__ void run(const Src& src, const uint8_t* xq, int Kx, int ncols, float (&d)[NT][4]) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
         for (int wbase = w0; wbase < nwin; wbase += NB * wstride) {
             if (!(preloaded && wbase == w0)) load(src, wbase);
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
                 const int win = wbase + i * wstride;
                 if (win >= nwin) break;                 // uniform across the warp
-                uint4 xb = make_uint4(0u, 0u, 0u, 0u);
-                if (g < ncols) xb = *reinterpret_cast<const uint4*>(xq + static_cast<size_t>(g) * Kx + win * kWin + t * 16);
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_e4m3_16x8x32(c, ra[i].x, rb[i].x, ra[i].y, rb[i].y, xb.x, xb.y);
-                mma_e4m3_16x8x32(c, ra[i].z, rb[i].z, ra[i].w, rb[i].w, xb.z, xb.w);
-                d[0] = fmaf(c[0], slo[i], d[0]); d[1] = fmaf(c[1], slo[i], d[1]);
-                d[2] = fmaf(c[2], shi[i], d[2]); d[3] = fmaf(c[3], shi[i], d[3]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int col = nt * 8 + g;
+                    uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+                    if (col < ncols) xb = *reinterpret_cast<const uint4*>(xq + static_cast<size_t>(col) * Kx + win * kWin + t * 16);
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_e4m3_16x8x32(c, ra[i].x, rb[i].x, ra[i].y, rb[i].y, xb.x, xb.y);
+                    mma_e4m3_16x8x32(c, ra[i].z, rb[i].z, ra[i].w, rb[i].w, xb.z, xb.w);
+                    d[nt][0] = fmaf(c[0], slo[i], d[nt][0]); d[nt][1] = fmaf(c[1], slo[i], d[nt][1]);
+                    d[nt][2] = fmaf(c[2], shi[i], d[nt][2]); d[nt][3] = fmaf(c[3], shi[i], d[nt][3]);
+                }
             }
         }
     }
-    // Write the accumulator tile to shared memory: tile[16 rows][8 cols].
-    __device__ __forceinline__ void store(float* tile, const float (&d)[4]) const {
-        tile[g * 8 + 2 * t] = d[0]; tile[g * 8 + 2 * t + 1] = d[1];
-        tile[(g + 8) * 8 + 2 * t] = d[2]; tile[(g + 8) * 8 + 2 * t + 1] = d[3];
+    // Write the accumulator tile to shared memory: tile[16 rows][8 * NT cols].
+    template <int NT>
+    __device__ __forceinline__ void store(float* tile, const float (&d)[NT][4]) const {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            tile[g * 8 * NT + nt * 8 + 2 * t] = d[nt][0]; tile[g * 8 * NT + nt * 8 + 2 * t + 1] = d[nt][1];
+            tile[(g + 8) * 8 * NT + nt * 8 + 2 * t] = d[nt][2]; tile[(g + 8) * 8 * NT + nt * 8 + 2 * t + 1] = d[nt][3];
+        }
     }
 };
 
 // Sum over the k-split warps and the split terms, in a fixed order.
-// tiles: [groups][ksplit][16][8]; returns y for (group, row in group, m).
-template <int TERMS>
-__device__ __forceinline__ float mma_result(const float* tiles, int group, int ksplit, int row, int m, float descale) {
+// tiles: [ksplit][16][8 * NT]; returns y for (row in group, m).
+template <int TERMS, int NT>
+__device__ __forceinline__ float mma_result(const float* tiles, int ksplit, int row, int m, float descale) {
     float v = 0.f;
     for (int ks = 0; ks < ksplit; ++ks) {
-        const float* tl = tiles + ((static_cast<size_t>(group) * ksplit + ks) * 16 + row) * 8 + m * TERMS;
+        const float* tl = tiles + (static_cast<size_t>(ks) * 16 + row) * 8 * NT + m * TERMS;
+        float w = 1.f;
 #pragma unroll
-        for (int term = 0; term < TERMS; ++term) v += tl[term];
+        for (int term = 0; term < TERMS; ++term) { v = fmaf(tl[term], w, v); w *= kTermInv; }
     }
     return v * descale;
 }
+
+// Row passes of the tensor-core kernels: 3 split terms per token row, so one n-tile of 8 columns
+// holds 2 rows and two n-tiles hold 4 (5 would fit; 4 keeps the passes even for 8 rows).
+template <int MP> struct MmaShape { static constexpr int TERMS = 3, NT = MP <= 2 ? 1 : 2, TILE = 16 * 8 * NT; };
 
 }  // namespace nexrt

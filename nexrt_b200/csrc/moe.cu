@@ -236,12 +236,12 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
         if (m) { __syncthreads(); mw.preloaded = false; }
         if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
         norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m) * a.H, 1, a.H, a.eps, red);
-        float d[4];
-        mw.run(src, xq, a.H, TERMS, d);
-        mw.store(tiles + warp * 128, d);
+        float d[1][4];
+        mw.template run<1>(src, xq, a.H, TERMS, d);
+        mw.template store<1>(tiles + warp * 128, d);
         __syncthreads();
         if (threadIdx.x < kRowsPerGroup)
-            a.gu[static_cast<size_t>(m) * vrows + v0 + threadIdx.x] = mma_result<TERMS>(tiles, 0, KS, threadIdx.x, 0, kSplitDescale);
+            a.gu[static_cast<size_t>(m) * vrows + v0 + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, kSplitDescale);
     }
 }
 
@@ -281,11 +281,11 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
         }
         __syncthreads();
         act_split<TERMS>(xq, hs, 1, VK, red, descale);
-        float d[4];
-        mw.run(src, xq, VK, TERMS, d);
-        if (warp < KS) mw.store(tiles + warp * 128, d);
+        float d[1][4];
+        mw.template run<1>(src, xq, VK, TERMS, d);
+        if (warp < KS) mw.template store<1>(tiles + warp * 128, d);
         __syncthreads();
-        if (threadIdx.x < kRowsPerGroup) res[m * kRowsPerGroup + threadIdx.x] = mma_result<TERMS>(tiles, 0, KS, threadIdx.x, 0, descale[0]);
+        if (threadIdx.x < kRowsPerGroup) res[m * kRowsPerGroup + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, descale[0]);
     }
     __syncthreads();
     allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x);
@@ -313,7 +313,7 @@ extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13,
     MoeL1Args a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const uint8_t*>(w13),
                 static_cast<const float*>(w13_s), static_cast<const int*>(ids), static_cast<float*>(gu), H, I, S, M, eps, shared_expert};
     const int vrows = S * 2 * I;
-    if (gemv_mode() == 1 && H % 512 == 0 && H <= 4096) {
+    if ((gemv_mode() & 4) && H % 512 == 0 && H <= 4096) {
         const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H;
         return launch(moe_l1_mma_kernel, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
     }
@@ -329,7 +329,7 @@ extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const voi
     a.gu = static_cast<const float*>(gu); a.ids = static_cast<const int*>(ids); a.wts = static_cast<const float*>(wts);
     a.w2 = static_cast<const uint8_t*>(w2); a.w2_s = static_cast<const float*>(w2_s); a.x = static_cast<__nv_bfloat16*>(x);
     a.H = H; a.I = I; a.S = S; a.M = M; a.ch = *ch; a.site = site;
-    if (gemv_mode() == 1 && H % 16 == 0) {
+    if ((gemv_mode() & 8) && H % 16 == 0) {
         const size_t VK = static_cast<size_t>(S) * I;
         const size_t smem_mma = sizeof(float) * (VK + 8 * 128 + kMaxRows * 16) + 3 * VK;
         return launch(moe_l2_allreduce_mma_kernel, dim3(H / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);

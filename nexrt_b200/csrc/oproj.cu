@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
 // that computed the rows reduces them across the ranks and updates the residual.
 template <int MP>
 __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a) {
-    constexpr int TERMS = MP <= 2 ? 3 : 2, NB = 8;
+    constexpr int TERMS = MmaShape<MP>::TERMS, NT = MmaShape<MP>::NT, TILE = MmaShape<MP>::TILE, NB = 8;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ float descale[MP];
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
     const int KS = min(nwarps, nwin);                                   // warps that share the K range
     float* xs = smem;                                                   // [MP][K]
     float* tiles = xs + static_cast<size_t>(MP) * a.K;                  // [KS][16][8]
-    float* res = tiles + 8 * 128;                                       // [kMaxRows][16]
+    float* res = tiles + 8 * TILE;                                       // [kMaxRows][16]
     uint8_t* xq = reinterpret_cast<uint8_t*>(res + kMaxRows * kRowsPerGroup);   // [MP*TERMS][K]
     const MmaPlain src{a.w, a.s, a.K};
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, warp < KS ? nwin : 0);
@@ -188,13 +188,13 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
         }
         __syncthreads();
         act_split<TERMS>(xq, xs, mb, a.K, red, descale);
-        float d[4];
-        mw.run(src, xq, a.K, mb * TERMS, d);
-        if (warp < KS) mw.store(tiles + warp * 128, d);
+        float d[NT][4];
+        mw.template run<NT>(src, xq, a.K, mb * TERMS, d);
+        if (warp < KS) mw.template store<NT>(tiles + warp * TILE, d);
         __syncthreads();
         if (threadIdx.x < kRowsPerGroup * mb) {
             const int rl = threadIdx.x % kRowsPerGroup, m = threadIdx.x / kRowsPerGroup;
-            res[(m0 + m) * kRowsPerGroup + rl] = mma_result<TERMS>(tiles, 0, KS, rl, m, descale[m]);
+            res[(m0 + m) * kRowsPerGroup + rl] = mma_result<TERMS, NT>(tiles, KS, rl, m, descale[m]);
         }
     }
     __syncthreads();
@@ -217,9 +217,9 @@ extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* 
     a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.eps = eps; a.ch = *ch; a.site = site;
     if (cp) { a.cp = *cp; a.cp_site = cp_site; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (gemv_mode() == 1 && H % 16 == 0 && K % 64 == 0) {
-        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = mp <= 2 ? 3 : 2;
-        const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * K + 8 * 128 + kMaxRows * 16) + static_cast<size_t>(mp) * terms * K;
+    if ((gemv_mode() & 2) && H % 16 == 0 && K % 64 == 0) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
+        const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * K + 8 * 256 + kMaxRows * 16) + static_cast<size_t>(mp) * terms * K;
         dim3 g(H / 16), b(256);
         if (mp == 1) return launch(oproj_allreduce_mma_kernel<1>, g, b, smem_mma, st, a);
         if (mp == 2) return launch(oproj_allreduce_mma_kernel<2>, g, b, smem_mma, st, a);

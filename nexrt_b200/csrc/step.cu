@@ -17,7 +17,7 @@ int& gemv_threads_ref() {
 }
 
 int& gemv_mode_ref() {
-    static int mode = 1;
+    static int mode = 15;
     return mode;
 }
 
@@ -82,7 +82,7 @@ extern "C" int nexrt_set_pdl(int enabled) {
 }
 extern "C" int nexrt_version(void) { return 100; }
 extern "C" int nexrt_set_gemv_mode(int mode) {
-    gemv_mode_ref() = mode ? 1 : 0;
+    gemv_mode_ref() = mode;
     return 0;
 }
 extern "C" int nexrt_set_gemv_threads(int threads) {

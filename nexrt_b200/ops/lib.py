@@ -9,6 +9,7 @@ fallback to PyTorch.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_float, c_int, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -84,6 +85,10 @@ def load(build: bool = True) -> ctypes.CDLL:
     lib.nexrt_attn_decode_smem.argtypes = [ci, ci, ci, ci]
     lib.nexrt_attn_decode_smem.restype = c_size_t
     _install_optional(lib)
+    if os.environ.get("NEXRT_GEMV_MODE") is not None:   # 0: CUDA-core GEMV kernels, 1: tensor-core (default)
+        lib.nexrt_set_gemv_mode(int(os.environ["NEXRT_GEMV_MODE"]))
+    if os.environ.get("NEXRT_PDL") is not None:
+        lib.nexrt_set_pdl(int(os.environ["NEXRT_PDL"]))
     _lib = lib
     return lib
 

@@ -61,7 +61,9 @@ def main():
             eng.step(rows)
             torch.cuda.synchronize()
             got.append(eng.head.logits[:rows].float().cpu())
-        assert rel_l2(torch.cat(got), want) < 2e-2
+        err = rel_l2(torch.cat(got), want)
+        per_row = [round(rel_l2(a, b), 4) for a, b in zip(torch.cat(got), want)]
+        assert err < 2e-2, (rows, err, per_row)
 
     # prefill + captured-graph generate: every rank emits the same stream, equal to the oracle's
     prompt = synthetic_prompt(cfg.vocab, 32, seed=1)
