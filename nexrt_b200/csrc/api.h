@@ -40,7 +40,7 @@ int nexrt_residual_add(void* x, const void* y, int n, void* stream);
 /* gated delta net */
 int nexrt_gdn_front(const void* x, const void* in_ln, const void* front_w, const void* front_s, const void* ba_w, const void* conv_w,
                     const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv, void* z, void* beta, void* g, int H,
-                    int R, int C, int nv, int M, int conv_ring_len, float eps, int n_cta, void* stream);
+                    int R, int C, int nv, int M, int conv_ring_len, float eps, int ba_rows_pad, int n_cta, void* stream);
 int nexrt_gdn_core(const void* qkv, const void* beta, const void* g, const void* ctl, void* state_ring, void* out, int nqk, int nv, int M,
                    int state_ring_len, int C, void* stream);
 
@@ -49,7 +49,7 @@ int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void
                      void* v_cache, int H, int hd, int nq, int ngate, int kvh, int M, int cache_len, float eps, int n_cta, void* stream);
 size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M);
 int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
-                      const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out, int hd, int nq,
+                      const void* rope_table, const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out, int hd, int nq,
                       int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int cp_size, int cp_rank,
                       const NexrtLLChannel* ch, unsigned int site, void* stream);
 
@@ -60,8 +60,10 @@ int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, co
                           unsigned int cp_site, int n_cta, void* stream);
 
 /* mixture of experts */
-int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket, int H, int E,
-                     int topk, int M, float eps, int n_cta, void* stream);
+/* w holds E+1 rows; if it is padded with zero rows to rows_pad (a multiple of 16) and `partial`
+ * ([4][M][rows_pad] floats) is given, the tensor-core form runs. */
+int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket, void* partial,
+                     int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* stream);
 int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I, int S, int M,
                  float eps, int shared_expert, int n_cta, void* stream);
 int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I, int S,

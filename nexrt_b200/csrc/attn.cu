@@ -135,6 +135,7 @@ struct AttnDecodeArgs {
     const float* qn;          // [hd] 1 + w
     const float* kn;          // [hd]
     const float* inv_freq;    // [rotary/2]
+    const float2* rope_table; // optional [cache_len][rotary/2] (cos, sin); null: computed with sincosf
     const int* ctl;
     __nv_bfloat16* k_cache;   // [kvh][cache_len][hd]
     const __nv_bfloat16* v_cache;
@@ -206,7 +207,12 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         for (int i = lane, c = 0; i < a.rotary; i += 32, ++c) {
             const int f = i < half ? i : i - half;
             float sn, cs;
-            sincosf(pos * a.inv_freq[f], &sn, &cs);
+            if (a.rope_table != nullptr) {
+                const float2 cssn = a.rope_table[static_cast<size_t>(C0 + m) * half + f];
+                cs = cssn.x; sn = cssn.y;
+            } else {
+                sincosf(pos * a.inv_freq[f], &sn, &cs);
+            }
             const float self = dst[i], other = i < half ? -dst[i + half] : dst[i - half];
             rot[c] = self * cs + other * sn;
             ri[c] = i;
@@ -246,40 +252,62 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             mx[r] = -INFINITY; l[r] = 0.f;
             limit[r] = (r < nr) ? C0 + rr / G : -1;   // last visible position of the row
         }
-        for (int p = lo + warp; p < hi; p += NW) {
-            float kf[EL], vf[EL];
-            if (p < C0) {
-                if (EL == 8) {
-                    unpack8_bf16(*reinterpret_cast<const uint4*>(kc + static_cast<size_t>(p) * HD + lane * 8), kf);
-                } else {
-                    const uint2 u = *reinterpret_cast<const uint2*>(kc + static_cast<size_t>(p) * HD + lane * 4);
-                    kf[0] = __uint_as_float(u.x << 16); kf[1] = __uint_as_float(u.x & 0xffff0000u);
-                    kf[2] = __uint_as_float(u.y << 16); kf[3] = __uint_as_float(u.y & 0xffff0000u);
+        constexpr int KBATCH = 4;   // keys whose K and V rows are in flight together per warp
+        for (int pb = lo + warp; pb < hi; pb += NW * KBATCH) {
+            uint4 kraw[KBATCH], vraw[KBATCH];
+#pragma unroll
+            for (int b = 0; b < KBATCH; ++b) {
+                const int p = pb + b * NW;
+                kraw[b] = make_uint4(0u, 0u, 0u, 0u);
+                vraw[b] = make_uint4(0u, 0u, 0u, 0u);
+                if (p < hi) {
+                    if (EL == 8) {
+                        if (p < C0) kraw[b] = *reinterpret_cast<const uint4*>(kc + static_cast<size_t>(p) * HD + lane * 8);
+                        vraw[b] = *reinterpret_cast<const uint4*>(vc + static_cast<size_t>(p) * HD + lane * 8);
+                    } else {
+                        if (p < C0) {
+                            const uint2 u = *reinterpret_cast<const uint2*>(kc + static_cast<size_t>(p) * HD + lane * 4);
+                            kraw[b].x = u.x; kraw[b].y = u.y;
+                        }
+                        const uint2 u = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(p) * HD + lane * 4);
+                        vraw[b].x = u.x; vraw[b].y = u.y;
+                    }
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < EL; ++i) kf[i] = k_s[static_cast<size_t>(p - C0) * HD + lane * EL + i];
-            }
-            if (EL == 8) {
-                unpack8_bf16(*reinterpret_cast<const uint4*>(vc + static_cast<size_t>(p) * HD + lane * 8), vf);
-            } else {
-                const uint2 u = *reinterpret_cast<const uint2*>(vc + static_cast<size_t>(p) * HD + lane * 4);
-                vf[0] = __uint_as_float(u.x << 16); vf[1] = __uint_as_float(u.x & 0xffff0000u);
-                vf[2] = __uint_as_float(u.y << 16); vf[3] = __uint_as_float(u.y & 0xffff0000u);
             }
 #pragma unroll
-            for (int r = 0; r < kRowsPerPass; ++r) {
-                float sdot = 0.f;
+            for (int b = 0; b < KBATCH; ++b) {
+                const int p = pb + b * NW;
+                if (p >= hi) break;     // uniform across the warp
+                float kf[EL], vf[EL];
+                if (p < C0) {
+                    if (EL == 8) unpack8_bf16(kraw[b], kf);
+                    else {
+                        kf[0] = __uint_as_float(kraw[b].x << 16); kf[1] = __uint_as_float(kraw[b].x & 0xffff0000u);
+                        kf[2] = __uint_as_float(kraw[b].y << 16); kf[3] = __uint_as_float(kraw[b].y & 0xffff0000u);
+                    }
+                } else {
 #pragma unroll
-                for (int i = 0; i < EL; ++i) sdot = fmaf(q[r][i], kf[i], sdot);
-                sdot = warp_sum(sdot);
-                if (p <= limit[r]) {
-                    const float nm = fmaxf(mx[r], sdot);
-                    const float corr = exp2f(mx[r] - nm), pw = exp2f(sdot - nm);
-                    l[r] = l[r] * corr + pw;
+                    for (int i = 0; i < EL; ++i) kf[i] = k_s[static_cast<size_t>(p - C0) * HD + lane * EL + i];
+                }
+                if (EL == 8) unpack8_bf16(vraw[b], vf);
+                else {
+                    vf[0] = __uint_as_float(vraw[b].x << 16); vf[1] = __uint_as_float(vraw[b].x & 0xffff0000u);
+                    vf[2] = __uint_as_float(vraw[b].y << 16); vf[3] = __uint_as_float(vraw[b].y & 0xffff0000u);
+                }
 #pragma unroll
-                    for (int i = 0; i < EL; ++i) acc[r][i] = fmaf(pw, vf[i], acc[r][i] * corr);
-                    mx[r] = nm;
+                for (int r = 0; r < kRowsPerPass; ++r) {
+                    float sdot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < EL; ++i) sdot = fmaf(q[r][i], kf[i], sdot);
+                    sdot = warp_sum(sdot);
+                    if (p <= limit[r]) {
+                        const float nm = fmaxf(mx[r], sdot);
+                        const float corr = exp2f(mx[r] - nm), pw = exp2f(sdot - nm);
+                        l[r] = l[r] * corr + pw;
+#pragma unroll
+                        for (int i = 0; i < EL; ++i) acc[r][i] = fmaf(pw, vf[i], acc[r][i] * corr);
+                        mx[r] = nm;
+                    }
                 }
             }
         }
@@ -418,7 +446,7 @@ extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
 }
 
 extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
-                                 const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out,
+                                 const void* rope_table, const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out,
                                  int hd, int nq, int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int cp_size,
                                  int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream) {
     if (M < 1 || M > kMaxRows || nq % kvh || rotary > 64 || rotary % 2) return cudaErrorInvalidValue;
@@ -427,6 +455,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     AttnDecodeArgs a{};
     a.q_raw = static_cast<const float*>(q_raw); a.gate = static_cast<const float*>(gate); a.k_raw = static_cast<const float*>(k_raw);
     a.qn = static_cast<const float*>(qn); a.kn = static_cast<const float*>(kn); a.inv_freq = static_cast<const float*>(inv_freq);
+    a.rope_table = static_cast<const float2*>(rope_table);
     a.ctl = static_cast<const int*>(ctl); a.k_cache = static_cast<__nv_bfloat16*>(k_cache);
     a.v_cache = static_cast<const __nv_bfloat16*>(v_cache); a.ws_acc = static_cast<float*>(ws_acc); a.ws_ml = static_cast<float*>(ws_ml);
     a.ticket = static_cast<int*>(ticket); a.out = static_cast<float*>(out);

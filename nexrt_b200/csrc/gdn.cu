@@ -38,6 +38,7 @@ struct GdnFrontArgs {
     float* g;                    // [M][nv]
     int H, R, C, nv, M, conv_ring_len;
     float eps;
+    int ba_rows_pad;             // rows of ba_w padded to a multiple of 16 (0: not padded)
     unsigned long long* events;  // optional in-kernel event ring: CTA 0 records %globaltimer at phase boundaries
 };
 
@@ -133,16 +134,19 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
+    // the first 2 * nv CTAs also project one bf16 b/a row each (CUDA cores, weights preloaded)
     const int ba_row = static_cast<int>(blockIdx.x) < 2 * a.nv ? static_cast<int>(blockIdx.x) : -1;
+    const bool ba_cta = ba_row >= 0;
     const GemvGeom gb = gemv_geom(a.H / 8, blockDim.x);
-    float* xs = smem;                                                      // [MP][H]
-    float* gs = xs + static_cast<size_t>(MP) * a.H;                        // [H]
-    float* tiles = gs + a.H;                                               // [KS][16][8]
-    float* part_ba = tiles + KS * TILE;                                     // [wpr][MP]
-    uint8_t* xq = reinterpret_cast<uint8_t*>(part_ba + gemv_part_floats(1, MP, gb));   // [MP*TERMS][H]
+    float* xs = smem;                                                      // [MP][H]   (b/a CTAs only)
+    float* tiles = xs + static_cast<size_t>(MP) * a.H;                     // [KS][TILE]
+    float* part_ba = tiles + KS * TILE;                                    // [wpr][MP]
+    uint8_t* xq = reinterpret_cast<uint8_t*>(part_ba + 64);                // [MP*TERMS][H]
     const MmaPlain src{a.front_w, a.front_s, a.H};
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
     mw.preload(src);
+    GemvCta<MP, 2, PlainBf16> gba(PlainBf16{a.ba_w, a.H}, ba_cta ? ba_row : 0, 1, a.H);
+    if (ba_cta) gba.preload();
     NEXRT_EVENT(1);
     RowNorm<4> norm;
     norm.preload_gamma(a.in_ln, a.H);
@@ -156,13 +160,16 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
         if (m0) { __syncthreads(); mw.preloaded = false; }
-        norm.template run<TERMS>(xq, ba_row >= 0 ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
+        norm.template run<TERMS>(xq, ba_cta ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
         NEXRT_EVENT(4);
         float d[NT][4];
         mw.template run<NT>(src, xq, a.H, mb * TERMS, d);
         mw.template store<NT>(tiles + warp * TILE, d);
         NEXRT_EVENT(5);
-        if (ba_row >= 0) gemv_cta<MP, 2>(PlainBf16{a.ba_w, a.H}, ba_row, 1, xs, a.H, part_ba);
+        if (ba_cta) {
+            if (m0 == 0) gba.run(xs, part_ba);
+            else gemv_cta<MP, 2>(PlainBf16{a.ba_w, a.H}, ba_row, 1, xs, a.H, part_ba);
+        }
         __syncthreads();
         NEXRT_EVENT(7);
         if (threadIdx.x < kRowsPerGroup) {
@@ -170,7 +177,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
 #pragma unroll
             for (int m = 0; m < MP; ++m) pre[m] = m < mb ? mma_result<TERMS, NT>(tiles, KS, threadIdx.x, m, kSplitDescale) : 0.f;
             gdn_front_row<MP>(a, row0 + threadIdx.x, pre, m0, mb, C0, cw);
-        } else if (ba_row >= 0 && threadIdx.x >= 32 && threadIdx.x < 32 + mb) {
+        } else if (ba_cta && threadIdx.x >= 32 && threadIdx.x < 32 + mb) {
             const int m = threadIdx.x - 32;
             gdn_ba_row(a, ba_row, gemv_result(part_ba, 0, m, MP, gb.wpr), m0 + m);
         }
@@ -231,19 +238,18 @@ extern "C" int nexrt_set_event_ring(void* ring) {
 
 extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* front_w, const void* front_s, const void* ba_w,
                                const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv,
-                               void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, float eps, int n_cta,
-                               void* stream) {
+                               void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, float eps, int ba_rows_pad,
+                               int n_cta, void* stream) {
     if (M < 1 || M > kMaxRows || H % 256 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
     GdnFrontArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(in_ln), static_cast<const uint8_t*>(front_w),
                    static_cast<const float*>(front_s), static_cast<const __nv_bfloat16*>(ba_w), static_cast<const float*>(conv_w),
                    static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), static_cast<const int*>(ctl),
                    static_cast<float*>(conv_ring), static_cast<float*>(qkv), static_cast<float*>(z), static_cast<float*>(beta),
-                   static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, eps, g_events};
+                   static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, eps, ba_rows_pad, g_events};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if ((gemv_mode() & 1) && R % 16 == 0 && H % 512 == 0 && H <= 4096 && R / 16 >= 2 * nv) {
-        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
-        const size_t smem = sizeof(float) * (static_cast<size_t>(mp + 1) * H + 8 * 256 + gemv_part_floats(1, mp, gemv_geom(H / 8, 256))) +
-                            static_cast<size_t>(mp) * terms * H;
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
+        const size_t smem = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 256 + 64) + static_cast<size_t>(mp) * 3 * H;
         dim3 g(R / 16), b(256);
         if (mp == 1) return launch(gdn_front_mma_kernel<1>, g, b, smem, st, a);
         if (mp == 2) return launch(gdn_front_mma_kernel<2>, g, b, smem, st, a);

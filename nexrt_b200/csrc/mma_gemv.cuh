@@ -340,6 +340,88 @@ __device__ __forceinline__ float mma_result(const float* tiles, int ksplit, int 
     return v * descale;
 }
 
+// ---- bf16 weights (router, gate rows): mma.m16n8k16 with the activation as bf16 hi + lo columns ----
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// fp32 rows xs[m][K] (shared memory) -> bf16 planes xh[(m * 2 + term)][K]: hi = bf16(x), lo = bf16(x - hi).
+__device__ __forceinline__ void split_bf16_rows(__nv_bfloat16* xh, const float* xs, int rows, int K) {
+    for (int idx = threadIdx.x * 2; idx < rows * K; idx += blockDim.x * 2) {
+        const int m = idx / K, k = idx % K;
+        const float2 v = *reinterpret_cast<const float2*>(xs + idx);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.x, v.y);
+        const float2 hf = __bfloat1622float2(hi);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x - hf.x, v.y - hf.y);
+        *reinterpret_cast<__nv_bfloat162*>(xh + static_cast<size_t>(m * 2) * K + k) = hi;
+        *reinterpret_cast<__nv_bfloat162*>(xh + static_cast<size_t>(m * 2 + 1) * K + k) = lo;
+    }
+    __syncthreads();
+}
+
+// One warp: 16 bf16 weight rows starting at row0 of W [rows][K], 64-byte windows (32 elements)
+// w0, w0 + wstride, ... < nwin.  Same lane mapping as the fp8 routine.
+template <int NB>
+struct MmaWarpBf16 {
+    uint4 ra[NB], rb[NB];
+    const __nv_bfloat16* w;
+    int K, row0, w0, wstride, nwin, g, t;
+    bool preloaded;
+    __device__ __forceinline__ MmaWarpBf16(const __nv_bfloat16* wt, int k, int r0, int first, int stride, int total)
+        : w(wt), K(k), row0(r0), w0(first), wstride(stride), nwin(total) {
+        const int lane = threadIdx.x & 31;
+        g = lane >> 2; t = lane & 3;
+        preloaded = false;
+    }
+    __device__ __forceinline__ void load(int wbase) {
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int win = wbase + i * wstride;
+            if (win < nwin) {
+                ra[i] = ld_stream16(w + static_cast<size_t>(row0 + g) * K + win * 32 + t * 8);
+                rb[i] = ld_stream16(w + static_cast<size_t>(row0 + g + 8) * K + win * 32 + t * 8);
+            } else {
+                ra[i] = make_uint4(0u, 0u, 0u, 0u);
+                rb[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    }
+    __device__ __forceinline__ void preload() { load(w0); preloaded = true; }
+    // xh: shared memory bf16 planes [ncols][K]
+    __device__ __forceinline__ void run(const __nv_bfloat16* xh, int ncols, float (&d)[4]) {
+        d[0] = d[1] = d[2] = d[3] = 0.f;
+        for (int wbase = w0; wbase < nwin; wbase += NB * wstride) {
+            if (!(preloaded && wbase == w0)) load(wbase);
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                const int win = wbase + i * wstride;
+                if (win >= nwin) break;
+                uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+                if (g < ncols) xb = *reinterpret_cast<const uint4*>(xh + static_cast<size_t>(g) * K + win * 32 + t * 8);
+                mma_bf16_16x8x16(d, ra[i].x, rb[i].x, ra[i].y, rb[i].y, xb.x, xb.y);
+                mma_bf16_16x8x16(d, ra[i].z, rb[i].z, ra[i].w, rb[i].w, xb.z, xb.w);
+            }
+        }
+    }
+    __device__ __forceinline__ void store(float* tile, const float (&d)[4]) const {
+        tile[g * 8 + 2 * t] = d[0]; tile[g * 8 + 2 * t + 1] = d[1];
+        tile[(g + 8) * 8 + 2 * t] = d[2]; tile[(g + 8) * 8 + 2 * t + 1] = d[3];
+    }
+};
+
+// tiles [ksplit][16][8]: value of (row, m) = sum over k-split warps of hi + lo columns.
+__device__ __forceinline__ float mma_bf16_result(const float* tiles, int ksplit, int row, int m) {
+    float v = 0.f;
+    for (int ks = 0; ks < ksplit; ++ks) {
+        const float* tl = tiles + (static_cast<size_t>(ks) * 16 + row) * 8 + m * 2;
+        v += tl[0] + tl[1];
+    }
+    return v;
+}
+
 // Row passes of the tensor-core kernels: 3 split terms per token row, so one n-tile of 8 columns
 // holds 2 rows and two n-tiles hold 4 (5 would fit; 4 keeps the passes even for 8 rows).
 template <int MP> struct MmaShape { static constexpr int TERMS = 3, NT = MP <= 2 ? 1 : 2, TILE = 16 * 8 * NT; };

@@ -35,48 +35,15 @@ struct RouterArgs {
     int* ticket;
     int H, E, topk, M;
     float eps;
+    float* partial;           // tensor-core form: [4 k-quarters][M][rows_pad]
+    int rows_pad;             // rows of w padded to a multiple of 16 (0: not padded)
 };
 
-template <int MB>
-__global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
-    constexpr int U = MB == 1 ? 4 : 2;
-    extern __shared__ __align__(16) float smem[];
-    __shared__ float red[32];
-    __shared__ int s_last;
-    pdl_launch_dependents();
+// Top-k of every token row by the calling CTA: warp m owns row m, lane holds logits lane,
+// lane + 32, ...; ties go to the lowest expert id; weights are a softmax over the selected logits.
+__device__ __forceinline__ void router_topk(const RouterArgs& a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int rows = a.E + 1;
-    int r0, r1;
-    cta_range(rows, blockIdx.x, gridDim.x, &r0, &r1);
-    const int nrows = r1 - r0;
-    if (nrows) prefetch_l2_range(a.w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(nrows) * a.H * 2);
-    const GemvGeom gg = gemv_geom(a.H / 8, blockDim.x);
-    float* xs = smem;
-    float* part = xs + static_cast<size_t>(MB) * a.H;
-    float* gs = part + gemv_part_floats((rows + gridDim.x - 1) / gridDim.x, MB, gg);   // [H] norm multiplier
-    GemvCta<MB, U, PlainBf16> gemv(PlainBf16{a.w, a.H}, r0, nrows, a.H);
-    gemv.preload();
-    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.post_ln[i];
-    pdl_wait();
-    for (int m0 = 0; m0 < a.M; m0 += MB) {
-        const int mb = min(MB, a.M - m0);
-        if (m0) __syncthreads();
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
-        if (m0 == 0) gemv.run(xs, part);
-        else gemv_cta<MB, U>(PlainBf16{a.w, a.H}, r0, nrows, xs, a.H, part);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
-            const int rl = idx / mb, m = idx % mb;
-            a.logits[static_cast<size_t>(m0 + m) * rows + r0 + rl] = gemv_result(part, rl, m, MB, gg.wpr);
-        }
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1) == static_cast<int>(gridDim.x) - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // ---- top-k: warp m owns row m; lane holds logits lane, lane+32, ...
     for (int m = warp; m < a.M; m += nwarps) {
         const float* lg = a.logits + static_cast<size_t>(m) * rows;
         float v[16];
@@ -118,6 +85,48 @@ __global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
             a.wts[m * S + lane] = sigmoid_f(__ldcg(lg + a.E));
         }
     }
+}
+
+template <int MB>
+__global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
+    constexpr int U = MB == 1 ? 4 : 2;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int rows = a.E + 1;
+    int r0, r1;
+    cta_range(rows, blockIdx.x, gridDim.x, &r0, &r1);
+    const int nrows = r1 - r0;
+    if (nrows) prefetch_l2_range(a.w + static_cast<size_t>(r0) * a.H, static_cast<size_t>(nrows) * a.H * 2);
+    const GemvGeom gg = gemv_geom(a.H / 8, blockDim.x);
+    float* xs = smem;
+    float* part = xs + static_cast<size_t>(MB) * a.H;
+    float* gs = part + gemv_part_floats((rows + gridDim.x - 1) / gridDim.x, MB, gg);   // [H] norm multiplier
+    GemvCta<MB, U, PlainBf16> gemv(PlainBf16{a.w, a.H}, r0, nrows, a.H);
+    gemv.preload();
+    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.post_ln[i];
+    pdl_wait();
+    for (int m0 = 0; m0 < a.M; m0 += MB) {
+        const int mb = min(MB, a.M - m0);
+        if (m0) __syncthreads();
+        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
+        if (m0 == 0) gemv.run(xs, part);
+        else gemv_cta<MB, U>(PlainBf16{a.w, a.H}, r0, nrows, xs, a.H, part);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nrows * mb; idx += blockDim.x) {
+            const int rl = idx / mb, m = idx % mb;
+            a.logits[static_cast<size_t>(m0 + m) * rows + r0 + rl] = gemv_result(part, rl, m, MB, gg.wpr);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1) == static_cast<int>(gridDim.x) - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    router_topk(a);
     if (threadIdx.x == 0) *a.ticket = 0;
 }
 
@@ -210,6 +219,59 @@ __global__ void __launch_bounds__(512, 1) moe_l2_allreduce_kernel(MoeL2Args a) {
     allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
 }
 
+// Router on the tensor cores: bf16 weights [rows_pad][H], one CTA per (16 rows, quarter of K), the
+// 8 warps split the quarter; the CTA that takes the last ticket adds the four quarters in a
+// fixed order and selects the experts.
+template <int MP>
+__global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
+    constexpr int KQ = 4, NB = 4, KS = 8;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[32];
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5;
+    const int rg = blockIdx.x / KQ, kq = blockIdx.x % KQ, rows = a.E + 1;
+    const int nq = a.H / 32 / KQ;                                       // 64-byte windows per quarter
+    float* xs = smem;                                                   // [MP][H]
+    float* tiles = xs + static_cast<size_t>(MP) * a.H;                  // [KS][16][8]
+    __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(tiles + KS * 128);   // [MP*2][H]
+    MmaWarpBf16<NB> mw(a.w, a.H, rg * kRowsPerGroup, kq * nq + warp, KS, (kq + 1) * nq);
+    mw.preload();
+    RowNorm<4> norm;
+    norm.preload_gamma(a.post_ln, a.H);
+    pdl_wait();
+    for (int m0 = 0; m0 < a.M; m0 += MP) {
+        const int mb = min(MP, a.M - m0);
+        if (m0) { __syncthreads(); mw.preloaded = false; }
+        norm.template run<3>(nullptr, xs, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
+        split_bf16_rows(xh, xs, mb, a.H);
+        float d[4];
+        mw.run(xh, mb * 2, d);
+        mw.store(tiles + warp * 128, d);
+        __syncthreads();
+        if (threadIdx.x < kRowsPerGroup * mb) {
+            const int rl = threadIdx.x % kRowsPerGroup, m = threadIdx.x / kRowsPerGroup;
+            a.partial[(static_cast<size_t>(kq) * a.M + m0 + m) * a.rows_pad + rg * kRowsPerGroup + rl] = mma_bf16_result(tiles, KS, rl, m);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1) == static_cast<int>(gridDim.x) - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < a.M * rows; idx += blockDim.x) {
+        const int m = idx / rows, e = idx % rows;
+        float v = 0.f;
+#pragma unroll
+        for (int q = 0; q < KQ; ++q) v += __ldcg(a.partial + (static_cast<size_t>(q) * a.M + m) * a.rows_pad + e);
+        a.logits[static_cast<size_t>(m) * rows + e] = v;
+    }
+    __syncthreads();
+    router_topk(a);
+    if (threadIdx.x == 0) *a.ticket = 0;
+}
+
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
 // Expert gate/up: one CTA per 16 virtual rows (slot, i), the 8 warps split K = H.
 __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
@@ -295,12 +357,21 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
 
 using namespace nexrt;
 
-extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket, int H,
-                                int E, int topk, int M, float eps, int n_cta, void* stream) {
+extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket,
+                                void* partial, int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* stream) {
     if (M < 1 || M > kMaxRows || H % 256 || E > 512 || topk < 1 || topk > 31 || topk > E) return cudaErrorInvalidValue;
     RouterArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const __nv_bfloat16*>(w),
-                 static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), static_cast<int*>(ticket), H, E, topk, M, eps};
+                 static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), static_cast<int*>(ticket), H, E, topk, M, eps,
+                 static_cast<float*>(partial), rows_pad};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((gemv_mode() & 16) && partial != nullptr && rows_pad >= E + 1 && rows_pad % 16 == 0 && H % 1024 == 0 && H <= 4096) {
+        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
+        const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 128) + sizeof(__nv_bfloat16) * static_cast<size_t>(mp) * 2 * H;
+        dim3 g(rows_pad / 16 * 4), b(256);
+        if (mp == 1) return launch(moe_router_mma_kernel<1>, g, b, smem_mma, st, a);
+        if (mp == 2) return launch(moe_router_mma_kernel<2>, g, b, smem_mma, st, a);
+        return launch(moe_router_mma_kernel<4>, g, b, smem_mma, st, a);
+    }
     const int mb = M == 1 ? 1 : 4;
     const size_t smem = sizeof(float) * (static_cast<size_t>(mb + 1) * H + gemv_part_floats((E + 1 + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, gemv_threads())));
     if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);

@@ -17,7 +17,7 @@ int& gemv_threads_ref() {
 }
 
 int& gemv_mode_ref() {
-    static int mode = 15;
+    static int mode = 31;
     return mode;
 }
 

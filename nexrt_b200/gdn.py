@@ -21,6 +21,12 @@ class Gdn:
         self.ctx, self.w = ctx, w
         spec, dev = ctx.spec, ctx.device
         self.state_ring_len, self.conv_ring_len = state_ring, conv_ring
+        ba = w["ba_w"]
+        self.ba_rows_pad = (ba.shape[0] + 15) // 16 * 16   # zero rows up to a whole 16-row tensor-core tile
+        if "ba_w_pad" not in w:
+            pad = torch.zeros(self.ba_rows_pad, ba.shape[1], dtype=ba.dtype, device=ba.device)
+            pad[: ba.shape[0]] = ba
+            w["ba_w_pad"] = pad
         self.conv_ring = torch.zeros(conv_ring, spec.gdn_qkv_rows, dtype=torch.float32, device=dev)
         self.state_ring = torch.zeros(state_ring, spec.gdn_v, 128, 128, dtype=torch.float32, device=dev)
 
@@ -33,9 +39,9 @@ class Gdn:
         cfg, spec, st = c.cfg, c.spec, c.stream()
         check(
             lib.nexrt_gdn_front(
-                ptr(c.x), ptr(w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(w["ba_w"]), ptr(w["conv_w"]), ptr(w["a_log"]),
+                ptr(c.x), ptr(w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]),
                 ptr(w["dt_bias"]), ptr(c.ctl), ptr(self.conv_ring), ptr(c.gdn_qkv), ptr(c.gdn_z), ptr(c.gdn_beta), ptr(c.gdn_g),
-                cfg.hidden, spec.gdn_front_rows, spec.gdn_qkv_rows, spec.gdn_v, M, self.conv_ring_len, cfg.rms_eps, c.n_cta, st,
+                cfg.hidden, spec.gdn_front_rows, spec.gdn_qkv_rows, spec.gdn_v, M, self.conv_ring_len, cfg.rms_eps, self.ba_rows_pad, c.n_cta, st,
             ),
             "gdn_front",
         )

@@ -11,6 +11,8 @@ checkpoint tensors are used as stored (the reference's folded mode re-quantises 
 
 from __future__ import annotations
 
+import torch
+
 from .ops.lib import check, ptr
 from .runtime.context import StepContext
 
@@ -18,6 +20,12 @@ from .runtime.context import StepContext
 class Moe:
     def __init__(self, ctx: StepContext, w: dict):
         self.ctx, self.w = ctx, w
+        rw = w["router_w"]
+        self.rows_pad = (rw.shape[0] + 15) // 16 * 16   # the reference pads the router to 528 rows too (moe.py:127-171)
+        if "router_w_pad" not in w:
+            pad = torch.zeros(self.rows_pad, rw.shape[1], dtype=rw.dtype, device=rw.device)
+            pad[: rw.shape[0]] = rw
+            w["router_w_pad"] = pad
 
     def forward(self, M: int = 1) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
@@ -25,8 +33,8 @@ class Moe:
         S = cfg.top_k + 1
         check(
             lib.nexrt_moe_router(
-                ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w"]), ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_ticket),
-                cfg.hidden, cfg.n_experts, cfg.top_k, M, cfg.rms_eps, c.n_cta, st,
+                ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_ticket),
+                ptr(c.moe_partial), self.rows_pad, cfg.hidden, cfg.n_experts, cfg.top_k, M, cfg.rms_eps, c.n_cta, st,
             ),
             "moe_router",
         )

@@ -48,12 +48,12 @@ _PROTOTYPES = {
     "nexrt_embed_gather": [vp, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_step_end": [vp, vp, cu, vp, vp, ci, vp],
     "nexrt_residual_add": [vp, vp, ci, vp],
-    "nexrt_gdn_front": [vp] * 14 + [ci] * 6 + [cf, ci, vp],
+    "nexrt_gdn_front": [vp] * 14 + [ci] * 6 + [cf, ci, ci, vp],
     "nexrt_gdn_core": [vp] * 6 + [ci] * 5 + [vp],
     "nexrt_attn_front": [vp] * 9 + [ci] * 7 + [cf, ci, vp],
-    "nexrt_attn_decode": [vp] * 13 + [ci] * 8 + [cf, ci, ci, CH, cu, vp],
+    "nexrt_attn_decode": [vp] * 14 + [ci] * 8 + [cf, ci, ci, CH, cu, vp],
     "nexrt_oproj_allreduce": [vp] * 6 + [ci] * 4 + [cf, ci, CH, cu, CH, cu, ci, vp],
-    "nexrt_moe_router": [vp] * 7 + [ci] * 4 + [cf, ci, vp],
+    "nexrt_moe_router": [vp] * 8 + [ci] * 5 + [cf, ci, vp],
     "nexrt_moe_l1": [vp] * 6 + [ci] * 4 + [cf, ci, ci, vp],
     "nexrt_moe_l2_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, ci, vp],
     "nexrt_lmhead_sample": [vp] * 9 + [ci] * 4 + [cf, ci, ci, CH, cu, ci, vp],

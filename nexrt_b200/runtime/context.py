@@ -74,12 +74,24 @@ class StepContext:
         self.moe_wts = z(MAX_ROWS, S)
         self.moe_gu = z(MAX_ROWS, S, 2 * spec.inter)
         self.moe_ticket = z(1, dtype=i32)
+        self.moe_partial = z(4, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)
         self.head_ticket = z(1, dtype=i32)
         self.head_export = z(MAX_ROWS, 64, dtype=i32)
         self.sampling = z(8, dtype=torch.int64)
         self.site = 0
+        self._rope = {}
+
+    def rope_table(self, cache_len: int) -> torch.Tensor:
+        """(cos, sin) of position * inv_freq for every cache position, built once per engine like the
+        reference's RoPE tables (``nex_n2_5_pro/attn.py:171-177``)."""
+        t = self._rope.get(cache_len)
+        if t is None:
+            ang = torch.arange(cache_len, dtype=torch.float32, device=self.device)[:, None] * self.inv_freq[None, :]
+            t = torch.stack([torch.cos(ang), torch.sin(ang)], -1).contiguous()
+            self._rope[cache_len] = t
+        return t
 
     # ---- site counting: one index per launch that touches an LL channel -----------------------
     def begin_step(self) -> None:
