@@ -16,6 +16,7 @@
 // renormalisation (reference moe.py:76-84) equals a softmax over the selected logits, which is
 // what the router computes.
 #include "api.h"
+#include "no_alloc.h"
 #include "epilogue.cuh"
 #include "gemv.cuh"
 #include "gemv_cta.cuh"
@@ -409,4 +410,49 @@ extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const voi
     const size_t smem = sizeof(float) * (static_cast<size_t>(S) * I + gemv_part_floats(max_rows, 1, gemv_geom(S * I / 16, gemv_threads())) +
                                          static_cast<size_t>(kMaxRows) * max_rows);
     return launch(moe_l2_allreduce_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
+}
+
+// ---- allocation-free router entry point (see no_alloc.h) ------------------------------------------
+namespace {
+constexpr size_t kNoAllocPartial = 4ull * NEXRT_ROUTER_NOALLOC_MAX_ROWS * NEXRT_ROUTER_NOALLOC_MAX_EXPERT_ROWS;   // floats
+constexpr size_t kNoAllocLogits = static_cast<size_t>(NEXRT_ROUTER_NOALLOC_MAX_ROWS) * NEXRT_ROUTER_NOALLOC_MAX_EXPERT_ROWS;
+constexpr size_t kNoAllocFloats = kNoAllocPartial + kNoAllocLogits + 64;   // + the ticket word (own 256-byte line)
+}  // namespace
+
+// Scratch of the allocation-free router: partial logits | logits | ticket.  In host code this name
+// is only a stand-in for the symbol; the device address is obtained with cudaGetSymbolAddress.
+static __device__ __align__(256) float g_router_noalloc_scratch[kNoAllocFloats];
+
+extern "C" int nexrt_moe_router_noalloc(const void* x, const void* post_ln, const void* w, void* ids, void* wts, int rows_pad, int H, int E,
+                                        int topk, int M, float eps, void* stream) {
+    if (M < 1 || M > NEXRT_ROUTER_NOALLOC_MAX_ROWS || rows_pad > NEXRT_ROUTER_NOALLOC_MAX_EXPERT_ROWS || rows_pad % 16 || rows_pad < E + 1 ||
+        H % 1024 || H > 4096 || E > 512 || topk < 1 || topk > 31 || topk > E)
+        return cudaErrorInvalidValue;
+    // one address per device, looked up on the first call made with that device current
+    static float* scratch_of_device[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (scratch_of_device[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_router_noalloc_scratch);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        scratch_of_device[dev] = p;
+    }
+    float* base = scratch_of_device[dev];
+    float* partial = base;
+    float* logits = base + kNoAllocPartial;
+    int* ticket = reinterpret_cast<int*>(base + kNoAllocPartial + kNoAllocLogits);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    e = cudaMemsetAsync(ticket, 0, sizeof(int), st);      // the ticket must start at zero whatever the last call left
+    if (e != cudaSuccess) return static_cast<int>(e);
+    RouterArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const __nv_bfloat16*>(w), logits,
+                 static_cast<int*>(ids), static_cast<float*>(wts), ticket, H, E, topk, M, eps, partial, rows_pad};
+    const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
+    const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 128) + sizeof(__nv_bfloat16) * static_cast<size_t>(mp) * 2 * H;
+    dim3 g(rows_pad / 16 * 4), b(256);
+    if (mp == 1) return launch(moe_router_mma_kernel<1>, g, b, smem_mma, st, a);
+    if (mp == 2) return launch(moe_router_mma_kernel<2>, g, b, smem_mma, st, a);
+    return launch(moe_router_mma_kernel<4>, g, b, smem_mma, st, a);
 }
