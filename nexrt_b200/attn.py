@@ -35,15 +35,18 @@ class FullAttn:
     def reset(self) -> None:
         pass  # rows beyond committed_len are never read
 
-    def forward(self, M: int = 1, cp: bool = False) -> None:
+    def forward(self, M: int = 1, cp: bool = False, ctl: Optional[torch.Tensor] = None) -> None:
+        """``ctl``: control block whose committed length is the base position of the rows (default:
+        the engine's; the MTP draft layer passes its own)."""
         c, lib = self.ctx, self.ctx.lib
+        ctl = c.ctl if ctl is None else ctl
         cfg, spec, st = c.cfg, c.spec, c.stream()
         use_cp = cp and c.cp_channel is not None and self.cp_w is not None
         w = self.cp_w if use_cp else self.w
         nq = spec.q_heads * (spec.cp_size if use_cp else 1)
         check(
             lib.nexrt_attn_front(
-                ptr(c.x), ptr(self.w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(c.ctl), ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw),
+                ptr(c.x), ptr(self.w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(ctl), ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw),
                 ptr(self.v_cache), cfg.hidden, cfg.head_dim, nq, spec.q_heads, spec.kv_heads, M, self.cache_len, cfg.rms_eps, c.n_cta, st,
             ),
             "attn_front",
@@ -51,7 +54,7 @@ class FullAttn:
         cp_site = c.next_site() if use_cp else 0
         check(
             lib.nexrt_attn_decode(
-                ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw), ptr(self.w["qn"]), ptr(self.w["kn"]), ptr(c.inv_freq), ptr(c.rope_table(self.cache_len)), ptr(c.ctl), ptr(self.k_cache),
+                ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw), ptr(self.w["qn"]), ptr(self.w["kn"]), ptr(c.inv_freq), ptr(c.rope_table(self.cache_len)), ptr(ctl), ptr(self.k_cache),
                 ptr(self.v_cache), ptr(c.ws_acc), ptr(c.ws_ml), ptr(c.attn_ticket), ptr(c.attn_out), cfg.head_dim, nq, spec.q_heads,
                 spec.kv_heads, M, self.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, spec.cp_size if use_cp else 1,
                 spec.cp_rank if use_cp else 0, c.cp_channel.ref if use_cp else None, cp_site, st,

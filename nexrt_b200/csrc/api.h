@@ -54,7 +54,8 @@ int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, co
                       const NexrtLLChannel* ch, unsigned int site, void* stream);
 
 /* output projection + all-reduce + residual.  mode 0: plain fp32 input; 1: GDN gated RMSNorm of
- * (in, z); 2: context-parallel merge of the partials waiting in `cp` followed by * sigmoid(gate). */
+ * (in, z); 2: context-parallel merge of the partials waiting in `cp` followed by * sigmoid(gate).
+ * Adding 4 to the mode makes x the reduced projection itself instead of adding it to x. */
 int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, const void* w, const void* s, void* x, int H, int K, int M,
                           int mode, float eps, int hd, const NexrtLLChannel* ch, unsigned int site, const NexrtLLChannel* cp,
                           unsigned int cp_site, int n_cta, void* stream);
@@ -74,6 +75,16 @@ int nexrt_lmhead_sample(const void* x, const void* final_ln, const void* w, void
                         void* ctl, void* export_buf, int H, int V_local, int vocab_base, int M, float eps, int mode, int arg,
                         const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
 int nexrt_sample_logits(const void* logits, const void* sampling, void* ctl, int V, int position_base, void* stream);
+
+/* speculative-decoding glue (spec.cu) */
+int nexrt_mtp_prep(const void* ctl, void* dctl, int mode, int rows, void* stream);
+int nexrt_mtp_preprocess(const void* embed, const void* dctl, const void* hidden, const void* ge, const void* gf, const void* gh, void* out,
+                         int H, int vocab, int win0, int win, float eps, int hidden_row, int M, void* stream);
+int nexrt_row_select(const void* x, const void* ctl, void* y, int H, int rows, void* stream);
+int nexrt_zero_rows(void* x, int n, void* stream);
+int nexrt_dflash_noise(const void* embed, const void* ctl, void* noise, void* dctl, int H, int vocab, int mask_id, int rows, void* stream);
+int nexrt_dflash_commit(void* ctl, const void* dctl, int rows, void* stream);
+int nexrt_feature_tap(const void* x, void* tap, int n, void* stream);
 
 /* host runtime (host_runtime.cu) */
 int nexrt_ipc_alloc(size_t bytes, void** ptr);

@@ -9,14 +9,14 @@ namespace nexrt {
 
 // res: shared memory [M][nrows] fp32 partial sums of this rank.
 __device__ __forceinline__ void allreduce_residual(const LLChannel& ch, unsigned int site, const float* res, int M, int row0, int nrows,
-                                                   int H, __nv_bfloat16* __restrict__ x) {
+                                                   int H, __nv_bfloat16* __restrict__ x, bool add_residual = true) {
     LLCall call{0u, 0u};
     if (ch.world > 1) call = ll_begin(ch, site);
     for (int idx = threadIdx.x; idx < M * nrows; idx += blockDim.x) {
         const int m = idx / nrows, r = idx % nrows;
         const size_t o = static_cast<size_t>(m) * H + row0 + r;
         const float sum = ll_allreduce_f32(ch, call, static_cast<unsigned int>(o), res[idx]);
-        x[o] = __float2bfloat16_rn(__bfloat162float(x[o]) + sum);
+        x[o] = __float2bfloat16_rn(add_residual ? __bfloat162float(x[o]) + sum : sum);
     }
 }
 

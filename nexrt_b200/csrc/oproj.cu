@@ -31,6 +31,7 @@ struct OProjArgs {
     const float* s;         // [H/128][K/128]
     __nv_bfloat16* x;       // [M][H] residual stream (read-modify-write)
     int H, K, M, mode, hd;
+    int overwrite;          // 1: x = reduced projection (no residual add)
     float eps;
     LLChannel ch;
     unsigned int site;
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
         }
     }
     __syncthreads();
-    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
+    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x, a.overwrite == 0);
 }
 
 // Tensor-core form: one CTA per 16 output rows, the 8 warps split K (see mma_gemv.cuh); the CTA
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
         }
     }
     __syncthreads();
-    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x);
+    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x, a.overwrite == 0);
 }
 
 }  // namespace nexrt
@@ -208,13 +209,15 @@ using namespace nexrt;
 extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, const void* w, const void* s, void* x, int H, int K,
                                      int M, int mode, float eps, int hd, const NexrtLLChannel* ch, unsigned int site,
                                      const NexrtLLChannel* cp, unsigned int cp_site, int n_cta, void* stream) {
+    const int overwrite = (mode & 4) ? 1 : 0;
+    mode &= 3;
     if (M < 1 || M > kMaxRows || K % 128 || H % 2 || ch == nullptr || mode < 0 || mode > 2) return cudaErrorInvalidValue;
     if (mode == 2 && (cp == nullptr || hd <= 0 || K % hd)) return cudaErrorInvalidValue;
     if (ch->world > 1 && ch->slots < static_cast<unsigned int>(kMaxRows) * H) return cudaErrorInvalidValue;
     OProjArgs a{};
     a.in = static_cast<const float*>(in); a.z = static_cast<const float*>(z); a.gnorm_w = static_cast<const float*>(gnorm_w);
     a.w = static_cast<const uint8_t*>(w); a.s = static_cast<const float*>(s); a.x = static_cast<__nv_bfloat16*>(x);
-    a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.eps = eps; a.ch = *ch; a.site = site;
+    a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.overwrite = overwrite; a.eps = eps; a.ch = *ch; a.site = site;
     if (cp) { a.cp = *cp; a.cp_site = cp_site; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if ((gemv_mode() & 2) && H % 16 == 0 && K % 64 == 0) {

@@ -123,10 +123,13 @@ class DecodeEngine:
         return [w[Ctl.PENDING], w[Ctl.COMMITTED_LEN]]
 
     # ---- one step -----------------------------------------------------------------------------
-    def step(self, M: int = 1, cp: bool = False, head_mode: int = MODE_COMMIT, end: bool = True) -> None:
-        """Launch one whole step on the current stream: embed, every layer, head, step end."""
+    def step(self, M: int = 1, cp: bool = False, head_mode: int = MODE_COMMIT, end: bool = True, begin: bool = True) -> None:
+        """Launch one whole step on the current stream: embed, every layer, head, step end.
+        ``begin`` / ``end`` are False when the step is one stage of a longer round (speculative
+        modes), whose channel sites are counted across all stages."""
         c = self.ctx
-        c.begin_step()
+        if begin:
+            c.begin_step()
         check(c.lib.nexrt_embed_gather(ptr(self.embed), ptr(c.ctl), ptr(c.x), ptr(c.status), self.cfg.hidden, self.cfg.vocab, M, c.stream()), "embed")
         for mixer, moe in zip(self.mixers, self.moes):
             if isinstance(mixer, FullAttn):

@@ -21,10 +21,11 @@ MODE_DRAFT = 2    # greedy: row r's token goes to ctl ids[arg + r]
 
 
 class Head:
-    def __init__(self, ctx: StepContext, w: dict):
+    def __init__(self, ctx: StepContext, w: dict, init_sampling: bool = True):
         self.ctx, self.w = ctx, w
         self.logits: Optional[torch.Tensor] = None
-        self.set_sampling_config(0, *GREEDY)
+        if init_sampling:
+            self.set_sampling_config(0, *GREEDY)
 
     def set_sampling_config(self, seed, temperature, top_p, top_k) -> None:
         """Write the 64-byte sampling buffer in place (its address never moves)."""

@@ -1,0 +1,90 @@
+"""Capture and serve loop of MTP speculative decoding.
+
+Counterpart of ``nex_n2_5_pro/mtp/serve.py:39-138``: ``capture_round`` captures one whole round
+(draft, 4-row verify, extend, control mirror) into a CUDA graph after warm-up; ``generate_mtp`` replays
+it, queues round k+1 before reading round k from the host mirror, and emits the tokens each round
+committed (``emitted[0 .. commit_count)``).
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..runtime.control import Ctl
+from .block import M_VERIFY, MtpDraft
+
+
+def capture_round(mtp: MtpDraft, cp: bool = False, warmup: int = 3):
+    eng = mtp.eng
+    key = ("mtp", bool(cp))
+    if key in eng.graphs:
+        return eng.graphs[key]
+    saved = eng._snapshot()
+    y_saved = mtp.y_sel.clone()
+    side = torch.cuda.Stream(device=eng.dev)
+    side.wait_stream(torch.cuda.current_stream(eng.dev))
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            mtp.round(cp=cp)
+    torch.cuda.current_stream(eng.dev).wait_stream(side)
+    torch.cuda.synchronize(eng.dev)
+    if eng.world > 1:
+        dist.barrier(group=eng.group)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        mtp.round(cp=cp)
+    eng._restore(saved)
+    mtp.y_sel.copy_(y_saved)
+    eng.graphs[key] = g
+    if eng.world > 1:
+        dist.barrier(group=eng.group)
+    return g
+
+
+def generate_mtp(mtp: MtpDraft, graph=None, max_new: int = 16, eos: Optional[int] = None,
+                 on_tokens: Optional[Callable[[List[int]], None]] = None, stats: Optional[dict] = None) -> List[int]:
+    """Decode up to ``max_new`` tokens by replaying the round graph.  Returns the emitted tokens
+    (the sequence is exactly what plain greedy / sampled decode would emit: drafts only decide how
+    many tokens a round commits).  ``stats`` receives ``rounds`` and ``accept_mean``."""
+    eng = mtp.eng
+    graph = graph or capture_round(mtp)
+    eng.mirror.resync()
+    out: List[int] = []
+    budget = eng._kv_budget() - 2 * M_VERIFY
+    rounds, accepted = 0, 0
+    pending = [_launch(eng, graph)]
+    while pending:
+        if len(pending) < 2 and len(out) + len(pending) < max_new:   # every round commits at least one token
+            pending.append(_launch(eng, graph))
+        words = eng.mirror.wait(pending.pop(0))
+        if words[Ctl.STATUS] != 0 or words[Ctl.COMMIT_COUNT] <= 0:
+            for gen in pending:
+                eng.mirror.wait(gen)
+            raise RuntimeError(f"MTP round failed: status {words[Ctl.STATUS]}")
+        n = words[Ctl.COMMIT_COUNT]
+        toks = words[Ctl.EMITTED : Ctl.EMITTED + n]
+        rounds += 1
+        accepted += n
+        stop = False
+        for t in toks:
+            out.append(t)
+            if (eos is not None and t == eos) or len(out) >= max_new:
+                stop = True
+                break
+        if on_tokens:
+            on_tokens(toks[: len(toks) if not stop else None])
+        if stop or words[Ctl.COMMITTED_LEN] >= budget:
+            for gen in pending:
+                eng.mirror.wait(gen)
+            break
+    if stats is not None:
+        stats.update(rounds=rounds, accept_mean=accepted / max(rounds, 1))
+    return out[:max_new]
+
+
+def _launch(eng, graph) -> int:
+    graph.replay()
+    return eng.mirror.next_gen()

@@ -58,6 +58,13 @@ _PROTOTYPES = {
     "nexrt_moe_l2_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, ci, vp],
     "nexrt_lmhead_sample": [vp] * 9 + [ci] * 4 + [cf, ci, ci, CH, cu, ci, vp],
     "nexrt_sample_logits": [vp, vp, vp, ci, ci, vp],
+    "nexrt_mtp_prep": [vp, vp, ci, ci, vp],
+    "nexrt_mtp_preprocess": [vp] * 7 + [ci] * 4 + [cf, ci, ci, vp],
+    "nexrt_row_select": [vp, vp, vp, ci, ci, vp],
+    "nexrt_zero_rows": [vp, ci, vp],
+    "nexrt_dflash_noise": [vp, vp, vp, vp, ci, ci, ci, ci, vp],
+    "nexrt_dflash_commit": [vp, vp, ci, vp],
+    "nexrt_feature_tap": [vp, vp, ci, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],
     "nexrt_ipc_get_handle": [vp, vp],
     "nexrt_ipc_open": [vp, POINTER(c_void_p)],

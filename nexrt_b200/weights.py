@@ -213,10 +213,11 @@ def shard_linear_attention(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, 
     }
 
 
-def shard_attention(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device) -> Dict[str, torch.Tensor]:
+def shard_attention(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device, base: Optional[str] = None) -> Dict[str, torch.Tensor]:
     """Attention shard: this rank's q heads (query|gate interleaved per head) plus the kv head(s)
     it serves (reference weights.py:84-105)."""
-    a = f"{PFX}layers.{layer}.self_attn."
+    base = base or f"{PFX}layers.{layer}."
+    a = base + "self_attn."
     hd, r = cfg.head_dim, spec.rank
     qrows = spec.q_heads * 2 * hd
     kvrows = spec.kv_heads * hd
@@ -238,7 +239,7 @@ def shard_attention(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device)
     d = lambda t: t.contiguous().to(device)
     return {
         "kind": "full",
-        "in_ln": d(_gamma(ckpt[f"{PFX}layers.{layer}.input_layernorm.weight"])),
+        "in_ln": d(_gamma(ckpt[base + "input_layernorm.weight"])),
         "front_w": d(front_w).view(FP8),
         "front_s": d(front_s),
         "qn": d(_gamma(_g(ckpt, a + "q_norm.weight"))),
@@ -248,10 +249,11 @@ def shard_attention(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device)
     }
 
 
-def shard_moe(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device, prefix: Optional[str] = None) -> Dict[str, torch.Tensor]:
+def shard_moe(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device, base: Optional[str] = None) -> Dict[str, torch.Tensor]:
     """MoE shard: every expert, ``inter/tp`` of its intermediate columns (reference moe.py:145-171);
     the shared expert is stored as expert index ``n_experts``."""
-    m = prefix or f"{PFX}layers.{layer}.mlp."
+    base = base or f"{PFX}layers.{layer}."
+    m = base + "mlp."
     E, I, Il, r, H = cfg.n_experts, cfg.moe_inter, spec.inter, spec.rank, cfg.hidden
     w13 = torch.empty(E + 1, 2 * Il, H, dtype=torch.uint8)
     w13s = torch.empty(E + 1, 2 * Il // BLOCK, H // BLOCK, dtype=torch.float32)
@@ -267,9 +269,8 @@ def shard_moe(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device, prefi
         w2s[e] = _g(ckpt, ep + "down_proj.weight_scale_inv").float()[:, r * nb : (r + 1) * nb].cpu()
     router = torch.cat([_g(ckpt, m + "gate.weight"), _g(ckpt, m + "shared_expert_gate.weight").reshape(1, H)], 0)
     d = lambda t: t.contiguous().to(device)
-    post = f"{PFX}layers.{layer}.post_attention_layernorm.weight"
     return {
-        "post_ln": d(_gamma(ckpt[post if prefix is None else prefix.replace("mlp.", "post_attention_layernorm.weight")])),
+        "post_ln": d(_gamma(ckpt[base + "post_attention_layernorm.weight"])),
         "router_w": d(router.to(torch.bfloat16)),
         "w13": d(w13).view(FP8),
         "w13_s": d(w13s),
