@@ -56,7 +56,7 @@ class FullAttn:
             lib.nexrt_attn_decode(
                 ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw), ptr(self.w["qn"]), ptr(self.w["kn"]), ptr(c.inv_freq), ptr(c.rope_table(self.cache_len)), ptr(ctl), ptr(self.k_cache),
                 ptr(self.v_cache), ptr(c.ws_acc), ptr(c.ws_ml), ptr(c.attn_ticket), ptr(c.attn_out), cfg.head_dim, nq, spec.q_heads,
-                spec.kv_heads, M, self.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, spec.cp_size if use_cp else 1,
+                spec.kv_heads, M, self.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, 0, 0, 0, 0, spec.cp_size if use_cp else 1,
                 spec.cp_rank if use_cp else 0, c.cp_channel.ref if use_cp else None, cp_site, st,
             ),
             "attn_decode",

@@ -50,8 +50,8 @@ int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void
 size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M);
 int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
                       const void* rope_table, const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out, int hd, int nq,
-                      int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int cp_size, int cp_rank,
-                      const NexrtLLChannel* ch, unsigned int site, void* stream);
+                      int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int flags, int window, int ldq, int ldk,
+                      int cp_size, int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream);
 
 /* output projection + all-reduce + residual.  mode 0: plain fp32 input; 1: GDN gated RMSNorm of
  * (in, z); 2: context-parallel merge of the partials waiting in `cp` followed by * sigmoid(gate).
@@ -84,7 +84,14 @@ int nexrt_row_select(const void* x, const void* ctl, void* y, int H, int rows, v
 int nexrt_zero_rows(void* x, int n, void* stream);
 int nexrt_dflash_noise(const void* embed, const void* ctl, void* noise, void* dctl, int H, int vocab, int mask_id, int rows, void* stream);
 int nexrt_dflash_commit(void* ctl, const void* dctl, int rows, void* stream);
-int nexrt_feature_tap(const void* x, void* tap, int n, void* stream);
+int nexrt_feature_tap(const void* x, void* tap, int H, int ld, int col0, int M, void* stream);
+
+/* dense BF16 projection (dense.cu).  in_mode 0: bf16 rows + RMSNorm * gamma, 1: fp32 rows, 2: SwiGLU of
+ * fp32 [gate | up], 3: bf16 rows as they are; ld_in = input row stride in elements (0: packed); out_mode 0: fp32 out, 1: all-reduce + residual add into bf16 x, 2: all-reduce + store. */
+int nexrt_dense_bf16(const void* in, const void* gamma, const void* w, void* out, void* x, int R, int K, int M, int in_mode, int out_mode,
+                     int ld_in, float eps, const NexrtLLChannel* ch, unsigned int site, void* stream);
+int nexrt_kv_publish(const void* kv, int ld, int k_off, int v_off, const void* kn, const void* rope_table, const void* ctl, void* k_cache,
+                     void* v_cache, int hd, int kvh, int M, int cache_len, int rotary, float eps, int ring, void* stream);
 
 /* host runtime (host_runtime.cu) */
 int nexrt_ipc_alloc(size_t bytes, void** ptr);

@@ -146,6 +146,9 @@ struct AttnDecodeArgs {
     int nq, ngate, kvh, M, cache_len, rotary, n_splits;
     float eps;
     // context parallel
+    int ldq, ldk;             // row strides of q_raw / k_raw in floats (0: packed)
+    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate
+    int window;               // > 0: sliding window, only the last `window` positions are attended
     int cp_size, cp_rank;     // window of the prefix this rank attends
     LLChannel ch;             // partial exchange inside the cp group (world == cp_size)
     unsigned int site;
@@ -169,6 +172,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     const int C0 = a.ctl[kCtlCommittedLen];
     // key window of this rank: [win_lo, win_hi) of positions, new rows included on the last cp rank
     int win_lo = 0, win_hi = C0 + a.M;
+    if (a.window > 0) win_lo = max(0, win_hi - a.window);
     if (a.cp_size > 1) {
         const int share = C0 / a.cp_size;
         win_lo = a.cp_rank * share;
@@ -190,8 +194,9 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     for (int v = warp; v < rows + a.M; v += NW) {
         const bool is_q = v < rows;
         const int m = is_q ? v / G : v - rows;
-        const float* src = is_q ? a.q_raw + (static_cast<size_t>(m) * a.nq + kv * G + (v % G)) * HD
-                                : a.k_raw + (static_cast<size_t>(m) * a.kvh + kv) * HD;
+        const size_t ldq = a.ldq ? a.ldq : static_cast<size_t>(a.nq) * HD, ldk = a.ldk ? a.ldk : static_cast<size_t>(a.kvh) * HD;
+        const float* src = is_q ? a.q_raw + static_cast<size_t>(m) * ldq + static_cast<size_t>(kv * G + (v % G)) * HD
+                                : a.k_raw + static_cast<size_t>(m) * ldk + static_cast<size_t>(kv) * HD;
         float* dst = is_q ? q_s + static_cast<size_t>(v) * HD : k_s + static_cast<size_t>(m) * HD;
         const float* gam = is_q ? a.qn : a.kn;
         float e[EL], ss = 0.f;
@@ -250,7 +255,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
 #pragma unroll
             for (int i = 0; i < EL; ++i) { q[r][i] = q_s[static_cast<size_t>(rr) * HD + lane * EL + i]; acc[r][i] = 0.f; }
             mx[r] = -INFINITY; l[r] = 0.f;
-            limit[r] = (r < nr) ? C0 + rr / G : -1;   // last visible position of the row
+            limit[r] = (r < nr) ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + rr / G) : -1;   // last visible position of the row
         }
         constexpr int KBATCH = 4;   // keys whose K and V rows are in flight together per warp
         for (int pb = lo + warp; pb < hi; pb += NW * KBATCH) {
@@ -395,8 +400,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         const float ctx = L_ > 0.f ? A_ / L_ : 0.f;
         if (a.cp_size == 1) {
             const int head = kv * G + hg;
-            const float gt = a.gate[(static_cast<size_t>(m) * a.ngate + head) * HD + d];
-            a.out[(static_cast<size_t>(m) * a.ngate + head) * HD + d] = ctx * sigmoid_f(gt);
+            const float gt = (a.flags & 2) ? 0.f : a.gate[(static_cast<size_t>(m) * a.ngate + head) * HD + d];
+            a.out[(static_cast<size_t>(m) * a.ngate + head) * HD + d] = (a.flags & 2) ? ctx : ctx * sigmoid_f(gt);
         } else {
             // head hg of the group belongs to cp rank hg / ngate; slot layout at the owner:
             // [m][local head][HD + 1] with the LSE in the last slot
@@ -447,8 +452,8 @@ extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
 
 extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void* k_raw, const void* qn, const void* kn, const void* inv_freq,
                                  const void* rope_table, const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out,
-                                 int hd, int nq, int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int cp_size,
-                                 int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream) {
+                                 int hd, int nq, int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int flags,
+                                 int window, int ldq, int ldk, int cp_size, int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream) {
     if (M < 1 || M > kMaxRows || nq % kvh || rotary > 64 || rotary % 2) return cudaErrorInvalidValue;
     if (cp_size > 1 && ch == nullptr) return cudaErrorInvalidValue;
     if (n_splits > 160) return cudaErrorInvalidValue;
@@ -460,6 +465,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     a.v_cache = static_cast<const __nv_bfloat16*>(v_cache); a.ws_acc = static_cast<float*>(ws_acc); a.ws_ml = static_cast<float*>(ws_ml);
     a.ticket = static_cast<int*>(ticket); a.out = static_cast<float*>(out);
     a.nq = nq; a.ngate = ngate; a.kvh = kvh; a.M = M; a.cache_len = cache_len; a.rotary = rotary; a.n_splits = n_splits; a.eps = eps;
+    a.flags = flags; a.window = window; a.ldq = ldq; a.ldk = ldk;
     a.cp_size = cp_size; a.cp_rank = cp_rank; a.site = site;
     if (ch) a.ch = *ch;
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);

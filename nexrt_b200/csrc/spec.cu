@@ -132,11 +132,15 @@ __global__ void __launch_bounds__(32) dflash_commit_kernel(int* __restrict__ ctl
     }
 }
 
-__global__ void __launch_bounds__(256) feature_tap_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ tap, int n) {
+// tap[m][col0 .. col0 + H) = x[m][0 .. H) for the rows of the step (tap rows are ld elements apart).
+__global__ void __launch_bounds__(256) feature_tap_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ tap, int H, int ld,
+                                                          int col0) {
     pdl_launch_dependents();
     pdl_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n / 8) reinterpret_cast<uint4*>(tap)[i] = reinterpret_cast<const uint4*>(x)[i];
+    const int m = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * H);
+    uint4* dst = reinterpret_cast<uint4*>(tap + static_cast<size_t>(m) * ld + col0);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
 }  // namespace nexrt
@@ -180,8 +184,8 @@ extern "C" int nexrt_dflash_commit(void* ctl, const void* dctl, int rows, void* 
                   static_cast<const int*>(dctl), rows);
 }
 
-extern "C" int nexrt_feature_tap(const void* x, void* tap, int n, void* stream) {
-    if (n % 8) return cudaErrorInvalidValue;
-    return launch(feature_tap_kernel, dim3((n / 8 + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream),
-                  static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(tap), n);
+extern "C" int nexrt_feature_tap(const void* x, void* tap, int H, int ld, int col0, int M, void* stream) {
+    if (H % 8 || ld % 8 || col0 % 8 || M < 1 || M > kMaxRows) return cudaErrorInvalidValue;
+    return launch(feature_tap_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
+                  static_cast<__nv_bfloat16*>(tap), H, ld, col0);
 }

@@ -79,6 +79,9 @@ class DecodeEngine:
         self.mirror = CtlMirror(self.dev, CTL_WORDS)
         self.graphs: Dict = {}
         self._n_sites: Dict = {}
+        # DFlash feature taps: residual rows after the MoE of chosen layers, concatenated per row
+        self.tap_layers: Dict[int, int] = {}
+        self.taps: Optional[torch.Tensor] = None
         if world > 1:
             dist.barrier(group=group)
 
@@ -131,15 +134,25 @@ class DecodeEngine:
         if begin:
             c.begin_step()
         check(c.lib.nexrt_embed_gather(ptr(self.embed), ptr(c.ctl), ptr(c.x), ptr(c.status), self.cfg.hidden, self.cfg.vocab, M, c.stream()), "embed")
-        for mixer, moe in zip(self.mixers, self.moes):
+        for layer, (mixer, moe) in enumerate(zip(self.mixers, self.moes)):
             if isinstance(mixer, FullAttn):
                 mixer.forward(M, cp=cp)
             else:
                 mixer.forward(M)
             moe.forward(M)
+            if self.taps is not None and layer in self.tap_layers:
+                check(c.lib.nexrt_feature_tap(ptr(c.x), ptr(self.taps), self.cfg.hidden, self.taps.shape[1],
+                                              self.tap_layers[layer] * self.cfg.hidden, M, c.stream()), "feature_tap")
         self.head.forward(M, mode=head_mode)
         if end:
             self.step_end()
+
+    def enable_taps(self, layer_ids: Sequence[int]) -> torch.Tensor:
+        """Record the residual rows after the MoE of ``layer_ids`` into ``taps [8][n * H]`` on every
+        step (reference M8FeatTapKernel, kernels/embed/nex_n2_5_pro_m8_feature_tap_ctypes.cu:45-68)."""
+        self.tap_layers = {int(l): i for i, l in enumerate(layer_ids)}
+        self.taps = torch.zeros(8, len(self.tap_layers) * self.cfg.hidden, dtype=torch.bfloat16, device=self.dev)
+        return self.taps
 
     def step_cp(self, M: int = 1) -> None:
         self.step(M, cp=True)

@@ -38,13 +38,14 @@ class Head:
             self.logits = torch.zeros(8, self.ctx.spec.vocab, dtype=torch.float32, device=self.ctx.device)
         return self.logits
 
-    def forward(self, M: int = 1, mode: int = MODE_COMMIT, arg: int = 0, x: Optional[torch.Tensor] = None) -> None:
+    def forward(self, M: int = 1, mode: int = MODE_COMMIT, arg: int = 0, x: Optional[torch.Tensor] = None,
+                ctl: Optional[torch.Tensor] = None) -> None:
         c, w = self.ctx, self.w
         cfg, spec = c.cfg, c.spec
         check(
             c.lib.nexrt_lmhead_sample(
                 ptr(c.x if x is None else x), ptr(w["final_ln"]), ptr(w["lm_head"]), ptr(self.logits), ptr(c.head_cand), ptr(c.head_ticket),
-                ptr(c.sampling), ptr(c.ctl), ptr(c.head_export), cfg.hidden, spec.vocab, spec.rank * spec.vocab, M, cfg.rms_eps, mode, arg,
+                ptr(c.sampling), ptr(c.ctl if ctl is None else ctl), ptr(c.head_export), cfg.hidden, spec.vocab, spec.rank * spec.vocab, M, cfg.rms_eps, mode, arg,
                 c.channel.ref, c.next_site(), c.n_cta, c.stream(),
             ),
             "lmhead_sample",

@@ -51,7 +51,7 @@ _PROTOTYPES = {
     "nexrt_gdn_front": [vp] * 14 + [ci] * 6 + [cf, ci, ci, vp],
     "nexrt_gdn_core": [vp] * 6 + [ci] * 5 + [vp],
     "nexrt_attn_front": [vp] * 9 + [ci] * 7 + [cf, ci, vp],
-    "nexrt_attn_decode": [vp] * 14 + [ci] * 8 + [cf, ci, ci, CH, cu, vp],
+    "nexrt_attn_decode": [vp] * 14 + [ci] * 8 + [cf, ci, ci, ci, ci, ci, ci, CH, cu, vp],
     "nexrt_oproj_allreduce": [vp] * 6 + [ci] * 4 + [cf, ci, CH, cu, CH, cu, ci, vp],
     "nexrt_moe_router": [vp] * 8 + [ci] * 5 + [cf, ci, vp],
     "nexrt_moe_l1": [vp] * 6 + [ci] * 4 + [cf, ci, ci, vp],
@@ -64,7 +64,9 @@ _PROTOTYPES = {
     "nexrt_zero_rows": [vp, ci, vp],
     "nexrt_dflash_noise": [vp, vp, vp, vp, ci, ci, ci, ci, vp],
     "nexrt_dflash_commit": [vp, vp, ci, vp],
-    "nexrt_feature_tap": [vp, vp, ci, vp],
+    "nexrt_feature_tap": [vp, vp, ci, ci, ci, ci, vp],
+    "nexrt_dense_bf16": [vp] * 5 + [ci] * 6 + [cf, CH, cu, vp],
+    "nexrt_kv_publish": [vp, ci, ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],
     "nexrt_ipc_get_handle": [vp, vp],
     "nexrt_ipc_open": [vp, POINTER(c_void_p)],
