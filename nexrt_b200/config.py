@@ -144,6 +144,12 @@ def shrunk_config() -> ModelConfig:
     )
 
 
+def shrunk_cp_config() -> ModelConfig:
+    """Shrunk geometry that can be split 4 ways: 2 kv heads over 4 ranks gives context-parallel groups
+    of 2 (multi-GPU tests of the CP arm)."""
+    return replace(shrunk_config(), name="nex-shrunk-cp", moe_inter=512, shared_inter=512)
+
+
 @dataclass(frozen=True)
 class ShardSpec:
     """What one tensor-parallel rank owns.

@@ -249,6 +249,31 @@ def shard_attention(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device,
     }
 
 
+def shard_attention_cp(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device, base: Optional[str] = None) -> Dict[str, torch.Tensor]:
+    """Context-parallel front of one rank: the query rows of EVERY q head that shares this rank's kv
+    head (the whole cp group's heads, in global head order), then the gate rows of the rank's own
+    heads, then k and v (the reference's duplicate-Q weights, attn.py:220-257)."""
+    base = base or f"{PFX}layers.{layer}."
+    a = base + "self_attn."
+    hd = cfg.head_dim
+    qw = _g(ckpt, a + "q_proj.weight").view(torch.uint8)
+    qs = _g(ckpt, a + "q_proj.weight_scale_inv").float()
+    g0 = spec.cp_group[0] * spec.q_heads                      # first global q head of the group
+    n_all = spec.q_heads * spec.cp_size
+    hb = hd // BLOCK
+    rows, scales = [], []
+    for h in range(g0, g0 + n_all):                           # query halves
+        rows.append(qw[h * 2 * hd : h * 2 * hd + hd]); scales.append(qs[h * 2 * hb : h * 2 * hb + hb])
+    for h in range(spec.rank * spec.q_heads, (spec.rank + 1) * spec.q_heads):   # own gate halves
+        rows.append(qw[h * 2 * hd + hd : (h + 1) * 2 * hd]); scales.append(qs[h * 2 * hb + hb : (h + 1) * 2 * hb])
+    kv0, kvrows = spec.kv_head0 * hd, spec.kv_heads * hd
+    for nm in ("k_proj", "v_proj"):
+        rows.append(_g(ckpt, a + nm + ".weight").view(torch.uint8)[kv0 : kv0 + kvrows])
+        scales.append(_g(ckpt, a + nm + ".weight_scale_inv").float()[kv0 // BLOCK : (kv0 + kvrows) // BLOCK])
+    d = lambda t: t.contiguous().to(device)
+    return {"front_w": d(torch.cat(rows, 0)).view(FP8), "front_s": d(torch.cat(scales, 0))}
+
+
 def shard_moe(ckpt, cfg: ModelConfig, layer: int, spec: ShardSpec, device, base: Optional[str] = None) -> Dict[str, torch.Tensor]:
     """MoE shard: every expert, ``inter/tp`` of its intermediate columns (reference moe.py:145-171);
     the shared expert is stored as expert index ``n_experts``."""
@@ -290,16 +315,21 @@ def shard_head(ckpt, cfg: ModelConfig, spec: ShardSpec, device) -> Dict[str, tor
     }
 
 
-def shard_model(ckpt, cfg: ModelConfig, tp: int, rank: int, device) -> Dict:
-    """All tensors one rank needs, in kernel layout."""
+def shard_model(ckpt, cfg: ModelConfig, tp: int, rank: int, device, cp: bool = False) -> Dict:
+    """All tensors one rank needs, in kernel layout.  ``cp`` adds the context-parallel attention
+    fronts (``mixer_cp``) when the rank shares its kv head with other ranks."""
     spec = ShardSpec(cfg, tp, rank)
     layers = []
     for layer in range(cfg.n_layers):
+        entry = {}
         if cfg.layer_types[layer] == "linear":
             mix = shard_linear_attention(ckpt, cfg, layer, spec, device)
         else:
             mix = shard_attention(ckpt, cfg, layer, spec, device)
-        layers.append({"mixer": mix, "moe": shard_moe(ckpt, cfg, layer, spec, device)})
+            if cp and spec.cp_size > 1:
+                entry["mixer_cp"] = shard_attention_cp(ckpt, cfg, layer, spec, device)
+        entry.update(mixer=mix, moe=shard_moe(ckpt, cfg, layer, spec, device))
+        layers.append(entry)
     return {"spec": spec, "layers": layers, "head": shard_head(ckpt, cfg, spec, device)}
 
 

