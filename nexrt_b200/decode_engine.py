@@ -277,15 +277,25 @@ class DecodeEngine:
         return min(lens) if lens else 1 << 30
 
     # ---- prefill ------------------------------------------------------------------------------
-    def prefill(self, ids: Sequence[int], chunk: int = 8, sample: bool = True) -> int:
-        """The engine's own chunked prefill: consume ``ids`` from an empty state and leave the
-        first generated token pending.  This arm runs the multi-row step kernels ``chunk`` rows at
-        a time with a forced full commit, so the state it leaves is the decode path's own."""
+    def prefill(self, ids: Sequence[int], chunk: int = 8, sample: bool = True, resume_from: int = 0,
+                on_chunk: Optional[Callable[[int, int], None]] = None) -> int:
+        """The engine's own chunked prefill: consume ``ids`` and leave the first generated token
+        pending.  This arm runs the multi-row step kernels ``chunk`` rows at a time with a forced full
+        commit, so the state it leaves is the decode path's own.  ``resume_from > 0`` keeps the state
+        of the first ``resume_from`` tokens (which must be what the engine currently holds) and only
+        evaluates the suffix; ``on_chunk(start, end)`` is called after each chunk is queued."""
         if self.max_rows < min(chunk, len(ids)) and len(ids) > 1:
             chunk = self.max_rows
         ids = list(int(t) for t in ids)
-        self.reset(first_token=ids[0])
-        pos = 0
+        if resume_from:
+            have = int(self.ctx.ctl[Ctl.COMMITTED_LEN].item())
+            if have != resume_from or resume_from > len(ids):
+                raise ValueError(f"cannot resume at {resume_from}: the engine holds {have} tokens")
+            if resume_from == len(ids):
+                return int(self.ctx.ctl[Ctl.PENDING].item())
+        else:
+            self.reset(first_token=ids[0])
+        pos = resume_from
         while pos < len(ids):
             n = min(chunk, len(ids) - pos)
             self.set_rows(ids[pos : pos + n])
@@ -295,6 +305,8 @@ class DecodeEngine:
                 g.replay()
             else:
                 self.step(n)
+            if on_chunk is not None:
+                on_chunk(pos, pos + n)
             pos += n
         self.set_forced_commit(0)
         torch.cuda.synchronize(self.dev)
