@@ -171,6 +171,24 @@ class DecodeEngine:
             dist.all_reduce(s, op=dist.ReduceOp.MAX, group=self.group)
         return int(s.item())
 
+    def logit_gap(self, a: int, b: int, row: int = 0) -> Optional[float]:
+        """``|logit[a] - logit[b]|`` of one row of the last step, over the vocabulary shards of all ranks
+        (``head.enable_logits()`` must have been called before the step or its capture)."""
+        if self.head.logits is None:
+            return None
+        v, base = self.spec.vocab, self.spec.rank * self.spec.vocab
+        vals = torch.full((2,), float("-inf"), dtype=torch.float32, device=self.dev)
+        for i, t in enumerate((a, b)):
+            if base <= t < base + v:
+                vals[i] = self.head.logits[row, t - base]
+        if self.world > 1:
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX, group=self.group)
+        return float((vals[0] - vals[1]).abs().item())
+
+    @property
+    def cp_threshold(self) -> int:
+        return CP_THRESHOLD
+
     # ---- graphs -------------------------------------------------------------------------------
     def capture(self, M: int = 1, cp: bool = False, warmup: int = WARMUP_STEPS):
         """Warm up, then capture one whole step into a CUDA graph (reference

@@ -1,0 +1,98 @@
+"""Split a Hugging Face sharded checkpoint into the per-layer files the loader reads.
+
+Output layout (same file names as the reference's ``tools/extract_layers.py:47-130``):
+``layer.<L>.safetensors`` for every decoder layer, ``embed_tokens.safetensors``, ``norm.safetensors``,
+``lm_head.safetensors`` and, when the source carries ``mtp.*`` tensors, ``mtp.safetensors``.  Scale
+tensors are written in fp32 under ``*.weight_scale_inv`` whichever of the two names the source uses.
+The source is read shard by shard through ``model.safetensors.index.json`` so peak host memory is one
+layer.
+
+    python -m nexrt_b200.extract_layers --src /ckpt/Nex-N2.5-Pro --dst /data/nexrt-layers [--layers 0 1 2]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+from typing import Dict, Iterable, List, Optional
+
+from .config import full_config
+from .weights import PFX
+
+GLOBAL_FILES = {"embed_tokens.safetensors": PFX + "embed_tokens.weight", "norm.safetensors": PFX + "norm.weight", "lm_head.safetensors": "lm_head.weight"}
+
+
+def canonical_key(key: str) -> str:
+    return key + "_inv" if key.endswith(".weight_scale") else key
+
+
+def plan_outputs(weight_map: Dict[str, str], layers: Iterable[int], with_globals: bool = True, with_mtp: bool = True) -> Dict[str, List[str]]:
+    """``{output file: [source keys]}``; raises ``KeyError`` for a layer or global tensor the source lacks."""
+    out: Dict[str, List[str]] = {}
+    for L in layers:
+        pref = f"{PFX}layers.{L}."
+        keys = sorted(k for k in weight_map if k.startswith(pref))
+        if not keys:
+            raise KeyError(f"no tensors for layer {L} in the source index")
+        out[f"layer.{L}.safetensors"] = keys
+    if with_globals:
+        for name, key in GLOBAL_FILES.items():
+            if key not in weight_map:
+                raise KeyError(f"required tensor {key} missing from the source index")
+            out[name] = [key]
+    mtp = sorted(k for k in weight_map if k.startswith("mtp."))
+    if with_mtp and mtp:
+        out["mtp.safetensors"] = mtp
+    return out
+
+
+def extract(src: str, dst: str, layers: Optional[Iterable[int]] = None, with_globals: bool = True, with_mtp: bool = True, log=print) -> Dict[str, int]:
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    with open(os.path.join(src, "model.safetensors.index.json"), encoding="utf-8") as f:
+        weight_map = json.load(f)["weight_map"]
+    n_layers = full_config().n_layers
+    layers = range(n_layers) if layers is None else list(layers)
+    targets = plan_outputs(weight_map, layers, with_globals, with_mtp)
+    os.makedirs(dst, exist_ok=True)
+    written, t0 = {}, time.time()
+    for name, keys in targets.items():
+        by_shard: Dict[str, List[str]] = {}
+        for k in keys:
+            by_shard.setdefault(weight_map[k], []).append(k)
+        tensors = {}
+        for shard, ks in sorted(by_shard.items()):
+            with safe_open(os.path.join(src, shard), framework="pt", device="cpu") as f:
+                for k in ks:
+                    ck = canonical_key(k)
+                    if ck in tensors and ck != k:
+                        continue                      # both spellings present: keep the first
+                    t = f.get_tensor(k)
+                    tensors[ck] = t.float() if ck.endswith(".weight_scale_inv") else t
+        tmp = os.path.join(dst, name + f".{os.getpid()}.tmp")
+        save_file(tensors, tmp)
+        os.replace(tmp, os.path.join(dst, name))
+        written[name] = len(tensors)
+        log(f"  wrote {name}: {len(tensors)} tensors, {sum(v.numel() * v.element_size() for v in tensors.values()) / 1e9:.2f} GB (t={time.time() - t0:.1f}s)")
+    return written
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--src", required=True)
+    ap.add_argument("--dst", default=os.environ.get("NEXRT_LAYERS_DIR"))
+    ap.add_argument("--layers", type=int, nargs="*", default=None)
+    ap.add_argument("--no-globals", action="store_true")
+    ap.add_argument("--no-mtp", action="store_true")
+    a = ap.parse_args(argv)
+    if not a.dst:
+        ap.error("--dst or NEXRT_LAYERS_DIR is required")
+    extract(a.src, a.dst, a.layers, not a.no_globals, not a.no_mtp)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

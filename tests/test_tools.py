@@ -1,0 +1,77 @@
+"""Host-side tools: checkpoint splitter, exact-length prompts, corpus builder, chat client parsing,
+state-file naming, preflight."""
+
+import json
+
+import pytest
+import torch
+
+from nexrt_b200.extract_layers import canonical_key, extract, plan_outputs
+from nexrt_b200.extract_state import make_prompt, state_dir
+from nexrt_b200.prep_english_docs import clean_turn, collect
+from nexrt_b200.real_prompts import build_real_prompt, fixed_suffix_len
+from nexrt_b200.serve.bridge_serve import ByteTokenizer
+from nexrt_b200.serve.launch import preflight
+from nexrt_b200.serve.stream_chat import completion_url, parse_sse, payload
+from nexrt_b200.weights import PFX
+
+
+def test_extract_layers_splits_and_normalises_scale_names(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    src, dst = tmp_path / "src", tmp_path / "dst"
+    src.mkdir()
+    a = {f"{PFX}layers.0.mlp.gate.weight": torch.ones(2, 2), f"{PFX}layers.0.self_attn.q_proj.weight_scale": torch.ones(1, 1, dtype=torch.bfloat16),
+         f"{PFX}embed_tokens.weight": torch.zeros(4, 2)}
+    b = {f"{PFX}layers.1.mlp.gate.weight": torch.full((2, 2), 2.0), f"{PFX}layers.1.self_attn.q_proj.weight_scale_inv": torch.ones(1, 1),
+         f"{PFX}norm.weight": torch.zeros(2), "lm_head.weight": torch.zeros(4, 2), "mtp.fc.weight": torch.zeros(2, 4)}
+    save_file(a, str(src / "model-00001.safetensors"))
+    save_file(b, str(src / "model-00002.safetensors"))
+    wm = {**{k: "model-00001.safetensors" for k in a}, **{k: "model-00002.safetensors" for k in b}}
+    (src / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    written = extract(str(src), str(dst), layers=[0, 1], log=lambda *_: None)
+    assert set(written) == {"layer.0.safetensors", "layer.1.safetensors", "embed_tokens.safetensors", "norm.safetensors", "lm_head.safetensors", "mtp.safetensors"}
+    l0 = load_file(str(dst / "layer.0.safetensors"))
+    key = f"{PFX}layers.0.self_attn.q_proj.weight_scale_inv"
+    assert key in l0 and l0[key].dtype == torch.float32 and canonical_key("x.weight_scale") == "x.weight_scale_inv"
+    assert not list(dst.glob("*.tmp"))
+    with pytest.raises(KeyError):
+        plan_outputs(wm, [5])
+    with pytest.raises(KeyError):
+        plan_outputs({k: v for k, v in wm.items() if k != "lm_head.weight"}, [0])
+
+
+@pytest.mark.parametrize("L", [16, 64, 257, 3000])
+def test_real_prompt_has_exact_length_and_intact_tail(L):
+    tok = ByteTokenizer()
+    ids = build_real_prompt(L, tok)
+    tail = fixed_suffix_len(tok)
+    full = tok.apply_chat_template([{"role": "user", "content": "zz"}], tokenize=True, add_generation_prompt=True)
+    assert len(ids) == L and ids == build_real_prompt(L, tok) and ids[-tail:] == full[-tail:]
+    with pytest.raises(ValueError):
+        build_real_prompt(4, tok)
+
+
+def test_corpus_builder_filters_turns():
+    long_text = "word " * 200
+    assert clean_turn("short") is None and clean_turn(long_text + "```code```") == long_text.strip()
+    assert clean_turn("é" * 1000) is None
+    recs = [{"conversations": [{"from": "human", "value": long_text}, {"from": "gpt", "value": long_text}]}, "junk", {"conversations": [{"from": "gpt", "value": long_text}]}]
+    assert len(list(collect(recs, 10))) == 1 and len(list(collect(recs, 10 ** 9))) == 2
+
+
+def test_chat_client_helpers():
+    assert completion_url("http://h:1/v1/") == "http://h:1/v1/chat/completions" == completion_url("http://h:1/v1/chat/completions")
+    body = payload("m", [{"role": "user", "content": "x"}], "k", 5, seed=3)
+    assert body["stream"] and body["cache_key"] == "k" and body["seed"] == 3 and "seed" not in payload("m", [], "k", 5)
+    lines = [b": comment\n", b'data: {"a": 1}\n', b"\n", b"data: [DONE]\n", b'data: {"never": 1}\n']
+    assert list(parse_sse(iter(lines))) == [{"a": 1}]
+
+
+def test_state_dir_prompt_and_preflight(tmp_path):
+    assert state_dir("/x", 60, 1024).name == "prefill_state_60_1024"
+    p = make_prompt(33, 1000)
+    assert len(p) == 33 and p == make_prompt(33, 1000) and max(p) < 1000
+    rows = {r["check"]: r for r in preflight(3, layers_dir=str(tmp_path), probe_gpu=False)}
+    assert not rows["tp degree"]["ok"] and not rows["layer directory"]["ok"] and "embed_tokens" in rows["layer directory"]["detail"]
+    assert {r["check"]: r["ok"] for r in preflight(8, probe_gpu=False)}["tp degree"]
