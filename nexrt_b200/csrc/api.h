@@ -103,6 +103,17 @@ int nexrt_host_mapped_alloc(size_t bytes, void** host, void** dev);
 int nexrt_host_mapped_free(void* host);
 int nexrt_host_wait_flag(const volatile int* flag, int want, double timeout_s);
 
+// ---- tensor-core GEMM (tcgen05 + TMEM + TMA) for many-row work; tc_gemm.cu ---------------------------------
+// Y[T, R] = dequant(Xq, sx) * dequant(Wq, sw)^T.  Wq [R, K] e4m3 with row stride ldw, sw [ceil(R/128), K/128],
+// Xq [T, K] e4m3, sx [T, K/128]; out_mode 0 fp32 store, 1 bf16 store, 2 fp32 accumulate.  K % 128 == 0, K <= 8192.
+int nexrt_tc_gemm_fp8(const void* wq, const float* sw, int64_t ldw, const void* xq, const float* sx, void* y, int T, int R, int K, int ldy,
+                      int out_mode, int* status, void* stream);
+// Y[T, R] = X[T, K] * W[R, K]^T, bf16 operands (leading dimensions in elements), fp32 accumulation.  K % 64 == 0, K <= 4096.
+int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, void* y, int T, int R, int K, int ldy, int out_mode, int* status,
+                       void* stream);
+// Optional RMSNorm (gamma != null, stored as the full multiplier) then per-row, per-128-column e4m3 quantisation.
+int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

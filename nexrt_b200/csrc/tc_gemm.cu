@@ -1,0 +1,479 @@
+// Tensor-core GEMM for many-row work (prefill chunks, wide verify): Y[T, R] = X[T, K] * W[R, K]^T on the
+// 5th-generation tensor cores.
+//
+//   * operands are staged by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no cluster qualifiers: every
+//     CTA fetches its own tiles, which is also the only form allowed to read a peer GPU's memory),
+//   * tcgen05.mma is issued by one thread; the weight tile is the A operand (M = 128 rows), the token tile
+//     is the B operand (N = 16..64 tokens), accumulators live in tensor memory,
+//   * FP8 variant: weights e4m3 with one fp32 scale per 128x128 block, activations e4m3 with one fp32 scale
+//     per token and 128-wide K block.  Each K block is accumulated on its own in one of two TMEM buffers
+//     and folded into fp32 registers with its scale product while the next block is being multiplied,
+//   * BF16 variant: plain kind::f16 accumulation over the whole K extent, one read-back at the end.
+//
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue (each owns
+// the 32 TMEM lanes its warp id selects).  Every wait is bounded by %globaltimer: on expiry the CTA raises
+// an abort flag, all roles leave their loops, outstanding copies are given time to land, TMEM is freed
+// and kStatusPipeTimeout is OR-ed into the caller's status word.
+//
+// The reference has no counterpart (its many-row GEMMs run inside SGLang during prefill); the block-scale
+// handling follows the checkpoint format read by nex_n2_5_pro/weights.py:27-31.
+#include <cuda.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+using namespace nexrt;
+
+constexpr int kBM = 128;            // weight rows per CTA tile == MMA M
+constexpr int kSpan = 128;          // bytes of K per stage == one swizzle span
+constexpr int kStages = 4;           // 4 x (16 KB + token tile): two CTAs fit one SM and overlap each other's prologue and epilogue
+constexpr int kAccBufs = 4;         // TMEM accumulator buffers of the FP8 variant (the MMA issuer runs this many K blocks ahead)
+constexpr int kThreads = 192;
+constexpr int kMaxKBlocks = 64;     // K <= 8192 (fp8) / 4096 (bf16)
+constexpr uint64_t kWaitBudgetNs = 200ull * 1000 * 1000;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the budget runs out or when another
+// role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T; `accumulate` == 0 overwrites D.
+template <bool FP8>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (FP8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one 128-byte swizzle span: rows 128 B
+// apart, groups of 8 rows 1024 B apart (stride byte offset), descriptor version 1, layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: fp32 accumulator, both operands K-major, N in units of 8, M in units of 16.
+template <bool FP8>
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+    const uint32_t fmt = FP8 ? 0u /* e4m3 */ : 1u /* bf16 */;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+template <int BN>
+struct Layout {
+    static constexpr int kA = kBM * kSpan;                 // 16 KB
+    static constexpr int kB = BN * kSpan;
+    static constexpr int kStage = kA + ((kB + 1023) / 1024) * 1024;
+    static constexpr int kBars = 1024;
+    // barriers first, then the stages, then the activation scales of this token tile ([kb][n], FP8 only)
+    static int total(int kblocks, bool fp8) { return kBars + kStages * kStage + (fp8 ? kblocks * BN * 4 : 0) + 1024; }
+};
+
+struct Args {
+    const float* sw;      // [ceil(R/128), KB] weight block scales (fp8 only)
+    const float* sx;      // [T, KB] activation scales (fp8 only)
+    void* y;              // [T, ldy]
+    int T, R, KB, ldy;
+    int out_mode;         // 0 fp32 store, 1 bf16 store, 2 fp32 accumulate (y += result)
+    int* status;
+};
+
+template <bool FP8, int BN>
+__global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Args a) {
+    using L = Layout<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base);
+    uint8_t* smem = base + L::kBars;
+    float* sxs = reinterpret_cast<float*>(smem + kStages * L::kStage);
+    // bars: [0, S) full, [S, 2S) empty, then kAccBufs tmem_full and kAccBufs tmem_empty
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2 * kAccBufs);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccBufs + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto tfull = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+    auto tempty = [&](int b) { return bar0 + 8u * (2 * kStages + kAccBufs + b); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;     // token tiles of one weight tile are neighbours: they share it in L2
+    const int KB = a.KB;
+    constexpr uint32_t kCols = kAccBufs * BN;                 // power of two, 64..256 columns
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        for (int b = 0; b < kAccBufs; ++b) {
+            mbar_init(tfull(b), 1);
+            mbar_init(tempty(b), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer -----------------------------------------------------------------------------
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % kStages;
+                if (!mbar_wait(empty(s), ((kb / kStages) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(full(s), L::kA + L::kB);
+                const uint32_t dst = smem_u32(smem + s * L::kStage);
+                const int c0 = kb * (FP8 ? kSpan : kSpan / 2);          // element coordinate along K
+                tma_load_2d(dst, &map_w, c0, m0, full(s));
+                tma_load_2d(dst + L::kA, &map_x, c0, n0, full(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc<FP8>(BN);
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % kStages;
+                const int buf = FP8 ? (kb % kAccBufs) : 0;
+                if (FP8 && !mbar_wait(tempty(buf), ((kb / kAccBufs) & 1) ^ 1, abort_flag)) break;
+                if (!mbar_wait(full(s), (kb / kStages) & 1, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(smem + s * L::kStage);
+                const uint64_t da = smem_desc(a0), db = smem_desc(a0 + L::kA);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)     // 4 x 32 bytes of K per stage; +2 in the 16-byte address field
+                    tc_mma<FP8>(tmem_base + buf * BN, da + 2u * k, db + 2u * k, idesc, (FP8 ? k : (kb | k)) != 0);
+                tc_commit(empty(s));            // smem stage reusable once these MMAs have read it
+                if (FP8 || kb == KB - 1) tc_commit(tfull(buf));
+            }
+        }
+    } else {
+        // ---- epilogue: 4 warps, warp q owns TMEM lanes [32q, 32q+32) ----------------------------------
+        const int q = warp & 3;
+        const int row = m0 + 32 * q + lane;
+        const int et = threadIdx.x - 64;        // 0..127
+        if (FP8) {
+            for (int i = et; i < KB * BN; i += 128) {
+                const int kb = i / BN, n = i % BN;
+                sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * KB + kb] : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        float acc[BN];
+#pragma unroll
+        for (int n = 0; n < BN; ++n) acc[n] = 0.f;
+        bool ok = true;
+        const int rounds = FP8 ? KB : 1;
+        for (int r = 0; r < rounds && ok; ++r) {
+            const int buf = FP8 ? (r % kAccBufs) : 0;
+            ok = mbar_wait(tfull(buf), FP8 ? ((r / kAccBufs) & 1) : 0, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * BN;
+            if (FP8) {
+                const float w = __ldg(a.sw + static_cast<size_t>(blockIdx.y) * KB + r);
+                const float4* sx4 = reinterpret_cast<const float4*>(sxs + r * BN);
+#pragma unroll
+                for (int c = 0; c < BN; c += 16) {
+                    float p[16];
+                    tmem_ld16(taddr + c, p);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int n = 0; n < 16; n += 4) {
+                        const float4 sc = sx4[(c + n) >> 2];
+                        acc[c + n] = fmaf(p[n], w * sc.x, acc[c + n]);
+                        acc[c + n + 1] = fmaf(p[n + 1], w * sc.y, acc[c + n + 1]);
+                        acc[c + n + 2] = fmaf(p[n + 2], w * sc.z, acc[c + n + 2]);
+                        acc[c + n + 3] = fmaf(p[n + 3], w * sc.w, acc[c + n + 3]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty(buf));
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; c += 16) tmem_ld16(taddr + c, acc + c);
+                tmem_ld_wait();
+            }
+        }
+        if (ok && row < a.R) {
+#pragma unroll
+            for (int n = 0; n < BN; ++n) {
+                if (n0 + n >= a.T) break;
+                const size_t o = static_cast<size_t>(n0 + n) * a.ldy + row;
+                if (a.out_mode == 0) {
+                    static_cast<float*>(a.y)[o] = acc[n];
+                } else if (a.out_mode == 1) {
+                    static_cast<__nv_bfloat16*>(a.y)[o] = __float2bfloat16(acc[n]);
+                } else {
+                    static_cast<float*>(a.y)[o] += acc[n];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies and MMAs that were already issued time to land before the memory they target is released
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 50000) {
+        }
+        if (threadIdx.x == 0 && a.status) atomicCAS(a.status, 0, static_cast<int>(kStatusPipeTimeout));
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_free(tmem_base, kCols);
+    }
+}
+
+// ---- row-wise activation quantisation: optional RMSNorm, then e4m3 with one scale per 128 columns ---------
+// x [T, ldx] bf16 (or fp32 when x_fp32), gamma [K] fp32 or null, xq [T, K] e4m3, sx [T, K/128] fp32.
+__global__ void act_quant_kernel(const void* __restrict__ x, int x_fp32, int ldx, const float* __restrict__ gamma, float eps,
+                                 __nv_fp8_storage_t* __restrict__ xq, float* __restrict__ sx, int K) {
+    const int t = blockIdx.x;
+    const int KB = K / 128;
+    __shared__ float red[32];
+    __shared__ float rinv_s;
+    auto load = [&](int k) -> float {
+        return x_fp32 ? static_cast<const float*>(x)[static_cast<size_t>(t) * ldx + k]
+                      : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[static_cast<size_t>(t) * ldx + k]);
+    };
+    float rinv = 1.f;
+    if (gamma) {
+        float ss = 0.f;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+            const float v = load(k);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+            v = warp_sum(v);
+            if (threadIdx.x == 0) rinv_s = rsqrtf(v / K + eps);
+        }
+        __syncthreads();
+        rinv = rinv_s;
+    }
+    // one warp per 128-column block
+    for (int kb = threadIdx.x >> 5; kb < KB; kb += blockDim.x >> 5) {
+        float v[4];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = kb * 128 + (threadIdx.x & 31) * 4 + i;
+            v[i] = load(k) * rinv * (gamma ? gamma[k] : 1.f);
+            amax = fmaxf(amax, fabsf(v[i]));
+        }
+        amax = warp_max(amax);
+        const float scale = fmaxf(amax, 1e-12f) / 448.f;
+        const float inv = 1.f / scale;
+        uint32_t packed = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+        reinterpret_cast<uint32_t*>(xq + static_cast<size_t>(t) * K + kb * 128)[threadIdx.x & 31] = packed;
+        if ((threadIdx.x & 31) == 0) sx[static_cast<size_t>(t) * KB + kb] = scale;
+    }
+}
+
+// ---- host side: tensor maps ----------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows, bf16;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && bf16 == o.bf16; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        for (uint64_t v : {k.rows, k.cols, k.ld, static_cast<uint64_t>(k.box_rows), static_cast<uint64_t>(k.bf16)}) h = h * 1000003u ^ std::hash<uint64_t>()(v);
+        return h;
+    }
+};
+
+// Row-major [rows, cols] matrix with leading dimension `ld` elements; box = box_rows x one 128-byte span.
+bool tensor_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, bool bf16) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{ptr, rows, cols, ld, box_rows, bf16 ? 1u : 0u};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const uint32_t esz = bf16 ? 2 : 1;
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * esz) & 15)) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * esz};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kSpan / esz), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+template <bool FP8, int BN>
+cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const Args& a, cudaStream_t stream) {
+    using L = Layout<BN>;
+    static bool configured = false;
+    auto kern = tc_gemm_kernel<FP8, BN>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(kMaxKBlocks, FP8));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((a.T + BN - 1) / BN, (a.R + kBM - 1) / kBM);
+    kern<<<grid, kThreads, L::total(a.KB, FP8), stream>>>(mw, mx, a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Y[T, R] = dequant(Xq, sx) * dequant(Wq, sw)^T.  Wq [R, K] e4m3 (row stride ldw), sw [ceil(R/128), K/128],
+// Xq [T, K] e4m3 (dense), sx [T, K/128].  K must be a multiple of 128 and at most 8192.
+int nexrt_tc_gemm_fp8(const void* wq, const float* sw, int64_t ldw, const void* xq, const float* sx, void* y, int T, int R, int K, int ldy, int out_mode,
+                      int* status, void* stream) {
+    if (T <= 0 || R <= 0 || K <= 0 || K % 128 || K / 128 > kMaxKBlocks || out_mode < 0 || out_mode > 2) return cudaErrorInvalidValue;
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    if (!tensor_map(&mw, wq, R, K, ldw, kBM, false) || !tensor_map(&mx, xq, T, K, K, bn, false)) return cudaErrorInvalidValue;
+    Args a{sw, sx, y, T, R, K / 128, ldy, out_mode, status};
+    auto s = static_cast<cudaStream_t>(stream);
+    if (bn == 16) return launch_tc<true, 16>(mw, mx, a, s);
+    if (bn == 32) return launch_tc<true, 32>(mw, mx, a, s);
+    return launch_tc<true, 64>(mw, mx, a, s);
+}
+
+// Y[T, R] = X[T, K] * W[R, K]^T, both bf16, fp32 accumulation.  K must be a multiple of 64, at most 4096.
+int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, void* y, int T, int R, int K, int ldy, int out_mode, int* status,
+                       void* stream) {
+    if (T <= 0 || R <= 0 || K <= 0 || K % 64 || K / 64 > kMaxKBlocks || out_mode < 0 || out_mode > 2) return cudaErrorInvalidValue;
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    if (!tensor_map(&mw, w, R, K, ldw, kBM, true) || !tensor_map(&mx, x, T, K, ldx, bn, true)) return cudaErrorInvalidValue;
+    Args a{nullptr, nullptr, y, T, R, K / 64, ldy, out_mode, status};
+    auto s = static_cast<cudaStream_t>(stream);
+    if (bn == 16) return launch_tc<false, 16>(mw, mx, a, s);
+    if (bn == 32) return launch_tc<false, 32>(mw, mx, a, s);
+    return launch_tc<false, 64>(mw, mx, a, s);
+}
+
+// Optional RMSNorm (gamma != null) followed by per-row, per-128-column e4m3 quantisation.
+int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream) {
+    if (T <= 0 || K <= 0 || K % 128) return cudaErrorInvalidValue;
+    act_quant_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, x_fp32, ldx, gamma, eps, static_cast<__nv_fp8_storage_t*>(xq), sx, K);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_float, c_int, c_size_t, c_uint, c_ulonglong, c_void_p
+from ctypes import POINTER, c_float, c_int, c_int64, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
@@ -67,6 +67,9 @@ _PROTOTYPES = {
     "nexrt_feature_tap": [vp, vp, ci, ci, ci, ci, vp],
     "nexrt_dense_bf16": [vp] * 5 + [ci] * 6 + [cf, CH, cu, vp],
     "nexrt_kv_publish": [vp, ci, ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp],
+    "nexrt_tc_gemm_fp8": [vp, vp, c_int64, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
+    "nexrt_tc_gemm_bf16": [vp, c_int64, vp, c_int64, vp, ci, ci, ci, ci, ci, vp, vp],
+    "nexrt_act_quant": [vp, ci, ci, vp, cf, vp, vp, ci, ci, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],
     "nexrt_ipc_get_handle": [vp, vp],
     "nexrt_ipc_open": [vp, POINTER(c_void_p)],
