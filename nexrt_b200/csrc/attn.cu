@@ -21,6 +21,7 @@
 #include "gemv.cuh"
 #include "gemv_cta.cuh"
 #include "mma_gemv.cuh"
+#include "attn_mma.cuh"
 #include "ll.cuh"
 
 namespace nexrt {
@@ -155,10 +156,14 @@ struct AttnDecodeArgs {
 };
 
 constexpr int kRowsPerPass = 4;
-constexpr int kMinKeysPerSplit = 32;
+constexpr int kMinKeysPerSplit = 128;   // short contexts stay on few CTAs: the combine's cost grows with the split count
 
-template <int HD>
+constexpr int kRowsPerPassMma = 8;
+
+// MMA: the key loop runs on the tensor cores (attn_mma.cuh); needs M * (nq / kvh) <= 8.
+template <int HD, bool MMA>
 __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
+    constexpr int RP = MMA ? kRowsPerPassMma : kRowsPerPass;
     constexpr int EL = HD / 32;  // elements per lane
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_last;
@@ -187,7 +192,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
 
     float* q_s = smem;                                   // [rows][HD]  normalised, roped, pre-scaled
     float* k_s = q_s + static_cast<size_t>(rows) * HD;   // [M][HD]     normalised, roped, bf16 rounded
-    float* part = k_s + static_cast<size_t>(a.M) * HD;   // [NW][kRowsPerPass][HD + 2]
+    float* part = k_s + static_cast<size_t>(a.M) * HD;   // [NW][RP][HD + 2]
     const float qscale = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;
     const int half = a.rotary / 2;
     // ---- prologue: q and new-k normalisation + RoPE, one warp per vector
@@ -245,6 +250,32 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     float* wsa = a.ws_acc + (static_cast<size_t>(kv) * a.n_splits + split) * rows * HD;
     float* wsm = a.ws_ml + (static_cast<size_t>(kv) * a.n_splits + split) * rows * 2;
 
+    // cross-warp merge of the per-warp partials in `part` ([NW][RP][HD + 2]) into this split's workspace rows
+    auto merge_warps = [&](int r0, int nr) {
+        for (int idx = threadIdx.x; idx < nr * HD; idx += blockDim.x) {
+            const int r = idx / HD, d = idx % HD;
+            float M_ = -INFINITY;
+            for (int w = 0; w < NW; ++w) M_ = fmaxf(M_, part[(static_cast<size_t>(w) * RP + r) * (HD + 2) + HD]);
+            float L_ = 0.f, A_ = 0.f;
+            for (int w = 0; w < NW; ++w) {
+                const float* pr = part + (static_cast<size_t>(w) * RP + r) * (HD + 2);
+                const float sc = pr[HD] == -INFINITY ? 0.f : exp2f(pr[HD] - M_);
+                L_ = fmaf(pr[HD + 1], sc, L_);
+                A_ = fmaf(pr[d], sc, A_);
+            }
+            wsa[static_cast<size_t>(r0 + r) * HD + d] = A_;
+            if (d == 0) { wsm[(r0 + r) * 2] = M_; wsm[(r0 + r) * 2 + 1] = L_; }
+        }
+    };
+    if constexpr (MMA) {
+        const int gr = lane >> 2;
+        const int my_limit = gr < rows ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + gr / G) : -1;
+        const AttnMmaKeys keys{kc, vc, k_s, C0, lo, hi};
+        attn_mma_pass<HD>(keys, q_s, rows, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        __syncthreads();
+        merge_warps(0, rows);
+        __syncthreads();
+    } else {
     for (int r0 = 0; r0 < rows; r0 += kRowsPerPass) {
         const int nr = min(kRowsPerPass, rows - r0);
         float q[kRowsPerPass][EL], acc[kRowsPerPass][EL], mx[kRowsPerPass], l[kRowsPerPass];
@@ -257,7 +288,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             mx[r] = -INFINITY; l[r] = 0.f;
             limit[r] = (r < nr) ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + rr / G) : -1;   // last visible position of the row
         }
-        constexpr int KBATCH = 4;   // keys whose K and V rows are in flight together per warp
+        constexpr int KBATCH = 8;   // keys whose K and V rows are in flight together per warp
         for (int pb = lo + warp; pb < hi; pb += NW * KBATCH) {
             uint4 kraw[KBATCH], vraw[KBATCH];
 #pragma unroll
@@ -326,21 +357,9 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             if (lane == 0) { pr[HD] = mx[r]; pr[HD + 1] = l[r]; }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nr * HD; idx += blockDim.x) {
-            const int r = idx / HD, d = idx % HD;
-            float M_ = -INFINITY;
-            for (int w = 0; w < NW; ++w) M_ = fmaxf(M_, part[(static_cast<size_t>(w) * kRowsPerPass + r) * (HD + 2) + HD]);
-            float L_ = 0.f, A_ = 0.f;
-            for (int w = 0; w < NW; ++w) {
-                const float* pr = part + (static_cast<size_t>(w) * kRowsPerPass + r) * (HD + 2);
-                const float sc = pr[HD] == -INFINITY ? 0.f : exp2f(pr[HD] - M_);
-                L_ = fmaf(pr[HD + 1], sc, L_);
-                A_ = fmaf(pr[d], sc, A_);
-            }
-            wsa[static_cast<size_t>(r0 + r) * HD + d] = A_;
-            if (d == 0) { wsm[(r0 + r) * 2] = M_; wsm[(r0 + r) * 2 + 1] = L_; }
-        }
+        merge_warps(r0, nr);
         __syncthreads();
+    }
     }
 
     // ---- ticket: the last CTA of this kv head to arrive combines all splits
@@ -382,19 +401,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         if (lane == 0) { rowM[r] = mxv; rowL[r] = lsum; }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * HD; idx += blockDim.x) {
-        const int r = idx / HD, d = idx % HD;
-        const float* pa = base_acc + static_cast<size_t>(r) * HD + d;
-        const size_t stride = static_cast<size_t>(rows) * HD;
-        float A_ = 0.f;
-        int sp = 0;
-        for (; sp + 4 <= n_active; sp += 4) {
-            const float a0 = __ldcg(pa + sp * stride), a1 = __ldcg(pa + (sp + 1) * stride);
-            const float a2 = __ldcg(pa + (sp + 2) * stride), a3 = __ldcg(pa + (sp + 3) * stride);
-            const float* w_ = sc + r * n_active + sp;
-            A_ = fmaf(a0, w_[0], A_); A_ = fmaf(a1, w_[1], A_); A_ = fmaf(a2, w_[2], A_); A_ = fmaf(a3, w_[3], A_);
-        }
-        for (; sp < n_active; ++sp) A_ = fmaf(__ldcg(pa + sp * stride), sc[r * n_active + sp], A_);
+    auto finish = [&](int r, int d, float A_) {
         const float L_ = rowL[r], M_ = rowM[r];
         const int m = r / G, hg = r % G;   // head inside the kv group
         const float ctx = L_ > 0.f ? A_ / L_ : 0.f;
@@ -410,6 +417,36 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             const float lse = L_ > 0.f ? M_ + log2f(L_) : -INFINITY;
             ll_send(a.ch, call, owner, slot, __float_as_uint(ctx));
             if (d == 0) ll_send(a.ch, call, owner, slot + HD, __float_as_uint(lse));
+        }
+    };
+    const size_t stride = static_cast<size_t>(rows) * HD;
+    // two outputs per thread and 16 splits per output in flight: with the usual 8..16 splits a decode row's
+    // combine is one or two round trips to L2 instead of one per four splits
+    for (int idx0 = threadIdx.x; idx0 < rows * HD; idx0 += 2 * blockDim.x) {
+        float A_[2] = {0.f, 0.f};
+        for (int sp0 = 0; sp0 < n_active; sp0 += 16) {
+            float v[2][16];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int idx = idx0 + u * blockDim.x;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    v[u][i] = (idx < rows * HD && sp0 + i < n_active) ? __ldcg(base_acc + idx + (sp0 + i) * stride) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int idx = idx0 + u * blockDim.x;
+                if (idx >= rows * HD) break;
+                const float* w_ = sc + (idx / HD) * n_active + sp0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (sp0 + i < n_active) A_[u] = fmaf(v[u][i], w_[i], A_[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int idx = idx0 + u * blockDim.x;
+            if (idx < rows * HD) finish(idx / HD, idx % HD, A_[u]);
         }
     }
     if (threadIdx.x == 0) a.ticket[kv] = 0;
@@ -444,7 +481,7 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
 
 extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
     const size_t rows = static_cast<size_t>(M) * (nq / kvh);
-    const size_t main_floats = rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPass * (hd + 2);
+    const size_t main_floats = rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPassMma * (hd + 2);
     const size_t n_sm = 160;  // upper bound of splits per kv head
     const size_t combine_floats = rows * n_sm * 2 + 2 * rows;
     return sizeof(float) * (main_floats > combine_floats ? main_floats : combine_floats);
@@ -470,7 +507,10 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     if (ch) a.ch = *ch;
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (hd == 256) return launch(attn_decode_kernel<256>, dim3(n_splits, kvh), dim3(256), smem, st, a);
-    if (hd == 128) return launch(attn_decode_kernel<128>, dim3(n_splits, kvh), dim3(256), smem, st, a);
+    const bool mma = (gemv_mode() & 32) && M * (nq / kvh) <= kRowsPerPassMma;
+    if (hd == 256) return mma ? launch(attn_decode_kernel<256, true>, dim3(n_splits, kvh), dim3(256), smem, st, a)
+                              : launch(attn_decode_kernel<256, false>, dim3(n_splits, kvh), dim3(256), smem, st, a);
+    if (hd == 128) return mma ? launch(attn_decode_kernel<128, true>, dim3(n_splits, kvh), dim3(256), smem, st, a)
+                              : launch(attn_decode_kernel<128, false>, dim3(n_splits, kvh), dim3(256), smem, st, a);
     return cudaErrorInvalidValue;
 }

@@ -42,16 +42,18 @@ struct RouterArgs {
 
 // Top-k of every token row by the calling CTA: warp m owns row m, lane holds logits lane,
 // lane + 32, ...; ties go to the lowest expert id; weights are a softmax over the selected logits.
-__device__ __forceinline__ void router_topk(const RouterArgs& a) {
+// `src` holds the summed logits [M][E+1]: the global array (read through L2) or a shared-memory copy.
+template <bool FROM_SMEM = false>
+__device__ __forceinline__ void router_topk(const RouterArgs& a, const float* src) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int rows = a.E + 1;
     for (int m = warp; m < a.M; m += nwarps) {
-        const float* lg = a.logits + static_cast<size_t>(m) * rows;
+        const float* lg = src + static_cast<size_t>(m) * rows;
         float v[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int e = lane + 32 * i;
-            v[i] = e < a.E ? __ldcg(lg + e) : -INFINITY;
+            v[i] = e < a.E ? (FROM_SMEM ? lg[e] : __ldcg(lg + e)) : -INFINITY;
         }
         float top0 = 0.f, denom = 0.f, mine = 0.f;
         int mine_id = -1;
@@ -83,7 +85,7 @@ __device__ __forceinline__ void router_topk(const RouterArgs& a) {
             a.wts[m * S + lane] = mine / denom;
         } else if (lane == a.topk) {
             a.ids[m * S + lane] = a.E;
-            a.wts[m * S + lane] = sigmoid_f(__ldcg(lg + a.E));
+            a.wts[m * S + lane] = sigmoid_f(FROM_SMEM ? lg[a.E] : __ldcg(lg + a.E));
         }
     }
 }
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    router_topk(a);
+    router_topk(a, a.logits);
     if (threadIdx.x == 0) *a.ticket = 0;
 }
 
@@ -261,15 +263,31 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int idx = threadIdx.x; idx < a.M * rows; idx += blockDim.x) {
-        const int m = idx / rows, e = idx % rows;
-        float v = 0.f;
+    // sum the K quarters in a fixed order into shared memory (the scratch of the GEMV phase is free now);
+    // three logits per thread are in flight together, so M = 1 needs one round trip to L2
+    float* lg_s = smem;
+    for (int idx0 = threadIdx.x; idx0 < a.M * rows; idx0 += 3 * blockDim.x) {
+        float v[3][KQ];
 #pragma unroll
-        for (int q = 0; q < KQ; ++q) v += __ldcg(a.partial + (static_cast<size_t>(q) * a.M + m) * a.rows_pad + e);
-        a.logits[static_cast<size_t>(m) * rows + e] = v;
+        for (int u = 0; u < 3; ++u) {
+            const int idx = idx0 + u * blockDim.x;
+            const int m = idx / rows, e = idx % rows;
+#pragma unroll
+            for (int q = 0; q < KQ; ++q)
+                v[u][q] = idx < a.M * rows ? __ldcg(a.partial + (static_cast<size_t>(q) * a.M + m) * a.rows_pad + e) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            const int idx = idx0 + u * blockDim.x;
+            if (idx < a.M * rows) {
+                const float t = ((v[u][0] + v[u][1]) + v[u][2]) + v[u][3];
+                lg_s[idx] = t;
+                a.logits[idx] = t;
+            }
+        }
     }
     __syncthreads();
-    router_topk(a);
+    router_topk<true>(a, lg_s);
     if (threadIdx.x == 0) *a.ticket = 0;
 }
 

@@ -17,7 +17,7 @@ int& gemv_threads_ref() {
 }
 
 int& gemv_mode_ref() {
-    static int mode = 31;
+    static int mode = 63;
     return mode;
 }
 

@@ -13,6 +13,18 @@ import os
 import torch
 
 
+class _Without:
+    """The kernel library with one entry point replaced by a no-op (timing attribution only)."""
+
+    def __init__(self, lib, name: str):
+        self._lib, self._name = lib, name
+
+    def __getattr__(self, item):
+        if item == self._name:
+            return lambda *args: 0
+        return getattr(self._lib, item)
+
+
 def main() -> None:
     p = argparse.ArgumentParser()
     p.add_argument("--layers", type=int, default=4)
@@ -24,6 +36,7 @@ def main() -> None:
     p.add_argument("--graph", action="store_true", help="time captured-graph replays and print us/step")
     p.add_argument("--no-pdl", action="store_true")
     p.add_argument("--threads", type=int, default=0)
+    p.add_argument("--leave-one-out", action="store_true", help="with --graph: re-capture with each kernel entry point stubbed out and print the time it adds to the step")
     a = p.parse_args()
     from ..config import full_config, shrunk_config
     from ..decode_engine import DecodeEngine
@@ -49,7 +62,17 @@ def main() -> None:
 
         g = eng.capture(a.rows)
         r = bench_graph(g, a.steps, warmup=5, device=dev)
-        print(f"rows={a.rows} ctx={a.ctx} layers={cfg.n_layers}: {r['ms_per_replay'] * 1e3:.1f} us/step")
+        full = r["ms_per_replay"] * 1e3
+        print(f"rows={a.rows} ctx={a.ctx} layers={cfg.n_layers}: {full:.1f} us/step")
+        if a.leave_one_out:
+            real = eng.ctx.lib
+            for name in ("nexrt_gdn_front", "nexrt_gdn_core", "nexrt_attn_front", "nexrt_attn_decode", "nexrt_oproj_allreduce", "nexrt_moe_router",
+                         "nexrt_moe_l1", "nexrt_moe_l2_allreduce", "nexrt_lmhead_sample"):
+                eng.ctx.lib = _Without(real, name)
+                eng.graphs.clear()
+                t = bench_graph(eng.capture(a.rows), a.steps, warmup=5, device=dev)["ms_per_replay"] * 1e3
+                print(f"  without {name:26s} {t:8.1f} us/step   (adds {full - t:6.1f} us)")
+            eng.ctx.lib = real
     else:
         for _ in range(a.steps):
             eng.step(a.rows)
