@@ -30,3 +30,23 @@ def gather_logits(engine, rows: int) -> torch.Tensor:
     """fp32 logits ``[rows, vocab_local]`` of the last step (engine.head.enable_logits() first)."""
     torch.cuda.synchronize()
     return engine.head.logits[:rows].float().cpu()
+
+
+def attach_silent_peer(engine, budget_ms: float = 50.0) -> None:
+    """Turn a single-rank engine's reduce channel into a two-rank channel whose second rank never
+    sends: every all-reduce wait then runs out of its (short) budget and latches a status instead of
+    completing.  The failure is made on the host (a peer that never joins); the kernels are untouched
+    and all their waits stay bounded.  Used by the failure-detection tests."""
+    ch = engine.ctx.channel
+    if ch.world != 1:
+        raise ValueError("attach_silent_peer expects a single-rank engine")
+    nbytes = 2 * 2 * ch.slots * 8
+    inbox = torch.zeros(nbytes, dtype=torch.uint8, device=engine.dev)
+    sink = torch.zeros(nbytes, dtype=torch.uint8, device=engine.dev)     # where packets "to rank 1" land
+    engine._silent_peer_buffers = (inbox, sink)
+    s = ch.struct
+    s.local, s.mc = inbox.data_ptr(), None
+    s.peer[0], s.peer[1] = inbox.data_ptr(), sink.data_ptr()
+    s.world, s.rank = 2, 0
+    s.budget_ns = int(budget_ms * 1e6)
+    ch.world = 2
