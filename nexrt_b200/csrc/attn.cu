@@ -212,9 +212,12 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         for (int i = 0; i < EL; ++i) dst[lane + 32 * i] = e[i] * inv * gam[lane + 32 * i];
         __syncwarp();
         const float pos = static_cast<float>(C0 + m);
-        float rot[2] = {0.f, 0.f};
-        int ri[2] = {-1, -1};
-        for (int i = lane, c = 0; i < a.rotary; i += 32, ++c) {
+        float rot[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // rotary <= 256: up to 8 rotated dims per lane
+        int ri[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int i = lane + 32 * c;
+            if (i >= a.rotary) break;
             const int f = i < half ? i : i - half;
             float sn, cs;
             if (a.rope_table != nullptr) {
@@ -228,7 +231,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             ri[c] = i;
         }
         __syncwarp();
-        for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
             if (ri[c] >= 0) dst[ri[c]] = rot[c];
         __syncwarp();
 #pragma unroll
@@ -491,7 +495,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
                                  const void* rope_table, const void* ctl, void* k_cache, const void* v_cache, void* ws_acc, void* ws_ml, void* ticket, void* out,
                                  int hd, int nq, int ngate, int kvh, int M, int cache_len, int rotary, int n_splits, float eps, int flags,
                                  int window, int ldq, int ldk, int cp_size, int cp_rank, const NexrtLLChannel* ch, unsigned int site, void* stream) {
-    if (M < 1 || M > kMaxRows || nq % kvh || rotary > 64 || rotary % 2) return cudaErrorInvalidValue;
+    if (M < 1 || M > kMaxRows || nq % kvh || rotary > hd || rotary % 2) return cudaErrorInvalidValue;
     if (cp_size > 1 && ch == nullptr) return cudaErrorInvalidValue;
     if (n_splits > 160) return cudaErrorInvalidValue;
     AttnDecodeArgs a{};

@@ -220,9 +220,11 @@ extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* 
     a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.overwrite = overwrite; a.eps = eps; a.ch = *ch; a.site = site;
     if (cp) { a.cp = *cp; a.cp_site = cp_site; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if ((gemv_mode() & 2) && H % 16 == 0 && K % 64 == 0) {
-        const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
-        const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * K + 8 * 256 + kMaxRows * 16) + static_cast<size_t>(mp) * terms * K;
+    const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
+    const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * K + 8 * 256 + kMaxRows * 16) + static_cast<size_t>(mp) * terms * K;
+    // wide K with several rows (an unsharded out-projection at tensor-parallel 1) does not fit the tensor-core
+    // kernel's staging buffers: those shapes take the CUDA-core kernel
+    if ((gemv_mode() & 2) && H % 16 == 0 && K % 64 == 0 && smem_mma <= 200 * 1024) {
         dim3 g(H / 16), b(256);
         if (mp == 1) return launch(oproj_allreduce_mma_kernel<1>, g, b, smem_mma, st, a);
         if (mp == 2) return launch(oproj_allreduce_mma_kernel<2>, g, b, smem_mma, st, a);

@@ -69,8 +69,8 @@ class DFlashConfig:
             problems.append("norm prologue supports hidden <= 4096")
         if not 0 <= self.mask_token_id < self.vocab:
             problems.append("mask_token_id outside the vocabulary")
-        if self.rotary_dim > 64 or self.rotary_dim % 2:
-            problems.append("rotary_dim must be even and at most 64 for the decode kernel")
+        if self.rotary_dim > self.head_dim or self.rotary_dim % 2:
+            problems.append("rotary_dim must be even and at most head_dim")
         if problems:
             raise ValueError("DFlash draft does not match the kernel contract: " + "; ".join(problems))
 
@@ -88,7 +88,7 @@ class DFlashConfig:
             block_size=cfg.get("block_size", d.get("block_size", cls.block_size)),
             mask_token_id=d.get("mask_token_id", cfg.get("mask_token_id", cls.mask_token_id)),
             rope_theta=cfg.get("rope_theta", cls.rope_theta), rms_eps=cfg.get("rms_norm_eps", cls.rms_eps),
-            vocab=cfg.get("vocab_size", cls.vocab), rotary_dim=min(64, cfg.get("rotary_dim", 64)),
+            vocab=cfg.get("vocab_size", cls.vocab), rotary_dim=cfg.get("rotary_dim", cfg.get("head_dim", cls.head_dim)),
         )
 
 
@@ -97,5 +97,5 @@ def shrunk_dflash_config(target: ModelConfig) -> DFlashConfig:
     return DFlashConfig(
         hidden=target.hidden, n_layers=2, n_q_heads=8, n_kv_heads=2, head_dim=128, mlp_inter=512, sliding_window=16,
         layer_types=("sliding", "full"), target_layer_ids=tuple(range(min(2, target.n_layers))), block_size=8,
-        mask_token_id=target.vocab - 1, rope_theta=target.rope_theta, rotary_dim=32, vocab=target.vocab,
+        mask_token_id=target.vocab - 1, rope_theta=target.rope_theta, rotary_dim=128, vocab=target.vocab,
     )

@@ -352,13 +352,16 @@ def _rand_fp8(gen, shape, device, chunk_rows=None):
     return q.reshape(*lead, R, C), s.reshape(*lead, R // BLOCK, C // BLOCK)
 
 
-def random_rank_model(cfg: ModelConfig, tp: int, rank: int, device, seed: int = 0) -> Dict:
+def random_rank_model(cfg: ModelConfig, tp: int, rank: int, device, seed: int = 0, cp: bool = False) -> Dict:
     """Random-init shards of the exact geometry generated straight on ``device``.
 
     Tensors that are replicated across ranks (norms, router, embedding, conv taps of shared
     kv heads) come from a generator seeded by ``seed`` only, rank-local slices from
     ``(seed, rank)``: the model is the concatenation of the shards.  Used by the benchmarks,
-    where a global 400 GB tensor set can never exist on one host.
+    where a global 400 GB tensor set can never exist on one host.  With ``cp`` the ranks that share
+    a kv head draw the query rows of their whole group from a group-seeded generator, so every rank
+    can also hold the context-parallel front (all the group's query heads) and it agrees with the
+    per-rank fronts of its neighbours.
     """
     spec = ShardSpec(cfg, tp, rank)
     shared = torch.Generator(device=device).manual_seed(seed)
@@ -384,7 +387,23 @@ def random_rank_model(cfg: ModelConfig, tp: int, rank: int, device, seed: int = 
             # the kv rows must agree inside the group of ranks sharing the kv head
             kvgen = torch.Generator(device=device).manual_seed(seed * 7919 + 31 * layer + spec.kv_head0)
             hd = cfg.head_dim
-            qw, qs = _rand_fp8(local, (spec.q_heads * 2 * hd, H), device)
+            cp_front = None
+            if cp and spec.cp_size > 1:
+                ggen = torch.Generator(device=device).manual_seed(seed * 104729 + 97 * layer + 13 * spec.kv_head0 + 5)
+                n_all, hb = spec.q_heads * spec.cp_size, hd // BLOCK
+                gw, gs = _rand_fp8(ggen, (n_all * 2 * hd, H), device)          # [(q | gate) per head] of the whole group
+                gw8 = gw.view(torch.uint8)
+                own = slice(spec.cp_rank * spec.q_heads * 2 * hd, (spec.cp_rank + 1) * spec.q_heads * 2 * hd)
+                owns = slice(spec.cp_rank * spec.q_heads * 2 * hb, (spec.cp_rank + 1) * spec.q_heads * 2 * hb)
+                qw, qs = gw8[own].contiguous().view(FP8), gs[owns].contiguous()
+                heads = range(n_all)
+                mine = range(spec.cp_rank * spec.q_heads, (spec.cp_rank + 1) * spec.q_heads)
+                cp_front = (
+                    [gw8[h * 2 * hd : h * 2 * hd + hd] for h in heads] + [gw8[h * 2 * hd + hd : (h + 1) * 2 * hd] for h in mine],
+                    [gs[h * 2 * hb : h * 2 * hb + hb] for h in heads] + [gs[h * 2 * hb + hb : (h + 1) * 2 * hb] for h in mine],
+                )
+            else:
+                qw, qs = _rand_fp8(local, (spec.q_heads * 2 * hd, H), device)
             kw, ks = _rand_fp8(kvgen, (2 * spec.kv_heads * hd, H), device)
             ow, os_ = _rand_fp8(local, (H, spec.attn_local), device)
             mix = {
@@ -401,7 +420,13 @@ def random_rank_model(cfg: ModelConfig, tp: int, rank: int, device, seed: int = 
             "post_ln": post_ln, "router_w": rn(shared, E + 1, H).to(bf),
             "w13": w13, "w13_s": w13s, "w2": w2, "w2_s": w2s,
         }
-        layers.append({"mixer": mix, "moe": moe})
+        entry = {"mixer": mix, "moe": moe}
+        if cfg.layer_types[layer] != "linear" and cp_front is not None:
+            entry["mixer_cp"] = {
+                "front_w": torch.cat(cp_front[0] + [kw.view(torch.uint8)], 0).contiguous().view(FP8),
+                "front_s": torch.cat(cp_front[1] + [ks], 0).contiguous(),
+            }
+        layers.append(entry)
     head = {
         "embed": rn(shared, cfg.vocab, H).to(bf),
         "final_ln": 1.0 + rn(shared, H),
