@@ -162,7 +162,9 @@ struct RowNorm {
         }
     }
     // xq: e4m3 byte planes [(m * TERMS + term)][K] or null; xs: fp32 rows [m][K] or null.
-    template <int TERMS>
+    // L2_LOADS: read x with ld.global.cg (used when the rows are read before this grid's dependency wait and
+    // must not be served from a cache line an earlier grid left on this SM).
+    template <int TERMS, bool L2_LOADS = false>
     __device__ __forceinline__ void run(uint8_t* xq, float* xs, const __nv_bfloat16* __restrict__ x, int rows, int K, float eps, float* red) {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
         for (int m = 0; m < rows; ++m) {
@@ -170,7 +172,8 @@ struct RowNorm {
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
                 const int k = (c * blockDim.x + threadIdx.x) * 4;
-                u[c] = k < K ? *reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + k) : make_uint2(0u, 0u);
+                const uint2* px = reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + k);
+                u[c] = k < K ? (L2_LOADS ? __ldcg(px) : *px) : make_uint2(0u, 0u);
             }
             float v[NCH][4], ss = 0.f;
 #pragma unroll

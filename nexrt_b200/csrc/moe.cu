@@ -96,7 +96,6 @@ __global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_last;
-    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int rows = a.E + 1;
     int r0, r1;
@@ -111,6 +110,7 @@ __global__ void __launch_bounds__(512, 1) moe_router_kernel(RouterArgs a) {
     gemv.preload();
     for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.post_ln[i];
     pdl_wait();
+    pdl_launch_dependents();   // after the wait: see the tensor-core router
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
@@ -231,7 +231,6 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_last;
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int rg = blockIdx.x / KQ, kq = blockIdx.x % KQ, rows = a.E + 1;
     const int nq = a.H / 32 / KQ;                                       // 64-byte windows per quarter
@@ -243,6 +242,9 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     RowNorm<4> norm;
     norm.preload_gamma(a.post_ln, a.H);
     pdl_wait();
+    // Released only now: the expert gate/up kernel that follows normalises x (complete since the wait above)
+    // before ITS dependency wait, which is safe only if it cannot start before x is final.
+    pdl_launch_dependents();
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
         if (m0) { __syncthreads(); mw.preloaded = false; }
@@ -312,11 +314,16 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
     if (shared_rows) mw.preload(src);
     RowNorm<4> norm;
     norm.preload_gamma(a.post_ln, a.H);
+    // x was finished two kernels back (out-projection + all-reduce); the router, this grid's direct predecessor,
+    // releases its dependents only after its own dependency wait, so x is complete and in L2 by now: row 0 is
+    // normalised and split while the router is still working, only the expert ids need the wait.
+    norm.template run<TERMS, true>(xq, nullptr, a.x, 1, a.H, a.eps, red);
     pdl_wait();
     for (int m = 0; m < a.M; ++m) {
         if (m) { __syncthreads(); mw.preloaded = false; }
         if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
-        norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m) * a.H, 1, a.H, a.eps, red);
+        if (m) norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m) * a.H, 1, a.H, a.eps, red);
+        else __syncthreads();
         float d[1][4];
         mw.template run<1>(src, xq, a.H, TERMS, d);
         mw.template store<1>(tiles + warp * 128, d);
