@@ -30,6 +30,7 @@ int nexrt_set_pdl(int enabled);
 int nexrt_version(void);
 int nexrt_set_gemv_threads(int threads);
 int nexrt_set_event_ring(void* ring);  /* 8 x u64 device words: phase timestamps of the GDN front kernel, NULL = off */
+int nexrt_set_attn_event_ring(void* ring);   /* 16 x u64 device words: phase timestamps of the attention decode kernel; null = off */
 int nexrt_set_gemv_mode(int mode);   /* bit mask: 1 fronts, 2 out-proj, 4 expert up, 8 expert down, 16 router, 32 attention key loop; 63 = all tensor-core (default), 0 = CUDA-core */
 
 /* step plumbing */

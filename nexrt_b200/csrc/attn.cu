@@ -153,6 +153,7 @@ struct AttnDecodeArgs {
     int cp_size, cp_rank;     // window of the prefix this rank attends
     LLChannel ch;             // partial exchange inside the cp group (world == cp_size)
     unsigned int site;
+    unsigned long long* events;   // optional timing ring: split 0 records phases 0..5, the combining CTA 6..9
 };
 
 constexpr int kRowsPerPass = 4;
@@ -164,6 +165,8 @@ constexpr int kRowsPerPassMma = 8;
 template <int HD, bool MMA>
 __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     constexpr int RP = MMA ? kRowsPerPassMma : kRowsPerPass;
+#define NEXRT_AEVENT(i, cond) do { if (a.events != nullptr && (cond) && blockIdx.y == 0 && threadIdx.x == 0) a.events[i] = globaltimer_ns(); } while (0)
+    NEXRT_AEVENT(0, blockIdx.x == 0);
     constexpr int EL = HD / 32;  // elements per lane
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_last;
@@ -174,6 +177,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     const int G = a.nq / a.kvh;             // q heads attending one kv head
     const int rows = a.M * G;               // row index = m * G + head_in_group
     pdl_wait();
+    NEXRT_AEVENT(1, blockIdx.x == 0);
     const int C0 = a.ctl[kCtlCommittedLen];
     // key window of this rank: [win_lo, win_hi) of positions, new rows included on the last cp rank
     int win_lo = 0, win_hi = C0 + a.M;
@@ -248,6 +252,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         }
     }
     __syncthreads();
+    NEXRT_AEVENT(2, split == 0);
 
     const __nv_bfloat16* kc = a.k_cache + static_cast<size_t>(kv) * a.cache_len * HD;
     const __nv_bfloat16* vc = a.v_cache + static_cast<size_t>(kv) * a.cache_len * HD;
@@ -275,10 +280,16 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         const int gr = lane >> 2;
         const int my_limit = gr < rows ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + gr / G) : -1;
         const AttnMmaKeys keys{kc, vc, k_s, C0, lo, hi};
-        attn_mma_pass<HD>(keys, q_s, rows, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        // the staged query fragments live behind the per-warp partials
+        uint4* qf = reinterpret_cast<uint4*>(part + static_cast<size_t>(NW) * RP * (HD + 2));
+        attn_mma_stage_q<HD>(qf, q_s, rows);
         __syncthreads();
+        attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        __syncthreads();
+        NEXRT_AEVENT(3, split == 0);
         merge_warps(0, rows);
         __syncthreads();
+        NEXRT_AEVENT(4, split == 0);
     } else {
     for (int r0 = 0; r0 < rows; r0 += kRowsPerPass) {
         const int nr = min(kRowsPerPass, rows - r0);
@@ -371,8 +382,10 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     __syncthreads();
     if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_active - 1);
     __syncthreads();
+    NEXRT_AEVENT(5, split == 0);
     if (!s_last) return;
     __threadfence();
+    NEXRT_AEVENT(6, true);
     const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
     const float* base_ml = a.ws_ml + static_cast<size_t>(kv) * a.n_splits * rows * 2;
     LLCall call{0u, 0u};
@@ -405,55 +418,65 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         if (lane == 0) { rowM[r] = mxv; rowL[r] = lsum; }
     }
     __syncthreads();
-    auto finish = [&](int r, int d, float A_) {
+    NEXRT_AEVENT(7, true);
+    // four consecutive dims of row r: normalise, gate and store (or send the partial to its owner in the cp group)
+    auto finish4 = [&](int r, int d, const float4& A_, const float4& gt) {
         const float L_ = rowL[r], M_ = rowM[r];
         const int m = r / G, hg = r % G;   // head inside the kv group
-        const float ctx = L_ > 0.f ? A_ / L_ : 0.f;
+        const float invl = L_ > 0.f ? 1.f / L_ : 0.f;
+        float4 ctx = make_float4(A_.x * invl, A_.y * invl, A_.z * invl, A_.w * invl);
         if (a.cp_size == 1) {
             const int head = kv * G + hg;
-            const float gt = (a.flags & 2) ? 0.f : a.gate[(static_cast<size_t>(m) * a.ngate + head) * HD + d];
-            a.out[(static_cast<size_t>(m) * a.ngate + head) * HD + d] = (a.flags & 2) ? ctx : ctx * sigmoid_f(gt);
+            if (!(a.flags & 2)) {
+                ctx.x *= sigmoid_f(gt.x); ctx.y *= sigmoid_f(gt.y); ctx.z *= sigmoid_f(gt.z); ctx.w *= sigmoid_f(gt.w);
+            }
+            *reinterpret_cast<float4*>(a.out + (static_cast<size_t>(m) * a.ngate + head) * HD + d) = ctx;
         } else {
             // head hg of the group belongs to cp rank hg / ngate; slot layout at the owner:
             // [m][local head][HD + 1] with the LSE in the last slot
             const int owner = hg / a.ngate, lh = hg % a.ngate;
             const unsigned int slot = (static_cast<unsigned int>(m) * a.ngate + lh) * (HD + 1) + d;
             const float lse = L_ > 0.f ? M_ + log2f(L_) : -INFINITY;
-            ll_send(a.ch, call, owner, slot, __float_as_uint(ctx));
+            ll_send(a.ch, call, owner, slot, __float_as_uint(ctx.x));
+            ll_send(a.ch, call, owner, slot + 1, __float_as_uint(ctx.y));
+            ll_send(a.ch, call, owner, slot + 2, __float_as_uint(ctx.z));
+            ll_send(a.ch, call, owner, slot + 3, __float_as_uint(ctx.w));
             if (d == 0) ll_send(a.ch, call, owner, slot + HD, __float_as_uint(lse));
         }
     };
     const size_t stride = static_cast<size_t>(rows) * HD;
-    // two outputs per thread and 16 splits per output in flight: with the usual 8..16 splits a decode row's
-    // combine is one or two round trips to L2 instead of one per four splits
-    for (int idx0 = threadIdx.x; idx0 < rows * HD; idx0 += 2 * blockDim.x) {
-        float A_[2] = {0.f, 0.f};
-        for (int sp0 = 0; sp0 < n_active; sp0 += 16) {
-            float v[2][16];
+    // One thread per four consecutive output dims, 16 splits of them in flight as 16-byte loads: a decode row's
+    // combine (up to 16 splits) is a single round trip to L2; the output gates are requested first.
+    constexpr int WAY = 16;
+    for (int q4 = threadIdx.x; q4 < rows * HD / 4; q4 += blockDim.x) {
+        const int idx = q4 * 4, r = idx / HD, d = idx % HD;
+        float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.cp_size == 1 && !(a.flags & 2))
+            gt = __ldcg(reinterpret_cast<const float4*>(a.gate + (static_cast<size_t>(r / G) * a.ngate + kv * G + r % G) * HD + d));
+        float4 A_ = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4* pa = reinterpret_cast<const float4*>(base_acc + idx);
+        for (int sp0 = 0; sp0 < n_active; sp0 += WAY) {
+            float4 v[WAY];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int idx = idx0 + u * blockDim.x;
+            for (int i = 0; i < WAY; ++i)
+                v[i] = (sp0 + i < n_active) ? __ldcg(pa + (sp0 + i) * (stride / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* w_ = sc + r * n_active + sp0;
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    v[u][i] = (idx < rows * HD && sp0 + i < n_active) ? __ldcg(base_acc + idx + (sp0 + i) * stride) : 0.f;
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int idx = idx0 + u * blockDim.x;
-                if (idx >= rows * HD) break;
-                const float* w_ = sc + (idx / HD) * n_active + sp0;
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (sp0 + i < n_active) A_[u] = fmaf(v[u][i], w_[i], A_[u]);
+            for (int i = 0; i < WAY; ++i) {
+                if (sp0 + i < n_active) {
+                    const float w = w_[i];
+                    A_.x = fmaf(v[i].x, w, A_.x); A_.y = fmaf(v[i].y, w, A_.y); A_.z = fmaf(v[i].z, w, A_.z); A_.w = fmaf(v[i].w, w, A_.w);
+                }
             }
         }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int idx = idx0 + u * blockDim.x;
-            if (idx < rows * HD) finish(idx / HD, idx % HD, A_[u]);
-        }
+        NEXRT_AEVENT(9, true);
+        finish4(r, d, A_, gt);
+        NEXRT_AEVENT(10, true);
     }
+    __syncthreads();
+    NEXRT_AEVENT(8, true);
     if (threadIdx.x == 0) a.ticket[kv] = 0;
+#undef NEXRT_AEVENT
 }
 
 }  // namespace nexrt
@@ -483,9 +506,16 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
     return launch(attn_front_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }
 
+// Optional timing ring (16 x u64 device memory) filled by the decode kernel of kv head 0; null switches it off.
+static unsigned long long* g_attn_events = nullptr;
+extern "C" int nexrt_set_attn_event_ring(void* ring) {
+    g_attn_events = static_cast<unsigned long long*>(ring);
+    return 0;
+}
+
 extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
     const size_t rows = static_cast<size_t>(M) * (nq / kvh);
-    const size_t main_floats = rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPassMma * (hd + 2);
+    const size_t main_floats = rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPassMma * (hd + 2) + static_cast<size_t>(hd / 16) * 32 * 4;
     const size_t n_sm = 160;  // upper bound of splits per kv head
     const size_t combine_floats = rows * n_sm * 2 + 2 * rows;
     return sizeof(float) * (main_floats > combine_floats ? main_floats : combine_floats);
@@ -509,6 +539,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     a.flags = flags; a.window = window; a.ldq = ldq; a.ldk = ldk;
     a.cp_size = cp_size; a.cp_rank = cp_rank; a.site = site;
     if (ch) a.ch = *ch;
+    a.events = g_attn_events;
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) && M * (nq / kvh) <= kRowsPerPassMma;

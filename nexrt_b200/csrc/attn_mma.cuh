@@ -47,23 +47,37 @@ struct AttnMmaKeys {
     int lo, hi;                // key window of this CTA
 };
 
-// Runs one warp over the tiles {lo + 16 * (warp + nwarps * i)}.  q_s: shared [rows][HD] fp32, already scaled for
-// exp2.  limit[r]: last position row r may see.  Result: part[r][0..HD) un-normalised output, part[r][HD] running
-// max, part[r][HD + 1] running sum, for r < 8 (rows beyond `rows` come out as max = -inf, sum = 0).
+// Query fragments in shared memory, built once per CTA: qf[(ks * 32 + lane) * 4 + {0,1,2,3}] = {hi(dims 0,1), hi(dims 2,3),
+// lo(dims 0,1), lo(dims 2,3)} of row g at dims (ks / 4) * 64 + t * 16 + 4 * (ks % 4): one conflict-free 16-byte load per
+// K step gives a lane its whole A fragment (hi and lo).  Needs HD / 16 * 32 * 16 bytes.
 template <int HD>
-__device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const float* q_s, int rows, int limit_row, int warp, int nwarps, int lane,
-                                              float* part) {
-    constexpr int KS = HD / 16;    // K steps of the score product == output tiles of the value product
-    const int g = lane >> 2, t = lane & 3;
-    uint32_t qh[KS][2], ql[KS][2];
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
+__device__ __forceinline__ void attn_mma_stage_q(uint4* qf, const float* q_s, int rows) {
+    constexpr int KS = HD / 16;
+    for (int idx = threadIdx.x; idx < KS * 32; idx += blockDim.x) {
+        const int ks = idx >> 5, lane = idx & 31, g = lane >> 2, t = lane & 3;
         const int d = (ks >> 2) * 64 + t * 16 + 4 * (ks & 3);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (g < rows) v = *reinterpret_cast<const float4*>(q_s + static_cast<size_t>(g) * HD + d);
-        split_pair(v.x, v.y, qh[ks][0], ql[ks][0]);
-        split_pair(v.z, v.w, qh[ks][1], ql[ks][1]);
+        uint4 f;
+        split_pair(v.x, v.y, f.x, f.z);
+        split_pair(v.z, v.w, f.y, f.w);
+        qf[idx] = f;
     }
+}
+
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
+// Runs one warp over the tiles {lo + 16 * (warp + nwarps * i)}.  qf: staged query fragments (attn_mma_stage_q).
+// limit_row: last position row g may see.  Result: part[r][0..HD) un-normalised output, part[r][HD] running max,
+// part[r][HD + 1] running sum, for r < 8 (rows beyond the step's rows come out as max = -inf, sum = 0).
+//
+// Per tile all K pieces are requested at once, the V rows of the tile and the K rows of the next tile are
+// prefetched into L1 at the same moment, so the dependent phases (scores -> softmax -> values) meet warm lines.
+template <int HD>
+__device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const uint4* qf, int limit_row, int warp, int nwarps, int lane, float* part) {
+    constexpr int KS = HD / 16;    // K steps of the score product == output tiles of the value product
+    constexpr int NB = HD / 64;
+    const int g = lane >> 2, t = lane & 3;
     float o[KS][4];
 #pragma unroll
     for (int j = 0; j < KS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -84,23 +98,36 @@ __device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const float*
             for (int i = 0; i < 8; ++i) r[i] = 0u;
         }
     };
+    // one lane per 128-byte line: rows [p0, p0 + 16) of a [.][HD] bf16 matrix
+    auto prefetch_rows = [&](const __nv_bfloat16* base, int p0, int p_end) {
+        constexpr int LINES = HD * 2 / 128;                  // lines per row
+#pragma unroll
+        for (int i = lane; i < 16 * LINES; i += 32) {
+            const int p = p0 + i / LINES;
+            if (p < p_end) prefetch_l1(base + static_cast<size_t>(p) * HD + (i % LINES) * 64);
+        }
+    };
 
     for (int tile = k.lo + 16 * warp; tile < k.hi; tile += 16 * nwarps) {
+        // ---- request every K piece of the tile, then warm the lines the later phases will want
+        uint32_t ka[NB][8], kb[NB][8];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            load_k(tile + g, b * 64 + t * 16, ka[b]);
+            load_k(tile + 8 + g, b * 64 + t * 16, kb[b]);
+        }
+        prefetch_rows(k.vc, tile, k.hi);
+        prefetch_rows(k.kc, tile + 16 * nwarps, min(k.hi, k.C0));
         // ---- scores of 16 keys: tile + g (s0) and tile + 8 + g (s1) on the N side
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int b = 0; b < HD / 64; ++b) {
-            uint32_t ka[8], kb[8];
-            load_k(tile + g, b * 64 + t * 16, ka);
-            load_k(tile + 8 + g, b * 64 + t * 16, kb);
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const int ks = b * 4 + s;
-                mma_bf16_16x8x16(s0, qh[ks][0], 0u, qh[ks][1], 0u, ka[2 * s], ka[2 * s + 1]);
-                mma_bf16_16x8x16(s0, ql[ks][0], 0u, ql[ks][1], 0u, ka[2 * s], ka[2 * s + 1]);
-                mma_bf16_16x8x16(s1, qh[ks][0], 0u, qh[ks][1], 0u, kb[2 * s], kb[2 * s + 1]);
-                mma_bf16_16x8x16(s1, ql[ks][0], 0u, ql[ks][1], 0u, kb[2 * s], kb[2 * s + 1]);
-            }
+        for (int ks = 0; ks < KS; ++ks) {
+            const uint4 q = qf[ks * 32 + lane];
+            const int b = ks >> 2, s = ks & 3;
+            mma_bf16_16x8x16(s0, q.x, 0u, q.y, 0u, ka[b][2 * s], ka[b][2 * s + 1]);
+            mma_bf16_16x8x16(s0, q.z, 0u, q.w, 0u, ka[b][2 * s], ka[b][2 * s + 1]);
+            mma_bf16_16x8x16(s1, q.x, 0u, q.y, 0u, kb[b][2 * s], kb[b][2 * s + 1]);
+            mma_bf16_16x8x16(s1, q.z, 0u, q.w, 0u, kb[b][2 * s], kb[b][2 * s + 1]);
         }
         // ---- mask and online softmax of row g (its 16 scores sit in the 4 lanes that share g)
         float sv[4] = {s0[0], s0[1], s1[0], s1[1]};

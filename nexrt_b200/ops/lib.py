@@ -44,6 +44,7 @@ _PROTOTYPES = {
     "nexrt_version": [],
     "nexrt_set_gemv_threads": [ci],
     "nexrt_set_event_ring": [vp],
+    "nexrt_set_attn_event_ring": [vp],
     "nexrt_set_gemv_mode": [ci],
     "nexrt_embed_gather": [vp, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_step_end": [vp, vp, cu, vp, vp, ci, vp],
