@@ -161,6 +161,21 @@ class EngineBackend:
             toks = self.eng.generate(max_new=max_new, eos=eos, on_tokens=on_tokens)
         return {"tokens": toks, **stats}
 
+    def verify_tokens(self, session: PrefillSession, tokens: Sequence[int], req: Dict) -> bool:
+        """Replay the request from the restored prompt boundary on the plain one-row decode path (eager, no
+        graph, no drafts) and compare: speculative modes must emit exactly the plain stream."""
+        self.eng._restore(session.snapshot)
+        plain = [session.first_token]
+        from ..runtime.control import Ctl
+
+        for _ in range(len(tokens) - 1):
+            self.eng.step(1)
+            w = self.eng.read_ctl()
+            if w["status"] != 0:
+                return False
+            plain.append(int(w["pending"]))
+        return plain == list(tokens)
+
     def status(self) -> int:
         return self.eng.status_max()
 
@@ -183,7 +198,8 @@ class BridgeServer:
     """Per-rank request pipeline + the rank-0 listen loop."""
 
     def __init__(self, backend, tokenizer, rank: int = 0, world: int = 1, control_group=None, mode: str = "bs1",
-                 report_path: Optional[str] = None, gather: Optional[Callable] = None, log: Callable[[str], None] = print):
+                 report_path: Optional[str] = None, gather: Optional[Callable] = None, log: Callable[[str], None] = print,
+                 consensus_fault_rank: Optional[int] = None, verify: bool = False):
         self.backend, self.tok, self.rank, self.world, self.group, self.mode = backend, tokenizer, rank, world, control_group, mode
         self.state = ServerState(CachedSession(backend.capacity, backend.model_epoch))
         self.report_path = report_path or os.environ.get("NEXRT_SERVE_REPORT")
@@ -192,6 +208,10 @@ class BridgeServer:
         self.log = log if rank == 0 else (lambda *_: None)
         eos = getattr(tokenizer, "eos_token_id", None)
         self.stop_ids = tuple(i for i in ([eos] if isinstance(eos, int) else (eos or [])) if i is not None)
+        # test-only host-side fault injection: this rank reports its READY boundary as lost on the next reuse,
+        # which must turn the request into a collective PREFILL on every rank
+        self.consensus_fault_rank = consensus_fault_rank
+        self.verify = verify
 
     # ---- one request, every rank ---------------------------------------------------------------------
     def tokenize(self, req: Dict) -> List[int]:
@@ -222,6 +242,8 @@ class BridgeServer:
                                  seed=req["seed"], temperature=req["temperature"], top_p=req["top_p"], top_k=req["top_k"])
         # validity 0 = "my device no longer holds the boundary I stored": turns the request into a collective PREFILL
         valid = live is None or live == cache.snapshot().boundary
+        if live is not None and self.consensus_fault_rank is not None and self.rank == self.consensus_fault_rank:
+            valid, self.consensus_fault_rank = False, None          # injected once
         consensus = resolve_request(self._gather(request_record(valid, plan, fp)))
         t_consensus = time.perf_counter() - t0
         lease = cache.begin_request(owner, ids, request_id=f"g{plan.generation}", live_boundary=live, force_prefill=consensus.forced_prefill)
@@ -268,6 +290,11 @@ class BridgeServer:
         st.active_lease = None
         toks = [session.first_token] + list(stats["tokens"])
         toks = toks[: req["max_new"]]
+        verified = None
+        if self.verify and hasattr(be, "verify_tokens"):
+            # re-decode from the restored boundary on the plain one-row path and compare the streams
+            verified = bool(be.verify_tokens(session, toks, req))
+            be.restore(session)
         stop = "eos" if any(t in self.stop_ids for t in toks) else ("length" if len(toks) >= req["max_new"] else "context")
         n_dec = max(len(toks) - 1, 1)
         return {
@@ -275,6 +302,7 @@ class BridgeServer:
             "prompt_tokens": len(ids), "cache": lease.decision.value, "forced_prefill": consensus.forced_prefill, "mode": self.mode,
             "prefill_s": round(prefill_s, 6), "ttft_s": round(ttft_s, 6), "decode_us_per_tok": round(decode_s * 1e6 / n_dec, 2),
             "consensus_ms": round(t_consensus * 1e3, 3), "rounds": stats.get("rounds"), "accept_mean": stats.get("accept_mean"),
+            "verified": verified, "cache_base_tokens": lease.base_length, "cache_retained": bool(keep),
         }
 
     def run_request(self, req: Dict, ids: Sequence[int], stream=None) -> Dict:
@@ -294,6 +322,51 @@ class BridgeServer:
 
         return execute_request_with_consensus(lambda: self.handle_request(req, ids, stream), lifecycle_state=lifecycle,
                                               gather_outcome=self._gather, reset_request=reset)
+
+    # ---- queued requests and the cache matrix (every rank calls these with the same arguments) ------------
+    def run_queue(self, requests: Sequence[Dict]) -> List[Dict]:
+        """Serve a fixed list of requests in order (synthetic lengths, prompt files); a request that ends in
+        a collective reset is reported and the queue goes on."""
+        out = []
+        for i, raw in enumerate(requests):
+            req = validate_request(raw, self.backend.capacity, self.mode)
+            ids = self.tokenize(req)
+            try:
+                res = self.run_request(req, ids)
+            except RequestResetError as error:
+                res = {"error": repr(error), "prompt_tokens": len(ids)}
+            res["request"] = i
+            out.append(res)
+            if self.rank == 0:
+                self.report.append(res)
+                self.log("@@ SERVE " + json.dumps({k: v for k, v in res.items() if k not in ("tokens", "generated_text")}))
+        self._flush_report()
+        return out
+
+    def cache_e2e(self, base_len: int, target_len: int, repetitions: int = 3, gen: int = 8, seed: int = 1) -> Dict:
+        """PREFILL(base) -> HIT(base) -> APPEND(target) under one owner, then the same prompts without an owner
+        (fresh prefills) as the oracle: a reused boundary must reproduce the oracle's tokens exactly."""
+        if not 0 < base_len < target_len:
+            raise ValueError("cache e2e needs 0 < base < target")
+        import random
+
+        rnd = random.Random(seed)
+        target = [rnd.randrange(3, self.backend.vocab) for _ in range(target_len)]
+        base = target[:base_len]
+        rows, ok = [], True
+        for rep in range(repetitions):
+            key = f"cache-e2e-{rep}"
+            steps = [("prefill", base, key), ("hit", base, key), ("append", target, key), ("oracle-base", base, None), ("oracle-target", target, None)]
+            got = {}
+            for name, ids, owner in steps:
+                req = validate_request({"ids": ids, "max_new": gen, "temperature": 0.0, "cache_key": owner}, self.backend.capacity, self.mode)
+                res = self.run_request(req, ids)
+                got[name] = res
+                rows.append({"rep": rep, "step": name, "cache": res["cache"], "prefill_s": res["prefill_s"], "ttft_s": res["ttft_s"]})
+            decisions = (got["prefill"]["cache"], got["hit"]["cache"], got["append"]["cache"])
+            same = got["hit"]["tokens"] == got["oracle-base"]["tokens"] == got["prefill"]["tokens"] and got["append"]["tokens"] == got["oracle-target"]["tokens"]
+            ok = ok and same and decisions == ("prefill", "hit", "append")
+        return {"base": base_len, "target": target_len, "repetitions": repetitions, "ok": ok, "rows": rows}
 
     # ---- broadcast plumbing -----------------------------------------------------------------------------
     def _broadcast(self, obj):
@@ -423,6 +496,25 @@ def build_backend(args, rank: int, world: int, dev, group):
     return EngineBackend(eng, args.mode, block, model_epoch=epoch)
 
 
+def queued_requests(args, vocab: int) -> List[Dict]:
+    """Requests of the queue mode: ``--lens`` synthetic prompts (seeded uniform-random ids) and ``--files`` prompt
+    texts, each with its own sampling seed ``seed_base + i``."""
+    import glob
+    import random
+
+    out: List[Dict] = []
+    for n in [int(v) for v in (args.lens or "").split(",") if v]:
+        rnd = random.Random(n)
+        out.append({"ids": [rnd.randrange(3, vocab) for _ in range(min(n, args.max_prompt))], "max_new": args.gen})
+    for pattern in args.files or ():
+        for path in sorted(glob.glob(pattern)):
+            with open(path, encoding="utf-8") as f:
+                out.append({"text": f.read(), "chat": True, "max_new": args.gen_files})
+    for i, req in enumerate(out):
+        req["seed"] = args.seed_base + i
+    return out
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description="nexrt_b200 bridge server (one process per GPU under torchrun)")
     p.add_argument("--host", default="127.0.0.1")
@@ -434,6 +526,18 @@ def main(argv=None) -> int:
     p.add_argument("--context", type=int, default=32768)
     p.add_argument("--cp", action="store_true")
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--lens", default=None, help="comma list of synthetic prompt lengths served before listening")
+    p.add_argument("--files", nargs="*", default=None, help="prompt files (globs) served before listening")
+    p.add_argument("--gen", type=int, default=64, help="new tokens for --lens requests")
+    p.add_argument("--gen-files", type=int, default=256, help="new tokens for --files requests")
+    p.add_argument("--max-prompt", type=int, default=262080)
+    p.add_argument("--seed-base", type=int, default=20260712, help="request i samples with seed base + i")
+    p.add_argument("--verify", action="store_true", help="compare every stream with a plain one-row re-decode")
+    p.add_argument("--cache-e2e", action="append", default=None, metavar="BASE,TARGET")
+    p.add_argument("--cache-e2e-repetitions", type=int, default=3)
+    p.add_argument("--cache-e2e-gen", type=int, default=8)
+    p.add_argument("--cache-consensus-fault-rank", type=int, default=None, help="test only: this rank rejects its READY boundary once")
+    p.add_argument("--no-listen", action="store_true", help="exit after the queued work")
     args = p.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -446,8 +550,18 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=dev)
         ctl_group = dist.new_group(backend="gloo")
     backend = build_backend(args, rank, world, dev, None)
-    server = BridgeServer(backend, load_tokenizer(args.tokenizer), rank, world, ctl_group, args.mode)
-    server.serve_forever(args.host, args.listen)
+    server = BridgeServer(backend, load_tokenizer(args.tokenizer), rank, world, ctl_group, args.mode,
+                          consensus_fault_rank=args.cache_consensus_fault_rank, verify=args.verify)
+    queue = queued_requests(args, backend.vocab)
+    if queue:
+        server.run_queue(queue)
+    for pair in args.cache_e2e or ():
+        base, target = (int(v) for v in pair.split(","))
+        result = server.cache_e2e(base, target, args.cache_e2e_repetitions, args.cache_e2e_gen)
+        if rank == 0:
+            print("@@ CACHE-E2E " + json.dumps(result), flush=True)
+    if not args.no_listen:
+        server.serve_forever(args.host, args.listen)
     return 0
 
 

@@ -71,3 +71,16 @@ def test_streamed_text_equals_the_final_text(server):
     events = [json.loads(x) for x in b.makefile("rb").read().decode().splitlines()]
     assert events[-1]["type"] == "done" and events[-1]["tokens"] == res["tokens"]
     assert "".join(e["text"] for e in events if e["type"] == "delta") == res["generated_text"]
+
+
+def test_verify_gate_and_cache_matrix_on_the_engine(server):
+    cfg = server.backend.eng.cfg
+    server.verify = True
+    try:
+        ids = synthetic_prompt(cfg.vocab, 20, seed=8)
+        r = server.run_request(_req(ids, cache_key=None), ids)
+        assert r["verified"] is True and r["status"] == 0
+    finally:
+        server.verify = False
+    res = server.cache_e2e(24, 37, repetitions=1, gen=6)
+    assert res["ok"], res

@@ -436,3 +436,45 @@ def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
+
+
+# ---- queue mode, cache matrix, injected consensus fault -------------------------------------------------------
+def test_queue_mode_and_cache_matrix():
+    import argparse
+
+    from nexrt_b200.serve.bridge_serve import queued_requests
+
+    args = argparse.Namespace(lens="5,9", files=None, gen=4, gen_files=8, max_prompt=7, seed_base=100)
+    queue = queued_requests(args, FakeBackend.vocab)
+    assert [len(r["ids"]) for r in queue] == [5, 7] and [r["seed"] for r in queue] == [100, 101] and queue == queued_requests(args, FakeBackend.vocab)
+    srv = BridgeServer(FakeBackend(), ByteTokenizer(), log=lambda *_: None)
+    out = srv.run_queue(queue)
+    assert [r["request"] for r in out] == [0, 1] and all(len(r["tokens"]) == 4 and r["cache"] == "prefill" for r in out)
+    res = srv.cache_e2e(6, 11, repetitions=2, gen=3)
+    assert res["ok"] and [r["cache"] for r in res["rows"][:5]] == ["prefill", "hit", "append", "prefill", "prefill"]
+    with pytest.raises(ValueError):
+        srv.cache_e2e(5, 5)
+
+
+def test_injected_boundary_fault_forces_one_collective_prefill():
+    srv = BridgeServer(FakeBackend(), ByteTokenizer(), log=lambda *_: None, consensus_fault_rank=0)
+    ids = srv.tok.encode("abc")
+    assert srv.run_request(_req(text="abc"), ids)["cache"] == "prefill"
+    r = srv.run_request(_req(text="abc"), ids)                       # would be a HIT; the injected fault rejects it
+    assert r["cache"] == "prefill" and r["forced_prefill"]
+    assert srv.run_request(_req(text="abc"), ids)["cache"] == "hit"   # injected once
+
+
+def test_verify_gate_reports_a_mismatch():
+    class Checking(FakeBackend):
+        def verify_tokens(self, session, tokens, req):
+            return list(tokens) == _expected(session.tokens, len(tokens)) and self.good
+
+    be = Checking()
+    be.good = True
+    srv = BridgeServer(be, ByteTokenizer(), log=lambda *_: None, verify=True)
+    ids = srv.tok.encode("abc")
+    assert srv.run_request(_req(text="abc"), ids)["verified"] is True
+    be.good = False
+    assert srv.run_request(_req(text="abc"), ids)["verified"] is False
+    assert BridgeServer(FakeBackend(), ByteTokenizer(), log=lambda *_: None).run_request(_req(text="abc"), ids)["verified"] is None
