@@ -115,6 +115,15 @@ int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, v
 // Optional RMSNorm (gamma != null, stored as the full multiplier) then per-row, per-128-column e4m3 quantisation.
 int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream);
 
+// ---- experts of a multi-row step on tcgen05 (tc_moe.cu) -------------------------------------------------------
+// Gate/up of every distinct expert named in ids [M][S] (streamed once each); planes is e4m3 scratch [3M][H].
+int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, void* planes, int H, int I, int S,
+                    int M, int n_experts_total, float eps, int* status, void* stream);
+// Down projection over each row's S experts + tensor-parallel all-reduce + residual in one kernel; planes is e4m3
+// scratch [3M][S*I], descale fp32 scratch [M].
+int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, void* planes, void* descale,
+                              int H, int I, int S, int M, int n_experts_total, const NexrtLLChannel* ch, unsigned int site, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

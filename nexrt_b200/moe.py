@@ -11,6 +11,8 @@ checkpoint tensors are used as stored (the reference's folded mode re-quantises 
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .ops.lib import check, ptr
@@ -26,6 +28,10 @@ class Moe:
             pad = torch.zeros(self.rows_pad, rw.shape[1], dtype=rw.dtype, device=rw.device)
             pad[: rw.shape[0]] = rw
             w["router_w_pad"] = pad
+        # rows from which the experts run on the tcgen05 kernels (NEXRT_TC_MOE_ROWS=0 switches them off)
+        self.tc_rows = int(os.environ.get("NEXRT_TC_MOE_ROWS", "2")) or 1 << 30
+        cfg, spec = ctx.cfg, ctx.spec
+        self.tc_ok = cfg.hidden % 128 == 0 and cfg.hidden <= 4096 and spec.inter % 128 == 0
 
     def forward(self, M: int = 1) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
@@ -38,6 +44,21 @@ class Moe:
             ),
             "moe_router",
         )
+        if M >= self.tc_rows and self.tc_ok:
+            # multi-row steps: experts on the tcgen05 tensor cores, each distinct expert streamed once, the
+            # tensor-parallel all-reduce fused into the down projection's epilogue (csrc/tc_moe.cu)
+            n_total = cfg.n_experts + 1
+            check(
+                lib.nexrt_tc_moe_l1(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_gu), ptr(c.moe_planes1),
+                                    cfg.hidden, spec.inter, S, M, n_total, cfg.rms_eps, ptr(c.status), st),
+                "tc_moe_l1",
+            )
+            check(
+                lib.nexrt_tc_moe_l2_allreduce(ptr(c.moe_gu), ptr(c.moe_ids), ptr(c.moe_wts), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), ptr(c.moe_planes2),
+                                              ptr(c.moe_descale), cfg.hidden, spec.inter, S, M, n_total, c.channel.ref, c.next_site(), ptr(c.status), st),
+                "tc_moe_l2_allreduce",
+            )
+            return
         check(
             lib.nexrt_moe_l1(
                 ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_gu), cfg.hidden, spec.inter, S, M,

@@ -75,6 +75,10 @@ class StepContext:
         self.moe_gu = z(MAX_ROWS, S, 2 * spec.inter)
         self.moe_ticket = z(1, dtype=i32)
         self.moe_partial = z(4, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)
+        # scratch of the tcgen05 expert kernels (multi-row steps): e4m3 activation planes and per-row scales
+        self.moe_planes1 = torch.zeros(3 * MAX_ROWS, cfg.hidden, dtype=torch.uint8, device=device)
+        self.moe_planes2 = torch.zeros(3 * MAX_ROWS, S * spec.inter, dtype=torch.uint8, device=device)
+        self.moe_descale = z(MAX_ROWS)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)
         self.head_ticket = z(1, dtype=i32)
