@@ -53,7 +53,8 @@ __device__ __forceinline__ void attn_front_row(const AttnFrontArgs& a, int row, 
         a.k_raw[(static_cast<size_t>(mm) * a.kvh + (head - a.nq - a.ngate)) * a.hd + d] = v;
     } else {
         const int kv = head - a.nq - a.ngate - a.kvh;
-        a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
+        if (C0 + mm < a.cache_len)      // a step past the end of the cache must not write outside it
+            a.v_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + mm) * a.hd + d] = __float2bfloat16_rn(v);
     }
 }
 
@@ -161,7 +162,7 @@ constexpr int kMinKeysPerSplit = 128;   // short contexts stay on few CTAs: the 
 
 constexpr int kRowsPerPassMma = 8;
 
-// MMA: the key loop runs on the tensor cores (attn_mma.cuh); needs M * (nq / kvh) <= 8.
+// MMA: the key loop runs on the tensor cores (attn_mma.cuh), eight query rows per pass.
 template <int HD, bool MMA>
 __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     constexpr int RP = MMA ? kRowsPerPassMma : kRowsPerPass;
@@ -180,12 +181,12 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     NEXRT_AEVENT(1, blockIdx.x == 0);
     const int C0 = a.ctl[kCtlCommittedLen];
     // key window of this rank: [win_lo, win_hi) of positions, new rows included on the last cp rank
-    int win_lo = 0, win_hi = C0 + a.M;
+    int win_lo = 0, win_hi = min(C0 + a.M, a.cache_len);   // never read past the end of the cache
     if (a.window > 0) win_lo = max(0, win_hi - a.window);
     if (a.cp_size > 1) {
         const int share = C0 / a.cp_size;
         win_lo = a.cp_rank * share;
-        win_hi = (a.cp_rank == a.cp_size - 1) ? C0 + a.M : (a.cp_rank + 1) * share;
+        win_hi = (a.cp_rank == a.cp_size - 1) ? min(C0 + a.M, a.cache_len) : (a.cp_rank + 1) * share;
     }
     const int n_keys = win_hi - win_lo;
     // At most one 16-key tile per warp (128 keys per CTA) while the context is short.  For longer contexts the
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             if (i >= a.rotary) break;
             const int f = i < half ? i : i - half;
             float sn, cs;
-            if (a.rope_table != nullptr) {
+            if (a.rope_table != nullptr && C0 + m < a.cache_len) {   // the table has one row per cache position
                 const float2 cssn = a.rope_table[static_cast<size_t>(C0 + m) * half + f];
                 cs = cssn.x; sn = cssn.y;
             } else {
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             const float val = dst[lane + 32 * i];
             dst[lane + 32 * i] = is_q ? val * qscale : bf16_round(val);
         }
-        if (!is_q && split == 0) {
+        if (!is_q && split == 0 && C0 + m < a.cache_len) {
             // every rank keeps the full cache: the new k rows are appended by split 0
 #pragma unroll
             for (int i = 0; i < EL; ++i)
@@ -281,18 +282,22 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         }
     };
     if constexpr (MMA) {
-        const int gr = lane >> 2;
-        const int my_limit = gr < rows ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + gr / G) : -1;
+        // eight query rows per pass; wider steps (a verify step's rows x the heads of the kv group) walk the keys
+        // once per pass - the K/V tiles of the later passes come from L2
         const AttnMmaKeys keys{kc, vc, k_s, C0, lo, hi};
-        // the staged query fragments live behind the per-warp partials
-        uint4* qf = reinterpret_cast<uint4*>(part + static_cast<size_t>(NW) * RP * (HD + 2));
-        attn_mma_stage_q<HD>(qf, q_s, rows);
-        __syncthreads();
-        attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
-        __syncthreads();
-        NEXRT_AEVENT(3, split == 0);
-        merge_warps(0, rows);
-        __syncthreads();
+        uint4* qf = reinterpret_cast<uint4*>(part + static_cast<size_t>(NW) * RP * (HD + 2));   // behind the per-warp partials
+        for (int r0 = 0; r0 < rows; r0 += RP) {
+            const int nr = min(RP, rows - r0);
+            const int gr = lane >> 2;
+            const int my_limit = gr < nr ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + (r0 + gr) / G) : -1;
+            attn_mma_stage_q<HD>(qf, q_s + static_cast<size_t>(r0) * HD, nr);
+            __syncthreads();
+            attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+            __syncthreads();
+            if (r0 == 0) NEXRT_AEVENT(3, split == 0);
+            merge_warps(r0, nr);
+            __syncthreads();
+        }
         NEXRT_AEVENT(4, split == 0);
     } else {
     for (int r0 = 0; r0 < rows; r0 += kRowsPerPass) {
@@ -546,7 +551,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     a.events = g_attn_events;
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool mma = (gemv_mode() & 32) && M * (nq / kvh) <= kRowsPerPassMma;
+    const bool mma = (gemv_mode() & 32) != 0;
     if (hd == 256) return mma ? launch(attn_decode_kernel<256, true>, dim3(n_splits, kvh), dim3(256), smem, st, a)
                               : launch(attn_decode_kernel<256, false>, dim3(n_splits, kvh), dim3(256), smem, st, a);
     if (hd == 128) return mma ? launch(attn_decode_kernel<128, true>, dim3(n_splits, kvh), dim3(256), smem, st, a)

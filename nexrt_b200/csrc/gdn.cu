@@ -185,6 +185,42 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     }
 }
 
+// Tail of the wide front (multi-row steps): the q|k|v|z projections of all rows were produced by the tcgen05 rows
+// GEMM into pre[M][R]; this kernel applies the per-channel conv ring + SiLU / the z store (one thread per weight
+// row, all token rows in registers), and extra CTAs project the bf16 b/a rows from the fp32 normalised rows xn.
+__global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, const float* __restrict__ pre, const float* __restrict__ xn, int row_ctas) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (static_cast<int>(blockIdx.x) < row_ctas) {
+        const int row = blockIdx.x * blockDim.x + threadIdx.x;
+        if (row >= a.R) return;
+        float p[kMaxRows];
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) p[m] = m < a.M ? pre[static_cast<size_t>(m) * a.R + row] : 0.f;
+        float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < a.C) cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
+        gdn_front_row<kMaxRows>(a, row, p, 0, a.M, a.ctl[kCtlCommittedLen], cw);
+        return;
+    }
+    // one warp per (b/a row, token row)
+    const int lane = threadIdx.x & 31;
+    const int item = (blockIdx.x - row_ctas) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= 2 * a.nv * a.M) return;
+    const int row = item / a.M, m = item % a.M;
+    const __nv_bfloat16* w = a.ba_w + static_cast<size_t>(row) * a.H;
+    const float* xr = xn + static_cast<size_t>(m) * a.H;
+    float acc = 0.f;
+    for (int k = lane * 8; k < a.H; k += 256) {
+        float wf[8];
+        unpack8_bf16(*reinterpret_cast<const uint4*>(w + k), wf);
+        const float4 x0 = *reinterpret_cast<const float4*>(xr + k), x1 = *reinterpret_cast<const float4*>(xr + k + 4);
+        acc = fmaf(wf[0], x0.x, fmaf(wf[1], x0.y, fmaf(wf[2], x0.z, fmaf(wf[3], x0.w, acc))));
+        acc = fmaf(wf[4], x1.x, fmaf(wf[5], x1.y, fmaf(wf[6], x1.z, fmaf(wf[7], x1.w, acc))));
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) gdn_ba_row(a, row, acc, m);
+}
+
 struct GdnCoreArgs {
     const float* qkv;     // [M][C]: q heads | k heads | v heads, 128 wide each
     const float* beta;    // [M][nv]
@@ -260,6 +296,20 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
                                          gemv_part_floats((2 * nv + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, gemv_threads())));
     if (M == 1) return launch(gdn_front_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
     return launch(gdn_front_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+}
+
+// Tail of the wide front: pre [M][R] fp32 projections, xn [M][H] fp32 normalised rows (see gdn_front_tail_kernel).
+extern "C" int nexrt_gdn_front_tail(const void* pre, const void* xn, const void* ba_w, const void* conv_w, const void* a_log, const void* dt_bias,
+                                    const void* ctl, void* conv_ring, void* qkv, void* z, void* beta, void* g, int H, int R, int C, int nv, int M,
+                                    int conv_ring_len, void* stream) {
+    if (M < 1 || M > kMaxRows || H % 256 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
+    GdnFrontArgs a{nullptr, nullptr, nullptr, nullptr, static_cast<const __nv_bfloat16*>(ba_w), static_cast<const float*>(conv_w),
+                   static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), static_cast<const int*>(ctl),
+                   static_cast<float*>(conv_ring), static_cast<float*>(qkv), static_cast<float*>(z), static_cast<float*>(beta),
+                   static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, 0.f, 0, nullptr};
+    const int row_ctas = (R + 255) / 256, ba_ctas = (2 * nv * M + 7) / 8;
+    return launch(gdn_front_tail_kernel, dim3(row_ctas + ba_ctas), dim3(256), 0, static_cast<cudaStream_t>(stream), a, static_cast<const float*>(pre),
+                  static_cast<const float*>(xn), row_ctas);
 }
 
 extern "C" int nexrt_gdn_core(const void* qkv, const void* beta, const void* g, const void* ctl, void* state_ring, void* out, int nqk, int nv,

@@ -204,16 +204,16 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     }
 }
 
-// rmsnorm(x[m]) * gamma -> planes[(3m + term)][H]
-__global__ void __launch_bounds__(256) rows_norm_split_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, uint8_t* planes, int H,
-                                                              float eps) {
+// rmsnorm(x[m]) * gamma -> planes[(3m + term)][H]; xn (optional) keeps the normalised row in fp32
+__global__ void __launch_bounds__(256) rows_norm_split_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, uint8_t* planes, float* xn,
+                                                              int H, float eps) {
     __shared__ float red[32];
     pdl_launch_dependents();
     RowNorm<4> norm;
     norm.preload_gamma(gamma, H);
     pdl_wait();
     const int m = blockIdx.x;
-    norm.template run<3>(planes + static_cast<size_t>(m) * 3 * H, nullptr, x + static_cast<size_t>(m) * H, 1, H, eps, red);
+    norm.template run<3>(planes + static_cast<size_t>(m) * 3 * H, xn ? xn + static_cast<size_t>(m) * H : nullptr, x + static_cast<size_t>(m) * H, 1, H, eps, red);
 }
 
 // h = silu(gate) * up * route weight -> planes[(3m + term)][S * I], descale[m]
@@ -259,7 +259,7 @@ int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const v
     if (M < 1 || M > kMaxRows || H % 128 || H > 4096 || I % 64 || S < 1 || S > 16) return cudaErrorInvalidValue;
     auto st = static_cast<cudaStream_t>(stream);
     int e = launch(rows_norm_split_kernel, dim3(M), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln),
-                   static_cast<uint8_t*>(planes), H, eps);
+                   static_cast<uint8_t*>(planes), static_cast<float*>(nullptr), H, eps);
     if (e) return e;
     CUtensorMap mw, mx;
     const uint64_t wrows = static_cast<uint64_t>(n_experts_total) * 2 * I;
@@ -268,6 +268,25 @@ int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const v
     a.w_s = static_cast<const float*>(w13_s); a.ids = static_cast<const int*>(ids); a.gu = static_cast<float*>(gu);
     a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.status = status;
     return launch_tc_moe<false>(mw, mx, a, dim3(2 * I / kBM, S, M), st);
+}
+
+// rmsnorm(x[m]) * gamma for M rows -> e4m3 planes [3M][H] (and, if xn != null, the fp32 rows [M][H]).
+int nexrt_rows_norm_split(const void* x, const void* gamma, void* planes, void* xn, int H, int M, float eps, void* stream) {
+    if (M < 1 || M > kMaxRows || H % 4 || H > 4096) return cudaErrorInvalidValue;
+    return launch(rows_norm_split_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
+                  static_cast<const float*>(gamma), static_cast<uint8_t*>(planes), static_cast<float*>(xn), H, eps);
+}
+
+// out[m][r] = sum_k W[r][k] * xhat[m][k] for M rows at once: W [R][K] e4m3 with 128x128 block scales, xhat given as
+// the planes of nexrt_rows_norm_split.  The weights are streamed once for all rows.  zero_ids: M zero int32 words.
+int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void* out, const void* zero_ids, int R, int K, int M, int* status, void* stream) {
+    if (M < 1 || M > kMaxRows || R % 128 || K % 128 || K > 8192) return cudaErrorInvalidValue;
+    CUtensorMap mw, mx;
+    if (!tensor_map(&mw, w, R, K, K, kBM, false) || !tensor_map(&mx, planes, 3 * M, K, K, kBN, false)) return cudaErrorInvalidValue;
+    TcMoeArgs a{};
+    a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(out);
+    a.H = K; a.I = R / 2; a.S = 1; a.M = M; a.n_total = 1; a.status = status;     // one "expert" of R rows, named by every row
+    return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM, 1, 1), static_cast<cudaStream_t>(stream));
 }
 
 // Down projections + all-reduce + residual.  planes: e4m3 [3M][S*I] scratch, descale: fp32 [M] scratch.

@@ -12,6 +12,8 @@ from __future__ import annotations
 
 import torch
 
+import os
+
 from .ops.lib import check, ptr
 from .runtime.context import StepContext
 
@@ -27,6 +29,9 @@ class Gdn:
             pad = torch.zeros(self.ba_rows_pad, ba.shape[1], dtype=ba.dtype, device=ba.device)
             pad[: ba.shape[0]] = ba
             w["ba_w_pad"] = pad
+        # rows from which the front projection runs as one tcgen05 GEMM (NEXRT_TC_ROWS=0 switches it off)
+        self.tc_rows = int(os.environ.get("NEXRT_TC_ROWS", "4")) or 1 << 30
+        self.tc_ok = spec.gdn_front_rows % 128 == 0 and ctx.cfg.hidden % 256 == 0 and ctx.cfg.hidden <= 4096
         self.conv_ring = torch.zeros(conv_ring, spec.gdn_qkv_rows, dtype=torch.float32, device=dev)
         self.state_ring = torch.zeros(state_ring, spec.gdn_v, 128, 128, dtype=torch.float32, device=dev)
 
@@ -37,6 +42,28 @@ class Gdn:
     def forward(self, M: int = 1) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
         cfg, spec, st = c.cfg, c.spec, c.stream()
+        if M >= self.tc_rows and self.tc_ok:
+            # multi-row steps: the q|k|v|z projection of all rows is one tcgen05 GEMM (weights streamed once),
+            # then a small tail kernel does the conv ring, SiLU, z store and the b/a rows
+            R = spec.gdn_front_rows
+            check(lib.nexrt_rows_norm_split(ptr(c.x), ptr(w["in_ln"]), ptr(c.moe_planes1), ptr(c.wide_xn), cfg.hidden, M, cfg.rms_eps, st), "rows_norm_split")
+            check(lib.nexrt_tc_rows_gemm(ptr(w["front_w"]), ptr(w["front_s"]), ptr(c.moe_planes1), ptr(c.wide_pre), ptr(c.zero_ids), R, cfg.hidden, M,
+                                         ptr(c.status), st), "tc_rows_gemm")
+            check(
+                lib.nexrt_gdn_front_tail(
+                    ptr(c.wide_pre), ptr(c.wide_xn), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]), ptr(w["dt_bias"]), ptr(c.ctl),
+                    ptr(self.conv_ring), ptr(c.gdn_qkv), ptr(c.gdn_z), ptr(c.gdn_beta), ptr(c.gdn_g), cfg.hidden, R, spec.gdn_qkv_rows, spec.gdn_v, M,
+                    self.conv_ring_len, st,
+                ),
+                "gdn_front_tail",
+            )
+        else:
+            self._front_fused(M)
+        self._rest(M)
+
+    def _front_fused(self, M: int) -> None:
+        c, w, lib = self.ctx, self.w, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
         check(
             lib.nexrt_gdn_front(
                 ptr(c.x), ptr(w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]),
@@ -45,6 +72,10 @@ class Gdn:
             ),
             "gdn_front",
         )
+
+    def _rest(self, M: int) -> None:
+        c, w, lib = self.ctx, self.w, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
         check(
             lib.nexrt_gdn_core(
                 ptr(c.gdn_qkv), ptr(c.gdn_beta), ptr(c.gdn_g), ptr(c.ctl), ptr(self.state_ring), ptr(c.gdn_out), spec.gdn_qk, spec.gdn_v,

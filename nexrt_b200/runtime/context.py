@@ -79,6 +79,9 @@ class StepContext:
         self.moe_planes1 = torch.zeros(3 * MAX_ROWS, cfg.hidden, dtype=torch.uint8, device=device)
         self.moe_planes2 = torch.zeros(3 * MAX_ROWS, S * spec.inter, dtype=torch.uint8, device=device)
         self.moe_descale = z(MAX_ROWS)
+        self.wide_xn = z(MAX_ROWS, cfg.hidden)                                    # fp32 normalised rows (b/a rows of the wide GDN front)
+        self.wide_pre = z(MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts
+        self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)
         self.head_ticket = z(1, dtype=i32)

@@ -53,7 +53,7 @@ def main() -> None:
     torch.cuda.set_device(dev)
     cfg = shrunk_config() if a.shrunk else full_config().truncated(a.layers)
     model = random_rank_model(cfg, a.tp, 0, dev)
-    eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, shape_tp=a.tp, max_rows=max(a.rows, 1), cache_len=a.ctx + 64 * a.rows + 1024)
+    eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, shape_tp=a.tp, max_rows=max(a.rows, 1), cache_len=a.ctx + (a.steps + 16) * 12 * max(a.rows, 1) + 1024)   # room for every replay of every re-capture
     eng.reset(first_token=1, committed_len=a.ctx)
     eng.set_rows(list(range(1, a.rows + 1)))
     eng.set_forced_commit(a.rows)
