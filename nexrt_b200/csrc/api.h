@@ -126,9 +126,11 @@ int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, 
 
 // ---- wide (multi-row) projections on tcgen05 ---------------------------------------------------------------------
 int nexrt_rows_norm_split(const void* x, const void* gamma, void* planes, void* xn, int H, int M, float eps, void* stream);
-int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void* out, const void* zero_ids, int R, int K, int M, int* status, void* stream);
+int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void* out, const void* zero_ids, int R, int K, int M, int ksplit, int* status,
+                       void* stream);   /* out: [ksplit][M][R] partial planes */
 int nexrt_gdn_front_tail(const void* pre, const void* xn, const void* ba_w, const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl,
-                         void* conv_ring, void* qkv, void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, void* stream);
+                         void* conv_ring, void* qkv, void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, int ksplit,
+                         void* stream);
 
 #ifdef __cplusplus
 }

@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
 // Tail of the wide front (multi-row steps): the q|k|v|z projections of all rows were produced by the tcgen05 rows
 // GEMM into pre[M][R]; this kernel applies the per-channel conv ring + SiLU / the z store (one thread per weight
 // row, all token rows in registers), and extra CTAs project the bf16 b/a rows from the fp32 normalised rows xn.
-__global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, const float* __restrict__ pre, const float* __restrict__ xn, int row_ctas) {
+__global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, const float* __restrict__ pre, const float* __restrict__ xn, int row_ctas,
+                                                             int ksplit) {
     pdl_launch_dependents();
     pdl_wait();
     if (static_cast<int>(blockIdx.x) < row_ctas) {
@@ -196,7 +197,11 @@ __global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, con
         if (row >= a.R) return;
         float p[kMaxRows];
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) p[m] = m < a.M ? pre[static_cast<size_t>(m) * a.R + row] : 0.f;
+        for (int m = 0; m < kMaxRows; ++m) {
+            p[m] = 0.f;
+            if (m < a.M)
+                for (int ks = 0; ks < ksplit; ++ks) p[m] += pre[(static_cast<size_t>(ks) * a.M + m) * a.R + row];   // K-split partials, fixed order
+        }
         float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
         if (row < a.C) cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
         gdn_front_row<kMaxRows>(a, row, p, 0, a.M, a.ctl[kCtlCommittedLen], cw);
@@ -301,7 +306,7 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
 // Tail of the wide front: pre [M][R] fp32 projections, xn [M][H] fp32 normalised rows (see gdn_front_tail_kernel).
 extern "C" int nexrt_gdn_front_tail(const void* pre, const void* xn, const void* ba_w, const void* conv_w, const void* a_log, const void* dt_bias,
                                     const void* ctl, void* conv_ring, void* qkv, void* z, void* beta, void* g, int H, int R, int C, int nv, int M,
-                                    int conv_ring_len, void* stream) {
+                                    int conv_ring_len, int ksplit, void* stream) {
     if (M < 1 || M > kMaxRows || H % 256 || conv_ring_len < M + 3) return cudaErrorInvalidValue;
     GdnFrontArgs a{nullptr, nullptr, nullptr, nullptr, static_cast<const __nv_bfloat16*>(ba_w), static_cast<const float*>(conv_w),
                    static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), static_cast<const int*>(ctl),
@@ -309,7 +314,7 @@ extern "C" int nexrt_gdn_front_tail(const void* pre, const void* xn, const void*
                    static_cast<float*>(g), H, R, C, nv, M, conv_ring_len, 0.f, 0, nullptr};
     const int row_ctas = (R + 255) / 256, ba_ctas = (2 * nv * M + 7) / 8;
     return launch(gdn_front_tail_kernel, dim3(row_ctas + ba_ctas), dim3(256), 0, static_cast<cudaStream_t>(stream), a, static_cast<const float*>(pre),
-                  static_cast<const float*>(xn), row_ctas);
+                  static_cast<const float*>(xn), row_ctas, ksplit);
 }
 
 extern "C" int nexrt_gdn_core(const void* qkv, const void* beta, const void* g, const void* ctl, void* state_ring, void* out, int nqk, int nv,

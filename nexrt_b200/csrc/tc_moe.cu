@@ -62,21 +62,6 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     int m, slot, mt, expert = 0;
     if (DOWN) { mt = blockIdx.x; m = blockIdx.y; slot = 0; }
     else { mt = blockIdx.x; slot = blockIdx.y; m = blockIdx.z; }
-    pdl_wait();
-    if (!DOWN) {
-        // route plan: the first row that names an expert computes it for every row that does
-        expert = a.ids[m * a.S + slot];
-        for (int m2 = 0; m2 < m; ++m2)
-            for (int s2 = 0; s2 < a.S; ++s2)
-                if (a.ids[m2 * a.S + s2] == expert) return;          // uniform for the CTA
-        if (threadIdx.x < kMaxRows) {
-            int u = -1;
-            if (static_cast<int>(threadIdx.x) >= m && static_cast<int>(threadIdx.x) < a.M)
-                for (int s2 = 0; s2 < a.S; ++s2)
-                    if (a.ids[threadIdx.x * a.S + s2] == expert) u = s2;
-            s_user[threadIdx.x] = u;
-        }
-    }
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base);
     uint8_t* smem = base + 1024;
@@ -90,7 +75,13 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     constexpr uint32_t kCols = kAccBufs * kBN;
 
     const int kpe = DOWN ? a.I / 128 : a.H / 128;      // K blocks per expert
-    const int KB = DOWN ? a.S * kpe : kpe;
+    // split K: blockIdx.y of the plain rows GEMM (S == 1) names a contiguous range of K blocks; partial sums go to
+    // separate output planes that the consumer adds in a fixed order
+    const int ksplit = (!DOWN && a.S == 1) ? static_cast<int>(gridDim.y) : 1;
+    const int kb_per = (kpe + ksplit - 1) / ksplit;
+    const int kb0 = (!DOWN && a.S == 1) ? static_cast<int>(blockIdx.y) * kb_per : 0;
+    const int KB = DOWN ? a.S * kpe : max(0, min(kb_per, kpe - kb0));
+    // everything that does not depend on the predecessor's output happens before the dependency wait
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
         for (int b = 0; b < kAccBufs; ++b) { mbar_init(tfull(b), 1); mbar_init(tempty(b), 4); }
@@ -98,31 +89,49 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kCols);
+    pdl_wait();
+    bool active = true;
+    if (!DOWN) {
+        // route plan: the first row that names an expert computes it for every row that does
+        if (a.S == 1) slot = 0;
+        expert = a.ids[m * a.S + slot];
+        for (int m2 = 0; m2 < m; ++m2)
+            for (int s2 = 0; s2 < a.S; ++s2)
+                if (a.ids[m2 * a.S + s2] == expert) active = false;   // uniform for the CTA
+        if (threadIdx.x < kMaxRows) {
+            int u = -1;
+            if (static_cast<int>(threadIdx.x) >= m && static_cast<int>(threadIdx.x) < a.M)
+                for (int s2 = 0; s2 < a.S; ++s2)
+                    if (a.ids[threadIdx.x * a.S + s2] == expert) u = s2;
+            s_user[threadIdx.x] = u;
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int n_kb = active ? KB : 0;
 
     // weight rows of K block kb start at this row of the flattened expert matrix
-    auto expert_of = [&](int kb) { return min(max(DOWN ? a.ids[m * a.S + kb / kpe] : expert, 0), a.n_total - 1); };
+    auto expert_of = [&](int kb) { return min(max(DOWN ? a.ids[m * a.S + kb / kpe] : expert, 0), a.n_total - 1); };   // kb: index in this CTA's range
     const int rows_per_expert = DOWN ? a.H : I2;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < KB; ++kb) {
+            for (int kb = 0; kb < n_kb; ++kb) {
                 const int s = kb % kStages;
                 if (!mbar_wait(empty(s), ((kb / kStages) & 1) ^ 1, abort_flag)) break;
                 mbar_expect_tx(full(s), kA + kB);
                 const uint32_t dst = smem_u32(smem + s * kStage);
                 const int e = expert_of(kb);
-                tma_load_2d(dst, &map_w, (kb % kpe) * kSpan, e * rows_per_expert + mt * kBM, full(s));
-                tma_load_2d(dst + kA, &map_x, kb * kSpan, 0, full(s));
+                tma_load_2d(dst, &map_w, ((kb0 + kb) % kpe) * kSpan, e * rows_per_expert + mt * kBM, full(s));
+                tma_load_2d(dst + kA, &map_x, (kb0 + kb) * kSpan, 0, full(s));
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc<true>(kBN);
-            for (int kb = 0; kb < KB; ++kb) {
+            for (int kb = 0; kb < n_kb; ++kb) {
                 const int s = kb % kStages, buf = kb % kAccBufs;
                 if (!mbar_wait(tempty(buf), ((kb / kAccBufs) & 1) ^ 1, abort_flag)) break;
                 if (!mbar_wait(full(s), (kb / kStages) & 1, abort_flag)) break;
@@ -143,14 +152,14 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
 #pragma unroll
         for (int n = 0; n < NC; ++n) acc[n] = 0.f;
         bool ok = true;
-        for (int kb = 0; kb < KB && ok; ++kb) {
+        for (int kb = 0; kb < n_kb && ok; ++kb) {
             const int buf = kb % kAccBufs;
             ok = mbar_wait(tfull(buf), (kb / kAccBufs) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
             const int e = expert_of(kb);
-            const float w = __ldg(a.w_s + (static_cast<size_t>(e) * (rows_per_expert / 128) + mt) * kpe + kb % kpe);
+            const float w = __ldg(a.w_s + (static_cast<size_t>(e) * (rows_per_expert / 128) + mt) * kpe + (kb0 + kb) % kpe);
             if (DOWN) {
                 float p[4];
                 tmem_ld4(taddr + 3 * m, p);
@@ -169,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty(buf));
         }
-        if (ok) {
+        if (ok && active) {
             if (DOWN) {
                 const float val = (acc[0] + acc[1] * (1.f / 16.f) + acc[2] * (1.f / 256.f)) * a.descale[m];
                 LLCall call{0u, 0u};
@@ -183,7 +192,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
                     const int u = s_user[m2];
                     if (u >= 0) {
                         const float val = (acc[3 * m2] + acc[3 * m2 + 1] * (1.f / 16.f) + acc[3 * m2 + 2] * (1.f / 256.f)) * kSplitDescale;
-                        a.gu[(static_cast<size_t>(m2) * a.S + u) * I2 + row] = val;
+                        a.gu[(static_cast<size_t>(ksplit > 1 ? blockIdx.y : 0) * a.M * a.S + static_cast<size_t>(m2) * a.S + u) * I2 + row] = val;
                     }
                 }
             }
@@ -279,14 +288,17 @@ int nexrt_rows_norm_split(const void* x, const void* gamma, void* planes, void* 
 
 // out[m][r] = sum_k W[r][k] * xhat[m][k] for M rows at once: W [R][K] e4m3 with 128x128 block scales, xhat given as
 // the planes of nexrt_rows_norm_split.  The weights are streamed once for all rows.  zero_ids: M zero int32 words.
-int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void* out, const void* zero_ids, int R, int K, int M, int* status, void* stream) {
-    if (M < 1 || M > kMaxRows || R % 128 || K % 128 || K > 8192) return cudaErrorInvalidValue;
+// ksplit > 1 splits K over that many CTAs per row tile: out then holds ksplit partial planes [ksplit][M][R] for the
+// consumer to add in order.
+int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void* out, const void* zero_ids, int R, int K, int M, int ksplit, int* status,
+                       void* stream) {
+    if (M < 1 || M > kMaxRows || R % 128 || K % 128 || K > 8192 || ksplit < 1 || ksplit > 8) return cudaErrorInvalidValue;
     CUtensorMap mw, mx;
     if (!tensor_map(&mw, w, R, K, K, kBM, false) || !tensor_map(&mx, planes, 3 * M, K, K, kBN, false)) return cudaErrorInvalidValue;
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(out);
     a.H = K; a.I = R / 2; a.S = 1; a.M = M; a.n_total = 1; a.status = status;     // one "expert" of R rows, named by every row
-    return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM, 1, 1), static_cast<cudaStream_t>(stream));
+    return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM, ksplit, 1), static_cast<cudaStream_t>(stream));
 }
 
 // Down projections + all-reduce + residual.  planes: e4m3 [3M][S*I] scratch, descale: fp32 [M] scratch.

@@ -48,12 +48,12 @@ class Gdn:
             R = spec.gdn_front_rows
             check(lib.nexrt_rows_norm_split(ptr(c.x), ptr(w["in_ln"]), ptr(c.moe_planes1), ptr(c.wide_xn), cfg.hidden, M, cfg.rms_eps, st), "rows_norm_split")
             check(lib.nexrt_tc_rows_gemm(ptr(w["front_w"]), ptr(w["front_s"]), ptr(c.moe_planes1), ptr(c.wide_pre), ptr(c.zero_ids), R, cfg.hidden, M,
-                                         ptr(c.status), st), "tc_rows_gemm")
+                                         c.wide_ksplit, ptr(c.status), st), "tc_rows_gemm")
             check(
                 lib.nexrt_gdn_front_tail(
                     ptr(c.wide_pre), ptr(c.wide_xn), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]), ptr(w["dt_bias"]), ptr(c.ctl),
                     ptr(self.conv_ring), ptr(c.gdn_qkv), ptr(c.gdn_z), ptr(c.gdn_beta), ptr(c.gdn_g), cfg.hidden, R, spec.gdn_qkv_rows, spec.gdn_v, M,
-                    self.conv_ring_len, st,
+                    self.conv_ring_len, c.wide_ksplit, st,
                 ),
                 "gdn_front_tail",
             )

@@ -7,6 +7,8 @@ buffers every block of an engine shares, so a 60-layer stack carries one set of 
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config import ModelConfig, ShardSpec
@@ -80,7 +82,8 @@ class StepContext:
         self.moe_planes2 = torch.zeros(3 * MAX_ROWS, S * spec.inter, dtype=torch.uint8, device=device)
         self.moe_descale = z(MAX_ROWS)
         self.wide_xn = z(MAX_ROWS, cfg.hidden)                                    # fp32 normalised rows (b/a rows of the wide GDN front)
-        self.wide_pre = z(MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts
+        self.wide_ksplit = int(os.environ.get("NEXRT_WIDE_KSPLIT", "4"))                                                       # K-split of the wide front GEMMs (partials summed by the tail)
+        self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts
         self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)

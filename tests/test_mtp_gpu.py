@@ -5,7 +5,7 @@ drafts are accepted in full, and the forced-commit controls behave (test_specula
 import pytest
 import torch
 
-from nexrt_b200.models.reference import RefModel, synthetic_prompt
+from nexrt_b200.models.reference import RefModel, robust_prompt, synthetic_prompt
 from nexrt_b200.mtp import MtpDraft, capture_round, generate_mtp
 from nexrt_b200.mtp.weights import random_mtp_checkpoint, shard_mtp
 from nexrt_b200.runtime.control import Ctl
@@ -49,8 +49,8 @@ def test_mtp_stream_equals_greedy_stream(setup):
 
 def test_perfect_drafts_are_all_accepted(setup):
     cfg, ref, eng, mtp = setup
-    prompt = synthetic_prompt(cfg.vocab, 24, seed=12)
-    ref.reset()
+    # expert selection is discontinuous: compare arithmetics on a prompt whose routing margins are wide
+    prompt, _ = robust_prompt(ref, cfg.vocab, 24, n_new=6, seeds=range(1, 17))
     toks_ref, _ = ref.greedy(prompt, 6)
     first = eng.prefill(prompt, chunk=8)
     assert first == toks_ref[0]
@@ -66,8 +66,7 @@ def test_perfect_drafts_are_all_accepted(setup):
 
 def test_wrong_drafts_commit_one_token(setup):
     cfg, ref, eng, mtp = setup
-    prompt = synthetic_prompt(cfg.vocab, 16, seed=13)
-    ref.reset()
+    prompt, _ = robust_prompt(ref, cfg.vocab, 16, n_new=3, seeds=range(1, 17))
     toks_ref, _ = ref.greedy(prompt, 3)
     first = eng.prefill(prompt, chunk=8)
     wrong = [(t + 1) % cfg.vocab for t in toks_ref[1:4]]
