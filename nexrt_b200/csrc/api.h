@@ -132,6 +132,10 @@ int nexrt_gdn_front_tail(const void* pre, const void* xn, const void* ba_w, cons
                          void* conv_ring, void* qkv, void* z, void* beta, void* g, int H, int R, int C, int nv, int M, int conv_ring_len, int ksplit,
                          void* stream);
 
+int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void* planes, void* partial, const void* zero_ids, int rows, int rows_pad, int K,
+                           int M, int ksplit, float eps, int* status, void* stream);   /* partial: [ksplit][M][rows_pad] */
+int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

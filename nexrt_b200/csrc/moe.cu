@@ -293,6 +293,25 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     if (threadIdx.x == 0) *a.ticket = 0;
 }
 
+// Top-k stage of the wide router (multi-row steps): the logits arrive as K-split partial planes
+// partial[ks][m][rows_pad] from the tcgen05 rows GEMM; they are added in a fixed order into shared memory, kept
+// in a.logits for inspection, and selected exactly like the fused router does.
+__global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ksplit) {
+    extern __shared__ __align__(16) float lg_s[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int rows = a.E + 1;
+    for (int idx = threadIdx.x; idx < a.M * rows; idx += blockDim.x) {
+        const int m = idx / rows, e = idx % rows;
+        float t = 0.f;
+        for (int ks = 0; ks < ksplit; ++ks) t += __ldcg(a.partial + (static_cast<size_t>(ks) * a.M + m) * a.rows_pad + e);
+        lg_s[idx] = t;
+        a.logits[idx] = t;
+    }
+    __syncthreads();
+    router_topk<true>(a, lg_s);
+}
+
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
 // Expert gate/up: one CTA per 16 virtual rows (slot, i), the 8 warps split K = H.
 __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
@@ -402,6 +421,13 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
     const size_t smem = sizeof(float) * (static_cast<size_t>(mb + 1) * H + gemv_part_floats((E + 1 + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, gemv_threads())));
     if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
     return launch(moe_router_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+}
+
+extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream) {
+    if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1) return cudaErrorInvalidValue;
+    RouterArgs a{nullptr, nullptr, nullptr, static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), nullptr, 0, E, topk, M, 0.f,
+                 const_cast<float*>(static_cast<const float*>(partial)), rows_pad};
+    return launch(moe_topk_rows_kernel, dim3(1), dim3(256), sizeof(float) * M * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit);
 }
 
 extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I,

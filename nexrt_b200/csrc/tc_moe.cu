@@ -52,7 +52,8 @@ struct TcMoeArgs {
 
 // DOWN = false: gate/up of one distinct expert for every row that routes to it.
 // DOWN = true : down projection of one row over its S experts + all-reduce + residual.
-template <bool DOWN>
+// BF16 = true (plain rows GEMM only): bf16 weights without block scales, two bf16 planes (hi, lo) per row.
+template <bool DOWN, bool BF16 = false>
 __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcMoeArgs a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_user[kMaxRows];     // gate/up: slot of row m that uses this CTA's expert, or -1
@@ -74,7 +75,9 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     auto tempty = [&](int b) { return bar0 + 8u * (2 * kStages + kAccBufs + b); };
     constexpr uint32_t kCols = kAccBufs * kBN;
 
-    const int kpe = DOWN ? a.I / 128 : a.H / 128;      // K blocks per expert
+    constexpr int kElems = BF16 ? kSpan / 2 : kSpan;   // elements of K per 128-byte block
+    constexpr int TERMS = BF16 ? 2 : 3;                // activation planes per row
+    const int kpe = DOWN ? a.I / 128 : a.H / kElems;   // K blocks per expert
     // split K: blockIdx.y of the plain rows GEMM (S == 1) names a contiguous range of K blocks; partial sums go to
     // separate output planes that the consumer adds in a fixed order
     const int ksplit = (!DOWN && a.S == 1) ? static_cast<int>(gridDim.y) : 1;
@@ -124,13 +127,13 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
                 mbar_expect_tx(full(s), kA + kB);
                 const uint32_t dst = smem_u32(smem + s * kStage);
                 const int e = expert_of(kb);
-                tma_load_2d(dst, &map_w, ((kb0 + kb) % kpe) * kSpan, e * rows_per_expert + mt * kBM, full(s));
-                tma_load_2d(dst + kA, &map_x, (kb0 + kb) * kSpan, 0, full(s));
+                tma_load_2d(dst, &map_w, ((kb0 + kb) % kpe) * kElems, e * rows_per_expert + mt * kBM, full(s));
+                tma_load_2d(dst + kA, &map_x, (kb0 + kb) * kElems, 0, full(s));
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc<true>(kBN);
+            constexpr uint32_t idesc = instr_desc<!BF16>(kBN);
             for (int kb = 0; kb < n_kb; ++kb) {
                 const int s = kb % kStages, buf = kb % kAccBufs;
                 if (!mbar_wait(tempty(buf), ((kb / kAccBufs) & 1) ^ 1, abort_flag)) break;
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
                 const uint32_t a0 = smem_u32(smem + s * kStage);
                 const uint64_t da = smem_desc(a0), db = smem_desc(a0 + kA);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) tc_mma<true>(tmem_base + buf * kBN, da + 2u * k, db + 2u * k, idesc, k != 0);
+                for (int k = 0; k < 4; ++k) tc_mma<!BF16>(tmem_base + buf * kBN, da + 2u * k, db + 2u * k, idesc, k != 0);
                 tc_commit(empty(s));
                 tc_commit(tfull(buf));
             }
@@ -159,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
             const int e = expert_of(kb);
-            const float w = __ldg(a.w_s + (static_cast<size_t>(e) * (rows_per_expert / 128) + mt) * kpe + (kb0 + kb) % kpe);
+            const float w = BF16 ? 1.f : __ldg(a.w_s + (static_cast<size_t>(e) * (rows_per_expert / 128) + mt) * kpe + (kb0 + kb) % kpe);
             if (DOWN) {
                 float p[4];
                 tmem_ld4(taddr + 3 * m, p);
@@ -190,8 +193,9 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
 #pragma unroll
                 for (int m2 = 0; m2 < kMaxRows; ++m2) {
                     const int u = s_user[m2];
-                    if (u >= 0) {
-                        const float val = (acc[3 * m2] + acc[3 * m2 + 1] * (1.f / 16.f) + acc[3 * m2 + 2] * (1.f / 256.f)) * kSplitDescale;
+                    if (u >= 0 && row < I2) {
+                        const float val = BF16 ? acc[TERMS * m2] + acc[TERMS * m2 + 1]
+                                               : (acc[3 * m2] + acc[3 * m2 + 1] * (1.f / 16.f) + acc[3 * m2 + 2] * (1.f / 256.f)) * kSplitDescale;
                         a.gu[(static_cast<size_t>(ksplit > 1 ? blockIdx.y : 0) * a.M * a.S + static_cast<size_t>(m2) * a.S + u) * I2 + row] = val;
                     }
                 }
@@ -225,6 +229,20 @@ __global__ void __launch_bounds__(256) rows_norm_split_kernel(const __nv_bfloat1
     norm.template run<3>(planes + static_cast<size_t>(m) * 3 * H, xn ? xn + static_cast<size_t>(m) * H : nullptr, x + static_cast<size_t>(m) * H, 1, H, eps, red);
 }
 
+// rmsnorm(x[m]) * gamma -> bf16 planes[(2m + {hi, lo})][H]: x' = hi + lo to ~2^-17
+__global__ void __launch_bounds__(256) rows_norm_split_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, __nv_bfloat16* planes,
+                                                                   int H, float eps) {
+    __shared__ float red[32];
+    extern __shared__ __align__(16) float xs[];
+    pdl_launch_dependents();
+    RowNorm<4> norm;
+    norm.preload_gamma(gamma, H);
+    pdl_wait();
+    const int m = blockIdx.x;
+    norm.template run<3>(nullptr, xs, x + static_cast<size_t>(m) * H, 1, H, eps, red);
+    split_bf16_rows(planes + static_cast<size_t>(m) * 2 * H, xs, 1, H);
+}
+
 // h = silu(gate) * up * route weight -> planes[(3m + term)][S * I], descale[m]
 __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restrict__ gu, const float* __restrict__ wts, uint8_t* planes, float* descale,
                                                            int I, int S) {
@@ -246,10 +264,10 @@ __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restri
     if (threadIdx.x == 0) descale[m] = ds[0];
 }
 
-template <bool DOWN>
+template <bool DOWN, bool BF16 = false>
 int launch_tc_moe(const CUtensorMap& mw, const CUtensorMap& mx, const TcMoeArgs& a, dim3 grid, cudaStream_t st) {
     static bool configured = false;
-    auto kern = tc_moe_kernel<DOWN>;
+    auto kern = tc_moe_kernel<DOWN, BF16>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -299,6 +317,24 @@ int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void*
     a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(out);
     a.H = K; a.I = R / 2; a.S = 1; a.M = M; a.n_total = 1; a.status = status;     // one "expert" of R rows, named by every row
     return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM, ksplit, 1), static_cast<cudaStream_t>(stream));
+}
+
+// Router logits of M rows: partial[ks][m][r] = sum over the K range ks of W[r][k] * xhat[m][k], W bf16 [rows][K] (rows
+// need not be a multiple of 128; rows_pad is the row stride of the output), xhat = rmsnorm(x) * gamma as bf16 hi + lo
+// planes written into `planes` ([2M][K] bf16 scratch).
+int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void* planes, void* partial, const void* zero_ids, int rows, int rows_pad, int K,
+                           int M, int ksplit, float eps, int* status, void* stream) {
+    if (M < 1 || M > kMaxRows || K % 64 || K > 4096 || rows_pad % 2 || rows_pad < rows || ksplit < 1 || ksplit > 16) return cudaErrorInvalidValue;
+    auto st = static_cast<cudaStream_t>(stream);
+    int e = launch(rows_norm_split_bf16_kernel, dim3(M), dim3(256), sizeof(float) * K, st, static_cast<const __nv_bfloat16*>(x),
+                   static_cast<const float*>(gamma), static_cast<__nv_bfloat16*>(planes), K, eps);
+    if (e) return e;
+    CUtensorMap mw, mx;
+    if (!tensor_map(&mw, w, rows, K, K, kBM, true) || !tensor_map(&mx, planes, 2 * M, K, K, kBN, true)) return cudaErrorInvalidValue;
+    TcMoeArgs a{};
+    a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(partial);
+    a.H = K; a.I = rows_pad / 2; a.S = 1; a.M = M; a.n_total = 1; a.status = status;
+    return launch_tc_moe<false, true>(mw, mx, a, dim3((rows + kBM - 1) / kBM, ksplit, 1), st);
 }
 
 // Down projections + all-reduce + residual.  planes: e4m3 [3M][S*I] scratch, descale: fp32 [M] scratch.

@@ -30,6 +30,7 @@ class Moe:
             w["router_w_pad"] = pad
         # rows from which the experts run on the tcgen05 kernels (NEXRT_TC_MOE_ROWS=0 switches them off)
         self.tc_rows = int(os.environ.get("NEXRT_TC_MOE_ROWS", "2")) or 1 << 30
+        self.tc_router_rows = int(os.environ.get("NEXRT_TC_ROUTER_ROWS", "8")) or 1 << 30   # below 8 rows the fused router kernel is as fast
         cfg, spec = ctx.cfg, ctx.spec
         self.tc_ok = cfg.hidden % 128 == 0 and cfg.hidden <= 4096 and spec.inter % 128 == 0
 
@@ -37,6 +38,24 @@ class Moe:
         c, w, lib = self.ctx, self.w, self.ctx.lib
         cfg, spec, st = c.cfg, c.spec, c.stream()
         S = cfg.top_k + 1
+        wide = M >= self.tc_router_rows and self.tc_ok and cfg.hidden % (64 * c.router_ksplit) == 0
+        if wide:
+            # multi-row steps: router logits of all rows in one tcgen05 GEMM (bf16 weights, hi + lo activation planes,
+            # K split over CTAs), then one small kernel adds the partial planes and selects the experts
+            check(
+                lib.nexrt_tc_router_logits(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.router_planes), ptr(c.router_partial), ptr(c.zero_ids),
+                                           cfg.n_experts + 1, self.rows_pad, cfg.hidden, M, c.router_ksplit, cfg.rms_eps, ptr(c.status), st),
+                "tc_router_logits",
+            )
+            check(lib.nexrt_moe_router_topk(ptr(c.router_partial), c.router_ksplit, self.rows_pad, ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts),
+                                            cfg.n_experts, cfg.top_k, M, st), "moe_router_topk")
+        else:
+            self._router_fused(M)
+        self._experts(M)
+
+    def _router_fused(self, M: int) -> None:
+        c, w, lib = self.ctx, self.w, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
         check(
             lib.nexrt_moe_router(
                 ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_ticket),
@@ -44,6 +63,11 @@ class Moe:
             ),
             "moe_router",
         )
+
+    def _experts(self, M: int) -> None:
+        c, w, lib = self.ctx, self.w, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
+        S = cfg.top_k + 1
         if M >= self.tc_rows and self.tc_ok:
             # multi-row steps: experts on the tcgen05 tensor cores, each distinct expert streamed once, the
             # tensor-parallel all-reduce fused into the down projection's epilogue (csrc/tc_moe.cu)

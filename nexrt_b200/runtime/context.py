@@ -85,6 +85,9 @@ class StepContext:
         self.wide_ksplit = int(os.environ.get("NEXRT_WIDE_KSPLIT", "4"))                                                       # K-split of the wide front GEMMs (partials summed by the tail)
         self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts
         self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
+        self.router_ksplit = 8
+        self.router_planes = torch.zeros(2 * MAX_ROWS, cfg.hidden, dtype=torch.bfloat16, device=device)
+        self.router_partial = z(self.router_ksplit, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)
         self.head_ticket = z(1, dtype=i32)
