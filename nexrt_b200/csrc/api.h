@@ -136,6 +136,9 @@ int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void
                            int M, int ksplit, float eps, int* status, void* stream);   /* partial: [ksplit][M][rows_pad] */
 int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream);
 
+int nexrt_lmhead_sample_from_logits(const void* logits_in, void* cand, void* ticket, const void* sampling, void* ctl, void* export_buf, int H, int V_local,
+                                    int vocab_base, int M, int mode, int arg, const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -187,6 +187,7 @@ struct HeadArgs {
     const float* final_ln;           // [H] 1 + w
     const __nv_bfloat16* w;          // [V_local][H]
     float* logits_out;               // optional [M][V_local]
+    const float* logits_in;          // optional [M][V_local]: logits computed beforehand (wide steps); skips the GEMV
     unsigned long long* cand;        // [M][n_cta][28]
     int* ticket;
     const unsigned long long* sampling;
@@ -212,7 +213,8 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     int v0, v1;
     cta_range(a.V_local, blockIdx.x, gridDim.x, &v0, &v1);
     const int nv = v1 - v0, nv_max = (a.V_local + gridDim.x - 1) / gridDim.x;
-    if (nv) prefetch_l2_range(a.w + static_cast<size_t>(v0) * a.H, static_cast<size_t>(nv) * a.H * 2);
+    const bool pre = a.logits_in != nullptr;
+    if (nv && !pre) prefetch_l2_range(a.w + static_cast<size_t>(v0) * a.H, static_cast<size_t>(nv) * a.H * 2);
     constexpr int kTile = 256;                                                          // rows per GEMV tile
     const GemvGeom gg = gemv_geom(a.H / 8, blockDim.x);
     float* xs = smem;                                                                   // [MB][H]
@@ -220,16 +222,25 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(part + gemv_part_floats(kTile, MB, gg));   // [MB][nv_max]
     float* gs = reinterpret_cast<float*>(keys + static_cast<size_t>(MB) * nv_max);                                // [H] norm multiplier
     GemvCta<MB, (MB == 1 ? 8 : 4), PlainBf16> gemv0(PlainBf16{a.w, a.H}, v0, min(kTile, nv), a.H);
-    gemv0.preload();
-    for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.final_ln[i];
+    if (!pre) {
+        gemv0.preload();
+        for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.final_ln[i];
+    }
     pdl_wait();
     const SamplingCfg cfg = read_sampling(a.sampling);
     const int K = a.mode == 2 ? 1 : cfg.top_k;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
         const int mb = min(MB, a.M - m0);
         if (m0) __syncthreads();
-        stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
-        for (int t0 = 0; t0 < nv; t0 += kTile) {
+        if (pre) {
+            for (int idx = threadIdx.x; idx < nv * mb; idx += blockDim.x) {
+                const int rl = idx % nv, m = idx / nv, row = v0 + rl;
+                keys[m * nv_max + rl] = make_key(__ldcg(a.logits_in + static_cast<size_t>(m0 + m) * a.V_local + row), a.vocab_base + row);
+            }
+            __syncthreads();
+        } else
+            stage_rmsnorm_plain(xs, a.x + static_cast<size_t>(m0) * a.H, gs, mb, a.H, a.eps, red);
+        for (int t0 = 0; t0 < nv && !pre; t0 += kTile) {
             const int nt = min(kTile, nv - t0);
             if (m0 == 0 && t0 == 0) gemv0.run(xs, part);
             else gemv_cta<MB, (MB == 1 ? 8 : 4)>(PlainBf16{a.w, a.H}, v0 + t0, nt, xs, a.H, part);
@@ -403,6 +414,25 @@ extern "C" int nexrt_lmhead_sample(const void* x, const void* final_ln, const vo
     a.logits_out = static_cast<float*>(logits_out); a.cand = static_cast<unsigned long long*>(cand); a.ticket = static_cast<int*>(ticket);
     a.sampling = static_cast<const unsigned long long*>(sampling); a.ctl = static_cast<int*>(ctl); a.export_buf = static_cast<int*>(export_buf);
     a.H = H; a.V_local = V_local; a.vocab_base = vocab_base; a.M = M; a.eps = eps; a.mode = mode; a.arg = arg; a.ch = *ch; a.site = site;
+    const int mb = M == 1 ? 1 : 4;
+    const int nv_max = (V_local + n_cta - 1) / n_cta;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, gemv_threads()))) +
+                        sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max + sizeof(float) * H;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (mb == 1) return launch(lmhead_sample_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+    return launch(lmhead_sample_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
+}
+
+// Same head on logits that were computed beforehand (the wide path of multi-row steps): logits_in [M][V_local] fp32.
+extern "C" int nexrt_lmhead_sample_from_logits(const void* logits_in, void* cand, void* ticket, const void* sampling, void* ctl, void* export_buf, int H,
+                                               int V_local, int vocab_base, int M, int mode, int arg, const NexrtLLChannel* ch, unsigned int site,
+                                               int n_cta, void* stream) {
+    if (M < 1 || M > kMaxRows || n_cta > 256 || ch == nullptr || (mode != 1 && mode != 2) || logits_in == nullptr) return cudaErrorInvalidValue;
+    if (ch->world > 1 && ch->slots < static_cast<unsigned int>(kMaxRows) * kMaxTopK * 2) return cudaErrorInvalidValue;
+    HeadArgs a{};
+    a.logits_in = static_cast<const float*>(logits_in); a.cand = static_cast<unsigned long long*>(cand); a.ticket = static_cast<int*>(ticket);
+    a.sampling = static_cast<const unsigned long long*>(sampling); a.ctl = static_cast<int*>(ctl); a.export_buf = static_cast<int*>(export_buf);
+    a.H = H; a.V_local = V_local; a.vocab_base = vocab_base; a.M = M; a.mode = mode; a.arg = arg; a.ch = *ch; a.site = site;
     const int mb = M == 1 ? 1 : 4;
     const int nv_max = (V_local + n_cta - 1) / n_cta;
     const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, gemv_threads()))) +

@@ -8,6 +8,8 @@ reference builds a fused ``W_fused = (1 + norm_w) x W`` copy, ``head.py:138-149`
 
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -24,6 +26,8 @@ class Head:
     def __init__(self, ctx: StepContext, w: dict, init_sampling: bool = True):
         self.ctx, self.w = ctx, w
         self.logits: Optional[torch.Tensor] = None
+        self.wide_logits: Optional[torch.Tensor] = None
+        self.tc_rows = int(os.environ.get("NEXRT_TC_HEAD_ROWS", "4")) or 1 << 30
         if init_sampling:
             self.set_sampling_config(0, *GREEDY)
 
@@ -42,6 +46,25 @@ class Head:
                 ctl: Optional[torch.Tensor] = None) -> None:
         c, w = self.ctx, self.w
         cfg, spec = c.cfg, c.spec
+        if M >= self.tc_rows and cfg.hidden % 64 == 0 and cfg.hidden <= 4096 and spec.vocab % 2 == 0:
+            # multi-row steps: logits of all rows in one tcgen05 GEMM (bf16 weights streamed once, hi + lo activation
+            # planes), then the same top-k / exchange / sample / commit kernel reading those logits
+            if self.wide_logits is None:
+                self.wide_logits = torch.zeros(8, spec.vocab, dtype=torch.float32, device=c.device)
+            lg = self.logits if self.logits is not None else self.wide_logits
+            check(
+                c.lib.nexrt_tc_router_logits(ptr(c.x if x is None else x), ptr(w["final_ln"]), ptr(w["lm_head"]), ptr(c.router_planes), ptr(lg),
+                                             ptr(c.zero_ids), spec.vocab, spec.vocab, cfg.hidden, M, 1, cfg.rms_eps, ptr(c.status), c.stream()),
+                "tc_lmhead_logits",
+            )
+            check(
+                c.lib.nexrt_lmhead_sample_from_logits(
+                    ptr(lg), ptr(c.head_cand), ptr(c.head_ticket), ptr(c.sampling), ptr(c.ctl if ctl is None else ctl), ptr(c.head_export), cfg.hidden,
+                    spec.vocab, spec.rank * spec.vocab, M, mode, arg, c.channel.ref, c.next_site(), c.n_cta, c.stream(),
+                ),
+                "lmhead_sample_from_logits",
+            )
+            return
         check(
             c.lib.nexrt_lmhead_sample(
                 ptr(c.x if x is None else x), ptr(w["final_ln"]), ptr(w["lm_head"]), ptr(self.logits), ptr(c.head_cand), ptr(c.head_ticket),

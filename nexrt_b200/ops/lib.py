@@ -76,6 +76,7 @@ _PROTOTYPES = {
     "nexrt_gdn_front_tail": [vp] * 12 + [ci] * 7 + [vp],
     "nexrt_tc_router_logits": [vp] * 6 + [ci] * 5 + [cf, vp, vp],
     "nexrt_moe_router_topk": [vp, ci, ci, vp, vp, vp, ci, ci, ci, vp],
+    "nexrt_lmhead_sample_from_logits": [vp] * 6 + [ci] * 6 + [CH, cu, ci, vp],
     "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 5 + [cf, vp, vp],
     "nexrt_tc_moe_l2_allreduce": [vp] * 8 + [ci] * 5 + [CH, cu, vp, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],
