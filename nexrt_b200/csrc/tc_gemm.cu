@@ -55,6 +55,7 @@ template <bool FP8, int BN>
 __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Args a) {
     using L = Layout<BN>;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ float sws[kMaxKBlocks];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base);
     uint8_t* smem = base + L::kBars;
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
                 const int kb = i / BN, n = i % BN;
                 sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * KB + kb] : 0.f;
             }
+            for (int i = et; i < KB; i += 128) sws[i] = __ldg(a.sw + static_cast<size_t>(blockIdx.y) * KB + i);   // weight block scales of this row tile
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         float acc[BN];
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * BN;
             if (FP8) {
-                const float w = __ldg(a.sw + static_cast<size_t>(blockIdx.y) * KB + r);
+                const float w = sws[r];
                 const float4* sx4 = reinterpret_cast<const float4*>(sxs + r * BN);
 #pragma unroll
                 for (int c = 0; c < BN; c += 16) {

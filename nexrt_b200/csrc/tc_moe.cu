@@ -35,7 +35,7 @@ constexpr int kBN = 32;                              // 3 planes x up to 8 rows,
 constexpr int kA = kBM * kSpan;                      // 16 KB weight tile
 constexpr int kB = kBN * kSpan;                      // 4 KB activation tile
 constexpr int kStage = kA + kB;
-constexpr int kSmem = 1024 + kStages * kStage + 1024;
+constexpr int smem_bytes(bool) { return 1024 + 4 * kStage + 1024; }
 
 struct TcMoeArgs {
     const float* w_s;       // block scales of the weight matrix, [rows / 128][K / 128] over the flattened experts
@@ -53,10 +53,16 @@ struct TcMoeArgs {
 // DOWN = false: gate/up of one distinct expert for every row that routes to it.
 // DOWN = true : down projection of one row over its S experts + all-reduce + residual.
 // BF16 = true (plain rows GEMM only): bf16 weights without block scales, two bf16 planes (hi, lo) per row.
+// Four shared-memory stages and EIGHT tensor-memory accumulator buffers, two CTAs per SM: what bounds one CTA's K walk is
+// the round trip commit -> epilogue wakes -> tcgen05.ld -> buffer released -> issuer wakes (about 2 us on B200), so the
+// number of K blocks in flight is what sets the rate; 8 buffers x 32 columns x 2 CTAs use all 512 TMEM columns.
 template <bool DOWN, bool BF16 = false>
 __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcMoeArgs a) {
+    constexpr int NS = 4;                // shared-memory stages
+    constexpr int NAB = 8;               // accumulator buffers in tensor memory
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_user[kMaxRows];     // gate/up: slot of row m that uses this CTA's expert, or -1
+    __shared__ float s_wscale[kMaxKBlocks + 16 * 8];   // block scale of every K block this CTA walks (no load in the loop)
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int I2 = 2 * a.I;
@@ -66,14 +72,14 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base);
     uint8_t* smem = base + 1024;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2 * kAccBufs);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccBufs + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * NS + 2 * NAB);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 2 * NAB + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
-    auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
-    auto tfull = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
-    auto tempty = [&](int b) { return bar0 + 8u * (2 * kStages + kAccBufs + b); };
-    constexpr uint32_t kCols = kAccBufs * kBN;
+    auto empty = [&](int s) { return bar0 + 8u * (NS + s); };
+    auto tfull = [&](int b) { return bar0 + 8u * (2 * NS + b); };
+    auto tempty = [&](int b) { return bar0 + 8u * (2 * NS + NAB + b); };
+    constexpr uint32_t kCols = NAB * kBN;
 
     constexpr int kElems = BF16 ? kSpan / 2 : kSpan;   // elements of K per 128-byte block
     constexpr int TERMS = BF16 ? 2 : 3;                // activation planes per row
@@ -86,8 +92,8 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     const int KB = DOWN ? a.S * kpe : max(0, min(kb_per, kpe - kb0));
     // everything that does not depend on the predecessor's output happens before the dependency wait
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
-        for (int b = 0; b < kAccBufs; ++b) { mbar_init(tfull(b), 1); mbar_init(tempty(b), 4); }
+        for (int s = 0; s < NS; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        for (int b = 0; b < NAB; ++b) { mbar_init(tfull(b), 1); mbar_init(tempty(b), 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -122,8 +128,8 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % kStages;
-                if (!mbar_wait(empty(s), ((kb / kStages) & 1) ^ 1, abort_flag)) break;
+                const int s = kb % NS;
+                if (!mbar_wait(empty(s), ((kb / NS) & 1) ^ 1, abort_flag)) break;
                 mbar_expect_tx(full(s), kA + kB);
                 const uint32_t dst = smem_u32(smem + s * kStage);
                 const int e = expert_of(kb);
@@ -135,9 +141,9 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc<!BF16>(kBN);
             for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % kStages, buf = kb % kAccBufs;
-                if (!mbar_wait(tempty(buf), ((kb / kAccBufs) & 1) ^ 1, abort_flag)) break;
-                if (!mbar_wait(full(s), (kb / kStages) & 1, abort_flag)) break;
+                const int s = kb % NS, buf = kb % NAB;
+                if (!mbar_wait(tempty(buf), ((kb / NAB) & 1) ^ 1, abort_flag)) break;
+                if (!mbar_wait(full(s), (kb / NS) & 1, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t a0 = smem_u32(smem + s * kStage);
                 const uint64_t da = smem_desc(a0), db = smem_desc(a0 + kA);
@@ -154,15 +160,23 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
         float acc[NC];
 #pragma unroll
         for (int n = 0; n < NC; ++n) acc[n] = 0.f;
+        // the block scales of the whole K walk go to shared memory first: a global load per K block would sit in the
+        // serial chain tmem-full -> load -> scale -> accumulate
+        if (!BF16) {
+            for (int kb = threadIdx.x - 64; kb < n_kb; kb += 128) {
+                const int e = expert_of(kb);
+                s_wscale[kb] = __ldg(a.w_s + (static_cast<size_t>(e) * (rows_per_expert / 128) + mt) * kpe + (kb0 + kb) % kpe);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         bool ok = true;
         for (int kb = 0; kb < n_kb && ok; ++kb) {
-            const int buf = kb % kAccBufs;
-            ok = mbar_wait(tfull(buf), (kb / kAccBufs) & 1, abort_flag);
+            const int buf = kb % NAB;
+            ok = mbar_wait(tfull(buf), (kb / NAB) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
-            const int e = expert_of(kb);
-            const float w = BF16 ? 1.f : __ldg(a.w_s + (static_cast<size_t>(e) * (rows_per_expert / 128) + mt) * kpe + (kb0 + kb) % kpe);
+            const float w = BF16 ? 1.f : s_wscale[kb];
             if (DOWN) {
                 float p[4];
                 tmem_ld4(taddr + 3 * m, p);
@@ -269,11 +283,11 @@ int launch_tc_moe(const CUtensorMap& mw, const CUtensorMap& mx, const TcMoeArgs&
     static bool configured = false;
     auto kern = tc_moe_kernel<DOWN, BF16>;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(DOWN));
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    return launch(kern, grid, dim3(kThreads), static_cast<size_t>(kSmem), st, mw, mx, a);
+    return launch(kern, grid, dim3(kThreads), static_cast<size_t>(smem_bytes(DOWN)), st, mw, mx, a);
 }
 
 }  // namespace
