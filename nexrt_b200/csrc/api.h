@@ -118,11 +118,12 @@ int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, floa
 // ---- experts of a multi-row step on tcgen05 (tc_moe.cu) -------------------------------------------------------
 // Gate/up of every distinct expert named in ids [M][S] (streamed once each); planes is e4m3 scratch [3M][H].
 int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, void* planes, int H, int I, int S,
-                    int M, int n_experts_total, float eps, int* status, void* stream);
+                    int M, int n_experts_total, int ksplit, float eps, int* status, void* stream);   /* gu: [ksplit][M][S][2I] partial planes */
 // Down projection over each row's S experts + tensor-parallel all-reduce + residual in one kernel; planes is e4m3
 // scratch [3M][S*I], descale fp32 scratch [M].
 int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, void* planes, void* descale,
-                              int H, int I, int S, int M, int n_experts_total, const NexrtLLChannel* ch, unsigned int site, int* status, void* stream);
+                              int H, int I, int S, int M, int n_experts_total, int gu_ksplit, const NexrtLLChannel* ch, unsigned int site, int* status,
+                              void* stream);
 
 // ---- wide (multi-row) projections on tcgen05 ---------------------------------------------------------------------
 int nexrt_rows_norm_split(const void* x, const void* gamma, void* planes, void* xn, int H, int M, float eps, void* stream);

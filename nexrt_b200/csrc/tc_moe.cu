@@ -45,6 +45,7 @@ struct TcMoeArgs {
     __nv_bfloat16* x;       // [M][H] residual stream (down projection only)
     int H, I, S, M;
     int n_total;            // experts in the weight matrix (routed + shared); ids are clamped into [0, n_total)
+    int ksplit;             // gate/up and plain GEMM: CTAs per row tile along K (partial planes [ksplit][M][S][rows])
     LLChannel ch;
     unsigned int site;
     int* status;
@@ -67,8 +68,12 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int I2 = 2 * a.I;
     int m, slot, mt, expert = 0;
+    int ks = 0;                                          // index of this CTA's K range
     if (DOWN) { mt = blockIdx.x; m = blockIdx.y; slot = 0; }
-    else { mt = blockIdx.x; slot = blockIdx.y; m = blockIdx.z; }
+    else {
+        const int n_mt = static_cast<int>(gridDim.x) / a.ksplit;
+        mt = blockIdx.x % n_mt; ks = blockIdx.x / n_mt; slot = blockIdx.y; m = blockIdx.z;
+    }
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base);
     uint8_t* smem = base + 1024;
@@ -84,11 +89,11 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     constexpr int kElems = BF16 ? kSpan / 2 : kSpan;   // elements of K per 128-byte block
     constexpr int TERMS = BF16 ? 2 : 3;                // activation planes per row
     const int kpe = DOWN ? a.I / 128 : a.H / kElems;   // K blocks per expert
-    // split K: blockIdx.y of the plain rows GEMM (S == 1) names a contiguous range of K blocks; partial sums go to
-    // separate output planes that the consumer adds in a fixed order
-    const int ksplit = (!DOWN && a.S == 1) ? static_cast<int>(gridDim.y) : 1;
+    // split K: each of the ksplit CTAs of a row tile walks a contiguous range of K blocks; partial sums go to separate
+    // output planes that the consumer adds in a fixed order
+    const int ksplit = DOWN ? 1 : a.ksplit;
     const int kb_per = (kpe + ksplit - 1) / ksplit;
-    const int kb0 = (!DOWN && a.S == 1) ? static_cast<int>(blockIdx.y) * kb_per : 0;
+    const int kb0 = ks * kb_per;
     const int KB = DOWN ? a.S * kpe : max(0, min(kb_per, kpe - kb0));
     // everything that does not depend on the predecessor's output happens before the dependency wait
     if (threadIdx.x == 0) {
@@ -102,7 +107,6 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     bool active = true;
     if (!DOWN) {
         // route plan: the first row that names an expert computes it for every row that does
-        if (a.S == 1) slot = 0;
         expert = a.ids[m * a.S + slot];
         for (int m2 = 0; m2 < m; ++m2)
             for (int s2 = 0; s2 < a.S; ++s2)
@@ -210,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
                     if (u >= 0 && row < I2) {
                         const float val = BF16 ? acc[TERMS * m2] + acc[TERMS * m2 + 1]
                                                : (acc[3 * m2] + acc[3 * m2 + 1] * (1.f / 16.f) + acc[3 * m2 + 2] * (1.f / 256.f)) * kSplitDescale;
-                        a.gu[(static_cast<size_t>(ksplit > 1 ? blockIdx.y : 0) * a.M * a.S + static_cast<size_t>(m2) * a.S + u) * I2 + row] = val;
+                        a.gu[(static_cast<size_t>(ks) * a.M * a.S + static_cast<size_t>(m2) * a.S + u) * I2 + row] = val;
                     }
                 }
             }
@@ -259,7 +263,7 @@ __global__ void __launch_bounds__(256) rows_norm_split_bf16_kernel(const __nv_bf
 
 // h = silu(gate) * up * route weight -> planes[(3m + term)][S * I], descale[m]
 __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restrict__ gu, const float* __restrict__ wts, uint8_t* planes, float* descale,
-                                                           int I, int S) {
+                                                           int I, int S, int M, int ksplit) {
     extern __shared__ __align__(16) float hs[];
     __shared__ float red[32];
     __shared__ float ds[1];
@@ -269,7 +273,13 @@ __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restri
     for (int k = threadIdx.x * 4; k < VK; k += blockDim.x * 4) {
         const int sl = k / I, i = k % I;
         const float* g = gu + (static_cast<size_t>(m) * S + sl) * 2 * I;
-        const float4 gt = *reinterpret_cast<const float4*>(g + i), up = *reinterpret_cast<const float4*>(g + I + i);
+        float4 gt = *reinterpret_cast<const float4*>(g + i), up = *reinterpret_cast<const float4*>(g + I + i);
+        for (int ks = 1; ks < ksplit; ++ks) {           // K-split partial planes of the gate/up product, fixed order
+            const float* gk = g + static_cast<size_t>(ks) * M * S * 2 * I;
+            const float4 g2 = *reinterpret_cast<const float4*>(gk + i), u2 = *reinterpret_cast<const float4*>(gk + I + i);
+            gt.x += g2.x; gt.y += g2.y; gt.z += g2.z; gt.w += g2.w;
+            up.x += u2.x; up.y += u2.y; up.z += u2.z; up.w += u2.w;
+        }
         const float wt = wts[m * S + sl];
         *reinterpret_cast<float4*>(hs + k) = make_float4(silu_f(gt.x) * up.x * wt, silu_f(gt.y) * up.y * wt, silu_f(gt.z) * up.z * wt, silu_f(gt.w) * up.w * wt);
     }
@@ -296,8 +306,8 @@ extern "C" {
 
 // Gate/up projections of all rows' experts.  planes: e4m3 [3M][H] scratch, written here.
 int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, void* planes, int H, int I, int S,
-                    int M, int n_experts_total, float eps, int* status, void* stream) {
-    if (M < 1 || M > kMaxRows || H % 128 || H > 4096 || I % 64 || S < 1 || S > 16) return cudaErrorInvalidValue;
+                    int M, int n_experts_total, int ksplit, float eps, int* status, void* stream) {
+    if (M < 1 || M > kMaxRows || H % 128 || H > 4096 || I % 64 || S < 1 || S > 16 || ksplit < 1 || ksplit > 4) return cudaErrorInvalidValue;
     auto st = static_cast<cudaStream_t>(stream);
     int e = launch(rows_norm_split_kernel, dim3(M), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln),
                    static_cast<uint8_t*>(planes), static_cast<float*>(nullptr), H, eps);
@@ -307,8 +317,8 @@ int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const v
     if (!tensor_map(&mw, w13, wrows, H, H, kBM, false) || !tensor_map(&mx, planes, 3 * M, H, H, kBN, false)) return cudaErrorInvalidValue;
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w13_s); a.ids = static_cast<const int*>(ids); a.gu = static_cast<float*>(gu);
-    a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.status = status;
-    return launch_tc_moe<false>(mw, mx, a, dim3(2 * I / kBM, S, M), st);
+    a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.ksplit = ksplit; a.status = status;
+    return launch_tc_moe<false>(mw, mx, a, dim3(2 * I / kBM * ksplit, S, M), st);
 }
 
 // rmsnorm(x[m]) * gamma for M rows -> e4m3 planes [3M][H] (and, if xn != null, the fp32 rows [M][H]).
@@ -329,8 +339,8 @@ int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void*
     if (!tensor_map(&mw, w, R, K, K, kBM, false) || !tensor_map(&mx, planes, 3 * M, K, K, kBN, false)) return cudaErrorInvalidValue;
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(out);
-    a.H = K; a.I = R / 2; a.S = 1; a.M = M; a.n_total = 1; a.status = status;     // one "expert" of R rows, named by every row
-    return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM, ksplit, 1), static_cast<cudaStream_t>(stream));
+    a.H = K; a.I = R / 2; a.S = 1; a.M = M; a.n_total = 1; a.ksplit = ksplit; a.status = status;     // one "expert" of R rows, named by every row
+    return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM * ksplit, 1, 1), static_cast<cudaStream_t>(stream));
 }
 
 // Router logits of M rows: partial[ks][m][r] = sum over the K range ks of W[r][k] * xhat[m][k], W bf16 [rows][K] (rows
@@ -347,26 +357,27 @@ int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void
     if (!tensor_map(&mw, w, rows, K, K, kBM, true) || !tensor_map(&mx, planes, 2 * M, K, K, kBN, true)) return cudaErrorInvalidValue;
     TcMoeArgs a{};
     a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(partial);
-    a.H = K; a.I = rows_pad / 2; a.S = 1; a.M = M; a.n_total = 1; a.status = status;
-    return launch_tc_moe<false, true>(mw, mx, a, dim3((rows + kBM - 1) / kBM, ksplit, 1), st);
+    a.H = K; a.I = rows_pad / 2; a.S = 1; a.M = M; a.n_total = 1; a.ksplit = ksplit; a.status = status;
+    return launch_tc_moe<false, true>(mw, mx, a, dim3((rows + kBM - 1) / kBM * ksplit, 1, 1), st);
 }
 
 // Down projections + all-reduce + residual.  planes: e4m3 [3M][S*I] scratch, descale: fp32 [M] scratch.
 int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, void* planes, void* descale,
-                              int H, int I, int S, int M, int n_experts_total, const NexrtLLChannel* ch, unsigned int site, int* status, void* stream) {
+                              int H, int I, int S, int M, int n_experts_total, int gu_ksplit, const NexrtLLChannel* ch, unsigned int site, int* status,
+                              void* stream) {
     if (M < 1 || M > kMaxRows || H % 128 || I % 128 || S < 1 || S > 16 || ch == nullptr) return cudaErrorInvalidValue;
     if (ch->world > 1 && ch->slots < static_cast<unsigned int>(kMaxRows) * H) return cudaErrorInvalidValue;
     auto st = static_cast<cudaStream_t>(stream);
     const int VK = S * I;
     int e = launch(rows_h_split_kernel, dim3(M), dim3(256), sizeof(float) * VK, st, static_cast<const float*>(gu), static_cast<const float*>(wts),
-                   static_cast<uint8_t*>(planes), static_cast<float*>(descale), I, S);
+                   static_cast<uint8_t*>(planes), static_cast<float*>(descale), I, S, M, gu_ksplit < 1 ? 1 : gu_ksplit);
     if (e) return e;
     CUtensorMap mw, mx;
     const uint64_t wrows = static_cast<uint64_t>(n_experts_total) * H;
     if (!tensor_map(&mw, w2, wrows, I, I, kBM, false) || !tensor_map(&mx, planes, 3 * M, VK, VK, kBN, false)) return cudaErrorInvalidValue;
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w2_s); a.ids = static_cast<const int*>(ids); a.descale = static_cast<const float*>(descale);
-    a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.ch = *ch; a.site = site; a.status = status;
+    a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.ksplit = 1; a.ch = *ch; a.site = site; a.status = status;
     return launch_tc_moe<true>(mw, mx, a, dim3(H / kBM, M), st);
 }
 

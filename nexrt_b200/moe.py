@@ -72,14 +72,18 @@ class Moe:
             # multi-row steps: experts on the tcgen05 tensor cores, each distinct expert streamed once, the
             # tensor-parallel all-reduce fused into the down projection's epilogue (csrc/tc_moe.cu)
             n_total = cfg.n_experts + 1
+            # K split of the gate/up product: two CTAs per expert tile while they all fit one wave (two per SM)
+            tiles = M * S * (2 * spec.inter // 128)
+            ks = c.moe_ksplit if tiles * c.moe_ksplit <= 2 * c.n_cta else 1
             check(
-                lib.nexrt_tc_moe_l1(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_gu), ptr(c.moe_planes1),
-                                    cfg.hidden, spec.inter, S, M, n_total, cfg.rms_eps, ptr(c.status), st),
+                lib.nexrt_tc_moe_l1(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_gu_tc), ptr(c.moe_planes1),
+                                    cfg.hidden, spec.inter, S, M, n_total, ks, cfg.rms_eps, ptr(c.status), st),
                 "tc_moe_l1",
             )
             check(
-                lib.nexrt_tc_moe_l2_allreduce(ptr(c.moe_gu), ptr(c.moe_ids), ptr(c.moe_wts), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), ptr(c.moe_planes2),
-                                              ptr(c.moe_descale), cfg.hidden, spec.inter, S, M, n_total, c.channel.ref, c.next_site(), ptr(c.status), st),
+                lib.nexrt_tc_moe_l2_allreduce(ptr(c.moe_gu_tc), ptr(c.moe_ids), ptr(c.moe_wts), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), ptr(c.moe_planes2),
+                                              ptr(c.moe_descale), cfg.hidden, spec.inter, S, M, n_total, ks, c.channel.ref, c.next_site(),
+                                              ptr(c.status), st),
                 "tc_moe_l2_allreduce",
             )
             return

@@ -77,8 +77,8 @@ _PROTOTYPES = {
     "nexrt_tc_router_logits": [vp] * 6 + [ci] * 5 + [cf, vp, vp],
     "nexrt_moe_router_topk": [vp, ci, ci, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_lmhead_sample_from_logits": [vp] * 6 + [ci] * 6 + [CH, cu, ci, vp],
-    "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 5 + [cf, vp, vp],
-    "nexrt_tc_moe_l2_allreduce": [vp] * 8 + [ci] * 5 + [CH, cu, vp, vp],
+    "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 6 + [cf, vp, vp],
+    "nexrt_tc_moe_l2_allreduce": [vp] * 8 + [ci] * 6 + [CH, cu, vp, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],
     "nexrt_ipc_get_handle": [vp, vp],
     "nexrt_ipc_open": [vp, POINTER(c_void_p)],

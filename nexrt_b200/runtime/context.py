@@ -81,6 +81,8 @@ class StepContext:
         self.moe_planes1 = torch.zeros(3 * MAX_ROWS, cfg.hidden, dtype=torch.uint8, device=device)
         self.moe_planes2 = torch.zeros(3 * MAX_ROWS, S * spec.inter, dtype=torch.uint8, device=device)
         self.moe_descale = z(MAX_ROWS)
+        self.moe_ksplit = int(os.environ.get("NEXRT_MOE_KSPLIT", "2"))              # K-split of the tcgen05 gate/up product
+        self.moe_gu_tc = z(self.moe_ksplit, MAX_ROWS, S, 2 * spec.inter)          # its partial planes
         self.wide_xn = z(MAX_ROWS, cfg.hidden)                                    # fp32 normalised rows (b/a rows of the wide GDN front)
         self.wide_ksplit = int(os.environ.get("NEXRT_WIDE_KSPLIT", "4"))                                                       # K-split of the wide front GEMMs (partials summed by the tail)
         self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts

@@ -26,6 +26,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--experts", type=int, default=512)
+    ap.add_argument("--ksplit", type=int, default=2, help="CTAs per expert row tile along K in the gate/up product")
     a = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     H, I, E, S, M = 4096, 128, a.experts, 11, a.rows
@@ -39,7 +40,7 @@ def main(argv=None) -> int:
     routings = [torch.stack([torch.cat([torch.randperm(E, device=dev, generator=g)[: S - 1], torch.tensor([E], device=dev)]) for _ in range(M)]).to(torch.int32)
                 for _ in range(a.reps + 3)]
     wts = torch.rand(M, S, device=dev, generator=g) * 0.2
-    gu = torch.zeros(M, S, 2 * I, device=dev)
+    gu = torch.zeros(a.ksplit, M, S, 2 * I, device=dev)
     p1 = torch.zeros(24, H, dtype=torch.uint8, device=dev)
     p2 = torch.zeros(24, S * I, dtype=torch.uint8, device=dev)
     ds = torch.zeros(8, device=dev)
@@ -48,10 +49,10 @@ def main(argv=None) -> int:
     lib, st = load(), torch.cuda.current_stream().cuda_stream
 
     def l1(ids):
-        check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13), ptr(w13s), ptr(ids), ptr(gu), ptr(p1), H, I, S, M, E + 1, 1e-6, ptr(status), st), "l1")
+        check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13), ptr(w13s), ptr(ids), ptr(gu), ptr(p1), H, I, S, M, E + 1, a.ksplit, 1e-6, ptr(status), st), "l1")
 
     def l2(ids):
-        check(lib.nexrt_tc_moe_l2_allreduce(ptr(gu), ptr(ids), ptr(wts), ptr(w2), ptr(w2s), ptr(x), ptr(p2), ptr(ds), H, I, S, M, E + 1, ch.ref, 0,
+        check(lib.nexrt_tc_moe_l2_allreduce(ptr(gu), ptr(ids), ptr(wts), ptr(w2), ptr(w2s), ptr(x), ptr(p2), ptr(ds), H, I, S, M, E + 1, a.ksplit, ch.ref, 0,
                                             ptr(status), st), "l2")
 
     for ids in routings[:3]:

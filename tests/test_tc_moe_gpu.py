@@ -17,8 +17,9 @@ def rel(a, b):
     return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-20))
 
 
+@pytest.mark.parametrize("ksplit", [1, 2])
 @pytest.mark.parametrize("H,I,E,S,M", [(1024, 256, 16, 5, 8), (4096, 128, 48, 11, 8), (4096, 128, 48, 11, 4), (1024, 128, 8, 3, 2)])
-def test_expert_kernels_match_fp32(H, I, E, S, M):
+def test_expert_kernels_match_fp32(H, I, E, S, M, ksplit):
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(H + I + M)
     w13 = torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.03
@@ -32,13 +33,14 @@ def test_expert_kernels_match_fp32(H, I, E, S, M):
     wts = torch.rand(M, S, device=dev, generator=g) * 0.3 + 0.05
     lib = load()
     st = torch.cuda.current_stream().cuda_stream
-    gu = torch.zeros(M, S, 2 * I, device=dev)
+    gu_planes = torch.zeros(ksplit, M, S, 2 * I, device=dev)
     planes1 = torch.zeros(3 * 8, H, dtype=torch.uint8, device=dev)
     planes2 = torch.zeros(3 * 8, S * I, dtype=torch.uint8, device=dev)
     descale = torch.zeros(8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13q), ptr(w13s), ptr(ids), ptr(gu), ptr(planes1), H, I, S, M, E + 1, 1e-6, ptr(status), st), "l1")
+    check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13q), ptr(w13s), ptr(ids), ptr(gu_planes), ptr(planes1), H, I, S, M, E + 1, ksplit, 1e-6, ptr(status), st), "l1")
     torch.cuda.synchronize()
+    gu = gu_planes.sum(0)
     xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * gamma
     w13d = dequantize_blockwise(w13q.reshape(-1, H), w13s.reshape(-1, H // 128)).reshape(E + 1, 2 * I, H)
     want_gu = torch.einsum("msrh,mh->msr", w13d[ids.long()], xn)
@@ -46,7 +48,7 @@ def test_expert_kernels_match_fp32(H, I, E, S, M):
     # down projection + (single-rank) all-reduce + residual
     ch = LLChannel(dev, 1, 0, 8 * H)
     xres = x.clone()
-    check(lib.nexrt_tc_moe_l2_allreduce(ptr(gu), ptr(ids), ptr(wts), ptr(w2q), ptr(w2s), ptr(xres), ptr(planes2), ptr(descale), H, I, S, M, E + 1,
+    check(lib.nexrt_tc_moe_l2_allreduce(ptr(gu_planes), ptr(ids), ptr(wts), ptr(w2q), ptr(w2s), ptr(xres), ptr(planes2), ptr(descale), H, I, S, M, E + 1, ksplit,
                                         ch.ref, 0, ptr(status), st), "l2")
     torch.cuda.synchronize()
     h = torch.nn.functional.silu(gu[..., :I]) * gu[..., I:] * wts[..., None]
