@@ -93,7 +93,7 @@ def main() -> int:
     prefill_s = time.time() - t0
     state = eng.export_state()
     g = eng.capture(1)
-    nodes_per_step = 1 + 6 * cfg.n_layers + 2
+    nodes_per_step = 1 + 6 * cfg.n_layers + 4   # embed, 6 kernels per layer, lm_head (split + tcgen05 logits GEMM + select), step end
 
     # ---- kernel-timed: K captured-graph replays on the device
     for _ in range(W):

@@ -27,7 +27,7 @@ class Head:
         self.ctx, self.w = ctx, w
         self.logits: Optional[torch.Tensor] = None
         self.wide_logits: Optional[torch.Tensor] = None
-        self.tc_rows = int(os.environ.get("NEXRT_TC_HEAD_ROWS", "4")) or 1 << 30
+        self.tc_rows = int(os.environ.get("NEXRT_TC_HEAD_ROWS", "1")) or 1 << 30   # the logits GEMM pays off from one row (254 MB of bf16 weights per rank)
         if init_sampling:
             self.set_sampling_config(0, *GREEDY)
 

@@ -67,7 +67,9 @@ def main() -> None:
         if a.leave_one_out:
             real = eng.ctx.lib
             for name in ("nexrt_gdn_front", "nexrt_gdn_core", "nexrt_attn_front", "nexrt_attn_decode", "nexrt_oproj_allreduce", "nexrt_moe_router",
-                         "nexrt_moe_l1", "nexrt_moe_l2_allreduce", "nexrt_lmhead_sample"):
+                         "nexrt_moe_l1", "nexrt_moe_l2_allreduce", "nexrt_lmhead_sample", "nexrt_rows_norm_split", "nexrt_tc_rows_gemm",
+                         "nexrt_gdn_front_tail", "nexrt_tc_router_logits", "nexrt_moe_router_topk", "nexrt_tc_moe_l1", "nexrt_tc_moe_l2_allreduce",
+                         "nexrt_lmhead_sample_from_logits"):
                 eng.ctx.lib = _Without(real, name)
                 eng.graphs.clear()
                 t = bench_graph(eng.capture(a.rows), a.steps, warmup=5, device=dev)["ms_per_replay"] * 1e3
