@@ -19,6 +19,7 @@ from typing import Optional
 
 import torch
 
+from .ops import wide
 from .ops.lib import check, ptr
 from .runtime.context import StepContext
 
@@ -62,6 +63,10 @@ class FullAttn:
             "attn_decode",
         )
         n_cta = c.n_cta
+        if wide.oproj_is_wide(c, spec.attn_local, M):
+            wide.oproj_allreduce(c, c.attn_out, c.gate, None, self.w["out_w"], self.w["out_s"], spec.attn_local, M, 2 if use_cp else 0, cfg.head_dim,
+                                 c.cp_channel.ref if use_cp else None, cp_site)
+            return
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.attn_out), ptr(c.gate), None, ptr(self.w["out_w"]), ptr(self.w["out_s"]), ptr(c.x), cfg.hidden, spec.attn_local, M,

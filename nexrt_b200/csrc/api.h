@@ -140,6 +140,12 @@ int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* l
 int nexrt_lmhead_sample_from_logits(const void* logits_in, void* cand, void* ticket, const void* sampling, void* ctl, void* export_buf, int H, int V_local,
                                     int vocab_base, int M, int mode, int arg, const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
 
+// Wide out-projection (multi-row steps): staging + split into planes, then tcgen05 GEMM with all-reduce epilogue.
+int nexrt_oproj_stage_split(const void* in, const void* z, const void* gnorm_w, void* planes, void* descale, int K, int M, int mode, float eps, int hd,
+                            const NexrtLLChannel* cp, unsigned int cp_site, void* stream);
+int nexrt_tc_oproj_allreduce(const void* planes, const void* descale, const void* w, const void* w_s, void* x, const void* zero_ids, int H, int K, int M,
+                             int overwrite, const NexrtLLChannel* ch, unsigned int site, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

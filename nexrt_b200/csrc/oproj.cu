@@ -202,9 +202,77 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
     allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x, a.overwrite == 0);
 }
 
+// Staging half of the wide out-projection (multi-row steps): one CTA per token row builds the projection's input
+// (mode 0 plain copy, 1 GDN gated RMSNorm with z, 2 context-parallel merge of the group's partials) and writes it as
+// three e4m3 planes [3M][K] plus a power-of-two scale per row - the B operand of the tcgen05 GEMM that follows
+// (nexrt_tc_oproj_allreduce in tc_moe.cu), which also does the all-reduce and the residual.
+__global__ void __launch_bounds__(256) oproj_stage_split_kernel(OProjArgs a, uint8_t* planes, float* descale_out) {
+    extern __shared__ __align__(16) float xs[];          // [K]
+    __shared__ float red[32];
+    __shared__ float ds[1];
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int m = blockIdx.x;
+    pdl_wait();
+    if (a.mode == 0) {
+        for (int idx = threadIdx.x * 4; idx < a.K; idx += blockDim.x * 4)
+            *reinterpret_cast<float4*>(xs + idx) = *reinterpret_cast<const float4*>(a.in + static_cast<size_t>(m) * a.K + idx);
+    } else if (a.mode == 1) {
+        const int heads = a.K / 128;
+        const float4 gw = *reinterpret_cast<const float4*>(a.gnorm_w + lane * 4);
+        for (int h = warp; h < heads; h += nwarps) {
+            const size_t base = static_cast<size_t>(m) * a.K + h * 128 + lane * 4;
+            const float4 o = *reinterpret_cast<const float4*>(a.in + base);
+            const float4 zz = *reinterpret_cast<const float4*>(a.z + base);
+            const float inv = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) / 128.f + a.eps);
+            *reinterpret_cast<float4*>(xs + h * 128 + lane * 4) =
+                make_float4(gw.x * o.x * inv * silu_f(zz.x), gw.y * o.y * inv * silu_f(zz.y), gw.z * o.z * inv * silu_f(zz.z), gw.w * o.w * inv * silu_f(zz.w));
+        }
+    } else {
+        const LLCall cpcall = ll_begin(a.cp, a.cp_site);
+        const int hd = a.hd, heads = a.K / hd;
+        for (int k = threadIdx.x; k < a.K; k += blockDim.x) {
+            const int lh = k / hd, d = k % hd;
+            const unsigned int base = (static_cast<unsigned int>(m) * heads + lh) * (hd + 1);
+            float lse[kMaxWorld], ctx[kMaxWorld], mx = -INFINITY;
+            for (int sr = 0; sr < a.cp.world; ++sr) {
+                unsigned int pl, pc;
+                ll_wait(a.cp, cpcall, sr, base + hd, &pl, kStatusCpTimeout);
+                ll_wait(a.cp, cpcall, sr, base + d, &pc, kStatusCpTimeout);
+                lse[sr] = __uint_as_float(pl);
+                ctx[sr] = __uint_as_float(pc);
+                mx = fmaxf(mx, lse[sr]);
+            }
+            float num = 0.f, den = 0.f;
+            for (int sr = 0; sr < a.cp.world; ++sr) {
+                const float wgt = lse[sr] == -INFINITY ? 0.f : exp2f(lse[sr] - mx);
+                num = fmaf(wgt, ctx[sr], num);
+                den += wgt;
+            }
+            xs[k] = (den > 0.f ? num / den : 0.f) * sigmoid_f(a.z[static_cast<size_t>(m) * a.K + k]);
+        }
+    }
+    __syncthreads();
+    act_split<3>(planes + static_cast<size_t>(m) * 3 * a.K, xs, 1, a.K, red, ds);
+    if (threadIdx.x == 0) descale_out[m] = ds[0];
+}
+
 }  // namespace nexrt
 
 using namespace nexrt;
+
+extern "C" int nexrt_oproj_stage_split(const void* in, const void* z, const void* gnorm_w, void* planes, void* descale, int K, int M, int mode, float eps,
+                                       int hd, const NexrtLLChannel* cp, unsigned int cp_site, void* stream) {
+    mode &= 3;
+    if (M < 1 || M > kMaxRows || K % 128 || mode < 0 || mode > 2) return cudaErrorInvalidValue;
+    if (mode == 2 && (cp == nullptr || hd <= 0 || K % hd)) return cudaErrorInvalidValue;
+    OProjArgs a{};
+    a.in = static_cast<const float*>(in); a.z = static_cast<const float*>(z); a.gnorm_w = static_cast<const float*>(gnorm_w);
+    a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.eps = eps;
+    if (cp) { a.cp = *cp; a.cp_site = cp_site; }
+    return launch(oproj_stage_split_kernel, dim3(M), dim3(256), sizeof(float) * K, static_cast<cudaStream_t>(stream), a, static_cast<uint8_t*>(planes),
+                  static_cast<float*>(descale));
+}
 
 extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, const void* w, const void* s, void* x, int H, int K,
                                      int M, int mode, float eps, int hd, const NexrtLLChannel* ch, unsigned int site,

@@ -45,6 +45,7 @@ struct TcMoeArgs {
     __nv_bfloat16* x;       // [M][H] residual stream (down projection only)
     int H, I, S, M;
     int n_total;            // experts in the weight matrix (routed + shared); ids are clamped into [0, n_total)
+    int overwrite;          // shared down projection: write the reduced sum instead of adding it to x
     int ksplit;             // gate/up and plain GEMM: CTAs per row tile along K (partial planes [ksplit][M][S][rows])
     LLChannel ch;
     unsigned int site;
@@ -57,7 +58,8 @@ struct TcMoeArgs {
 // Four shared-memory stages and EIGHT tensor-memory accumulator buffers, two CTAs per SM: what bounds one CTA's K walk is
 // the round trip commit -> epilogue wakes -> tcgen05.ld -> buffer released -> issuer wakes (about 2 us on B200), so the
 // number of K blocks in flight is what sets the rate; 8 buffers x 32 columns x 2 CTAs use all 512 TMEM columns.
-template <bool DOWN, bool BF16 = false>
+// SHARED = true (with DOWN): one weight matrix for all rows (out-projection): the epilogue all-reduces every row.
+template <bool DOWN, bool BF16 = false, bool SHARED = false>
 __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcMoeArgs a) {
     constexpr int NS = 4;                // shared-memory stages
     constexpr int NAB = 8;               // accumulator buffers in tensor memory
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     } else {
         const int q = warp & 3;
         const int row = mt * kBM + 32 * q + lane;        // row inside the expert's matrix
-        constexpr int NC = DOWN ? 4 : kBN;               // columns this thread accumulates
+        constexpr int NC = (DOWN && !SHARED) ? 4 : kBN;   // columns this thread accumulates
         float acc[NC];
 #pragma unroll
         for (int n = 0; n < NC; ++n) acc[n] = 0.f;
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * kBN;
             const float w = BF16 ? 1.f : s_wscale[kb];
-            if (DOWN) {
+            if (DOWN && !SHARED) {
                 float p[4];
                 tmem_ld4(taddr + 3 * m, p);
                 tmem_ld_wait();
@@ -200,7 +202,19 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
             if (lane == 0) mbar_arrive(tempty(buf));
         }
         if (ok && active) {
-            if (DOWN) {
+            if (DOWN && SHARED) {
+                LLCall call{0u, 0u};
+                if (a.ch.world > 1) call = ll_begin(a.ch, a.site);
+#pragma unroll
+                for (int m2 = 0; m2 < kMaxRows; ++m2) {
+                    if (m2 < a.M) {
+                        const float val = (acc[3 * m2] + acc[3 * m2 + 1] * (1.f / 16.f) + acc[3 * m2 + 2] * (1.f / 256.f)) * a.descale[m2];
+                        const size_t o = static_cast<size_t>(m2) * a.H + row;
+                        const float sum = ll_allreduce_f32(a.ch, call, static_cast<unsigned int>(o), val);
+                        a.x[o] = __float2bfloat16_rn(a.overwrite ? sum : __bfloat162float(a.x[o]) + sum);
+                    }
+                }
+            } else if (DOWN) {
                 const float val = (acc[0] + acc[1] * (1.f / 16.f) + acc[2] * (1.f / 256.f)) * a.descale[m];
                 LLCall call{0u, 0u};
                 if (a.ch.world > 1) call = ll_begin(a.ch, a.site);
@@ -288,10 +302,10 @@ __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restri
     if (threadIdx.x == 0) descale[m] = ds[0];
 }
 
-template <bool DOWN, bool BF16 = false>
+template <bool DOWN, bool BF16 = false, bool SHARED = false>
 int launch_tc_moe(const CUtensorMap& mw, const CUtensorMap& mx, const TcMoeArgs& a, dim3 grid, cudaStream_t st) {
     static bool configured = false;
-    auto kern = tc_moe_kernel<DOWN, BF16>;
+    auto kern = tc_moe_kernel<DOWN, BF16, SHARED>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(DOWN));
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -379,6 +393,21 @@ int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, 
     a.w_s = static_cast<const float*>(w2_s); a.ids = static_cast<const int*>(ids); a.descale = static_cast<const float*>(descale);
     a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.ksplit = 1; a.ch = *ch; a.site = site; a.status = status;
     return launch_tc_moe<true>(mw, mx, a, dim3(H / kBM, M), st);
+}
+
+// Wide out-projection: x[m] (+)= all-reduce(W * in[m]) for M rows; planes / descale come from nexrt_oproj_stage_split.
+// W [H][K] e4m3 with block scales w_s [H/128][K/128]; zero_ids: M zero int32 words.
+int nexrt_tc_oproj_allreduce(const void* planes, const void* descale, const void* w, const void* w_s, void* x, const void* zero_ids, int H, int K, int M,
+                             int overwrite, const NexrtLLChannel* ch, unsigned int site, int* status, void* stream) {
+    if (M < 1 || M > kMaxRows || H % 128 || K % 128 || K > 8192 || ch == nullptr) return cudaErrorInvalidValue;
+    if (ch->world > 1 && ch->slots < static_cast<unsigned int>(kMaxRows) * H) return cudaErrorInvalidValue;
+    CUtensorMap mw, mx;
+    if (!tensor_map(&mw, w, H, K, K, kBM, false) || !tensor_map(&mx, planes, 3 * M, K, K, kBN, false)) return cudaErrorInvalidValue;
+    TcMoeArgs a{};
+    a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.descale = static_cast<const float*>(descale);
+    a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = K; a.S = 1; a.M = M; a.n_total = 1; a.ksplit = 1; a.overwrite = overwrite ? 1 : 0;
+    a.ch = *ch; a.site = site; a.status = status;
+    return launch_tc_moe<true, false, true>(mw, mx, a, dim3(H / kBM, 1), static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -14,6 +14,7 @@ import torch
 
 import os
 
+from .ops import wide
 from .ops.lib import check, ptr
 from .runtime.context import StepContext
 
@@ -84,6 +85,9 @@ class Gdn:
             "gdn_core",
         )
         n_cta = c.n_cta
+        if wide.oproj_is_wide(c, spec.gdn_local, M):
+            wide.oproj_allreduce(c, c.gdn_out, c.gdn_z, w["gnorm_w"], w["out_w"], w["out_s"], spec.gdn_local, M, 1, 128, None, 0)
+            return
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.gdn_out), ptr(c.gdn_z), ptr(w["gnorm_w"]), ptr(w["out_w"]), ptr(w["out_s"]), ptr(c.x), cfg.hidden, spec.gdn_local,

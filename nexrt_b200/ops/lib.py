@@ -77,6 +77,8 @@ _PROTOTYPES = {
     "nexrt_tc_router_logits": [vp] * 6 + [ci] * 5 + [cf, vp, vp],
     "nexrt_moe_router_topk": [vp, ci, ci, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_lmhead_sample_from_logits": [vp] * 6 + [ci] * 6 + [CH, cu, ci, vp],
+    "nexrt_oproj_stage_split": [vp] * 5 + [ci, ci, ci, cf, ci, CH, cu, vp],
+    "nexrt_tc_oproj_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, vp, vp],
     "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 6 + [cf, vp, vp],
     "nexrt_tc_moe_l2_allreduce": [vp] * 8 + [ci] * 6 + [CH, cu, vp, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],

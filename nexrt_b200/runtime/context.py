@@ -87,6 +87,9 @@ class StepContext:
         self.wide_ksplit = int(os.environ.get("NEXRT_WIDE_KSPLIT", "4"))                                                       # K-split of the wide front GEMMs (partials summed by the tail)
         self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts
         self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
+        self.oproj_planes = torch.zeros(3 * MAX_ROWS, max(spec.gdn_local, spec.attn_local), dtype=torch.uint8, device=device)
+        self.oproj_descale = z(MAX_ROWS)
+        self.tc_oproj_rows = int(os.environ.get("NEXRT_TC_OPROJ_ROWS", "4")) or 1 << 30
         self.router_ksplit = 8
         self.router_planes = torch.zeros(2 * MAX_ROWS, cfg.hidden, dtype=torch.bfloat16, device=device)
         self.router_partial = z(self.router_ksplit, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)

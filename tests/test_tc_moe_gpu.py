@@ -58,3 +58,33 @@ def test_expert_kernels_match_fp32(H, I, E, S, M, ksplit):
     assert int(status.item()) == 0
     assert rel(xres.float() - x.float(), y) < 6e-2, rel(xres.float() - x.float(), y)       # bf16 rounding of x + y dominates
     assert (xres.float() - want.float()).abs().max() <= 2 * torch.finfo(torch.bfloat16).eps * want.float().abs().max()
+
+
+@pytest.mark.parametrize("mode,K,M", [(0, 1024, 8), (1, 1024, 4), (1, 512, 8), (0, 2048, 5)])
+def test_wide_out_projection_matches_the_fused_kernel(mode, K, M):
+    """Staging + tcgen05 GEMM with the all-reduce epilogue against the fused mma.sync out-projection kernel."""
+    dev = torch.device("cuda", 0)
+    H = 1024
+    g = torch.Generator(device=dev).manual_seed(K + M + mode)
+    wq, ws = quantize_blockwise(torch.randn(H, K, device=dev, generator=g) * 0.03)
+    inp = torch.randn(8, K, device=dev, generator=g)
+    z = torch.randn(8, K, device=dev, generator=g)
+    gnorm = 1 + 0.1 * torch.randn(128, device=dev, generator=g)
+    x0 = torch.randn(8, H, device=dev, generator=g).to(torch.bfloat16)
+    lib, st = load(), torch.cuda.current_stream().cuda_stream
+    ch = LLChannel(dev, 1, 0, 8 * H)
+    x_ref = x0.clone()
+    check(lib.nexrt_oproj_allreduce(ptr(inp), ptr(z), ptr(gnorm), ptr(wq), ptr(ws), ptr(x_ref), H, K, M, mode, 1e-6, 128, ch.ref, 0, None, 0, 148, st), "fused")
+    x_new = x0.clone()
+    planes = torch.zeros(24, K, dtype=torch.uint8, device=dev)
+    descale = torch.zeros(8, device=dev)
+    zero = torch.zeros(8, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    check(lib.nexrt_oproj_stage_split(ptr(inp), ptr(z), ptr(gnorm), ptr(planes), ptr(descale), K, M, mode, 1e-6, 128, None, 0, st), "stage")
+    check(lib.nexrt_tc_oproj_allreduce(ptr(planes), ptr(descale), ptr(wq), ptr(ws), ptr(x_new), ptr(zero), H, K, M, 0, ch.ref, 1, ptr(status), st), "wide")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(x_new[M:], x0[M:])                                  # rows beyond M untouched
+    d_ref, d_new = x_ref[:M].float() - x0[:M].float(), x_new[:M].float() - x0[:M].float()
+    assert rel(d_new, d_ref) < 3e-2                                       # both are bf16-rounded sums of the same fp32 result
+    assert (x_new[:M].float() - x_ref[:M].float()).abs().max() <= 2 * torch.finfo(torch.bfloat16).eps * x_ref[:M].float().abs().max()
