@@ -89,7 +89,7 @@ class StepContext:
         self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
         self.oproj_planes = torch.zeros(3 * MAX_ROWS, max(spec.gdn_local, spec.attn_local), dtype=torch.uint8, device=device)
         self.oproj_descale = z(MAX_ROWS)
-        self.tc_oproj_rows = int(os.environ.get("NEXRT_TC_OPROJ_ROWS", "4")) or 1 << 30
+        self.tc_oproj_rows = int(os.environ.get("NEXRT_TC_OPROJ_ROWS", "0")) or 1 << 30   # measured no faster than the fused kernel at 4 and 8 rows: off unless asked for
         self.router_ksplit = 8
         self.router_planes = torch.zeros(2 * MAX_ROWS, cfg.hidden, dtype=torch.bfloat16, device=device)
         self.router_partial = z(self.router_ksplit, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)
