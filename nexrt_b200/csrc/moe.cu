@@ -301,12 +301,27 @@ __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ks
     pdl_launch_dependents();
     pdl_wait();
     const int rows = a.E + 1;
-    for (int idx = threadIdx.x; idx < a.M * rows; idx += blockDim.x) {
-        const int m = idx / rows, e = idx % rows;
-        float t = 0.f;
-        for (int ks = 0; ks < ksplit; ++ks) t += __ldcg(a.partial + (static_cast<size_t>(ks) * a.M + m) * a.rows_pad + e);
-        lg_s[idx] = t;
-        a.logits[idx] = t;
+    // four consecutive experts per thread, every K-split plane of them requested before the first add (16-byte
+    // loads, all in flight): the sum is one or two round trips to L2
+    const int quads = a.rows_pad / 4;
+    for (int q = threadIdx.x; q < a.M * quads; q += blockDim.x) {
+        const int m = q / quads, e0 = (q % quads) * 4;
+        float4 v[16];
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks)
+            v[ks] = ks < ksplit ? __ldcg(reinterpret_cast<const float4*>(a.partial + (static_cast<size_t>(ks) * a.M + m) * a.rows_pad + e0))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 t = v[0];
+#pragma unroll
+        for (int ks = 1; ks < 16; ++ks)
+            if (ks < ksplit) { t.x += v[ks].x; t.y += v[ks].y; t.z += v[ks].z; t.w += v[ks].w; }
+        const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (e0 + i < rows) {
+                lg_s[m * rows + e0 + i] = tv[i];
+                a.logits[m * rows + e0 + i] = tv[i];
+            }
     }
     __syncthreads();
     router_topk<true>(a, lg_s);
@@ -424,7 +439,7 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
 }
 
 extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream) {
-    if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1) return cudaErrorInvalidValue;
+    if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1 || ksplit > 16 || rows_pad % 4) return cudaErrorInvalidValue;
     RouterArgs a{nullptr, nullptr, nullptr, static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), nullptr, 0, E, topk, M, 0.f,
                  const_cast<float*>(static_cast<const float*>(partial)), rows_pad};
     return launch(moe_topk_rows_kernel, dim3(1), dim3(256), sizeof(float) * M * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit);
