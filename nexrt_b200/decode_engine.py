@@ -28,7 +28,10 @@ from .ops.lib import check, ptr
 from .runtime.context import StepContext
 from .runtime.control import CTL_WORDS, Ctl, decode_ctl
 
-CP_THRESHOLD = int(os.environ.get("NEXRT_CP_THRESHOLD", str(48 * 1024)))  # reference decode_engine.py:63-66
+# Context length from which generate() switches to the context-parallel graph.  The reference crosses over at 48K on
+# H100 (decode_engine.py:63-66); on 8 x B200 the non-CP arm measured faster at 64K (3248 vs 3800 us per token) and at
+# 256K (3735 vs 4383 us), so by default the CP arm is only taken beyond the model's 256K context, i.e. when asked for.
+CP_THRESHOLD = int(os.environ.get("NEXRT_CP_THRESHOLD", str(512 * 1024)))
 WARMUP_STEPS = 3
 
 
