@@ -40,7 +40,7 @@ def parse_args():
 
 
 def reference_arm(args) -> int:
-    why = ("reference cannot run here: pip install of /root/reference fails (flat layout, run-from-source project); "
+    why = ("reference cannot run here: pip install of the reference tree fails (flat layout, run-from-source project); "
            "its kernels target sm_90a wgmma (absent on sm_100a) and it needs the real checkpoint, SGLang and TP=8 NVLS")
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}))

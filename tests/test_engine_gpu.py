@@ -63,7 +63,7 @@ def test_multi_row_step_matches_sequential(setup, rows):
 
 
 def test_greedy_decode_config1(setup):
-    """BASELINE config 1 shape: random prompt, greedy decode, logits checked against fp32."""
+    """Random prompt, greedy decode, logits checked against the fp32 oracle (the shrunk two-layer configuration)."""
     cfg, ref, eng = setup
     prompt = synthetic_prompt(cfg.vocab, 64, seed=1)
     ref.reset()
