@@ -15,6 +15,8 @@ the whole context (``attn.py:71-75,305-306``); ``cache_len`` may be shrunk for t
 
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -32,6 +34,8 @@ class FullAttn:
         shape = (spec.kv_heads, self.cache_len, cfg.head_dim)
         self.k_cache = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+        # rows from which the front projection runs as one tcgen05 GEMM (NEXRT_TC_ATTN_ROWS=0 switches it off)
+        self.tc_rows = int(os.environ.get("NEXRT_TC_ATTN_ROWS", "8")) or 1 << 30   # no gain measured at 4 rows
 
     def reset(self) -> None:
         pass  # rows beyond committed_len are never read
@@ -45,6 +49,21 @@ class FullAttn:
         use_cp = cp and c.cp_channel is not None and self.cp_w is not None
         w = self.cp_w if use_cp else self.w
         nq = spec.q_heads * (spec.cp_size if use_cp else 1)
+        R = (nq + spec.q_heads + 2 * spec.kv_heads) * cfg.head_dim
+        if M >= self.tc_rows and R % 128 == 0 and cfg.hidden % 256 == 0 and cfg.hidden <= 4096:
+            # multi-row steps: the q|gate|k|v projection of all rows is one tcgen05 GEMM, a tail kernel scatters it
+            check(lib.nexrt_rows_norm_split(ptr(c.x), ptr(self.w["in_ln"]), ptr(c.moe_planes1), None, cfg.hidden, M, cfg.rms_eps, st), "rows_norm_split")
+            check(lib.nexrt_tc_rows_gemm(ptr(w["front_w"]), ptr(w["front_s"]), ptr(c.moe_planes1), ptr(c.wide_pre), ptr(c.zero_ids), R, cfg.hidden, M,
+                                         c.wide_ksplit, ptr(c.status), st), "tc_rows_gemm")
+            check(lib.nexrt_attn_front_tail(ptr(c.wide_pre), ptr(ctl), ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw), ptr(self.v_cache), cfg.head_dim, nq,
+                                            spec.q_heads, spec.kv_heads, M, self.cache_len, c.wide_ksplit, st), "attn_front_tail")
+        else:
+            self._front_fused(M, w, nq, ctl)
+        self._rest(M, use_cp, nq, ctl)
+
+    def _front_fused(self, M, w, nq, ctl) -> None:
+        c, lib = self.ctx, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
         check(
             lib.nexrt_attn_front(
                 ptr(c.x), ptr(self.w["in_ln"]), ptr(w["front_w"]), ptr(w["front_s"]), ptr(ctl), ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw),
@@ -52,6 +71,10 @@ class FullAttn:
             ),
             "attn_front",
         )
+
+    def _rest(self, M, use_cp, nq, ctl) -> None:
+        c, lib = self.ctx, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
         cp_site = c.next_site() if use_cp else 0
         check(
             lib.nexrt_attn_decode(

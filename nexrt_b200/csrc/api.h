@@ -146,6 +146,9 @@ int nexrt_oproj_stage_split(const void* in, const void* z, const void* gnorm_w, 
 int nexrt_tc_oproj_allreduce(const void* planes, const void* descale, const void* w, const void* w_s, void* x, const void* zero_ids, int H, int K, int M,
                              int overwrite, const NexrtLLChannel* ch, unsigned int site, int* status, void* stream);
 
+int nexrt_attn_front_tail(const void* pre, const void* ctl, void* q_raw, void* gate, void* k_raw, void* v_cache, int hd, int nq, int ngate, int kvh, int M,
+                          int cache_len, int ksplit, void* stream);   /* pre: [ksplit][M][R] partial planes of the rows GEMM */
+
 #ifdef __cplusplus
 }
 #endif

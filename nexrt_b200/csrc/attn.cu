@@ -157,6 +157,22 @@ struct AttnDecodeArgs {
     unsigned long long* events;   // optional timing ring: split 0 records phases 0..5, the combining CTA 6..9
 };
 
+// Tail of the wide front (multi-row steps): the projections of all rows come from the tcgen05 rows GEMM as K-split
+// partial planes pre[ks][M][R]; one thread per weight row adds them in order and scatters the row's M values.
+__global__ void __launch_bounds__(256) attn_front_tail_kernel(AttnFrontArgs a, const float* __restrict__ pre, int R, int ksplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= R) return;
+    const int C0 = a.ctl[kCtlCommittedLen];
+    const bool interleaved = a.ngate == a.nq;
+    for (int m = 0; m < a.M; ++m) {
+        float v = 0.f;
+        for (int ks = 0; ks < ksplit; ++ks) v += pre[(static_cast<size_t>(ks) * a.M + m) * R + row];
+        attn_front_row(a, row, m, v, C0, interleaved);
+    }
+}
+
 constexpr int kRowsPerPass = 4;
 constexpr int kMinKeysPerSplit = 128;   // short contexts stay on few CTAs: the combine's cost grows with the split count
 
@@ -491,6 +507,15 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
 }  // namespace nexrt
 
 using namespace nexrt;
+
+extern "C" int nexrt_attn_front_tail(const void* pre, const void* ctl, void* q_raw, void* gate, void* k_raw, void* v_cache, int hd, int nq, int ngate, int kvh,
+                                     int M, int cache_len, int ksplit, void* stream) {
+    if (M < 1 || M > kMaxRows || ksplit < 1) return cudaErrorInvalidValue;
+    AttnFrontArgs a{nullptr, nullptr, nullptr, nullptr, static_cast<const int*>(ctl), static_cast<float*>(q_raw), static_cast<float*>(gate),
+                    static_cast<float*>(k_raw), static_cast<__nv_bfloat16*>(v_cache), 0, hd, nq, ngate, kvh, M, cache_len, 0.f};
+    const int R = (nq + ngate + 2 * kvh) * hd;
+    return launch(attn_front_tail_kernel, dim3((R + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), a, static_cast<const float*>(pre), R, ksplit);
+}
 
 extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void* s, const void* ctl, void* q_raw, void* gate,
                                 void* k_raw, void* v_cache, int H, int hd, int nq, int ngate, int kvh, int M, int cache_len, float eps,

@@ -79,6 +79,7 @@ _PROTOTYPES = {
     "nexrt_lmhead_sample_from_logits": [vp] * 6 + [ci] * 6 + [CH, cu, ci, vp],
     "nexrt_oproj_stage_split": [vp] * 5 + [ci, ci, ci, cf, ci, CH, cu, vp],
     "nexrt_tc_oproj_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, vp, vp],
+    "nexrt_attn_front_tail": [vp] * 6 + [ci] * 7 + [vp],
     "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 6 + [cf, vp, vp],
     "nexrt_tc_moe_l2_allreduce": [vp] * 8 + [ci] * 6 + [CH, cu, vp, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],

@@ -85,7 +85,8 @@ class StepContext:
         self.moe_gu_tc = z(self.moe_ksplit, MAX_ROWS, S, 2 * spec.inter)          # its partial planes
         self.wide_xn = z(MAX_ROWS, cfg.hidden)                                    # fp32 normalised rows (b/a rows of the wide GDN front)
         self.wide_ksplit = int(os.environ.get("NEXRT_WIDE_KSPLIT", "4"))                                                       # K-split of the wide front GEMMs (partials summed by the tail)
-        self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows))  # projections of the wide fronts
+        cp_front_rows = (spec.q_heads * spec.cp_size + spec.q_heads + 2 * spec.kv_heads) * cfg.head_dim
+        self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows, cp_front_rows))  # projections of the wide fronts
         self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
         self.oproj_planes = torch.zeros(3 * MAX_ROWS, max(spec.gdn_local, spec.attn_local), dtype=torch.uint8, device=device)
         self.oproj_descale = z(MAX_ROWS)
