@@ -65,7 +65,7 @@ int nexrt_oproj_allreduce(const void* in, const void* z, const void* gnorm_w, co
 /* w holds E+1 rows; if it is padded with zero rows to rows_pad (a multiple of 16) and `partial`
  * ([4][M][rows_pad] floats) is given, the tensor-core form runs. */
 int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket, void* partial,
-                     int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* stream);
+                     int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* planes, void* stream);   /* planes: optional e4m3 [3M][H] for the tcgen05 experts */
 int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I, int S, int M,
                  float eps, int shared_expert, int n_cta, void* stream);
 int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I, int S,
@@ -118,7 +118,7 @@ int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, floa
 // ---- experts of a multi-row step on tcgen05 (tc_moe.cu) -------------------------------------------------------
 // Gate/up of every distinct expert named in ids [M][S] (streamed once each); planes is e4m3 scratch [3M][H].
 int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, void* planes, int H, int I, int S,
-                    int M, int n_experts_total, int ksplit, float eps, int* status, void* stream);   /* gu: [ksplit][M][S][2I] partial planes */
+                    int M, int n_experts_total, int ksplit, float eps, int planes_ready, int* status, void* stream);   /* gu: [ksplit][M][S][2I] partial planes */
 // Down projection over each row's S experts + tensor-parallel all-reduce + residual in one kernel; planes is e4m3
 // scratch [3M][S*I], descale fp32 scratch [M].
 int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, void* planes, void* descale,
@@ -134,7 +134,7 @@ int nexrt_gdn_front_tail(const void* pre, const void* xn, const void* ba_w, cons
                          void* stream);
 
 int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void* planes, void* partial, const void* zero_ids, int rows, int rows_pad, int K,
-                           int M, int ksplit, float eps, int* status, void* stream);   /* partial: [ksplit][M][rows_pad] */
+                           int M, int ksplit, float eps, void* planes_e4m3, int* status, void* stream);   /* partial: [ksplit][M][rows_pad] */
 int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream);
 
 int nexrt_lmhead_sample_from_logits(const void* logits_in, void* cand, void* ticket, const void* sampling, void* ctl, void* export_buf, int H, int V_local,

@@ -38,6 +38,7 @@ struct RouterArgs {
     float eps;
     float* partial;           // tensor-core form: [4 k-quarters][M][rows_pad]
     int rows_pad;             // rows of w padded to a multiple of 16 (0: not padded)
+    uint8_t* planes;          // optional [3M][H] e4m3: the normalised rows split for the tcgen05 expert kernels (CTA m writes row m)
 };
 
 // Top-k of every token row by the calling CTA: warp m owns row m, lane holds logits lane,
@@ -249,6 +250,10 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
         const int mb = min(MP, a.M - m0);
         if (m0) { __syncthreads(); mw.preloaded = false; }
         norm.template run<3>(nullptr, xs, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
+        // the expert kernels of a multi-row step take the same normalised rows as three e4m3 planes: CTA m0 + m
+        // writes row m0 + m's, which saves them a kernel of their own
+        if (a.planes != nullptr && static_cast<int>(blockIdx.x) >= m0 && static_cast<int>(blockIdx.x) < m0 + mb)
+            split_rows<3>(a.planes + static_cast<size_t>(blockIdx.x) * 3 * a.H, xs + static_cast<size_t>(blockIdx.x - m0) * a.H, 1, a.H, kSplitScale);
         split_bf16_rows(xh, xs, mb, a.H);
         float d[4];
         mw.run(xh, mb * 2, d);
@@ -418,11 +423,11 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
 using namespace nexrt;
 
 extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* logits, void* ids, void* wts, void* ticket,
-                                void* partial, int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* stream) {
+                                void* partial, int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* planes, void* stream) {
     if (M < 1 || M > kMaxRows || H % 256 || E > 512 || topk < 1 || topk > 31 || topk > E) return cudaErrorInvalidValue;
     RouterArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const __nv_bfloat16*>(w),
                  static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), static_cast<int*>(ticket), H, E, topk, M, eps,
-                 static_cast<float*>(partial), rows_pad};
+                 static_cast<float*>(partial), rows_pad, static_cast<uint8_t*>(planes)};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if ((gemv_mode() & 16) && partial != nullptr && rows_pad >= E + 1 && rows_pad % 16 == 0 && H % 1024 == 0 && H <= 4096) {
         const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
@@ -432,6 +437,7 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
         if (mp == 2) return launch(moe_router_mma_kernel<2>, g, b, smem_mma, st, a);
         return launch(moe_router_mma_kernel<4>, g, b, smem_mma, st, a);
     }
+    if (planes != nullptr) return cudaErrorInvalidValue;   // only the tensor-core router writes the planes
     const int mb = M == 1 ? 1 : 4;
     const size_t smem = sizeof(float) * (static_cast<size_t>(mb + 1) * H + gemv_part_floats((E + 1 + n_cta - 1) / n_cta, mb, gemv_geom(H / 8, gemv_threads())));
     if (M == 1) return launch(moe_router_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
@@ -441,7 +447,7 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
 extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream) {
     if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1 || ksplit > 16 || rows_pad % 4) return cudaErrorInvalidValue;
     RouterArgs a{nullptr, nullptr, nullptr, static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), nullptr, 0, E, topk, M, 0.f,
-                 const_cast<float*>(static_cast<const float*>(partial)), rows_pad};
+                 const_cast<float*>(static_cast<const float*>(partial)), rows_pad, nullptr};
     return launch(moe_topk_rows_kernel, dim3(1), dim3(256), sizeof(float) * M * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit);
 }
 
@@ -514,7 +520,7 @@ extern "C" int nexrt_moe_router_noalloc(const void* x, const void* post_ln, cons
     e = cudaMemsetAsync(ticket, 0, sizeof(int), st);      // the ticket must start at zero whatever the last call left
     if (e != cudaSuccess) return static_cast<int>(e);
     RouterArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const __nv_bfloat16*>(w), logits,
-                 static_cast<int*>(ids), static_cast<float*>(wts), ticket, H, E, topk, M, eps, partial, rows_pad};
+                 static_cast<int*>(ids), static_cast<float*>(wts), ticket, H, E, topk, M, eps, partial, rows_pad, nullptr};
     const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
     const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 128) + sizeof(__nv_bfloat16) * static_cast<size_t>(mp) * 2 * H;
     dim3 g(rows_pad / 16 * 4), b(256);

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) rows_norm_split_kernel(const __nv_bfloat1
 
 // rmsnorm(x[m]) * gamma -> bf16 planes[(2m + {hi, lo})][H]: x' = hi + lo to ~2^-17
 __global__ void __launch_bounds__(256) rows_norm_split_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, __nv_bfloat16* planes,
-                                                                   int H, float eps) {
+                                                                   uint8_t* planes_e4m3, int H, float eps) {
     __shared__ float red[32];
     extern __shared__ __align__(16) float xs[];
     pdl_launch_dependents();
@@ -273,6 +273,7 @@ __global__ void __launch_bounds__(256) rows_norm_split_bf16_kernel(const __nv_bf
     const int m = blockIdx.x;
     norm.template run<3>(nullptr, xs, x + static_cast<size_t>(m) * H, 1, H, eps, red);
     split_bf16_rows(planes + static_cast<size_t>(m) * 2 * H, xs, 1, H);
+    if (planes_e4m3 != nullptr) split_rows<3>(planes_e4m3 + static_cast<size_t>(m) * 3 * H, xs, 1, H, kSplitScale);   // same rows for the expert kernels
 }
 
 // h = silu(gate) * up * route weight -> planes[(3m + term)][S * I], descale[m]
@@ -320,12 +321,14 @@ extern "C" {
 
 // Gate/up projections of all rows' experts.  planes: e4m3 [3M][H] scratch, written here.
 int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, void* planes, int H, int I, int S,
-                    int M, int n_experts_total, int ksplit, float eps, int* status, void* stream) {
+                    int M, int n_experts_total, int ksplit, float eps, int planes_ready, int* status, void* stream) {
     if (M < 1 || M > kMaxRows || H % 128 || H > 4096 || I % 64 || S < 1 || S > 16 || ksplit < 1 || ksplit > 4) return cudaErrorInvalidValue;
     auto st = static_cast<cudaStream_t>(stream);
-    int e = launch(rows_norm_split_kernel, dim3(M), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln),
-                   static_cast<uint8_t*>(planes), static_cast<float*>(nullptr), H, eps);
-    if (e) return e;
+    if (!planes_ready) {      // the router of this step did not leave the planes: make them here
+        int e = launch(rows_norm_split_kernel, dim3(M), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln),
+                       static_cast<uint8_t*>(planes), static_cast<float*>(nullptr), H, eps);
+        if (e) return e;
+    }
     CUtensorMap mw, mx;
     const uint64_t wrows = static_cast<uint64_t>(n_experts_total) * 2 * I;
     if (!tensor_map(&mw, w13, wrows, H, H, kBM, false) || !tensor_map(&mx, planes, 3 * M, H, H, kBN, false)) return cudaErrorInvalidValue;
@@ -361,11 +364,11 @@ int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void*
 // need not be a multiple of 128; rows_pad is the row stride of the output), xhat = rmsnorm(x) * gamma as bf16 hi + lo
 // planes written into `planes` ([2M][K] bf16 scratch).
 int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void* planes, void* partial, const void* zero_ids, int rows, int rows_pad, int K,
-                           int M, int ksplit, float eps, int* status, void* stream) {
+                           int M, int ksplit, float eps, void* planes_e4m3, int* status, void* stream) {
     if (M < 1 || M > kMaxRows || K % 64 || K > 4096 || rows_pad % 2 || rows_pad < rows || ksplit < 1 || ksplit > 16) return cudaErrorInvalidValue;
     auto st = static_cast<cudaStream_t>(stream);
     int e = launch(rows_norm_split_bf16_kernel, dim3(M), dim3(256), sizeof(float) * K, st, static_cast<const __nv_bfloat16*>(x),
-                   static_cast<const float*>(gamma), static_cast<__nv_bfloat16*>(planes), K, eps);
+                   static_cast<const float*>(gamma), static_cast<__nv_bfloat16*>(planes), static_cast<uint8_t*>(planes_e4m3), K, eps);
     if (e) return e;
     CUtensorMap mw, mx;
     if (!tensor_map(&mw, w, rows, K, K, kBM, true) || !tensor_map(&mx, planes, 2 * M, K, K, kBN, true)) return cudaErrorInvalidValue;

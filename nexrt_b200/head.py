@@ -54,7 +54,7 @@ class Head:
             lg = self.logits if self.logits is not None else self.wide_logits
             check(
                 c.lib.nexrt_tc_router_logits(ptr(c.x if x is None else x), ptr(w["final_ln"]), ptr(w["lm_head"]), ptr(c.router_planes), ptr(lg),
-                                             ptr(c.zero_ids), spec.vocab, spec.vocab, cfg.hidden, M, 1, cfg.rms_eps, ptr(c.status), c.stream()),
+                                             ptr(c.zero_ids), spec.vocab, spec.vocab, cfg.hidden, M, 1, cfg.rms_eps, None, ptr(c.status), c.stream()),
                 "tc_lmhead_logits",
             )
             check(

@@ -33,33 +33,40 @@ class Moe:
         self.tc_router_rows = int(os.environ.get("NEXRT_TC_ROUTER_ROWS", "8")) or 1 << 30   # below 8 rows the fused router kernel is as fast
         cfg, spec = ctx.cfg, ctx.spec
         self.tc_ok = cfg.hidden % 128 == 0 and cfg.hidden <= 4096 and spec.inter % 128 == 0
+        # the fused router takes its tensor-core form (the one that can also write the planes) under these conditions
+        self.router_mma = (int(os.environ.get("NEXRT_GEMV_MODE", "63")) & 16) != 0 and cfg.hidden % 1024 == 0 and cfg.hidden <= 4096
+        self._planes_ready = False
 
     def forward(self, M: int = 1) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
         cfg, spec, st = c.cfg, c.spec, c.stream()
         S = cfg.top_k + 1
         wide = M >= self.tc_router_rows and self.tc_ok and cfg.hidden % (64 * c.router_ksplit) == 0
+        tc_experts = M >= self.tc_rows and self.tc_ok
+        # the routers of a step whose experts run on tcgen05 also leave the experts' activation planes
+        self._planes_ready = tc_experts and (wide or self.router_mma)
+        planes = ptr(c.moe_planes1) if self._planes_ready else None
         if wide:
             # multi-row steps: router logits of all rows in one tcgen05 GEMM (bf16 weights, hi + lo activation planes,
             # K split over CTAs), then one small kernel adds the partial planes and selects the experts
             check(
                 lib.nexrt_tc_router_logits(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.router_planes), ptr(c.router_partial), ptr(c.zero_ids),
-                                           cfg.n_experts + 1, self.rows_pad, cfg.hidden, M, c.router_ksplit, cfg.rms_eps, ptr(c.status), st),
+                                           cfg.n_experts + 1, self.rows_pad, cfg.hidden, M, c.router_ksplit, cfg.rms_eps, planes, ptr(c.status), st),
                 "tc_router_logits",
             )
             check(lib.nexrt_moe_router_topk(ptr(c.router_partial), c.router_ksplit, self.rows_pad, ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts),
                                             cfg.n_experts, cfg.top_k, M, st), "moe_router_topk")
         else:
-            self._router_fused(M)
+            self._router_fused(M, planes)
         self._experts(M)
 
-    def _router_fused(self, M: int) -> None:
+    def _router_fused(self, M: int, planes=None) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
         cfg, spec, st = c.cfg, c.spec, c.stream()
         check(
             lib.nexrt_moe_router(
                 ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts), ptr(c.moe_ticket),
-                ptr(c.moe_partial), self.rows_pad, cfg.hidden, cfg.n_experts, cfg.top_k, M, cfg.rms_eps, c.n_cta, st,
+                ptr(c.moe_partial), self.rows_pad, cfg.hidden, cfg.n_experts, cfg.top_k, M, cfg.rms_eps, c.n_cta, planes, st,
             ),
             "moe_router",
         )
@@ -77,7 +84,7 @@ class Moe:
             ks = c.moe_ksplit if tiles * c.moe_ksplit <= 2 * c.n_cta else 1
             check(
                 lib.nexrt_tc_moe_l1(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_ids), ptr(c.moe_gu_tc), ptr(c.moe_planes1),
-                                    cfg.hidden, spec.inter, S, M, n_total, ks, cfg.rms_eps, ptr(c.status), st),
+                                    cfg.hidden, spec.inter, S, M, n_total, ks, cfg.rms_eps, int(self._planes_ready), ptr(c.status), st),
                 "tc_moe_l1",
             )
             check(

@@ -54,7 +54,7 @@ _PROTOTYPES = {
     "nexrt_attn_front": [vp] * 9 + [ci] * 7 + [cf, ci, vp],
     "nexrt_attn_decode": [vp] * 14 + [ci] * 8 + [cf, ci, ci, ci, ci, ci, ci, CH, cu, vp],
     "nexrt_oproj_allreduce": [vp] * 6 + [ci] * 4 + [cf, ci, CH, cu, CH, cu, ci, vp],
-    "nexrt_moe_router": [vp] * 8 + [ci] * 5 + [cf, ci, vp],
+    "nexrt_moe_router": [vp] * 8 + [ci] * 5 + [cf, ci, vp, vp],
     "nexrt_moe_l1": [vp] * 6 + [ci] * 4 + [cf, ci, ci, vp],
     "nexrt_moe_l2_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, ci, vp],
     "nexrt_lmhead_sample": [vp] * 9 + [ci] * 4 + [cf, ci, ci, CH, cu, ci, vp],
@@ -74,13 +74,13 @@ _PROTOTYPES = {
     "nexrt_rows_norm_split": [vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_tc_rows_gemm": [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp],
     "nexrt_gdn_front_tail": [vp] * 12 + [ci] * 7 + [vp],
-    "nexrt_tc_router_logits": [vp] * 6 + [ci] * 5 + [cf, vp, vp],
+    "nexrt_tc_router_logits": [vp] * 6 + [ci] * 5 + [cf, vp, vp, vp],
     "nexrt_moe_router_topk": [vp, ci, ci, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_lmhead_sample_from_logits": [vp] * 6 + [ci] * 6 + [CH, cu, ci, vp],
     "nexrt_oproj_stage_split": [vp] * 5 + [ci, ci, ci, cf, ci, CH, cu, vp],
     "nexrt_tc_oproj_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, vp, vp],
     "nexrt_attn_front_tail": [vp] * 6 + [ci] * 7 + [vp],
-    "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 6 + [cf, vp, vp],
+    "nexrt_tc_moe_l1": [vp] * 7 + [ci] * 6 + [cf, ci, vp, vp],
     "nexrt_tc_moe_l2_allreduce": [vp] * 8 + [ci] * 6 + [CH, cu, vp, vp],
     "nexrt_ipc_alloc": [c_size_t, POINTER(c_void_p)],
     "nexrt_ipc_get_handle": [vp, vp],

@@ -49,7 +49,7 @@ def main(argv=None) -> int:
     lib, st = load(), torch.cuda.current_stream().cuda_stream
 
     def l1(ids):
-        check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13), ptr(w13s), ptr(ids), ptr(gu), ptr(p1), H, I, S, M, E + 1, a.ksplit, 1e-6, ptr(status), st), "l1")
+        check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13), ptr(w13s), ptr(ids), ptr(gu), ptr(p1), H, I, S, M, E + 1, a.ksplit, 1e-6, 0, ptr(status), st), "l1")
 
     def l2(ids):
         check(lib.nexrt_tc_moe_l2_allreduce(ptr(gu), ptr(ids), ptr(wts), ptr(w2), ptr(w2s), ptr(x), ptr(p2), ptr(ds), H, I, S, M, E + 1, a.ksplit, ch.ref, 0,

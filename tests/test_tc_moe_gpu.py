@@ -38,7 +38,7 @@ def test_expert_kernels_match_fp32(H, I, E, S, M, ksplit):
     planes2 = torch.zeros(3 * 8, S * I, dtype=torch.uint8, device=dev)
     descale = torch.zeros(8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13q), ptr(w13s), ptr(ids), ptr(gu_planes), ptr(planes1), H, I, S, M, E + 1, ksplit, 1e-6, ptr(status), st), "l1")
+    check(lib.nexrt_tc_moe_l1(ptr(x), ptr(gamma), ptr(w13q), ptr(w13s), ptr(ids), ptr(gu_planes), ptr(planes1), H, I, S, M, E + 1, ksplit, 1e-6, 0, ptr(status), st), "l1")
     torch.cuda.synchronize()
     gu = gu_planes.sum(0)
     xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * gamma

@@ -46,7 +46,7 @@ def test_noalloc_router_matches_regular_entry_point(M, H, E, topk):
         ids_ref = torch.zeros(M, S, dtype=torch.int32, device="cuda")
         wts_ref = torch.zeros(M, S, device="cuda")
         L.check(lib.nexrt_moe_router(x.data_ptr(), ln.data_ptr(), w.data_ptr(), logits.data_ptr(), ids_ref.data_ptr(), wts_ref.data_ptr(),
-                                     ticket.data_ptr(), partial.data_ptr(), rows_pad, H, E, topk, M, 1e-6, 148, stream), "router")
+                                     ticket.data_ptr(), partial.data_ptr(), rows_pad, H, E, topk, M, 1e-6, 148, None, stream), "router")
         ids = torch.full((M, S), -7, dtype=torch.int32, device="cuda")
         wts = torch.zeros(M, S, device="cuda")
         L.check(fn(x.data_ptr(), ln.data_ptr(), w.data_ptr(), ids.data_ptr(), wts.data_ptr(), rows_pad, H, E, topk, M, 1e-6, stream), "router_noalloc")
