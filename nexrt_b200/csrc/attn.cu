@@ -182,7 +182,7 @@ constexpr int kRowsPerPassMma = 8;
 template <int HD, bool MMA>
 __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     constexpr int RP = MMA ? kRowsPerPassMma : kRowsPerPass;
-#define NEXRT_AEVENT(i, cond) do { if (a.events != nullptr && (cond) && blockIdx.y == 0 && threadIdx.x == 0) a.events[i] = globaltimer_ns(); } while (0)
+#define NEXRT_AEVENT(i, cond) do { if (a.events != nullptr && (cond) && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) a.events[i] = globaltimer_ns(); } while (0)
     NEXRT_AEVENT(0, blockIdx.x == 0);
     constexpr int EL = HD / 32;  // elements per lane
     extern __shared__ __align__(16) float smem[];
@@ -302,7 +302,10 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
         // once per pass - the K/V tiles of the later passes come from L2
         const AttnMmaKeys keys{kc, vc, k_s, C0, lo, hi};
         uint4* qf = reinterpret_cast<uint4*>(part + static_cast<size_t>(NW) * RP * (HD + 2));   // behind the per-warp partials
-        for (int r0 = 0; r0 < rows; r0 += RP) {
+        // blockIdx.z names the pass: the passes of a wide step run side by side on different CTAs instead of one after
+        // the other (their K/V tiles meet in L2); the ticket below counts splits x passes
+        {
+            const int r0 = static_cast<int>(blockIdx.z) * RP;
             const int nr = min(RP, rows - r0);
             const int gr = lane >> 2;
             const int my_limit = gr < nr ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + (r0 + gr) / G) : -1;
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             __syncthreads();
             attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
             __syncthreads();
-            if (r0 == 0) NEXRT_AEVENT(3, split == 0);
+            NEXRT_AEVENT(3, split == 0);
             merge_warps(r0, nr);
             __syncthreads();
         }
@@ -405,7 +408,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     // ---- ticket: the last CTA of this kv head to arrive combines all splits
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_active - 1);
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_active * static_cast<int>(gridDim.z) - 1);
     __syncthreads();
     NEXRT_AEVENT(5, split == 0);
     if (!s_last) return;
@@ -577,9 +580,10 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) != 0;
-    if (hd == 256) return mma ? launch(attn_decode_kernel<256, true>, dim3(n_splits, kvh), dim3(256), smem, st, a)
+    const int passes = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;     // tensor-core path: eight query rows per CTA
+    if (hd == 256) return mma ? launch(attn_decode_kernel<256, true>, dim3(n_splits, kvh, passes), dim3(256), smem, st, a)
                               : launch(attn_decode_kernel<256, false>, dim3(n_splits, kvh), dim3(256), smem, st, a);
-    if (hd == 128) return mma ? launch(attn_decode_kernel<128, true>, dim3(n_splits, kvh), dim3(256), smem, st, a)
+    if (hd == 128) return mma ? launch(attn_decode_kernel<128, true>, dim3(n_splits, kvh, passes), dim3(256), smem, st, a)
                               : launch(attn_decode_kernel<128, false>, dim3(n_splits, kvh), dim3(256), smem, st, a);
     return cudaErrorInvalidValue;
 }
