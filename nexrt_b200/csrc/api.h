@@ -112,8 +112,22 @@ int nexrt_tc_gemm_fp8(const void* wq, const float* sw, int64_t ldw, const void* 
 // Y[T, R] = X[T, K] * W[R, K]^T, bf16 operands (leading dimensions in elements), fp32 accumulation.  K % 64 == 0, K <= 4096.
 int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, void* y, int T, int R, int K, int ldy, int out_mode, int* status,
                        void* stream);
+// The same product with K split over ksplit CTAs per tile (fp32 partial planes of T * ldy elements, added by the consumer in
+// plane order) and, with group_rows > 0, W stored as K / group_k matrices [group_rows, group_k] one after the other (expert
+// down projections; sw [groups][group_rows / 128][group_k / 128], R == group_rows).  K / 128 / ksplit <= 64.
+int nexrt_tc_gemm_fp8_ex(const void* wq, const float* sw, int64_t ldw, const void* xq, const float* sx, void* y, int T, int R, int K, int ldy,
+                         int ksplit, int group_k, int group_rows, int* status, void* stream);
 // Optional RMSNorm (gamma != null, stored as the full multiplier) then per-row, per-128-column e4m3 quantisation.
 int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream);
+
+// ---- glue kernels of the wide prefill path (prefill.cu) ---------------------------------------------------------
+int nexrt_prefill_embed(const void* embed, const void* ids, void* x, void* status, int H, int vocab, int T, void* stream);
+int nexrt_prefill_ctl(const void* ctl, void* table, int n_sub, int rows, void* stream);   /* table[j] = ctl with committed length + j * rows */
+int nexrt_prefill_advance(void* ctl, int rows, void* stream);
+int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, void* stream);
+int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream);
+int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, void* stream);
+int nexrt_planes_residual(void* x, const void* y, void* sum_out, int64_t n, int ksplit, void* stream);
 
 // ---- experts of a multi-row step on tcgen05 (tc_moe.cu) -------------------------------------------------------
 // Gate/up of every distinct expert named in ids [M][S] (streamed once each); planes is e4m3 scratch [3M][H].

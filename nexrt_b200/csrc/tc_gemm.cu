@@ -46,9 +46,15 @@ struct Args {
     const float* sw;      // [ceil(R/128), KB] weight block scales (fp8 only)
     const float* sx;      // [T, KB] activation scales (fp8 only)
     void* y;              // [T, ldy]
-    int T, R, KB, ldy;
+    int T, R, KB, ldy;    // KB: K blocks of the whole product
     int out_mode;         // 0 fp32 store, 1 bf16 store, 2 fp32 accumulate (y += result)
     int* status;
+    // split K: blockIdx.z walks K blocks [z * kb_per, (z + 1) * kb_per) and writes its partial sums to plane z of
+    // y (planes are T * ldy elements apart); the consumer adds the planes in a fixed order
+    int kb_per;
+    // grouped K (expert down projections stored as [group][rows][group_kb * 128]): K block kb of the product is
+    // block kb % group_kb of group kb / group_kb, whose rows start at (kb / group_kb) * group_rows; 0 = plain matrix
+    int group_kb, group_rows;
 };
 
 template <bool FP8, int BN>
@@ -71,7 +77,8 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;     // token tiles of one weight tile are neighbours: they share it in L2
-    const int KB = a.KB;
+    const int kb0 = static_cast<int>(blockIdx.z) * a.kb_per;     // first K block of this CTA's range
+    const int KB = max(0, min(a.kb_per, a.KB - kb0));
     constexpr uint32_t kCols = kAccBufs * BN;                 // power of two, 64..256 columns
 
     if (threadIdx.x == 0) {
@@ -100,9 +107,11 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
                 if (!mbar_wait(empty(s), ((kb / kStages) & 1) ^ 1, abort_flag)) break;
                 mbar_expect_tx(full(s), L::kA + L::kB);
                 const uint32_t dst = smem_u32(smem + s * L::kStage);
-                const int c0 = kb * (FP8 ? kSpan : kSpan / 2);          // element coordinate along K
-                tma_load_2d(dst, &map_w, c0, m0, full(s));
-                tma_load_2d(dst + L::kA, &map_x, c0, n0, full(s));
+                constexpr int kElems = FP8 ? kSpan : kSpan / 2;          // elements of K per block
+                const int kg = kb0 + kb;
+                if (a.group_kb > 0) tma_load_2d(dst, &map_w, (kg % a.group_kb) * kElems, (kg / a.group_kb) * a.group_rows + m0, full(s));
+                else tma_load_2d(dst, &map_w, kg * kElems, m0, full(s));
+                tma_load_2d(dst + L::kA, &map_x, kg * kElems, n0, full(s));
             }
         }
     } else if (warp == 1) {
@@ -132,9 +141,13 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
         if (FP8) {
             for (int i = et; i < KB * BN; i += 128) {
                 const int kb = i / BN, n = i % BN;
-                sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * KB + kb] : 0.f;
+                sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * a.KB + kb0 + kb] : 0.f;
             }
-            for (int i = et; i < KB; i += 128) sws[i] = __ldg(a.sw + static_cast<size_t>(blockIdx.y) * KB + i);   // weight block scales of this row tile
+            for (int i = et; i < KB; i += 128) {     // weight block scales of this row tile
+                const int kg = kb0 + i;
+                sws[i] = a.group_kb > 0 ? __ldg(a.sw + (static_cast<size_t>(kg / a.group_kb) * (a.group_rows / kBM) + blockIdx.y) * a.group_kb + kg % a.group_kb)
+                                        : __ldg(a.sw + static_cast<size_t>(blockIdx.y) * a.KB + kg);
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         float acc[BN];
@@ -175,10 +188,11 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
             }
         }
         if (ok && row < a.R) {
+            const size_t plane = static_cast<size_t>(blockIdx.z) * a.T * a.ldy;
 #pragma unroll
             for (int n = 0; n < BN; ++n) {
                 if (n0 + n >= a.T) break;
-                const size_t o = static_cast<size_t>(n0 + n) * a.ldy + row;
+                const size_t o = plane + static_cast<size_t>(n0 + n) * a.ldy + row;
                 if (a.out_mode == 0) {
                     static_cast<float*>(a.y)[o] = acc[n];
                 } else if (a.out_mode == 1) {
@@ -267,8 +281,8 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const Args& 
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    dim3 grid((a.T + BN - 1) / BN, (a.R + kBM - 1) / kBM);
-    kern<<<grid, kThreads, L::total(a.KB, FP8), stream>>>(mw, mx, a);
+    dim3 grid((a.T + BN - 1) / BN, (a.R + kBM - 1) / kBM, (a.KB + a.kb_per - 1) / a.kb_per);
+    kern<<<grid, kThreads, L::total(a.kb_per, FP8), stream>>>(mw, mx, a);
     return cudaGetLastError();
 }
 
@@ -345,7 +359,29 @@ int nexrt_tc_gemm_fp8(const void* wq, const float* sw, int64_t ldw, const void* 
     const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
     CUtensorMap mw, mx;
     if (!tensor_map(&mw, wq, R, K, ldw, kBM, false) || !tensor_map(&mx, xq, T, K, K, bn, false)) return cudaErrorInvalidValue;
-    Args a{sw, sx, y, T, R, K / 128, ldy, out_mode, status};
+    Args a{sw, sx, y, T, R, K / 128, ldy, out_mode, status, K / 128, 0, 0};
+    auto s = static_cast<cudaStream_t>(stream);
+    if (bn == 16) return launch_tc<true, 16>(mw, mx, a, s);
+    if (bn == 32) return launch_tc<true, 32>(mw, mx, a, s);
+    return launch_tc<true, 64>(mw, mx, a, s);
+}
+
+// The same product with K split over `ksplit` CTAs per tile (partial sums to ksplit fp32 planes of T * ldy elements each,
+// which the consumer adds in plane order) and, when group_rows > 0, with W stored as `groups` matrices of
+// [group_rows, group_k] one after the other (expert down projections): K = groups * group_k, R = group_rows, block
+// scales sw [groups][group_rows / 128][group_k / 128].  Any K whose per-CTA share is at most 64 blocks.
+int nexrt_tc_gemm_fp8_ex(const void* wq, const float* sw, int64_t ldw, const void* xq, const float* sx, void* y, int T, int R, int K, int ldy,
+                         int ksplit, int group_k, int group_rows, int* status, void* stream) {
+    if (T <= 0 || R <= 0 || K <= 0 || K % 128 || ksplit < 1) return cudaErrorInvalidValue;
+    const int KB = K / 128, kb_per = (KB + ksplit - 1) / ksplit;
+    if (kb_per > kMaxKBlocks) return cudaErrorInvalidValue;
+    if (group_rows > 0 && (group_k <= 0 || group_k % 128 || K % group_k || group_rows % kBM || R != group_rows)) return cudaErrorInvalidValue;
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    const bool okw = group_rows > 0 ? tensor_map(&mw, wq, static_cast<uint64_t>(K / group_k) * group_rows, group_k, ldw, kBM, false)
+                                    : tensor_map(&mw, wq, R, K, ldw, kBM, false);
+    if (!okw || !tensor_map(&mx, xq, T, K, K, bn, false)) return cudaErrorInvalidValue;
+    Args a{sw, sx, y, T, R, KB, ldy, 0, status, kb_per, group_rows > 0 ? group_k / 128 : 0, group_rows};
     auto s = static_cast<cudaStream_t>(stream);
     if (bn == 16) return launch_tc<true, 16>(mw, mx, a, s);
     if (bn == 32) return launch_tc<true, 32>(mw, mx, a, s);
@@ -359,7 +395,7 @@ int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, v
     const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
     CUtensorMap mw, mx;
     if (!tensor_map(&mw, w, R, K, ldw, kBM, true) || !tensor_map(&mx, x, T, K, ldx, bn, true)) return cudaErrorInvalidValue;
-    Args a{nullptr, nullptr, y, T, R, K / 64, ldy, out_mode, status};
+    Args a{nullptr, nullptr, y, T, R, K / 64, ldy, out_mode, status, K / 64, 0, 0};
     auto s = static_cast<cudaStream_t>(stream);
     if (bn == 16) return launch_tc<false, 16>(mw, mx, a, s);
     if (bn == 32) return launch_tc<false, 32>(mw, mx, a, s);

@@ -81,6 +81,7 @@ class DecodeEngine:
         self.embed = ext["head"]["embed"]
         self.mirror = CtlMirror(self.dev, CTL_WORDS)
         self.graphs: Dict = {}
+        self._wide: Dict = {}     # wide prefill paths by chunk size
         self._n_sites: Dict = {}
         # DFlash feature taps: residual rows after the MoE of chosen layers, concatenated per row
         self.tap_layers: Dict[int, int] = {}
@@ -299,12 +300,15 @@ class DecodeEngine:
 
     # ---- prefill ------------------------------------------------------------------------------
     def prefill(self, ids: Sequence[int], chunk: int = 8, sample: bool = True, resume_from: int = 0,
-                on_chunk: Optional[Callable[[int, int], None]] = None) -> int:
+                on_chunk: Optional[Callable[[int, int], None]] = None, wide: Optional[int] = None) -> int:
         """The engine's own chunked prefill: consume ``ids`` and leave the first generated token
         pending.  This arm runs the multi-row step kernels ``chunk`` rows at a time with a forced full
         commit, so the state it leaves is the decode path's own.  ``resume_from > 0`` keeps the state
         of the first ``resume_from`` tokens (which must be what the engine currently holds) and only
-        evaluates the suffix; ``on_chunk(start, end)`` is called after each chunk is queued."""
+        evaluates the suffix; ``on_chunk(start, end)`` is called after each chunk is queued.  ``wide`` (default: the
+        ``NEXRT_WIDE_PREFILL`` environment variable, 0 = off) is the row count of the wide path
+        (``prefill_wide.WidePrefill``): whole chunks of that many tokens go through one tcgen05 GEMM per projection,
+        the rest of the prompt (at least its last token) through the 8-row steps."""
         if self.max_rows < min(chunk, len(ids)) and len(ids) > 1:
             chunk = self.max_rows
         ids = list(int(t) for t in ids)
@@ -317,6 +321,17 @@ class DecodeEngine:
         else:
             self.reset(first_token=ids[0])
         pos = resume_from
+        wide = int(os.environ.get("NEXRT_WIDE_PREFILL", "0")) if wide is None else int(wide)
+        if wide and len(ids) - 1 - pos >= wide:
+            from . import prefill_wide
+
+            if prefill_wide.supported(self):
+                wp = self._wide.get(wide)
+                if wp is None:
+                    wp = self._wide[wide] = prefill_wide.WidePrefill(self, wide)
+                n = (len(ids) - 1 - pos) // wide * wide
+                wp.run(ids[pos : pos + n], base=pos, on_chunk=on_chunk)
+                pos += n
         while pos < len(ids):
             n = min(chunk, len(ids) - pos)
             self.set_rows(ids[pos : pos + n])

@@ -60,3 +60,18 @@ def bf16_gemm(w: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = No
     mode = 2 if accumulate else (0 if out.dtype == torch.float32 else 1)
     check(lib().nexrt_tc_gemm_bf16(ptr(w), w.stride(0), ptr(x), x.stride(0), ptr(out), T, R, K, out.stride(0), mode, ptr(status), _stream()), "tc_gemm_bf16")
     return out
+
+
+def fp8_gemm_split(wq: torch.Tensor, sw: torch.Tensor, xq: torch.Tensor, sx: torch.Tensor, out: torch.Tensor, ksplit: int = 1,
+                   group_k: int = 0, group_rows: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The block-scaled FP8 product with K split over ``ksplit`` CTAs per tile: ``out [ksplit, T, R]`` fp32 partial
+    planes (add them in plane order).  With ``group_rows`` the weight is a stack of ``K / group_k`` matrices
+    ``[group_rows, group_k]`` (the experts' down projections, ``w2 [E+1, H, I]`` viewed as ``[(E+1) * H, I]``) whose
+    K extents are concatenated: ``out[t, r] = sum_g x[t, g*group_k:(g+1)*group_k] . w[g, r, :]``."""
+    T, K = xq.shape
+    R = group_rows if group_rows else wq.shape[0]
+    if out.dtype != torch.float32 or out.numel() < ksplit * T * R or not (xq.is_contiguous() and sx.is_contiguous() and sw.is_contiguous()):
+        raise ValueError("fp8_gemm_split: output / operand layout")
+    check(lib().nexrt_tc_gemm_fp8_ex(ptr(wq), ptr(sw), wq.stride(0), ptr(xq), ptr(sx), ptr(out), T, R, K, R, ksplit, group_k, group_rows, ptr(status), _stream()),
+          "tc_gemm_fp8_ex")
+    return out

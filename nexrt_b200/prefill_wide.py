@@ -1,0 +1,246 @@
+"""Wide prefill: prompt chunks of 16..128 tokens per pass instead of the 8-row steps of ``DecodeEngine.prefill``.
+
+The reference hands prefill to SGLang (``nex_n2_5_pro/sglang_prefill/bridge.py:310-398``, 4096-token extends); this
+engine prefills through its own kernels, and at 8 rows per step every weight of the model is streamed once per 8
+tokens.  Here a chunk of ``T`` rows goes through each layer in one pass:
+
+* every projection (GDN / attention fronts, out-projections, router, expert gate/up and down) is one tcgen05 GEMM
+  over all ``T`` rows (``csrc/tc_gemm.cu``): e4m3 activations with one scale per row and 128 columns, the
+  checkpoint's block-scaled FP8 weights, fp32 accumulation - every weight byte is read once per chunk;
+* the experts run **dense**: the gate/up GEMM multiplies the chunk by all ``E + 1`` experts (with 64 rows x 10
+  routes nearly every expert is used anyway, and the FP8 tensor cores make the extra columns cheaper than a
+  gather), a small kernel turns the routed ``(row, expert)`` pairs into quantised ``h`` and leaves a zero scale
+  everywhere else, and the down GEMM walks ``K = (E + 1) * I`` split over CTAs;
+* what is sequential in the model (conv ring, delta rule, causal attention over the cache) reuses the multi-row
+  step kernels eight rows at a time; sub-step ``j`` reads its base position from entry ``j`` of a control-block
+  table, so the whole chunk is position-independent on the host and is captured once into a CUDA graph.
+
+The state it leaves (conv / state rings, KV cache, committed length) is the decode path's own, so decode - or the
+8-row prefill of the prompt's tail - continues from it.  Activations are quantised to one e4m3 plane here (the
+decode kernels use an exact three-term split), so hidden states agree with the 8-row path to FP8 rounding, not
+bit for bit; the same holds between the reference's SGLang prefill and its decode kernels.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .attn import FullAttn
+from .ops.lib import check, ptr
+from .ops.tc_gemm import bf16_gemm, fp8_gemm, fp8_gemm_split
+from .quant import FP8
+from .runtime.control import CTL_WORDS, Ctl
+
+SUB = 8   # rows per sub-step of the sequential kernels
+
+
+def supported(eng) -> bool:
+    """Shapes the wide path covers: everything the tcgen05 GEMMs tile (128-row weight tiles, 128-wide K blocks)."""
+    cfg, spec = eng.cfg, eng.spec
+    return (
+        eng.max_rows >= SUB and eng.taps is None
+        and cfg.hidden % 128 == 0 and cfg.hidden <= 8192 and spec.inter % 128 == 0
+        and spec.gdn_front_rows % 128 == 0 and spec.attn_front_rows % 128 == 0
+        and spec.gdn_local % 128 == 0 and spec.gdn_local <= 8192 and spec.attn_local % 128 == 0 and spec.attn_local <= 8192
+        and cfg.hidden // 64 <= 64 and cfg.gdn_dim == 128
+    )
+
+
+class WidePrefill:
+    def __init__(self, eng, chunk: int = 64, graph: bool = True):
+        if chunk % SUB or chunk < 2 * SUB or chunk > 128:
+            raise ValueError("chunk must be a multiple of 8 between 16 and 128")
+        if not supported(eng):
+            raise ValueError("model shapes outside the wide prefill path")
+        self.eng, self.T, self.use_graph = eng, chunk, graph and eng.world == 1
+        c, cfg, spec, dev = eng.ctx, eng.cfg, eng.spec, eng.dev
+        T, H = chunk, cfg.hidden
+        f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
+        z = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=dev)
+        self.n_sub = T // SUB
+        self.ids = z(T, dtype=i32)
+        self.x = z(T, H, dtype=bf)
+        self.xq, self.sx = torch.zeros(T, H, dtype=FP8, device=dev), z(T, H // 128)
+        self.xn = z(T, H)
+        self.planes = z(T, 2 * H, dtype=bf)
+        self.pre = z(T * max(spec.gdn_front_rows, spec.attn_front_rows))
+        self.ctl_tab = z(self.n_sub, CTL_WORDS, dtype=i32)
+        self.gdn_qkv, self.gdn_z = z(T, spec.gdn_qkv_rows), z(T, spec.gdn_local)
+        self.gdn_beta, self.gdn_g, self.gdn_out = z(T, spec.gdn_v), z(T, spec.gdn_v), z(T, spec.gdn_local)
+        self.gate, self.attn_out = z(T, spec.q_heads, cfg.head_dim), z(T, spec.attn_local)
+        kmax = max(spec.gdn_local, spec.attn_local)
+        self.oq, self.os = torch.zeros(T * kmax, dtype=FP8, device=dev), z(T * (kmax // 128))
+        self.S, self.n_total = cfg.top_k + 1, cfg.n_experts + 1
+        self.rows_pad = eng.moes[0].rows_pad
+        self.logits = z(T, self.rows_pad)
+        self.moe_logits, self.moe_ids, self.moe_wts = z(T, cfg.n_experts + 1), z(T, self.S, dtype=i32), z(T, self.S)
+        I = spec.inter
+        self.gu = z(T, self.n_total * 2 * I)
+        self.hq, self.hs = torch.zeros(T, self.n_total * I, dtype=FP8, device=dev), z(T, self.n_total * I // 128)
+        # K split of the expert down product: at most 64 K blocks per CTA, and about two CTAs per SM over the grid
+        kb = self.n_total * I // 128
+        tiles = (H // 128) * ((T + 63) // 64)
+        ks = max((kb + 63) // 64, min(kb, 16, max(1, 2 * c.n_cta // tiles)))
+        while (kb + (kb + ks - 1) // ks - 1) // ((kb + ks - 1) // ks) != ks:    # every plane gets a non-empty K range
+            ks = (kb + (kb + ks - 1) // ks - 1) // ((kb + ks - 1) // ks)
+        self.down_ksplit = ks
+        self.y = z(max(self.down_ksplit, 1), T, H)
+        self.ysum = z(T, H) if eng.world > 1 else None
+        self.graph = None
+
+    # ---- one chunk ---------------------------------------------------------------------------------------------
+    def _finish(self, ksplit: int) -> None:
+        """x += (all-reduced) sum of the projection's K-split planes."""
+        c, lib, st = self.eng.ctx, self.eng.ctx.lib, self.eng.ctx.stream()
+        n = self.T * self.eng.cfg.hidden
+        if self.eng.world == 1:
+            check(lib.nexrt_planes_residual(ptr(self.x), ptr(self.y), None, n, ksplit, st), "planes_residual")
+            return
+        check(lib.nexrt_planes_residual(None, ptr(self.y), ptr(self.ysum), n, ksplit, st), "planes_residual")
+        dist.all_reduce(self.ysum, group=self.eng.group)
+        check(lib.nexrt_planes_residual(ptr(self.x), ptr(self.ysum), None, n, 1, st), "planes_residual")
+
+    def _gdn(self, m) -> None:
+        eng, T = self.eng, self.T
+        c, lib, cfg, spec = eng.ctx, eng.ctx.lib, eng.cfg, eng.spec
+        st, w, H = c.stream(), m.w, cfg.hidden
+        R, C, nv, K = spec.gdn_front_rows, spec.gdn_qkv_rows, spec.gdn_v, spec.gdn_local
+        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), ptr(self.xn), None, H, T, cfg.rms_eps, st), "norm_rows")
+        pre = self.pre[: T * R].view(T, R)
+        fp8_gemm(w["front_w"], w["front_s"], self.xq, self.sx, out=pre, status=c.status)
+        for j in range(self.n_sub):
+            r = slice(j * SUB, (j + 1) * SUB)
+            check(
+                lib.nexrt_gdn_front_tail(ptr(pre[r]), ptr(self.xn[r]), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]), ptr(w["dt_bias"]), ptr(self.ctl_tab[j]),
+                                         ptr(m.conv_ring), ptr(self.gdn_qkv[r]), ptr(self.gdn_z[r]), ptr(self.gdn_beta[r]), ptr(self.gdn_g[r]), H, R, C, nv, SUB,
+                                         m.conv_ring_len, 1, st),
+                "gdn_front_tail",
+            )
+        for j in range(self.n_sub):
+            r = slice(j * SUB, (j + 1) * SUB)
+            check(lib.nexrt_gdn_core(ptr(self.gdn_qkv[r]), ptr(self.gdn_beta[r]), ptr(self.gdn_g[r]), ptr(self.ctl_tab[j]), ptr(m.state_ring), ptr(self.gdn_out[r]),
+                                     spec.gdn_qk, nv, SUB, m.state_ring_len, C, st), "gdn_core")
+        oq, os_ = self.oq[: T * K].view(T, K), self.os[: T * (K // 128)].view(T, K // 128)
+        check(lib.nexrt_gdn_gate_quant(ptr(self.gdn_out), ptr(self.gdn_z), ptr(w["gnorm_w"]), ptr(oq), ptr(os_), K, T, cfg.rms_eps, st), "gdn_gate_quant")
+        fp8_gemm(w["out_w"], w["out_s"], oq, os_, out=self.y[0], status=c.status)
+        self._finish(1)
+
+    def _attn(self, m: FullAttn) -> None:
+        eng, T = self.eng, self.T
+        c, lib, cfg, spec = eng.ctx, eng.ctx.lib, eng.cfg, eng.spec
+        st, w, H, hd = c.stream(), m.w, cfg.hidden, cfg.head_dim
+        nq, kvh, K = spec.q_heads, spec.kv_heads, spec.attn_local
+        R = spec.attn_front_rows
+        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), None, None, H, T, cfg.rms_eps, st), "norm_rows")
+        pre = self.pre[: T * R].view(T, R)
+        fp8_gemm(w["front_w"], w["front_s"], self.xq, self.sx, out=pre, status=c.status)
+        rope = c.rope_table(m.cache_len)
+        for j in range(self.n_sub):
+            r = slice(j * SUB, (j + 1) * SUB)
+            ctl = self.ctl_tab[j]
+            check(lib.nexrt_attn_front_tail(ptr(pre[r]), ptr(ctl), ptr(c.q_raw), ptr(self.gate[r]), ptr(c.k_raw), ptr(m.v_cache), hd, nq, nq, kvh, SUB,
+                                            m.cache_len, 1, st), "attn_front_tail")
+            check(
+                lib.nexrt_attn_decode(ptr(c.q_raw), ptr(self.gate[r]), ptr(c.k_raw), ptr(w["qn"]), ptr(w["kn"]), ptr(c.inv_freq), ptr(rope), ptr(ctl), ptr(m.k_cache),
+                                      ptr(m.v_cache), ptr(c.ws_acc), ptr(c.ws_ml), ptr(c.attn_ticket), ptr(self.attn_out[r]), hd, nq, nq, kvh, SUB, m.cache_len,
+                                      cfg.rotary_dim, c.n_splits, cfg.rms_eps, 0, 0, 0, 0, 1, 0, None, 0, st),
+                "attn_decode",
+            )
+        oq, os_ = self.oq[: T * K].view(T, K), self.os[: T * (K // 128)].view(T, K // 128)
+        check(lib.nexrt_act_quant(ptr(self.attn_out), 1, K, None, cfg.rms_eps, ptr(oq), ptr(os_), T, K, st), "act_quant")
+        fp8_gemm(w["out_w"], w["out_s"], oq, os_, out=self.y[0], status=c.status)
+        self._finish(1)
+
+    def _moe(self, moe) -> None:
+        eng, T = self.eng, self.T
+        c, lib, cfg, spec = eng.ctx, eng.ctx.lib, eng.cfg, eng.spec
+        st, w, H, I, S, n_total = c.stream(), moe.w, cfg.hidden, spec.inter, self.S, self.n_total
+        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["post_ln"]), ptr(self.xq), ptr(self.sx), None, ptr(self.planes), H, T, cfg.rms_eps, st), "norm_rows")
+        # router: bf16 weights, activations as hi + lo bf16 planes in two accumulating GEMMs
+        bf16_gemm(w["router_w_pad"], self.planes[:, :H], out=self.logits, status=c.status)
+        bf16_gemm(w["router_w_pad"], self.planes[:, H:], out=self.logits, accumulate=True, status=c.status)
+        for j in range(self.n_sub):
+            r = slice(j * SUB, (j + 1) * SUB)
+            check(lib.nexrt_moe_router_topk(ptr(self.logits[r]), 1, self.rows_pad, ptr(self.moe_logits[r]), ptr(self.moe_ids[r]), ptr(self.moe_wts[r]),
+                                            cfg.n_experts, cfg.top_k, SUB, st), "moe_router_topk")
+        # experts, dense: gate/up of every expert for every row, activation of the routed pairs, down over all experts
+        fp8_gemm(w["w13"].view(n_total * 2 * I, H), w["w13_s"].view(-1, H // 128), self.xq, self.sx, out=self.gu, status=c.status)
+        self.hq.view(torch.uint8).zero_()
+        self.hs.zero_()
+        check(lib.nexrt_moe_dense_act(ptr(self.gu), ptr(self.moe_ids), ptr(self.moe_wts), ptr(self.hq), ptr(self.hs), I, S, T, n_total, st), "moe_dense_act")
+        fp8_gemm_split(w["w2"].view(n_total * H, I), w["w2_s"], self.hq, self.hs, self.y, ksplit=self.down_ksplit, group_k=I, group_rows=H, status=c.status)
+        self._finish(self.down_ksplit)
+
+    def _chunk(self) -> None:
+        """All layers over the rows named by ``self.ids`` at the engine's committed length, which then advances by T."""
+        eng = self.eng
+        c, lib, st = eng.ctx, eng.ctx.lib, eng.ctx.stream()
+        check(lib.nexrt_prefill_ctl(ptr(c.ctl), ptr(self.ctl_tab), self.n_sub, SUB, st), "prefill_ctl")
+        check(lib.nexrt_prefill_embed(ptr(eng.embed), ptr(self.ids), ptr(self.x), ptr(c.status), eng.cfg.hidden, eng.cfg.vocab, self.T, st), "prefill_embed")
+        for mixer, moe in zip(eng.mixers, eng.moes):
+            if isinstance(mixer, FullAttn):
+                self._attn(mixer)
+            else:
+                self._gdn(mixer)
+            self._moe(moe)
+        check(lib.nexrt_prefill_advance(ptr(c.ctl), self.T, st), "prefill_advance")
+
+    def run(self, ids: Sequence[int], base: int = 0, on_chunk=None) -> None:
+        """Consume ``len(ids)`` (a multiple of the chunk size) prompt tokens starting at the engine's committed length
+        (``base``, only used to report progress through ``on_chunk(start, end)``)."""
+        if len(ids) % self.T:
+            raise ValueError("the wide path takes whole chunks")
+        dev = self.eng.dev
+        for pos in range(0, len(ids), self.T):
+            self.ids.copy_(torch.tensor(list(ids[pos : pos + self.T]), dtype=torch.int32), non_blocking=False)
+            if on_chunk is not None:
+                on_chunk(base + pos, base + pos + self.T)
+            if not self.use_graph:
+                self._chunk()
+                continue
+            if self.graph is None:
+                # one eager pass (lazy initialisation in the launchers must not happen under capture), whose state
+                # changes are undone before the captured pass is replayed for the same rows
+                snap = self._snapshot()
+                self._chunk()
+                torch.cuda.synchronize(dev)
+                self._restore(snap)
+                g = torch.cuda.CUDAGraph()
+                s = torch.cuda.Stream(dev)
+                s.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(s):
+                    with torch.cuda.graph(g, stream=s):
+                        self._chunk()
+                torch.cuda.current_stream(dev).wait_stream(s)
+                torch.cuda.synchronize(dev)
+                self._restore(snap)
+                self.graph = g
+            self.graph.replay()
+        torch.cuda.synchronize(dev)
+
+    # the eager warm-up pass and the capture itself touch the rings, the caches and the committed length
+    def _snapshot(self) -> List:
+        eng = self.eng
+        snap: List = [eng.ctx.ctl.clone()]
+        C0 = int(eng.ctx.ctl[Ctl.COMMITTED_LEN].item())
+        for m in eng.mixers:
+            if isinstance(m, FullAttn):
+                snap.append((m.k_cache[:, C0 : C0 + self.T].clone(), m.v_cache[:, C0 : C0 + self.T].clone(), C0))
+            else:
+                snap.append((m.conv_ring.clone(), m.state_ring.clone()))
+        return snap
+
+    def _restore(self, snap: List) -> None:
+        eng = self.eng
+        eng.ctx.ctl.copy_(snap[0])
+        for m, s in zip(eng.mixers, snap[1:]):
+            if isinstance(m, FullAttn):
+                k, v, C0 = s
+                m.k_cache[:, C0 : C0 + self.T] = k
+                m.v_cache[:, C0 : C0 + self.T] = v
+            else:
+                m.conv_ring.copy_(s[0])
+                m.state_ring.copy_(s[1])
