@@ -116,7 +116,11 @@ int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, v
 // plane order) and, with group_rows > 0, W stored as K / group_k matrices [group_rows, group_k] one after the other (expert
 // down projections; sw [groups][group_rows / 128][group_k / 128], R == group_rows).  K / 128 / ksplit <= 64.
 int nexrt_tc_gemm_fp8_ex(const void* wq, const float* sw, int64_t ldw, const void* xq, const float* sx, void* y, int T, int R, int K, int ldy,
-                         int ksplit, int group_k, int group_rows, int* status, void* stream);
+                         int ksplit, int group_k, int group_rows, const int* used, int used_rows, int* status, void* stream);
+/* used (optional, one int per group): plain matrix - row tiles of group m0 / used_rows with used == 0 are skipped (their
+   output is left untouched); grouped K - the K blocks of unused groups are left out of the walk */
+int nexrt_tc_gemm_bf16_ex(const void* w, int64_t ldw, const void* x, int64_t ldx, void* y, int T, int R, int K, int ldy, int ksplit, int* status,
+                          void* stream);   /* K / 64 must divide into ksplit non-empty ranges of at most 64 blocks */
 // Optional RMSNorm (gamma != null, stored as the full multiplier) then per-row, per-128-column e4m3 quantisation.
 int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream);
 
@@ -127,7 +131,11 @@ int nexrt_prefill_advance(void* ctl, int rows, void* stream);
 int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, void* stream);
 int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream);
 int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, void* stream);
+int nexrt_moe_mark_used(const void* ids, void* used, int n_ids, int n_total, void* stream);   /* used[e] = 1 for every routed expert id */
 int nexrt_planes_residual(void* x, const void* y, void* sum_out, int64_t n, int ksplit, void* stream);
+int nexrt_gdn_chunk(const void* pre, const void* xn, const void* ba_w, const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl,
+                    void* conv_ring, void* qkv, void* z, void* beta, void* g, void* state_ring, void* out, int H, int R, int C, int nv, int nqk, int T,
+                    int conv_ring_len, int state_ring_len, int ksplit, void* stream);   /* conv + gates + delta rule of T rows after their q|k|v|z projection (pre: [ksplit][T][R]) */
 
 // ---- experts of a multi-row step on tcgen05 (tc_moe.cu) -------------------------------------------------------
 // Gate/up of every distinct expert named in ids [M][S] (streamed once each); planes is e4m3 scratch [3M][H].

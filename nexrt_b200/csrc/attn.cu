@@ -149,7 +149,7 @@ struct AttnDecodeArgs {
     float eps;
     // context parallel
     int ldq, ldk;             // row strides of q_raw / k_raw in floats (0: packed)
-    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate
+    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate; 4: the new k rows are in the cache already
     int window;               // > 0: sliding window, only the last `window` positions are attended
     int cp_size, cp_rank;     // window of the prefix this rank attends
     LLChannel ch;             // partial exchange inside the cp group (world == cp_size)
@@ -166,11 +166,19 @@ __global__ void __launch_bounds__(256) attn_front_tail_kernel(AttnFrontArgs a, c
     if (row >= R) return;
     const int C0 = a.ctl[kCtlCommittedLen];
     const bool interleaved = a.ngate == a.nq;
-    for (int m = 0; m < a.M; ++m) {
-        float v = 0.f;
-        for (int ks = 0; ks < ksplit; ++ks) v += pre[(static_cast<size_t>(ks) * a.M + m) * R + row];
-        attn_front_row(a, row, m, v, C0, interleaved);
+    // blockIdx.y names a block of eight token rows (one block in a decode step, several in a prefill chunk); the loads of
+    // the block are all requested before the first scatter
+    const int m0 = blockIdx.y * kMaxRows;
+    float v[kMaxRows];
+#pragma unroll
+    for (int i = 0; i < kMaxRows; ++i) {
+        v[i] = 0.f;
+        if (m0 + i < a.M)
+            for (int ks = 0; ks < ksplit; ++ks) v[i] += pre[(static_cast<size_t>(ks) * a.M + m0 + i) * R + row];
     }
+#pragma unroll
+    for (int i = 0; i < kMaxRows; ++i)
+        if (m0 + i < a.M) attn_front_row(a, row, m0 + i, v[i], C0, interleaved);
 }
 
 constexpr int kRowsPerPass = 4;
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
             const float val = dst[lane + 32 * i];
             dst[lane + 32 * i] = is_q ? val * qscale : bf16_round(val);
         }
-        if (!is_q && split == 0 && C0 + m < a.cache_len) {
+        if (!is_q && split == 0 && C0 + m < a.cache_len && !(a.flags & 4)) {
             // every rank keeps the full cache: the new k rows are appended by split 0
 #pragma unroll
             for (int i = 0; i < EL; ++i)
@@ -513,11 +521,12 @@ using namespace nexrt;
 
 extern "C" int nexrt_attn_front_tail(const void* pre, const void* ctl, void* q_raw, void* gate, void* k_raw, void* v_cache, int hd, int nq, int ngate, int kvh,
                                      int M, int cache_len, int ksplit, void* stream) {
-    if (M < 1 || M > kMaxRows || ksplit < 1) return cudaErrorInvalidValue;
+    if (M < 1 || M > 128 || ksplit < 1) return cudaErrorInvalidValue;   // no per-row state in the kernel: a prefill chunk goes through in one launch
     AttnFrontArgs a{nullptr, nullptr, nullptr, nullptr, static_cast<const int*>(ctl), static_cast<float*>(q_raw), static_cast<float*>(gate),
                     static_cast<float*>(k_raw), static_cast<__nv_bfloat16*>(v_cache), 0, hd, nq, ngate, kvh, M, cache_len, 0.f};
     const int R = (nq + ngate + 2 * kvh) * hd;
-    return launch(attn_front_tail_kernel, dim3((R + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), a, static_cast<const float*>(pre), R, ksplit);
+    return launch(attn_front_tail_kernel, dim3((R + 255) / 256, (M + kMaxRows - 1) / kMaxRows), dim3(256), 0, static_cast<cudaStream_t>(stream), a,
+                  static_cast<const float*>(pre), R, ksplit);
 }
 
 extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w, const void* s, const void* ctl, void* q_raw, void* gate,

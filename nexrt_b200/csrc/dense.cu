@@ -173,8 +173,9 @@ extern "C" int nexrt_dense_bf16(const void* in, const void* gamma, const void* w
 extern "C" int nexrt_kv_publish(const void* kv, int ld, int k_off, int v_off, const void* kn, const void* rope_table, const void* ctl,
                                 void* k_cache, void* v_cache, int hd, int kvh, int M, int cache_len, int rotary, float eps, int ring,
                                 void* stream) {
-    if (M < 1 || M > kMaxRows || hd % 32 || hd > 256 || rotary > hd || rotary % 2) return cudaErrorInvalidValue;
-    return launch(kv_publish_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(kv), ld, k_off, v_off,
+    if (M < 1 || M > 128 || hd % 32 || hd > 256 || rotary > hd || rotary % 2) return cudaErrorInvalidValue;
+    const int ctas = M * kvh <= 8 ? 1 : (M * kvh + 7) / 8;     // eight vectors per CTA (a prefill chunk publishes up to 128 rows)
+    return launch(kv_publish_kernel, dim3(ctas < 16 ? ctas : 16), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(kv), ld, k_off, v_off,
                   static_cast<const float*>(kn), static_cast<const float2*>(rope_table), static_cast<const int*>(ctl),
                   static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), hd, kvh, M, cache_len, rotary, eps, ring);
 }

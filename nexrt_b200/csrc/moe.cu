@@ -301,20 +301,22 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
 // Top-k stage of the wide router (multi-row steps): the logits arrive as K-split partial planes
 // partial[ks][m][rows_pad] from the tcgen05 rows GEMM; they are added in a fixed order into shared memory, kept
 // in a.logits for inspection, and selected exactly like the fused router does.
-__global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ksplit) {
+__global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ksplit, int rpc) {
     extern __shared__ __align__(16) float lg_s[];
     pdl_launch_dependents();
     pdl_wait();
     const int rows = a.E + 1;
+    // one CTA per block of rpc token rows (a decode step is one block of up to kMaxRows; a prefill chunk has many small ones)
+    const int m0 = blockIdx.x * rpc, mb = min(rpc, a.M - m0);
     // four consecutive experts per thread, every K-split plane of them requested before the first add (16-byte
     // loads, all in flight): the sum is one or two round trips to L2
     const int quads = a.rows_pad / 4;
-    for (int q = threadIdx.x; q < a.M * quads; q += blockDim.x) {
+    for (int q = threadIdx.x; q < mb * quads; q += blockDim.x) {
         const int m = q / quads, e0 = (q % quads) * 4;
         float4 v[16];
 #pragma unroll
         for (int ks = 0; ks < 16; ++ks)
-            v[ks] = ks < ksplit ? __ldcg(reinterpret_cast<const float4*>(a.partial + (static_cast<size_t>(ks) * a.M + m) * a.rows_pad + e0))
+            v[ks] = ks < ksplit ? __ldcg(reinterpret_cast<const float4*>(a.partial + (static_cast<size_t>(ks) * a.M + m0 + m) * a.rows_pad + e0))
                                 : make_float4(0.f, 0.f, 0.f, 0.f);
         float4 t = v[0];
 #pragma unroll
@@ -325,11 +327,16 @@ __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ks
         for (int i = 0; i < 4; ++i)
             if (e0 + i < rows) {
                 lg_s[m * rows + e0 + i] = tv[i];
-                a.logits[m * rows + e0 + i] = tv[i];
+                a.logits[(m0 + m) * rows + e0 + i] = tv[i];
             }
     }
     __syncthreads();
-    router_topk<true>(a, lg_s);
+    RouterArgs b = a;
+    b.M = mb;
+    b.logits = a.logits + static_cast<size_t>(m0) * rows;
+    b.ids = a.ids + static_cast<size_t>(m0) * (a.topk + 1);
+    b.wts = a.wts + static_cast<size_t>(m0) * (a.topk + 1);
+    router_topk<true>(b, lg_s);
 }
 
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
@@ -445,10 +452,11 @@ extern "C" int nexrt_moe_router(const void* x, const void* post_ln, const void* 
 }
 
 extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_pad, void* logits, void* ids, void* wts, int E, int topk, int M, void* stream) {
-    if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1 || ksplit > 16 || rows_pad % 4) return cudaErrorInvalidValue;
+    if (M < 1 || M > 1024 || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1 || ksplit > 16 || rows_pad % 4) return cudaErrorInvalidValue;
     RouterArgs a{nullptr, nullptr, nullptr, static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), nullptr, 0, E, topk, M, 0.f,
                  const_cast<float*>(static_cast<const float*>(partial)), rows_pad, nullptr};
-    return launch(moe_topk_rows_kernel, dim3(1), dim3(256), sizeof(float) * M * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit);
+    const int rpc = M <= kMaxRows ? M : 2;
+    return launch(moe_topk_rows_kernel, dim3((M + rpc - 1) / rpc), dim3(256), sizeof(float) * rpc * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit, rpc);
 }
 
 extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I,

@@ -55,6 +55,10 @@ struct Args {
     // grouped K (expert down projections stored as [group][rows][group_kb * 128]): K block kb of the product is
     // block kb % group_kb of group kb / group_kb, whose rows start at (kb / group_kb) * group_rows; 0 = plain matrix
     int group_kb, group_rows;
+    // optional skip list (dense expert products): used[g] == 0 means nothing is routed to group g.  Plain matrix: a row tile
+    // whose group (m0 / used_rows) is unused does nothing; grouped K: the K blocks of unused groups are left out of the walk
+    const int* used;
+    int used_rows;
 };
 
 template <bool FP8, int BN>
@@ -77,9 +81,31 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;     // token tiles of one weight tile are neighbours: they share it in L2
+    // launched with programmatic serialisation: the grid may become resident while its predecessor drains; nothing of the
+    // predecessor's output (skip list, activations, scales) is touched before the wait
+    pdl_launch_dependents();
+    pdl_wait();
+    if (a.used != nullptr && a.group_kb == 0 && a.used[m0 / a.used_rows] == 0) return;   // the whole CTA: nothing allocated yet
+    __shared__ unsigned short s_kb[kMaxKBlocks];               // K blocks this CTA walks (offsets from kb0), in order
+    __shared__ int s_nact;
     const int kb0 = static_cast<int>(blockIdx.z) * a.kb_per;     // first K block of this CTA's range
-    const int KB = max(0, min(a.kb_per, a.KB - kb0));
-    constexpr uint32_t kCols = kAccBufs * BN;                 // power of two, 64..256 columns
+    const int KBrange = max(0, min(a.kb_per, a.KB - kb0));
+    constexpr uint32_t kCols = kAccBufs * BN;
+    if (threadIdx.x < 32) {
+        // compact the range to the blocks of used groups (all of them without a skip list)
+        const int l = threadIdx.x;
+        bool f[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kb = l + 32 * h;
+            f[h] = kb < KBrange && (a.used == nullptr || a.group_kb == 0 || a.used[(kb0 + kb) / a.group_kb] != 0);
+        }
+        const unsigned b0 = __ballot_sync(0xffffffffu, f[0]), b1 = __ballot_sync(0xffffffffu, f[1]);
+        const unsigned lt = (1u << l) - 1u;
+        if (f[0]) s_kb[__popc(b0 & lt)] = static_cast<unsigned short>(l);
+        if (f[1]) s_kb[__popc(b0) + __popc(b1 & lt)] = static_cast<unsigned short>(l + 32);
+        if (l == 0) s_nact = __popc(b0) + __popc(b1);
+    }                 // power of two, 64..256 columns
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -98,6 +124,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int KB = s_nact;
 
     if (warp == 0) {
         // ---- TMA producer -----------------------------------------------------------------------------
@@ -108,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
                 mbar_expect_tx(full(s), L::kA + L::kB);
                 const uint32_t dst = smem_u32(smem + s * L::kStage);
                 constexpr int kElems = FP8 ? kSpan : kSpan / 2;          // elements of K per block
-                const int kg = kb0 + kb;
+                const int kg = kb0 + s_kb[kb];
                 if (a.group_kb > 0) tma_load_2d(dst, &map_w, (kg % a.group_kb) * kElems, (kg / a.group_kb) * a.group_rows + m0, full(s));
                 else tma_load_2d(dst, &map_w, kg * kElems, m0, full(s));
                 tma_load_2d(dst + L::kA, &map_x, kg * kElems, n0, full(s));
@@ -141,10 +168,10 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
         if (FP8) {
             for (int i = et; i < KB * BN; i += 128) {
                 const int kb = i / BN, n = i % BN;
-                sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * a.KB + kb0 + kb] : 0.f;
+                sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * a.KB + kb0 + s_kb[kb]] : 0.f;
             }
             for (int i = et; i < KB; i += 128) {     // weight block scales of this row tile
-                const int kg = kb0 + i;
+                const int kg = kb0 + s_kb[i];
                 sws[i] = a.group_kb > 0 ? __ldg(a.sw + (static_cast<size_t>(kg / a.group_kb) * (a.group_rows / kBM) + blockIdx.y) * a.group_kb + kg % a.group_kb)
                                         : __ldg(a.sw + static_cast<size_t>(blockIdx.y) * a.KB + kg);
             }
@@ -223,6 +250,8 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
 // x [T, ldx] bf16 (or fp32 when x_fp32), gamma [K] fp32 or null, xq [T, K] e4m3, sx [T, K/128] fp32.
 __global__ void act_quant_kernel(const void* __restrict__ x, int x_fp32, int ldx, const float* __restrict__ gamma, float eps,
                                  __nv_fp8_storage_t* __restrict__ xq, float* __restrict__ sx, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int KB = K / 128;
     __shared__ float red[32];
@@ -282,8 +311,7 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const Args& 
         configured = true;
     }
     dim3 grid((a.T + BN - 1) / BN, (a.R + kBM - 1) / kBM, (a.KB + a.kb_per - 1) / a.kb_per);
-    kern<<<grid, kThreads, L::total(a.kb_per, FP8), stream>>>(mw, mx, a);
-    return cudaGetLastError();
+    return static_cast<cudaError_t>(launch(kern, grid, dim3(kThreads), L::total(a.kb_per, FP8), stream, mw, mx, a));
 }
 
 }  // namespace
@@ -371,7 +399,7 @@ int nexrt_tc_gemm_fp8(const void* wq, const float* sw, int64_t ldw, const void* 
 // [group_rows, group_k] one after the other (expert down projections): K = groups * group_k, R = group_rows, block
 // scales sw [groups][group_rows / 128][group_k / 128].  Any K whose per-CTA share is at most 64 blocks.
 int nexrt_tc_gemm_fp8_ex(const void* wq, const float* sw, int64_t ldw, const void* xq, const float* sx, void* y, int T, int R, int K, int ldy,
-                         int ksplit, int group_k, int group_rows, int* status, void* stream) {
+                         int ksplit, int group_k, int group_rows, const int* used, int used_rows, int* status, void* stream) {
     if (T <= 0 || R <= 0 || K <= 0 || K % 128 || ksplit < 1) return cudaErrorInvalidValue;
     const int KB = K / 128, kb_per = (KB + ksplit - 1) / ksplit;
     if (kb_per > kMaxKBlocks) return cudaErrorInvalidValue;
@@ -381,7 +409,8 @@ int nexrt_tc_gemm_fp8_ex(const void* wq, const float* sw, int64_t ldw, const voi
     const bool okw = group_rows > 0 ? tensor_map(&mw, wq, static_cast<uint64_t>(K / group_k) * group_rows, group_k, ldw, kBM, false)
                                     : tensor_map(&mw, wq, R, K, ldw, kBM, false);
     if (!okw || !tensor_map(&mx, xq, T, K, K, bn, false)) return cudaErrorInvalidValue;
-    Args a{sw, sx, y, T, R, KB, ldy, 0, status, kb_per, group_rows > 0 ? group_k / 128 : 0, group_rows};
+    if (used != nullptr && group_rows == 0 && (used_rows <= 0 || used_rows % kBM)) return cudaErrorInvalidValue;
+    Args a{sw, sx, y, T, R, KB, ldy, 0, status, kb_per, group_rows > 0 ? group_k / 128 : 0, group_rows, used, used_rows};
     auto s = static_cast<cudaStream_t>(stream);
     if (bn == 16) return launch_tc<true, 16>(mw, mx, a, s);
     if (bn == 32) return launch_tc<true, 32>(mw, mx, a, s);
@@ -402,11 +431,26 @@ int nexrt_tc_gemm_bf16(const void* w, int64_t ldw, const void* x, int64_t ldx, v
     return launch_tc<false, 64>(mw, mx, a, s);
 }
 
+// The bf16 product with K split over ksplit CTAs per tile: fp32 partial planes of T * ldy elements each.
+int nexrt_tc_gemm_bf16_ex(const void* w, int64_t ldw, const void* x, int64_t ldx, void* y, int T, int R, int K, int ldy, int ksplit, int* status,
+                          void* stream) {
+    if (T <= 0 || R <= 0 || K <= 0 || K % 64 || ksplit < 1) return cudaErrorInvalidValue;
+    const int KB = K / 64, kb_per = (KB + ksplit - 1) / ksplit;
+    if (kb_per > kMaxKBlocks || (KB + kb_per - 1) / kb_per != ksplit) return cudaErrorInvalidValue;   // every plane needs a non-empty K range
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    if (!tensor_map(&mw, w, R, K, ldw, kBM, true) || !tensor_map(&mx, x, T, K, ldx, bn, true)) return cudaErrorInvalidValue;
+    Args a{nullptr, nullptr, y, T, R, KB, ldy, 0, status, kb_per, 0, 0};
+    auto s = static_cast<cudaStream_t>(stream);
+    if (bn == 16) return launch_tc<false, 16>(mw, mx, a, s);
+    if (bn == 32) return launch_tc<false, 32>(mw, mx, a, s);
+    return launch_tc<false, 64>(mw, mx, a, s);
+}
+
 // Optional RMSNorm (gamma != null) followed by per-row, per-128-column e4m3 quantisation.
 int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream) {
     if (T <= 0 || K <= 0 || K % 128) return cudaErrorInvalidValue;
-    act_quant_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, x_fp32, ldx, gamma, eps, static_cast<__nv_fp8_storage_t*>(xq), sx, K);
-    return cudaGetLastError();
+    return launch(act_quant_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), x, x_fp32, ldx, gamma, eps, static_cast<__nv_fp8_storage_t*>(xq), sx, K);
 }
 
 }  // extern "C"

@@ -71,7 +71,9 @@ _PROTOTYPES = {
     "nexrt_tc_gemm_fp8": [vp, vp, c_int64, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
     "nexrt_tc_gemm_bf16": [vp, c_int64, vp, c_int64, vp, ci, ci, ci, ci, ci, vp, vp],
     "nexrt_act_quant": [vp, ci, ci, vp, cf, vp, vp, ci, ci, vp],
-    "nexrt_tc_gemm_fp8_ex": [vp, vp, c_int64, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp, vp],
+    "nexrt_tc_gemm_bf16_ex": [vp, c_int64, vp, c_int64, vp, ci, ci, ci, ci, ci, vp, vp],
+    "nexrt_tc_gemm_fp8_ex": [vp, vp, c_int64, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp, ci, vp, vp],
+    "nexrt_moe_mark_used": [vp, vp, ci, ci, vp],
     "nexrt_prefill_embed": [vp, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_prefill_ctl": [vp, vp, ci, ci, vp],
     "nexrt_prefill_advance": [vp, ci, vp],
@@ -79,6 +81,7 @@ _PROTOTYPES = {
     "nexrt_gdn_gate_quant": [vp, vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp],
     "nexrt_planes_residual": [vp, vp, vp, c_int64, ci, vp],
+    "nexrt_gdn_chunk": [vp] * 14 + [ci] * 9 + [vp],
     "nexrt_rows_norm_split": [vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_tc_rows_gemm": [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp],
     "nexrt_gdn_front_tail": [vp] * 12 + [ci] * 7 + [vp],

@@ -63,15 +63,28 @@ def bf16_gemm(w: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = No
 
 
 def fp8_gemm_split(wq: torch.Tensor, sw: torch.Tensor, xq: torch.Tensor, sx: torch.Tensor, out: torch.Tensor, ksplit: int = 1,
-                   group_k: int = 0, group_rows: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   group_k: int = 0, group_rows: int = 0, used: Optional[torch.Tensor] = None, used_rows: int = 0,
+                   status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The block-scaled FP8 product with K split over ``ksplit`` CTAs per tile: ``out [ksplit, T, R]`` fp32 partial
     planes (add them in plane order).  With ``group_rows`` the weight is a stack of ``K / group_k`` matrices
     ``[group_rows, group_k]`` (the experts' down projections, ``w2 [E+1, H, I]`` viewed as ``[(E+1) * H, I]``) whose
-    K extents are concatenated: ``out[t, r] = sum_g x[t, g*group_k:(g+1)*group_k] . w[g, r, :]``."""
+    K extents are concatenated: ``out[t, r] = sum_g x[t, g*group_k:(g+1)*group_k] . w[g, r, :]``.  ``used`` (int32, one
+    entry per group) leaves out what nothing is routed to: with a stack, the K blocks of unused groups; with a plain
+    matrix whose rows come in groups of ``used_rows``, the row tiles of unused groups (their output is not written)."""
     T, K = xq.shape
     R = group_rows if group_rows else wq.shape[0]
     if out.dtype != torch.float32 or out.numel() < ksplit * T * R or not (xq.is_contiguous() and sx.is_contiguous() and sw.is_contiguous()):
         raise ValueError("fp8_gemm_split: output / operand layout")
-    check(lib().nexrt_tc_gemm_fp8_ex(ptr(wq), ptr(sw), wq.stride(0), ptr(xq), ptr(sx), ptr(out), T, R, K, R, ksplit, group_k, group_rows, ptr(status), _stream()),
+    check(lib().nexrt_tc_gemm_fp8_ex(ptr(wq), ptr(sw), wq.stride(0), ptr(xq), ptr(sx), ptr(out), T, R, K, R, ksplit, group_k, group_rows, ptr(used), used_rows, ptr(status), _stream()),
           "tc_gemm_fp8_ex")
+    return out
+
+
+def bf16_gemm_split(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, ksplit: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The bf16 product with K split over ``ksplit`` CTAs per tile: ``out [ksplit, T, R]`` fp32 partial planes."""
+    R, K = w.shape
+    T = x.shape[0]
+    if x.shape[1] != K or w.stride(1) != 1 or x.stride(1) != 1 or out.dtype != torch.float32 or out.numel() < ksplit * T * R or not out.is_contiguous():
+        raise ValueError("bf16_gemm_split: operand / output layout")
+    check(lib().nexrt_tc_gemm_bf16_ex(ptr(w), w.stride(0), ptr(x), x.stride(0), ptr(out), T, R, K, R, ksplit, ptr(status), _stream()), "tc_gemm_bf16_ex")
     return out

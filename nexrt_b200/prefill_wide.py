@@ -30,7 +30,7 @@ import torch.distributed as dist
 
 from .attn import FullAttn
 from .ops.lib import check, ptr
-from .ops.tc_gemm import bf16_gemm, fp8_gemm, fp8_gemm_split
+from .ops.tc_gemm import bf16_gemm_split, fp8_gemm, fp8_gemm_split
 from .quant import FP8
 from .runtime.control import CTL_WORDS, Ctl
 
@@ -66,18 +66,29 @@ class WidePrefill:
         self.xq, self.sx = torch.zeros(T, H, dtype=FP8, device=dev), z(T, H // 128)
         self.xn = z(T, H)
         self.planes = z(T, 2 * H, dtype=bf)
-        self.pre = z(T * max(spec.gdn_front_rows, spec.attn_front_rows))
+        kb = H // 128
+        self.front_ksplit = next(k for k in (4, 2, 1) if kb % k == 0)     # K split of the GDN front projection (few row tiles)
+        self.pre = z(T * max(self.front_ksplit * spec.gdn_front_rows, spec.attn_front_rows))
         self.ctl_tab = z(self.n_sub, CTL_WORDS, dtype=i32)
         self.gdn_qkv, self.gdn_z = z(T, spec.gdn_qkv_rows), z(T, spec.gdn_local)
         self.gdn_beta, self.gdn_g, self.gdn_out = z(T, spec.gdn_v), z(T, spec.gdn_v), z(T, spec.gdn_local)
         self.gate, self.attn_out = z(T, spec.q_heads, cfg.head_dim), z(T, spec.attn_local)
+        self.q_raw, self.k_raw = z(T, spec.q_heads, cfg.head_dim), z(T, spec.kv_heads, cfg.head_dim)
+        # the attention sub-steps of a chunk run side by side: one split-KV workspace, ticket and stream per sub-step
+        self.ws_acc = z(self.n_sub, *c.ws_acc.shape)
+        self.ws_ml = z(self.n_sub, *c.ws_ml.shape)
+        self.attn_ticket = z(self.n_sub, spec.kv_heads, dtype=i32)
+        self.side = [torch.cuda.Stream(dev) for _ in range(self.n_sub)]
         kmax = max(spec.gdn_local, spec.attn_local)
         self.oq, self.os = torch.zeros(T * kmax, dtype=FP8, device=dev), z(T * (kmax // 128))
         self.S, self.n_total = cfg.top_k + 1, cfg.n_experts + 1
         self.rows_pad = eng.moes[0].rows_pad
-        self.logits = z(T, self.rows_pad)
+        kb64 = H // 64
+        self.router_ksplit = next(k for k in (8, 4, 2, 1) if kb64 % k == 0)
+        self.logits = z(2 * self.router_ksplit, T, self.rows_pad)
         self.moe_logits, self.moe_ids, self.moe_wts = z(T, cfg.n_experts + 1), z(T, self.S, dtype=i32), z(T, self.S)
         I = spec.inter
+        self.used = z(self.n_total, dtype=i32)
         self.gu = z(T, self.n_total * 2 * I)
         self.hq, self.hs = torch.zeros(T, self.n_total * I, dtype=FP8, device=dev), z(T, self.n_total * I // 128)
         # K split of the expert down product: at most 64 K blocks per CTA, and about two CTAs per SM over the grid
@@ -109,20 +120,16 @@ class WidePrefill:
         st, w, H = c.stream(), m.w, cfg.hidden
         R, C, nv, K = spec.gdn_front_rows, spec.gdn_qkv_rows, spec.gdn_v, spec.gdn_local
         check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), ptr(self.xn), None, H, T, cfg.rms_eps, st), "norm_rows")
-        pre = self.pre[: T * R].view(T, R)
-        fp8_gemm(w["front_w"], w["front_s"], self.xq, self.sx, out=pre, status=c.status)
-        for j in range(self.n_sub):
-            r = slice(j * SUB, (j + 1) * SUB)
-            check(
-                lib.nexrt_gdn_front_tail(ptr(pre[r]), ptr(self.xn[r]), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]), ptr(w["dt_bias"]), ptr(self.ctl_tab[j]),
-                                         ptr(m.conv_ring), ptr(self.gdn_qkv[r]), ptr(self.gdn_z[r]), ptr(self.gdn_beta[r]), ptr(self.gdn_g[r]), H, R, C, nv, SUB,
-                                         m.conv_ring_len, 1, st),
-                "gdn_front_tail",
-            )
-        for j in range(self.n_sub):
-            r = slice(j * SUB, (j + 1) * SUB)
-            check(lib.nexrt_gdn_core(ptr(self.gdn_qkv[r]), ptr(self.gdn_beta[r]), ptr(self.gdn_g[r]), ptr(self.ctl_tab[j]), ptr(m.state_ring), ptr(self.gdn_out[r]),
-                                     spec.gdn_qk, nv, SUB, m.state_ring_len, C, st), "gdn_core")
+        ks = self.front_ksplit
+        pre = self.pre[: ks * T * R]
+        fp8_gemm_split(w["front_w"], w["front_s"], self.xq, self.sx, pre, ksplit=ks, status=c.status)
+        # conv ring + gates and the delta rule for all T rows: two kernels, the state carried in registers along the chunk
+        check(
+            lib.nexrt_gdn_chunk(ptr(pre), ptr(self.xn), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]), ptr(w["dt_bias"]), ptr(self.ctl_tab[0]),
+                                ptr(m.conv_ring), ptr(self.gdn_qkv), ptr(self.gdn_z), ptr(self.gdn_beta), ptr(self.gdn_g), ptr(m.state_ring), ptr(self.gdn_out),
+                                H, R, C, nv, spec.gdn_qk, T, m.conv_ring_len, m.state_ring_len, ks, st),
+            "gdn_chunk",
+        )
         oq, os_ = self.oq[: T * K].view(T, K), self.os[: T * (K // 128)].view(T, K // 128)
         check(lib.nexrt_gdn_gate_quant(ptr(self.gdn_out), ptr(self.gdn_z), ptr(w["gnorm_w"]), ptr(oq), ptr(os_), K, T, cfg.rms_eps, st), "gdn_gate_quant")
         fp8_gemm(w["out_w"], w["out_s"], oq, os_, out=self.y[0], status=c.status)
@@ -138,17 +145,28 @@ class WidePrefill:
         pre = self.pre[: T * R].view(T, R)
         fp8_gemm(w["front_w"], w["front_s"], self.xq, self.sx, out=pre, status=c.status)
         rope = c.rope_table(m.cache_len)
+        base = self.ctl_tab[0]
+        # q / gate / k rows to scratch and v rows to the cache for the whole chunk, then the chunk's k rows (norm + RoPE) to
+        # the cache: after that the 8-row attention sub-steps do not depend on each other and run side by side
+        check(lib.nexrt_attn_front_tail(ptr(pre), ptr(base), ptr(self.q_raw), ptr(self.gate), ptr(self.k_raw), ptr(m.v_cache), hd, nq, nq, kvh, T,
+                                        m.cache_len, 1, st), "attn_front_tail")
+        check(lib.nexrt_kv_publish(ptr(pre), R, 2 * nq * hd, (2 * nq + kvh) * hd, ptr(w["kn"]), ptr(rope), ptr(base), ptr(m.k_cache), ptr(m.v_cache), hd, kvh, T,
+                                   m.cache_len, cfg.rotary_dim, cfg.rms_eps, 0, st), "kv_publish")
+        cur = torch.cuda.current_stream(eng.dev)
         for j in range(self.n_sub):
             r = slice(j * SUB, (j + 1) * SUB)
-            ctl = self.ctl_tab[j]
-            check(lib.nexrt_attn_front_tail(ptr(pre[r]), ptr(ctl), ptr(c.q_raw), ptr(self.gate[r]), ptr(c.k_raw), ptr(m.v_cache), hd, nq, nq, kvh, SUB,
-                                            m.cache_len, 1, st), "attn_front_tail")
-            check(
-                lib.nexrt_attn_decode(ptr(c.q_raw), ptr(self.gate[r]), ptr(c.k_raw), ptr(w["qn"]), ptr(w["kn"]), ptr(c.inv_freq), ptr(rope), ptr(ctl), ptr(m.k_cache),
-                                      ptr(m.v_cache), ptr(c.ws_acc), ptr(c.ws_ml), ptr(c.attn_ticket), ptr(self.attn_out[r]), hd, nq, nq, kvh, SUB, m.cache_len,
-                                      cfg.rotary_dim, c.n_splits, cfg.rms_eps, 0, 0, 0, 0, 1, 0, None, 0, st),
-                "attn_decode",
-            )
+            side = self.side[j]
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                check(
+                    lib.nexrt_attn_decode(ptr(self.q_raw[r]), ptr(self.gate[r]), ptr(self.k_raw[r]), ptr(w["qn"]), ptr(w["kn"]), ptr(c.inv_freq), ptr(rope),
+                                          ptr(self.ctl_tab[j]), ptr(m.k_cache), ptr(m.v_cache), ptr(self.ws_acc[j]), ptr(self.ws_ml[j]), ptr(self.attn_ticket[j]),
+                                          ptr(self.attn_out[r]), hd, nq, nq, kvh, SUB, m.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, 4, 0, 0, 0, 1, 0,
+                                          None, 0, c.stream()),
+                    "attn_decode",
+                )
+        for j in range(self.n_sub):
+            cur.wait_stream(self.side[j])
         oq, os_ = self.oq[: T * K].view(T, K), self.os[: T * (K // 128)].view(T, K // 128)
         check(lib.nexrt_act_quant(ptr(self.attn_out), 1, K, None, cfg.rms_eps, ptr(oq), ptr(os_), T, K, st), "act_quant")
         fp8_gemm(w["out_w"], w["out_s"], oq, os_, out=self.y[0], status=c.status)
@@ -159,19 +177,22 @@ class WidePrefill:
         c, lib, cfg, spec = eng.ctx, eng.ctx.lib, eng.cfg, eng.spec
         st, w, H, I, S, n_total = c.stream(), moe.w, cfg.hidden, spec.inter, self.S, self.n_total
         check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["post_ln"]), ptr(self.xq), ptr(self.sx), None, ptr(self.planes), H, T, cfg.rms_eps, st), "norm_rows")
-        # router: bf16 weights, activations as hi + lo bf16 planes in two accumulating GEMMs
-        bf16_gemm(w["router_w_pad"], self.planes[:, :H], out=self.logits, status=c.status)
-        bf16_gemm(w["router_w_pad"], self.planes[:, H:], out=self.logits, accumulate=True, status=c.status)
-        for j in range(self.n_sub):
-            r = slice(j * SUB, (j + 1) * SUB)
-            check(lib.nexrt_moe_router_topk(ptr(self.logits[r]), 1, self.rows_pad, ptr(self.moe_logits[r]), ptr(self.moe_ids[r]), ptr(self.moe_wts[r]),
-                                            cfg.n_experts, cfg.top_k, SUB, st), "moe_router_topk")
+        # router: bf16 weights, activations as hi + lo bf16 planes, each product split over K; the top-k kernel adds the
+        # 2 * ksplit partial planes in a fixed order (one CTA per eight rows)
+        ks = self.router_ksplit
+        bf16_gemm_split(w["router_w_pad"], self.planes[:, :H], self.logits[:ks], ks, status=c.status)
+        bf16_gemm_split(w["router_w_pad"], self.planes[:, H:], self.logits[ks:], ks, status=c.status)
+        check(lib.nexrt_moe_router_topk(ptr(self.logits), 2 * ks, self.rows_pad, ptr(self.moe_logits), ptr(self.moe_ids), ptr(self.moe_wts),
+                                        cfg.n_experts, cfg.top_k, T, st), "moe_router_topk")
         # experts, dense: gate/up of every expert for every row, activation of the routed pairs, down over all experts
-        fp8_gemm(w["w13"].view(n_total * 2 * I, H), w["w13_s"].view(-1, H // 128), self.xq, self.sx, out=self.gu, status=c.status)
+        # (experts no row of the chunk routes to are skipped: their weights are not read)
+        check(lib.nexrt_moe_mark_used(ptr(self.moe_ids), ptr(self.used), T * S, n_total, st), "moe_mark_used")
+        fp8_gemm_split(w["w13"].view(n_total * 2 * I, H), w["w13_s"].view(-1, H // 128), self.xq, self.sx, self.gu, ksplit=1, used=self.used, used_rows=2 * I,
+                       status=c.status)
         self.hq.view(torch.uint8).zero_()
         self.hs.zero_()
         check(lib.nexrt_moe_dense_act(ptr(self.gu), ptr(self.moe_ids), ptr(self.moe_wts), ptr(self.hq), ptr(self.hs), I, S, T, n_total, st), "moe_dense_act")
-        fp8_gemm_split(w["w2"].view(n_total * H, I), w["w2_s"], self.hq, self.hs, self.y, ksplit=self.down_ksplit, group_k=I, group_rows=H, status=c.status)
+        fp8_gemm_split(w["w2"].view(n_total * H, I), w["w2_s"], self.hq, self.hs, self.y, ksplit=self.down_ksplit, group_k=I, group_rows=H, used=self.used, status=c.status)
         self._finish(self.down_ksplit)
 
     def _chunk(self) -> None:

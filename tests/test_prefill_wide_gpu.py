@@ -60,6 +60,34 @@ def test_grouped_k_walks_a_stack_of_matrices(T, G, R, gk, ksplit):
     assert int(status.item()) == 0 and rel(out.sum(0), want) < 1e-5
 
 
+def test_skip_list_leaves_out_unused_groups():
+    g = torch.Generator(device="cuda").manual_seed(11)
+    T, G, R, gk = 32, 12, 256, 128
+    used = torch.tensor([1, 0, 1, 1, 0, 0, 1, 0, 1, 1, 1, 0], dtype=torch.int32, device="cuda")
+    # stack walked along K (expert down): unused groups do not contribute
+    wq, sw = quantize_blockwise(torch.randn(G * R, gk, device="cuda", generator=g) * 0.05)
+    xq, sx = act_quant((torch.randn(T, G * gk, device="cuda", generator=g) * 2).to(torch.bfloat16))
+    wd = dequantize_blockwise(wq, sw).reshape(G, R, gk).double()
+    xd = _deq_act(xq, sx).double().reshape(T, G, gk) * used.double()[None, :, None]
+    want = torch.einsum("tgk,grk->tr", xd, wd)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(2, T, R, device="cuda")
+    fp8_gemm_split(wq, sw, xq, sx, out, ksplit=2, group_k=gk, group_rows=R, used=used, status=status)
+    assert rel(out.sum(0), want) < 1e-5
+    # plain matrix whose rows come in groups (expert gate/up): row tiles of unused groups are not written
+    K = 512
+    wq, sw = quantize_blockwise(torch.randn(G * R, K, device="cuda", generator=g) * 0.05)
+    xq, sx = act_quant((torch.randn(T, K, device="cuda", generator=g) * 2).to(torch.bfloat16))
+    want = (_deq_act(xq, sx).double() @ dequantize_blockwise(wq, sw).double().T).reshape(T, G, R)
+    out = torch.full((T, G * R), 7.0, device="cuda")
+    fp8_gemm_split(wq, sw, xq, sx, out, ksplit=1, used=used, used_rows=R, status=status)
+    torch.cuda.synchronize()
+    got = out.reshape(T, G, R)
+    on = used.bool()
+    assert int(status.item()) == 0 and rel(got[:, on], want[:, on]) < 1e-5
+    assert bool((got[:, ~on] == 7.0).all())
+
+
 def test_glue_kernels_against_pytorch():
     lib = load()
     g = torch.Generator(device="cuda").manual_seed(3)

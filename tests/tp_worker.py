@@ -80,6 +80,23 @@ def main():
             assert logits_ref[i].max() - logits_ref[i][a] < 0.05, (i, a, b)
             break
     assert eng.status_max() == 0
+
+    # wide prefill chunks (tcgen05 GEMM per projection, all-reduce of the chunk's partial sums) against the 8-row steps
+    long_prompt = synthetic_prompt(cfg.vocab, 53, seed=9)
+    eng.prefill(long_prompt, chunk=8, wide=0)
+    want_state = eng.export_state()
+    first_w = eng.prefill(long_prompt, chunk=8, wide=16)
+    got_state = eng.export_state()
+    assert eng.status_max() == 0 and got_state["L"] == 53
+    for idx, st in want_state["layers"].items():
+        for key, w_ in st.items():
+            if key != "kind":
+                assert rel_l2(got_state["layers"][idx][key].float(), w_.float()) < 0.3, (idx, key)
+    t = torch.tensor([first_w], device=dev)
+    allt = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(allt, t)
+    assert all(torch.equal(allt[0], u) for u in allt), allt
+    assert len(eng.generate(max_new=4)) == 4 and eng.status_max() == 0
     dist.barrier()
     if rank == 0:
         print("TP_WORKER_OK", flush=True)
