@@ -127,7 +127,8 @@ int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, floa
 // ---- glue kernels of the wide prefill path (prefill.cu) ---------------------------------------------------------
 int nexrt_prefill_embed(const void* embed, const void* ids, void* x, void* status, int H, int vocab, int T, void* stream);
 int nexrt_prefill_ctl(const void* ctl, void* table, int n_sub, int rows, void* stream);   /* table[j] = ctl with committed length + j * rows */
-int nexrt_prefill_advance(void* ctl, int rows, void* stream);
+int nexrt_prefill_advance(void* ctl, int rows, void* seq, unsigned int n_sites, void* stream);   /* committed length += rows, LL sequence base += n_sites */
+int nexrt_planes_allreduce_residual(void* x, const void* y, int64_t n, int ksplit, const NexrtLLChannel* ch, unsigned int site, void* stream);
 int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, void* stream);
 int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream);
 int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, void* stream);

@@ -10,6 +10,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "ll.cuh"
 
 namespace nexrt {
 namespace {
@@ -41,10 +42,15 @@ __global__ void prefill_ctl_kernel(const int* __restrict__ ctl, int* __restrict_
     table[j * kCtlWords + w] = v;
 }
 
-__global__ void prefill_advance_kernel(int* ctl, int rows) {
+// last node of a chunk: the committed length moves on, and so does the LL sequence base by the number of channel users
+// of the chunk (what step_end does for a decode step)
+__global__ void prefill_advance_kernel(int* ctl, int rows, unsigned int* seq, unsigned int n_sites) {
     pdl_launch_dependents();
     pdl_wait();
-    if (threadIdx.x == 0) ctl[kCtlCommittedLen] += rows;
+    if (threadIdx.x == 0) {
+        ctl[kCtlCommittedLen] += rows;
+        if (seq != nullptr) *seq += n_sites;
+    }
 }
 
 __device__ __forceinline__ void quant_block4(const float v[4], __nv_fp8_storage_t* dst, float* scale_out, int lane) {
@@ -127,6 +133,44 @@ __global__ void __launch_bounds__(256) planes_residual_kernel(__nv_bfloat16* x, 
         xp[0] = __floats2bfloat162_rn(a.x + t.x, a.y + t.y);
         xp[1] = __floats2bfloat162_rn(b.x + t.z, b.y + t.w);
     }
+}
+
+// Tensor-parallel form of the residual add: the sum of this rank's K-split planes is all-reduced over the LL packet
+// channel inside the kernel (one 8-byte tagged packet per value through the NVSwitch multicast alias or peer stores, the
+// world's values added in rank order so every rank gets the same bits), then x = bf16(x + sum).  The channel has one slot
+// per value of the chunk; every wait is bounded (ll.cuh) and a failure latches the status word.
+__global__ void __launch_bounds__(256) planes_allreduce_residual_kernel(__nv_bfloat16* x, const float* __restrict__ y, size_t n, int ksplit, LLChannel ch,
+                                                                        unsigned int site) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 t = *reinterpret_cast<const float4*>(y + i);
+    for (int ks = 1; ks < ksplit; ++ks) {
+        const float4 v = *reinterpret_cast<const float4*>(y + static_cast<size_t>(ks) * n + i);
+        t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+    }
+    const float own[4] = {t.x, t.y, t.z, t.w};
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    const LLCall call = ll_begin(ch, site);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ll_publish(ch, call, static_cast<unsigned int>(i) + j, __float_as_uint(own[j]));
+    for (int src = 0; src < ch.world; ++src) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v = own[j];
+            if (src != ch.rank) {
+                unsigned int payload;
+                ll_wait(ch, call, src, static_cast<unsigned int>(i) + j, &payload);     // a timeout yields 0 and a status
+                v = __uint_as_float(payload);
+            }
+            sum[j] += v;
+        }
+    }
+    __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(x + i);
+    const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
+    xp[0] = __floats2bfloat162_rn(a.x + sum[0], a.y + sum[1]);
+    xp[1] = __floats2bfloat162_rn(b.x + sum[2], b.y + sum[3]);
 }
 
 // rmsnorm(x[t]) * gamma of every chunk row, written in the forms the chunk's GEMMs take (each output optional):
@@ -379,8 +423,16 @@ int nexrt_prefill_ctl(const void* ctl, void* table, int n_sub, int rows, void* s
     return launch(prefill_ctl_kernel, dim3(n_sub), dim3(32), 0, static_cast<cudaStream_t>(stream), static_cast<const int*>(ctl), static_cast<int*>(table), n_sub, rows);
 }
 
-int nexrt_prefill_advance(void* ctl, int rows, void* stream) {
-    return launch(prefill_advance_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), static_cast<int*>(ctl), rows);
+int nexrt_prefill_advance(void* ctl, int rows, void* seq, unsigned int n_sites, void* stream) {
+    return launch(prefill_advance_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), static_cast<int*>(ctl), rows, static_cast<unsigned int*>(seq),
+                  n_sites);
+}
+
+int nexrt_planes_allreduce_residual(void* x, const void* y, int64_t n, int ksplit, const NexrtLLChannel* ch, unsigned int site, void* stream) {
+    if (n < 4 || n % 4 || ksplit < 1 || ch == nullptr || ch->world < 2 || ch->slots < static_cast<unsigned int>(n)) return cudaErrorInvalidValue;
+    const int64_t threads = n / 4;
+    return launch(planes_allreduce_residual_kernel, dim3(static_cast<unsigned int>((threads + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                  static_cast<__nv_bfloat16*>(x), static_cast<const float*>(y), static_cast<size_t>(n), ksplit, *ch, site);
 }
 
 int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream) {

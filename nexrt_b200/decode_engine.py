@@ -105,6 +105,9 @@ class DecodeEngine:
         c.ctl[Ctl.PENDING] = first_token
         c.ctl[Ctl.IDS] = first_token
         c.channel.reset()
+        for wp in self._wide.values():          # the wide prefill path's channel shares the sequence word that just restarted
+            if wp.channel is not None:
+                wp.channel.buf.tensor.zero_()
         if c.cp_channel is not None:
             c.cp_channel.buf.tensor.zero_()
         torch.cuda.synchronize(self.dev)

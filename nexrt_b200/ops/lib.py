@@ -76,7 +76,8 @@ _PROTOTYPES = {
     "nexrt_moe_mark_used": [vp, vp, ci, ci, vp],
     "nexrt_prefill_embed": [vp, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_prefill_ctl": [vp, vp, ci, ci, vp],
-    "nexrt_prefill_advance": [vp, ci, vp],
+    "nexrt_prefill_advance": [vp, ci, vp, cu, vp],
+    "nexrt_planes_allreduce_residual": [vp, vp, c_int64, ci, CH, cu, vp],
     "nexrt_norm_rows": [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_gdn_gate_quant": [vp, vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp],

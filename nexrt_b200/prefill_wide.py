@@ -26,7 +26,6 @@ from __future__ import annotations
 from typing import Dict, List, Sequence
 
 import torch
-import torch.distributed as dist
 
 from .attn import FullAttn
 from .ops.lib import check, ptr
@@ -55,7 +54,7 @@ class WidePrefill:
             raise ValueError("chunk must be a multiple of 8 between 16 and 128")
         if not supported(eng):
             raise ValueError("model shapes outside the wide prefill path")
-        self.eng, self.T, self.use_graph = eng, chunk, graph and eng.world == 1
+        self.eng, self.T, self.use_graph = eng, chunk, graph
         c, cfg, spec, dev = eng.ctx, eng.cfg, eng.spec, eng.dev
         T, H = chunk, cfg.hidden
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
@@ -99,7 +98,16 @@ class WidePrefill:
             ks = (kb + (kb + ks - 1) // ks - 1) // ((kb + ks - 1) // ks)
         self.down_ksplit = ks
         self.y = z(max(self.down_ksplit, 1), T, H)
-        self.ysum = z(T, H) if eng.world > 1 else None
+        # tensor parallel: the chunk's partial sums are all-reduced inside the residual kernel over an LL packet channel with
+        # one slot per value of the chunk (the step kernels' channel holds eight rows); it shares the engine's sequence
+        # word and status, so its tags never collide with the decode steps' and a failure stops both
+        self.channel = None
+        if eng.world > 1:
+            from .parallel.channel import LLChannel
+
+            self.channel = LLChannel(dev, eng.world, eng.rank, T * H, group=eng.group, seq=c.seq, status=c.status)
+            self.channel.struct.budget_ns = c.channel.struct.budget_ns
+        self.site = 0
         self.graph = None
 
     # ---- one chunk ---------------------------------------------------------------------------------------------
@@ -107,12 +115,11 @@ class WidePrefill:
         """x += (all-reduced) sum of the projection's K-split planes."""
         c, lib, st = self.eng.ctx, self.eng.ctx.lib, self.eng.ctx.stream()
         n = self.T * self.eng.cfg.hidden
-        if self.eng.world == 1:
+        if self.channel is None:
             check(lib.nexrt_planes_residual(ptr(self.x), ptr(self.y), None, n, ksplit, st), "planes_residual")
             return
-        check(lib.nexrt_planes_residual(None, ptr(self.y), ptr(self.ysum), n, ksplit, st), "planes_residual")
-        dist.all_reduce(self.ysum, group=self.eng.group)
-        check(lib.nexrt_planes_residual(ptr(self.x), ptr(self.ysum), None, n, 1, st), "planes_residual")
+        check(lib.nexrt_planes_allreduce_residual(ptr(self.x), ptr(self.y), n, ksplit, self.channel.ref, self.site, st), "planes_allreduce_residual")
+        self.site += 1
 
     def _gdn(self, m) -> None:
         eng, T = self.eng, self.T
@@ -199,6 +206,7 @@ class WidePrefill:
         """All layers over the rows named by ``self.ids`` at the engine's committed length, which then advances by T."""
         eng = self.eng
         c, lib, st = eng.ctx, eng.ctx.lib, eng.ctx.stream()
+        self.site = 0
         check(lib.nexrt_prefill_ctl(ptr(c.ctl), ptr(self.ctl_tab), self.n_sub, SUB, st), "prefill_ctl")
         check(lib.nexrt_prefill_embed(ptr(eng.embed), ptr(self.ids), ptr(self.x), ptr(c.status), eng.cfg.hidden, eng.cfg.vocab, self.T, st), "prefill_embed")
         for mixer, moe in zip(eng.mixers, eng.moes):
@@ -207,7 +215,7 @@ class WidePrefill:
             else:
                 self._gdn(mixer)
             self._moe(moe)
-        check(lib.nexrt_prefill_advance(ptr(c.ctl), self.T, st), "prefill_advance")
+        check(lib.nexrt_prefill_advance(ptr(c.ctl), self.T, ptr(c.seq), self.site, st), "prefill_advance")
 
     def run(self, ids: Sequence[int], base: int = 0, on_chunk=None) -> None:
         """Consume ``len(ids)`` (a multiple of the chunk size) prompt tokens starting at the engine's committed length
