@@ -131,7 +131,7 @@ int nexrt_prefill_advance(void* ctl, int rows, void* seq, unsigned int n_sites, 
 int nexrt_planes_allreduce_residual(void* x, const void* y, int64_t n, int ksplit, const NexrtLLChannel* ch, unsigned int site, void* stream);
 int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, void* stream);
 int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream);
-int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, void* stream);
+int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, int ksplit, void* stream);   /* gu: [ksplit][T][n_total * 2I] */
 int nexrt_moe_mark_used(const void* ids, void* used, int n_ids, int n_total, void* stream);   /* used[e] = 1 for every routed expert id */
 int nexrt_planes_residual(void* x, const void* y, void* sum_out, int64_t n, int ksplit, void* stream);
 int nexrt_gdn_chunk(const void* pre, const void* xn, const void* ba_w, const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl,

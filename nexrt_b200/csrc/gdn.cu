@@ -215,7 +215,8 @@ __global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, con
     const __nv_bfloat16* w = a.ba_w + static_cast<size_t>(row) * a.H;
     const float* xr = xn + static_cast<size_t>(m) * a.H;
     float acc = 0.f;
-    for (int k = lane * 8; k < a.H; k += 256) {
+#pragma unroll 4
+    for (int k = lane * 8; k < a.H; k += 256) {      // unrolled so that the loads of four steps are in flight together
         float wf[8];
         unpack8_bf16(*reinterpret_cast<const uint4*>(w + k), wf);
         const float4 x0 = *reinterpret_cast<const float4*>(xr + k), x1 = *reinterpret_cast<const float4*>(xr + k + 4);

@@ -91,7 +91,8 @@ __global__ void __launch_bounds__(256) gdn_gate_quant_kernel(const float* __rest
 // per 128 columns into hq [T][n_total * I] with scales hs [T][n_total * I / 128].  Both were zeroed before: a zero scale
 // removes an unrouted block from the down product.  One warp per (row, slot, 128-column block).
 __global__ void __launch_bounds__(256) moe_dense_act_kernel(const float* __restrict__ gu, const int* __restrict__ ids, const float* __restrict__ wts,
-                                                            __nv_fp8_storage_t* __restrict__ hq, float* __restrict__ hs, int I, int S, int T, int n_total) {
+                                                            __nv_fp8_storage_t* __restrict__ hq, float* __restrict__ hs, int I, int S, int T, int n_total,
+                                                            int ksplit) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -102,7 +103,13 @@ __global__ void __launch_bounds__(256) moe_dense_act_kernel(const float* __restr
     const int e = min(max(ids[m * S + s], 0), n_total - 1);
     const float wt = wts[m * S + s];
     const float* g = gu + (static_cast<size_t>(m) * n_total + e) * 2 * I + b * 128 + lane * 4;
-    const float4 gt = *reinterpret_cast<const float4*>(g), up = *reinterpret_cast<const float4*>(g + I);
+    float4 gt = *reinterpret_cast<const float4*>(g), up = *reinterpret_cast<const float4*>(g + I);
+    for (int ks = 1; ks < ksplit; ++ks) {        // K-split partial planes of the gate/up product, added in plane order
+        const float* gk = g + static_cast<size_t>(ks) * T * n_total * 2 * I;
+        const float4 g2 = *reinterpret_cast<const float4*>(gk), u2 = *reinterpret_cast<const float4*>(gk + I);
+        gt.x += g2.x; gt.y += g2.y; gt.z += g2.z; gt.w += g2.w;
+        up.x += u2.x; up.y += u2.y; up.z += u2.z; up.w += u2.w;
+    }
     const float v[4] = {silu_f(gt.x) * up.x * wt, silu_f(gt.y) * up.y * wt, silu_f(gt.z) * up.z * wt, silu_f(gt.w) * up.w * wt};
     quant_block4(v, hq + (static_cast<size_t>(m) * n_total + e) * I + b * 128, hs + (static_cast<size_t>(m) * n_total + e) * nb + b, lane);
 }
@@ -322,7 +329,8 @@ __global__ void __launch_bounds__(256) gdn_front_chunk_kernel(GdnChunkArgs a, in
     const __nv_bfloat16* w = a.ba_w + static_cast<size_t>(row) * a.H;
     const float* xr = a.xn + static_cast<size_t>(m) * a.H;
     float acc = 0.f;
-    for (int k = lane * 8; k < a.H; k += 256) {
+#pragma unroll 4
+    for (int k = lane * 8; k < a.H; k += 256) {      // H % 256 == 0; unrolled so that the loads of four steps are in flight together
         float wf[8];
         unpack8_bf16(*reinterpret_cast<const uint4*>(w + k), wf);
         const float4 x0 = *reinterpret_cast<const float4*>(xr + k), x1 = *reinterpret_cast<const float4*>(xr + k + 4);
@@ -442,11 +450,11 @@ int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void
                   static_cast<const float*>(z), static_cast<const float*>(gnorm_w), static_cast<__nv_fp8_storage_t*>(xq), static_cast<float*>(sx), K, T, eps);
 }
 
-int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, void* stream) {
-    if (T < 1 || I % 128 || S < 1) return cudaErrorInvalidValue;
+int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, int ksplit, void* stream) {
+    if (T < 1 || I % 128 || S < 1 || ksplit < 1) return cudaErrorInvalidValue;
     const int items = T * S * (I / 128);
     return launch(moe_dense_act_kernel, dim3((items + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(gu),
-                  static_cast<const int*>(ids), static_cast<const float*>(wts), static_cast<__nv_fp8_storage_t*>(hq), static_cast<float*>(hs), I, S, T, n_total);
+                  static_cast<const int*>(ids), static_cast<const float*>(wts), static_cast<__nv_fp8_storage_t*>(hq), static_cast<float*>(hs), I, S, T, n_total, ksplit);
 }
 
 int nexrt_moe_mark_used(const void* ids, void* used, int n_ids, int n_total, void* stream) {

@@ -80,7 +80,7 @@ _PROTOTYPES = {
     "nexrt_planes_allreduce_residual": [vp, vp, c_int64, ci, CH, cu, vp],
     "nexrt_norm_rows": [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_gdn_gate_quant": [vp, vp, vp, vp, vp, ci, ci, cf, vp],
-    "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp],
+    "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
     "nexrt_planes_residual": [vp, vp, vp, c_int64, ci, vp],
     "nexrt_gdn_chunk": [vp] * 14 + [ci] * 9 + [vp],
     "nexrt_rows_norm_split": [vp, vp, vp, vp, ci, ci, cf, vp],

@@ -121,7 +121,7 @@ def test_glue_kernels_against_pytorch():
     ids = torch.stack([torch.randperm(n_total, device="cuda", generator=g)[:S] for _ in range(T)]).to(torch.int32)
     wts = torch.rand(T, S, device="cuda", generator=g)
     hq, hs = torch.zeros(T, n_total * I, dtype=FP8, device="cuda"), torch.zeros(T, n_total * I // 128, device="cuda")
-    check(lib.nexrt_moe_dense_act(ptr(gu), ptr(ids), ptr(wts), ptr(hq), ptr(hs), I, S, T, n_total, _stream()), "moe_dense_act")
+    check(lib.nexrt_moe_dense_act(ptr(gu), ptr(ids), ptr(wts), ptr(hq), ptr(hs), I, S, T, n_total, 1, _stream()), "moe_dense_act")
     want = torch.zeros(T, n_total, I, device="cuda")
     gv = gu.reshape(T, n_total, 2, I)
     for t in range(T):
