@@ -66,6 +66,8 @@ def serve(a) -> int:
         worker += ["--tokenizer", a.tokenizer]
     if a.cp:
         worker += ["--cp"]
+    if a.wide_prefill:
+        worker += ["--wide-prefill", str(a.wide_prefill)]
     facade = [sys.executable, "-m", "nexrt_b200.serve.openai_serve", "--port", str(a.http_port), "--backend-port", str(a.port), "--model-name", a.model_name]
     if a.forward_sampling:
         facade += ["--forward-sampling"]
@@ -112,6 +114,7 @@ def main(argv=None) -> int:
     s.add_argument("--tokenizer", default=None)
     s.add_argument("--context", type=int, default=32768)
     s.add_argument("--cp", action="store_true")
+    s.add_argument("--wide-prefill", type=int, default=0, help="rows per wide prefill chunk of the workers (0 = 8-row steps)")
     s.add_argument("--model-name", default="Nex-N2.5-Pro")
     s.add_argument("--forward-sampling", action="store_true")
     k = sub.add_parser("smoke")
