@@ -84,3 +84,18 @@ def test_verify_gate_and_cache_matrix_on_the_engine(server):
         server.verify = False
     res = server.cache_e2e(24, 37, repetitions=1, gen=6)
     assert res["ok"], res
+
+
+def test_wide_prefill_boundary_is_reusable(server, monkeypatch):
+    """Prompts prefilled in wide chunks leave a boundary that HIT and APPEND requests continue from."""
+    monkeypatch.setenv("NEXRT_WIDE_PREFILL", "16")
+    cfg = server.backend.eng.cfg
+    base = synthetic_prompt(cfg.vocab, 45, seed=21)
+    longer = base + synthetic_prompt(cfg.vocab, 20, seed=22)
+    r1 = server.run_request(_req(base, cache_key="w"), base)
+    assert r1["cache"] == "prefill" and r1["status"] == 0 and len(r1["tokens"]) == 8
+    assert 16 in server.backend.eng._wide                       # the wide path ran
+    r2 = server.run_request(_req(base, cache_key="w"), base)
+    assert r2["cache"] == "hit" and r2["tokens"] == r1["tokens"]
+    r3 = server.run_request(_req(longer, cache_key="w"), longer)
+    assert r3["cache"] == "append" and r3["status"] == 0 and len(r3["tokens"]) == 8
