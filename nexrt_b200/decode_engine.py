@@ -16,6 +16,7 @@ import os
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
+from .runtime.capture import graph_capture
 import torch.distributed as dist
 
 from .attn import FullAttn
@@ -215,7 +216,7 @@ class DecodeEngine:
         if self.world > 1:
             dist.barrier(group=self.group)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=side):
+        with graph_capture(g, side):
             self.step(M, cp=cp)
         self._restore(saved)
         self.graphs[key] = g

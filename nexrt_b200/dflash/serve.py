@@ -6,6 +6,7 @@ from __future__ import annotations
 from typing import Callable, List, Optional
 
 import torch
+from ..runtime.capture import graph_capture
 import torch.distributed as dist
 
 from ..runtime.control import Ctl
@@ -30,7 +31,7 @@ def capture_request(block: DFlashBlock, cp: bool = False, warmup: int = 3):
     if eng.world > 1:
         dist.barrier(group=eng.group)
     g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g, stream=side):
+    with graph_capture(g, side):
         block.round(cp=cp)
     eng._restore(saved)
     eng.graphs[key] = g

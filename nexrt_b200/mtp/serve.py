@@ -11,6 +11,7 @@ from __future__ import annotations
 from typing import Callable, List, Optional
 
 import torch
+from ..runtime.capture import graph_capture
 import torch.distributed as dist
 
 from ..runtime.control import Ctl
@@ -34,7 +35,7 @@ def capture_round(mtp: MtpDraft, cp: bool = False, warmup: int = 3):
     if eng.world > 1:
         dist.barrier(group=eng.group)
     g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g, stream=side):
+    with graph_capture(g, side):
         mtp.round(cp=cp)
     eng._restore(saved)
     mtp.y_sel.copy_(y_saved)

@@ -23,9 +23,11 @@ bit for bit; the same holds between the reference's SGLang prefill and its decod
 
 from __future__ import annotations
 
+import weakref
 from typing import Dict, List, Sequence
 
 import torch
+from .runtime.capture import graph_capture
 
 from .attn import FullAttn
 from .ops.lib import check, ptr
@@ -54,7 +56,7 @@ class WidePrefill:
             raise ValueError("chunk must be a multiple of 8 between 16 and 128")
         if not supported(eng):
             raise ValueError("model shapes outside the wide prefill path")
-        self.eng, self.T, self.use_graph = eng, chunk, graph
+        self.eng, self.T, self.use_graph = weakref.proxy(eng), chunk, graph     # the engine owns this object: no reference cycle
         c, cfg, spec, dev = eng.ctx, eng.cfg, eng.spec, eng.dev
         T, H = chunk, cfg.hidden
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
@@ -244,7 +246,7 @@ class WidePrefill:
                 s = torch.cuda.Stream(dev)
                 s.wait_stream(torch.cuda.current_stream(dev))
                 with torch.cuda.stream(s):
-                    with torch.cuda.graph(g, stream=s):
+                    with graph_capture(g, s):
                         self._chunk()
                 torch.cuda.current_stream(dev).wait_stream(s)
                 torch.cuda.synchronize(dev)

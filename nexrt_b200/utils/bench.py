@@ -16,6 +16,7 @@ import threading
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
+from ..runtime.capture import graph_capture
 import torch.distributed as dist
 
 L2_FLUSH_BYTES = 256 << 20
@@ -86,7 +87,7 @@ def profile_pipeline(stages: Sequence[Callable[[], None]], names: Sequence[str],
                 run()
         torch.cuda.synchronize(device)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=side):
+        with graph_capture(g, side):
             run()
         t = bench_graph(g, reps, warmup, device, group)["ms_per_replay"]
         out.append({"stage": names[k], "cumulative_us": t * 1e3, "increment_us": (t - prev) * 1e3})

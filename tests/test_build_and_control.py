@@ -68,3 +68,31 @@ def test_ring_no_alias_law():
     assert C.ring_no_alias(8, 16, 9) and C.ring_no_alias(4, 16, 5) and C.ring_no_alias(1, 16, 2)
     assert not C.ring_no_alias(8, 16, 8) and not C.ring_no_alias(8, 10, 9)
     assert C.state_slot(9, 9) == 0 and C.conv_slot(17, 16) == 1
+
+
+def test_graph_capture_holds_the_garbage_collector(monkeypatch):
+    """The capture helper collects first and keeps the cyclic collector off while the capture runs."""
+    import contextlib
+    import gc
+
+    import torch
+
+    from nexrt_b200.runtime import capture
+
+    seen = {}
+
+    @contextlib.contextmanager
+    def fake_graph(graph, stream=None):
+        seen["inside_enter"] = gc.isenabled()
+        yield
+        seen["inside_exit"] = gc.isenabled()
+
+    monkeypatch.setattr(torch.cuda, "graph", fake_graph)
+    assert gc.isenabled()
+    with capture.graph_capture(object(), object()):
+        seen["body"] = gc.isenabled()
+    assert seen == {"inside_enter": False, "body": False, "inside_exit": False} and gc.isenabled()
+    with pytest.raises(RuntimeError):
+        with capture.graph_capture(object(), object()):
+            raise RuntimeError("launch failed")
+    assert gc.isenabled()
