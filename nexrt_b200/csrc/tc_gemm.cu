@@ -166,9 +166,10 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
         const int row = m0 + 32 * q + lane;
         const int et = threadIdx.x - 64;        // 0..127
         if (FP8) {
+            // activation scales of this token tile, read along K (neighbouring threads, neighbouring addresses)
             for (int i = et; i < KB * BN; i += 128) {
-                const int kb = i / BN, n = i % BN;
-                sxs[i] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * a.KB + kb0 + s_kb[kb]] : 0.f;
+                const int n = i / KB, kb = i % KB;
+                sxs[kb * BN + n] = (n0 + n < a.T) ? a.sx[static_cast<size_t>(n0 + n) * a.KB + kb0 + s_kb[kb]] : 0.f;
             }
             for (int i = et; i < KB; i += 128) {     // weight block scales of this row tile
                 const int kg = kb0 + s_kb[i];
@@ -191,23 +192,23 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
             if (FP8) {
                 const float w = sws[r];
                 const float4* sx4 = reinterpret_cast<const float4*>(sxs + r * BN);
+                // all columns of the block are requested before the one wait (a tensor-memory round trip per 16 columns
+                // was what bounded a CTA's K walk), and the buffer goes back to the issuer before the arithmetic
+                float p[BN];
 #pragma unroll
-                for (int c = 0; c < BN; c += 16) {
-                    float p[16];
-                    tmem_ld16(taddr + c, p);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int n = 0; n < 16; n += 4) {
-                        const float4 sc = sx4[(c + n) >> 2];
-                        acc[c + n] = fmaf(p[n], w * sc.x, acc[c + n]);
-                        acc[c + n + 1] = fmaf(p[n + 1], w * sc.y, acc[c + n + 1]);
-                        acc[c + n + 2] = fmaf(p[n + 2], w * sc.z, acc[c + n + 2]);
-                        acc[c + n + 3] = fmaf(p[n + 3], w * sc.w, acc[c + n + 3]);
-                    }
-                }
+                for (int c = 0; c < BN; c += 16) tmem_ld16(taddr + c, p + c);
+                tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty(buf));
+#pragma unroll
+                for (int n = 0; n < BN; n += 4) {
+                    const float4 sc = sx4[n >> 2];
+                    acc[n] = fmaf(p[n], w * sc.x, acc[n]);
+                    acc[n + 1] = fmaf(p[n + 1], w * sc.y, acc[n + 1]);
+                    acc[n + 2] = fmaf(p[n + 2], w * sc.z, acc[n + 2]);
+                    acc[n + 3] = fmaf(p[n + 3], w * sc.w, acc[n + 3]);
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < BN; c += 16) tmem_ld16(taddr + c, acc + c);
