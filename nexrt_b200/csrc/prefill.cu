@@ -1,9 +1,9 @@
-// Small kernels of the wide prefill path (chunks of 16..128 prompt tokens per pass).  The chunk's projections,
-// router and experts are tcgen05 GEMMs over all rows (tc_gemm.cu), so every weight is streamed once per chunk;
-// the sequential parts (conv ring, delta rule, causal attention) reuse the multi-row step kernels eight rows at
-// a time, each sub-step reading its base position from its own copy of the control block.  What is left are the
-// glue kernels here: embedding rows from an id list, the control-block table, the GDN output gate + quantisation,
-// the expert activation of the dense expert product, and the residual add over K-split planes.
+// Kernels of the wide prefill path (chunks of 16..128 prompt tokens per pass) that are not GEMMs.  The chunk's
+// projections, router and experts are tcgen05 GEMMs over all rows (tc_gemm.cu), so every weight is streamed once per
+// chunk.  Here: embedding rows from an id list, the control-block table that gives each 8-row attention sub-step its
+// base position, rmsnorm + quantisation of the chunk rows, the GDN layer's conv / gates / delta rule over the whole
+// chunk, the GDN output gate + quantisation, the expert activation of the dense expert product, the skip list of
+// unused experts, and the residual add over K-split planes with or without the tensor-parallel all-reduce.
 //
 // The reference has no counterpart: its prefill runs inside SGLang (nex_n2_5_pro/sglang_prefill/bridge.py:310-398).
 #include <cuda_fp8.h>

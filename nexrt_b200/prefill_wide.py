@@ -11,9 +11,14 @@ tokens.  Here a chunk of ``T`` rows goes through each layer in one pass:
   routes nearly every expert is used anyway, and the FP8 tensor cores make the extra columns cheaper than a
   gather), a small kernel turns the routed ``(row, expert)`` pairs into quantised ``h`` and leaves a zero scale
   everywhere else, and the down GEMM walks ``K = (E + 1) * I`` split over CTAs;
-* what is sequential in the model (conv ring, delta rule, causal attention over the cache) reuses the multi-row
-  step kernels eight rows at a time; sub-step ``j`` reads its base position from entry ``j`` of a control-block
-  table, so the whole chunk is position-independent on the host and is captured once into a CUDA graph.
+* the GDN layer's conv ring, gates and delta rule run over the whole chunk in two kernels (``csrc/prefill.cu``: the
+  step kernels' arithmetic, the recurrent state kept in registers along the chunk);
+* causal attention reuses the multi-row decode kernel eight rows at a time: the chunk's q / gate / k rows are scattered
+  and its K rows (norm + RoPE) published to the cache first, so the sub-steps do not depend on each other and run
+  side by side on their own streams; sub-step ``j`` reads its base position from entry ``j`` of a control-block table,
+  which makes the chunk position-independent on the host: it is captured once into a CUDA graph and replayed;
+* on a tensor-parallel group the residual add also all-reduces the chunk's partial sums inside the kernel (LL packets
+  through the multicast alias or peer stores), so the graph holds the whole chunk on every rank.
 
 The state it leaves (conv / state rings, KV cache, committed length) is the decode path's own, so decode - or the
 8-row prefill of the prompt's tail - continues from it.  Activations are quantised to one e4m3 plane here (the
@@ -24,7 +29,7 @@ bit for bit; the same holds between the reference's SGLang prefill and its decod
 from __future__ import annotations
 
 import weakref
-from typing import Dict, List, Sequence
+from typing import List, Sequence
 
 import torch
 from .runtime.capture import graph_capture
