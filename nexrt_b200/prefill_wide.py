@@ -55,6 +55,19 @@ def supported(eng) -> bool:
     )
 
 
+def down_split(k_blocks: int, tiles: int, n_cta: int, max_blocks: int = 64, max_split: int = 16) -> int:
+    """Number of K ranges of the expert down product: every CTA walks at most ``max_blocks`` K blocks, the grid
+    (``tiles`` output tiles x ranges) has about two CTAs per SM, and every range is non-empty (the split is a fixed
+    point of ``ceil(k_blocks / ceil(k_blocks / split))``, which is what the kernel launcher derives its ranges from)."""
+    ks = max((k_blocks + max_blocks - 1) // max_blocks, min(k_blocks, max_split, max(1, 2 * n_cta // max(tiles, 1))))
+    while True:
+        per = (k_blocks + ks - 1) // ks
+        eff = (k_blocks + per - 1) // per
+        if eff == ks:
+            return ks
+        ks = eff
+
+
 class WidePrefill:
     def __init__(self, eng, chunk: int = 64, graph: bool = True):
         if chunk % SUB or chunk < 2 * SUB or chunk > 128:
@@ -101,12 +114,7 @@ class WidePrefill:
         self.gu = z(self.up_ksplit, T, self.n_total * 2 * I)
         self.hq, self.hs = torch.zeros(T, self.n_total * I, dtype=FP8, device=dev), z(T, self.n_total * I // 128)
         # K split of the expert down product: at most 64 K blocks per CTA, and about two CTAs per SM over the grid
-        kb = self.n_total * I // 128
-        tiles = (H // 128) * ((T + 63) // 64)
-        ks = max((kb + 63) // 64, min(kb, 16, max(1, 2 * c.n_cta // tiles)))
-        while (kb + (kb + ks - 1) // ks - 1) // ((kb + ks - 1) // ks) != ks:    # every plane gets a non-empty K range
-            ks = (kb + (kb + ks - 1) // ks - 1) // ((kb + ks - 1) // ks)
-        self.down_ksplit = ks
+        self.down_ksplit = down_split(self.n_total * I // 128, (H // 128) * ((T + 63) // 64), c.n_cta)
         self.y = z(max(self.down_ksplit, 1), T, H)
         # tensor parallel: the chunk's partial sums are all-reduced inside the residual kernel over an LL packet channel with
         # one slot per value of the chunk (the step kernels' channel holds eight rows); it shares the engine's sequence

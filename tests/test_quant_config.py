@@ -93,3 +93,17 @@ def test_checkpoint_roundtrip_and_sharding(tmp_path):
     assert torch.equal(got, o)
     assert s0["layers"][0]["moe"]["w13"].shape == (cfg.n_experts + 1, 2 * 128, cfg.hidden)
     assert s0["head"]["lm_head"].shape == (cfg.vocab // 2, cfg.hidden)
+
+
+def test_wide_prefill_down_split_gives_every_range_work():
+    """The expert down product of the wide prefill path is split along K so that no CTA walks more than 64 blocks and no
+    range is empty (the kernel derives its ranges as ceil(blocks / split) per CTA)."""
+    from nexrt_b200.prefill_wide import down_split
+
+    assert down_split(513, 32, 148) == 9          # 513 experts x one 128-wide block, TP = 8 shard: 57 blocks per CTA, 288 CTAs
+    assert down_split(1, 8, 148) == 1
+    for k_blocks in list(range(1, 200)) + [513, 1026, 4104]:
+        for tiles in (1, 8, 32, 64):
+            ks = down_split(k_blocks, tiles, 148)
+            per = -(-k_blocks // ks)
+            assert per <= 64 and -(-k_blocks // per) == ks and 1 <= ks <= k_blocks
