@@ -4,6 +4,7 @@ model, its CPU oracle and an engine over it."""
 from __future__ import annotations
 
 import functools
+from dataclasses import replace
 
 import torch
 
@@ -12,8 +13,11 @@ from .weights import random_checkpoint, shard_model
 
 
 @functools.lru_cache(maxsize=4)
-def shrunk_checkpoint(seed: int = 0, cp: bool = False):
+def shrunk_checkpoint(seed: int = 0, cp: bool = False, kv_heads: int = 0):
+    """``kv_heads`` overrides the number of kv heads (1: two ranks already form a context-parallel group)."""
     cfg = shrunk_cp_config() if cp else shrunk_config()
+    if kv_heads:
+        cfg = replace(cfg, name=f"{cfg.name}-kv{kv_heads}", n_kv_heads=kv_heads)
     return cfg, random_checkpoint(cfg, seed)
 
 

@@ -1,4 +1,5 @@
-"""Child process of the context-parallel test: 4 ranks, 2 kv heads -> two CP groups of 2."""
+"""Child process of the context-parallel tests: 4 ranks with 2 kv heads (two CP groups of 2), or 2 ranks with 1 kv head
+(one CP group of 2)."""
 
 import os
 import sys
@@ -21,7 +22,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    cfg, ckpt = shrunk_checkpoint(0, cp=True)
+    cfg, ckpt = shrunk_checkpoint(0, cp=True, kv_heads=1 if world == 2 else 0)
     ref = RefModel(cfg, ckpt)
     eng = make_engine(cfg, ckpt, rank=rank, world=world, device=dev, max_rows=8, cp=True)
     assert eng.cp and eng.spec.cp_size == 2

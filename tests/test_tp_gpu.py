@@ -37,3 +37,11 @@ def test_context_parallel_tp4():
         pytest.skip("needs 4 GPUs")
     r = _run(4, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29613, script="cp_worker.py")
     assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_context_parallel_tp2():
+    """2 ranks, 1 kv head: one context-parallel group of 2 (the same worker; needs half the GPUs)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _run(2, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29614, script="cp_worker.py")
+    assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
