@@ -20,6 +20,7 @@ length in the draft layer's KV cache are speculative and are overwritten by the 
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Sequence
 
 import torch
@@ -103,14 +104,48 @@ class MtpDraft:
         self.eng.step_end()
 
     # ---- prefill ------------------------------------------------------------------------------------
-    def prefill(self, ids: Sequence[int], chunk: int = 8) -> int:
+    def _extend_wide(self, wp, ids: Sequence[int], n: int) -> None:
+        """Target through wide chunks over ``ids[:n]``; after each chunk the draft layer extends over its rows, eight at
+        a time: block ``k`` pairs the hidden rows of positions ``8k .. 8k+7`` with the tokens one position later (what
+        ``_prep(PREP_EXTEND)`` derives from the control block after an 8-row step)."""
+        eng, c = self.eng, self.ctx
+        rows = 8
+        table = torch.zeros(n // rows, CTL_WORDS, dtype=torch.int32)
+        for k in range(n // rows):
+            table[k, Ctl.COMMITTED_LEN] = k * rows
+            table[k, Ctl.COMMIT_COUNT] = rows
+            table[k, Ctl.IDS : Ctl.IDS + rows] = torch.tensor(ids[k * rows + 1 : k * rows + rows + 1], dtype=torch.int32)
+        table = table.to(c.device)
+
+        def after_chunk(start: int, x: torch.Tensor) -> None:
+            for j in range(wp.T // rows):
+                self.dctl.copy_(table[start // rows + j])
+                c.begin_step()
+                self._layer(rows, x[j * rows : (j + 1) * rows], -1)
+                eng.step_end()
+
+        wp.run(ids[:n], base=0, after_chunk=after_chunk)
+
+    def prefill(self, ids: Sequence[int], chunk: int = 8, wide: Optional[int] = None) -> int:
         """Chunked prefill of target and draft layer together; returns the first generated token and
-        leaves draft 1 ready for the first round."""
+        leaves draft 1 ready for the first round.  ``wide`` (default: ``NEXRT_WIDE_PREFILL``, 0 = off): whole chunks of
+        that many tokens go through the target's wide prefill path, the draft layer following eight rows at a time on
+        the chunk's final hidden rows; the rest of the prompt takes the 8-row steps below."""
         eng, c = self.eng, self.ctx
         ids = [int(t) for t in ids]
         chunk = min(chunk, eng.max_rows)
         eng.reset(first_token=ids[0])
         pos = 0
+        wide = int(os.environ.get("NEXRT_WIDE_PREFILL", "0") or 0) if wide is None else int(wide)
+        if wide and len(ids) - 1 >= wide:
+            from .. import prefill_wide
+
+            if prefill_wide.supported(eng):
+                wp = eng._wide.get(wide)
+                if wp is None:
+                    wp = eng._wide[wide] = prefill_wide.WidePrefill(eng, wide)
+                pos = (len(ids) - 1) // wide * wide
+                self._extend_wide(wp, ids, pos)
         while pos < len(ids):
             n = min(chunk, len(ids) - pos)
             last = pos + n >= len(ids)

@@ -235,9 +235,11 @@ class WidePrefill:
             self._moe(moe)
         check(lib.nexrt_prefill_advance(ptr(c.ctl), self.T, ptr(c.seq), self.site, st), "prefill_advance")
 
-    def run(self, ids: Sequence[int], base: int = 0, on_chunk=None) -> None:
+    def run(self, ids: Sequence[int], base: int = 0, on_chunk=None, after_chunk=None) -> None:
         """Consume ``len(ids)`` (a multiple of the chunk size) prompt tokens starting at the engine's committed length
-        (``base``, only used to report progress through ``on_chunk(start, end)``)."""
+        (``base``, only used to report progress through ``on_chunk(start, end)``).  ``after_chunk(start, x)`` is called once
+        a chunk is queued, with ``x [T, H]`` the residual rows after the last layer (speculative-decoding drafts that follow
+        the target's hidden states queue their own work on them before the next chunk overwrites the buffer)."""
         if len(ids) % self.T:
             raise ValueError("the wide path takes whole chunks")
         dev = self.eng.dev
@@ -247,6 +249,8 @@ class WidePrefill:
                 on_chunk(base + pos, base + pos + self.T)
             if not self.use_graph:
                 self._chunk()
+                if after_chunk is not None:
+                    after_chunk(base + pos, self.x)
                 continue
             if self.graph is None:
                 # one eager pass (lazy initialisation in the launchers must not happen under capture), whose state
@@ -266,6 +270,8 @@ class WidePrefill:
                 self._restore(snap)
                 self.graph = g
             self.graph.replay()
+            if after_chunk is not None:
+                after_chunk(base + pos, self.x)
         torch.cuda.synchronize(dev)
 
     # the eager warm-up pass and the capture itself touch the rings, the caches and the committed length

@@ -103,3 +103,29 @@ def test_upstream_status_fails_closed(setup):
     eng.step(4)
     ctl = eng.read_ctl()
     assert ctl["commit_count"] == 0 and ctl["committed_len"] == before and ctl["pending"] == -1 and ctl["status"] != 0
+
+
+def test_wide_prefill_feeds_the_draft_layer(setup):
+    """Target prefilled in wide chunks, draft layer extended eight rows at a time on the chunks' hidden rows: the draft
+    cache agrees with the one the 8-row prefill leaves (to the FP8 rounding of the wide path), and the rounds that follow
+    emit what plain decode emits from the same prefill."""
+    cfg, ref, eng, mtp = setup
+    prompt = synthetic_prompt(cfg.vocab, 53, seed=13)
+    mtp.prefill(prompt, chunk=8, wide=0)
+    want_k = mtp.attn.k_cache[:, :52].float().clone()
+    first = mtp.prefill(prompt, chunk=8, wide=16)
+    assert eng.status_max() == 0 and 16 in eng._wide
+    got_k = mtp.attn.k_cache[:, :52].float()
+    assert float((got_k - want_k).norm() / want_k.norm()) < 0.3
+    stats = {}
+    out = generate_mtp(mtp, capture_round(mtp), max_new=10, stats=stats)
+    assert eng.status_max() == 0 and len(out) == 10 and stats["rounds"] >= 3
+    first_plain = eng.prefill(prompt, chunk=8, wide=16)
+    plain = eng.generate(max_new=10)
+    assert first_plain == first
+    same = 0
+    for a, b in zip(out, plain):       # a near tie between the 4-row and the 1-row arithmetic may end the common prefix early
+        if a != b:
+            break
+        same += 1
+    assert same >= 3, (out, plain)
