@@ -185,7 +185,7 @@ extern "C" int nexrt_dflash_commit(void* ctl, const void* dctl, int rows, void* 
 }
 
 extern "C" int nexrt_feature_tap(const void* x, void* tap, int H, int ld, int col0, int M, void* stream) {
-    if (H % 8 || ld % 8 || col0 % 8 || M < 1 || M > kMaxRows) return cudaErrorInvalidValue;
+    if (H % 8 || ld % 8 || col0 % 8 || M < 1 || M > 128) return cudaErrorInvalidValue;   // one CTA per row: a prefill chunk taps up to 128 rows
     return launch(feature_tap_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
                   static_cast<__nv_bfloat16*>(tap), H, ld, col0);
 }

@@ -327,12 +327,8 @@ class DecodeEngine:
         pos = resume_from
         wide = int(os.environ.get("NEXRT_WIDE_PREFILL", "0")) if wide is None else int(wide)
         if wide and len(ids) - 1 - pos >= wide:
-            from . import prefill_wide
-
-            if prefill_wide.supported(self):
-                wp = self._wide.get(wide)
-                if wp is None:
-                    wp = self._wide[wide] = prefill_wide.WidePrefill(self, wide)
+            wp = self.wide_path(wide)
+            if wp is not None:
                 n = (len(ids) - 1 - pos) // wide * wide
                 wp.run(ids[pos : pos + n], base=pos, on_chunk=on_chunk)
                 pos += n
@@ -352,6 +348,19 @@ class DecodeEngine:
         torch.cuda.synchronize(self.dev)
         self.mirror.resync()
         return int(self.ctx.ctl[Ctl.PENDING].item())
+
+    def wide_path(self, rows: int):
+        """The wide prefill path for chunks of ``rows`` tokens (built on first use, one per chunk size and per feature-tap
+        configuration, because its captured graph contains the taps), or None when the model shapes are outside it."""
+        from . import prefill_wide
+
+        if not prefill_wide.supported(self):
+            return None
+        key = rows if self.taps is None else (rows, tuple(sorted(self.tap_layers)))
+        wp = self._wide.get(key)
+        if wp is None:
+            wp = self._wide[key] = prefill_wide.WidePrefill(self, rows)
+        return wp
 
     def load_prefill(self, state: Dict) -> None:
         """Install a saved prefill state ``{L, first_token, layers{idx: {kind, k_cache, v_cache |

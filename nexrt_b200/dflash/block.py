@@ -20,6 +20,7 @@ attention bakes the base position, ``dflash/serve.py:29-45``).
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Sequence
 
 import torch
@@ -122,12 +123,31 @@ class DFlashBlock:
         self.eng.step_end()
 
     # ---- prefill -------------------------------------------------------------------------------------
-    def prefill(self, ids: Sequence[int]) -> int:
-        """Chunked prefill of the target (8-row steps with taps) and of the draft's context caches."""
+    def prefill(self, ids: Sequence[int], wide: Optional[int] = None) -> int:
+        """Chunked prefill of the target (8-row steps with taps) and of the draft's context caches.  ``wide`` (default:
+        ``NEXRT_WIDE_PREFILL``, 0 = off): whole chunks of that many tokens go through the target's wide prefill path,
+        which also records the taps of its rows; the context phase follows eight rows at a time."""
         eng, c = self.eng, self.ctx
         ids = [int(t) for t in ids]
         eng.reset(first_token=ids[0])
         pos = 0
+        wide = int(os.environ.get("NEXRT_WIDE_PREFILL", "0") or 0) if wide is None else int(wide)
+        if wide and len(ids) - 1 >= wide:
+            wp = eng.wide_path(wide)
+            if wp is not None:
+                pos = (len(ids) - 1) // wide * wide
+
+                def after_chunk(start: int, x: torch.Tensor) -> None:
+                    for j in range(wp.T // M8):
+                        self.taps.copy_(wp.taps[j * M8 : (j + 1) * M8])
+                        self.cctl.zero_()
+                        self.cctl[Ctl.COMMITTED_LEN] = start + j * M8      # positions of the eight context rows
+                        self.cctl[Ctl.COMMIT_COUNT] = M8
+                        c.begin_step()
+                        self.context_phase(M8, prep=False)
+                        eng.step_end()
+
+                wp.run(ids[:pos], base=0, after_chunk=after_chunk)
         while pos < len(ids):
             n = min(M8, len(ids) - pos)
             eng.set_rows(ids[pos : pos + n])

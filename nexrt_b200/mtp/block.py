@@ -138,12 +138,8 @@ class MtpDraft:
         pos = 0
         wide = int(os.environ.get("NEXRT_WIDE_PREFILL", "0") or 0) if wide is None else int(wide)
         if wide and len(ids) - 1 >= wide:
-            from .. import prefill_wide
-
-            if prefill_wide.supported(eng):
-                wp = eng._wide.get(wide)
-                if wp is None:
-                    wp = eng._wide[wide] = prefill_wide.WidePrefill(eng, wide)
+            wp = eng.wide_path(wide)
+            if wp is not None:
                 pos = (len(ids) - 1) // wide * wide
                 self._extend_wide(wp, ids, pos)
         while pos < len(ids):

@@ -47,7 +47,7 @@ def supported(eng) -> bool:
     """Shapes the wide path covers: everything the tcgen05 GEMMs tile (128-row weight tiles, 128-wide K blocks)."""
     cfg, spec = eng.cfg, eng.spec
     return (
-        eng.max_rows >= SUB and eng.taps is None
+        eng.max_rows >= SUB
         and cfg.hidden % 128 == 0 and cfg.hidden <= 8192 and spec.inter % 128 == 0
         and spec.gdn_front_rows % 128 == 0 and spec.attn_front_rows % 128 == 0
         and spec.gdn_local % 128 == 0 and spec.gdn_local <= 8192 and spec.attn_local % 128 == 0 and spec.attn_local <= 8192
@@ -125,6 +125,10 @@ class WidePrefill:
 
             self.channel = LLChannel(dev, eng.world, eng.rank, T * H, group=eng.group, seq=c.seq, status=c.status)
             self.channel.struct.budget_ns = c.channel.struct.budget_ns
+        # feature taps (DFlash): the residual rows after the MoE of the tapped layers, concatenated per row like the
+        # engine's 8-row tap buffer
+        self.taps = None if eng.taps is None else torch.zeros(T, eng.taps.shape[1], dtype=bf, device=dev)
+        self.tap_layers = dict(eng.tap_layers)
         self.site = 0
         self.graph = None
 
@@ -227,12 +231,15 @@ class WidePrefill:
         self.site = 0
         check(lib.nexrt_prefill_ctl(ptr(c.ctl), ptr(self.ctl_tab), self.n_sub, SUB, st), "prefill_ctl")
         check(lib.nexrt_prefill_embed(ptr(eng.embed), ptr(self.ids), ptr(self.x), ptr(c.status), eng.cfg.hidden, eng.cfg.vocab, self.T, st), "prefill_embed")
-        for mixer, moe in zip(eng.mixers, eng.moes):
+        for layer, (mixer, moe) in enumerate(zip(eng.mixers, eng.moes)):
             if isinstance(mixer, FullAttn):
                 self._attn(mixer)
             else:
                 self._gdn(mixer)
             self._moe(moe)
+            if self.taps is not None and layer in self.tap_layers:
+                check(lib.nexrt_feature_tap(ptr(self.x), ptr(self.taps), eng.cfg.hidden, self.taps.shape[1], self.tap_layers[layer] * eng.cfg.hidden, self.T, st),
+                      "feature_tap")
         check(lib.nexrt_prefill_advance(ptr(c.ctl), self.T, ptr(c.seq), self.site, st), "prefill_advance")
 
     def run(self, ids: Sequence[int], base: int = 0, on_chunk=None, after_chunk=None) -> None:

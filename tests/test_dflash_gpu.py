@@ -65,3 +65,32 @@ def test_dflash_stream_equals_greedy_stream():
     else:
         assert len(out) == len(toks_ref)
     assert eng.status_max() == 0 and stats["rounds"] >= 1
+
+
+def test_wide_prefill_fills_the_context_caches():
+    """Target prefilled in wide chunks that also record the feature taps; the draft's context phase follows eight rows at
+    a time.  The context K/V agree with what the 8-row prefill leaves (to the FP8 rounding of the wide path) and the
+    rounds that follow emit what plain decode emits from the same prefill."""
+    cfg, ckpt = shrunk_checkpoint(0)
+    dev = torch.device("cuda", 0)
+    eng = make_engine(cfg, ckpt, max_rows=8)
+    dc = shrunk_dflash_config(cfg)
+    block = DFlashBlock(eng, dc, load_dflash_shard(random_dflash_checkpoint(dc, 11), dc, 1, 0, dev))
+    prompt = synthetic_prompt(cfg.vocab, 53, seed=23)
+    block.prefill(prompt, wide=0)
+    want_k = block.k_cache[0][:, :48].float().clone()
+    first = block.prefill(prompt, wide=16)
+    assert eng.status_max() == 0 and len(eng._wide) == 1
+    got_k = block.k_cache[0][:, :48].float()
+    assert float((got_k - want_k).norm() / want_k.norm()) < 0.3
+    out = generate_dflash(block, capture_request(block), max_new=10, stats={})
+    assert eng.status_max() == 0 and len(out) >= 10
+    plain_first = eng.prefill(prompt, chunk=8, wide=16)
+    plain = eng.generate(max_new=10)
+    assert plain_first == first
+    same = 0
+    for a, b in zip(out, plain):       # a near tie between the 8-row and the 1-row arithmetic may end the common prefix early
+        if a != b:
+            break
+        same += 1
+    assert same >= 3, (out, plain)
