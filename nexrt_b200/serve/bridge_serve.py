@@ -539,7 +539,7 @@ def main(argv=None) -> int:
     p.add_argument("--cache-consensus-fault-rank", type=int, default=None, help="test only: this rank rejects its READY boundary once")
     p.add_argument("--no-listen", action="store_true", help="exit after the queued work")
     p.add_argument("--wide-prefill", type=int, default=int(os.environ.get("NEXRT_WIDE_PREFILL", "0") or 0),
-                   help="rows per wide prefill chunk (16..128, a multiple of 8; plain one-row mode only); 0 = 8-row steps")
+                   help="rows per wide prefill chunk (16..128, a multiple of 8; every decode mode); 0 = 8-row steps")
     args = p.parse_args(argv)
     os.environ["NEXRT_WIDE_PREFILL"] = str(args.wide_prefill)      # read by DecodeEngine.prefill
     import torch
