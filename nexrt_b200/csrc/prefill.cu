@@ -142,42 +142,102 @@ __global__ void __launch_bounds__(256) planes_residual_kernel(__nv_bfloat16* x, 
     }
 }
 
-// Tensor-parallel form of the residual add: the sum of this rank's K-split planes is all-reduced over the LL packet
-// channel inside the kernel (one 8-byte tagged packet per value through the NVSwitch multicast alias or peer stores, the
-// world's values added in rank order so every rank gets the same bits), then x = bf16(x + sum).  The channel has one slot
-// per value of the chunk; every wait is bounded (ll.cuh) and a failure latches the status word.
+// Tensor-parallel form of the residual add: the sum of this rank's K-split planes is all-reduced inside the kernel, then
+// x = bf16(x + sum).  A chunk moves megabytes per reduce, so the 8-byte tagged packets of the decode steps (half of every
+// packet is the tag, one NVLink transaction per value) give way to a block protocol over the same symmetric inbox: the 256
+// threads of a CTA store their 1024 values as plain 16-byte vectors into every rank's copy of region [half][this rank]
+// (one multimem.st through the NVSwitch alias, or one store per peer), make them visible (fence.sys + barrier), and one
+// thread publishes the call's tag in the CTA's flag word; the same CTA of every other rank does the same, so the CTA polls
+// its flag word of each peer region (bounded like every LL wait, status latched on expiry), then adds the world's
+// vectors in rank order: every rank gets the same bits.  Region layout: n floats of data, then one u32 flag per CTA.
+// Halves alternate with the global call sequence as in ll.cuh: a peer can publish call k + 2 into a half only after this
+// rank has left the kernel of call k.
+__device__ __forceinline__ void st_sys_v4(float* p, const float4& v) {
+    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void mc_st_v4(float* p, const float4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float4 ld_sys_v4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_sys_u32(unsigned int* p, unsigned int v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void mc_st_u32(unsigned int* p, unsigned int v) {
+    asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __global__ void __launch_bounds__(256) planes_allreduce_residual_kernel(__nv_bfloat16* x, const float* __restrict__ y, size_t n, int ksplit, LLChannel ch,
                                                                         unsigned int site) {
+    __shared__ int s_ok[kMaxWorld];
     pdl_launch_dependents();
     pdl_wait();
-    const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
-    if (i >= n) return;
+    const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;     // n is a multiple of 1024: every thread has work
     float4 t = *reinterpret_cast<const float4*>(y + i);
     for (int ks = 1; ks < ksplit; ++ks) {
         const float4 v = *reinterpret_cast<const float4*>(y + static_cast<size_t>(ks) * n + i);
         t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
     }
-    const float own[4] = {t.x, t.y, t.z, t.w};
-    float sum[4] = {0.f, 0.f, 0.f, 0.f};
     const LLCall call = ll_begin(ch, site);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) ll_publish(ch, call, static_cast<unsigned int>(i) + j, __float_as_uint(own[j]));
-    for (int src = 0; src < ch.world; ++src) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float v = own[j];
-            if (src != ch.rank) {
-                unsigned int payload;
-                ll_wait(ch, call, src, static_cast<unsigned int>(i) + j, &payload);     // a timeout yields 0 and a status
-                v = __uint_as_float(payload);
-            }
-            sum[j] += v;
+    // byte offset of region [half][src] inside every rank's inbox, and of this CTA's flag word inside a region
+    auto region = [&](int src) { return (static_cast<size_t>(call.half) * ch.world + src) * ch.slots * 8; };
+    const size_t flag_off = n * 4 + static_cast<size_t>(blockIdx.x) * 4;
+    const size_t mine = region(ch.rank);
+    if (ch.mc != nullptr) {
+        mc_st_v4(reinterpret_cast<float*>(reinterpret_cast<char*>(ch.mc) + mine) + i, t);
+    } else {
+        for (int p = 0; p < ch.world; ++p)
+            if (p != ch.rank) st_sys_v4(reinterpret_cast<float*>(reinterpret_cast<char*>(ch.peer[p]) + mine) + i, t);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (ch.mc != nullptr) {
+            mc_st_u32(reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ch.mc) + mine + flag_off), call.tag);
+        } else {
+            for (int p = 0; p < ch.world; ++p)
+                if (p != ch.rank) st_sys_u32(reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ch.peer[p]) + mine + flag_off), call.tag);
         }
+    }
+    // thread s waits for the flag of rank s
+    if (static_cast<int>(threadIdx.x) < ch.world) {
+        const int src = threadIdx.x;
+        int ok = 1;
+        if (src != ch.rank) {
+            const unsigned int* f = reinterpret_cast<const unsigned int*>(reinterpret_cast<const char*>(ch.local) + region(src) + flag_off);
+            if (ld_acquire_sys_u32(f) != call.tag) {
+                const bool failed = *reinterpret_cast<volatile int*>(ch.status) != 0;     // a latched failure makes every later wait give up at once
+                const unsigned long long t0 = globaltimer_ns();
+                unsigned int spins = 0;
+                while (ld_acquire_sys_u32(f) != call.tag) {
+                    if (failed || ((++spins & 63u) == 0 && globaltimer_ns() - t0 > ch.budget_ns)) {
+                        atomicCAS(ch.status, 0, static_cast<int>(kStatusReduceTimeout));
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+        }
+        s_ok[src] = ok;
+    }
+    __syncthreads();
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int src = 0; src < ch.world; ++src) {
+        float4 v = t;
+        if (src != ch.rank)
+            v = s_ok[src] ? ld_sys_v4(reinterpret_cast<const float*>(reinterpret_cast<const char*>(ch.local) + region(src)) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
     }
     __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(x + i);
     const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
-    xp[0] = __floats2bfloat162_rn(a.x + sum[0], a.y + sum[1]);
-    xp[1] = __floats2bfloat162_rn(b.x + sum[2], b.y + sum[3]);
+    xp[0] = __floats2bfloat162_rn(a.x + sum.x, a.y + sum.y);
+    xp[1] = __floats2bfloat162_rn(b.x + sum.z, b.y + sum.w);
 }
 
 // rmsnorm(x[t]) * gamma of every chunk row, written in the forms the chunk's GEMMs take (each output optional):
@@ -437,7 +497,7 @@ int nexrt_prefill_advance(void* ctl, int rows, void* seq, unsigned int n_sites, 
 }
 
 int nexrt_planes_allreduce_residual(void* x, const void* y, int64_t n, int ksplit, const NexrtLLChannel* ch, unsigned int site, void* stream) {
-    if (n < 4 || n % 4 || ksplit < 1 || ch == nullptr || ch->world < 2 || ch->slots < static_cast<unsigned int>(n)) return cudaErrorInvalidValue;
+    if (n < 1024 || n % 1024 || ksplit < 1 || ch == nullptr || ch->world < 2 || ch->slots < static_cast<unsigned int>(n)) return cudaErrorInvalidValue;
     const int64_t threads = n / 4;
     return launch(planes_allreduce_residual_kernel, dim3(static_cast<unsigned int>((threads + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
                   static_cast<__nv_bfloat16*>(x), static_cast<const float*>(y), static_cast<size_t>(n), ksplit, *ch, site);

@@ -17,8 +17,9 @@ tokens.  Here a chunk of ``T`` rows goes through each layer in one pass:
   and its K rows (norm + RoPE) published to the cache first, so the sub-steps do not depend on each other and run
   side by side on their own streams; sub-step ``j`` reads its base position from entry ``j`` of a control-block table,
   which makes the chunk position-independent on the host: it is captured once into a CUDA graph and replayed;
-* on a tensor-parallel group the residual add also all-reduces the chunk's partial sums inside the kernel (LL packets
-  through the multicast alias or peer stores), so the graph holds the whole chunk on every rank.
+* on a tensor-parallel group the residual add also all-reduces the chunk's partial sums inside the kernel (vector
+  stores through the multicast alias or to each peer, one tagged flag word per CTA), so the graph holds the whole
+  chunk on every rank.
 
 The state it leaves (conv / state rings, KV cache, committed length) is the decode path's own, so decode - or the
 8-row prefill of the prompt's tail - continues from it.  Activations are quantised to one e4m3 plane here (the
@@ -116,9 +117,9 @@ class WidePrefill:
         # K split of the expert down product: at most 64 K blocks per CTA, and about two CTAs per SM over the grid
         self.down_ksplit = down_split(self.n_total * I // 128, (H // 128) * ((T + 63) // 64), c.n_cta)
         self.y = z(max(self.down_ksplit, 1), T, H)
-        # tensor parallel: the chunk's partial sums are all-reduced inside the residual kernel over an LL packet channel with
-        # one slot per value of the chunk (the step kernels' channel holds eight rows); it shares the engine's sequence
-        # word and status, so its tags never collide with the decode steps' and a failure stops both
+        # tensor parallel: the chunk's partial sums are all-reduced inside the residual kernel over a symmetric inbox of its
+        # own (8 bytes per value of the chunk and half: data vectors, then one flag word per CTA); it shares the engine's
+        # sequence word and status, so its tags never collide with the decode steps' and a failure stops both
         self.channel = None
         if eng.world > 1:
             from .parallel.channel import LLChannel

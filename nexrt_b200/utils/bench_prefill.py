@@ -1,6 +1,7 @@
 """Prefill throughput of the engine's two prefill paths on one GPU: the 8-row steps and the wide chunks
 (``prefill_wide.WidePrefill``), on a random-init model with the shard shapes of one rank of a ``--tp``-wide group
-(no communication), ``--layers`` layers of the full geometry.
+(no communication), ``--layers`` layers of the full geometry; under ``torchrun`` the ranks form a real tensor-parallel
+group instead and the in-kernel all-reduces run.
 
     python -m nexrt_b200.utils.bench_prefill --layers 8 --tp 8 --length 1024 --wide 64,128
 
@@ -99,11 +100,24 @@ def main(argv=None) -> int:
     from ..models.reference import synthetic_prompt
     from ..weights import random_rank_model
 
-    dev = torch.device("cuda", 0)
+    # under torchrun (WORLD_SIZE > 1) the ranks form a real tensor-parallel group of that size: the all-reduces of both
+    # paths run (in-kernel LL packets), times are the maximum over the ranks
+    import os
+
+    import torch.distributed as dist
+
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     cfg = shrunk_config() if a.shrunk else full_config().truncated(a.layers)
-    model = random_rank_model(cfg, a.tp, 0, dev)
-    eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, shape_tp=a.tp, max_rows=8, cache_len=max(a.length + 1024, 16 * a.stages))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        a.tp = world
+        model = random_rank_model(cfg, world, rank, dev)
+        eng = DecodeEngine(rank, world, dev, ext=model, cfg=cfg, max_rows=8, cache_len=max(a.length + 1024, 16 * a.stages))
+    else:
+        model = random_rank_model(cfg, a.tp, 0, dev)
+        eng = DecodeEngine(0, 1, dev, ext=model, cfg=cfg, shape_tp=a.tp, max_rows=8, cache_len=max(a.length + 1024, 16 * a.stages))
     if a.stages:
         res = stage_costs(eng, a.stages)
         res.update({"layers": cfg.n_layers, "tp_shapes": a.tp, "rows": a.stages, "status": eng.status_max()})
@@ -121,16 +135,23 @@ def main(argv=None) -> int:
         eng.prefill(prompt, chunk=8, wide=wide)
         e1.record()
         torch.cuda.synchronize(dev)
-        return e0.elapsed_time(e1)
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
 
-    out = {"layers": cfg.n_layers, "tp_shapes": a.tp, "length": a.length, "paths": {}}
+    out = {"layers": cfg.n_layers, "tp_shapes": a.tp, "ranks": world, "length": a.length, "paths": {}}
     cases = ([] if a.no_rows else [0]) + [int(w) for w in a.wide.split(",") if w]
     for wide in cases:
         ms = timed(wide)
         name = "rows8" if wide == 0 else f"wide{wide}"
         out["paths"][name] = {"ms": round(ms, 2), "tok_s": round(a.length / ms * 1e3, 1), "us_per_layer_per_token": round(ms * 1e3 / a.length / cfg.n_layers, 2)}
     out["status"] = eng.status_max()
-    print(json.dumps(out), flush=True)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     return 0 if out["status"] == 0 else 1
 
 
