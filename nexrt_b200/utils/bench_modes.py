@@ -3,14 +3,15 @@
 context-parallel attention.
 
     torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 8 -m nexrt_b200.utils.bench_modes \
-        --cases bs1:1024,bs1:65536,bs1cp:65536,mtp:1024,dflash:1024 --rounds 200
+        --cases bs1:1024,bs1:65536,bs1cp:65536,mtp:1024,dflash:1024,prefill:8192 --rounds 200 [--wide 64]
 
 Speculative modes run a real chunked prefill of ``--ctx`` uniform-random tokens (target and draft
 together) and then replay the captured round graph; tokens per round come from the control block, so
 ``tok/s = committed tokens / time``.  Batch-1 long-context cases are timing fixtures: the committed
 length is set to ``--ctx`` over a zero-filled cache (what the reference does for its long-context
 timings, ``nex_n2_5_pro/decode_engine.py:687-723``), because attention time depends on the length of
-the cache and not on its contents.  Timing is CUDA events around back-to-back replays after warm-up,
+the cache and not on its contents.  ``prefill:N`` times the engine's own prefill of N tokens (8-row steps, or wide
+chunks with ``--wide``).  Timing is CUDA events around back-to-back replays after warm-up,
 barrier + synchronise on both sides, MAX over ranks; rank 0 prints one JSON line.
 """
 
@@ -27,7 +28,8 @@ import torch.distributed as dist
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--cases", default="mtp:1024", help="comma list of mode:ctx with mode in bs1, bs1cp, mtp, mtpcp, dflash, dflashcp; run in order on one engine")
+    ap.add_argument("--cases", default="mtp:1024", help="comma list of mode:ctx with mode in bs1, bs1cp, mtp, mtpcp, dflash, dflashcp, prefill; run in order on one engine")
+    ap.add_argument("--wide", type=int, default=0, help="rows per wide prefill chunk for the prefills this tool runs (0 = 8-row steps)")
     ap.add_argument("--rounds", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--layers", type=int, default=0)
@@ -86,6 +88,28 @@ def main(argv=None) -> int:
         t0 = time.time()
         prompt = synthetic_prompt(cfg.vocab, ctx, seed=1)
         eng.set_forced_commit(0)
+        if kind == "prefill":
+            # the engine's own prefill of ctx tokens: second call timed (the first captures the step / chunk graphs)
+            eng.capture(8)
+            eng.prefill(prompt, chunk=8, wide=a.wide)
+            torch.cuda.synchronize(dev)
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.prefill(prompt, chunk=8, wide=a.wide)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms = tp_max(e0.elapsed_time(e1), dev)
+            status = eng.status_max()
+            worst = max(worst, status)
+            if rank == 0:
+                print(json.dumps({"mode": "prefill", "ctx": ctx, "n_gpus": world, "layers": layers, "wide": a.wide, "ms": round(ms, 2),
+                                  "tok_s": round(ctx / ms * 1e3, 1), "status": status, "multicast": bool(eng.ctx.channel.multicast),
+                                  "build_s": round(build_s, 1)}), flush=True)
+            if status:
+                break
+            continue
         if kind == "bs1":
             eng.reset(first_token=prompt[0], committed_len=ctx)
             graph, mean10 = eng.capture(1, cp=use_cp), 10
@@ -93,7 +117,7 @@ def main(argv=None) -> int:
             from ..mtp import capture_round
 
             block = spec_block("mtp")
-            block.prefill(prompt, chunk=8)
+            block.prefill(prompt, chunk=8, wide=a.wide)
             mean10 = 30
             eng.set_forced_commit(0, seed=1234, mean10=mean10)
             graph = capture_round(block, cp=use_cp)
@@ -101,7 +125,7 @@ def main(argv=None) -> int:
             from ..dflash import capture_request
 
             block = spec_block("dflash")
-            block.prefill(prompt)
+            block.prefill(prompt, wide=a.wide)
             mean10 = 50
             eng.set_forced_commit(0, seed=1234, mean10=mean10)
             graph = capture_request(block, cp=use_cp)
