@@ -541,6 +541,8 @@ def main(argv=None) -> int:
     p.add_argument("--wide-prefill", type=int, default=int(os.environ.get("NEXRT_WIDE_PREFILL", "0") or 0),
                    help="rows per wide prefill chunk (16..128, a multiple of 8; every decode mode); 0 = 8-row steps")
     args = p.parse_args(argv)
+    if args.wide_prefill and (args.wide_prefill % 8 or not 16 <= args.wide_prefill <= 128):
+        p.error("--wide-prefill must be 0 or a multiple of 8 between 16 and 128")
     os.environ["NEXRT_WIDE_PREFILL"] = str(args.wide_prefill)      # read by DecodeEngine.prefill
     import torch
     import torch.distributed as dist

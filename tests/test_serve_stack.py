@@ -478,3 +478,13 @@ def test_verify_gate_reports_a_mismatch():
     be.good = False
     assert srv.run_request(_req(text="abc"), ids)["verified"] is False
     assert BridgeServer(FakeBackend(), ByteTokenizer(), log=lambda *_: None).run_request(_req(text="abc"), ids)["verified"] is None
+
+
+def test_worker_rejects_a_bad_wide_prefill_size(capsys):
+    """The chunk size of the wide prefill path is checked before any engine is built."""
+    from nexrt_b200.serve import bridge_serve
+
+    for bad in ("12", "8", "136", "20"):
+        with pytest.raises(SystemExit):
+            bridge_serve.main(["--wide-prefill", bad, "--no-listen"])
+    assert "--wide-prefill must be 0 or a multiple of 8" in capsys.readouterr().err
