@@ -8,7 +8,9 @@ group instead and the in-kernel all-reduces run.
 Timing: CUDA events around a whole ``prefill`` call (host launches included: the 8-row path replays one captured
 step per 8 tokens, the wide path one captured chunk), after one untimed call of the same kind; the prompt is
 uniform-random ids.  ``--stages T`` instead replays the captured wide chunk of ``T`` rows with one stage stubbed out at a
-time and prints what each stage adds to the chunk (timing attribution only: a chunk without a stage is not a prefill).
+time and prints what each stage adds to the chunk (timing attribution only: a chunk without a stage is not a prefill; without
+the norm or the router every row routes to expert 0, the skip list then empties the expert products, and the figure printed
+for those three stages is the experts' cost, not theirs).
 """
 
 from __future__ import annotations
