@@ -19,7 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from ..config import ModelConfig
-from ..quant import dequantize_blockwise
+from ..quant import act_quant_dequant, dequantize_blockwise
 from ..weights import PFX, _scale_key
 
 L2_EPS = 1e-6
@@ -62,8 +62,12 @@ class RefLayerState:
 class RefModel:
     """Token-at-a-time fp32 reference over an HF-named checkpoint dict."""
 
-    def __init__(self, cfg: ModelConfig, ckpt: Dict[str, torch.Tensor]):
+    def __init__(self, cfg: ModelConfig, ckpt: Dict[str, torch.Tensor], fp8_activations: bool = False):
+        """``fp8_activations``: round the input of every FP8 projection to e4m3 with one scale per 128 elements, which is
+        the arithmetic of the wide prefill path (``prefill_wide.py``; the step kernels split activations exactly and
+        match the default).  The router and the b/a projections keep full-precision inputs in both."""
         self.cfg = cfg
+        self.fp8_activations = fp8_activations
         c = cfg
         self.embed = ckpt[PFX + "embed_tokens.weight"].float()
         self.final_ln = 1.0 + ckpt[PFX + "norm.weight"].float()
@@ -110,6 +114,12 @@ class RefModel:
             self.layers.append(w)
         self.reset()
 
+    def _aq(self, v: torch.Tensor) -> torch.Tensor:
+        """Input of an FP8 projection: as is, or through the e4m3 round trip of the wide prefill path."""
+        if not self.fp8_activations:
+            return v
+        return act_quant_dequant(v.reshape(1, -1)).reshape(v.shape)
+
     def reset(self):
         self.pos = 0
         self.route_margin = float("inf")   # smallest gap between the last selected and the first rejected router logit
@@ -120,8 +130,9 @@ class RefModel:
         c = self.cfg
         D, nqk, nv = c.gdn_dim, c.gdn_qk_heads, c.gdn_v_heads
         xn = rms_norm(x, w["in_ln"], c.rms_eps)
-        mixed = w["qkv"] @ xn
-        z = w["z"] @ xn
+        xq = self._aq(xn)
+        mixed = w["qkv"] @ xq
+        z = w["z"] @ xq
         if st.conv is None:
             st.conv = torch.zeros(mixed.numel(), c.conv_kernel - 1)
             st.state = torch.zeros(nv, D, D)
@@ -141,12 +152,12 @@ class RefModel:
         out = (s * q.unsqueeze(-1)).sum(-2)
         on = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + c.rms_eps)
         core = (w["gnorm"] * on * F.silu(z.reshape(nv, D))).reshape(-1)
-        return w["out"] @ core
+        return w["out"] @ self._aq(core)
 
     def _attn(self, w, st: RefLayerState, x: torch.Tensor, pos: int) -> torch.Tensor:
         c = self.cfg
         hd, nq, nkv = c.head_dim, c.n_q_heads, c.n_kv_heads
-        xn = rms_norm(x, w["in_ln"], c.rms_eps)
+        xn = self._aq(rms_norm(x, w["in_ln"], c.rms_eps))
         qg = (w["q"] @ xn).reshape(nq, 2 * hd)
         q, gate = qg[:, :hd], qg[:, hd:]
         k = (w["k"] @ xn).reshape(nkv, hd)
@@ -161,7 +172,7 @@ class RefModel:
         scores = torch.einsum("hd,hsd->hs", q, K.repeat_interleave(rep, 0)) * hd**-0.5
         ctx = torch.einsum("hs,hsd->hd", torch.softmax(scores, -1), V.repeat_interleave(rep, 0))
         gated = (ctx * torch.sigmoid(gate)).reshape(-1)
-        return w["o"] @ gated
+        return w["o"] @ self._aq(gated)
 
     def _moe(self, w, x: torch.Tensor) -> torch.Tensor:
         c = self.cfg
@@ -173,12 +184,13 @@ class RefModel:
         tw, te = probs.topk(c.top_k)
         tw = tw / tw.sum()
         y = torch.zeros(c.hidden)
+        xq = self._aq(xn)
         for wt, e in zip(tw.tolist(), te.tolist()):
-            h = F.silu(w["w1"][e] @ xn) * (w["w3"][e] @ xn)
-            y += wt * (w["w2"][e] @ h)
+            h = F.silu(w["w1"][e] @ xq) * (w["w3"][e] @ xq)
+            y += wt * (w["w2"][e] @ self._aq(h))
         E = c.n_experts
-        h = F.silu(w["w1"][E] @ xn) * (w["w3"][E] @ xn)
-        y += torch.sigmoid(w["sgate"] @ xn) * (w["w2"][E] @ h)
+        h = F.silu(w["w1"][E] @ xq) * (w["w3"][E] @ xq)
+        y += torch.sigmoid(w["sgate"] @ xn) * (w["w2"][E] @ self._aq(h))
         return y
 
     # ---- one token -------------------------------------------------------------------------
