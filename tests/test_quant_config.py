@@ -127,3 +127,17 @@ def test_oracle_with_fp8_activations_quantifies_the_wide_prefill_rounding():
     gdn = rel(rounded.states[0].state, exact.states[0].state)
     keys = rel(torch.stack(rounded.states[1].k, 1), torch.stack(exact.states[1].k, 1))
     assert 0.005 < gdn < 0.1 and 0.02 < keys < 0.3, (gdn, keys)
+
+
+def test_wide_prefill_covers_every_tensor_parallel_degree_of_the_full_model():
+    from types import SimpleNamespace
+
+    from nexrt_b200.config import ShardSpec, full_config, shrunk_config
+    from nexrt_b200.prefill_wide import supported
+
+    for cfg, degrees in ((full_config(), (1, 2, 4, 8)), (shrunk_config(), (1, 2))):
+        for tp in degrees:
+            eng = SimpleNamespace(cfg=cfg, spec=ShardSpec(cfg, tp, 0), max_rows=8)
+            assert supported(eng), (cfg.name, tp)
+    # the sequential parts run eight rows at a time on the step kernels' rings: an engine built for fewer rows is out
+    assert not supported(SimpleNamespace(cfg=full_config(), spec=ShardSpec(full_config(), 8, 0), max_rows=4))
