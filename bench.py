@@ -9,8 +9,15 @@ measures the same metric end to end through ``DecodeEngine.generate`` (per step:
 copy of the request's sampling words from pinned memory, the graph replay, and the token read
 back through the host-mapped control mirror).  Rank 0 prints one JSON line.
 
-The full 60-layer model needs about 390 GB of expert weights, so it runs at N = 8 (and 4); at
-smaller N the stack is truncated to ``--layers`` (default 4) as the scaling configuration names.
+One curve, one model: ``value`` and ``e2e`` are measured on the layer-truncated scaling configuration
+(``--layers``, default 4) at EVERY N, so the ratio between two N is a scaling figure.  The full 60-layer
+model needs about 390 GB of expert weights and therefore exists only at N = 8; there it is run in the same
+process after the scaling configuration and reported under ``full_model`` (device-timed and end-to-end
+tokens/s, ``vs_baseline`` against the published 8xH100 figure, status, clocks).
+
+``--impl nccl`` runs the library-baseline arm: the same step with every fused all-reduce epilogue replaced
+by three graph nodes (projection kernel storing fp32 partials, ``ncclAllReduce``, residual-add kernel).
+``--impl reference`` tries the unmodified reference under ``baseline/_ref`` and reports why it cannot run.
 """
 
 from __future__ import annotations
@@ -19,9 +26,12 @@ import argparse
 import json
 import os
 import sys
+import threading
 import time
+import traceback
 
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
 
 BASELINE_BS1_1K = 386.0   # tok/s, reference chart, 8xH100 TP=8, 1K context, non-CP
 
@@ -31,75 +41,178 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=256)
     p.add_argument("--warmup", type=int, default=10)
-    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--layers", type=int, default=0, help="0: 60 when the model fits (N >= 8), else 4")
+    p.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
+    p.add_argument("--layers", type=int, default=4, help="layers of the scaling configuration (the same at every N)")
+    p.add_argument("--full-model", default="auto", choices=["auto", "on", "off"], help="also run the 60-layer model (auto: at N = 8)")
     p.add_argument("--ctx", type=int, default=1024, help="prompt length")
-    p.add_argument("--mode", default="bs1", choices=["bs1"])
     p.add_argument("--no-pdl", action="store_true")
     return p.parse_args()
 
 
+# ---- reference arm ------------------------------------------------------------------------------------
 def reference_arm(args) -> int:
-    why = ("reference cannot run here: pip install of the reference tree fails (flat layout, run-from-source project); "
-           "its kernels target sm_90a wgmma (absent on sm_100a) and it needs the real checkpoint, SGLang and TP=8 NVLS")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    """Try the unmodified reference from ``baseline/_ref`` and say, with the real error text, why it stops."""
+    rank = int(os.environ.get("RANK", "0"))
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    log_lines = []
+
+    def note(msg: str) -> None:
+        log_lines.append(msg)
+
+    why = None
+    if not os.path.isdir(os.path.join(ref_root, "nex_n2_5_pro")):
+        why = ("baseline/_ref holds no reference tree: `pip install --no-index --target baseline/_ref <reference>` stops at metadata generation "
+               "(\"Multiple top-level packages discovered in a flat-layout: ['assets', 'nex_n2_5_pro']\": the project is run from source)")
+    else:
+        try:
+            import torch
+
+            cap = torch.cuda.get_device_capability(0) if torch.cuda.is_available() else None
+            note(f"device capability: {cap}")
+            sys.path.insert(0, ref_root)
+            import importlib
+
+            kb = importlib.import_module("nex_n2_5_pro.kernel_build")
+            note(f"imported {kb.__file__}")
+            # its stock build of one translation unit that uses no wgmma (the bf16 residual add), then one launch on 256 values
+            kdir = os.path.join(ref_root, "nex_n2_5_pro", "kernels", "util")
+            so = kb.build_kernel(kdir, "nex_n2_5_pro_residual_add_ctypes")
+            note(f"stock build_kernel produced {so} (its flags: -arch=sm_90a)")
+            if cap is None:
+                why = "no GPU visible to the reference arm"
+            else:
+                import ctypes
+
+                lib = ctypes.CDLL(str(so))
+                lib.NexN25ProResidualAddLaunch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+                lib.NexN25ProResidualAddCudaErrorString.restype = ctypes.c_char_p
+                x = torch.zeros(256, dtype=torch.bfloat16, device="cuda")
+                y = torch.ones(256, dtype=torch.float32, device="cuda")
+                err = lib.NexN25ProResidualAddLaunch(x.data_ptr(), y.data_ptr(), 256, None)
+                text = lib.NexN25ProResidualAddCudaErrorString(err).decode()
+                note(f"launch of its residual-add kernel returned cudaError {err}: {text}")
+                if err != 0:
+                    why = (f"the reference's kernels are built for sm_90a only (nex_n2_5_pro/kernel_build.py:173) and do not load on this GPU "
+                           f"(capability {cap[0]}.{cap[1]}): its residual-add launch returns cudaError {err} ({text}); its attention and expert "
+                           f"kernels use wgmma, which sm_100a does not have; it also needs the real checkpoint, SGLang and exactly 8 ranks")
+                else:
+                    why = ("its non-wgmma kernels load, but the decode engine needs the real Nex-N2.5-Pro checkpoint (NEXRT_LAYERS_DIR), SGLang for "
+                           "prefill, exactly 8 ranks with NVLS, and wgmma kernels (attention, experts) that sm_100a cannot run")
+        except BaseException as e:  # noqa: BLE001 - the point is to report whatever stops it
+            note(traceback.format_exc())
+            why = f"the reference stops with {type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:400]
+    if rank == 0:
+        try:
+            os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+            with open(os.path.join(ROOT, "gpurun_out", "reference_attempt.log"), "w") as f:
+                f.write("\n".join(log_lines + [f"unavailable: {why}"]) + "\n")
+        except OSError:
+            pass
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())}), flush=True)
     return 0
 
 
-def main() -> int:
-    args = parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
+# ---- clocks ---------------------------------------------------------------------------------------------
+class NvmlClocks:
+    """SM clock and throttle reasons read through NVML every few milliseconds while a timed region runs (reading only).
+    Falls back to the ``nvidia-smi`` sampler when NVML is not importable."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period_s = index, period_s
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self._h = None
+
+    def sample(self) -> None:
+        if self._h is None:
+            return
+        nv = self._nv
+        try:
+            self.sm.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+            bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+        except Exception:  # noqa: BLE001
+            return
+        for name, const in (("hw_slowdown", "nvmlClocksThrottleReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
+                            ("sw_thermal_slowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksThrottleReasonSwPowerCap")):
+            mask = getattr(nv, const, 0)
+            if mask and bits & mask:
+                self.reasons.add(name)
+
+    def start(self) -> "NvmlClocks":
+        self.sample()                                      # one sample at the start of the region whatever its length
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def _loop(self) -> None:
+        while not self._stop.wait(self.period_s):
+            self.sample()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        self.sample()                                      # and one at its end
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.sm)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ---- one measured configuration ---------------------------------------------------------------------------
+def run_config(args, layers: int, world: int, rank: int, local: int, dev, collective: str) -> dict:
     import torch
     import torch.distributed as dist
 
     from nexrt_b200.config import full_config
-    from nexrt_b200.decode_engine import DecodeEngine
+    from nexrt_b200.decode_engine import WARMUP_STEPS, DecodeEngine
     from nexrt_b200.models.reference import synthetic_prompt
     from nexrt_b200.ops import lib as L
     from nexrt_b200.utils.bench import ClockSampler, tp_max
     from nexrt_b200.weights import random_rank_model
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    group = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     lib = L.load()
-    if args.no_pdl:
-        lib.nexrt_set_pdl(0)
-
-    layers = args.layers or (60 if world >= 8 else 4)
     cfg = full_config().truncated(layers) if layers < 60 else full_config()
     K, W = args.steps, args.warmup
     cache_len = args.ctx + 2 * (K + W) + 128
     t0 = time.time()
     model = random_rank_model(cfg, world, rank, dev, seed=0)
-    eng = DecodeEngine(rank, world, dev, cp=False, ext=model, cfg=cfg, group=group, max_rows=8, cache_len=cache_len)
+    eng = DecodeEngine(rank, world, dev, cp=False, ext=model, cfg=cfg, group=None, max_rows=8, cache_len=cache_len, collective=collective)
     build_s = time.time() - t0
 
-    # ---- the engine's own chunked prefill of a uniform-random prompt
+    # ---- the engine's own chunked prefill of a uniform-random prompt (the library-baseline arm has one-row steps only)
     prompt = synthetic_prompt(cfg.vocab, args.ctx, seed=1)
     eng.reset(first_token=prompt[0])
-    eng.capture(8)
+    chunk = 1 if collective == "nccl" else 8
+    eng.capture(chunk)
     t0 = time.time()
-    first = eng.prefill(prompt, chunk=8)
+    first = eng.prefill(prompt, chunk=chunk)
     prefill_s = time.time() - t0
     state = eng.export_state()
+    # kernels of this library in one step: the launcher counts every kernel it launches; capture() runs WARMUP_STEPS eager
+    # steps and the captured one, all identical
+    eng.graphs.pop((1, False), None)
+    n0 = int(lib.nexrt_launch_count())
     g = eng.capture(1)
-    nodes_per_step = 1 + 6 * cfg.n_layers + 4   # embed, 6 kernels per layer, lm_head (split + tcgen05 logits GEMM + select), step end
+    nodes_per_step = (int(lib.nexrt_launch_count()) - n0) // (WARMUP_STEPS + 1)
 
     # ---- kernel-timed: K captured-graph replays on the device
-    for _ in range(W):
+    for _ in range(max(W, 3)):
         g.replay()
     torch.cuda.synchronize(dev)
-    sampler = ClockSampler(local).start() if rank == 0 else None
+    clocks = NvmlClocks(local).start() if rank == 0 else None
+    smi = ClockSampler(local).start() if rank == 0 else None
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(dev)
@@ -117,7 +230,7 @@ def main() -> int:
     # ---- end to end through the public API: generate() from the same prefill boundary
     eng.load_prefill(state)
     pinned = eng.ctx.sampling.cpu().pin_memory()
-    for _ in range(max(3, W // 2)):
+    for _ in range(3):
         eng.generate(g, max_new=4, host_inputs=pinned)
     eng.load_prefill(state)
     torch.cuda.synchronize(dev)
@@ -127,29 +240,90 @@ def main() -> int:
     out = eng.generate(g, max_new=K, host_inputs=pinned)
     torch.cuda.synchronize(dev)
     e2e_s = tp_max(time.perf_counter() - t0, dev)
-    clocks = sampler.stop() if sampler else {}
+    ck = clocks.stop() if clocks else {}
+    sm = smi.stop() if smi else {}
+    if ck.get("sm_mhz") is None and sm.get("sm_mhz") is not None:
+        ck = sm
+    elif sm.get("reasons"):
+        ck["reasons"] = sorted(set(ck.get("reasons", [])) | set(sm["reasons"]))
     status = max(status, eng.status_max())
+    h2d = pinned.numel() * pinned.element_size()
+    d2h = eng.mirror.bytes_per_read
+    res = {
+        "layers": layers, "ms_per_step": ms / K, "tok_s": K / (ms / 1e3), "e2e_tok_s": len(out) / e2e_s, "status": status, "first_token": first,
+        "nodes_per_step": nodes_per_step, "h2d": h2d, "d2h": d2h, "clocks": {"sm_mhz": ck.get("sm_mhz"), "sm_max_mhz": ck.get("sm_max_mhz"),
+                                                                             "reasons": ck.get("reasons", []), "samples": ck.get("samples", 0)},
+        "build_s": build_s, "prefill_s": prefill_s, "multicast": bool(eng.ctx.channel.multicast), "symm": eng.ctx.channel.buf.backend,
+    }
+    # free the model before the next configuration is built
+    del eng, model, g, state
+    import gc
 
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def main() -> int:
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import torch
+    import torch.distributed as dist
+
+    from nexrt_b200.ops import lib as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = L.load()
+    if args.no_pdl:
+        lib.nexrt_set_pdl(0)
+    collective = "nccl" if args.impl == "nccl" else "fused"
+
+    r = run_config(args, args.layers, world, rank, local, dev, collective)
+    full = None
+    want_full = args.full_model == "on" or (args.full_model == "auto" and world == 8)
+    if want_full and args.layers != 60:
+        full = run_config(args, 60, world, rank, local, dev, collective)
+
+    K, W = args.steps, args.warmup
     if rank == 0:
-        value = K / (ms / 1e3)
-        full = layers == 60 and world == 8 and args.ctx == 1024
         line = {
-            "metric": "decode tok/s per request (BS=1)", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_BS1_1K, 4) if full else None, "dtype": "fp8 e4m3 weights (128x128 block scales), bf16 activations/KV, fp32 accumulate",
+            "metric": "decode tok/s per request (BS=1)", "value": round(r["tok_s"], 2), "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": round(r["ms_per_step"], 5), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(r["tok_s"] / BASELINE_BS1_1K, 4) if (r["layers"] == 60 and world == 8 and args.ctx == 1024) else None,
+            "dtype": "fp8 e4m3 weights (128x128 block scales), bf16 activations/KV, fp32 accumulate",
             "data": "synthetic: uniform-random token prompt, random-init N(0,0.02) weights of the exact geometry",
-            "config": {"model": "Nex-N2.5-Pro" + ("" if layers == 60 else f" truncated to {layers} layers"), "global_batch": 1,
-                       "seq_len": args.ctx, "parallelism": f"tp{world}", "decode": "greedy, whole-step CUDA graph replay",
-                       "l2": "per-step weight working set exceeds the 126 MB L2 (no flush)", "layers": layers,
-                       "prefill": "engine chunked prefill (8-row steps)", "pdl": not args.no_pdl,
-                       "multicast": bool(eng.ctx.channel.multicast), "symm": eng.ctx.channel.buf.backend},
-            "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", [])},
-            "e2e": {"value": round(len(out) / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 64, "d2h_bytes_per_step": 132,
+            "impl": "ours" if collective == "fused" else "nccl-baseline (projection kernel + ncclAllReduce + residual kernel per site)",
+            "config": {"model": "Nex-N2.5-Pro" + ("" if r["layers"] == 60 else f" truncated to {r['layers']} layers (scaling configuration, the same at every N)"),
+                       "global_batch": 1, "seq_len": args.ctx, "parallelism": f"tp{world}", "decode": "greedy, whole-step CUDA graph replay",
+                       "l2": "per-step weight working set exceeds the 126 MB L2 (no flush)", "layers": r["layers"],
+                       "prefill": "engine chunked prefill", "pdl": not args.no_pdl, "multicast": r["multicast"], "symm": r["symm"]},
+            "clocks": r["clocks"],
+            "e2e": {"value": round(r["e2e_tok_s"], 2), "unit": "tok/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
                     "api": "DecodeEngine.generate"},
-            "gpu_launches": K * nodes_per_step, "status": status, "first_token": first,
-            "setup": {"build_s": round(build_s, 1), "prefill_s": round(prefill_s, 2)},
+            "gpu_launches": K * r["nodes_per_step"], "kernel_nodes_per_step": r["nodes_per_step"], "status": r["status"], "first_token": r["first_token"],
+            "setup": {"build_s": round(r["build_s"], 1), "prefill_s": round(r["prefill_s"], 2)},
         }
+        if full is not None:
+            line["full_model"] = {
+                "model": "Nex-N2.5-Pro, all 60 layers", "ms_per_step": round(full["ms_per_step"], 5), "tok_s": round(full["tok_s"], 2),
+                "e2e": {"value": round(full["e2e_tok_s"], 2), "unit": "tok/s", "h2d_bytes_per_step": full["h2d"], "d2h_bytes_per_step": full["d2h"]},
+                "vs_baseline": round(full["tok_s"] / BASELINE_BS1_1K, 4) if (world == 8 and args.ctx == 1024) else None,
+                "e2e_vs_baseline": round(full["e2e_tok_s"] / BASELINE_BS1_1K, 4) if (world == 8 and args.ctx == 1024) else None,
+                "baseline": "386 tok/s, published 8xH100 TP=8 curve at 1K context", "status": full["status"], "clocks": full["clocks"],
+                "kernel_nodes_per_step": full["nodes_per_step"], "gpu_launches": K * full["nodes_per_step"],
+                "setup": {"build_s": round(full["build_s"], 1), "prefill_s": round(full["prefill_s"], 2)},
+            }
         print(json.dumps(line), flush=True)
+    status = max(r["status"], full["status"] if full else 0)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

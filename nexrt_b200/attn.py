@@ -76,11 +76,15 @@ class FullAttn:
         c, lib = self.ctx, self.ctx.lib
         cfg, spec, st = c.cfg, c.spec, c.stream()
         cp_site = c.next_site() if use_cp else 0
+        # bit 8: the kernel may read the committed length before its dependency wait - true for the engine's own control
+        # block inside a step (its only writer is the head at the end of the step, and the step's first kernel holds its
+        # dependents back until everything before the step is complete), not for a draft layer's private block
+        flags = 8 if (ctl is c.ctl and c.early_ctl) else 0
         check(
             lib.nexrt_attn_decode(
                 ptr(c.q_raw), ptr(c.gate), ptr(c.k_raw), ptr(self.w["qn"]), ptr(self.w["kn"]), ptr(c.inv_freq), ptr(c.rope_table(self.cache_len)), ptr(ctl), ptr(self.k_cache),
                 ptr(self.v_cache), ptr(c.ws_acc), ptr(c.ws_ml), ptr(c.attn_ticket), ptr(c.attn_out), cfg.head_dim, nq, spec.q_heads,
-                spec.kv_heads, M, self.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, 0, 0, 0, 0, spec.cp_size if use_cp else 1,
+                spec.kv_heads, M, self.cache_len, cfg.rotary_dim, c.n_splits, cfg.rms_eps, flags, 0, 0, 0, spec.cp_size if use_cp else 1,
                 spec.cp_rank if use_cp else 0, c.cp_channel.ref if use_cp else None, cp_site, st,
             ),
             "attn_decode",
@@ -93,11 +97,12 @@ class FullAttn:
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.attn_out), ptr(c.gate), None, ptr(self.w["out_w"]), ptr(self.w["out_s"]), ptr(c.x), cfg.hidden, spec.attn_local, M,
-                2 if use_cp else 0, cfg.rms_eps, cfg.head_dim, c.channel.ref, c.next_site(), c.cp_channel.ref if use_cp else None, cp_site,
+                2 if use_cp else 0, cfg.rms_eps, cfg.head_dim, c.ar_channel.ref, c.next_site(), c.cp_channel.ref if use_cp else None, cp_site,
                 n_cta, st,
             ),
             "attn_oproj_allreduce",
         )
+        c.after_allreduce(M)
 
     def load_kv(self, k: torch.Tensor, v: torch.Tensor) -> None:
         """Install ``k, v [kv_heads_local][S][head_dim]`` (already normalised and rotated)."""

@@ -25,10 +25,14 @@ from typing import Iterable, List
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-BUILD_ROOT = PKG / "build" / "sm100a"
-LIB_NAME = "libnexrt_b200.so"
+# NEXRT_TRACE_BUILD=1 selects the timeline variant of the library: the same sources compiled with -DNEXRT_TRACE
+# (every kernel records %globaltimer at its phase boundaries, see csrc/common.cuh) into objects and a library of
+# their own, so the product library never carries the instrumentation.
+TRACE_BUILD = os.environ.get("NEXRT_TRACE_BUILD", "0") == "1"
+BUILD_ROOT = PKG / "build" / ("sm100a_trace" if TRACE_BUILD else "sm100a")
+LIB_NAME = "libnexrt_b200_trace.so" if TRACE_BUILD else "libnexrt_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"] + (["-DNEXRT_TRACE"] if TRACE_BUILD else [])
 _INCLUDE_RE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
 
 

@@ -24,6 +24,8 @@
 #include "attn_mma.cuh"
 #include "ll.cuh"
 
+#include <cooperative_groups.h>
+
 namespace nexrt {
 
 struct AttnFrontArgs {
@@ -102,6 +104,8 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
     constexpr int TERMS = MmaShape<MP>::TERMS, NT = MmaShape<MP>::NT, TILE = MmaShape<MP>::TILE, NB = 8, KS = 8;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
+    TraceCta tr;
+    tr.begin(kTrAttnFront);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
@@ -113,6 +117,7 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
     RowNorm<4> norm;
     norm.preload_gamma(a.in_ln, a.H);
     pdl_wait();
+    tr.mark(1);
     const int C0 = a.ctl[kCtlCommittedLen];
     const bool interleaved = a.ngate == a.nq;
     for (int m0 = 0; m0 < a.M; m0 += MP) {
@@ -128,6 +133,7 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
             attn_front_row(a, row0 + rl, m0 + m, mma_result<TERMS, NT>(tiles, KS, rl, m, kSplitDescale), C0, interleaved);
         }
     }
+    tr.mark(3);
 }
 
 struct AttnDecodeArgs {
@@ -195,6 +201,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     constexpr int EL = HD / 32;  // elements per lane
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_last;
+    TraceCta tr;
+    tr.begin(kTrAttnDecode);
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int NW = 8;
@@ -202,6 +210,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     const int G = a.nq / a.kvh;             // q heads attending one kv head
     const int rows = a.M * G;               // row index = m * G + head_in_group
     pdl_wait();
+    tr.mark(1);
     NEXRT_AEVENT(1, blockIdx.x == 0);
     const int C0 = a.ctl[kCtlCommittedLen];
     // key window of this rank: [win_lo, win_hi) of positions, new rows included on the last cp rank
@@ -219,7 +228,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     int n_active = (n_keys + kMinKeysPerSplit - 1) / kMinKeysPerSplit;
     n_active = min(n_active, max(8, static_cast<int>(0.6f * sqrtf(static_cast<float>(n_keys)))));
     n_active = max(1, min(a.n_splits, n_active));
-    if (split >= n_active) return;
+    if (split >= n_active) { tr.mark(3); return; }
     const int per = (n_keys + n_active - 1) / n_active;
     const int lo = win_lo + split * per, hi = min(win_hi, lo + per);
 
@@ -414,12 +423,13 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     }
 
     // ---- ticket: the last CTA of this kv head to arrive combines all splits
+    tr.mark(2);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_active * static_cast<int>(gridDim.z) - 1);
     __syncthreads();
     NEXRT_AEVENT(5, split == 0);
-    if (!s_last) return;
+    if (!s_last) { tr.mark(3); return; }
     __threadfence();
     NEXRT_AEVENT(6, true);
     const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
@@ -512,7 +522,260 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
     __syncthreads();
     NEXRT_AEVENT(8, true);
     if (threadIdx.x == 0) a.ticket[kv] = 0;
+    tr.mark(3);
 #undef NEXRT_AEVENT
+}
+
+
+// ---- cluster form of the tensor-core decode (cp_size == 1) -------------------------------------------------------------
+// The key window is cut over clusters of 8 CTAs.  Inside a cluster the 8 per-CTA partials (un-normalised context, max,
+// sum) are combined through distributed shared memory: after one cluster barrier CTA c reads dims [c HD/8, (c+1) HD/8) of
+// every row from all 8 CTAs, so the split-KV combine of a short context (one cluster = 1024 keys, one 16-key tile per
+// warp) is one DSMEM round trip instead of fence + ticket + a last CTA re-reading everything from L2.  Longer contexts
+// use up to n_splits / 8 clusters, whose partials (at most 18 per kv head) meet in a small ticketed tail.
+//
+// With `flags & 8` the committed length is read BEFORE the dependency wait (the step's first kernel releases its
+// dependents only after its own wait and the head is the only writer of the control block, so the value is final), and
+// the cache rows of this warp's first tile - positions below the committed length, written by earlier steps - are pulled
+// into L1 while the projection front is still running.
+//
+// Replaces wgmma_fd4_mega's software grid barrier + combine (nex_n2_5_pro/kernels/full_attn/
+// nex_n2_5_pro_attn_fd4_wgmma_ctypes.cu:98-118,389-401) with hardware cluster barriers; nothing here spins.
+namespace cg = cooperative_groups;
+constexpr int kClusterCtas = 8;
+constexpr int kKeysPerCluster = kClusterCtas * 8 * 16;   // one 16-key tile per warp
+
+template <int HD>
+__global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs a) {
+    constexpr int RP = kRowsPerPassMma, NW = 8, EL = HD / 32, CL = kClusterCtas, SL = HD / CL;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ int s_last;
+    TraceCta tr;
+    tr.begin(kTrAttnDecode);
+    cg::cluster_group cluster = cg::this_cluster();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kv = blockIdx.y, crank = static_cast<int>(cluster.block_rank()), cidx = blockIdx.x / CL;
+    const int G = a.nq / a.kvh, rows = a.M * G;
+    const bool early = (a.flags & 8) != 0;
+
+    float* q_s = smem;                                   // [rows][HD]
+    float* k_s = q_s + static_cast<size_t>(rows) * HD;   // [M][HD]
+    float* part = k_s + static_cast<size_t>(a.M) * HD;   // [NW][RP][HD + 2]
+    uint4* qf = reinterpret_cast<uint4*>(part + static_cast<size_t>(NW) * RP * (HD + 2));   // [HD / 16][32]
+    float* cpart = reinterpret_cast<float*>(qf + (HD / 16) * 32);                            // [RP][HD] this CTA's partial
+    float* cml = cpart + RP * HD;                                                            // [RP][2]  (max, sum)
+
+    int C0 = 0, win_lo = 0, win_hi = 0, n_act = 1, lo = 0, hi = 0;
+    auto ranges = [&]() {
+        win_lo = 0;
+        win_hi = min(C0 + a.M, a.cache_len);
+        if (a.window > 0) win_lo = max(0, win_hi - a.window);
+        const int n_keys = win_hi - win_lo;
+        n_act = max(1, min(static_cast<int>(gridDim.x) / CL, (n_keys + kKeysPerCluster / 2) / kKeysPerCluster));
+        const int n_ctas = n_act * CL, idx = cidx * CL + crank;
+        const int per = (n_keys + n_ctas - 1) / n_ctas;
+        lo = min(win_hi, win_lo + idx * per);
+        hi = min(win_hi, lo + per);
+    };
+    const __nv_bfloat16* kc = a.k_cache + static_cast<size_t>(kv) * a.cache_len * HD;
+    const __nv_bfloat16* vc = a.v_cache + static_cast<size_t>(kv) * a.cache_len * HD;
+    if (early) {
+        C0 = *reinterpret_cast<const volatile int*>(a.ctl + kCtlCommittedLen);
+        ranges();
+        if (cidx < n_act) {
+            // rows of this warp's first tile that earlier steps wrote: one lane per 128-byte line
+            constexpr int LINES = HD * 2 / 128;
+            const int t0 = lo + 16 * warp, t1 = min(min(t0 + 16, hi), C0);
+            for (int i = lane; i < 16 * LINES; i += 32) {
+                const int p = t0 + i / LINES;
+                if (p < t1) {
+                    prefetch_l1(kc + static_cast<size_t>(p) * HD + (i % LINES) * 64);
+                    prefetch_l1(vc + static_cast<size_t>(p) * HD + (i % LINES) * 64);
+                }
+            }
+        }
+    }
+    pdl_wait();
+    tr.mark(1);
+    if (!early) {
+        C0 = a.ctl[kCtlCommittedLen];
+        ranges();
+    }
+    if (cidx >= n_act) { tr.mark(3); return; }          // whole clusters leave: no barrier is left half attended
+
+    const int r0 = static_cast<int>(blockIdx.z) * RP, nr = min(RP, rows - r0);
+    // the output gates of this CTA's slice are needed only at the very end: request them now
+    float gate_v = 0.f;
+    const int fr = static_cast<int>(threadIdx.x) / SL, fd = crank * SL + static_cast<int>(threadIdx.x) % SL;   // (row, dim) of the final combine
+    if (fr < nr && !(a.flags & 2))
+        gate_v = __ldcg(a.gate + (static_cast<size_t>((r0 + fr) / G) * a.ngate + kv * G + (r0 + fr) % G) * HD + fd);
+
+    const float qscale = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;
+    const int half = a.rotary / 2;
+    // ---- q and new-k normalisation + RoPE, one warp per vector (same arithmetic as attn_decode_kernel)
+    for (int v = warp; v < rows + a.M; v += NW) {
+        const bool is_q = v < rows;
+        const int m = is_q ? v / G : v - rows;
+        const size_t ldq = a.ldq ? a.ldq : static_cast<size_t>(a.nq) * HD, ldk = a.ldk ? a.ldk : static_cast<size_t>(a.kvh) * HD;
+        const float* src = is_q ? a.q_raw + static_cast<size_t>(m) * ldq + static_cast<size_t>(kv * G + (v % G)) * HD
+                                : a.k_raw + static_cast<size_t>(m) * ldk + static_cast<size_t>(kv) * HD;
+        float* dst = is_q ? q_s + static_cast<size_t>(v) * HD : k_s + static_cast<size_t>(m) * HD;
+        const float* gam = is_q ? a.qn : a.kn;
+        float e[EL], ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < EL; ++i) { e[i] = src[lane + 32 * i]; ss = fmaf(e[i], e[i], ss); }
+        const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(HD) + a.eps);
+#pragma unroll
+        for (int i = 0; i < EL; ++i) dst[lane + 32 * i] = e[i] * inv * gam[lane + 32 * i];
+        __syncwarp();
+        const float pos = static_cast<float>(C0 + m);
+        float rot[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        int ri[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int i = lane + 32 * c;
+            if (i >= a.rotary) break;
+            const int f = i < half ? i : i - half;
+            float sn, cs;
+            if (a.rope_table != nullptr && C0 + m < a.cache_len) {
+                const float2 cssn = a.rope_table[static_cast<size_t>(C0 + m) * half + f];
+                cs = cssn.x; sn = cssn.y;
+            } else {
+                sincosf(pos * a.inv_freq[f], &sn, &cs);
+            }
+            const float self = dst[i], other = i < half ? -dst[i + half] : dst[i - half];
+            rot[c] = self * cs + other * sn;
+            ri[c] = i;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            if (ri[c] >= 0) dst[ri[c]] = rot[c];
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < EL; ++i) {
+            const float val = dst[lane + 32 * i];
+            dst[lane + 32 * i] = is_q ? val * qscale : bf16_round(val);
+        }
+        if (!is_q && cidx == 0 && crank == 0 && C0 + m < a.cache_len && !(a.flags & 4)) {
+#pragma unroll
+            for (int i = 0; i < EL; ++i)
+                a.k_cache[(static_cast<size_t>(kv) * a.cache_len + C0 + m) * HD + lane + 32 * i] = __float2bfloat16_rn(dst[lane + 32 * i]);
+        }
+    }
+    __syncthreads();
+
+    // ---- this CTA's keys on the tensor cores, eight query rows
+    {
+        const AttnMmaKeys keys{kc, vc, k_s, C0, lo, hi};
+        const int gr = lane >> 2;
+        const int my_limit = gr < nr ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + (r0 + gr) / G) : -1;
+        attn_mma_stage_q<HD>(qf, q_s + static_cast<size_t>(r0) * HD, nr);
+        __syncthreads();
+        attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        __syncthreads();
+    }
+    // ---- the 8 warps of the CTA into one partial in shared memory
+    for (int idx = threadIdx.x; idx < nr * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx % HD;
+        float M_ = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M_ = fmaxf(M_, part[(static_cast<size_t>(w) * RP + r) * (HD + 2) + HD]);
+        float L_ = 0.f, A_ = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float* pr = part + (static_cast<size_t>(w) * RP + r) * (HD + 2);
+            const float sc = pr[HD] == -INFINITY ? 0.f : exp2f(pr[HD] - M_);
+            L_ = fmaf(pr[HD + 1], sc, L_);
+            A_ = fmaf(pr[d], sc, A_);
+        }
+        cpart[idx] = A_;
+        if (d == 0) { cml[r * 2] = M_; cml[r * 2 + 1] = L_; }
+    }
+    tr.mark(2);
+    cluster.sync();
+    // ---- CTA c combines dims [c SL, (c + 1) SL) of every row over the cluster
+    if (fr < nr) {
+        float Av[CL], Mv[CL], Lv[CL], Mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < CL; ++c) {
+            const float* rp = cluster.map_shared_rank(cpart, c);
+            const float* rm = cluster.map_shared_rank(cml, c);
+            Av[c] = rp[fr * HD + fd];
+            Mv[c] = rm[fr * 2];
+            Lv[c] = rm[fr * 2 + 1];
+        }
+#pragma unroll
+        for (int c = 0; c < CL; ++c) Mx = fmaxf(Mx, Mv[c]);
+        float A_ = 0.f, L_ = 0.f;
+#pragma unroll
+        for (int c = 0; c < CL; ++c) {
+            const float w = Mv[c] == -INFINITY ? 0.f : exp2f(Mv[c] - Mx);
+            A_ = fmaf(Av[c], w, A_);
+            L_ = fmaf(Lv[c], w, L_);
+        }
+        const int row = r0 + fr;
+        if (n_act == 1) {
+            float ctx = L_ > 0.f ? A_ / L_ : 0.f;
+            if (!(a.flags & 2)) ctx *= sigmoid_f(gate_v);
+            a.out[(static_cast<size_t>(row / G) * a.ngate + kv * G + row % G) * HD + fd] = ctx;
+        } else {
+            a.ws_acc[((static_cast<size_t>(kv) * a.n_splits + cidx) * rows + row) * HD + fd] = A_;
+            if (fd == 0) {
+                float* ml = a.ws_ml + ((static_cast<size_t>(kv) * a.n_splits + cidx) * rows + row) * 2;
+                ml[0] = Mx; ml[1] = L_;
+            }
+        }
+    }
+    if (n_act > 1) __threadfence();
+    cluster.sync();                                      // nobody leaves while a peer may still read its shared memory
+    if (n_act == 1 || crank != 0) { tr.mark(3); return; }
+
+    // ---- several clusters: the last one to arrive (per kv head, over all passes) merges their partials
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_act * static_cast<int>(gridDim.z) - 1);
+    __syncthreads();
+    if (!s_last) { tr.mark(3); return; }
+    __threadfence();
+    const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
+    const float* base_ml = a.ws_ml + static_cast<size_t>(kv) * a.n_splits * rows * 2;
+    constexpr int MAXC = 20;                             // clusters per kv head: n_splits (<= 160) / 8
+    for (int q4 = threadIdx.x; q4 < rows * HD / 4; q4 += blockDim.x) {
+        const int idx = q4 * 4, r = idx / HD, d = idx % HD;
+        float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!(a.flags & 2)) gt = __ldcg(reinterpret_cast<const float4*>(a.gate + (static_cast<size_t>(r / G) * a.ngate + kv * G + r % G) * HD + d));
+        float2 ml[MAXC];
+        float4 v[MAXC];
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+            ml[c] = make_float2(-INFINITY, 0.f);
+            v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < n_act) {
+                ml[c] = __ldcg(reinterpret_cast<const float2*>(base_ml + (static_cast<size_t>(c) * rows + r) * 2));
+                v[c] = __ldcg(reinterpret_cast<const float4*>(base_acc + (static_cast<size_t>(c) * rows + r) * HD + d));
+            }
+        }
+        float Mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) Mx = fmaxf(Mx, ml[c].x);
+        float4 A_ = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L_ = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+            const float w = ml[c].x == -INFINITY ? 0.f : exp2f(ml[c].x - Mx);
+            L_ = fmaf(ml[c].y, w, L_);
+            A_.x = fmaf(v[c].x, w, A_.x); A_.y = fmaf(v[c].y, w, A_.y); A_.z = fmaf(v[c].z, w, A_.z); A_.w = fmaf(v[c].w, w, A_.w);
+        }
+        const float invl = L_ > 0.f ? 1.f / L_ : 0.f;
+        float4 ctx = make_float4(A_.x * invl, A_.y * invl, A_.z * invl, A_.w * invl);
+        if (!(a.flags & 2)) {
+            ctx.x *= sigmoid_f(gt.x); ctx.y *= sigmoid_f(gt.y); ctx.z *= sigmoid_f(gt.z); ctx.w *= sigmoid_f(gt.w);
+        }
+        *reinterpret_cast<float4*>(a.out + (static_cast<size_t>(r / G) * a.ngate + kv * G + r % G) * HD + d) = ctx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) a.ticket[kv] = 0;
+    tr.mark(3);
 }
 
 }  // namespace nexrt
@@ -589,6 +852,18 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) != 0;
+    if (mma && (gemv_mode() & 64) && cp_size == 1 && n_splits >= kClusterCtas) {
+        // cluster form: whole clusters of 8 CTAs along x; its shared memory adds this CTA's partial for the DSMEM combine
+        const int n_clusters = n_splits / kClusterCtas, passes_c = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;
+        const size_t rows = static_cast<size_t>(M) * (nq / kvh);
+        const size_t smem_c = sizeof(float) * (rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPassMma * (hd + 2) + static_cast<size_t>(hd / 16) * 32 * 4 +
+                                               kRowsPerPassMma * hd + kRowsPerPassMma * 2);
+        const dim3 g(n_clusters * kClusterCtas, kvh, passes_c);
+        if (hd == 256) return launch_cluster(attn_decode_cluster_kernel<256>, g, dim3(256), smem_c, st, kClusterCtas, a);
+        if (hd == 128) return launch_cluster(attn_decode_cluster_kernel<128>, g, dim3(256), smem_c, st, kClusterCtas, a);
+        return cudaErrorInvalidValue;
+    }
+    a.flags &= ~8;   // only the cluster kernel reads the control block before its dependency wait
     const int passes = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;     // tensor-core path: eight query rows per CTA
     if (hd == 256) return mma ? launch(attn_decode_kernel<256, true>, dim3(n_splits, kvh, passes), dim3(256), smem, st, a)
                               : launch(attn_decode_kernel<256, false>, dim3(n_splits, kvh), dim3(256), smem, st, a);

@@ -121,6 +121,28 @@ __device__ __forceinline__ void prefetch_l2(const void* p) {
 
 // Pull a byte range towards L2 with the whole CTA (used in the window before the dependency
 // wait, where a kernel may touch only constant weights).
+// CTA `b` of `n` pulls its share of [base, base + bytes) towards L2, one 128-byte line per prefetch: the way a kernel
+// that is idle before its dependency wait warms the cache for a LATER kernel whose CTAs will not be resident in time to
+// preload their weights themselves.
+__device__ __forceinline__ void prefetch_l2_slice(const void* base, size_t bytes, int b, int n) {
+    if (base == nullptr || bytes == 0) return;
+    const size_t lines = (bytes + 127) >> 7, per = (lines + n - 1) / n;
+    const size_t lo = static_cast<size_t>(b) * per, hi = lo + per < lines ? lo + per : lines;
+    const char* p = static_cast<const char*>(base);
+    for (size_t l = lo + threadIdx.x; l < hi; l += blockDim.x) prefetch_l2(p + (l << 7));
+}
+
+__device__ __forceinline__ unsigned int redux_max_u32(unsigned int v) {
+    unsigned int r;
+    asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ unsigned int redux_min_u32(unsigned int v) {
+    unsigned int r;
+    asm volatile("redux.sync.min.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+    return r;
+}
+
 __device__ __forceinline__ void prefetch_l2_range(const void* base, size_t bytes) {
     const char* p = static_cast<const char*>(base);
     for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < bytes; off += static_cast<size_t>(blockDim.x) * 128)
@@ -151,6 +173,46 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+
+// ---- kernel timeline (trace build only: -DNEXRT_TRACE) ------------------------------------------
+// Thread 0 of every CTA records %globaltimer at four points of its life - 0 entry, 1 dependency
+// wait over, 2 a kernel-specific midpoint (own product finished, before the ticket / all-reduce),
+// 3 exit - into a per-kind record list.  The slot comes from one atomicAdd issued at entry, whose
+// latency hides behind the weight preload; the four stores are fire-and-forget.  The regular
+// build compiles all of this to nothing, so the product kernels carry no extra registers.
+enum TraceKind : int {
+    kTrEmbed = 0, kTrGdnFront, kTrGdnCore, kTrOproj, kTrRouter, kTrMoeL1, kTrMoeL2, kTrAttnFront, kTrAttnDecode, kTrHead, kTrStepEnd,
+    kTrMoeFused, kTrGdnFused, kTraceKinds = 16
+};
+constexpr int kTraceSlots = 20480;        // records per kind
+constexpr int kTraceWords = 5;            // cta | grid << 32, t0, t1, t2, t3
+#ifdef NEXRT_TRACE
+static __constant__ unsigned long long* c_trace;   // [kTraceKinds cursors][kinds][slots][words]; one copy per translation unit
+struct TraceCta {
+    unsigned long long* rec;
+    unsigned long long t0;
+    __device__ __forceinline__ void begin(int kind) {
+        rec = nullptr;
+        if (threadIdx.x != 0 || c_trace == nullptr) return;
+        t0 = globaltimer_ns();
+        const unsigned long long slot = atomicAdd(c_trace + kind, 1ull);
+        if (slot >= static_cast<unsigned long long>(kTraceSlots)) return;
+        rec = c_trace + kTraceKinds + (static_cast<size_t>(kind) * kTraceSlots + slot) * kTraceWords;
+        const unsigned long long cta = blockIdx.x + gridDim.x * (blockIdx.y + static_cast<unsigned long long>(gridDim.y) * blockIdx.z);
+        rec[0] = cta | (static_cast<unsigned long long>(gridDim.x * gridDim.y * gridDim.z) << 32);
+        rec[1] = t0;
+    }
+    __device__ __forceinline__ void mark(int phase) {
+        if (threadIdx.x == 0 && rec != nullptr) rec[1 + phase] = globaltimer_ns();
+    }
+};
+#else
+struct TraceCta {
+    __device__ __forceinline__ void begin(int) {}
+    __device__ __forceinline__ void mark(int) {}
+};
+#endif
+
 }  // namespace nexrt
 
 // ---- host side --------------------------------------------------------------------------------
@@ -158,14 +220,36 @@ namespace nexrt {
 
 // Process-wide switch: launch with the programmatic-stream-serialisation attribute.
 int& pdl_enabled();
+// Kernels launched through launch() since the library was loaded (a capture counts its nodes with it).
+unsigned long long& launch_counter();
+// Library-baseline arm: when set, the projection kernels that end in an all-reduce store their fp32 partial sums here
+// instead of exchanging them (see epilogue.cuh); null in normal operation.
+float*& partial_out_buffer();
+
+#ifdef NEXRT_TRACE
+unsigned long long*& trace_buffer();   // device address of the trace buffer (step.cu), null: off
+// Copies the buffer address into this translation unit's constant; called by every launch, so it must have
+// run once (an eager step) before a stream capture begins.
+static inline int trace_install() {
+    static unsigned long long* installed = nullptr;
+    unsigned long long* want = trace_buffer();
+    if (want == installed) return 0;
+    const cudaError_t e = cudaMemcpyToSymbol(c_trace, &want, sizeof(want));
+    if (e == cudaSuccess) installed = want;
+    return static_cast<int>(e);
+}
+#endif
 
 template <typename... KArgs, typename... Args>
-inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                   Args... args) {
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
     }
+#ifdef NEXRT_TRACE
+    if (const int te = trace_install()) return te;
+#endif
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -176,6 +260,37 @@ inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    ++launch_counter();
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
+
+// Same launch with thread-block clusters of `cluster_x` CTAs along x (grid.x must be a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x, Args... args) {
+    if (cluster_x < 1 || grid.x % cluster_x) return static_cast<int>(cudaErrorInvalidValue);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+#ifdef NEXRT_TRACE
+    if (const int te = trace_install()) return te;
+#endif
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    ++launch_counter();
     return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 

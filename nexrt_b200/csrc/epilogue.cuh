@@ -8,8 +8,15 @@
 namespace nexrt {
 
 // res: shared memory [M][nrows] fp32 partial sums of this rank.
+// partial_out (library-baseline arm only): when non-null the CTA stores its fp32 partial sums there ([M][H]) and leaves
+// both the exchange and the residual to the nodes that follow (a library all-reduce and a residual-add kernel).
 __device__ __forceinline__ void allreduce_residual(const LLChannel& ch, unsigned int site, const float* res, int M, int row0, int nrows,
-                                                   int H, __nv_bfloat16* __restrict__ x, bool add_residual = true) {
+                                                   int H, __nv_bfloat16* __restrict__ x, bool add_residual = true, float* partial_out = nullptr) {
+    if (partial_out != nullptr) {
+        for (int idx = threadIdx.x; idx < M * nrows; idx += blockDim.x)
+            partial_out[static_cast<size_t>(idx / nrows) * H + row0 + idx % nrows] = res[idx];
+        return;
+    }
     LLCall call{0u, 0u};
     if (ch.world > 1) call = ll_begin(ch, site);
     for (int idx = threadIdx.x; idx < M * nrows; idx += blockDim.x) {

@@ -131,6 +131,8 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     NEXRT_EVENT(0);
+    TraceCta tr;
+    tr.begin(kTrGdnFront);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
@@ -155,6 +157,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row0 + threadIdx.x) * 4);
     NEXRT_EVENT(2);
     pdl_wait();
+    tr.mark(1);
     NEXRT_EVENT(3);
     const int C0 = a.ctl[kCtlCommittedLen];
     for (int m0 = 0; m0 < a.M; m0 += MP) {
@@ -165,6 +168,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         float d[NT][4];
         mw.template run<NT>(src, xq, a.H, mb * TERMS, d);
         mw.template store<NT>(tiles + warp * TILE, d);
+        tr.mark(2);
         NEXRT_EVENT(5);
         if (ba_cta) {
             if (m0 == 0) gba.run(xs, part_ba);
@@ -183,6 +187,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         }
         NEXRT_EVENT(6);
     }
+    tr.mark(3);
 }
 
 // Tail of the wide front (multi-row steps): the q|k|v|z projections of all rows were produced by the tcgen05 rows
@@ -239,6 +244,8 @@ struct GdnCoreArgs {
 
 // grid (nv, 128 / warps-per-CTA); one warp per value column, lane holds 4 key rows.
 __global__ void __launch_bounds__(256) gdn_core_kernel(GdnCoreArgs a) {
+    TraceCta tr;
+    tr.begin(kTrGdnCore);
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int head = blockIdx.x, col = blockIdx.y * nwarps + warp;
@@ -246,6 +253,7 @@ __global__ void __launch_bounds__(256) gdn_core_kernel(GdnCoreArgs a) {
     const size_t head_stride = static_cast<size_t>(128) * 128, slot_stride = head_stride * a.nv;
     const size_t elem = head * head_stride + static_cast<size_t>(col) * 128 + lane * 4;
     pdl_wait();
+    tr.mark(1);
     const int C0 = a.ctl[kCtlCommittedLen];
     float4 S = *reinterpret_cast<const float4*>(a.state_ring + static_cast<size_t>(C0 % a.state_ring_len) * slot_stride + elem);
     for (int m = 0; m < a.M; ++m) {
@@ -265,6 +273,7 @@ __global__ void __launch_bounds__(256) gdn_core_kernel(GdnCoreArgs a) {
         *reinterpret_cast<float4*>(a.state_ring + static_cast<size_t>((C0 + m + 1) % a.state_ring_len) * slot_stride + elem) = S;
         if (lane == 0) a.out[static_cast<size_t>(m) * a.nv * 128 + head * 128 + col] = o;
     }
+    tr.mark(3);
 }
 
 }  // namespace nexrt

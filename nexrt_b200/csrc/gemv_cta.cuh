@@ -27,7 +27,8 @@ namespace nexrt {
 int& gemv_threads_ref();
 inline int gemv_threads() { return gemv_threads_ref(); }
 // Bit mask of the kernels that use the tensor-core GEMV where the shape allows (1: projection
-// fronts, 2: out-projection, 4: expert gate/up, 8: expert down, 16: router and gate rows); 0 selects the CUDA-core kernels.
+// fronts, 2: out-projection, 4: expert gate/up, 8: expert down, 16: router and gate rows, 32: attention key loop; 64: the
+// attention decode runs as thread-block clusters with a DSMEM combine); 0 selects the CUDA-core kernels.
 int& gemv_mode_ref();
 inline int gemv_mode() { return gemv_mode_ref(); }
 

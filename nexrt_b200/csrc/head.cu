@@ -198,6 +198,7 @@ struct HeadArgs {
     int mode, arg;                   // 1: sample + accept + commit; 2: greedy, row r -> ctl ids[arg + r]
     LLChannel ch;
     unsigned int site;
+    size_t smem_bytes;               // dynamic shared memory of the launch (the last CTA stages the candidate lists in it)
 };
 
 template <int MB>
@@ -208,6 +209,8 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     __shared__ int s_tok[kMaxRows];
     __shared__ int s_status;
     __shared__ unsigned long long s_top[kMaxRows][kMaxTopK];
+    TraceCta tr;
+    tr.begin(kTrHead);
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     int v0, v1;
@@ -227,6 +230,7 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
         for (int i = threadIdx.x; i < a.H; i += blockDim.x) gs[i] = a.final_ln[i];
     }
     pdl_wait();
+    tr.mark(1);
     const SamplingCfg cfg = read_sampling(a.sampling);
     const int K = a.mode == 2 ? 1 : cfg.top_k;
     for (int m0 = 0; m0 < a.M; m0 += MB) {
@@ -270,20 +274,37 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
             }
         }
     }
+    tr.mark(2);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1) == static_cast<int>(gridDim.x) - 1);
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) { tr.mark(3); return; }
     __threadfence();
     if (threadIdx.x == 0) s_status = cfg.bad ? kStatusBadConfig : 0;
     __syncthreads();
-    // ---- last CTA: warp m merges row m's per-CTA lists (each sorted descending)
+    // ---- last CTA: the per-CTA lists (each sorted descending) are staged in shared memory with one round of coalesced
+    // loads - the GEMV's buffers are free now - and warp m merges row m's lists from there, `rows_fit` rows at a time
     const int n_lists = gridDim.x;
     LLCall call{0u, 0u};
     if (a.ch.world > 1) call = ll_begin(a.ch, a.site);
-    for (int m = warp; m < a.M; m += nwarps) {
+    unsigned long long* stage = reinterpret_cast<unsigned long long*>(smem);
+    const int per_row = n_lists * K;
+    const int rows_fit = max(1, min(nwarps, static_cast<int>(a.smem_bytes / (sizeof(unsigned long long) * per_row))));
+    const bool staged = a.smem_bytes >= sizeof(unsigned long long) * per_row;
+    for (int mbase = 0; mbase < a.M; mbase += rows_fit) {
+    const int mcount = min(rows_fit, a.M - mbase);
+    __syncthreads();
+    if (staged) {
+        for (int idx = threadIdx.x; idx < mcount * per_row; idx += blockDim.x) {
+            const int mm = idx / per_row, rem = idx % per_row, li = rem / K, k = rem % K;
+            stage[idx] = __ldcg(a.cand + (static_cast<size_t>(mbase + mm) * n_lists + li) * kMaxTopK + k);
+        }
+    }
+    __syncthreads();
+    for (int m = mbase + warp; m < mbase + mcount; m += nwarps) {
         const unsigned long long* lists = a.cand + static_cast<size_t>(m) * n_lists * kMaxTopK;
+        const unsigned long long* srow = stage + static_cast<size_t>(m - mbase) * per_row;
         constexpr int kListsPerLane = 8;   // up to 256 CTAs
         int head[kListsPerLane];
 #pragma unroll
@@ -295,11 +316,14 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
             for (int i = 0; i < kListsPerLane; ++i) {
                 const int li = lane + 32 * i;
                 if (li < n_lists && head[i] < K) {
-                    const unsigned long long c = __ldcg(lists + static_cast<size_t>(li) * kMaxTopK + head[i]);
+                    const unsigned long long c = staged ? srow[li * K + head[i]] : __ldcg(lists + static_cast<size_t>(li) * kMaxTopK + head[i]);
                     if (c > best) { best = c; bl = i; }
                 }
             }
-            const unsigned long long win = warp_max_u64(best);
+            // 64-bit maximum over the warp on the warp-reduce unit: high words first, then the low words of the lanes that tie
+            const unsigned int hi_max = redux_max_u32(static_cast<unsigned int>(best >> 32));
+            const unsigned int lo_max = redux_max_u32(static_cast<unsigned int>(best >> 32) == hi_max ? static_cast<unsigned int>(best) : 0u);
+            const unsigned long long win = (static_cast<unsigned long long>(hi_max) << 32) | lo_max;
             if (win != 0ull && best == win && bl >= 0) {
 #pragma unroll
                 for (int i = 0; i < kListsPerLane; ++i)
@@ -354,6 +378,7 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
             if (st) atomicCAS(&s_status, 0, st);
         }
     }
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         const int upstream = s_status | (a.ch.status ? *reinterpret_cast<volatile int*>(a.ch.status) : 0);
@@ -365,6 +390,7 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
         }
         *a.ticket = 0;
     }
+    tr.mark(3);
 }
 
 // Sample row 0 from full fp32 logits [V] already in memory (first token after a prefill whose
@@ -419,6 +445,7 @@ extern "C" int nexrt_lmhead_sample(const void* x, const void* final_ln, const vo
     const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, gemv_threads()))) +
                         sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max + sizeof(float) * H;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    a.smem_bytes = smem;
     if (mb == 1) return launch(lmhead_sample_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
     return launch(lmhead_sample_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }
@@ -438,6 +465,7 @@ extern "C" int nexrt_lmhead_sample_from_logits(const void* logits_in, void* cand
     const size_t smem = sizeof(float) * (static_cast<size_t>(mb) * H + gemv_part_floats(256, mb, gemv_geom(H / 8, gemv_threads()))) +
                         sizeof(unsigned long long) * static_cast<size_t>(mb) * nv_max + sizeof(float) * H;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    a.smem_bytes = smem;
     if (mb == 1) return launch(lmhead_sample_kernel<1>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
     return launch(lmhead_sample_kernel<4>, dim3(n_cta), dim3(gemv_threads()), smem, st, a);
 }

@@ -39,7 +39,62 @@ struct RouterArgs {
     float* partial;           // tensor-core form: [4 k-quarters][M][rows_pad]
     int rows_pad;             // rows of w padded to a multiple of 16 (0: not padded)
     uint8_t* planes;          // optional [3M][H] e4m3: the normalised rows split for the tcgen05 expert kernels (CTA m writes row m)
+    int no_tail;              // 1: stop after the partial logits; the expert gate/up kernel sums them and selects (moe_l1_mma_kernel)
 };
+
+// Order-preserving image of an fp32 in u32 (never 0 for a finite value or an infinity), so that an integer max picks the
+// largest logit.
+__device__ __forceinline__ unsigned int router_key(float f) {
+    const unsigned int b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float router_unkey(unsigned int o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o); }
+
+// Top-k of one token row by one warp from logits in shared memory, on the warp-reduce unit: lane holds experts lane,
+// lane + 32, ... as integer keys and its running maximum; a round is one `redux.sync.max` for the value, one
+// `redux.sync.min` over the ids that hold it (ties go to the lowest expert id), and a 16-way rescan by the one lane
+// that owned the winner.  Same selection and the same softmax over the selected logits as router_topk above.
+// ids / wts: [topk + 1] (shared or global); the last entry is the shared expert E with sigmoid(gate logit).
+__device__ __forceinline__ void router_topk_warp(const float* lg, int E, int topk, int* ids, float* wts) {
+    const int lane = threadIdx.x & 31;
+    unsigned int key[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int e = lane + 32 * i;
+        key[i] = e < E ? router_key(lg[e]) : 0u;
+    }
+    unsigned int lm = 0u;
+    int li = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        if (key[i] > lm) { lm = key[i]; li = i; }
+    float top0 = 0.f, denom = 0.f, mine = 0.f;
+    int mine_id = -1;
+    for (int k = 0; k < topk; ++k) {
+        const unsigned int gm = redux_max_u32(lm);
+        const unsigned int gi = redux_min_u32(lm == gm ? static_cast<unsigned int>(lane + 32 * li) : 0xffffffffu);
+        const float bv = router_unkey(gm);
+        if (k == 0) top0 = bv;
+        const float ex = __expf(bv - top0);
+        denom += ex;
+        if (lane == k) { mine = ex; mine_id = static_cast<int>(gi); }
+        if ((gi & 31u) == static_cast<unsigned int>(lane)) {
+            lm = 0u; li = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if (i == static_cast<int>(gi >> 5)) key[i] = 0u;
+                if (key[i] > lm) { lm = key[i]; li = i; }
+            }
+        }
+    }
+    if (lane < topk) {
+        ids[lane] = mine_id;
+        wts[lane] = mine / denom;
+    } else if (lane == topk) {
+        ids[lane] = E;
+        wts[lane] = sigmoid_f(lg[E]);
+    }
+}
 
 // Top-k of every token row by the calling CTA: warp m owns row m, lane holds logits lane,
 // lane + 32, ...; ties go to the lowest expert id; weights are a softmax over the selected logits.
@@ -145,6 +200,15 @@ struct MoeL1Args {
     int H, I, S, M;
     float eps;
     int shared_expert;      // index whose weights may be prefetched before the dependency wait
+    // routed form (tensor-core kernel only): the router left K-quarter partial logits and this kernel selects the experts
+    const float* partial;   // [4][M][rows_pad] or null (ids come from memory)
+    int rows_pad, E, topk;
+    int* ids_out;           // [M][S]   written by CTA 0 for the down projection
+    float* wts_out;         // [M][S]
+    float* logits_out;      // [M][E+1] summed logits (inspection, tests)
+    const uint8_t* w2;      // [E+1][H][I]: the selected experts' down weights are pulled towards L2 once the ids are known
+    const void* pf;         // a later kernel's constant weights to pull towards L2 before the dependency wait (or null)
+    unsigned long long pf_bytes;
 };
 
 __global__ void __launch_bounds__(512, 1) moe_l1_kernel(MoeL1Args a) {
@@ -190,6 +254,7 @@ struct MoeL2Args {
     int H, I, S, M;
     LLChannel ch;
     unsigned int site;
+    float* partial_out;     // library-baseline arm: fp32 partial sums go here, no exchange, no residual
 };
 
 __global__ void __launch_bounds__(512, 1) moe_l2_allreduce_kernel(MoeL2Args a) {
@@ -220,7 +285,7 @@ __global__ void __launch_bounds__(512, 1) moe_l2_allreduce_kernel(MoeL2Args a) {
         for (int rl = threadIdx.x; rl < nrows; rl += blockDim.x) res[m * nrows + rl] = gemv_result(part, rl, 0, 1, gg.wpr);
     }
     __syncthreads();
-    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x);
+    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x, true, a.partial_out);
 }
 
 // Router on the tensor cores: bf16 weights [rows_pad][H], one CTA per (16 rows, quarter of K), the
@@ -232,6 +297,8 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_last;
+    TraceCta tr;
+    tr.begin(kTrRouter);
     const int warp = threadIdx.x >> 5;
     const int rg = blockIdx.x / KQ, kq = blockIdx.x % KQ, rows = a.E + 1;
     const int nq = a.H / 32 / KQ;                                       // 64-byte windows per quarter
@@ -243,6 +310,7 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     RowNorm<4> norm;
     norm.preload_gamma(a.post_ln, a.H);
     pdl_wait();
+    tr.mark(1);
     // Released only now: the expert gate/up kernel that follows normalises x (complete since the wait above)
     // before ITS dependency wait, which is safe only if it cannot start before x is final.
     pdl_launch_dependents();
@@ -264,11 +332,13 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
             a.partial[(static_cast<size_t>(kq) * a.M + m0 + m) * a.rows_pad + rg * kRowsPerGroup + rl] = mma_bf16_result(tiles, KS, rl, m);
         }
     }
+    tr.mark(2);
+    if (a.no_tail) { tr.mark(3); return; }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1) == static_cast<int>(gridDim.x) - 1);
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) { tr.mark(3); return; }
     __threadfence();
     // sum the K quarters in a fixed order into shared memory (the scratch of the GEMV phase is free now);
     // three logits per thread are in flight together, so M = 1 needs one round trip to L2
@@ -296,6 +366,7 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     __syncthreads();
     router_topk<true>(a, lg_s);
     if (threadIdx.x == 0) *a.ticket = 0;
+    tr.mark(3);
 }
 
 // Top-k stage of the wide router (multi-row steps): the logits arrive as K-split partial planes
@@ -342,16 +413,21 @@ __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ks
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
 // Expert gate/up: one CTA per 16 virtual rows (slot, i), the 8 warps split K = H.
 __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
-    constexpr int TERMS = 3, NB = 8, KS = 8;
+    constexpr int TERMS = 3, NB = 8, KS = 8, KQ = 4;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_ids[16];
+    __shared__ int s_ids_all[kMaxRows][16];
+    __shared__ float s_wts_all[kMaxRows][16];
+    TraceCta tr;
+    tr.begin(kTrMoeL1);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int I2 = 2 * a.I, vrows = a.S * I2;
     const int v0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
     float* tiles = smem;                                             // [KS][16][8]
     uint8_t* xq = reinterpret_cast<uint8_t*>(tiles + KS * 128);      // [TERMS][H]
+    float* lg_s = reinterpret_cast<float*>(xq + static_cast<size_t>(TERMS) * a.H);   // routed form: [M][E + 1]
     const bool shared_rows = v0 >= (a.S - 1) * I2;                   // the shared expert is known before routing
     if (threadIdx.x == 0) s_ids[a.S - 1] = a.shared_expert;
     __syncthreads();
@@ -360,16 +436,63 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
     if (shared_rows) mw.preload(src);
     RowNorm<4> norm;
     norm.preload_gamma(a.post_ln, a.H);
+    // idle until the router is done: warm L2 with the constant weights of a kernel further down the step
+    prefetch_l2_slice(a.pf, a.pf_bytes, blockIdx.x, gridDim.x);
     // x was finished two kernels back (out-projection + all-reduce); the router, this grid's direct predecessor,
     // releases its dependents only after its own dependency wait, so x is complete and in L2 by now: row 0 is
     // normalised and split while the router is still working, only the expert ids need the wait.
     norm.template run<TERMS, true>(xq, nullptr, a.x, 1, a.H, a.eps, red);
+    tr.mark(2);
     pdl_wait();
+    tr.mark(1);
+    if (a.partial != nullptr) {
+        // the router stopped at its K-quarter partials: add them in a fixed order (every load of a thread in flight
+        // together) and select the experts here, in every CTA alike; CTA 0 leaves ids / weights / logits for the rest
+        const int rows = a.E + 1, total = a.M * rows;
+        for (int idx0 = threadIdx.x; idx0 < total; idx0 += 3 * blockDim.x) {
+            float v[3][KQ];
+#pragma unroll
+            for (int u = 0; u < 3; ++u) {
+                const int idx = idx0 + u * blockDim.x, m = idx / rows, e = idx % rows;
+#pragma unroll
+                for (int q = 0; q < KQ; ++q)
+                    v[u][q] = idx < total ? __ldcg(a.partial + (static_cast<size_t>(q) * a.M + m) * a.rows_pad + e) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 3; ++u) {
+                const int idx = idx0 + u * blockDim.x;
+                if (idx < total) {
+                    const float t = ((v[u][0] + v[u][1]) + v[u][2]) + v[u][3];
+                    lg_s[idx] = t;
+                    if (blockIdx.x == 0 && a.logits_out != nullptr) a.logits_out[idx] = t;
+                }
+            }
+        }
+        __syncthreads();
+        for (int m = warp; m < a.M; m += KS) router_topk_warp(lg_s + static_cast<size_t>(m) * rows, a.E, a.topk, s_ids_all[m], s_wts_all[m]);
+        __syncthreads();
+        if (blockIdx.x == 0 && threadIdx.x < a.M * a.S) {
+            const int m = threadIdx.x / a.S, sl = threadIdx.x % a.S;
+            a.ids_out[threadIdx.x] = s_ids_all[m][sl];
+            a.wts_out[threadIdx.x] = s_wts_all[m][sl];
+        }
+    }
     for (int m = 0; m < a.M; ++m) {
         if (m) { __syncthreads(); mw.preloaded = false; }
-        if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
+        if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.partial != nullptr ? s_ids_all[m][threadIdx.x] : a.ids[m * a.S + threadIdx.x];
         if (m) norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m) * a.H, 1, a.H, a.eps, red);
         else __syncthreads();
+        if (m == 0 && !shared_rows) mw.preload(src);                 // own gate/up rows first ...
+        if (m == 0 && a.w2 != nullptr && a.M == 1) {
+            // ... then the down weights of the selected experts towards L2 for the kernel that follows: one line per
+            // thread of the S x H x I bytes
+            const size_t per_expert = static_cast<size_t>(a.H) * a.I >> 7, lines = per_expert * a.S;
+            const size_t per = (lines + gridDim.x - 1) / gridDim.x, lo = blockIdx.x * per, hi = lo + per < lines ? lo + per : lines;
+            for (size_t l = lo + threadIdx.x; l < hi; l += blockDim.x) {
+                const size_t sl = l / per_expert, off = l % per_expert;
+                prefetch_l2(a.w2 + (static_cast<size_t>(s_ids[sl]) * per_expert + off) * 128);
+            }
+        }
         float d[1][4];
         mw.template run<1>(src, xq, a.H, TERMS, d);
         mw.template store<1>(tiles + warp * 128, d);
@@ -377,6 +500,7 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
         if (threadIdx.x < kRowsPerGroup)
             a.gu[static_cast<size_t>(m) * vrows + v0 + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, kSplitDescale);
     }
+    tr.mark(3);
 }
 
 // Expert down + all-reduce + residual: one CTA per 16 output rows, warps split the virtual K = S x I.
@@ -386,6 +510,8 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
     __shared__ float red[32];
     __shared__ float descale[1];
     __shared__ int s_ids[16];
+    TraceCta tr;
+    tr.begin(kTrMoeL2);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int row0 = blockIdx.x * kRowsPerGroup;
@@ -397,6 +523,7 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
     uint8_t* xq = reinterpret_cast<uint8_t*>(res + kMaxRows * kRowsPerGroup);   // [TERMS][VK]
     const MmaExpertDown src{a.w2, a.w2_s, s_ids, a.H, a.I};
     pdl_wait();
+    tr.mark(1);
     for (int m = 0; m < a.M; ++m) {
         if (m) __syncthreads();
         if (threadIdx.x < a.S) s_ids[threadIdx.x] = a.ids[m * a.S + threadIdx.x];
@@ -422,7 +549,9 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
         if (threadIdx.x < kRowsPerGroup) res[m * kRowsPerGroup + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, descale[0]);
     }
     __syncthreads();
-    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x);
+    tr.mark(2);
+    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x, true, a.partial_out);
+    tr.mark(3);
 }
 
 }  // namespace nexrt
@@ -462,8 +591,10 @@ extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_p
 extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I,
                             int S, int M, float eps, int shared_expert, int n_cta, void* stream) {
     if (M < 1 || M > kMaxRows || H % 256 || I % 128 || S > 16) return cudaErrorInvalidValue;
-    MoeL1Args a{static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(post_ln), static_cast<const uint8_t*>(w13),
-                static_cast<const float*>(w13_s), static_cast<const int*>(ids), static_cast<float*>(gu), H, I, S, M, eps, shared_expert};
+    MoeL1Args a{};
+    a.x = static_cast<const __nv_bfloat16*>(x); a.post_ln = static_cast<const float*>(post_ln); a.w13 = static_cast<const uint8_t*>(w13);
+    a.w13_s = static_cast<const float*>(w13_s); a.ids = static_cast<const int*>(ids); a.gu = static_cast<float*>(gu);
+    a.H = H; a.I = I; a.S = S; a.M = M; a.eps = eps; a.shared_expert = shared_expert;
     const int vrows = S * 2 * I;
     if ((gemv_mode() & 4) && H % 512 == 0 && H <= 4096) {
         const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H;
@@ -471,6 +602,47 @@ extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13,
     }
     const size_t smem = sizeof(float) * (static_cast<size_t>(2) * H + gemv_part_floats((vrows + n_cta - 1) / n_cta, 1, gemv_geom(H / 16, gemv_threads())));
     return launch(moe_l1_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
+}
+
+// Routed pair of the one-row step: the router stops at its K-quarter partial logits (no ticket, no tail by one CTA) and
+// the gate/up kernel - every CTA alike - adds them, selects the experts on the warp-reduce unit and goes straight on to
+// its weight rows; its CTA 0 leaves ids / wts / logits in memory for the down projection.  While it waits for the
+// router it pulls [pf, pf + pf_bytes) towards L2 (constant weights of a later kernel), and once the ids are known the
+// selected experts' down weights (w2, may be null).
+extern "C" int nexrt_moe_router_partial(const void* x, const void* post_ln, const void* w, void* partial, int rows_pad, int H, int E, int topk, int M,
+                                        float eps, void* stream) {
+    if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || partial == nullptr || rows_pad < E + 1 || rows_pad % 16 ||
+        H % 1024 || H > 4096)
+        return cudaErrorInvalidValue;
+    RouterArgs a{};
+    a.x = static_cast<const __nv_bfloat16*>(x); a.post_ln = static_cast<const float*>(post_ln); a.w = static_cast<const __nv_bfloat16*>(w);
+    a.H = H; a.E = E; a.topk = topk; a.M = M; a.eps = eps; a.partial = static_cast<float*>(partial); a.rows_pad = rows_pad; a.no_tail = 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
+    const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 128) + sizeof(__nv_bfloat16) * static_cast<size_t>(mp) * 2 * H;
+    dim3 g(rows_pad / 16 * 4), b(256);
+    if (mp == 1) return launch(moe_router_mma_kernel<1>, g, b, smem_mma, st, a);
+    if (mp == 2) return launch(moe_router_mma_kernel<2>, g, b, smem_mma, st, a);
+    return launch(moe_router_mma_kernel<4>, g, b, smem_mma, st, a);
+}
+
+extern "C" int nexrt_moe_l1_routed(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* partial, int rows_pad, void* ids_out,
+                                   void* wts_out, void* logits_out, void* gu, const void* w2, const void* pf, unsigned long long pf_bytes, int H, int I,
+                                   int E, int topk, int M, float eps, void* stream) {
+    const int S = topk + 1;
+    if (M < 1 || M > kMaxRows || H % 512 || H > 4096 || I % 128 || S > 16 || E > 512 || topk < 1 || topk > E || partial == nullptr ||
+        rows_pad < E + 1 || ids_out == nullptr || wts_out == nullptr)
+        return cudaErrorInvalidValue;
+    MoeL1Args a{};
+    a.x = static_cast<const __nv_bfloat16*>(x); a.post_ln = static_cast<const float*>(post_ln); a.w13 = static_cast<const uint8_t*>(w13);
+    a.w13_s = static_cast<const float*>(w13_s); a.gu = static_cast<float*>(gu);
+    a.H = H; a.I = I; a.S = S; a.M = M; a.eps = eps; a.shared_expert = E;
+    a.partial = static_cast<const float*>(partial); a.rows_pad = rows_pad; a.E = E; a.topk = topk;
+    a.ids_out = static_cast<int*>(ids_out); a.wts_out = static_cast<float*>(wts_out); a.logits_out = static_cast<float*>(logits_out);
+    a.w2 = static_cast<const uint8_t*>(w2); a.pf = pf; a.pf_bytes = pf_bytes;
+    const int vrows = S * 2 * I;
+    const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H + sizeof(float) * static_cast<size_t>(M) * (E + 1);
+    return launch(moe_l1_mma_kernel, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
 }
 
 extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I,
@@ -481,6 +653,7 @@ extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const voi
     a.gu = static_cast<const float*>(gu); a.ids = static_cast<const int*>(ids); a.wts = static_cast<const float*>(wts);
     a.w2 = static_cast<const uint8_t*>(w2); a.w2_s = static_cast<const float*>(w2_s); a.x = static_cast<__nv_bfloat16*>(x);
     a.H = H; a.I = I; a.S = S; a.M = M; a.ch = *ch; a.site = site;
+    a.partial_out = partial_out_buffer();
     if ((gemv_mode() & 8) && H % 16 == 0) {
         const size_t VK = static_cast<size_t>(S) * I;
         const size_t smem_mma = sizeof(float) * (VK + 8 * 128 + kMaxRows * 16) + 3 * VK;

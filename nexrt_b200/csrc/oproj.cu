@@ -33,6 +33,7 @@ struct OProjArgs {
     int H, K, M, mode, hd;
     int overwrite;          // 1: x = reduced projection (no residual add)
     float eps;
+    float* partial_out;     // library-baseline arm: fp32 partial sums go here, no exchange, no residual
     LLChannel ch;
     unsigned int site;
     LLChannel cp;           // mode 2: partial inbox of the context-parallel group
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(512, 1) oproj_allreduce_kernel(OProjArgs a) {
         }
     }
     __syncthreads();
-    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x, a.overwrite == 0);
+    allreduce_residual(a.ch, a.site, res, a.M, row0, nrows, a.H, a.x, a.overwrite == 0, a.partial_out);
 }
 
 // Tensor-core form: one CTA per 16 output rows, the 8 warps split K (see mma_gemv.cuh); the CTA
@@ -127,6 +128,8 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ float descale[MP];
+    TraceCta tr;
+    tr.begin(kTrOproj);
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.K / kWin;
@@ -139,6 +142,7 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, warp < KS ? nwin : 0);
     mw.preload(src);
     pdl_wait();
+    tr.mark(1);
     LLCall cpcall{0u, 0u};
     if (a.mode == 2) cpcall = ll_begin(a.cp, a.cp_site);
     for (int m0 = 0; m0 < a.M; m0 += MP) {
@@ -199,7 +203,9 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
         }
     }
     __syncthreads();
-    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x, a.overwrite == 0);
+    tr.mark(2);
+    allreduce_residual(a.ch, a.site, res, a.M, row0, kRowsPerGroup, a.H, a.x, a.overwrite == 0, a.partial_out);
+    tr.mark(3);
 }
 
 // Staging half of the wide out-projection (multi-row steps): one CTA per token row builds the projection's input
@@ -286,6 +292,7 @@ extern "C" int nexrt_oproj_allreduce(const void* in, const void* z, const void* 
     a.in = static_cast<const float*>(in); a.z = static_cast<const float*>(z); a.gnorm_w = static_cast<const float*>(gnorm_w);
     a.w = static_cast<const uint8_t*>(w); a.s = static_cast<const float*>(s); a.x = static_cast<__nv_bfloat16*>(x);
     a.H = H; a.K = K; a.M = M; a.mode = mode; a.hd = hd; a.overwrite = overwrite; a.eps = eps; a.ch = *ch; a.site = site;
+    a.partial_out = partial_out_buffer();
     if (cp) { a.cp = *cp; a.cp_site = cp_site; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;

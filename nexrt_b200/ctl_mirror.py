@@ -34,6 +34,8 @@ class CtlMirror:
         self.host = np.frombuffer(buf, dtype=np.int32).reshape(2, words + 1)
         self.gen_dev = torch.zeros(1, dtype=torch.int32, device=device)
         self.gen = 0  # generations launched by the host
+        # bytes the device writes into host memory per step (control words + generation flag) == bytes a wait() reads back
+        self.bytes_per_read = int(self.host[0].nbytes)
 
     def next_gen(self) -> int:
         self.gen += 1

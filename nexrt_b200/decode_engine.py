@@ -51,6 +51,7 @@ class DecodeEngine:
         cache_len: Optional[int] = None,
         budget_ms: Optional[float] = None,
         shape_tp: Optional[int] = None,
+        collective: str = "fused",
     ):
         """``ext`` is the per-rank model dict in kernel layout (``weights.shard_model`` or
         ``weights.random_rank_model``); the reference uses the same argument to alias tensors that
@@ -66,7 +67,7 @@ class DecodeEngine:
         self.max_rows = max_rows
         self.cp = bool(cp) and self.spec.cp_size > 1
         self.ctx = StepContext(self.cfg, self.spec, self.dev, group=group, budget_ms=budget_ms, cp=self.cp,
-                               comm_world=world, comm_rank=rank)
+                               comm_world=world, comm_rank=rank, collective=collective)
         state_ring = max(2, max_rows + 1)
         conv_ring = 16
         self.mixers: List = []
@@ -78,6 +79,13 @@ class DecodeEngine:
             else:
                 self.mixers.append(FullAttn(self.ctx, mw, cache_len=cache_len, cp_w=lw.get("mixer_cp") if self.cp else None))
             self.moes.append(Moe(self.ctx, lw["moe"]))
+        # the expert gate/up kernel of layer l idles until its router is done: it warms L2 with the projection front of
+        # layer l + 1, whose CTAs find no free SM slot early enough to preload their weight rows themselves
+        # (same idea as the reference's wait-window prefetch wiring, nex_n2_5_pro/decode_engine.py:154-186)
+        if os.environ.get("NEXRT_PREFETCH_FRONT", "1") != "0":
+            for layer in range(len(self.mixers) - 1):
+                fw = ext["layers"][layer + 1]["mixer"]["front_w"]
+                self.moes[layer].prefetch = (fw.data_ptr(), fw.numel() * fw.element_size())
         self.head = Head(self.ctx, ext["head"])
         self.embed = ext["head"]["embed"]
         self.mirror = CtlMirror(self.dev, CTL_WORDS)

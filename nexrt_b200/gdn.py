@@ -91,10 +91,11 @@ class Gdn:
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.gdn_out), ptr(c.gdn_z), ptr(w["gnorm_w"]), ptr(w["out_w"]), ptr(w["out_s"]), ptr(c.x), cfg.hidden, spec.gdn_local,
-                M, 1, cfg.rms_eps, 128, c.channel.ref, c.next_site(), None, 0, n_cta, st,
+                M, 1, cfg.rms_eps, 128, c.ar_channel.ref, c.next_site(), None, 0, n_cta, st,
             ),
             "gdn_oproj_allreduce",
         )
+        c.after_allreduce(M)
 
     # ---- state hand-off (prefill states, tests) ------------------------------------------------
     def load_state(self, position: int, conv_tail: torch.Tensor, state: torch.Tensor) -> None:

@@ -34,8 +34,15 @@ class Moe:
         cfg, spec = ctx.cfg, ctx.spec
         self.tc_ok = cfg.hidden % 128 == 0 and cfg.hidden <= 4096 and spec.inter % 128 == 0
         # the fused router takes its tensor-core form (the one that can also write the planes) under these conditions
-        self.router_mma = (int(os.environ.get("NEXRT_GEMV_MODE", "63")) & 16) != 0 and cfg.hidden % 1024 == 0 and cfg.hidden <= 4096
+        self.router_mma = (int(os.environ.get("NEXRT_GEMV_MODE", "127")) & 16) != 0 and cfg.hidden % 1024 == 0 and cfg.hidden <= 4096
         self._planes_ready = False
+        # routed pair (router stops at partial logits, the gate/up kernel selects): NEXRT_MOE_ROUTED=0 goes back to the
+        # router with the one-CTA top-k tail
+        gm = int(os.environ.get("NEXRT_GEMV_MODE", "127"))
+        self.routed_ok = (os.environ.get("NEXRT_MOE_ROUTED", "1") != "0" and (gm & 4) != 0 and (gm & 16) != 0 and cfg.hidden % 1024 == 0
+                          and cfg.hidden <= 4096 and spec.inter % 128 == 0)
+        self.prefetch = None          # (address, bytes) of a later kernel's constant weights, set by the engine
+        self.prefetch_w2 = os.environ.get("NEXRT_PREFETCH_W2", "1") != "0"
 
     def forward(self, M: int = 1) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
@@ -56,9 +63,32 @@ class Moe:
             )
             check(lib.nexrt_moe_router_topk(ptr(c.router_partial), c.router_ksplit, self.rows_pad, ptr(c.moe_logits), ptr(c.moe_ids), ptr(c.moe_wts),
                                             cfg.n_experts, cfg.top_k, M, st), "moe_router_topk")
+        elif not tc_experts and self.routed_ok:
+            self._routed(M)
+            return
         else:
             self._router_fused(M, planes)
         self._experts(M)
+
+    def _routed(self, M: int) -> None:
+        """One-row form (and any step whose experts stay on the ``mma.sync`` kernels): the router stops at its partial
+        logits, the gate/up kernel selects the experts itself and warms L2 for the kernels behind it."""
+        c, w, lib = self.ctx, self.w, self.ctx.lib
+        cfg, spec, st = c.cfg, c.spec, c.stream()
+        check(lib.nexrt_moe_router_partial(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_partial), self.rows_pad, cfg.hidden,
+                                           cfg.n_experts, cfg.top_k, M, cfg.rms_eps, st), "moe_router_partial")
+        pf, pf_bytes = self.prefetch if (self.prefetch is not None and M == 1) else (None, 0)
+        check(lib.nexrt_moe_l1_routed(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_partial), self.rows_pad, ptr(c.moe_ids),
+                                      ptr(c.moe_wts), ptr(c.moe_logits), ptr(c.moe_gu), ptr(w["w2"]) if self.prefetch_w2 else None, pf, pf_bytes,
+                                      cfg.hidden, spec.inter, cfg.n_experts, cfg.top_k, M, cfg.rms_eps, st), "moe_l1_routed")
+        check(
+            lib.nexrt_moe_l2_allreduce(
+                ptr(c.moe_gu), ptr(c.moe_ids), ptr(c.moe_wts), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), cfg.hidden, spec.inter, cfg.top_k + 1, M,
+                c.ar_channel.ref, c.next_site(), c.n_cta, st,
+            ),
+            "moe_l2_allreduce",
+        )
+        c.after_allreduce(M)
 
     def _router_fused(self, M: int, planes=None) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib
@@ -104,7 +134,8 @@ class Moe:
         check(
             lib.nexrt_moe_l2_allreduce(
                 ptr(c.moe_gu), ptr(c.moe_ids), ptr(c.moe_wts), ptr(w["w2"]), ptr(w["w2_s"]), ptr(c.x), cfg.hidden, spec.inter, S, M,
-                c.channel.ref, c.next_site(), c.n_cta, st,
+                c.ar_channel.ref, c.next_site(), c.n_cta, st,
             ),
             "moe_l2_allreduce",
         )
+        c.after_allreduce(M)

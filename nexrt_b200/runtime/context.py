@@ -22,7 +22,7 @@ MAX_TOPK = 28
 
 class StepContext:
     def __init__(self, cfg: ModelConfig, spec: ShardSpec, device: torch.device, group=None, budget_ms=None, cp: bool = False,
-                 comm_world=None, comm_rank=None):
+                 comm_world=None, comm_rank=None, collective: str = "fused"):
         self.cfg, self.spec, self.device, self.group = cfg, spec, device, group
         self.lib = L.load()
         self.tp, self.rank = spec.tp, spec.rank
@@ -42,6 +42,18 @@ class StepContext:
         self.status = self.ctl[Ctl.STATUS : Ctl.STATUS + 1]
         kw = {} if budget_ms is None else {"budget_ms": budget_ms}
         self.channel = LLChannel(device, cw, cr, MAX_ROWS * H, group=group, seq=self.seq, status=self.status, **kw)
+        # Library-baseline arm (collective="nccl"): the projection kernels that normally end in the in-kernel all-reduce
+        # store their fp32 partial sums instead, and an NCCL all-reduce plus a residual-add kernel follow as separate
+        # graph nodes - the arm the fused epilogues are measured against.  One-row steps only.
+        self.collective = collective
+        self.ar_channel = self.channel
+        self.ar_partial = None
+        if collective == "nccl":
+            self.ar_channel = LLChannel(device, 1, 0, MAX_ROWS * H, group=None, seq=self.seq, status=self.status, **kw)
+            self.ar_partial = z(MAX_ROWS, H)
+            self.lib.nexrt_set_partial_out(self.ar_partial.data_ptr())
+        elif collective != "fused":
+            raise ValueError(f"unknown collective arm {collective!r}")
         self.cp_channel = None
         if cp and spec.cp_size > 1 and cw == spec.tp:
             slots = MAX_ROWS * spec.q_heads * (cfg.head_dim + 1)
@@ -101,6 +113,7 @@ class StepContext:
         self.sampling = z(8, dtype=torch.int64)
         self.site = 0
         self._rope = {}
+        self.early_ctl = os.environ.get("NEXRT_EARLY_CTL", "1") != "0"
 
     def rope_table(self, cache_len: int) -> torch.Tensor:
         """(cos, sin) of position * inv_freq for every cache position, built once per engine like the
@@ -123,3 +136,14 @@ class StepContext:
 
     def stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    def after_allreduce(self, M: int) -> None:
+        """Library-baseline arm: sum the partial rows the last projection kernel stored over the ranks with NCCL, then add
+        them to the residual rows (two more graph nodes per site).  Nothing to do in the fused arm."""
+        if self.collective != "nccl":
+            return
+        import torch.distributed as dist
+
+        if self.tp > 1 and dist.is_initialized():
+            dist.all_reduce(self.ar_partial[:M], group=self.group)
+        L.check(self.lib.nexrt_residual_add(self.x.data_ptr(), self.ar_partial.data_ptr(), M * self.cfg.hidden, self.stream()), "residual_add")

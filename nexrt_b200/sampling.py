@@ -9,11 +9,12 @@ live in device memory so a captured graph never needs recapture when a request c
 from __future__ import annotations
 
 import json
-import math
-import operator
 import os
-import struct
+from dataclasses import dataclass
 from pathlib import Path
+from typing import Any, List, Mapping, Optional, Tuple
+
+import numpy as np
 
 MAX_TOP_K = 28
 SAMPLING_WORDS = 8
@@ -21,57 +22,95 @@ DEFAULT_SAMPLING = (0.6, 0.95, 20)
 GREEDY = (0.0, 1.0, 1)
 
 
-def checked_sampling_config(temperature, top_p, top_k):
-    """Validate and return the values exactly as the device will see them (float32 rounded)."""
-    temperature, top_p = float(temperature), float(top_p)
-    if not math.isfinite(temperature) or temperature < 0:
-        raise ValueError("temperature must be finite and >= 0")
-    if not math.isfinite(top_p) or not 0 < top_p <= 1:
-        raise ValueError("top_p must be finite and in (0, 1]")
-    if isinstance(top_k, bool):
-        raise ValueError(f"top_k must be an integer in [1, {MAX_TOP_K}]")
+def _as_f32(name: str, value: Any) -> np.float32:
+    """``value`` rounded the way the device will hold it; anything float32 cannot represent is refused."""
     try:
-        top_k = operator.index(top_k)
-    except TypeError as error:
-        raise ValueError(f"top_k must be an integer in [1, {MAX_TOP_K}]") from error
-    if not 1 <= top_k <= MAX_TOP_K:
-        raise ValueError(f"top_k must be in [1, {MAX_TOP_K}]")
-    try:
-        t32, p32 = struct.unpack("<ff", struct.pack("<ff", temperature, top_p))
-    except (OverflowError, struct.error) as error:
-        raise ValueError("sampling parameters must fit float32") from error
-    if (temperature > 0 and t32 == 0) or p32 == 0:
-        raise ValueError("sampling parameters must not underflow float32")
-    return t32, p32, top_k
+        wide = float(value)
+    except (TypeError, ValueError) as error:
+        raise ValueError(f"{name} must be a real number") from error
+    if wide != wide or wide in (float("inf"), float("-inf")):
+        raise ValueError(f"{name} must be finite")
+    with np.errstate(over="ignore"):
+        narrow = np.float32(wide)
+    if not np.isfinite(narrow):
+        raise ValueError(f"{name} must fit float32")
+    if wide != 0.0 and narrow == 0.0:
+        raise ValueError(f"{name} must not underflow float32")
+    return narrow
 
 
-def resolve_sampling_config(defaults, temperature=None, top_p=None, top_k=None):
-    given = (temperature, top_p, top_k)
-    return checked_sampling_config(*(d if g is None else g for d, g in zip(defaults, given)))
+@dataclass(frozen=True)
+class SamplingConfig:
+    """One request's sampling parameters, already in device precision.  ``pack(seed)`` gives the eight 64-bit words
+    of the device buffer: word 0 the seed, word 1 the two float32 bit patterns (temperature low, top_p high), word 2
+    top_k, words 3..7 reserved as zero."""
+
+    temperature: float
+    top_p: float
+    top_k: int
+
+    @classmethod
+    def make(cls, temperature: Any, top_p: Any, top_k: Any) -> "SamplingConfig":
+        t = _as_f32("temperature", temperature)
+        if t < 0:
+            raise ValueError("temperature must be >= 0")
+        p = _as_f32("top_p", top_p)
+        if not (0 < p <= 1):
+            raise ValueError("top_p must lie in (0, 1]")
+        # an integer type only: True, 2.5 or "3" are not top-k values
+        if isinstance(top_k, (bool, np.bool_)) or not isinstance(top_k, (int, np.integer)):
+            raise ValueError(f"top_k must be an integer in [1, {MAX_TOP_K}]")
+        k = int(top_k)
+        if k < 1 or k > MAX_TOP_K:
+            raise ValueError(f"top_k must be an integer in [1, {MAX_TOP_K}]")
+        return cls(float(t), float(p), k)
+
+    def with_overrides(self, temperature: Any = None, top_p: Any = None, top_k: Any = None) -> "SamplingConfig":
+        return SamplingConfig.make(self.temperature if temperature is None else temperature, self.top_p if top_p is None else top_p,
+                                   self.top_k if top_k is None else top_k)
+
+    def as_tuple(self) -> Tuple[float, float, int]:
+        return (self.temperature, self.top_p, self.top_k)
+
+    def pack(self, seed: int) -> List[int]:
+        floats = np.array([self.temperature, self.top_p], dtype="<f4")
+        words = np.zeros(SAMPLING_WORDS, dtype=np.uint64)
+        words[0] = int(seed) % (1 << 64)
+        words[1] = int(floats.view("<u8")[0])
+        words[2] = self.top_k
+        return [int(w) for w in words.view(np.int64)]      # the buffer is a torch int64 tensor: two's-complement view
 
 
-def sampling_defaults():
-    model_dir = os.environ.get("NEXRT_MODEL_DIR") or os.environ.get("NEXRT_LAYERS_DIR")
-    config = {}
-    if model_dir:
-        path = Path(model_dir) / "generation_config.json"
-        if path.is_file():
-            config = json.loads(path.read_text())
-    temperature = config.get("temperature", DEFAULT_SAMPLING[0])
-    top_p = config.get("top_p", DEFAULT_SAMPLING[1])
-    top_k = config.get("top_k", DEFAULT_SAMPLING[2])
-    if config.get("do_sample") is False:
-        temperature, top_k = 0.0, 1
-    return checked_sampling_config(temperature, top_p, top_k)
+def checked_sampling_config(temperature, top_p, top_k) -> Tuple[float, float, int]:
+    """Validate and return ``(temperature, top_p, top_k)`` exactly as the device will see them (float32 rounded)."""
+    return SamplingConfig.make(temperature, top_p, top_k).as_tuple()
 
 
-def sampling_words(seed, temperature, top_p, top_k):
+def resolve_sampling_config(defaults, temperature=None, top_p=None, top_k=None) -> Tuple[float, float, int]:
+    """Request values over server defaults; ``None`` keeps the default."""
+    return SamplingConfig.make(*defaults).with_overrides(temperature, top_p, top_k).as_tuple()
+
+
+def _generation_config(directory: Optional[str]) -> Mapping[str, Any]:
+    if not directory:
+        return {}
+    path = Path(directory) / "generation_config.json"
+    return json.loads(path.read_text()) if path.is_file() else {}
+
+
+def sampling_defaults() -> Tuple[float, float, int]:
+    """Server defaults: ``DEFAULT_SAMPLING`` overridden by the checkpoint's ``generation_config.json`` (looked up under
+    ``NEXRT_MODEL_DIR``, else ``NEXRT_LAYERS_DIR``); ``do_sample: false`` means greedy."""
+    gen = _generation_config(os.environ.get("NEXRT_MODEL_DIR") or os.environ.get("NEXRT_LAYERS_DIR"))
+    if gen.get("do_sample") is False:
+        return SamplingConfig.make(GREEDY[0], gen.get("top_p", DEFAULT_SAMPLING[1]), GREEDY[2]).as_tuple()
+    picked = [gen.get(key, default) for key, default in zip(("temperature", "top_p", "top_k"), DEFAULT_SAMPLING)]
+    return SamplingConfig.make(*picked).as_tuple()
+
+
+def sampling_words(seed, temperature, top_p, top_k) -> List[int]:
     """Eight signed 64-bit words: seed, packed (temperature, top_p), top_k, zeros."""
-    temperature, top_p, top_k = checked_sampling_config(temperature, top_p, top_k)
-    seed = int(seed) & ((1 << 64) - 1)
-    signed_seed = seed if seed < (1 << 63) else seed - (1 << 64)
-    packed = struct.unpack("<q", struct.pack("<ff", temperature, top_p))[0]
-    return [signed_seed, packed, top_k] + [0] * (SAMPLING_WORDS - 3)
+    return SamplingConfig.make(temperature, top_p, top_k).pack(seed)
 
 
 # ---- CPU oracle of the device sampler (exact integer RNG, float32 arithmetic) ----------------

@@ -10,6 +10,7 @@ the launcher supervises lifetime.
 
 from __future__ import annotations
 
+import enum
 import json
 from typing import Callable, Optional
 
@@ -81,70 +82,112 @@ def reset_failed_request(reason: str, *, cache, runtime_state: dict, engine, spe
         raise FatalBackendError(f"failed to reset request state after {reason}: {error!r}") from error
 
 
-def execute_request_with_consensus(request: Callable[[], object], *, lifecycle_state: Callable[[], tuple],
-                                   gather_outcome: Callable[[tuple], list], reset_request: Callable[[str], None]):
-    """Run one request on this rank, then agree with the other ranks on what happened."""
-    local_error: Optional[BaseException] = None
-    result = None
+class LocalOutcome(enum.Enum):
+    """What one rank saw when it ran the request, before the ranks compare notes."""
+
+    DONE = "done"                  # returned a result
+    RECOVERABLE = "recoverable"    # raised RecoverableRequestError
+    FATAL_BACKEND = "fatal-backend"    # CUDA / NCCL / driver trouble: nothing can be agreed any more
+    FATAL_UNKNOWN = "fatal-unknown"    # any other exception: state unknown, a reset could not be trusted
+
+
+def _run_locally(request: Callable[[], object]):
+    """Run ``request`` and classify how it ended: ``(outcome, result, error)``.  ``FatalTPInvariantError`` and
+    ``FatalBackendError`` pass through untouched - they are verdicts already."""
     try:
-        result = request()
-    except FatalTPInvariantError:
+        return LocalOutcome.DONE, request(), None
+    except (FatalTPInvariantError, FatalBackendError):
         raise
     except RecoverableRequestError as error:
-        local_error = error
-    except Exception as error:  # noqa: BLE001
-        if isinstance(error, FatalBackendError):
-            raise
-        if is_fatal_backend_error(error):
-            raise FatalBackendError(f"fatal backend failure during request: {error!r}") from error
-        raise FatalTPInvariantError(f"unexpected request failure cannot be reset safely: {error!r}") from error
-    generation, phase, active_generation, kind = lifecycle_state()
-    rows = gather_outcome(failure_record(True if local_error is not None else None, generation, phase, active_generation, kind))
-    outcome, _ = resolve_request_outcome(rows)
-    if outcome == "reset":
-        resolve_failure(rows)
-        reason = str(local_error or "collective request reset")
-        reset_request(reason)
-        raise RequestResetError(reason)
-    if local_error is not None:
-        raise FatalTPInvariantError(f"this rank failed but the group reports success: {rows}")
-    return result
+        return LocalOutcome.RECOVERABLE, None, error
+    except Exception as error:  # noqa: BLE001 - classified below
+        return (LocalOutcome.FATAL_BACKEND if is_fatal_backend_error(error) else LocalOutcome.FATAL_UNKNOWN), None, error
+
+
+# what a fatal local outcome turns into (raised from the original error)
+_FATAL_VERDICTS = {
+    LocalOutcome.FATAL_BACKEND: (FatalBackendError, "fatal backend failure during request: {error!r}"),
+    LocalOutcome.FATAL_UNKNOWN: (FatalTPInvariantError, "unexpected request failure cannot be reset safely: {error!r}"),
+}
+
+
+def execute_request_with_consensus(request: Callable[[], object], *, lifecycle_state: Callable[[], tuple],
+                                   gather_outcome: Callable[[tuple], list], reset_request: Callable[[str], None]):
+    """Run one request on this rank, then agree with the other ranks on what happened.
+
+    Local verdicts that cannot be negotiated (backend failure, unknown exception) are raised at once.  Otherwise every
+    rank contributes one compact record (failed or not, plus its cache lifecycle point); the group outcome is either
+    "all fine" - the local result is returned, and a rank that failed alone is a broken invariant - or "reset", in which
+    case ``reset_request(reason)`` runs on every rank and ``RequestResetError`` reports it to the caller."""
+    outcome, result, error = _run_locally(request)
+    if outcome in _FATAL_VERDICTS:
+        verdict, template = _FATAL_VERDICTS[outcome]
+        raise verdict(template.format(error=error)) from error
+    failed_here = outcome is LocalOutcome.RECOVERABLE
+    records = gather_outcome(failure_record(True if failed_here else None, *lifecycle_state()))
+    group_outcome, _ = resolve_request_outcome(records)
+    if group_outcome != "reset":
+        if failed_here:
+            raise FatalTPInvariantError(f"this rank failed but the group reports success: {records}")
+        return result
+    resolve_failure(records)       # raises when the ranks do not agree on where they failed
+    reason = str(error) if failed_here else "collective request reset"
+    reset_request(reason)
+    raise RequestResetError(reason)
+
+
+class _Reply:
+    """Where rank 0 writes the answer of one socket request: the NDJSON event stream when the client asked for one,
+    else a single JSON line on the connection.  Other ranks get a reply object that writes nothing."""
+
+    def __init__(self, conn, event_stream, active: bool):
+        self.conn, self.stream, self.active = conn, event_stream, active
+
+    def _line(self, payload) -> None:
+        self.conn.sendall((json.dumps(payload, ensure_ascii=False) + "\n").encode())
+
+    def result(self, payload) -> None:
+        if self.active:
+            self.stream.finish(payload) if self.stream is not None else self._line(payload)
+
+    def error(self, text: str) -> None:
+        if self.active:
+            self.stream.fail(text) if self.stream is not None else self._line({"error": text})
+
+    def abandon(self) -> None:
+        if self.active and self.stream is not None:
+            self.stream.cancel()
+
+    def release(self) -> None:
+        if self.active and self.conn is not None:
+            if self.stream is not None:
+                self.stream.close()
+            self.conn.close()
 
 
 def dispatch_port_request(request: Callable[[], dict], *, tp_rank: int, conn, event_stream, report: list,
                           terminate_fatally: Callable, log_reset: Optional[Callable] = None):
-    """Answer one socket request without ever leaving the ranks in different states."""
-
-    def send_line(payload) -> None:
-        conn.sendall((json.dumps(payload, ensure_ascii=False) + "\n").encode())
-
+    """Answer one socket request without ever leaving the ranks in different states: a result is sent and recorded, an
+    agreed reset is answered with an error and serving goes on, anything else ends every rank through
+    ``terminate_fatally`` (which must not return).  Only rank 0 touches the socket; it is always released."""
+    reply = _Reply(conn, event_stream, active=tp_rank == 0)
     try:
-        result = request()
-        if tp_rank == 0:
-            report.append(result)
-            if event_stream is not None:
-                event_stream.finish(result)
-            else:
-                send_line(result)
-        return result
-    except RequestResetError as error:
-        if log_reset is not None:
-            log_reset(error)
-        if tp_rank == 0:
-            if event_stream is not None:
-                event_stream.fail(repr(error))
-            else:
-                send_line({"error": repr(error)})
-        return None
-    except BaseException as error:  # noqa: BLE001 - fatal invariant, backend failure or anything unexpected
-        if isinstance(error, (KeyboardInterrupt, SystemExit)):
+        try:
+            result = request()
+        except RequestResetError as reset:
+            if log_reset is not None:
+                log_reset(reset)
+            reply.error(repr(reset))
+            return None
+        except (KeyboardInterrupt, SystemExit):
             raise
-        if tp_rank == 0 and event_stream is not None:
-            event_stream.cancel()
-        terminate_fatally(error, None if event_stream is not None else conn)
-        raise AssertionError("terminate_fatally returned")
+        except BaseException as fatal:  # noqa: BLE001 - broken invariant, backend failure or a bug: all ranks must stop
+            reply.abandon()
+            terminate_fatally(fatal, None if event_stream is not None else conn)
+            raise AssertionError("terminate_fatally returned")
+        if reply.active:
+            report.append(result)
+        reply.result(result)
+        return result
     finally:
-        if tp_rank == 0 and conn is not None:
-            if event_stream is not None:
-                event_stream.close()
-            conn.close()
+        reply.release()

@@ -11,8 +11,10 @@ Wire format, one JSON object per line: ``{"type":"delta","text":…}`` ..., then
 
 from __future__ import annotations
 
+import collections
+import contextlib
+import enum
 import json
-import queue
 import socket
 import threading
 from typing import Iterable, List, Optional, Sequence
@@ -109,11 +111,20 @@ class IncrementalDetokenizer:
         return out
 
 
-_END = object()
+class WriterState(enum.Enum):
+    OPEN = "open"            # accepting output
+    SEALED = "sealed"        # the terminal event (done / error) is queued, or close() was asked for: nothing more is accepted
+    DROPPED = "dropped"      # the client is gone or too slow, or the request was cancelled: queued output is discarded
 
 
 class BridgeStreamWriter:
-    """Owns the client socket; drains a bounded queue of events on its own thread."""
+    """Owns the client socket of a streaming request.
+
+    Producers (the decode loop's token callback) append to a bounded deque under a condition variable and return at
+    once; one writer thread pops, detokenises and sends.  A backlog that reaches its limit means the client cannot keep
+    up: the stream is dropped, never the decode loop.  Exactly one terminal event (``done`` or ``error``) can be
+    queued; ``close()`` waits a bounded time for the thread and shuts the socket down under it if it is stuck in a send.
+    """
 
     DEFAULT_MAX_BACKLOG = 256
     DEFAULT_SHUTDOWN_TIMEOUT = 0.25
@@ -122,122 +133,134 @@ class BridgeStreamWriter:
     def __init__(self, conn, tokenizer, stop_ids=(), *, max_backlog=None, shutdown_timeout=None, write_timeout=None, max_tail_tokens=None):
         self.conn = conn
         self.detok = IncrementalDetokenizer(tokenizer, stop_ids, max_tail_tokens=max_tail_tokens)
-        backlog = self.DEFAULT_MAX_BACKLOG if max_backlog is None else int(max_backlog)
-        if backlog < 2:
-            raise ValueError("max_backlog must be >= 2")
-        self.shutdown_timeout = self.DEFAULT_SHUTDOWN_TIMEOUT if shutdown_timeout is None else float(shutdown_timeout)
-        wt = self.DEFAULT_WRITE_TIMEOUT if write_timeout is None else float(write_timeout)
-        if self.shutdown_timeout <= 0 or wt <= 0:
-            raise ValueError("writer timeouts must be > 0")
-        self.q: "queue.Queue" = queue.Queue(maxsize=backlog)
-        self.lock = threading.Lock()
-        self.disconnected = threading.Event()
-        self.stopped = threading.Event()
-        self.finished = False
+        self.max_backlog = int(self.DEFAULT_MAX_BACKLOG if max_backlog is None else max_backlog)
+        self.shutdown_timeout = float(self.DEFAULT_SHUTDOWN_TIMEOUT if shutdown_timeout is None else shutdown_timeout)
+        write_timeout = float(self.DEFAULT_WRITE_TIMEOUT if write_timeout is None else write_timeout)
+        if self.max_backlog < 2:
+            raise ValueError("the backlog needs room for at least one event and the terminal one")
+        if min(self.shutdown_timeout, write_timeout) <= 0:
+            raise ValueError("shutdown_timeout and write_timeout must be positive")
+        self._pending: "collections.deque" = collections.deque()
+        self._cv = threading.Condition()
+        self._state = WriterState.OPEN
+        self.stopped = threading.Event()          # set when the writer thread has left its loop
         self.error: Optional[BaseException] = None
-        try:
-            conn.settimeout(wt)
-        except (AttributeError, OSError):
-            pass
-        self.thread = threading.Thread(target=self._drain, name="bridge-stream-writer", daemon=True)
+        with contextlib.suppress(AttributeError, OSError):
+            conn.settimeout(write_timeout)
+        self.thread = threading.Thread(target=self._writer_loop, name="bridge-stream-writer", daemon=True)
         self.thread.start()
 
-    # ---- producer side (decode callback; never blocks) ---------------------------------------------
-    def _put(self, item, final: bool = False) -> bool:
-        with self.lock:
-            if self.finished or self.disconnected.is_set():
+    @property
+    def state(self) -> WriterState:
+        return self._state
+
+    @property
+    def disconnected(self) -> bool:
+        return self._state is WriterState.DROPPED
+
+    # ---- producer side: never blocks -------------------------------------------------------------------
+    def _offer(self, kind: str, payload, terminal: bool = False) -> bool:
+        with self._cv:
+            if self._state is not WriterState.OPEN:
                 return False
-            try:
-                self.q.put_nowait(item)
-            except queue.Full:
-                self.disconnected.set()
-                if final:
-                    self.finished = True
+            if len(self._pending) >= self.max_backlog:
+                self._state = WriterState.DROPPED
+                self._pending.clear()
+                self._cv.notify_all()
                 return False
-            if final:
-                self.finished = True
+            self._pending.append((kind, payload))
+            if terminal:
+                self._state = WriterState.SEALED
+            self._cv.notify_all()
             return True
 
     def event(self, payload: dict) -> bool:
-        return self._put(("event", dict(payload)))
+        return self._offer("raw", dict(payload))
 
     def tokens(self, token_ids: Iterable[int]) -> bool:
-        return self._put(("tokens", tuple(int(t) for t in token_ids)))
+        return self._offer("tokens", tuple(int(t) for t in token_ids))
 
     def finish(self, result: dict) -> bool:
-        return self._put(("finish", dict(result)), final=True)
+        return self._offer("done", dict(result), terminal=True)
 
     def fail(self, error) -> bool:
-        return self._put(("error", str(error)), final=True)
+        return self._offer("error", str(error), terminal=True)
 
     def cancel(self) -> None:
-        """Drop queued output and free a writer stuck in a send."""
-        with self.lock:
-            self.finished = True
-            self.disconnected.set()
-            try:
-                self.q.put_nowait(_END)
-            except queue.Full:
-                pass
-        self._shutdown()
+        """Discard queued output and free a writer thread that may be stuck in a send."""
+        with self._cv:
+            self._state = WriterState.DROPPED
+            self._pending.clear()
+            self._cv.notify_all()
+        self._shutdown_socket()
 
     def close(self) -> bool:
-        """Stop the writer within a fixed deadline; returns False if it had to be abandoned."""
-        with self.lock:
-            if not self.finished:
-                self.finished = True
-                try:
-                    self.q.put_nowait(_END)
-                except queue.Full:
-                    self.disconnected.set()
+        """Let the thread flush what is queued, within ``shutdown_timeout``; past that the socket is shut down under it.
+        Returns False if the thread had to be abandoned."""
+        with self._cv:
+            if self._state is WriterState.OPEN:
+                self._state = WriterState.SEALED
+            self._cv.notify_all()
         self.thread.join(self.shutdown_timeout)
         if self.thread.is_alive():
-            self.disconnected.set()
-            self._shutdown()
+            with self._cv:
+                self._state = WriterState.DROPPED
+                self._pending.clear()
+                self._cv.notify_all()
+            self._shutdown_socket()
             self.thread.join(self.shutdown_timeout)
         return not self.thread.is_alive()
 
-    # ---- consumer side -----------------------------------------------------------------------------
-    def _shutdown(self) -> None:
-        try:
+    # ---- writer thread ---------------------------------------------------------------------------------------
+    def _shutdown_socket(self) -> None:
+        with contextlib.suppress(AttributeError, OSError):
             self.conn.shutdown(socket.SHUT_RDWR)
-        except (AttributeError, OSError):
-            pass
 
-    def _send(self, payload: dict) -> None:
+    def _write(self, payload: dict) -> None:
         self.conn.sendall((json.dumps(payload, ensure_ascii=False) + "\n").encode())
 
-    def _drain(self) -> None:
+    def _next(self):
+        """The next queued item, or None when there is nothing left to do."""
+        with self._cv:
+            while not self._pending:
+                if self._state is not WriterState.OPEN:
+                    return None
+                self._cv.wait(self.shutdown_timeout)
+            if self._state is WriterState.DROPPED:
+                return None
+            return self._pending.popleft()
+
+    def _emit(self, kind: str, payload) -> bool:
+        """Send one item; True when it was the terminal one."""
+        if kind == "tokens":
+            text = self.detok.push(payload)
+            if text:
+                self._write({"type": "delta", "text": text})
+            return False
+        if kind == "raw":
+            self._write(payload)
+            return False
+        if kind == "done":
+            tail = self.detok.finish()
+            if tail:
+                self._write({"type": "delta", "text": tail})
+            body = {k: v for k, v in payload.items() if k != "generated_text"}   # the client has the text as deltas already
+            body["type"] = "done"
+            self._write(body)
+        else:
+            self._write({"type": "error", "error": payload})
+        return True
+
+    def _writer_loop(self) -> None:
         try:
-            while not self.disconnected.is_set():
-                try:
-                    item = self.q.get(timeout=self.shutdown_timeout)
-                except queue.Empty:
-                    if self.finished:
-                        break
-                    continue
-                if item is _END:
+            while True:
+                item = self._next()
+                if item is None or self._emit(*item):
                     break
-                kind, payload = item
-                if kind == "tokens":
-                    text = self.detok.push(payload)
-                    if text:
-                        self._send({"type": "delta", "text": text})
-                elif kind == "finish":
-                    text = self.detok.finish()
-                    if text:
-                        self._send({"type": "delta", "text": text})
-                    payload.pop("generated_text", None)
-                    payload["type"] = "done"
-                    self._send(payload)
-                    break
-                elif kind == "error":
-                    self._send({"type": "error", "error": payload})
-                    break
-                else:
-                    self._send(payload)
         except Exception as error:  # noqa: BLE001 - a broken client only ends this stream
             self.error = error
-            self.disconnected.set()
+            with self._cv:
+                self._state = WriterState.DROPPED
+                self._pending.clear()
         finally:
             self.stopped.set()
