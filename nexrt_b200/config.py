@@ -56,7 +56,7 @@ class ModelConfig:
     # caches
     max_context: int = 256 * 1024
     decode_headroom: int = 1024
-    # speculative-decoding state rings (position indexed; see runtime/rings.py)
+    # speculative-decoding state rings (position indexed; the no-alias law is checked by runtime/control.py: ring_no_alias)
     conv_ring: int = 16
     state_ring: int = 9
 
@@ -140,6 +140,34 @@ def shrunk_config() -> ModelConfig:
         moe_inter=256,
         shared_inter=256,
         max_context=4096,
+        decode_headroom=256,
+    )
+
+
+def rank_shard_config() -> ModelConfig:
+    """A two-layer model whose GLOBAL shapes are one rank's shard of the full geometry at tensor-parallel 8: hidden 4096,
+    4 query heads over 1 kv head of dim 256, 2 + 8 gated-delta-net heads, 512 experts top-10 of width 128, 31 040
+    vocabulary rows.  Run at tp = 1 it drives exactly the kernel instantiations of the 8-GPU deployment (head_dim-256
+    attention, 528-row router with top-10, K = 4096 fronts, the 31 040-row head) while staying small enough for the
+    fp32 oracle, which keeps the experts in FP8 and dequantises the handful a token selects."""
+    return ModelConfig(
+        name="nex-rank-shard",
+        hidden=4096,
+        vocab=31040,
+        n_layers=2,
+        layer_types=("linear", "full"),
+        n_q_heads=4,
+        n_kv_heads=1,
+        head_dim=256,
+        rotary_dim=64,
+        gdn_qk_heads=2,
+        gdn_v_heads=8,
+        gdn_dim=128,
+        n_experts=512,
+        top_k=10,
+        moe_inter=128,
+        shared_inter=128,
+        max_context=2048,
         decode_headroom=256,
     )
 

@@ -111,11 +111,12 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
     const int row0 = blockIdx.x * kRowsPerGroup, nwin = a.H / kWin;
     float* tiles = smem;                                              // [KS][16][8]
     uint8_t* xq = reinterpret_cast<uint8_t*>(tiles + KS * TILE);       // [MP*TERMS][H]
+    float* gpark = reinterpret_cast<float*>(xq + static_cast<size_t>(MP) * TERMS * a.H);   // [H] norm multiplier, parked until the norm
     const MmaPlain src{a.w, a.s, a.H};
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
     mw.preload(src);
     RowNorm<4> norm;
-    norm.preload_gamma(a.in_ln, a.H);
+    norm.preload_gamma_async(gpark, a.in_ln, a.H);
     pdl_wait();
     tr.mark(1);
     const int C0 = a.ctl[kCtlCommittedLen];
@@ -665,6 +666,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         }
     }
     __syncthreads();
+    tr.mark(4);
 
     // ---- this CTA's keys on the tensor cores, eight query rows
     {
@@ -676,6 +678,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
         __syncthreads();
     }
+    tr.mark(5);
     // ---- the 8 warps of the CTA into one partial in shared memory
     for (int idx = threadIdx.x; idx < nr * HD; idx += blockDim.x) {
         const int r = idx / HD, d = idx % HD;
@@ -695,6 +698,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
     }
     tr.mark(2);
     cluster.sync();
+    tr.mark(6);
     // ---- CTA c combines dims [c SL, (c + 1) SL) of every row over the cluster
     if (fr < nr) {
         float Av[CL], Mv[CL], Lv[CL], Mx = -INFINITY;
@@ -803,7 +807,7 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
     const int R = (nq + ngate + 2 * kvh) * hd;
     if ((gemv_mode() & 1) && H % 512 == 0 && H <= 4096) {
         const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
-        const size_t smem_mma = sizeof(float) * 8 * 256 + static_cast<size_t>(mp) * terms * H;
+        const size_t smem_mma = sizeof(float) * 8 * 256 + static_cast<size_t>(mp) * terms * H + sizeof(float) * H;
         dim3 g(R / 16), b(256);
         if (mp == 1) return launch(attn_front_mma_kernel<1>, g, b, smem_mma, st, a);
         if (mp == 2) return launch(attn_front_mma_kernel<2>, g, b, smem_mma, st, a);

@@ -13,8 +13,10 @@
 // one byte-permute per register.  The C fragment of S is already the B fragment of P^T.
 //
 // Q and P enter as bf16 hi + lo pairs (x = hi + lo to ~2^-17 relative), so the result matches an fp32
-// evaluation on the bf16-rounded K/V the cache holds; the reference's decode kernel is CUDA-core code
-// (kernels/full_attn/nex_n2_5_pro_attn_decode_ctypes.cu), this is its tensor-core replacement.
+// evaluation on the bf16-rounded K/V the cache holds.  The reference's decode kernel does the same products with Hopper's
+// wgmma m64n8k16 fed by TMA tiles (wgmma_fd4_mega, nex_n2_5_pro/kernels/full_attn/nex_n2_5_pro_attn_fd4_wgmma_ctypes.cu:120-401,
+// keys on the M side, the 4 q heads padded to N = 8); wgmma does not exist on sm_100a, and with at most 8 query rows per kv
+// head a warp-level mma.sync fed straight from the cache is the shape that fits.
 #pragma once
 
 #include "common.cuh"

@@ -115,6 +115,15 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return v;
 }
 
+// One constant fp32 (a block scale) through the read-only path, as a volatile asm so that the load is ISSUED where it is
+// written: a plain __ldg may be sunk by the compiler to its first use, which for a scale preloaded before the dependency
+// wait means a full L2 round trip inside every iteration of the tensor-core loop that consumes it.
+__device__ __forceinline__ float ld_const_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void prefetch_l2(const void* p) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
@@ -185,7 +194,7 @@ enum TraceKind : int {
     kTrMoeFused, kTrGdnFused, kTraceKinds = 16
 };
 constexpr int kTraceSlots = 20480;        // records per kind
-constexpr int kTraceWords = 5;            // cta | grid << 32, t0, t1, t2, t3
+constexpr int kTraceWords = 9;            // cta | grid << 32, t0, t1, t2, t3, then four kernel-specific extras t4..t7
 #ifdef NEXRT_TRACE
 static __constant__ unsigned long long* c_trace;   // [kTraceKinds cursors][kinds][slots][words]; one copy per translation unit
 struct TraceCta {

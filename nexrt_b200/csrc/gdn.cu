@@ -139,22 +139,33 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     // the first 2 * nv CTAs also project one bf16 b/a row each (CUDA cores, weights preloaded)
     const int ba_row = static_cast<int>(blockIdx.x) < 2 * a.nv ? static_cast<int>(blockIdx.x) : -1;
     const bool ba_cta = ba_row >= 0;
-    const GemvGeom gb = gemv_geom(a.H / 8, blockDim.x);
     float* xs = smem;                                                      // [MP][H]   (b/a CTAs only)
     float* tiles = xs + static_cast<size_t>(MP) * a.H;                     // [KS][TILE]
     float* part_ba = tiles + KS * TILE;                                    // [wpr][MP]
     uint8_t* xq = reinterpret_cast<uint8_t*>(part_ba + 64);                // [MP*TERMS][H]
+    float* gpark = reinterpret_cast<float*>(xq + static_cast<size_t>(MP) * TERMS * a.H);   // [H] norm multiplier, parked until the norm
+    __nv_bfloat16* bpark = reinterpret_cast<__nv_bfloat16*>(gpark + a.H);                  // [H] this CTA's b/a row (b/a CTAs only)
+    float4* cpark = reinterpret_cast<float4*>(bpark + a.H);                                // [16] conv taps of the CTA's rows
     const MmaPlain src{a.front_w, a.front_s, a.H};
     MmaWarp<NB, MmaPlain> mw(row0, warp, KS, nwin);
     mw.preload(src);
-    GemvCta<MP, 2, PlainBf16> gba(PlainBf16{a.ba_w, a.H}, ba_cta ? ba_row : 0, 1, a.H);
-    if (ba_cta) gba.preload();
+    // b/a row of this CTA and the conv taps of its 16 rows: asynchronous copies into shared memory (no registers held across
+    // the wait); thread t owns elements [16 t, 16 t + 16) of the bf16 row and reads back only what it copied itself
+    const bool ba_thread = ba_cta && static_cast<int>(threadIdx.x) * 16 < a.H;
+    if (ba_thread) {
+        const __nv_bfloat16* p = a.ba_w + static_cast<size_t>(ba_row) * a.H + threadIdx.x * 16;
+        const unsigned int dst = static_cast<unsigned int>(__cvta_generic_to_shared(bpark + threadIdx.x * 16));
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(p) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst + 16u), "l"(p + 8) : "memory");
+    }
+    const bool conv_thread = threadIdx.x < kRowsPerGroup && row0 + static_cast<int>(threadIdx.x) < a.C;
+    if (conv_thread) {
+        const unsigned int dst = static_cast<unsigned int>(__cvta_generic_to_shared(cpark + threadIdx.x));
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(a.conv_w + static_cast<size_t>(row0 + threadIdx.x) * 4) : "memory");
+    }
     NEXRT_EVENT(1);
     RowNorm<4> norm;
-    norm.preload_gamma(a.in_ln, a.H);
-    float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (threadIdx.x < kRowsPerGroup && row0 + static_cast<int>(threadIdx.x) < a.C)
-        cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row0 + threadIdx.x) * 4);
+    norm.preload_gamma_async(gpark, a.in_ln, a.H);
     NEXRT_EVENT(2);
     pdl_wait();
     tr.mark(1);
@@ -163,27 +174,51 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
         if (m0) { __syncthreads(); mw.preloaded = false; }
-        norm.template run<TERMS>(xq, ba_cta ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
+        norm.template run<TERMS>(xq, ba_cta ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red, &tr);
+        tr.mark(4);
         NEXRT_EVENT(4);
         float d[NT][4];
-        mw.template run<NT>(src, xq, a.H, mb * TERMS, d);
+        mw.template run<NT>(src, xq, a.H, mb * TERMS, d, &tr);
         mw.template store<NT>(tiles + warp * TILE, d);
         tr.mark(2);
         NEXRT_EVENT(5);
         if (ba_cta) {
-            if (m0 == 0) gba.run(xs, part_ba);
-            else gemv_cta<MP, 2>(PlainBf16{a.ba_w, a.H}, ba_row, 1, xs, a.H, part_ba);
+            // dot of the b/a row with the normalised fp32 rows (xs, written by the norm above): per-warp partials
+            float wf[16];
+            if (ba_thread) {
+                const uint4* bp = reinterpret_cast<const uint4*>(bpark + threadIdx.x * 16);
+                unpack8_bf16(bp[0], wf);
+                unpack8_bf16(bp[1], wf + 8);
+            }
+            for (int m = 0; m < mb; ++m) {
+                float acc = 0.f;
+                if (ba_thread) {
+                    const float* xr = xs + static_cast<size_t>(m) * a.H + threadIdx.x * 16;
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4) {
+                        const float4 xv = *reinterpret_cast<const float4*>(xr + e);
+                        acc = fmaf(wf[e], xv.x, fmaf(wf[e + 1], xv.y, fmaf(wf[e + 2], xv.z, fmaf(wf[e + 3], xv.w, acc))));
+                    }
+                }
+                acc = warp_sum(acc);
+                if ((threadIdx.x & 31) == 0) part_ba[m * 8 + warp] = acc;
+            }
         }
         __syncthreads();
+        tr.mark(5);
         NEXRT_EVENT(7);
         if (threadIdx.x < kRowsPerGroup) {
             float pre[MP];
 #pragma unroll
             for (int m = 0; m < MP; ++m) pre[m] = m < mb ? mma_result<TERMS, NT>(tiles, KS, threadIdx.x, m, kSplitDescale) : 0.f;
+            const float4 cw = conv_thread ? cpark[threadIdx.x] : make_float4(0.f, 0.f, 0.f, 0.f);
             gdn_front_row<MP>(a, row0 + threadIdx.x, pre, m0, mb, C0, cw);
         } else if (ba_cta && threadIdx.x >= 32 && threadIdx.x < 32 + mb) {
             const int m = threadIdx.x - 32;
-            gdn_ba_row(a, ba_row, gemv_result(part_ba, 0, m, MP, gb.wpr), m0 + m);
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += part_ba[m * 8 + w];      // fixed order over the 8 warps
+            gdn_ba_row(a, ba_row, v, m0 + m);
         }
         NEXRT_EVENT(6);
     }
@@ -300,7 +335,8 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if ((gemv_mode() & 1) && R % 16 == 0 && H % 512 == 0 && H <= 4096 && R / 16 >= 2 * nv) {
         const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
-        const size_t smem = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 256 + 64) + static_cast<size_t>(mp) * 3 * H;
+        const size_t smem = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 256 + 64) + static_cast<size_t>(mp) * 3 * H + sizeof(float) * H +
+                            sizeof(__nv_bfloat16) * H + 16 * sizeof(float4);
         dim3 g(R / 16), b(256);
         if (mp == 1) return launch(gdn_front_mma_kernel<1>, g, b, smem, st, a);
         if (mp == 2) return launch(gdn_front_mma_kernel<2>, g, b, smem, st, a);

@@ -151,9 +151,15 @@ __device__ __forceinline__ void norm_split_rows(uint8_t* xq, float* xs, const __
 // wait, the activation right after it, so the prologue costs one memory round trip instead of one
 // per loop iteration.  A thread owns up to NCH groups of 4 consecutive elements: K <= NCH * 4 *
 // blockDim.x.
+//
+// The norm multiplier can be parked in shared memory instead of registers (preload_gamma_async): an asynchronous
+// global-to-shared copy issued before the wait, read back by the thread that issued it.  The kernels that also hold a
+// whole K range of weight bytes in registers are at the 128-register limit, and a spilled weight register is reloaded
+// from local memory inside the tensor-core loop - an L2 round trip per K window when the line has left L1.
 template <int NCH>
 struct RowNorm {
     float4 gm[NCH];
+    const float* park = nullptr;
     __device__ __forceinline__ void preload_gamma(const float* __restrict__ gamma, int K) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
@@ -161,12 +167,27 @@ struct RowNorm {
             gm[c] = k < K ? *reinterpret_cast<const float4*>(gamma + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
+    // park_smem: K floats of shared memory, 16-byte aligned
+    __device__ __forceinline__ void preload_gamma_async(float* park_smem, const float* __restrict__ gamma, int K) {
+        park = park_smem;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+            const int k = (c * blockDim.x + threadIdx.x) * 4;
+            if (k < K) {
+                const unsigned int dst = static_cast<unsigned int>(__cvta_generic_to_shared(park_smem + k));
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gamma + k) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     // xq: e4m3 byte planes [(m * TERMS + term)][K] or null; xs: fp32 rows [m][K] or null.
     // L2_LOADS: read x with ld.global.cg (used when the rows are read before this grid's dependency wait and
     // must not be served from a cache line an earlier grid left on this SM).
     template <int TERMS, bool L2_LOADS = false>
-    __device__ __forceinline__ void run(uint8_t* xq, float* xs, const __nv_bfloat16* __restrict__ x, int rows, int K, float eps, float* red) {
+    __device__ __forceinline__ void run(uint8_t* xq, float* xs, const __nv_bfloat16* __restrict__ x, int rows, int K, float eps, float* red,
+                                        TraceCta* tr = nullptr) {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+        if (park != nullptr) asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's own copies: no barrier needed
         for (int m = 0; m < rows; ++m) {
             uint2 u[NCH];
 #pragma unroll
@@ -194,7 +215,8 @@ struct RowNorm {
             for (int c = 0; c < NCH; ++c) {
                 const int k = (c * blockDim.x + threadIdx.x) * 4;
                 if (k < K) {
-                    float r[4] = {v[c][0] * inv * gm[c].x, v[c][1] * inv * gm[c].y, v[c][2] * inv * gm[c].z, v[c][3] * inv * gm[c].w};
+                    const float4 g4 = park != nullptr ? *reinterpret_cast<const float4*>(park + k) : gm[c];
+                    float r[4] = {v[c][0] * inv * g4.x, v[c][1] * inv * g4.y, v[c][2] * inv * g4.z, v[c][3] * inv * g4.w};
                     if (xs) *reinterpret_cast<float4*>(xs + static_cast<size_t>(m) * K + k) = make_float4(r[0], r[1], r[2], r[3]);
                     if (xq) {
 #pragma unroll
@@ -232,7 +254,7 @@ __device__ __forceinline__ void split_rows(uint8_t* xq, const float* xs, int row
 struct MmaPlain {           // W [rows][K] fp8, S [rows/128][K/128]
     const uint8_t* w; const float* s; int K;
     __device__ __forceinline__ const uint8_t* ptr(int row, int win) const { return w + static_cast<size_t>(row) * K + win * kWin; }
-    __device__ __forceinline__ float scale(int row, int win) const { return __ldg(s + (row >> 7) * (K >> 7) + (win >> 1)); }
+    __device__ __forceinline__ float scale(int row, int win) const { return ld_const_f32(s + (row >> 7) * (K >> 7) + (win >> 1)); }
 };
 
 struct MmaExpertUp {        // virtual rows (slot, i) of the selected experts: W13 [E+1][2I][H]
@@ -243,7 +265,7 @@ struct MmaExpertUp {        // virtual rows (slot, i) of the selected experts: W
     }
     __device__ __forceinline__ float scale(int v, int win) const {
         const int e = ids[v / I2], i = v % I2;
-        return __ldg(s + (static_cast<size_t>(e) * (I2 >> 7) + (i >> 7)) * (H >> 7) + (win >> 1));
+        return ld_const_f32(s + (static_cast<size_t>(e) * (I2 >> 7) + (i >> 7)) * (H >> 7) + (win >> 1));
     }
 };
 
@@ -255,7 +277,7 @@ struct MmaExpertDown {      // virtual K = [slot][I]: W2 [E+1][H][I]
     }
     __device__ __forceinline__ float scale(int row, int win) const {
         const int wps = I / kWin, slot = win / wps, kw = win % wps;
-        return __ldg(s + (static_cast<size_t>(ids[slot]) * (H >> 7) + (row >> 7)) * (I >> 7) + (kw >> 1));
+        return ld_const_f32(s + (static_cast<size_t>(ids[slot]) * (H >> 7) + (row >> 7)) * (I >> 7) + (kw >> 1));
     }
 };
 
@@ -265,7 +287,7 @@ struct MmaExpertDown {      // virtual K = [slot][I]: W2 [E+1][H][I]
 template <int NB, typename Src>
 struct MmaWarp {
     uint4 ra[NB], rb[NB];
-    float slo[NB], shi[NB];
+    float sc[NB];           // one scale per window: rows g and g + 8 of a 16-row tile (row0 a multiple of 16) share their 128-row block
     int row0, w0, wstride, nwin, g, t;
     bool preloaded;
 
@@ -281,12 +303,11 @@ struct MmaWarp {
             if (win < nwin) {
                 ra[i] = ld_stream16(src.ptr(row0 + g, win) + t * 16);
                 rb[i] = ld_stream16(src.ptr(row0 + g + 8, win) + t * 16);
-                slo[i] = src.scale(row0 + g, win);
-                shi[i] = src.scale(row0 + g + 8, win);
+                sc[i] = src.scale(row0 + g, win);
             } else {
                 ra[i] = make_uint4(0u, 0u, 0u, 0u);
                 rb[i] = make_uint4(0u, 0u, 0u, 0u);
-                slo[i] = shi[i] = 0.f;
+                sc[i] = 0.f;
             }
         }
     }
@@ -295,7 +316,7 @@ struct MmaWarp {
 
     // xq: shared memory [ncols][Kx] byte planes; columns >= ncols are zero.  NT n-tiles of 8 columns.
     template <int NT>
-    __device__ __forceinline__ void run(const Src& src, const uint8_t* xq, int Kx, int ncols, float (&d)[NT][4]) {
+    __device__ __forceinline__ void run(const Src& src, const uint8_t* xq, int Kx, int ncols, float (&d)[NT][4], TraceCta* tr = nullptr) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
         for (int wbase = w0; wbase < nwin; wbase += NB * wstride) {
@@ -312,11 +333,13 @@ struct MmaWarp {
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
                     mma_e4m3_16x8x32(c, ra[i].x, rb[i].x, ra[i].y, rb[i].y, xb.x, xb.y);
                     mma_e4m3_16x8x32(c, ra[i].z, rb[i].z, ra[i].w, rb[i].w, xb.z, xb.w);
-                    d[nt][0] = fmaf(c[0], slo[i], d[nt][0]); d[nt][1] = fmaf(c[1], slo[i], d[nt][1]);
-                    d[nt][2] = fmaf(c[2], shi[i], d[nt][2]); d[nt][3] = fmaf(c[3], shi[i], d[nt][3]);
+                    d[nt][0] = fmaf(c[0], sc[i], d[nt][0]); d[nt][1] = fmaf(c[1], sc[i], d[nt][1]);
+                    d[nt][2] = fmaf(c[2], sc[i], d[nt][2]); d[nt][3] = fmaf(c[3], sc[i], d[nt][3]);
                 }
+                if (tr && i == 0 && wbase == w0) tr->mark(6);   // timeline: the first window's weights were there and are consumed
             }
         }
+        if (tr) tr->mark(7);                                    // timeline: every window consumed
     }
     // Write the accumulator tile to shared memory: tile[16 rows][8 * NT cols].
     template <int NT>

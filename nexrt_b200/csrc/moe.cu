@@ -23,6 +23,8 @@
 #include "mma_gemv.cuh"
 #include "ll.cuh"
 
+#include <atomic>
+
 namespace nexrt {
 
 // ---------------------------------------------------------------------------------------------
@@ -42,6 +44,8 @@ struct RouterArgs {
     int no_tail;              // 1: stop after the partial logits; the expert gate/up kernel sums them and selects (moe_l1_mma_kernel)
 };
 
+constexpr int kRouterPartialSplit = 2;   // K halves of the partial-logit router (layout [2][M][rows_pad])
+
 // Order-preserving image of an fp32 in u32 (never 0 for a finite value or an infinity), so that an integer max picks the
 // largest logit.
 __device__ __forceinline__ unsigned int router_key(float f) {
@@ -50,50 +54,106 @@ __device__ __forceinline__ unsigned int router_key(float f) {
 }
 __device__ __forceinline__ float router_unkey(unsigned int o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o); }
 
-// Top-k of one token row by one warp from logits in shared memory, on the warp-reduce unit: lane holds experts lane,
-// lane + 32, ... as integer keys and its running maximum; a round is one `redux.sync.max` for the value, one
-// `redux.sync.min` over the ids that hold it (ties go to the lowest expert id), and a 16-way rescan by the one lane
-// that owned the winner.  Same selection and the same softmax over the selected logits as router_topk above.
-// ids / wts: [topk + 1] (shared or global); the last entry is the shared expert E with sigmoid(gate logit).
-__device__ __forceinline__ void router_topk_warp(const float* lg, int E, int topk, int* ids, float* wts) {
+// Top-k of one token row by one warp from logits in shared memory.  Same selection (ties go to the lowest expert id) and the
+// same softmax over the selected logits as router_topk below, but built from rank counts over values in shared memory
+// instead of rounds of cross-lane reductions: on this GPU a `redux.sync` or a shuffle chain costs on the order of a
+// hundred cycles, and ten to thirty of them in a row made the selection the longest phase of the gate/up kernel.
+//   A  every lane finds the maximum of its 16 experts (a 4-level tree) and publishes it;
+//   B  every lane counts the published maxima above its own (ties ordered by lane): the lane with exactly topk - 1 above
+//      it holds T, a lower bound of the topk-th largest logit;
+//   C  the experts with logit >= T - a few more than topk - are compacted into shared memory with 16 ballots as 64-bit
+//      (key, ~id) words;
+//   D  every lane counts, for its one or two candidates, the candidates above them: that count is the final position,
+//      and ties resolve to the lowest id because ~id is part of the word;
+//   E  the softmax over the selected logits is summed in rank order.
+// More than 64 candidates (many equal logits) fall back to rounds over all 16 values per lane.
+// ids / wts: [topk + 1] (shared or global); the last entry is the shared expert E with sigmoid(gate logit).  topk <= 31.
+struct alignas(16) TopkScratch {      // 16-byte aligned and sized: gmax is read with 128-bit loads from every element of an array
+    unsigned long long cand[64];
+    unsigned int gmax[32];
+    float val[32];
+    unsigned int T;
+};
+
+__device__ __forceinline__ void router_topk_warp(const float* lg, int E, int topk, int* ids, float* wts, TopkScratch& sc) {
     const int lane = threadIdx.x & 31;
-    unsigned int key[16];
+    const unsigned int lt_mask = (1u << lane) - 1u;
+    unsigned int key[16];                       // 0 marks an empty entry
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const int e = lane + 32 * i;
         key[i] = e < E ? router_key(lg[e]) : 0u;
     }
-    unsigned int lm = 0u;
-    int li = 0;
+    unsigned int t8[8], t4[4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
-        if (key[i] > lm) { lm = key[i]; li = i; }
-    float top0 = 0.f, denom = 0.f, mine = 0.f;
-    int mine_id = -1;
-    for (int k = 0; k < topk; ++k) {
-        const unsigned int gm = redux_max_u32(lm);
-        const unsigned int gi = redux_min_u32(lm == gm ? static_cast<unsigned int>(lane + 32 * li) : 0xffffffffu);
-        const float bv = router_unkey(gm);
-        if (k == 0) top0 = bv;
-        const float ex = __expf(bv - top0);
-        denom += ex;
-        if (lane == k) { mine = ex; mine_id = static_cast<int>(gi); }
-        if ((gi & 31u) == static_cast<unsigned int>(lane)) {
-            lm = 0u; li = 0;
+    for (int i = 0; i < 8; ++i) t8[i] = max(key[2 * i], key[2 * i + 1]);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                if (i == static_cast<int>(gi >> 5)) key[i] = 0u;
-                if (key[i] > lm) { lm = key[i]; li = i; }
+    for (int i = 0; i < 4; ++i) t4[i] = max(t8[2 * i], t8[2 * i + 1]);
+    const unsigned int my = max(max(t4[0], t4[1]), max(t4[2], t4[3]));
+    sc.gmax[lane] = my;
+    __syncwarp();
+    {
+        int above = 0;
+        const uint4* g4 = reinterpret_cast<const uint4*>(sc.gmax);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint4 v = g4[j];
+            above += (v.x > my || (v.x == my && 4 * j < lane)) + (v.y > my || (v.y == my && 4 * j + 1 < lane)) +
+                     (v.z > my || (v.z == my && 4 * j + 2 < lane)) + (v.w > my || (v.w == my && 4 * j + 3 < lane));
+        }
+        if (above == topk - 1) sc.T = my;
+    }
+    __syncwarp();
+    const unsigned int T = sc.T;
+    int n = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const bool in = key[i] != 0u && key[i] >= T;
+        const unsigned int b = __ballot_sync(0xffffffffu, in);
+        const int pos = n + __popc(b & lt_mask);
+        if (in && pos < 64) sc.cand[pos] = (static_cast<unsigned long long>(key[i]) << 32) | static_cast<unsigned int>(~(lane + 32 * i));
+        n += __popc(b);
+    }
+    __syncwarp();
+    if (n <= 64) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c = lane + 32 * h;
+            if (c < n) {
+                const unsigned long long mine = sc.cand[c];
+                int above = 0;
+                for (int j = 0; j < n; ++j) above += sc.cand[j] > mine ? 1 : 0;
+                if (above < topk) {
+                    ids[above] = static_cast<int>(~static_cast<unsigned int>(mine));
+                    sc.val[above] = router_unkey(static_cast<unsigned int>(mine >> 32));
+                }
             }
         }
+    } else {
+        for (int k = 0; k < topk; ++k) {
+            unsigned int lm = 0u;
+            int li = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (key[i] > lm) { lm = key[i]; li = i; }
+            const unsigned int gm = redux_max_u32(lm);
+            const unsigned int gi = redux_min_u32(lm == gm ? static_cast<unsigned int>(lane + 32 * li) : 0xffffffffu);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) key[i] = gi == static_cast<unsigned int>(lane + 32 * i) ? 0u : key[i];
+            if (lane == 0) { ids[k] = static_cast<int>(gi); sc.val[k] = router_unkey(gm); }
+        }
     }
+    __syncwarp();
     if (lane < topk) {
-        ids[lane] = mine_id;
-        wts[lane] = mine / denom;
+        const float top0 = sc.val[0];
+        float denom = 0.f;
+        for (int j = 0; j < topk; ++j) denom += __expf(sc.val[j] - top0);
+        wts[lane] = __expf(sc.val[lane] - top0) / denom;
     } else if (lane == topk) {
         ids[lane] = E;
         wts[lane] = sigmoid_f(lg[E]);
     }
+    __syncwarp();
 }
 
 // Top-k of every token row by the calling CTA: warp m owns row m, lane holds logits lane,
@@ -291,9 +351,12 @@ __global__ void __launch_bounds__(512, 1) moe_l2_allreduce_kernel(MoeL2Args a) {
 // Router on the tensor cores: bf16 weights [rows_pad][H], one CTA per (16 rows, quarter of K), the
 // 8 warps split the quarter; the CTA that takes the last ticket adds the four quarters in a
 // fixed order and selects the experts.
-template <int MP>
+// KQ: CTAs that share the reduction dimension of one 16-row group (4: 132 CTAs of 4 windows per warp; 2: 66 CTAs of 8
+// windows per warp, the form of the routed one-row step, whose small grid leaves SM slots for the gate/up kernel that
+// follows to become resident - and preload - while this one runs).
+template <int MP, int KQ = 4>
 __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
-    constexpr int KQ = 4, NB = 4, KS = 8;
+    constexpr int NB = 16 / KQ, KS = 8;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_last;
@@ -374,10 +437,11 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
 // in a.logits for inspection, and selected exactly like the fused router does.
 __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ksplit, int rpc) {
     extern __shared__ __align__(16) float lg_s[];
+    __shared__ TopkScratch s_topk[8];
     pdl_launch_dependents();
     pdl_wait();
     const int rows = a.E + 1;
-    // one CTA per block of rpc token rows (a decode step is one block of up to kMaxRows; a prefill chunk has many small ones)
+    // one CTA per block of rpc token rows (one row per CTA in a decode step; a prefill chunk packs a few rows per CTA)
     const int m0 = blockIdx.x * rpc, mb = min(rpc, a.M - m0);
     // four consecutive experts per thread, every K-split plane of them requested before the first add (16-byte
     // loads, all in flight): the sum is one or two round trips to L2
@@ -402,23 +466,22 @@ __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ks
             }
     }
     __syncthreads();
-    RouterArgs b = a;
-    b.M = mb;
-    b.logits = a.logits + static_cast<size_t>(m0) * rows;
-    b.ids = a.ids + static_cast<size_t>(m0) * (a.topk + 1);
-    b.wts = a.wts + static_cast<size_t>(m0) * (a.topk + 1);
-    router_topk<true>(b, lg_s);
+    const int S = a.topk + 1;
+    for (int m = threadIdx.x >> 5; m < mb; m += blockDim.x >> 5)
+        router_topk_warp(lg_s + static_cast<size_t>(m) * rows, a.E, a.topk, a.ids + static_cast<size_t>(m0 + m) * S, a.wts + static_cast<size_t>(m0 + m) * S,
+                         s_topk[threadIdx.x >> 5]);
 }
 
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
 // Expert gate/up: one CTA per 16 virtual rows (slot, i), the 8 warps split K = H.
 __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
-    constexpr int TERMS = 3, NB = 8, KS = 8, KQ = 4;
+    constexpr int TERMS = 3, NB = 8, KS = 8, KQ = kRouterPartialSplit;
     extern __shared__ __align__(16) float smem[];
     __shared__ float red[32];
     __shared__ int s_ids[16];
     __shared__ int s_ids_all[kMaxRows][16];
     __shared__ float s_wts_all[kMaxRows][16];
+    __shared__ TopkScratch s_topk[KS];
     TraceCta tr;
     tr.begin(kTrMoeL1);
     pdl_launch_dependents();
@@ -438,6 +501,7 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
     norm.preload_gamma(a.post_ln, a.H);
     // idle until the router is done: warm L2 with the constant weights of a kernel further down the step
     prefetch_l2_slice(a.pf, a.pf_bytes, blockIdx.x, gridDim.x);
+    tr.mark(4);
     // x was finished two kernels back (out-projection + all-reduce); the router, this grid's direct predecessor,
     // releases its dependents only after its own dependency wait, so x is complete and in L2 by now: row 0 is
     // normalised and split while the router is still working, only the expert ids need the wait.
@@ -462,15 +526,19 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
             for (int u = 0; u < 3; ++u) {
                 const int idx = idx0 + u * blockDim.x;
                 if (idx < total) {
-                    const float t = ((v[u][0] + v[u][1]) + v[u][2]) + v[u][3];
+                    float t = v[u][0];
+#pragma unroll
+                    for (int q = 1; q < KQ; ++q) t += v[u][q];
                     lg_s[idx] = t;
                     if (blockIdx.x == 0 && a.logits_out != nullptr) a.logits_out[idx] = t;
                 }
             }
         }
         __syncthreads();
-        for (int m = warp; m < a.M; m += KS) router_topk_warp(lg_s + static_cast<size_t>(m) * rows, a.E, a.topk, s_ids_all[m], s_wts_all[m]);
+        tr.mark(5);
+        for (int m = warp; m < a.M; m += KS) router_topk_warp(lg_s + static_cast<size_t>(m) * rows, a.E, a.topk, s_ids_all[m], s_wts_all[m], s_topk[warp]);
         __syncthreads();
+        tr.mark(6);
         if (blockIdx.x == 0 && threadIdx.x < a.M * a.S) {
             const int m = threadIdx.x / a.S, sl = threadIdx.x % a.S;
             a.ids_out[threadIdx.x] = s_ids_all[m][sl];
@@ -497,6 +565,7 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
         mw.template run<1>(src, xq, a.H, TERMS, d);
         mw.template store<1>(tiles + warp * 128, d);
         __syncthreads();
+        tr.mark(7);
         if (threadIdx.x < kRowsPerGroup)
             a.gu[static_cast<size_t>(m) * vrows + v0 + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, kSplitDescale);
     }
@@ -541,9 +610,12 @@ __global__ void __launch_bounds__(256, 2) moe_l2_allreduce_mma_kernel(MoeL2Args 
                 make_float4(silu_f(gt.x) * up.x * wt, silu_f(gt.y) * up.y * wt, silu_f(gt.z) * up.z * wt, silu_f(gt.w) * up.w * wt);
         }
         __syncthreads();
+        tr.mark(4);
         act_split<TERMS>(xq, hs, 1, VK, red, descale);
+        tr.mark(5);
         float d[1][4];
         mw.template run<1>(src, xq, VK, TERMS, d);
+        tr.mark(6);
         if (warp < KS) mw.template store<1>(tiles + warp * 128, d);
         __syncthreads();
         if (threadIdx.x < kRowsPerGroup) res[m * kRowsPerGroup + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, descale[0]);
@@ -584,7 +656,7 @@ extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_p
     if (M < 1 || M > 1024 || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1 || ksplit > 16 || rows_pad % 4) return cudaErrorInvalidValue;
     RouterArgs a{nullptr, nullptr, nullptr, static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), nullptr, 0, E, topk, M, 0.f,
                  const_cast<float*>(static_cast<const float*>(partial)), rows_pad, nullptr};
-    const int rpc = M <= kMaxRows ? M : 2;
+    const int rpc = M <= kMaxRows ? M : 2;   // a decode step: one CTA, a warp per token row; prefill chunks: two rows per CTA
     return launch(moe_topk_rows_kernel, dim3((M + rpc - 1) / rpc), dim3(256), sizeof(float) * rpc * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit, rpc);
 }
 
@@ -604,26 +676,29 @@ extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13,
     return launch(moe_l1_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
 }
 
+extern "C" int nexrt_moe_router_partial_split(void) { return nexrt::kRouterPartialSplit; }
+
 // Routed pair of the one-row step: the router stops at its K-quarter partial logits (no ticket, no tail by one CTA) and
 // the gate/up kernel - every CTA alike - adds them, selects the experts on the warp-reduce unit and goes straight on to
 // its weight rows; its CTA 0 leaves ids / wts / logits in memory for the down projection.  While it waits for the
 // router it pulls [pf, pf + pf_bytes) towards L2 (constant weights of a later kernel), and once the ids are known the
 // selected experts' down weights (w2, may be null).
 extern "C" int nexrt_moe_router_partial(const void* x, const void* post_ln, const void* w, void* partial, int rows_pad, int H, int E, int topk, int M,
-                                        float eps, void* stream) {
+                                        float eps, void* planes, void* stream) {
     if (M < 1 || M > kMaxRows || E > 512 || topk < 1 || topk > 31 || topk > E || partial == nullptr || rows_pad < E + 1 || rows_pad % 16 ||
         H % 1024 || H > 4096)
         return cudaErrorInvalidValue;
     RouterArgs a{};
     a.x = static_cast<const __nv_bfloat16*>(x); a.post_ln = static_cast<const float*>(post_ln); a.w = static_cast<const __nv_bfloat16*>(w);
     a.H = H; a.E = E; a.topk = topk; a.M = M; a.eps = eps; a.partial = static_cast<float*>(partial); a.rows_pad = rows_pad; a.no_tail = 1;
+    a.planes = static_cast<uint8_t*>(planes);   // optional: the rows' e4m3 planes for the tcgen05 expert kernels (CTA m writes row m)
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4);
     const size_t smem_mma = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 128) + sizeof(__nv_bfloat16) * static_cast<size_t>(mp) * 2 * H;
-    dim3 g(rows_pad / 16 * 4), b(256);
-    if (mp == 1) return launch(moe_router_mma_kernel<1>, g, b, smem_mma, st, a);
-    if (mp == 2) return launch(moe_router_mma_kernel<2>, g, b, smem_mma, st, a);
-    return launch(moe_router_mma_kernel<4>, g, b, smem_mma, st, a);
+    dim3 g(rows_pad / 16 * kRouterPartialSplit), b(256);
+    if (mp == 1) return launch(moe_router_mma_kernel<1, kRouterPartialSplit>, g, b, smem_mma, st, a);
+    if (mp == 2) return launch(moe_router_mma_kernel<2, kRouterPartialSplit>, g, b, smem_mma, st, a);
+    return launch(moe_router_mma_kernel<4, kRouterPartialSplit>, g, b, smem_mma, st, a);
 }
 
 extern "C" int nexrt_moe_l1_routed(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* partial, int rows_pad, void* ids_out,
@@ -682,18 +757,17 @@ extern "C" int nexrt_moe_router_noalloc(const void* x, const void* post_ln, cons
         H % 1024 || H > 4096 || E > 512 || topk < 1 || topk > 31 || topk > E)
         return cudaErrorInvalidValue;
     // one address per device, looked up on the first call made with that device current
-    static float* scratch_of_device[64] = {nullptr};
+    static std::atomic<float*> scratch_of_device[64];   // zero-initialised; every writer of a slot stores the same address
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (scratch_of_device[dev] == nullptr) {
-        float* p = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_router_noalloc_scratch);
+    float* base = scratch_of_device[dev].load(std::memory_order_acquire);
+    if (base == nullptr) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_router_noalloc_scratch);
         if (e != cudaSuccess) return static_cast<int>(e);
-        scratch_of_device[dev] = p;
+        scratch_of_device[dev].store(base, std::memory_order_release);
     }
-    float* base = scratch_of_device[dev];
     float* partial = base;
     float* logits = base + kNoAllocPartial;
     int* ticket = reinterpret_cast<int*>(base + kNoAllocPartial + kNoAllocLogits);

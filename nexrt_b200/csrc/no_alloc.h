@@ -16,9 +16,10 @@
  *   - at most NEXRT_ROUTER_NOALLOC_MAX_ROWS token rows, router weights padded to at most
  *     NEXRT_ROUTER_NOALLOC_MAX_EXPERT_ROWS rows (a multiple of 16), H a multiple of 1024 and at most
  *     4096; anything larger is rejected with cudaErrorInvalidValue and nothing is launched;
- *   - the array (about 101 KB) is held by every GPU that loads the library until the process exits;
+ *   - the array (21 184 floats, 84.7 KB) is held by every GPU that loads the library until the process exits;
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make
- *     that first call outside of any stream capture;
+ *     that first call outside of any stream capture.  The per-device address cache is a table of atomics, so host
+ *     threads may make their first calls concurrently (they store the same value);
  *   - every call shares the one array and leaves its logits in it: the ticket word is cleared on
  *     the caller's stream before each launch, and two calls that overlap on the GPU (different
  *     streams, no dependency) race - serialise them;

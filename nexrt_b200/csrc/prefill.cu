@@ -198,6 +198,9 @@ __global__ void __launch_bounds__(256) planes_allreduce_residual_kernel(__nv_bfl
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
+        // release pattern of the publishing thread itself: the barrier ordered the other threads' (already fenced) data
+        // stores before this point, and this fence orders them, cumulatively, before the flag store that follows
+        __threadfence_system();
         if (ch.mc != nullptr) {
             mc_st_u32(reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ch.mc) + mine + flag_off), call.tag);
         } else {

@@ -94,12 +94,18 @@ __global__ void __launch_bounds__(32) step_end_kernel(int* ctl, unsigned int* se
 }
 
 // Empty node for the launch-floor fit: waits for its predecessor, optionally spins `body_ns` on %globaltimer, leaves.
-__global__ void null_kernel(unsigned long long body_ns, int early_release) {
+__global__ void null_kernel(unsigned long long body_ns, int early_release, unsigned long long* clock_out) {
     if (early_release) pdl_launch_dependents();
     pdl_wait();
+    const long long c0 = clock64();
+    const unsigned long long t0 = globaltimer_ns();
     if (body_ns) {
-        const unsigned long long t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < body_ns) {}
+    }
+    if (clock_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        // SM cycles against wall-clock nanoseconds over the spin: the SM clock this node actually ran at
+        clock_out[0] = static_cast<unsigned long long>(clock64() - c0);
+        clock_out[1] = globaltimer_ns() - t0;
     }
     if (!early_release) pdl_launch_dependents();
 }
@@ -168,9 +174,10 @@ extern "C" int nexrt_step_end(void* ctl, void* seq, unsigned int n_sites, void* 
 // step kernel: programmatic dependent launch when it is switched on).  The fit latency(K) = a + b K over K such nodes
 // separates the per-node cost of a captured graph from the work inside the nodes (the reference's `--scale` mode,
 // nex_n2_5_pro/decode_engine.py:549-630).
-extern "C" int nexrt_null_node(int grid, int block, int smem, unsigned long long body_ns, int early_release, void* stream) {
+extern "C" int nexrt_null_node(int grid, int block, int smem, unsigned long long body_ns, int early_release, void* clock_out, void* stream) {
     if (grid < 1 || block < 32 || block > 1024 || smem < 0 || smem > 200 * 1024) return cudaErrorInvalidValue;
-    return launch(null_kernel, dim3(grid), dim3(block), static_cast<size_t>(smem), static_cast<cudaStream_t>(stream), body_ns, early_release);
+    return launch(null_kernel, dim3(grid), dim3(block), static_cast<size_t>(smem), static_cast<cudaStream_t>(stream), body_ns, early_release,
+                  static_cast<unsigned long long*>(clock_out));
 }
 
 extern "C" int nexrt_residual_add(void* x, const void* y, int n, void* stream) {

@@ -18,7 +18,22 @@ constexpr int kStages = 4;           // 4 x (16 KB + token tile): two CTAs fit o
 constexpr int kAccBufs = 4;         // TMEM accumulator buffers of the FP8 variant (the MMA issuer runs this many K blocks ahead)
 constexpr int kThreads = 192;
 constexpr int kMaxKBlocks = 64;     // K <= 8192 (fp8) / 4096 (bf16)
-constexpr uint64_t kWaitBudgetNs = 200ull * 1000 * 1000;
+// Budget of every mbarrier / TMA / tensor-core completion wait.  It follows NEXRT_WAIT_BUDGET_MS like the waits of the
+// packet channel do (one knob bounds every device-side wait of the engine); unset, it is 200 ms.  The value sits in a
+// per-translation-unit constant that the launch wrappers install once (pipe_budget_install) before their first launch.
+static __constant__ uint64_t c_pipe_budget_ns = 200ull * 1000 * 1000;
+
+static inline cudaError_t pipe_budget_install() {
+    static bool done = false;
+    if (done) return cudaSuccess;
+    done = true;
+    const char* env = getenv("NEXRT_WAIT_BUDGET_MS");
+    if (env == nullptr || *env == 0) return cudaSuccess;
+    const double ms = atof(env);
+    if (!(ms > 0.0)) return cudaSuccess;
+    const uint64_t ns = static_cast<uint64_t>(ms * 1e6);
+    return cudaMemcpyToSymbol(c_pipe_budget_ns, &ns, sizeof(ns));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -51,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try(bar, parity)) return true;
         if ((it & 63u) == 63u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            if (globaltimer_ns() - t0 > c_pipe_budget_ns) {
                 *abort_flag = 1;
                 return false;
             }

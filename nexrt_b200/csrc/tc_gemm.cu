@@ -311,6 +311,7 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const Args& 
         if (e != cudaSuccess) return e;
         configured = true;
     }
+    if (const cudaError_t e = pipe_budget_install()) return e;
     dim3 grid((a.T + BN - 1) / BN, (a.R + kBM - 1) / kBM, (a.KB + a.kb_per - 1) / a.kb_per);
     return static_cast<cudaError_t>(launch(kern, grid, dim3(kThreads), L::total(a.kb_per, FP8), stream, mw, mx, a));
 }

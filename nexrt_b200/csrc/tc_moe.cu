@@ -312,6 +312,7 @@ int launch_tc_moe(const CUtensorMap& mw, const CUtensorMap& mx, const TcMoeArgs&
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
+    if (const cudaError_t e = pipe_budget_install()) return static_cast<int>(e);
     return launch(kern, grid, dim3(kThreads), static_cast<size_t>(smem_bytes(DOWN)), st, mw, mx, a);
 }
 

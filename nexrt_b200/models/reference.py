@@ -29,6 +29,24 @@ def _deq(ckpt, name):
     return dequantize_blockwise(ckpt[name + ".weight"], ckpt[_scale_key(ckpt.keys(), name + ".weight_scale_inv")])
 
 
+class _LazyDeq:
+    """Indexable list of dequantised expert matrices that dequantises an entry on first use: a step touches top_k + 1 of
+    several hundred experts, and the full fp32 set of the real geometry (hundreds of experts x 3 matrices) would not
+    fit the host."""
+
+    def __init__(self, ckpt, names):
+        self.ckpt, self.names, self.cache = ckpt, names, {}
+
+    def __len__(self):
+        return len(self.names)
+
+    def __getitem__(self, e: int) -> torch.Tensor:
+        w = self.cache.get(e)
+        if w is None:
+            w = self.cache[e] = _deq(self.ckpt, self.names[e])
+        return w
+
+
 def rms_norm(x: torch.Tensor, gamma_plus_one: torch.Tensor, eps: float) -> torch.Tensor:
     xf = x.float()
     return xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * gamma_plus_one
@@ -108,9 +126,9 @@ class RefModel:
             w["router"] = ckpt[m + "gate.weight"].float()
             w["sgate"] = ckpt[m + "shared_expert_gate.weight"].float().reshape(-1)
             names = [f"experts.{e}." for e in range(c.n_experts)] + ["shared_expert."]
-            w["w1"] = [_deq(ckpt, m + n + "gate_proj") for n in names]
-            w["w3"] = [_deq(ckpt, m + n + "up_proj") for n in names]
-            w["w2"] = [_deq(ckpt, m + n + "down_proj") for n in names]
+            w["w1"] = _LazyDeq(ckpt, [m + n + "gate_proj" for n in names])
+            w["w3"] = _LazyDeq(ckpt, [m + n + "up_proj" for n in names])
+            w["w2"] = _LazyDeq(ckpt, [m + n + "down_proj" for n in names])
             self.layers.append(w)
         self.reset()
 

@@ -66,6 +66,13 @@ class Moe:
         elif not tc_experts and self.routed_ok:
             self._routed(M)
             return
+        elif self.routed_ok and self.router_mma:
+            # a few rows with the experts on tcgen05: the router stops at its partial logits (no ticket, no one-CTA tail)
+            # and a one-CTA node adds them and selects - two short nodes instead of one long one
+            check(lib.nexrt_moe_router_partial(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_partial), self.rows_pad, cfg.hidden,
+                                               cfg.n_experts, cfg.top_k, M, cfg.rms_eps, planes, st), "moe_router_partial")
+            check(lib.nexrt_moe_router_topk(ptr(c.moe_partial), lib.nexrt_moe_router_partial_split(), self.rows_pad, ptr(c.moe_logits),
+                                            ptr(c.moe_ids), ptr(c.moe_wts), cfg.n_experts, cfg.top_k, M, st), "moe_router_topk")
         else:
             self._router_fused(M, planes)
         self._experts(M)
@@ -76,7 +83,10 @@ class Moe:
         c, w, lib = self.ctx, self.w, self.ctx.lib
         cfg, spec, st = c.cfg, c.spec, c.stream()
         check(lib.nexrt_moe_router_partial(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_partial), self.rows_pad, cfg.hidden,
-                                           cfg.n_experts, cfg.top_k, M, cfg.rms_eps, st), "moe_router_partial")
+                                           cfg.n_experts, cfg.top_k, M, cfg.rms_eps, None, st), "moe_router_partial")
+        if os.environ.get("NEXRT_DUP") == "router":     # timing experiment: the same kernel again, with warm instruction caches
+            check(lib.nexrt_moe_router_partial(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_partial), self.rows_pad, cfg.hidden,
+                                               cfg.n_experts, cfg.top_k, M, cfg.rms_eps, None, st), "moe_router_partial")
         pf, pf_bytes = self.prefetch if (self.prefetch is not None and M == 1) else (None, 0)
         check(lib.nexrt_moe_l1_routed(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_partial), self.rows_pad, ptr(c.moe_ids),
                                       ptr(c.moe_wts), ptr(c.moe_logits), ptr(c.moe_gu), ptr(w["w2"]) if self.prefetch_w2 else None, pf, pf_bytes,

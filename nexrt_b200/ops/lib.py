@@ -47,7 +47,7 @@ _PROTOTYPES = {
     "nexrt_set_attn_event_ring": [vp],
     "nexrt_set_gemv_mode": [ci],
     "nexrt_set_trace": [vp],
-    "nexrt_null_node": [ci, ci, ci, c_ulonglong, ci, vp],
+    "nexrt_null_node": [ci, ci, ci, c_ulonglong, ci, vp, vp],
     "nexrt_trace_layout": [POINTER(ci), POINTER(ci), POINTER(ci)],
     "nexrt_embed_gather": [vp, vp, vp, vp, ci, ci, ci, vp],
     "nexrt_step_end": [vp, vp, cu, vp, vp, ci, vp],
@@ -59,7 +59,7 @@ _PROTOTYPES = {
     "nexrt_oproj_allreduce": [vp] * 6 + [ci] * 4 + [cf, ci, CH, cu, CH, cu, ci, vp],
     "nexrt_moe_router": [vp] * 8 + [ci] * 5 + [cf, ci, vp, vp],
     "nexrt_moe_l1": [vp] * 6 + [ci] * 4 + [cf, ci, ci, vp],
-    "nexrt_moe_router_partial": [vp] * 4 + [ci] * 5 + [cf, vp],
+    "nexrt_moe_router_partial": [vp] * 4 + [ci] * 5 + [cf, vp, vp],
     "nexrt_moe_l1_routed": [vp] * 5 + [ci] + [vp] * 6 + [c_ulonglong] + [ci] * 5 + [cf, vp],
     "nexrt_set_partial_out": [vp],
     "nexrt_moe_l2_allreduce": [vp] * 6 + [ci] * 4 + [CH, cu, ci, vp],
@@ -126,6 +126,8 @@ def load(build: bool = True) -> ctypes.CDLL:
         fn.restype = ci
     lib.nexrt_attn_decode_smem.argtypes = [ci, ci, ci, ci]
     lib.nexrt_attn_decode_smem.restype = c_size_t
+    lib.nexrt_moe_router_partial_split.argtypes = []
+    lib.nexrt_moe_router_partial_split.restype = ci
     lib.nexrt_launch_count.argtypes = []
     lib.nexrt_launch_count.restype = c_ulonglong
     _install_optional(lib)

@@ -38,6 +38,7 @@ def main() -> int:
     if a.no_pdl:
         lib.nexrt_set_pdl(0)
     side = torch.cuda.Stream(device=dev)
+    clk = torch.zeros(2, dtype=torch.int64, device=dev)     # SM cycles and nanoseconds of the last spinning node
     counts = [int(v) for v in a.nodes.split(",")]
     for grid in (int(v) for v in a.grids.split(",")):
         for smem in (int(v) for v in a.smem.split(",")):
@@ -46,7 +47,7 @@ def main() -> int:
                 for k in counts:
                     def run():
                         for _ in range(k):
-                            err = lib.nexrt_null_node(grid, a.block, smem, body, 0 if a.late_release else 1, side.cuda_stream)
+                            err = lib.nexrt_null_node(grid, a.block, smem, body, 0 if a.late_release else 1, clk.data_ptr() if body else None, side.cuda_stream)
                             if err:
                                 raise RuntimeError(f"nexrt_null_node: cudaError {err}")
                     with torch.cuda.stream(side):
@@ -59,7 +60,9 @@ def main() -> int:
                 n = len(counts)
                 mx, my = sum(counts) / n, sum(times) / n
                 b = sum((x - mx) * (y - my) for x, y in zip(counts, times)) / sum((x - mx) ** 2 for x in counts)
+                cyc, ns = clk.tolist()
                 print(json.dumps({"grid": grid, "block": a.block, "smem": smem, "body_ns": body, "pdl": not a.no_pdl, "early_release": not a.late_release,
+                                  "sm_mhz_in_graph": round(cyc / ns * 1e3, 1) if (body and ns) else None,
                                   "us_per_node": round(b, 3), "intercept_us": round(my - b * mx, 2), "us_total": [round(t, 1) for t in times]}), flush=True)
     return 0
 

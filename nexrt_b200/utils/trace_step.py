@@ -52,11 +52,12 @@ def collect(buf: torch.Tensor, kinds: int, slots: int, words: int):
         for i in range(0, n - n % grid if n % grid else n, grid):
             g = r[i : i + grid]
             t0, t1, t2, t3 = g[:, 1], g[:, 2], g[:, 3], g[:, 4]
+            extras = [int(g[:, j][g[:, j] > 0].max()) if (g[:, j] > 0).any() else 0 for j in range(5, words)]
             t2v = t2[t2 > 0]
             launches.append({
                 "kind": k, "grid": grid, "entry": int(t0.min()), "entry_last": int(t0.max()),
                 "wait_first": int(t1[t1 > 0].min()) if (t1 > 0).any() else int(t0.min()), "wait_last": int(t1.max()),
-                "mid_last": int(t2v.max()) if t2v.numel() else 0, "exit_first": int(t3[t3 > 0].min()) if (t3 > 0).any() else 0, "exit": int(t3.max()),
+                "mid_last": int(t2v.max()) if t2v.numel() else 0, "exit_first": int(t3[t3 > 0].min()) if (t3 > 0).any() else 0, "exit": int(t3.max()), "extras": extras,
             })
     launches.sort(key=lambda d: d["exit"])
     return launches
@@ -126,7 +127,7 @@ def main() -> int:
     prev_exit = launches[0]["wait_first"]
     n_per_layer = 6
     print(f"timeline of one step: rows={a.rows} ctx={a.ctx} layers={cfg.n_layers} world={world} tp-shapes={tp} status={status}")
-    print(f"{'#':>4} {'kernel':12} {'grid':>5} {'entry':>8} {'wait0':>8} {'wait1':>8} {'mid':>8} {'exit0':>8} {'exit':>8} | {'cost':>6} {'hand':>6} {'body':>6} {'tail':>6}")
+    print(f"{'#':>4} {'kernel':12} {'grid':>5} {'entry':>8} {'entryN':>8} {'wait0':>8} {'wait1':>8} {'mid':>8} {'exit0':>8} {'exit':>8} | {'cost':>6} {'hand':>6} {'body':>6} {'tail':>6} | extras (last CTA at marks 4..7)")
     out_rows = []
     for i, l in enumerate(launches):
         rel = lambda t: (t - t_base) / 1e3 if t else float("nan")
@@ -141,8 +142,9 @@ def main() -> int:
                "mid_last": rel(l["mid_last"]), "exit_first": rel(l["exit_first"]), "exit": rel(l["exit"]), "cost": cost, "hand": hand, "body": body, "tail": tail}
         out_rows.append(row)
         if i < 1 + n_per_layer * a.show_layers or i >= len(launches) - 2:
-            print(f"{i:4d} {name:12} {l['grid']:5d} {row['entry']:8.2f} {row['wait_first']:8.2f} {row['wait_last']:8.2f} {row['mid_last']:8.2f} "
-                  f"{row['exit_first']:8.2f} {row['exit']:8.2f} | {cost:6.2f} {hand:6.2f} {body:6.2f} {tail:6.2f}")
+            ex = " ".join(f"{rel(t):8.2f}" for t in l["extras"] if t)
+            print(f"{i:4d} {name:12} {l['grid']:5d} {row['entry']:8.2f} {rel(l['entry_last']):8.2f} {row['wait_first']:8.2f} {row['wait_last']:8.2f} {row['mid_last']:8.2f} "
+                  f"{row['exit_first']:8.2f} {row['exit']:8.2f} | {cost:6.2f} {hand:6.2f} {body:6.2f} {tail:6.2f} | {ex}")
         prev_exit = l["exit"]
     total = (launches[-1]["exit"] - t_base) / 1e3
     print(f"step: {total:.1f} us from the first kernel's wait to the last exit, {len(launches)} launches")

@@ -86,11 +86,20 @@ def test_wide_prefill_fills_the_context_caches():
     out = generate_dflash(block, capture_request(block), max_new=10, stats={})
     assert eng.status_max() == 0 and len(out) >= 10
     plain_first = eng.prefill(prompt, chunk=8, wide=16)
+    state = eng.export_state()
     plain = eng.generate(max_new=10)
     assert plain_first == first
     same = 0
-    for a, b in zip(out, plain):       # a near tie between the 8-row and the 1-row arithmetic may end the common prefix early
+    for a, b in zip(out, plain):
         if a != b:
             break
         same += 1
-    assert same >= 3, (out, plain)
+    if same < len(plain):
+        # the 8-row and the 1-row arithmetic may part ways only at a near tie: replay the plain decode up to that step with
+        # the logits kept and look at the gap between the two candidates
+        eng.head.enable_logits()
+        eng.load_prefill(state)
+        for _ in range(same + 1):
+            eng.step(1)
+        gap = eng.logit_gap(out[same], plain[same])
+        assert gap is not None and gap < 0.05, (same, gap, out, plain)

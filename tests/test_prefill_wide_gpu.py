@@ -133,35 +133,66 @@ def test_glue_kernels_against_pytorch():
     assert int((hs != 0).sum()) == T * S
 
 
+def _oracle_state(ref):
+    """Per-layer state of a RefModel in the layout of DecodeEngine.export_state."""
+    out = {}
+    for idx, st in enumerate(ref.states):
+        if st.state is not None:
+            out[idx] = {"conv_state": st.conv, "recurrent_state": st.state}
+        else:
+            out[idx] = {"k_cache": torch.stack(st.k, 1), "v_cache": torch.stack(st.v, 1)}
+    return out
+
+
 @pytest.mark.parametrize("length,wide", [(53, 16), (150, 64)])
-def test_wide_prefill_leaves_the_state_of_the_row_steps(length, wide):
+def test_wide_prefill_matches_the_oracle_with_the_same_arithmetic(length, wide):
+    """The wide path rounds the input of every FP8 projection to one e4m3 plane; ``RefModel(fp8_activations=True)`` does the
+    same on the CPU.  Against THAT oracle the state the wide prefill leaves (GDN state and conv history, every K/V row) is
+    held to the tolerance of the step kernels, so a lost block of the chunk all-reduce, a wrong row of one attention
+    sub-step or a mis-masked expert cannot pass.  The prompt is the one whose oracle run stays furthest from routing
+    near ties (a tie broken the other way is a property of random weights, not of the kernels)."""
+    from nexrt_b200.models.reference import RefModel, robust_prompt
+
     cfg, ckpt = shrunk_checkpoint(0)
+    ref = RefModel(cfg, ckpt, fp8_activations=True)
+    prompt, margin = robust_prompt(ref, cfg.vocab, length, seeds=range(1, 9))
+    logits = ref.prefill(prompt)
+    want = _oracle_state(ref)
     eng = make_engine(cfg, ckpt, max_rows=8)
-    prompt = synthetic_prompt(cfg.vocab, length, seed=5)
-    first_ref = eng.prefill(prompt, chunk=8, wide=0)
-    ref = eng.export_state()
-    out_ref = eng.generate(max_new=6)
     first = eng.prefill(prompt, chunk=8, wide=wide)
     assert eng.status_max() == 0
     got = eng.export_state()
-    assert got["L"] == ref["L"] == length
-    # One e4m3 plane per activation (the 8-row steps use an exact three-term split) costs about 2 % per projection,
-    # and a routing near tie broken the other way changes single tokens by more; a wrong position, layout or
-    # weight would leave the states uncorrelated (relative error above 1).
-    for idx, st in ref["layers"].items():
-        for key, want in st.items():
-            if key == "kind":
-                continue
-            have = got["layers"][idx][key].float()
-            assert rel(have, want.float()) < 0.3, (idx, key)
-            if key in ("k_cache", "v_cache"):
-                per_pos = (have - want.float()).norm(dim=-1) / want.float().norm(dim=-1).clamp_min(1e-6)
-                assert float(per_pos.median()) < 0.12, (idx, key, float(per_pos.median()), float(per_pos.max()))
-    out = eng.generate(max_new=6)
-    assert eng.status_max() == 0 and len(out) == 6
-    # greedy tokens agree unless a near tie is broken the other way by the FP8 rounding of the activations
-    agree = sum(a == b for a, b in zip([first] + out, [first_ref] + out_ref))
-    assert agree >= 1, (first, out, first_ref, out_ref)
+    assert got["L"] == length
+    for idx, st in want.items():
+        for key, w in st.items():
+            have = got["layers"][idx][key].float().cpu()
+            # e4m3 rounds in steps of 2^-4: an activation that lands on the other side of a rounding boundary on the GPU
+            # (its norm differs from the oracle's in the last bits) moves by 6 %, which over a 1024-wide dot product leaves
+            # 2 - 3 % between the two evaluations of the same arithmetic; a lost or misplaced row is off by 100 %
+            assert rel(have, w.float()) < 4e-2, (idx, key, rel(have, w.float()), margin)
+            if key in ("k_cache", "v_cache"):      # every position on its own: one bad row must not hide in the norm of the rest
+                per_pos = (have - w.float()).norm(dim=-1) / w.float().norm(dim=-1).clamp_min(1e-6)
+                assert float(per_pos.max()) < 0.1, (idx, key, int(per_pos.argmax()), float(per_pos.max()))
+    top = int(logits.argmax())
+    assert first == top or float(logits.max() - logits[first]) < 0.05
     # a second prompt replays the captured chunk graph
     again = eng.prefill(prompt, chunk=8, wide=wide)
     assert again == first and eng.status_max() == 0
+
+
+@pytest.mark.parametrize("length,wide", [(53, 16)])
+def test_wide_prefill_stays_close_to_the_exact_row_steps(length, wide):
+    """Against the exact 8-row path the one-plane activations cost about 2 % per projection: the states stay correlated
+    (a wrong position, layout or weight would leave them uncorrelated, relative error above 1)."""
+    cfg, ckpt = shrunk_checkpoint(0)
+    eng = make_engine(cfg, ckpt, max_rows=8)
+    prompt = synthetic_prompt(cfg.vocab, length, seed=5)
+    eng.prefill(prompt, chunk=8, wide=0)
+    ref = eng.export_state()
+    eng.prefill(prompt, chunk=8, wide=wide)
+    assert eng.status_max() == 0
+    got = eng.export_state()
+    for idx, st in ref["layers"].items():
+        for key, want in st.items():
+            if key != "kind":
+                assert rel(got["layers"][idx][key].float(), want.float()) < 0.3, (idx, key)

@@ -26,7 +26,8 @@ def _router_inputs(M, H, E, seed):
     return x, ln, w, rows_pad
 
 
-@pytest.mark.parametrize("M,H,E,topk", [(1, 4096, 512, 10), (4, 1024, 16, 4)])
+# one row, the two-row and four-row instantiations, and eight rows of the full geometry: the array used up to its last float
+@pytest.mark.parametrize("M,H,E,topk", [(1, 4096, 512, 10), (4, 1024, 16, 4), (2, 1024, 16, 4), (8, 4096, 512, 10)])
 def test_noalloc_router_matches_regular_entry_point(M, H, E, topk):
     from nexrt_b200.ops import lib as L
 
