@@ -82,7 +82,9 @@ class DecodeEngine:
         # the expert gate/up kernel of layer l idles until its router is done: it warms L2 with the projection front of
         # layer l + 1, whose CTAs find no free SM slot early enough to preload their weight rows themselves
         # (same idea as the reference's wait-window prefetch wiring, nex_n2_5_pro/decode_engine.py:154-186)
-        if os.environ.get("NEXRT_PREFETCH_FRONT", "1") != "0":
+        # (measured on B200: no gain - the late CTAs are bound by how fast an SM can take 64 KB in, not by where the bytes
+        # come from - so the wiring is off unless NEXRT_PREFETCH_FRONT=1)
+        if os.environ.get("NEXRT_PREFETCH_FRONT", "0") == "1":
             for layer in range(len(self.mixers) - 1):
                 fw = ext["layers"][layer + 1]["mixer"]["front_w"]
                 self.moes[layer].prefetch = (fw.data_ptr(), fw.numel() * fw.element_size())

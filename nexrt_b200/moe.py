@@ -42,7 +42,7 @@ class Moe:
         self.routed_ok = (os.environ.get("NEXRT_MOE_ROUTED", "1") != "0" and (gm & 4) != 0 and (gm & 16) != 0 and cfg.hidden % 1024 == 0
                           and cfg.hidden <= 4096 and spec.inter % 128 == 0)
         self.prefetch = None          # (address, bytes) of a later kernel's constant weights, set by the engine
-        self.prefetch_w2 = os.environ.get("NEXRT_PREFETCH_W2", "1") != "0"
+        self.prefetch_w2 = os.environ.get("NEXRT_PREFETCH_W2", "0") == "1"      # measured: no gain on B200, off by default
 
     def forward(self, M: int = 1) -> None:
         c, w, lib = self.ctx, self.w, self.ctx.lib

@@ -55,6 +55,7 @@ def collect(buf: torch.Tensor, kinds: int, slots: int, words: int):
             extras = [int(g[:, j][g[:, j] > 0].max()) if (g[:, j] > 0).any() else 0 for j in range(5, words)]
             t2v = t2[t2 > 0]
             launches.append({
+                "raw": g.clone(),
                 "kind": k, "grid": grid, "entry": int(t0.min()), "entry_last": int(t0.max()),
                 "wait_first": int(t1[t1 > 0].min()) if (t1 > 0).any() else int(t0.min()), "wait_last": int(t1.max()),
                 "mid_last": int(t2v.max()) if t2v.numel() else 0, "exit_first": int(t3[t3 > 0].min()) if (t3 > 0).any() else 0, "exit": int(t3.max()), "extras": extras,
@@ -71,6 +72,7 @@ def main() -> int:
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--show-layers", type=int, default=4, help="print the launches of the first N layers in full")
     ap.add_argument("--json", default="")
+    ap.add_argument("--phases", default="", help="kernel name: print per-CTA durations between its stamps (mean / max over CTAs and launches)")
     a = ap.parse_args()
     if os.environ.get("NEXRT_TRACE_BUILD", "0") != "1":
         raise SystemExit("set NEXRT_TRACE_BUILD=1: the timeline lives in the trace variant of the library")
@@ -153,6 +155,26 @@ def main() -> int:
         n = len(d["cost"])
         mean = lambda k: sum(d[k]) / n
         print(f"{name:12} {n:4d} {mean('cost'):7.2f} {mean('hand'):7.2f} {mean('body'):7.2f} {mean('tail'):7.2f} {mean('lead'):7.2f}")
+    if a.phases:
+        # per-CTA time between consecutive stamps of one kernel kind: the launch table above shows the LAST CTA at each mark,
+        # which mixes different CTAs; this is what one CTA spends in each phase
+        k = KIND_NAMES.index(a.phases)
+        order = {"gdn_front": [1, 2, 5, 7, 3, 6, 4], "moe_l1": [1, 5, 2, 6, 7, 8, 4], "moe_l2_ar": [1, 2, 5, 6, 7, 3, 4]}.get(a.phases, [1, 2, 3, 4])
+        names = {1: "entry", 2: "wait", 3: "mid", 4: "exit", 5: "m4", 6: "m5", 7: "m6", 8: "m7"}
+        rows = torch.cat([l["raw"] for l in launches[1 + n_per_layer :] if l["kind"] == k])      # skip the first layer (cold)
+        print(f"per-CTA phase durations of {a.phases} ({rows.shape[0]} CTA records), us: mean / p50 / max")
+        prev = None
+        for col in order:
+            t = rows[:, col].double()
+            if prev is not None:
+                ok = (t > 0) & (rows[:, prev] > 0)
+                d = (t[ok] - rows[:, prev].double()[ok]) / 1e3
+                if d.numel():
+                    print(f"  {names[prev]:>6} -> {names[col]:<6} {d.mean():7.2f} {d.median():7.2f} {d.max():7.2f}")
+            if (t > 0).any():
+                prev = col
+    for l in launches:
+        l.pop("raw", None)
     if a.json:
         with open(a.json, "w") as f:
             json.dump({"rows": out_rows, "total_us": total, "world": world, "layers": cfg.n_layers, "ctx": a.ctx}, f)
