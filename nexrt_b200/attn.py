@@ -90,14 +90,17 @@ class FullAttn:
             "attn_decode",
         )
         n_cta = c.n_cta
+        # the cluster form of the decode kernel has merged the context-parallel partials already (and gated them): the
+        # out-projection then reads a plain input; the ticket form leaves the merge to the out-projection (mode 2)
+        merge_here = use_cp and not lib.nexrt_attn_decode_merges_cp(c.n_splits)
         if wide.oproj_is_wide(c, spec.attn_local, M):
-            wide.oproj_allreduce(c, c.attn_out, c.gate, None, self.w["out_w"], self.w["out_s"], spec.attn_local, M, 2 if use_cp else 0, cfg.head_dim,
-                                 c.cp_channel.ref if use_cp else None, cp_site)
+            wide.oproj_allreduce(c, c.attn_out, c.gate, None, self.w["out_w"], self.w["out_s"], spec.attn_local, M, 2 if merge_here else 0, cfg.head_dim,
+                                 c.cp_channel.ref if merge_here else None, cp_site)
             return
         check(
             lib.nexrt_oproj_allreduce(
                 ptr(c.attn_out), ptr(c.gate), None, ptr(self.w["out_w"]), ptr(self.w["out_s"]), ptr(c.x), cfg.hidden, spec.attn_local, M,
-                2 if use_cp else 0, cfg.rms_eps, cfg.head_dim, c.ar_channel.ref, c.next_site(), c.cp_channel.ref if use_cp else None, cp_site,
+                2 if merge_here else 0, cfg.rms_eps, cfg.head_dim, c.ar_channel.ref, c.next_site(), c.cp_channel.ref if merge_here else None, cp_site,
                 n_cta, st,
             ),
             "attn_oproj_allreduce",

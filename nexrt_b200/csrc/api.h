@@ -38,6 +38,12 @@ int nexrt_embed_gather(const void* embed, const void* ctl, void* x, void* status
 int nexrt_step_end(void* ctl, void* seq, unsigned int n_sites, void* mirror_host, void* mirror_gen, int words, void* stream);
 int nexrt_residual_add(void* x, const void* y, int n, void* stream);
 
+/* the all-reduce epilogue in isolation (partial [M][H] fp32 -> x [M][H] bf16, H / 16 CTAs; stamps: per-CTA ns or NULL), the
+ * sequence advance that closes a batch of such calls, and a two-rank packet ping-pong (out: elapsed ns, round trips done) */
+int nexrt_ll_allreduce_bench(const void* partial, void* x, int M, int H, const NexrtLLChannel* ch, unsigned int site, void* stamps, void* stream);
+int nexrt_ll_seq_advance(void* seq, unsigned int n, void* stream);
+int nexrt_ll_pingpong(const NexrtLLChannel* ch, int a, int b, unsigned int tag0, int iters, int use_mc, void* out, void* stream);
+
 /* gated delta net */
 int nexrt_gdn_front(const void* x, const void* in_ln, const void* front_w, const void* front_s, const void* ba_w, const void* conv_w,
                     const void* a_log, const void* dt_bias, const void* ctl, void* conv_ring, void* qkv, void* z, void* beta, void* g, int H,

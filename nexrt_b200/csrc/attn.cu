@@ -572,6 +572,13 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         win_lo = 0;
         win_hi = min(C0 + a.M, a.cache_len);
         if (a.window > 0) win_lo = max(0, win_hi - a.window);
+        if (a.cp_size > 1) {
+            // context parallel: the committed prefix is cut into cp_size equal windows, the last rank of the group also
+            // takes the rows of this step
+            const int share = C0 / a.cp_size;
+            win_lo = a.cp_rank * share;
+            win_hi = (a.cp_rank == a.cp_size - 1) ? min(C0 + a.M, a.cache_len) : (a.cp_rank + 1) * share;
+        }
         const int n_keys = win_hi - win_lo;
         n_act = max(1, min(static_cast<int>(gridDim.x) / CL, (n_keys + kKeysPerCluster / 2) / kKeysPerCluster));
         const int n_ctas = n_act * CL, idx = cidx * CL + crank;
@@ -606,10 +613,13 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
     if (cidx >= n_act) { tr.mark(3); return; }          // whole clusters leave: no barrier is left half attended
 
     const int r0 = static_cast<int>(blockIdx.z) * RP, nr = min(RP, rows - r0);
+    // one cluster and no context parallelism: the cluster's combine is the final result; otherwise the clusters' partials
+    // (and, context parallel, the other ranks') meet in the ticketed tail below
+    const bool direct = n_act == 1 && a.cp_size == 1;
     // the output gates of this CTA's slice are needed only at the very end: request them now
     float gate_v = 0.f;
     const int fr = static_cast<int>(threadIdx.x) / SL, fd = crank * SL + static_cast<int>(threadIdx.x) % SL;   // (row, dim) of the final combine
-    if (fr < nr && !(a.flags & 2))
+    if (fr < nr && !(a.flags & 2) && direct)
         gate_v = __ldcg(a.gate + (static_cast<size_t>((r0 + fr) / G) * a.ngate + kv * G + (r0 + fr) % G) * HD + fd);
 
     const float qscale = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;
@@ -720,7 +730,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
             L_ = fmaf(Lv[c], w, L_);
         }
         const int row = r0 + fr;
-        if (n_act == 1) {
+        if (direct) {
             float ctx = L_ > 0.f ? A_ / L_ : 0.f;
             if (!(a.flags & 2)) ctx *= sigmoid_f(gate_v);
             a.out[(static_cast<size_t>(row / G) * a.ngate + kv * G + row % G) * HD + fd] = ctx;
@@ -732,9 +742,9 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
             }
         }
     }
-    if (n_act > 1) __threadfence();
+    if (!direct) __threadfence();
     cluster.sync();                                      // nobody leaves while a peer may still read its shared memory
-    if (n_act == 1 || crank != 0) { tr.mark(3); return; }
+    if (direct || crank != 0) { tr.mark(3); return; }
 
     // ---- several clusters: the last one to arrive (per kv head, over all passes) merges their partials
     if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_act * static_cast<int>(gridDim.z) - 1);
@@ -744,10 +754,20 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
     const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
     const float* base_ml = a.ws_ml + static_cast<size_t>(kv) * a.n_splits * rows * 2;
     constexpr int MAXC = 20;                             // clusters per kv head: n_splits (<= 160) / 8
+    LLCall cpcall{0u, 0u};
+    if (a.cp_size > 1) cpcall = ll_begin(a.ch, a.site);
+    // Context parallel: two passes over the items - first everything that belongs to another rank is sent, then this
+    // rank's own heads are merged - so that no rank sits in a wait while it still owes a peer its packets.
+    for (int pass = 0; pass < (a.cp_size > 1 ? 2 : 1); ++pass)
     for (int q4 = threadIdx.x; q4 < rows * HD / 4; q4 += blockDim.x) {
         const int idx = q4 * 4, r = idx / HD, d = idx % HD;
+        const int m = r / G, hg = r % G;                 // token row, head inside the kv group
+        // context parallel: head hg of the group belongs to cp rank hg / ngate; only the owner needs the gate
+        const int owner = a.cp_size > 1 ? hg / a.ngate : 0, lh = a.cp_size > 1 ? hg % a.ngate : kv * G + hg;
+        const bool mine = a.cp_size == 1 || owner == a.cp_rank;
+        if (a.cp_size > 1 && mine != (pass == 1)) continue;
         float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!(a.flags & 2)) gt = __ldcg(reinterpret_cast<const float4*>(a.gate + (static_cast<size_t>(r / G) * a.ngate + kv * G + r % G) * HD + d));
+        if (!(a.flags & 2) && mine) gt = __ldcg(reinterpret_cast<const float4*>(a.gate + (static_cast<size_t>(m) * a.ngate + lh) * HD + d));
         float2 ml[MAXC];
         float4 v[MAXC];
 #pragma unroll
@@ -772,10 +792,55 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         }
         const float invl = L_ > 0.f ? 1.f / L_ : 0.f;
         float4 ctx = make_float4(A_.x * invl, A_.y * invl, A_.z * invl, A_.w * invl);
+        if (a.cp_size > 1) {
+            // This rank's partial of (row m, head hg): locally normalised context and log2-domain LSE.  Partials of other
+            // ranks' heads go to their owner as packets (every thread of the CTA sends its own four values); for this
+            // rank's own heads the same thread then waits for the other ranks' packets and merges the cp_size partials
+            // in rank order - once, here, instead of in every CTA of the out-projection that follows.
+            const float lse = L_ > 0.f ? Mx + log2f(L_) : -INFINITY;
+            const unsigned int slot = (static_cast<unsigned int>(m) * a.ngate + lh) * (HD + 1) + d;
+            if (!mine) {
+                ll_send(a.ch, cpcall, owner, slot, __float_as_uint(ctx.x));
+                ll_send(a.ch, cpcall, owner, slot + 1, __float_as_uint(ctx.y));
+                ll_send(a.ch, cpcall, owner, slot + 2, __float_as_uint(ctx.z));
+                ll_send(a.ch, cpcall, owner, slot + 3, __float_as_uint(ctx.w));
+                if (d == 0) ll_send(a.ch, cpcall, owner, (static_cast<unsigned int>(m) * a.ngate + lh) * (HD + 1) + HD, __float_as_uint(lse));
+                continue;
+            }
+            float lses[kMaxWorld];
+            float4 parts[kMaxWorld];
+            float mx = -INFINITY;
+            for (int sr = 0; sr < a.cp_size; ++sr) {
+                if (sr == a.cp_rank) {
+                    lses[sr] = lse;
+                    parts[sr] = ctx;
+                } else {
+                    unsigned int pl, p0, p1, p2, p3;
+                    ll_wait(a.ch, cpcall, sr, (static_cast<unsigned int>(m) * a.ngate + lh) * (HD + 1) + HD, &pl, kStatusCpTimeout);
+                    ll_wait(a.ch, cpcall, sr, slot, &p0, kStatusCpTimeout);
+                    ll_wait(a.ch, cpcall, sr, slot + 1, &p1, kStatusCpTimeout);
+                    ll_wait(a.ch, cpcall, sr, slot + 2, &p2, kStatusCpTimeout);
+                    ll_wait(a.ch, cpcall, sr, slot + 3, &p3, kStatusCpTimeout);
+                    lses[sr] = __uint_as_float(pl);
+                    parts[sr] = make_float4(__uint_as_float(p0), __uint_as_float(p1), __uint_as_float(p2), __uint_as_float(p3));
+                }
+                mx = fmaxf(mx, lses[sr]);
+            }
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.f;
+            for (int sr = 0; sr < a.cp_size; ++sr) {
+                const float wgt = lses[sr] == -INFINITY ? 0.f : exp2f(lses[sr] - mx);
+                num.x = fmaf(wgt, parts[sr].x, num.x); num.y = fmaf(wgt, parts[sr].y, num.y);
+                num.z = fmaf(wgt, parts[sr].z, num.z); num.w = fmaf(wgt, parts[sr].w, num.w);
+                den += wgt;
+            }
+            const float invd = den > 0.f ? 1.f / den : 0.f;
+            ctx = make_float4(num.x * invd, num.y * invd, num.z * invd, num.w * invd);
+        }
         if (!(a.flags & 2)) {
             ctx.x *= sigmoid_f(gt.x); ctx.y *= sigmoid_f(gt.y); ctx.z *= sigmoid_f(gt.z); ctx.w *= sigmoid_f(gt.w);
         }
-        *reinterpret_cast<float4*>(a.out + (static_cast<size_t>(r / G) * a.ngate + kv * G + r % G) * HD + d) = ctx;
+        *reinterpret_cast<float4*>(a.out + (static_cast<size_t>(m) * a.ngate + lh) * HD + d) = ctx;
     }
     __syncthreads();
     if (threadIdx.x == 0) a.ticket[kv] = 0;
@@ -826,6 +891,13 @@ extern "C" int nexrt_set_attn_event_ring(void* ring) {
     return 0;
 }
 
+// 1 when nexrt_attn_decode with these settings runs the cluster kernel, which in context-parallel mode also merges the
+// group's partials (its `out` is then the final gated context and the out-projection takes it as a plain input); 0 when
+// the ticket kernel runs, which only sends the partials and leaves the merge to the out-projection (mode 2).
+extern "C" int nexrt_attn_decode_merges_cp(int n_splits) {
+    return ((gemv_mode() & 32) != 0 && (gemv_mode() & 64) != 0 && n_splits >= kClusterCtas) ? 1 : 0;
+}
+
 extern "C" size_t nexrt_attn_decode_smem(int hd, int nq, int kvh, int M) {
     const size_t rows = static_cast<size_t>(M) * (nq / kvh);
     const size_t main_floats = rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPassMma * (hd + 2) + static_cast<size_t>(hd / 16) * 32 * 4;
@@ -856,7 +928,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     const size_t smem = nexrt_attn_decode_smem(hd, nq, kvh, M);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) != 0;
-    if (mma && (gemv_mode() & 64) && cp_size == 1 && n_splits >= kClusterCtas) {
+    if (mma && (gemv_mode() & 64) && n_splits >= kClusterCtas) {
         // cluster form: whole clusters of 8 CTAs along x; its shared memory adds this CTA's partial for the DSMEM combine
         const int n_clusters = n_splits / kClusterCtas, passes_c = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;
         const size_t rows = static_cast<size_t>(M) * (nq / kvh);

@@ -381,10 +381,14 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
         const int mb = min(MP, a.M - m0);
         if (m0) { __syncthreads(); mw.preloaded = false; }
         norm.template run<3>(nullptr, xs, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
-        // the expert kernels of a multi-row step take the same normalised rows as three e4m3 planes: CTA m0 + m
-        // writes row m0 + m's, which saves them a kernel of their own
-        if (a.planes != nullptr && static_cast<int>(blockIdx.x) >= m0 && static_cast<int>(blockIdx.x) < m0 + mb)
-            split_rows<3>(a.planes + static_cast<size_t>(blockIdx.x) * 3 * a.H, xs + static_cast<size_t>(blockIdx.x - m0) * a.H, 1, a.H, kSplitScale);
+        // the expert kernels of a multi-row step take the same normalised rows as three e4m3 planes: the CTA whose index
+        // is the row's (modulo the grid: a router of few experts has fewer CTAs than the step has rows) writes them,
+        // which saves them a kernel of their own
+        if (a.planes != nullptr) {
+            for (int m = 0; m < mb; ++m)
+                if ((m0 + m) % static_cast<int>(gridDim.x) == static_cast<int>(blockIdx.x))
+                    split_rows<3>(a.planes + static_cast<size_t>(m0 + m) * 3 * a.H, xs + static_cast<size_t>(m) * a.H, 1, a.H, kSplitScale);
+        }
         split_bf16_rows(xh, xs, mb, a.H);
         float d[4];
         mw.run(xh, mb * 2, d);

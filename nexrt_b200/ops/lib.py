@@ -55,6 +55,7 @@ _PROTOTYPES = {
     "nexrt_gdn_front": [vp] * 14 + [ci] * 6 + [cf, ci, ci, vp],
     "nexrt_gdn_core": [vp] * 6 + [ci] * 5 + [vp],
     "nexrt_attn_front": [vp] * 9 + [ci] * 7 + [cf, ci, vp],
+    "nexrt_attn_decode_merges_cp": [ci],
     "nexrt_attn_decode": [vp] * 14 + [ci] * 8 + [cf, ci, ci, ci, ci, ci, ci, CH, cu, vp],
     "nexrt_oproj_allreduce": [vp] * 6 + [ci] * 4 + [cf, ci, CH, cu, CH, cu, ci, vp],
     "nexrt_moe_router": [vp] * 8 + [ci] * 5 + [cf, ci, vp, vp],
@@ -84,6 +85,9 @@ _PROTOTYPES = {
     "nexrt_prefill_ctl": [vp, vp, ci, ci, vp],
     "nexrt_prefill_advance": [vp, ci, vp, cu, vp],
     "nexrt_planes_allreduce_residual": [vp, vp, c_int64, ci, CH, cu, vp],
+    "nexrt_ll_allreduce_bench": [vp, vp, ci, ci, CH, cu, vp, vp],
+    "nexrt_ll_seq_advance": [vp, cu, vp],
+    "nexrt_ll_pingpong": [CH, ci, ci, cu, ci, ci, vp, vp],
     "nexrt_norm_rows": [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_gdn_gate_quant": [vp, vp, vp, vp, vp, ci, ci, cf, vp],
     "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],

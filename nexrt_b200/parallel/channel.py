@@ -69,6 +69,16 @@ class LLChannel:
     def multicast(self) -> bool:
         return bool(self.struct.mc)
 
+    def variant(self, multicast: bool = True, budget_ms: Optional[float] = None) -> LLChannelStruct:
+        """A copy of the launch descriptor over the same inbox: without the multicast alias (one store per peer) and / or
+        with another wait budget.  Benchmarks and tests use it to run both publishing forms in one process."""
+        s = LLChannelStruct.from_buffer_copy(self.struct)
+        if not multicast:
+            s.mc = None
+        if budget_ms is not None:
+            s.budget_ns = int(budget_ms * 1e6)
+        return s
+
     def set_budget_ms(self, ms: float) -> None:
         self.struct.budget_ns = int(ms * 1e6)
 

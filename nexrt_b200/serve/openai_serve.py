@@ -16,6 +16,7 @@ can be tested without sockets; the HTTP part is a thin ``http.server`` handler.
 from __future__ import annotations
 
 import argparse
+import itertools
 import json
 import threading
 import time
@@ -165,6 +166,18 @@ def stream_chunk(endpoint: str, base: Dict, *, text: Optional[str] = None, role:
     return chunk
 
 
+def primed(events: Iterator[Dict]) -> Iterator[Dict]:
+    """Pull the first event now.  ``bridge_client.stream_request`` is a generator, so it connects only when first advanced:
+    priming it before the status line goes out turns an unreachable backend into a 502 JSON reply instead of a broken
+    200 stream."""
+    source = iter(events)
+    try:
+        first = next(source)
+    except StopIteration:
+        return iter(())
+    return itertools.chain((first,), source)
+
+
 def sse_events(endpoint: str, events: Iterator[Dict], model: str, requested: int, include_usage: bool, request_id: Optional[str] = None) -> Iterator[str]:
     """Bridge NDJSON events -> SSE ``data:`` lines (ending with ``[DONE]``)."""
     rid = request_id or uuid.uuid4().hex
@@ -179,7 +192,17 @@ def sse_events(endpoint: str, events: Iterator[Dict], model: str, requested: int
     if endpoint == "chat":
         yield line(stream_chunk(endpoint, base, role=True))
     final = None
-    for ev in events:
+    source = iter(events)
+    while True:
+        try:
+            ev = next(source)
+        except StopIteration:
+            break
+        except (ConnectionError, OSError, TimeoutError, ValueError) as error:
+            # the 200 header is out: a backend that dies in mid-stream is reported in-band, and the stream still ends with [DONE]
+            yield line({"error": {"message": f"backend stream failed: {error}", "type": "backend_error", "param": None, "code": None}})
+            yield "data: [DONE]\n\n"
+            return
         kind = ev.get("type")
         if kind == "delta":
             yield line(stream_chunk(endpoint, base, text=ev.get("text", "")))
@@ -288,7 +311,7 @@ class Handler(BaseHTTPRequestHandler):
             self._json(502, ApiError(f"backend unreachable: {error}", status=HTTPStatus.BAD_GATEWAY, kind="backend_error").body())
 
     def _stream(self, endpoint: str, req: Dict, include_usage: bool) -> None:
-        events = self.st.stream(req, self.st.backend_host, self.st.backend_port, self.st.backend_timeout)
+        events = primed(self.st.stream(req, self.st.backend_host, self.st.backend_port, self.st.backend_timeout))   # may raise: do_POST answers 502
         self.send_response(200)
         self.send_header("Content-Type", "text/event-stream")
         self.send_header("Cache-Control", "no-cache")

@@ -29,7 +29,7 @@ def main():
     eng.head.enable_logits()
     V = cfg.vocab // world
     sl = slice(rank * V, (rank + 1) * V)
-    prompt, margin = robust_prompt(ref, cfg.vocab, 21, n_new=6)
+    prompt, margin = robust_prompt(ref, cfg.vocab, 29, n_new=6)
     # non-CP prefill of the first 13 tokens, then CP steps (single-row and 4-row) against the oracle
     ref.reset()
     eng.reset(first_token=prompt[0])
@@ -49,6 +49,12 @@ def main():
     got = eng.head.logits[:4].float().cpu()
     err = rel_l2(got, torch.stack(want[17:21])[:, sl])
     assert err < 2e-2, ("cp four rows", err)
+    # the 8-row verify step of the DFlash mode through the context-parallel arm
+    eng.set_rows(prompt[21:29]); eng.set_forced_commit(8); eng.step_cp(8)
+    torch.cuda.synchronize()
+    got = eng.head.logits[:8].float().cpu()
+    err = rel_l2(got, torch.stack(want[21:29])[:, sl])
+    assert err < 2e-2, ("cp eight rows", err)
     assert eng.status_max() == 0
     # the CP graph and the non-CP graph continue the same stream
     first = eng.prefill(prompt, chunk=8)

@@ -44,7 +44,7 @@ def test_single_row_steps_match_oracle(setup):
     assert ctl["committed_len"] == len(prompt) and ctl["status"] == 0
 
 
-@pytest.mark.parametrize("rows", [2, 4, 8])
+@pytest.mark.parametrize("rows", [2, 3, 4, 5, 7, 8])     # 3, 5, 7: the ragged last chunk of a prefill (second pass of the four-row kernels)
 def test_multi_row_step_matches_sequential(setup, rows):
     cfg, ref, eng = setup
     prompt = synthetic_prompt(cfg.vocab, 3 * rows, seed=2)

@@ -89,8 +89,14 @@ def facade():
         return dict(RESULT)
 
     def stream(req, host, port, timeout):
+        # a generator, like bridge_client.stream_request: it connects when first advanced
         calls.append(req)
-        return iter([{"type": "delta", "text": "abc"}, dict(RESULT, type="done")])
+        if req.get("text") == "explode":
+            raise ConnectionRefusedError("down")
+        yield {"type": "delta", "text": "abc"}
+        if req.get("text") == "dies":
+            raise ConnectionResetError("backend went away")
+        yield dict(RESULT, type="done")
 
     state = FacadeState(model_name="m", call=call, stream=stream, queue_timeout=0.2)
     srv = OpenAIServer(("127.0.0.1", 0), state)
@@ -123,6 +129,12 @@ def test_http_round_trip(facade):
     assert _http(port, "POST", "/v1/completions", {"model": "other", "prompt": "hi"})[0] == 404
     assert _http(port, "POST", "/v1/embeddings", {"input": "x"})[0] == 404
     assert _http(port, "POST", "/v1/completions", {"prompt": "explode"})[0] == 502
+    # a stream whose backend is unreachable is a 502 JSON reply, not a 200 with a broken body
+    status, data = _http(port, "POST", "/v1/completions", {"prompt": "explode", "stream": True})
+    assert status == 502 and json.loads(data)["error"]["type"] == "backend_error"
+    # a backend that dies in mid-stream: the delta, an in-band error, and the stream still ends with [DONE]
+    status, data = _http(port, "POST", "/v1/completions", {"prompt": "dies", "stream": True})
+    assert status == 200 and '"text": "abc"' in data and "backend went away" in data and data.strip().endswith("data: [DONE]")
     # one slot: while it is held a second request is refused after the queue timeout
     state.slot.acquire()
     try:

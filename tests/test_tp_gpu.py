@@ -45,3 +45,12 @@ def test_context_parallel_tp2():
         pytest.skip("needs 2 GPUs")
     r = _run(2, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29614, script="cp_worker.py")
     assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_allreduce_ops():
+    """The packet and block all-reduce protocols as operators: rank-ordered bits, determinism under skew, a silent peer."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    r = _run(world, {"NCCL_NVLS_ENABLE": "0"}, 29615, script="ar_worker.py")
+    assert r.returncode == 0 and "AR_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
