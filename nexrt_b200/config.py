@@ -172,6 +172,13 @@ def rank_shard_config() -> ModelConfig:
     )
 
 
+def shrunk_tp8_config() -> ModelConfig:
+    """Shrunk geometry that splits 8 ways (every head count a multiple of 8, expert width 8 x 128): the numerics of the
+    8-rank deployment against the CPU oracle.  2 kv heads over 8 ranks also gives context-parallel groups of 4, the
+    reference's deployment geometry (``nex_n2_5_pro/attn_cp.py:76-174``)."""
+    return replace(shrunk_config(), name="nex-shrunk-tp8", n_q_heads=8, gdn_qk_heads=8, gdn_v_heads=8, moe_inter=1024, shared_inter=1024)
+
+
 def shrunk_cp_config() -> ModelConfig:
     """Shrunk geometry that can be split 4 ways: 2 kv heads over 4 ranks gives context-parallel groups
     of 2 (multi-GPU tests of the CP arm)."""

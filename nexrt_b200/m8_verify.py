@@ -57,6 +57,14 @@ class M8Verify:
             dist.barrier(group=eng.group)
 
 
+    def guard_ok(self) -> bool:
+        """No kernel of the unit wrote outside a scratch buffer it was handed.  Meaningful when the engine was built under
+        ``NEXRT_CANARY=1`` (guard bands around every scratch buffer, ``runtime/audit.py``); without them there is nothing
+        to check and the answer is True.  The reference guards its CP workspaces the same way
+        (``nex_n2_5_pro/m8_cp.py:143-220,493-500``)."""
+        return not self.eng.ctx.canaries_violated()
+
+
 class M8CpVerify(M8Verify):
     cp = True
 
@@ -64,3 +72,18 @@ class M8CpVerify(M8Verify):
         super().__init__(engine)
         if not engine.cp:
             raise ValueError("the engine was built without the context-parallel arm")
+
+    def cp_protocol_reset(self) -> None:
+        """Resynchronise the context-parallel exchange after a round in which a rank of the kv group did not publish
+        (collective, host side, never inside a capture).  The exchange carries no arrival counters - a packet is matched
+        by the global call sequence in its tag - so resynchronising means: nothing in flight, every inbox of the group
+        zero, the sequence restarted on every rank at once.  ``reset_unit`` already does that for both channels; this
+        name exists for callers written against the reference's retry contract (``nex_n2_5_pro/m8_cp.py:328-431``)."""
+        self.reset_unit()
+
+    def cp_status_max(self) -> int:
+        """Largest status word over the ranks (the CP waits latch into the engine's one status word)."""
+        return self.eng.status_max()
+
+    def cp_guard_ok(self) -> bool:
+        return self.guard_ok()

@@ -138,6 +138,9 @@ class RefModel:
             return v
         return act_quant_dequant(v.reshape(1, -1)).reshape(v.shape)
 
+    tap_layers: tuple = ()      # layers whose output row ``step`` also keeps in ``last_taps``
+    last_taps = None
+
     def reset(self):
         self.pos = 0
         self.route_margin = float("inf")   # smallest gap between the last selected and the first rejected router logit
@@ -217,11 +220,16 @@ class RefModel:
         """Consume ``token`` at the current position, return fp32 logits ``[vocab]``."""
         c = self.cfg
         x = self.embed[token].to(torch.bfloat16)
+        taps = []
         for L, w in enumerate(self.layers):
             st = self.states[L]
             y = self._gdn(w, st, x) if w["kind"] == "linear" else self._attn(w, st, x, self.pos)
             x = (x.float() + y).to(torch.bfloat16)
             x = (x.float() + self._moe(w, x)).to(torch.bfloat16)
+            if L in self.tap_layers:
+                taps.append(x)
+        if taps:
+            self.last_taps = torch.cat(taps)      # the bf16 residual rows after the tapped layers, concatenated (DFlash features)
         self.pos += 1
         if return_hidden:
             return x

@@ -14,6 +14,7 @@ import torch
 from ..config import ModelConfig, ShardSpec
 from ..ops import lib as L
 from ..parallel.channel import LLChannel
+from .audit import guarded_zeros, violated
 from .control import CTL_WORDS, Ctl
 
 MAX_ROWS = 8
@@ -33,7 +34,14 @@ class StepContext:
         self.n_cta = props.multi_processor_count
         H = cfg.hidden
         i32, f32, bf = torch.int32, torch.float32, torch.bfloat16
-        z = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=device)
+        # NEXRT_CANARY=1: every scratch buffer gets guard bands (runtime/audit.py) that ``canaries_violated`` checks
+        self._guards = [] if os.environ.get("NEXRT_CANARY", "0") == "1" else None
+
+        def z(*shape, dtype=f32):
+            if self._guards is None:
+                return torch.zeros(*shape, dtype=dtype, device=device)
+            return guarded_zeros(self._guards, shape, dtype, device)
+
         self.ctl = z(CTL_WORDS, dtype=i32)
         self.ctl[Ctl.EOS] = -1
         self.ctl[Ctl.STOP_POS] = -1
@@ -90,8 +98,8 @@ class StepContext:
         self.moe_ticket = z(1, dtype=i32)
         self.moe_partial = z(4, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)
         # scratch of the tcgen05 expert kernels (multi-row steps): e4m3 activation planes and per-row scales
-        self.moe_planes1 = torch.zeros(3 * MAX_ROWS, cfg.hidden, dtype=torch.uint8, device=device)
-        self.moe_planes2 = torch.zeros(3 * MAX_ROWS, S * spec.inter, dtype=torch.uint8, device=device)
+        self.moe_planes1 = z(3 * MAX_ROWS, cfg.hidden, dtype=torch.uint8)
+        self.moe_planes2 = z(3 * MAX_ROWS, S * spec.inter, dtype=torch.uint8)
         self.moe_descale = z(MAX_ROWS)
         self.moe_ksplit = int(os.environ.get("NEXRT_MOE_KSPLIT", "2"))              # K-split of the tcgen05 gate/up product
         self.moe_gu_tc = z(self.moe_ksplit, MAX_ROWS, S, 2 * spec.inter)          # its partial planes
@@ -99,12 +107,12 @@ class StepContext:
         self.wide_ksplit = int(os.environ.get("NEXRT_WIDE_KSPLIT", "4"))                                                       # K-split of the wide front GEMMs (partials summed by the tail)
         cp_front_rows = (spec.q_heads * spec.cp_size + spec.q_heads + 2 * spec.kv_heads) * cfg.head_dim
         self.wide_pre = z(self.wide_ksplit, MAX_ROWS, max(spec.gdn_front_rows, spec.attn_front_rows, cp_front_rows))  # projections of the wide fronts
-        self.zero_ids = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
-        self.oproj_planes = torch.zeros(3 * MAX_ROWS, max(spec.gdn_local, spec.attn_local), dtype=torch.uint8, device=device)
+        self.zero_ids = z(MAX_ROWS, dtype=torch.int32)
+        self.oproj_planes = z(3 * MAX_ROWS, max(spec.gdn_local, spec.attn_local), dtype=torch.uint8)
         self.oproj_descale = z(MAX_ROWS)
         self.tc_oproj_rows = int(os.environ.get("NEXRT_TC_OPROJ_ROWS", "0")) or 1 << 30   # measured no faster than the fused kernel at 4 and 8 rows: off unless asked for
         self.router_ksplit = 8
-        self.router_planes = torch.zeros(2 * MAX_ROWS, cfg.hidden, dtype=torch.bfloat16, device=device)
+        self.router_planes = z(2 * MAX_ROWS, cfg.hidden, dtype=torch.bfloat16)
         self.router_partial = z(self.router_ksplit, MAX_ROWS, (cfg.n_experts + 1 + 15) // 16 * 16)
         # head scratch
         self.head_cand = z(MAX_ROWS, self.n_cta, MAX_TOPK, dtype=torch.int64)
@@ -114,6 +122,17 @@ class StepContext:
         self.site = 0
         self._rope = {}
         self.early_ctl = os.environ.get("NEXRT_EARLY_CTL", "1") != "0"
+
+    def canaries_violated(self):
+        """Names of the scratch buffers whose guard bands were written (``NEXRT_CANARY=1`` only; ``None`` when off)."""
+        if self._guards is None:
+            return None
+        torch.cuda.synchronize(self.device)
+        bad = violated(self._guards)
+        if not bad:
+            return []
+        by_ptr = {t.data_ptr(): name for name, t in vars(self).items() if isinstance(t, torch.Tensor)}
+        return [by_ptr.get(self._guards[i][0].data_ptr() + 256, f"allocation {i}") for i in bad]
 
     def rope_table(self, cache_len: int) -> torch.Tensor:
         """(cos, sin) of position * inv_freq for every cache position, built once per engine like the

@@ -8,14 +8,15 @@ from dataclasses import replace
 
 import torch
 
-from .config import ModelConfig, shrunk_config, shrunk_cp_config
+from .config import ModelConfig, shrunk_config, shrunk_cp_config, shrunk_tp8_config
 from .weights import random_checkpoint, shard_model
 
 
 @functools.lru_cache(maxsize=4)
-def shrunk_checkpoint(seed: int = 0, cp: bool = False, kv_heads: int = 0):
-    """``kv_heads`` overrides the number of kv heads (1: two ranks already form a context-parallel group)."""
-    cfg = shrunk_cp_config() if cp else shrunk_config()
+def shrunk_checkpoint(seed: int = 0, cp: bool = False, kv_heads: int = 0, tp8: bool = False):
+    """``kv_heads`` overrides the number of kv heads (1: two ranks already form a context-parallel group); ``tp8`` picks the
+    geometry that splits 8 ways."""
+    cfg = shrunk_tp8_config() if tp8 else (shrunk_cp_config() if cp else shrunk_config())
     if kv_heads:
         cfg = replace(cfg, name=f"{cfg.name}-kv{kv_heads}", n_kv_heads=kv_heads)
     return cfg, random_checkpoint(cfg, seed)
@@ -47,10 +48,23 @@ def attach_silent_peer(engine, budget_ms: float = 50.0) -> None:
     nbytes = 2 * 2 * ch.slots * 8
     inbox = torch.zeros(nbytes, dtype=torch.uint8, device=engine.dev)
     sink = torch.zeros(nbytes, dtype=torch.uint8, device=engine.dev)     # where packets "to rank 1" land
-    engine._silent_peer_buffers = (inbox, sink)
     s = ch.struct
+    engine._silent_peer_buffers = (inbox, sink, (s.local, s.mc, s.peer[0], s.peer[1], s.world, s.rank, s.budget_ns))
     s.local, s.mc = inbox.data_ptr(), None
     s.peer[0], s.peer[1] = inbox.data_ptr(), sink.data_ptr()
     s.world, s.rank = 2, 0
     s.budget_ns = int(budget_ms * 1e6)
     ch.world = 2
+
+
+def detach_silent_peer(engine) -> None:
+    """Undo ``attach_silent_peer``: the channel is the single-rank channel again (the peer "came back")."""
+    ch = engine.ctx.channel
+    saved = getattr(engine, "_silent_peer_buffers", None)
+    if saved is None:
+        raise ValueError("no silent peer attached")
+    s = ch.struct
+    s.local, s.mc, s.peer[0], s.peer[1], s.world, s.rank, s.budget_ns = saved[2]
+    ch.world = 1
+    torch.cuda.synchronize(engine.dev)
+    engine._silent_peer_buffers = None

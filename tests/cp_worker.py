@@ -50,12 +50,16 @@ def main():
     err = rel_l2(got, torch.stack(want[17:21])[:, sl])
     assert err < 2e-2, ("cp four rows", err)
     # the 8-row verify step of the DFlash mode through the context-parallel arm
-    eng.set_rows(prompt[21:29]); eng.set_forced_commit(8); eng.step_cp(8)
+    from nexrt_b200.m8_verify import M8CpVerify
+
+    unit = M8CpVerify(eng)
+    unit.seed(prompt[21:29]); eng.set_forced_commit(8); unit.run(begin=True, end=True)
     torch.cuda.synchronize()
     got = eng.head.logits[:8].float().cpu()
     err = rel_l2(got, torch.stack(want[21:29])[:, sl])
     assert err < 2e-2, ("cp eight rows", err)
-    assert eng.status_max() == 0
+    assert unit.cp_status_max() == 0 and unit.cp_guard_ok()
+    unit.cp_protocol_reset()            # collective; the exchange keeps working after it (the prefill and generate below)
     # the CP graph and the non-CP graph continue the same stream
     first = eng.prefill(prompt, chunk=8)
     state = eng.export_state()

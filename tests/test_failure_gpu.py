@@ -49,3 +49,38 @@ def test_generate_raises_on_a_failed_step_and_serving_classifies_it():
         eng.generate(max_new=4)
     assert "status" in str(info.value) and not is_fatal_backend_error(info.value)   # recoverable: reset the request, keep serving
     assert int(eng.ctx.ctl[Ctl.STATUS]) == Status.REDUCE_TIMEOUT
+
+
+def test_failed_eight_row_unit_runs_again_after_reset_unit():
+    """An 8-row verify unit that failed (its peer stayed silent) is re-executed from the same base after ``reset_unit``:
+    the state rings are position indexed with a spare slot, so the second run reads what the first one read
+    (reference tests/test_m8_state_units.py, m8_verify.py:722-741)."""
+    from nexrt_b200.m8_verify import M8Verify
+    from nexrt_b200.models.reference import RefModel, robust_prompt
+    from nexrt_b200.testing import detach_silent_peer, gather_logits
+
+    cfg, ckpt = shrunk_checkpoint(0)
+    ref = RefModel(cfg, ckpt)
+    prompt, _ = robust_prompt(ref, cfg.vocab, 24, seeds=range(1, 9))
+    ref.reset()
+    want = torch.stack([ref.step(t) for t in prompt])[16:]
+    eng = make_engine(cfg, ckpt, max_rows=8)
+    eng.head.enable_logits()
+    eng.prefill(prompt[:16], chunk=8)
+    unit = M8Verify(eng)
+    attach_silent_peer(eng, budget_ms=30.0)
+    unit.seed(prompt[16:24])
+    eng.set_forced_commit(8)
+    unit.run(begin=True, end=True)
+    torch.cuda.synchronize()
+    failed = eng.read_ctl()
+    assert failed["status"] == Status.REDUCE_TIMEOUT and failed["committed_len"] == 16 and failed["commit_count"] == 0
+    detach_silent_peer(eng)
+    unit.reset_unit()
+    unit.seed(prompt[16:24])            # the failed commit cleared ids[0]
+    unit.run(begin=True, end=True)
+    got = gather_logits(eng, 8)
+    ctl = eng.read_ctl()
+    assert ctl["status"] == 0 and ctl["committed_len"] == 24 and ctl["commit_count"] == 8
+    err = float((got - want).norm() / want.norm())
+    assert err < 2e-2, err

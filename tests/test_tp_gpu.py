@@ -35,7 +35,7 @@ def test_context_parallel_tp4():
     out-projection prologue) against the oracle."""
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
-    r = _run(4, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29613, script="cp_worker.py")
+    r = _run(4, {"NEXRT_WAIT_BUDGET_MS": "5000", "NEXRT_CANARY": "1"}, 29613, script="cp_worker.py")
     assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -43,7 +43,7 @@ def test_context_parallel_tp2():
     """2 ranks, 1 kv head: one context-parallel group of 2 (the same worker; needs half the GPUs)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    r = _run(2, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29614, script="cp_worker.py")
+    r = _run(2, {"NEXRT_WAIT_BUDGET_MS": "5000", "NEXRT_CANARY": "1"}, 29614, script="cp_worker.py")
     assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -54,3 +54,22 @@ def test_allreduce_ops():
     world = 4 if torch.cuda.device_count() >= 4 else 2
     r = _run(world, {"NCCL_NVLS_ENABLE": "0"}, 29615, script="ar_worker.py")
     assert r.returncode == 0 and "AR_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_speculative_drafts_tp2():
+    """MTP draft layer and DFlash block draft on 2 ranks against their CPU oracles (draft K/V, draft ids)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _run(2, {"NEXRT_WAIT_BUDGET_MS": "5000"}, 29616, script="spec_worker.py")
+    assert r.returncode == 0 and "SPEC_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_tp8_matches_oracle():
+    """All eight ranks: single-row and multi-row logits, the generated stream and the wide prefill against the CPU oracle on a
+    shrunk geometry that splits 8 ways (the deployment's world size; the other tests stop at 2 and 4)."""
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    if os.environ.get("NEXRT_RUN_TP8_TEST", "0") != "1":
+        pytest.skip("eight-rank run is opt-in (NEXRT_RUN_TP8_TEST=1): it holds a whole node")
+    r = _run(8, {"NEXRT_WAIT_BUDGET_MS": "5000", "NEXRT_TEST_GEOMETRY": "tp8"}, 29617)
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

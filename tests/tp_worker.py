@@ -22,7 +22,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    cfg, ckpt = shrunk_checkpoint(0)
+    cfg, ckpt = shrunk_checkpoint(0, tp8=os.environ.get("NEXRT_TEST_GEOMETRY") == "tp8")
     ref = RefModel(cfg, ckpt)
     eng = make_engine(cfg, ckpt, rank=rank, world=world, device=dev, max_rows=8)
     eng.head.enable_logits()
