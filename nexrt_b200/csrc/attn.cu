@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
     const bool interleaved = a.ngate == a.nq;
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
-        if (m0) { __syncthreads(); mw.preloaded = false; }
+        if (m0) { __syncthreads(); mw.next_pass(); }
         norm.template run<TERMS>(xq, nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
         float d[NT][4];
         mw.template run<NT>(src, xq, a.H, mb * TERMS, d);
@@ -167,8 +167,11 @@ struct AttnDecodeArgs {
 // Tail of the wide front (multi-row steps): the projections of all rows come from the tcgen05 rows GEMM as K-split
 // partial planes pre[ks][M][R]; one thread per weight row adds them in order and scatters the row's M values.
 __global__ void __launch_bounds__(256) attn_front_tail_kernel(AttnFrontArgs a, const float* __restrict__ pre, int R, int ksplit) {
+    TraceCta tr;
+    tr.begin(kTrHelper);
     pdl_launch_dependents();
     pdl_wait();
+    tr.mark(1);
     const int row = blockIdx.x * blockDim.x + threadIdx.x;
     if (row >= R) return;
     const int C0 = a.ctl[kCtlCommittedLen];
@@ -186,6 +189,7 @@ __global__ void __launch_bounds__(256) attn_front_tail_kernel(AttnFrontArgs a, c
 #pragma unroll
     for (int i = 0; i < kMaxRows; ++i)
         if (m0 + i < a.M) attn_front_row(a, row, m0 + i, v[i], C0, interleaved);
+    tr.mark(3);
 }
 
 constexpr int kRowsPerPass = 4;
@@ -543,12 +547,13 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnDecodeArgs a) {
 // Replaces wgmma_fd4_mega's software grid barrier + combine (nex_n2_5_pro/kernels/full_attn/
 // nex_n2_5_pro_attn_fd4_wgmma_ctypes.cu:98-118,389-401) with hardware cluster barriers; nothing here spins.
 namespace cg = cooperative_groups;
-constexpr int kClusterCtas = 8;
-constexpr int kKeysPerCluster = kClusterCtas * 8 * 16;   // one 16-key tile per warp
+constexpr int kClusterCtas = 8;       // portable cluster size
+constexpr int kClusterCtasWide = 16;  // the largest (non-portable) size: twice the warps, so one 16-key tile per warp up to 2048 keys
 
-template <int HD>
+template <int HD, int CL>
 __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs a) {
-    constexpr int RP = kRowsPerPassMma, NW = 8, EL = HD / 32, CL = kClusterCtas, SL = HD / CL;
+    constexpr int RP = kRowsPerPassMma, NW = 8, EL = HD / 32, SL = HD / CL;
+    constexpr int kKeysPerCluster = CL * 8 * 16;   // one 16-key tile per warp
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_last;
     TraceCta tr;
@@ -851,6 +856,37 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
 
 using namespace nexrt;
 
+// Can the device place one cluster of 16 CTAs of this kernel (one GPC with 16 SMs that each take a CTA of `smem` bytes)?
+// Asked once per kernel; also switches the non-portable cluster size on for it.  Host-side queries only: safe while a
+// stream is being captured.
+template <int HD>
+static bool wide_cluster_fits(size_t smem) {
+    static int cached = -1;                   // one answer per kernel instantiation (the function's type would not tell them apart)
+    auto kernel = attn_decode_cluster_kernel<HD, kClusterCtasWide>;
+    if (cached >= 0) return cached == 1;
+    cached = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kClusterCtasWide, 1, 1);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kClusterCtasWide;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    cached = n >= 1 ? 1 : 0;
+    return cached == 1;
+}
+
 extern "C" int nexrt_attn_front_tail(const void* pre, const void* ctl, void* q_raw, void* gate, void* k_raw, void* v_cache, int hd, int nq, int ngate, int kvh,
                                      int M, int cache_len, int ksplit, void* stream) {
     if (M < 1 || M > 128 || ksplit < 1) return cudaErrorInvalidValue;   // no per-row state in the kernel: a prefill chunk goes through in one launch
@@ -929,14 +965,26 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) != 0;
     if (mma && (gemv_mode() & 64) && n_splits >= kClusterCtas) {
-        // cluster form: whole clusters of 8 CTAs along x; its shared memory adds this CTA's partial for the DSMEM combine
-        const int n_clusters = n_splits / kClusterCtas, passes_c = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;
+        // cluster form: whole clusters along x; its shared memory adds this CTA's partial for the DSMEM combine
+        const int passes_c = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;
         const size_t rows = static_cast<size_t>(M) * (nq / kvh);
         const size_t smem_c = sizeof(float) * (rows * hd + static_cast<size_t>(M) * hd + 8 * kRowsPerPassMma * (hd + 2) + static_cast<size_t>(hd / 16) * 32 * 4 +
                                                kRowsPerPassMma * hd + kRowsPerPassMma * 2);
-        const dim3 g(n_clusters * kClusterCtas, kvh, passes_c);
-        if (hd == 256) return launch_cluster(attn_decode_cluster_kernel<256>, g, dim3(256), smem_c, st, kClusterCtas, a);
-        if (hd == 128) return launch_cluster(attn_decode_cluster_kernel<128>, g, dim3(256), smem_c, st, kClusterCtas, a);
+        const size_t smem_max = sizeof(float) * (static_cast<size_t>(kMaxRows) * (nq / kvh) * hd + static_cast<size_t>(kMaxRows) * hd +
+                                                 8 * kRowsPerPassMma * (hd + 2) + static_cast<size_t>(hd / 16) * 32 * 4 + kRowsPerPassMma * hd + kRowsPerPassMma * 2);
+        // clusters of 16 (non-portable size) when asked for and when the device can place one: twice the warps per cluster, so a
+        // context of up to 2048 keys is one 16-key tile per warp and still needs no cross-cluster tail
+        if ((gemv_mode() & 128) && n_splits >= kClusterCtasWide) {
+            const bool fits = hd == 256 ? wide_cluster_fits<256>(smem_max) : (hd == 128 && wide_cluster_fits<128>(smem_max));
+            if (fits) {
+                const dim3 gw(n_splits / kClusterCtasWide * kClusterCtasWide, kvh, passes_c);
+                if (hd == 256) return launch_cluster(attn_decode_cluster_kernel<256, kClusterCtasWide>, gw, dim3(256), smem_c, st, kClusterCtasWide, a);
+                return launch_cluster(attn_decode_cluster_kernel<128, kClusterCtasWide>, gw, dim3(256), smem_c, st, kClusterCtasWide, a);
+            }
+        }
+        const dim3 g(n_splits / kClusterCtas * kClusterCtas, kvh, passes_c);
+        if (hd == 256) return launch_cluster(attn_decode_cluster_kernel<256, kClusterCtas>, g, dim3(256), smem_c, st, kClusterCtas, a);
+        if (hd == 128) return launch_cluster(attn_decode_cluster_kernel<128, kClusterCtas>, g, dim3(256), smem_c, st, kClusterCtas, a);
         return cudaErrorInvalidValue;
     }
     a.flags &= ~8;   // only the cluster kernel reads the control block before its dependency wait

@@ -191,7 +191,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // build compiles all of this to nothing, so the product kernels carry no extra registers.
 enum TraceKind : int {
     kTrEmbed = 0, kTrGdnFront, kTrGdnCore, kTrOproj, kTrRouter, kTrMoeL1, kTrMoeL2, kTrAttnFront, kTrAttnDecode, kTrHead, kTrStepEnd,
-    kTrMoeFused, kTrGdnFused, kTraceKinds = 16
+    kTrTcMoeL1, kTrTcMoeL2, kTrTcRows, kTrTcRouter, kTrHelper, kTraceKinds = 16
 };
 constexpr int kTraceSlots = 20480;        // records per kind
 constexpr int kTraceWords = 9;            // cta | grid << 32, t0, t1, t2, t3, then four kernel-specific extras t4..t7

@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256, 2) dense_bf16_kernel(DenseArgs a) {
     pdl_wait();
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
-        if (m0) { __syncthreads(); mw.preloaded = false; }
+        if (m0) { __syncthreads(); mw.next_pass(); }
         if (a.in_mode == 0) {
             norm.template run<3>(nullptr, xs, static_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(m0) * a.K, mb, a.K, a.eps, red);
         } else if (a.in_mode == 3) {

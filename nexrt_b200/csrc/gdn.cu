@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     const int C0 = a.ctl[kCtlCommittedLen];
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
-        if (m0) { __syncthreads(); mw.preloaded = false; }
+        if (m0) { __syncthreads(); mw.next_pass(); }
         norm.template run<TERMS>(xq, ba_cta ? xs : nullptr, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red, &tr);
         tr.mark(4);
         NEXRT_EVENT(4);
@@ -230,21 +230,58 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
 // row, all token rows in registers), and extra CTAs project the bf16 b/a rows from the fp32 normalised rows xn.
 __global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, const float* __restrict__ pre, const float* __restrict__ xn, int row_ctas,
                                                              int ksplit) {
+    TraceCta tr;
+    tr.begin(kTrHelper);
     pdl_launch_dependents();
     pdl_wait();
+    tr.mark(1);
     if (static_cast<int>(blockIdx.x) < row_ctas) {
         const int row = blockIdx.x * blockDim.x + threadIdx.x;
         if (row >= a.R) return;
+        // Every load of the thread is requested before the first use: the three history taps (positions C0 - 3 .. C0 - 1
+        // of the ring, independent of this step's projections), the conv weights, and up to 8 x 8 K-split partials.  In
+        // program order (sum, store the ring, read the ring back) the same work is four dependent trips to L2.
+        const bool conv = row < a.C;
+        const int C0 = a.ctl[kCtlCommittedLen], ring = a.conv_ring_len;
+        float hist[3] = {0.f, 0.f, 0.f};
+        float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (conv) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j) hist[j] = __ldcg(a.conv_ring + static_cast<size_t>((C0 - 3 + j + ring) % ring) * a.C + row);
+            cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
+        }
+        constexpr int kMaxSplit = 8;
+        float part[kMaxRows][kMaxSplit];
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m)
+#pragma unroll
+            for (int ks = 0; ks < kMaxSplit; ++ks)
+                part[m][ks] = (m < a.M && ks < ksplit) ? __ldcg(pre + (static_cast<size_t>(ks) * a.M + m) * a.R + row) : 0.f;
         float p[kMaxRows];
 #pragma unroll
         for (int m = 0; m < kMaxRows; ++m) {
             p[m] = 0.f;
-            if (m < a.M)
-                for (int ks = 0; ks < ksplit; ++ks) p[m] += pre[(static_cast<size_t>(ks) * a.M + m) * a.R + row];   // K-split partials, fixed order
+#pragma unroll
+            for (int ks = 0; ks < kMaxSplit; ++ks) p[m] += part[m][ks];      // K-split partials, fixed order (absent ones are zero)
         }
-        float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row < a.C) cw = *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4);
-        gdn_front_row<kMaxRows>(a, row, p, 0, a.M, a.ctl[kCtlCommittedLen], cw);
+        if (!conv) {
+#pragma unroll
+            for (int m = 0; m < kMaxRows; ++m)
+                if (m < a.M) a.z[static_cast<size_t>(m) * (a.R - a.C) + (row - a.C)] = p[m];
+        } else {
+            // window of the causal conv: positions C0 - 3 .. C0 + M - 1
+#pragma unroll
+            for (int m = 0; m < kMaxRows; ++m) {
+                if (m < a.M) {
+                    const float h0 = m >= 3 ? p[m - 3 < 0 ? 0 : m - 3] : hist[m], h1 = m >= 2 ? p[m - 2 < 0 ? 0 : m - 2] : hist[m + 1],
+                                h2 = m >= 1 ? p[m - 1 < 0 ? 0 : m - 1] : hist[m + 2 > 2 ? 2 : m + 2];
+                    const float v = fmaf(cw.x, h0, fmaf(cw.y, h1, fmaf(cw.z, h2, cw.w * p[m])));
+                    a.conv_ring[static_cast<size_t>((C0 + m) % ring) * a.C + row] = p[m];
+                    a.qkv[static_cast<size_t>(m) * a.C + row] = silu_f(v);
+                }
+            }
+        }
+        tr.mark(3);
         return;
     }
     // one warp per (b/a row, token row)
@@ -265,6 +302,7 @@ __global__ void __launch_bounds__(256) gdn_front_tail_kernel(GdnFrontArgs a, con
     }
     acc = warp_sum(acc);
     if (lane == 0) gdn_ba_row(a, row, acc, m);
+    tr.mark(3);
 }
 
 struct GdnCoreArgs {
@@ -296,15 +334,30 @@ __global__ void __launch_bounds__(256) gdn_core_kernel(GdnCoreArgs a) {
         const float4 q4 = *reinterpret_cast<const float4*>(row + qk_head * 128 + lane * 4);
         const float4 k4 = *reinterpret_cast<const float4*>(row + (a.nqk + qk_head) * 128 + lane * 4);
         const float v = row[(2 * a.nqk + head) * 128 + col];
-        const float qn = rsqrtf(warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w) + 1e-6f) * 0.08838834764831845f;
-        const float kn = rsqrtf(warp_sum(k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w) + 1e-6f);
         const float decay = __expf(a.g[m * a.nv + head]), b = a.beta[m * a.nv + head];
         S.x *= decay; S.y *= decay; S.z *= decay; S.w *= decay;
-        const float kx = k4.x * kn, ky = k4.y * kn, kz = k4.z * kn, kw = k4.w * kn;
-        const float kv = warp_sum(kx * S.x + ky * S.y + kz * S.z + kw * S.w);
-        const float delta = (v - kv) * b;
-        S.x = fmaf(kx, delta, S.x); S.y = fmaf(ky, delta, S.y); S.z = fmaf(kz, delta, S.z); S.w = fmaf(kw, delta, S.w);
-        const float o = warp_sum(q4.x * S.x + q4.y * S.y + q4.z * S.z + q4.w * S.w) * qn;
+        // One reduction round per row: with S the decayed state, k^ = k / |k| and delta = (v - k^.S) b, the output is
+        // q.(S + k^ delta) = q.S + (q.k^) delta, so the five lane sums q.q, k.k, q.k, k.S and q.S are reduced side by side
+        // and neither the delta nor the output waits for a second, dependent reduction (the reference's core kernel
+        // reduces k.S and q.S_new one after the other, linear_attn/nex_n2_5_pro_linear_recurrent_core_ctypes.cu:117-146).
+        float qq = q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w;
+        float kk = k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w;
+        float qk = q4.x * k4.x + q4.y * k4.y + q4.z * k4.z + q4.w * k4.w;
+        float ks = k4.x * S.x + k4.y * S.y + k4.z * S.z + k4.w * S.w;
+        float qs = q4.x * S.x + q4.y * S.y + q4.z * S.z + q4.w * S.w;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            qq += __shfl_xor_sync(0xffffffffu, qq, off);
+            kk += __shfl_xor_sync(0xffffffffu, kk, off);
+            qk += __shfl_xor_sync(0xffffffffu, qk, off);
+            ks += __shfl_xor_sync(0xffffffffu, ks, off);
+            qs += __shfl_xor_sync(0xffffffffu, qs, off);
+        }
+        const float qn = rsqrtf(qq + 1e-6f) * 0.08838834764831845f, kn = rsqrtf(kk + 1e-6f);
+        const float delta = (v - ks * kn) * b;
+        const float kd = kn * delta;
+        S.x = fmaf(k4.x, kd, S.x); S.y = fmaf(k4.y, kd, S.y); S.z = fmaf(k4.z, kd, S.z); S.w = fmaf(k4.w, kd, S.w);
+        const float o = (qs + qk * kd) * qn;
         *reinterpret_cast<float4*>(a.state_ring + static_cast<size_t>((C0 + m + 1) % a.state_ring_len) * slot_stride + elem) = S;
         if (lane == 0) a.out[static_cast<size_t>(m) * a.nv * 128 + head * 128 + col] = o;
     }

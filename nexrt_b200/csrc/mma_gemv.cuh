@@ -313,6 +313,10 @@ struct MmaWarp {
     }
     // Only for sources that do not depend on data written by earlier kernels of the step.
     __device__ __forceinline__ void preload(const Src& src) { load(src, w0); preloaded = true; }
+    // Before another pass over the SAME weights (the next block of token rows): when one load covers every window of this
+    // warp, the registers still hold them and the pass starts without a trip to L2.  Sources whose rows change between
+    // passes (expert ids per token row) clear `preloaded` themselves instead.
+    __device__ __forceinline__ void next_pass() { preloaded = w0 + NB * wstride >= nwin; }
 
     // xq: shared memory [ncols][Kx] byte planes; columns >= ncols are zero.  NT n-tiles of 8 columns.
     template <int NT>
@@ -416,6 +420,7 @@ struct MmaWarpBf16 {
         }
     }
     __device__ __forceinline__ void preload() { load(w0); preloaded = true; }
+    __device__ __forceinline__ void next_pass() { preloaded = w0 + NB * wstride >= nwin; }   // see MmaWarp::next_pass
     // xh: shared memory bf16 planes [ncols][K]
     __device__ __forceinline__ void run(const __nv_bfloat16* xh, int ncols, float (&d)[4]) {
         d[0] = d[1] = d[2] = d[3] = 0.f;

@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
     pdl_launch_dependents();
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
-        if (m0) { __syncthreads(); mw.preloaded = false; }
+        if (m0) { __syncthreads(); mw.next_pass(); }
         norm.template run<3>(nullptr, xs, a.x + static_cast<size_t>(m0) * a.H, mb, a.H, a.eps, red);
         // the expert kernels of a multi-row step take the same normalised rows as three e4m3 planes: the CTA whose index
         // is the row's (modulo the grid: a router of few experts has fewer CTAs than the step has rows) writes them,
@@ -442,8 +442,11 @@ __global__ void __launch_bounds__(256, 2) moe_router_mma_kernel(RouterArgs a) {
 __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ksplit, int rpc) {
     extern __shared__ __align__(16) float lg_s[];
     __shared__ TopkScratch s_topk[8];
+    TraceCta tr;
+    tr.begin(kTrHelper);
     pdl_launch_dependents();
     pdl_wait();
+    tr.mark(1);
     const int rows = a.E + 1;
     // one CTA per block of rpc token rows (one row per CTA in a decode step; a prefill chunk packs a few rows per CTA)
     const int m0 = blockIdx.x * rpc, mb = min(rpc, a.M - m0);
@@ -474,6 +477,8 @@ __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ks
     for (int m = threadIdx.x >> 5; m < mb; m += blockDim.x >> 5)
         router_topk_warp(lg_s + static_cast<size_t>(m) * rows, a.E, a.topk, a.ids + static_cast<size_t>(m0 + m) * S, a.wts + static_cast<size_t>(m0 + m) * S,
                          s_topk[threadIdx.x >> 5]);
+    __syncthreads();
+    tr.mark(3);
 }
 
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
@@ -660,7 +665,7 @@ extern "C" int nexrt_moe_router_topk(const void* partial, int ksplit, int rows_p
     if (M < 1 || M > 1024 || E > 512 || topk < 1 || topk > 31 || topk > E || ksplit < 1 || ksplit > 16 || rows_pad % 4) return cudaErrorInvalidValue;
     RouterArgs a{nullptr, nullptr, nullptr, static_cast<float*>(logits), static_cast<int*>(ids), static_cast<float*>(wts), nullptr, 0, E, topk, M, 0.f,
                  const_cast<float*>(static_cast<const float*>(partial)), rows_pad, nullptr};
-    const int rpc = M <= kMaxRows ? M : 2;   // a decode step: one CTA, a warp per token row; prefill chunks: two rows per CTA
+    const int rpc = M <= kMaxRows ? 1 : 2;   // a decode step: one CTA per token row (the rows' partial sums and selections run side by side); prefill chunks: two rows per CTA
     return launch(moe_topk_rows_kernel, dim3((M + rpc - 1) / rpc), dim3(256), sizeof(float) * rpc * (E + 1), static_cast<cudaStream_t>(stream), a, ksplit, rpc);
 }
 

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(256, 2) oproj_allreduce_mma_kernel(OProjArgs a
     if (a.mode == 2) cpcall = ll_begin(a.cp, a.cp_site);
     for (int m0 = 0; m0 < a.M; m0 += MP) {
         const int mb = min(MP, a.M - m0);
-        if (m0) { __syncthreads(); mw.preloaded = false; }
+        if (m0) { __syncthreads(); mw.next_pass(); }
         if (a.mode == 0) {
             for (int idx = threadIdx.x * 4; idx < mb * a.K; idx += blockDim.x * 4)
                 *reinterpret_cast<float4*>(xs + idx) = *reinterpret_cast<const float4*>(a.in + static_cast<size_t>(m0) * a.K + idx);

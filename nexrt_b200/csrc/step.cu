@@ -17,7 +17,7 @@ int& gemv_threads_ref() {
 }
 
 int& gemv_mode_ref() {
-    static int mode = 127;
+    static int mode = 255;
     return mode;
 }
 

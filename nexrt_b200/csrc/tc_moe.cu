@@ -50,6 +50,7 @@ struct TcMoeArgs {
     LLChannel ch;
     unsigned int site;
     int* status;
+    int trace_kind;         // timeline builds: which record list this launch writes (kTrTcMoeL1, ...)
 };
 
 // DOWN = false: gate/up of one distinct expert for every row that routes to it.
@@ -66,6 +67,8 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_user[kMaxRows];     // gate/up: slot of row m that uses this CTA's expert, or -1
     __shared__ float s_wscale[kMaxKBlocks + 16 * 8];   // block scale of every K block this CTA walks (no load in the loop)
+    TraceCta tr;
+    tr.begin(a.trace_kind);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int I2 = 2 * a.I;
@@ -106,6 +109,7 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kCols);
     pdl_wait();
+    tr.mark(1);
     bool active = true;
     if (!DOWN) {
         // route plan: the first row that names an expert computes it for every row that does
@@ -247,18 +251,23 @@ __global__ void __launch_bounds__(kThreads, 2) tc_moe_kernel(const __grid_consta
         tc_fence_after();
         tmem_free(tmem_base, kCols);
     }
+    tr.mark(3);
 }
 
 // rmsnorm(x[m]) * gamma -> planes[(3m + term)][H]; xn (optional) keeps the normalised row in fp32
 __global__ void __launch_bounds__(256) rows_norm_split_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, uint8_t* planes, float* xn,
                                                               int H, float eps) {
     __shared__ float red[32];
+    TraceCta tr;
+    tr.begin(kTrHelper);
     pdl_launch_dependents();
     RowNorm<4> norm;
     norm.preload_gamma(gamma, H);
     pdl_wait();
+    tr.mark(1);
     const int m = blockIdx.x;
     norm.template run<3>(planes + static_cast<size_t>(m) * 3 * H, xn ? xn + static_cast<size_t>(m) * H : nullptr, x + static_cast<size_t>(m) * H, 1, H, eps, red);
+    tr.mark(3);
 }
 
 // rmsnorm(x[m]) * gamma -> bf16 planes[(2m + {hi, lo})][H]: x' = hi + lo to ~2^-17
@@ -266,14 +275,18 @@ __global__ void __launch_bounds__(256) rows_norm_split_bf16_kernel(const __nv_bf
                                                                    uint8_t* planes_e4m3, int H, float eps) {
     __shared__ float red[32];
     extern __shared__ __align__(16) float xs[];
+    TraceCta tr;
+    tr.begin(kTrHelper);
     pdl_launch_dependents();
     RowNorm<4> norm;
     norm.preload_gamma(gamma, H);
     pdl_wait();
+    tr.mark(1);
     const int m = blockIdx.x;
     norm.template run<3>(nullptr, xs, x + static_cast<size_t>(m) * H, 1, H, eps, red);
     split_bf16_rows(planes + static_cast<size_t>(m) * 2 * H, xs, 1, H);
     if (planes_e4m3 != nullptr) split_rows<3>(planes_e4m3 + static_cast<size_t>(m) * 3 * H, xs, 1, H, kSplitScale);   // same rows for the expert kernels
+    tr.mark(3);
 }
 
 // h = silu(gate) * up * route weight -> planes[(3m + term)][S * I], descale[m]
@@ -282,8 +295,11 @@ __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restri
     extern __shared__ __align__(16) float hs[];
     __shared__ float red[32];
     __shared__ float ds[1];
+    TraceCta tr;
+    tr.begin(kTrHelper);
     pdl_launch_dependents();
     pdl_wait();
+    tr.mark(1);
     const int m = blockIdx.x, VK = S * I;
     for (int k = threadIdx.x * 4; k < VK; k += blockDim.x * 4) {
         const int sl = k / I, i = k % I;
@@ -301,6 +317,7 @@ __global__ void __launch_bounds__(256) rows_h_split_kernel(const float* __restri
     __syncthreads();
     act_split<3>(planes + static_cast<size_t>(m) * 3 * VK, hs, 1, VK, red, ds);
     if (threadIdx.x == 0) descale[m] = ds[0];
+    tr.mark(3);
 }
 
 template <bool DOWN, bool BF16 = false, bool SHARED = false>
@@ -336,6 +353,7 @@ int nexrt_tc_moe_l1(const void* x, const void* post_ln, const void* w13, const v
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w13_s); a.ids = static_cast<const int*>(ids); a.gu = static_cast<float*>(gu);
     a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.ksplit = ksplit; a.status = status;
+    a.trace_kind = kTrTcMoeL1;
     return launch_tc_moe<false>(mw, mx, a, dim3(2 * I / kBM * ksplit, S, M), st);
 }
 
@@ -358,6 +376,7 @@ int nexrt_tc_rows_gemm(const void* w, const void* w_s, const void* planes, void*
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(out);
     a.H = K; a.I = R / 2; a.S = 1; a.M = M; a.n_total = 1; a.ksplit = ksplit; a.status = status;     // one "expert" of R rows, named by every row
+    a.trace_kind = kTrTcRows;
     return launch_tc_moe<false>(mw, mx, a, dim3(R / kBM * ksplit, 1, 1), static_cast<cudaStream_t>(stream));
 }
 
@@ -376,6 +395,7 @@ int nexrt_tc_router_logits(const void* x, const void* gamma, const void* w, void
     TcMoeArgs a{};
     a.ids = static_cast<const int*>(zero_ids); a.gu = static_cast<float*>(partial);
     a.H = K; a.I = rows_pad / 2; a.S = 1; a.M = M; a.n_total = 1; a.ksplit = ksplit; a.status = status;
+    a.trace_kind = kTrTcRouter;
     return launch_tc_moe<false, true>(mw, mx, a, dim3((rows + kBM - 1) / kBM * ksplit, 1, 1), st);
 }
 
@@ -396,6 +416,7 @@ int nexrt_tc_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, 
     TcMoeArgs a{};
     a.w_s = static_cast<const float*>(w2_s); a.ids = static_cast<const int*>(ids); a.descale = static_cast<const float*>(descale);
     a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = I; a.S = S; a.M = M; a.n_total = n_experts_total; a.ksplit = 1; a.ch = *ch; a.site = site; a.status = status;
+    a.trace_kind = kTrTcMoeL2;
     return launch_tc_moe<true>(mw, mx, a, dim3(H / kBM, M), st);
 }
 
@@ -411,6 +432,7 @@ int nexrt_tc_oproj_allreduce(const void* planes, const void* descale, const void
     a.w_s = static_cast<const float*>(w_s); a.ids = static_cast<const int*>(zero_ids); a.descale = static_cast<const float*>(descale);
     a.x = static_cast<__nv_bfloat16*>(x); a.H = H; a.I = K; a.S = 1; a.M = M; a.n_total = 1; a.ksplit = 1; a.overwrite = overwrite ? 1 : 0;
     a.ch = *ch; a.site = site; a.status = status;
+    a.trace_kind = kTrTcRows;
     return launch_tc_moe<true, false, true>(mw, mx, a, dim3(H / kBM, 1), static_cast<cudaStream_t>(stream));
 }
 

@@ -34,11 +34,11 @@ class Moe:
         cfg, spec = ctx.cfg, ctx.spec
         self.tc_ok = cfg.hidden % 128 == 0 and cfg.hidden <= 4096 and spec.inter % 128 == 0
         # the fused router takes its tensor-core form (the one that can also write the planes) under these conditions
-        self.router_mma = (int(os.environ.get("NEXRT_GEMV_MODE", "127")) & 16) != 0 and cfg.hidden % 1024 == 0 and cfg.hidden <= 4096
+        self.router_mma = (int(os.environ.get("NEXRT_GEMV_MODE", "255")) & 16) != 0 and cfg.hidden % 1024 == 0 and cfg.hidden <= 4096
         self._planes_ready = False
         # routed pair (router stops at partial logits, the gate/up kernel selects): NEXRT_MOE_ROUTED=0 goes back to the
         # router with the one-CTA top-k tail
-        gm = int(os.environ.get("NEXRT_GEMV_MODE", "127"))
+        gm = int(os.environ.get("NEXRT_GEMV_MODE", "255"))
         self.routed_ok = (os.environ.get("NEXRT_MOE_ROUTED", "1") != "0" and (gm & 4) != 0 and (gm & 16) != 0 and cfg.hidden % 1024 == 0
                           and cfg.hidden <= 4096 and spec.inter % 128 == 0)
         self.prefetch = None          # (address, bytes) of a later kernel's constant weights, set by the engine

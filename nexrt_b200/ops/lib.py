@@ -135,7 +135,7 @@ def load(build: bool = True) -> ctypes.CDLL:
     lib.nexrt_launch_count.argtypes = []
     lib.nexrt_launch_count.restype = c_ulonglong
     _install_optional(lib)
-    if os.environ.get("NEXRT_GEMV_MODE") is not None:   # 0: CUDA-core GEMV kernels, 1: tensor-core (default)
+    if os.environ.get("NEXRT_GEMV_MODE") is not None:   # bit mask of the tensor-core / cluster kernel forms (csrc/api.h: nexrt_set_gemv_mode); 0 = CUDA-core kernels
         lib.nexrt_set_gemv_mode(int(os.environ["NEXRT_GEMV_MODE"]))
     if os.environ.get("NEXRT_PDL") is not None:
         lib.nexrt_set_pdl(int(os.environ["NEXRT_PDL"]))

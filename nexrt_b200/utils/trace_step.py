@@ -32,7 +32,7 @@ import torch
 import torch.distributed as dist
 
 KIND_NAMES = ["embed", "gdn_front", "gdn_core", "oproj_ar", "router", "moe_l1", "moe_l2_ar", "attn_front", "attn_decode", "head", "step_end",
-              "moe_fused", "gdn_fused", "k13", "k14", "k15"]
+              "tc_moe_l1", "tc_moe_l2", "tc_rows", "tc_router", "helper"]
 
 
 def collect(buf: torch.Tensor, kinds: int, slots: int, words: int):
@@ -46,11 +46,19 @@ def collect(buf: torch.Tensor, kinds: int, slots: int, words: int):
         if n == 0:
             continue
         r = recs[k, :n]
-        grid = int(r[0, 0].item() >> 32)
         order = torch.argsort(r[:, 1])
         r = r[order]
-        for i in range(0, n - n % grid if n % grid else n, grid):
-            g = r[i : i + grid]
+        # a kind may hold launches of different grids (the helper kernels): records are grouped, in entry order, with the
+        # others of their own grid size until a launch is complete
+        grids = (r[:, 0] >> 32).tolist()
+        open_groups, groups = {}, []
+        for i, gsz in enumerate(grids):
+            open_groups.setdefault(gsz, []).append(i)
+            if len(open_groups[gsz]) == gsz:
+                groups.append(open_groups.pop(gsz))
+        for idxs in groups:
+            g = r[torch.tensor(idxs)]
+            grid = g.shape[0]
             t0, t1, t2, t3 = g[:, 1], g[:, 2], g[:, 3], g[:, 4]
             extras = [int(g[:, j][g[:, j] > 0].max()) if (g[:, j] > 0).any() else 0 for j in range(5, words)]
             t2v = t2[t2 > 0]

@@ -75,3 +75,34 @@ def test_state_dir_prompt_and_preflight(tmp_path):
     rows = {r["check"]: r for r in preflight(3, layers_dir=str(tmp_path), probe_gpu=False)}
     assert not rows["tp degree"]["ok"] and not rows["layer directory"]["ok"] and "embed_tokens" in rows["layer directory"]["detail"]
     assert {r["check"]: r["ok"] for r in preflight(8, probe_gpu=False)}["tp degree"]
+
+
+def test_timeline_collector_groups_launches_of_mixed_grids():
+    """Records of one kind may come from launches of different grid sizes (the helper kernels share a list): the
+    collector must rebuild each launch from the records of its own grid size, in entry order."""
+    import torch
+
+    from nexrt_b200.utils.trace_step import collect
+
+    kinds, slots, words = 3, 16, 9
+    buf = torch.zeros(kinds + kinds * slots * words, dtype=torch.int64)
+    recs = buf[kinds:].view(kinds, slots, words)
+
+    def rec(kind, slot, cta, grid, t0, t1, t3):
+        recs[kind, slot, 0] = cta | (grid << 32)
+        recs[kind, slot, 1], recs[kind, slot, 2], recs[kind, slot, 4] = t0, t1, t3
+
+    # kind 1: a 2-CTA launch, then a 3-CTA launch whose first CTA entered before the first launch's second CTA
+    rec(1, 0, 0, 2, 100, 110, 150)
+    rec(1, 1, 0, 3, 105, 160, 200)
+    rec(1, 2, 1, 2, 108, 112, 155)
+    rec(1, 3, 1, 3, 120, 161, 210)
+    rec(1, 4, 2, 3, 121, 162, 205)
+    buf[1] = 5
+    # kind 2: one complete single-CTA launch and one record of an unfinished 4-CTA launch (dropped)
+    rec(2, 0, 0, 1, 300, 301, 320)
+    rec(2, 1, 0, 4, 330, 331, 340)
+    buf[2] = 2
+    launches = collect(buf, kinds, slots, words)
+    assert [(l["kind"], l["grid"], l["exit"]) for l in launches] == [(1, 2, 155), (1, 3, 210), (2, 1, 320)]
+    assert launches[1]["wait_first"] == 160 and launches[0]["entry"] == 100
