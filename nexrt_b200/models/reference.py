@@ -143,6 +143,8 @@ class RefModel:
 
     def reset(self):
         self.pos = 0
+        self.margins = []                  # per consumed token: the smallest top-k routing gap over the layers
+        self.step_margin = float("inf")
         self.route_margin = float("inf")   # smallest gap between the last selected and the first rejected router logit
         self.states = [RefLayerState() for _ in range(self.cfg.n_layers)]
 
@@ -200,7 +202,9 @@ class RefModel:
         xn = rms_norm(x, w["post_ln"], c.rms_eps)
         logits = w["router"] @ xn
         top = logits.topk(c.top_k + 1).values
-        self.route_margin = min(self.route_margin, float(top[c.top_k - 1] - top[c.top_k]))
+        gap = float(top[c.top_k - 1] - top[c.top_k])
+        self.route_margin = min(self.route_margin, gap)
+        self.step_margin = min(self.step_margin, gap)
         probs = torch.softmax(logits, -1)
         tw, te = probs.topk(c.top_k)
         tw = tw / tw.sum()
@@ -221,6 +225,7 @@ class RefModel:
         c = self.cfg
         x = self.embed[token].to(torch.bfloat16)
         taps = []
+        self.step_margin = float("inf")     # smallest routing gap of THIS token over the layers (``margins`` keeps one per step)
         for L, w in enumerate(self.layers):
             st = self.states[L]
             y = self._gdn(w, st, x) if w["kind"] == "linear" else self._attn(w, st, x, self.pos)
@@ -231,6 +236,7 @@ class RefModel:
         if taps:
             self.last_taps = torch.cat(taps)      # the bf16 residual rows after the tapped layers, concatenated (DFlash features)
         self.pos += 1
+        self.margins.append(self.step_margin)
         if return_hidden:
             return x
         return self.lm_head @ rms_norm(x, self.final_ln, c.rms_eps)

@@ -68,3 +68,34 @@ def detach_silent_peer(engine) -> None:
     ch.world = 1
     torch.cuda.synchronize(engine.dev)
     engine._silent_peer_buffers = None
+
+
+class RouteAwareCheck:
+    """Tolerance policy for comparing a run against the fp32 oracle on RANDOM weights.
+
+    Expert selection is discontinuous: where the oracle's gap between the last selected and the first rejected router
+    logit is tiny (``RefModel.margins``, one value per consumed token), two correct evaluations may pick different
+    experts, and the outputs then differ by ten percent or more - at that token and, through the caches, mildly at
+    every later one.  Tokens with a clear gap are held to ``tol``; a token on a near tie may deviate up to ``loose``, and
+    once one of them has actually deviated the clear-gap tokens after it are held to ``4 * tol`` (their caches carry the
+    other choice).  A kernel bug shows at the clear-gap tokens too, so it cannot hide behind this."""
+
+    def __init__(self, margins, tol: float = 2e-2, near: float = 0.01, loose: float = 0.3):
+        self.margins, self.tol, self.near, self.loose = list(margins), tol, near, loose
+        self.flipped = False
+        self.strict = 0
+
+    def limit(self, first: int, last: int = None) -> float:
+        last = first if last is None else last
+        gap = min(self.margins[first : last + 1])
+        if gap < self.near:
+            return self.loose
+        return 4 * self.tol if self.flipped else self.tol
+
+    def check(self, err: float, first: int, last: int = None, what: str = "") -> None:
+        limit = self.limit(first, last)
+        assert err < limit, (what, first, last, err, limit, min(self.margins[first : (first if last is None else last) + 1]))
+        if limit == self.tol:
+            self.strict += 1
+        elif err >= self.tol:
+            self.flipped = True

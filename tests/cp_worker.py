@@ -10,7 +10,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from nexrt_b200.models.reference import RefModel, robust_prompt, synthetic_prompt  # noqa: E402
-from nexrt_b200.testing import make_engine, shrunk_checkpoint  # noqa: E402
+from nexrt_b200.testing import RouteAwareCheck, make_engine, shrunk_checkpoint  # noqa: E402
 
 
 def rel_l2(a, b):
@@ -34,21 +34,22 @@ def main():
     ref.reset()
     eng.reset(first_token=prompt[0])
     want = [ref.step(t) for t in prompt]
+    chk = RouteAwareCheck(ref.margins)      # near-tie routing positions of this prompt get a looser bound
     for i, tok in enumerate(prompt[:13]):
         eng.set_rows([tok]); eng.set_forced_commit(1); eng.step(1)
         torch.cuda.synchronize()
         err = rel_l2(eng.head.logits[0].float().cpu(), want[i][sl])
-        assert err < 2e-2, ("tp4 single row", i, err)
+        chk.check(err, i, what="single row")
     for i in range(13, 17):
         eng.set_rows([prompt[i]]); eng.set_forced_commit(1); eng.step_cp(1)
         torch.cuda.synchronize()
         err = rel_l2(eng.head.logits[0].float().cpu(), want[i][sl])
-        assert err < 2e-2, ("cp single row", i, err)
+        chk.check(err, i, what="cp single row")
     eng.set_rows(prompt[17:21]); eng.set_forced_commit(4); eng.step_cp(4)
     torch.cuda.synchronize()
     got = eng.head.logits[:4].float().cpu()
     err = rel_l2(got, torch.stack(want[17:21])[:, sl])
-    assert err < 2e-2, ("cp four rows", err)
+    chk.check(err, 17, 20, what="cp four rows")
     # the 8-row verify step of the DFlash mode through the context-parallel arm
     from nexrt_b200.m8_verify import M8CpVerify
 
@@ -57,7 +58,8 @@ def main():
     torch.cuda.synchronize()
     got = eng.head.logits[:8].float().cpu()
     err = rel_l2(got, torch.stack(want[21:29])[:, sl])
-    assert err < 2e-2, ("cp eight rows", err)
+    chk.check(err, 21, 28, what="cp eight rows")
+    assert chk.strict >= 5, chk.strict       # the clear-gap positions before any near tie were held to the tight bound
     assert unit.cp_status_max() == 0 and unit.cp_guard_ok()
     unit.cp_protocol_reset()            # collective; the exchange keeps working after it (the prefill and generate below)
     # the CP graph and the non-CP graph continue the same stream

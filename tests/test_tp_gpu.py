@@ -16,7 +16,12 @@ def _run(world, env_extra, port, script="tp_worker.py"):
     env = dict(os.environ, **env_extra)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(HERE, script)]
-    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    if r.returncode != 0:
+        # the ranks' own tracebacks sit above torchrun's summary: keep the lines that name the failure
+        keep = [ln for ln in (r.stdout + "\n" + r.stderr).splitlines() if any(k in ln for k in ("Error", "assert", "File \"", "rank"))]
+        r.stderr = "\n".join(keep[:60]) + "\n...\n" + r.stderr[-1500:]
+    return r
 
 
 @pytest.mark.parametrize("mode", ["auto", "peer-stores"])
