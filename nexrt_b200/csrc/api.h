@@ -38,6 +38,13 @@ int nexrt_embed_gather(const void* embed, const void* ctl, void* x, void* status
 int nexrt_step_end(void* ctl, void* seq, unsigned int n_sites, void* mirror_host, void* mirror_gen, int words, void* stream);
 int nexrt_residual_add(void* x, const void* y, int n, void* stream);
 
+/* measurement plumbing */
+unsigned long long nexrt_launch_count(void);   /* kernels launched through the library since it was loaded */
+int nexrt_set_partial_out(void* buffer);       /* library-baseline arm: reduce sites store fp32 partial sums [8][H] here instead of exchanging them; NULL = normal */
+int nexrt_set_trace(void* buffer);             /* timeline build only (returns non-zero otherwise): device buffer of nexrt_trace_layout() words, NULL = off */
+int nexrt_trace_layout(int* kinds, int* slots, int* words);
+int nexrt_null_node(int grid, int block, int smem, unsigned long long body_ns, int early_release, void* clock_out, void* stream);   /* empty kernel node that spins body_ns */
+
 /* the all-reduce epilogue in isolation (partial [M][H] fp32 -> x [M][H] bf16, H / 16 CTAs; stamps: per-CTA ns or NULL), the
  * sequence advance that closes a batch of such calls, and a two-rank packet ping-pong (out: elapsed ns, round trips done) */
 int nexrt_ll_allreduce_bench(const void* partial, void* x, int M, int H, const NexrtLLChannel* ch, unsigned int site, void* stamps, void* stream);
@@ -74,6 +81,15 @@ int nexrt_moe_router(const void* x, const void* post_ln, const void* w, void* lo
                      int rows_pad, int H, int E, int topk, int M, float eps, int n_cta, void* planes, void* stream);   /* planes: optional e4m3 [3M][H] for the tcgen05 experts */
 int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* ids, void* gu, int H, int I, int S, int M,
                  float eps, int shared_expert, int n_cta, void* stream);
+/* routed pair of the one-row step: the router stops at K-split partial logits [split][M][rows_pad]; the gate/up kernel adds
+ * them, selects the experts in every CTA and leaves ids / weights / logits for the down projection */
+int nexrt_moe_router_partial(const void* x, const void* post_ln, const void* w, void* partial, int rows_pad, int H, int E, int topk, int M,
+                             float eps, void* planes, void* stream);
+int nexrt_moe_router_partial_split(void);
+int nexrt_moe_l1_routed(const void* x, const void* post_ln, const void* w13, const void* w13_s, const void* partial, int rows_pad, void* ids_out,
+                        void* wts_out, void* logits_out, void* gu, const void* w2, const void* pf, unsigned long long pf_bytes, int H, int I,
+                        int E, int topk, int M, float eps, void* stream);
+int nexrt_attn_decode_merges_cp(int n_splits);   /* 1: the decode kernel chosen for this split count also merges the context-parallel partials */
 int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I, int S,
                            int M, const NexrtLLChannel* ch, unsigned int site, int n_cta, void* stream);
 

@@ -749,12 +749,21 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
     }
     if (!direct) __threadfence();
     cluster.sync();                                      // nobody leaves while a peer may still read its shared memory
-    if (direct || crank != 0) { tr.mark(3); return; }
+    if (direct) { tr.mark(3); return; }
 
-    // ---- several clusters: the last one to arrive (per kv head, over all passes) merges their partials
-    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket + kv, 1) == n_act * static_cast<int>(gridDim.z) - 1);
-    __syncthreads();
+    // ---- several clusters (or a context-parallel group): the last cluster to arrive (per kv head, over all passes) merges
+    // the clusters' partials, and ALL its CTAs share that work.  CTA 0 takes the ticket and stores the verdict into every
+    // CTA's shared memory; the second cluster barrier makes it visible.  (With the tail in one CTA it was the longest
+    // phase of the kernel: 13 us for 8 query rows, 33 us for the 16 rows of a context-parallel group.)
+    if (crank == 0 && threadIdx.x == 0) {
+        const int last = atomicAdd(a.ticket + kv, 1) == n_act * static_cast<int>(gridDim.z) - 1;
+        if (last) a.ticket[kv] = 0;                      // every other cluster of this launch has taken its ticket already
+#pragma unroll
+        for (int c = 0; c < CL; ++c) *cluster.map_shared_rank(&s_last, c) = last;
+    }
+    cluster.sync();
     if (!s_last) { tr.mark(3); return; }
+    tr.mark(7);
     __threadfence();
     const float* base_acc = a.ws_acc + static_cast<size_t>(kv) * a.n_splits * rows * HD;
     const float* base_ml = a.ws_ml + static_cast<size_t>(kv) * a.n_splits * rows * 2;
@@ -764,7 +773,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
     // Context parallel: two passes over the items - first everything that belongs to another rank is sent, then this
     // rank's own heads are merged - so that no rank sits in a wait while it still owes a peer its packets.
     for (int pass = 0; pass < (a.cp_size > 1 ? 2 : 1); ++pass)
-    for (int q4 = threadIdx.x; q4 < rows * HD / 4; q4 += blockDim.x) {
+    for (int q4 = crank * static_cast<int>(blockDim.x) + static_cast<int>(threadIdx.x); q4 < rows * HD / 4; q4 += CL * static_cast<int>(blockDim.x)) {
         const int idx = q4 * 4, r = idx / HD, d = idx % HD;
         const int m = r / G, hg = r % G;                 // token row, head inside the kv group
         // context parallel: head hg of the group belongs to cp rank hg / ngate; only the owner needs the gate
@@ -847,8 +856,6 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         }
         *reinterpret_cast<float4*>(a.out + (static_cast<size_t>(m) * a.ngate + lh) * HD + d) = ctx;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) a.ticket[kv] = 0;
     tr.mark(3);
 }
 

@@ -139,12 +139,14 @@ __device__ __forceinline__ int forced_schedule(unsigned int seed, unsigned int e
 }
 
 // Accept / commit by one thread.  tok[j] is the target's token for the position after row j.
-__device__ __forceinline__ void commit_rows(int* ctl, const int* tok, int M, int upstream_status) {
-    const int C = ctl[kCtlCommittedLen];
-    int status = ctl[kCtlStatus] | upstream_status;
+// `in` is a snapshot of the control block taken by one coalesced load at the start of the tail (shared memory): read word by
+// word from global memory, this single-thread routine is a chain of L2 round trips.
+__device__ __forceinline__ void commit_rows(int* ctl, const int* in, const int* tok, int M, int upstream_status) {
+    const int C = in[kCtlCommittedLen];
+    int status = in[kCtlStatus] | upstream_status;
     for (int j = 0; j < M; ++j)
         if (tok[j] < 0 && status == 0) status = kStatusNonFinite;
-    const unsigned int epoch = static_cast<unsigned int>(ctl[kCtlStepEpoch]);
+    const unsigned int epoch = static_cast<unsigned int>(in[kCtlStepEpoch]);
     if (status != 0) {
         // fail closed: nothing is committed anywhere
         ctl[kCtlStatus] = status;
@@ -160,14 +162,14 @@ __device__ __forceinline__ void commit_rows(int* ctl, const int* tok, int M, int
     }
     int accepted = 0;
     for (int j = 0; j + 1 < M; ++j)
-        if (accepted == j && tok[j] == ctl[kCtlIds + j + 1]) accepted = j + 1;
-    int forced = ctl[kCtlForcedCommit];
-    if (ctl[kCtlForcedSeed] != 0) forced = forced_schedule(static_cast<unsigned int>(ctl[kCtlForcedSeed]), epoch, ctl[kCtlForcedMean10], M);
+        if (accepted == j && tok[j] == in[kCtlIds + j + 1]) accepted = j + 1;
+    int forced = in[kCtlForcedCommit];
+    if (in[kCtlForcedSeed] != 0) forced = forced_schedule(static_cast<unsigned int>(in[kCtlForcedSeed]), epoch, in[kCtlForcedMean10], M);
     if (forced > 0) accepted = min(forced, M) - 1;
     const int commit = accepted + 1;
     int emitted[kMaxRows];
-    for (int j = 0; j < kMaxRows; ++j) emitted[j] = j < accepted ? ctl[kCtlIds + j + 1] : (j == accepted ? tok[accepted] : -1);
-    const int eos = ctl[kCtlEos];
+    for (int j = 0; j < kMaxRows; ++j) emitted[j] = j < accepted ? in[kCtlIds + j + 1] : (j == accepted ? tok[accepted] : -1);
+    const int eos = in[kCtlEos];
     int stop = -1;
     for (int j = 0; j < commit; ++j)
         if (stop < 0 && eos >= 0 && emitted[j] == eos) stop = j;
@@ -209,6 +211,7 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     __shared__ int s_tok[kMaxRows];
     __shared__ int s_status;
     __shared__ unsigned long long s_top[kMaxRows][kMaxTopK];
+    __shared__ int s_ctl[kCtlWords];
     TraceCta tr;
     tr.begin(kTrHead);
     pdl_launch_dependents();
@@ -280,8 +283,10 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1) == static_cast<int>(gridDim.x) - 1);
     __syncthreads();
     if (!s_last) { tr.mark(3); return; }
+    tr.mark(4);
     __threadfence();
     if (threadIdx.x == 0) s_status = cfg.bad ? kStatusBadConfig : 0;
+    if (threadIdx.x < kCtlWords) s_ctl[threadIdx.x] = __ldcg(a.ctl + threadIdx.x);     // one coalesced load for everything the sampler and the commit read
     __syncthreads();
     // ---- last CTA: the per-CTA lists (each sorted descending) are staged in shared memory with one round of coalesced
     // loads - the GEMV's buffers are free now - and warp m merges row m's lists from there, `rows_fit` rows at a time
@@ -302,6 +307,7 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
         }
     }
     __syncthreads();
+    tr.mark(5);
     for (int m = mbase + warp; m < mbase + mcount; m += nwarps) {
         const unsigned long long* lists = a.cand + static_cast<size_t>(m) * n_lists * kMaxTopK;
         const unsigned long long* srow = stage + static_cast<size_t>(m - mbase) * per_row;
@@ -371,7 +377,7 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
             if (a.mode == 2) {
                 tok = s_top[m][0] == 0ull ? -1 : key_id(s_top[m][0]);
             } else {
-                const unsigned int pos = static_cast<unsigned int>(a.ctl[kCtlCommittedLen] + m);
+                const unsigned int pos = static_cast<unsigned int>(s_ctl[kCtlCommittedLen] + m);
                 tok = sample_row(s_top[m], K, cfg, pos, &st, a.export_buf ? a.export_buf + m * kExportWords : nullptr);
             }
             s_tok[m] = tok;
@@ -380,13 +386,14 @@ __global__ void __launch_bounds__(512, 1) lmhead_sample_kernel(HeadArgs a) {
     }
     }
     __syncthreads();
+    tr.mark(6);
     if (threadIdx.x == 0) {
         const int upstream = s_status | (a.ch.status ? *reinterpret_cast<volatile int*>(a.ch.status) : 0);
         if (a.mode == 2) {
             for (int m = 0; m < a.M; ++m) a.ctl[kCtlIds + a.arg + m] = s_tok[m];
             if (upstream) atomicOr(a.ctl + kCtlStatus, upstream);
         } else {
-            commit_rows(a.ctl, s_tok, a.M, upstream);
+            commit_rows(a.ctl, s_ctl, s_tok, a.M, upstream);
         }
         *a.ticket = 0;
     }

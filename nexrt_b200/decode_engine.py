@@ -398,3 +398,46 @@ class DecodeEngine:
                 conv, st = m.export_state(L)
                 layers[idx] = {"kind": "linear", "conv_state": conv.clone(), "recurrent_state": st.clone()}
         return {"rank": self.rank, "tp": self.world, "L": L, "first_token": w[Ctl.PENDING], "layers": layers}
+
+
+# ---- command line ----------------------------------------------------------------------------------------------
+_CLI_MODES = {
+    # flag -> (module under nexrt_b200.utils, arguments it adds); everything after the flag is passed through
+    "--graph": ("profile_step", ["--graph"]),
+    "--profile": ("profile_step", ["--graph", "--leave-one-out"]),
+    "--timeline": ("trace_step", []),
+    "--scale": ("launch_floor", []),
+    "--cp": ("bench_modes", ["--cases", "bs1cp:65536"]),
+    "--cp-sweep": ("bench_modes", ["--cases", "bs1:8192,bs1cp:8192,bs1:65536,bs1cp:65536,bs1:131072,bs1cp:131072,bs1:262144,bs1cp:262144"]),
+    "--generate": ("bench_modes", ["--cases", "bs1:1024"]),
+}
+
+
+def cli_dispatch(argv):
+    """``python -m nexrt_b200.decode_engine MODE [tool arguments]``: the engine's measurement modes under the flag names
+    of the reference's ``decode_engine.py`` CLI (eager / ``--graph`` / ``--profile`` / ``--scale`` / ``--cp`` /
+    ``--cp-sweep`` / ``--generate``, ``nex_n2_5_pro/decode_engine.py:402-934``).  Each mode is one of the tools under
+    ``nexrt_b200/utils``; this returns ``(module name, argument list)`` and ``main`` runs it.  No mode = eager steps."""
+    argv = list(argv)
+    for flag, (module, extra) in _CLI_MODES.items():
+        if flag in argv:
+            argv.remove(flag)
+            if "--cases" in argv and "--cases" in extra:       # an explicit case list wins over the mode's default
+                extra = []
+            return module, extra + argv
+    return "profile_step", argv
+
+
+def main(argv=None) -> int:
+    import importlib
+    import sys
+
+    module, args = cli_dispatch(sys.argv[1:] if argv is None else argv)
+    tool = importlib.import_module(f"nexrt_b200.utils.{module}")
+    sys.argv = [f"nexrt_b200.utils.{module}"] + args
+    out = tool.main()
+    return int(out or 0)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

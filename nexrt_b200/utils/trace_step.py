@@ -78,6 +78,7 @@ def main() -> int:
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--tp", type=int, default=8, help="shard shapes when run on one GPU")
     ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--cp", action="store_true", help="context-parallel attention arm (needs a world whose ranks share kv heads)")
     ap.add_argument("--show-layers", type=int, default=4, help="print the launches of the first N layers in full")
     ap.add_argument("--json", default="")
     ap.add_argument("--phases", default="", help="kernel name: print per-CTA durations between its stamps (mean / max over CTAs and launches)")
@@ -101,15 +102,17 @@ def main() -> int:
     kinds, slots, words = kinds.value, slots.value, words.value
     cfg = full_config().truncated(a.layers)
     tp = world if world > 1 else a.tp
-    model = random_rank_model(cfg, tp, rank if world > 1 else 0, dev)
-    eng = DecodeEngine(rank, world, dev, ext=model, cfg=cfg, shape_tp=None if world > 1 else a.tp, max_rows=max(a.rows, 1), cache_len=a.ctx + 4096)
+    model = random_rank_model(cfg, tp, rank if world > 1 else 0, dev, cp=a.cp)
+    eng = DecodeEngine(rank, world, dev, cp=a.cp, ext=model, cfg=cfg, shape_tp=None if world > 1 else a.tp, max_rows=max(a.rows, 1), cache_len=a.ctx + 4096)
+    if a.cp and not eng.cp:
+        raise SystemExit("--cp: this world has no context-parallel group (every rank owns whole kv heads)")
     eng.reset(first_token=1, committed_len=a.ctx)
     eng.set_rows(list(range(1, a.rows + 1)))
     eng.set_forced_commit(a.rows)
     buf = torch.zeros(kinds + kinds * slots * words, dtype=torch.int64, device=dev)
     if lib.nexrt_set_trace(buf.data_ptr()) != 0:
         raise SystemExit("the loaded library is not the trace variant")
-    graph = eng.capture(a.rows)            # its eager warm-up steps install the buffer address in every translation unit
+    graph = eng.capture(a.rows, cp=a.cp)   # its eager warm-up steps install the buffer address in every translation unit
     for _ in range(10):
         graph.replay()
     torch.cuda.synchronize(dev)
@@ -167,7 +170,8 @@ def main() -> int:
         # per-CTA time between consecutive stamps of one kernel kind: the launch table above shows the LAST CTA at each mark,
         # which mixes different CTAs; this is what one CTA spends in each phase
         k = KIND_NAMES.index(a.phases)
-        order = {"gdn_front": [1, 2, 5, 7, 3, 6, 4], "moe_l1": [1, 5, 2, 6, 7, 8, 4], "moe_l2_ar": [1, 2, 5, 6, 7, 3, 4]}.get(a.phases, [1, 2, 3, 4])
+        order = {"gdn_front": [1, 2, 5, 7, 3, 6, 4], "moe_l1": [1, 5, 2, 6, 7, 8, 4], "moe_l2_ar": [1, 2, 5, 6, 7, 3, 4],
+                 "attn_decode": [1, 2, 5, 6, 3, 7, 8, 4], "head": [1, 2, 3, 5, 6, 7, 4]}.get(a.phases, [1, 2, 3, 4])
         names = {1: "entry", 2: "wait", 3: "mid", 4: "exit", 5: "m4", 6: "m5", 7: "m6", 8: "m7"}
         rows = torch.cat([l["raw"] for l in launches[1 + n_per_layer :] if l["kind"] == k])      # skip the first layer (cold)
         print(f"per-CTA phase durations of {a.phases} ({rows.shape[0]} CTA records), us: mean / p50 / max")

@@ -96,3 +96,32 @@ def test_graph_capture_holds_the_garbage_collector(monkeypatch):
         with capture.graph_capture(object(), object()):
             raise RuntimeError("launch failed")
     assert gc.isenabled()
+
+
+def test_every_entry_point_has_a_matching_ctypes_prototype():
+    """ABI audit: each ``int nexrt_*(...)`` of ``csrc/api.h`` (and of the ``extern "C"`` definitions in the sources) has a
+    ctypes prototype with the same number of arguments, and no prototype names an entry point that does not exist."""
+    import re
+    from pathlib import Path
+
+    from nexrt_b200.ops import lib as L
+
+    csrc = Path(L.__file__).resolve().parent.parent / "csrc"
+    text = (csrc / "api.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = {}
+    for name, args in re.findall(r"\bint\s+(nexrt_\w+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S):
+        args = args.strip()
+        declared[name] = 0 if args in ("", "void") else len([a for a in args.split(",") if a.strip()])
+    defined = set()
+    for src in csrc.glob("*.cu"):
+        body = src.read_text()
+        defined.update(re.findall(r"\b(?:int|size_t|unsigned long long)\s+(nexrt_\w+)\s*\(", body))
+    protos = dict(L._PROTOTYPES)
+    assert protos, "no prototypes found"
+    missing = [n for n in protos if n not in defined]
+    assert not missing, f"prototypes without a definition in csrc: {missing}"
+    wrong = {n: (len(protos[n]), declared[n]) for n in protos if n in declared and len(protos[n]) != declared[n]}
+    assert not wrong, f"argument count differs between ops/lib.py and csrc/api.h (prototype, header): {wrong}"
+    undeclared = [n for n in protos if n not in declared]
+    assert not undeclared, f"entry points without a declaration in api.h: {undeclared}"

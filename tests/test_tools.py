@@ -106,3 +106,15 @@ def test_timeline_collector_groups_launches_of_mixed_grids():
     launches = collect(buf, kinds, slots, words)
     assert [(l["kind"], l["grid"], l["exit"]) for l in launches] == [(1, 2, 155), (1, 3, 210), (2, 1, 320)]
     assert launches[1]["wait_first"] == 160 and launches[0]["entry"] == 100
+
+
+def test_engine_cli_maps_the_reference_modes_to_tools():
+    from nexrt_b200.decode_engine import cli_dispatch
+
+    assert cli_dispatch(["--graph", "--layers", "8"]) == ("profile_step", ["--graph", "--layers", "8"])
+    assert cli_dispatch(["--profile"]) == ("profile_step", ["--graph", "--leave-one-out"])
+    assert cli_dispatch(["--scale", "--nodes", "64"]) == ("launch_floor", ["--nodes", "64"])
+    module, args = cli_dispatch(["--cp-sweep", "--rounds", "50"])
+    assert module == "bench_modes" and args[0] == "--cases" and "bs1cp:262144" in args[1] and args[-2:] == ["--rounds", "50"]
+    assert cli_dispatch(["--cp", "--cases", "bs1cp:8192"]) == ("bench_modes", ["--cases", "bs1cp:8192"])
+    assert cli_dispatch(["--steps", "3"]) == ("profile_step", ["--steps", "3"])
