@@ -156,7 +156,7 @@ struct AttnDecodeArgs {
     float eps;
     // context parallel
     int ldq, ldk;             // row strides of q_raw / k_raw in floats (0: packed)
-    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate; 4: the new k rows are in the cache already
+    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate; 4: the new k rows are in the cache already; 8: control block readable before the dependency wait; 16: single-term bf16 Q / P in the key loop
     int window;               // > 0: sliding window, only the last `window` positions are attended
     int cp_size, cp_rank;     // window of the prefix this rank attends
     LLChannel ch;             // partial exchange inside the cp group (world == cp_size)
@@ -690,7 +690,9 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         const int my_limit = gr < nr ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + (r0 + gr) / G) : -1;
         attn_mma_stage_q<HD>(qf, q_s + static_cast<size_t>(r0) * HD, nr);
         __syncthreads();
-        attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        // bit 16 of the launch flags: bf16 Q and P without their lo terms (see attn_mma_pass)
+        if (a.flags & 16) attn_mma_pass<HD, false>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        else attn_mma_pass<HD, true>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
         __syncthreads();
     }
     tr.mark(5);
@@ -863,35 +865,37 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
 
 using namespace nexrt;
 
-// Can the device place one cluster of 16 CTAs of this kernel (one GPC with 16 SMs that each take a CTA of `smem` bytes)?
-// Asked once per kernel; also switches the non-portable cluster size on for it.  Host-side queries only: safe while a
-// stream is being captured.
-template <int HD>
-static bool wide_cluster_fits(size_t smem) {
-    static int cached = -1;                   // one answer per kernel instantiation (the function's type would not tell them apart)
-    auto kernel = attn_decode_cluster_kernel<HD, kClusterCtasWide>;
-    if (cached >= 0) return cached == 1;
+// How many clusters of CL CTAs of this kernel the device runs at once (0: it cannot place one).  A cluster lives inside
+// one GPC, so 144 CTAs in clusters of 16 are NOT one wave on 148 SMs: eight GPCs hold eight such clusters and the ninth
+// runs after them - at long contexts, where every cluster has work, that doubled the kernel.  The launcher therefore never
+// asks for more clusters than fit.  Asked once per kernel instantiation; also switches the non-portable cluster size on.
+// Host-side queries only: safe while a stream is being captured.
+template <int HD, int CL>
+static int cluster_capacity(size_t smem) {
+    static int cached = -1;                   // one answer per kernel instantiation
+    auto kernel = attn_decode_cluster_kernel<HD, CL>;
+    if (cached >= 0) return cached;
     cached = 0;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    if (CL > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
-        return false;
+        return 0;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kClusterCtasWide, 1, 1);
+    cfg.gridDim = dim3(CL, 1, 1);
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kClusterCtasWide;
+    attr[0].val.clusterDim.x = CL;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return false; }
-    cached = n >= 1 ? 1 : 0;
-    return cached == 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    cached = n > 0 ? n : 0;
+    return cached;
 }
 
 extern "C" int nexrt_attn_front_tail(const void* pre, const void* ctl, void* q_raw, void* gate, void* k_raw, void* v_cache, int hd, int nq, int ngate, int kvh,
@@ -972,6 +976,7 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) != 0;
     if (mma && (gemv_mode() & 64) && n_splits >= kClusterCtas) {
+        if (gemv_mode() & 256) a.flags |= 16;      // single-term bf16 operands in the key loop
         // cluster form: whole clusters along x; its shared memory adds this CTA's partial for the DSMEM combine
         const int passes_c = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;
         const size_t rows = static_cast<size_t>(M) * (nq / kvh);
@@ -981,15 +986,19 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
                                                  8 * kRowsPerPassMma * (hd + 2) + static_cast<size_t>(hd / 16) * 32 * 4 + kRowsPerPassMma * hd + kRowsPerPassMma * 2);
         // clusters of 16 (non-portable size) when asked for and when the device can place one: twice the warps per cluster, so a
         // context of up to 2048 keys is one 16-key tile per warp and still needs no cross-cluster tail
+        const int groups = kvh * passes_c;                      // cluster rows of the grid (y x z)
         if ((gemv_mode() & 128) && n_splits >= kClusterCtasWide) {
-            const bool fits = hd == 256 ? wide_cluster_fits<256>(smem_max) : (hd == 128 && wide_cluster_fits<128>(smem_max));
-            if (fits) {
-                const dim3 gw(n_splits / kClusterCtasWide * kClusterCtasWide, kvh, passes_c);
+            const int cap = hd == 256 ? cluster_capacity<256, kClusterCtasWide>(smem_max) : (hd == 128 ? cluster_capacity<128, kClusterCtasWide>(smem_max) : 0);
+            if (cap > 0) {
+                const int n_clusters = max(1, min(n_splits / kClusterCtasWide, cap / groups));
+                const dim3 gw(n_clusters * kClusterCtasWide, kvh, passes_c);
                 if (hd == 256) return launch_cluster(attn_decode_cluster_kernel<256, kClusterCtasWide>, gw, dim3(256), smem_c, st, kClusterCtasWide, a);
                 return launch_cluster(attn_decode_cluster_kernel<128, kClusterCtasWide>, gw, dim3(256), smem_c, st, kClusterCtasWide, a);
             }
         }
-        const dim3 g(n_splits / kClusterCtas * kClusterCtas, kvh, passes_c);
+        const int cap8 = hd == 256 ? cluster_capacity<256, kClusterCtas>(smem_max) : (hd == 128 ? cluster_capacity<128, kClusterCtas>(smem_max) : 0);
+        const int n_clusters = max(1, min(n_splits / kClusterCtas, cap8 > 0 ? cap8 / groups : n_splits / kClusterCtas));
+        const dim3 g(n_clusters * kClusterCtas, kvh, passes_c);
         if (hd == 256) return launch_cluster(attn_decode_cluster_kernel<256, kClusterCtas>, g, dim3(256), smem_c, st, kClusterCtas, a);
         if (hd == 128) return launch_cluster(attn_decode_cluster_kernel<128, kClusterCtas>, g, dim3(256), smem_c, st, kClusterCtas, a);
         return cudaErrorInvalidValue;

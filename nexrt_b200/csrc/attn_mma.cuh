@@ -75,7 +75,10 @@ __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefe
 //
 // Per tile all K pieces are requested at once, the V rows of the tile and the K rows of the next tile are
 // prefetched into L1 at the same moment, so the dependent phases (scores -> softmax -> values) meet warm lines.
-template <int HD>
+// EXACT = false drops the lo terms of Q and P (bf16 operands, as flash-attention kernels use them: about 1e-3 relative
+// on the output) and with them half of the tensor-core instructions; at long contexts the pass is bound by their issue
+// rate (8 warps share 4 tensor pipes), not by the cache stream.
+template <int HD, bool EXACT = true>
 __device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const uint4* qf, int limit_row, int warp, int nwarps, int lane, float* part) {
     constexpr int KS = HD / 16;    // K steps of the score product == output tiles of the value product
     constexpr int NB = HD / 64;
@@ -127,9 +130,9 @@ __device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const uint4*
             const uint4 q = qf[ks * 32 + lane];
             const int b = ks >> 2, s = ks & 3;
             mma_bf16_16x8x16(s0, q.x, 0u, q.y, 0u, ka[b][2 * s], ka[b][2 * s + 1]);
-            mma_bf16_16x8x16(s0, q.z, 0u, q.w, 0u, ka[b][2 * s], ka[b][2 * s + 1]);
+            if (EXACT) mma_bf16_16x8x16(s0, q.z, 0u, q.w, 0u, ka[b][2 * s], ka[b][2 * s + 1]);
             mma_bf16_16x8x16(s1, q.x, 0u, q.y, 0u, kb[b][2 * s], kb[b][2 * s + 1]);
-            mma_bf16_16x8x16(s1, q.z, 0u, q.w, 0u, kb[b][2 * s], kb[b][2 * s + 1]);
+            if (EXACT) mma_bf16_16x8x16(s1, q.z, 0u, q.w, 0u, kb[b][2 * s], kb[b][2 * s + 1]);
         }
         // ---- mask and online softmax of row g (its 16 scores sit in the 4 lanes that share g)
         float sv[4] = {s0[0], s0[1], s1[0], s1[1]};
@@ -179,7 +182,7 @@ __device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const uint4*
                 const uint32_t a0 = prmt(word(v[0][0]), word(v[1][0]), sel), a1 = prmt(word(v[0][1]), word(v[1][1]), sel);
                 const uint32_t a2 = prmt(word(v[2][0]), word(v[3][0]), sel), a3 = prmt(word(v[2][1]), word(v[3][1]), sel);
                 mma_bf16_16x8x16(o[blk * 8 + j], a0, a1, a2, a3, ph0, ph1);
-                mma_bf16_16x8x16(o[blk * 8 + j], a0, a1, a2, a3, pl0, pl1);
+                if (EXACT) mma_bf16_16x8x16(o[blk * 8 + j], a0, a1, a2, a3, pl0, pl1);
             }
         }
     }
