@@ -134,6 +134,20 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
             attn_front_row(a, row0 + rl, m0 + m, mma_result<TERMS, NT>(tiles, KS, rl, m, kSplitDescale), C0, interleaved);
         }
     }
+    if constexpr (MP == 1) {
+        // further row groups of this CTA when the grid was capped (wide shards, one row): see gdn_front_mma_kernel
+        const int R = (a.nq + a.ngate + 2 * a.kvh) * a.hd;
+        for (int rg = row0 + static_cast<int>(gridDim.x) * kRowsPerGroup; rg < R; rg += static_cast<int>(gridDim.x) * kRowsPerGroup) {
+            __syncthreads();
+            mw.row0 = rg;
+            mw.preloaded = false;
+            float d[NT][4];
+            mw.template run<NT>(src, xq, a.H, TERMS, d);
+            mw.template store<NT>(tiles + warp * TILE, d);
+            __syncthreads();
+            if (threadIdx.x < kRowsPerGroup) attn_front_row(a, rg + threadIdx.x, 0, mma_result<TERMS, NT>(tiles, KS, threadIdx.x, 0, kSplitDescale), C0, interleaved);
+        }
+    }
     tr.mark(3);
 }
 
@@ -921,7 +935,7 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
         const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
         const size_t smem_mma = sizeof(float) * 8 * 256 + static_cast<size_t>(mp) * terms * H + sizeof(float) * H;
         dim3 g(R / 16), b(256);
-        if (mp == 1) return launch(attn_front_mma_kernel<1>, g, b, smem_mma, st, a);
+        if (mp == 1) return launch(attn_front_mma_kernel<1>, dim3(min(R / 16, 2 * n_cta)), b, smem_mma, st, a);   // capped: the kernel walks the rest
         if (mp == 2) return launch(attn_front_mma_kernel<2>, g, b, smem_mma, st, a);
         return launch(attn_front_mma_kernel<4>, g, b, smem_mma, st, a);
     }

@@ -227,6 +227,16 @@ struct TraceCta {
 // ---- host side --------------------------------------------------------------------------------
 namespace nexrt {
 
+// SMs of the current device (asked once per process).
+static inline int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    }
+    return n;
+}
+
 // Process-wide switch: launch with the programmatic-stream-serialisation attribute.
 int& pdl_enabled();
 // Kernels launched through launch() since the library was loaded (a capture counts its nodes with it).

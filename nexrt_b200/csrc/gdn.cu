@@ -222,6 +222,26 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         }
         NEXRT_EVENT(6);
     }
+    if constexpr (MP == 1) {
+        // One-row steps on wide shards (tensor-parallel 1 or 2: up to 1280 row groups): the grid is capped at the CTAs the
+        // machine holds at once and a CTA walks its further groups here - the row is normalised and split once per CTA, not
+        // once per group, and only the weight stream repeats.
+        for (int rg = row0 + static_cast<int>(gridDim.x) * kRowsPerGroup; rg < a.R; rg += static_cast<int>(gridDim.x) * kRowsPerGroup) {
+            __syncthreads();
+            mw.row0 = rg;
+            mw.preloaded = false;
+            float d[NT][4];
+            mw.template run<NT>(src, xq, a.H, TERMS, d);
+            mw.template store<NT>(tiles + warp * TILE, d);
+            __syncthreads();
+            if (threadIdx.x < kRowsPerGroup) {
+                const int row = rg + static_cast<int>(threadIdx.x);
+                float pre[MP] = {mma_result<TERMS, NT>(tiles, KS, threadIdx.x, 0, kSplitDescale)};
+                const float4 cw = row < a.C ? *reinterpret_cast<const float4*>(a.conv_w + static_cast<size_t>(row) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                gdn_front_row<MP>(a, row, pre, 0, 1, C0, cw);
+            }
+        }
+    }
     tr.mark(3);
 }
 
@@ -405,7 +425,8 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
         const size_t smem = sizeof(float) * (static_cast<size_t>(mp) * H + 8 * 256 + 64) + static_cast<size_t>(mp) * 3 * H + sizeof(float) * H +
                             sizeof(__nv_bfloat16) * H + 16 * sizeof(float4);
         dim3 g(R / 16), b(256);
-        if (mp == 1) return launch(gdn_front_mma_kernel<1>, g, b, smem, st, a);
+        // one row: no more CTAs than the machine holds at once (two per SM), but at least the 2 nv that carry a b/a row
+        if (mp == 1) return launch(gdn_front_mma_kernel<1>, dim3(min(R / 16, max(2 * n_cta, 2 * nv))), b, smem, st, a);
         if (mp == 2) return launch(gdn_front_mma_kernel<2>, g, b, smem, st, a);
         return launch(gdn_front_mma_kernel<4>, g, b, smem, st, a);
     }

@@ -578,6 +578,21 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
         if (threadIdx.x < kRowsPerGroup)
             a.gu[static_cast<size_t>(m) * vrows + v0 + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, kSplitDescale);
     }
+    // One-row steps on wide shards: the grid is capped at the CTAs the machine holds at once; a CTA walks its further
+    // groups of 16 virtual rows here.  The row was normalised and the experts selected once per CTA; only the weight
+    // stream repeats.
+    if (a.M == 1) {
+        for (int vg = v0 + static_cast<int>(gridDim.x) * kRowsPerGroup; vg < vrows; vg += static_cast<int>(gridDim.x) * kRowsPerGroup) {
+            __syncthreads();
+            mw.row0 = vg;
+            mw.preloaded = false;
+            float d[1][4];
+            mw.template run<1>(src, xq, a.H, TERMS, d);
+            mw.template store<1>(tiles + warp * 128, d);
+            __syncthreads();
+            if (threadIdx.x < kRowsPerGroup) a.gu[vg + threadIdx.x] = mma_result<TERMS, 1>(tiles, KS, threadIdx.x, 0, kSplitDescale);
+        }
+    }
     tr.mark(3);
 }
 
@@ -679,7 +694,7 @@ extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13,
     const int vrows = S * 2 * I;
     if ((gemv_mode() & 4) && H % 512 == 0 && H <= 4096) {
         const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H;
-        return launch(moe_l1_mma_kernel, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
+        return launch(moe_l1_mma_kernel, dim3(M == 1 ? min(vrows / 16, 2 * sm_count()) : vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
     }
     const size_t smem = sizeof(float) * (static_cast<size_t>(2) * H + gemv_part_floats((vrows + n_cta - 1) / n_cta, 1, gemv_geom(H / 16, gemv_threads())));
     return launch(moe_l1_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
@@ -726,7 +741,7 @@ extern "C" int nexrt_moe_l1_routed(const void* x, const void* post_ln, const voi
     a.w2 = static_cast<const uint8_t*>(w2); a.pf = pf; a.pf_bytes = pf_bytes;
     const int vrows = S * 2 * I;
     const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H + sizeof(float) * static_cast<size_t>(M) * (E + 1);
-    return launch(moe_l1_mma_kernel, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
+    return launch(moe_l1_mma_kernel, dim3(M == 1 ? min(vrows / 16, 2 * sm_count()) : vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
 }
 
 extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I,

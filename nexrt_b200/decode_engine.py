@@ -30,9 +30,10 @@ from .runtime.context import StepContext
 from .runtime.control import CTL_WORDS, Ctl, decode_ctl
 
 # Context length from which generate() switches to the context-parallel graph.  The reference crosses over at 48K on
-# H100 (decode_engine.py:63-66); on 8 x B200 the non-CP arm measured faster at 64K (3248 vs 3800 us per token) and at
-# 256K (3735 vs 4383 us), so by default the CP arm is only taken beyond the model's 256K context, i.e. when asked for.
-CP_THRESHOLD = int(os.environ.get("NEXRT_CP_THRESHOLD", str(512 * 1024)))
+# H100 (decode_engine.py:63-66).  On 8 x B200 (groups of four ranks per kv head, full model) the context-parallel arm
+# measured 28 us per token slower at 64K (3070 vs 3042 us) and 140 us faster at 256K (3549 vs 3689 us); the straight line
+# through the two differences crosses zero at about 96K.
+CP_THRESHOLD = int(os.environ.get("NEXRT_CP_THRESHOLD", str(96 * 1024)))
 WARMUP_STEPS = 3
 
 
@@ -205,7 +206,12 @@ class DecodeEngine:
 
     @property
     def cp_threshold(self) -> int:
-        return CP_THRESHOLD
+        """Context length from which this engine's context-parallel graph is the faster one.  Groups of two ranks never
+        win (a rank then walks half the keys for twice the query rows: 4 x B200, 803 vs 790 us per 8 layers at 256K), so
+        without an explicit ``NEXRT_CP_THRESHOLD`` the arm stays off for them."""
+        if "NEXRT_CP_THRESHOLD" in os.environ or self.spec.cp_size >= 4:
+            return CP_THRESHOLD
+        return 1 << 30
 
     # ---- graphs -------------------------------------------------------------------------------
     def capture(self, M: int = 1, cp: bool = False, warmup: int = WARMUP_STEPS):
@@ -263,7 +269,7 @@ class DecodeEngine:
         g_cp=None,
         max_new: int = 16,
         eos: Optional[int] = None,
-        cp_threshold: int = CP_THRESHOLD,
+        cp_threshold: Optional[int] = None,
         on_tokens: Optional[Callable[[List[int]], None]] = None,
         host_inputs: Optional[torch.Tensor] = None,
     ) -> List[int]:
@@ -273,6 +279,8 @@ class DecodeEngine:
         idles on the host; EOS is therefore learned one step late and the extra replay is simply
         not reported (reference decode_engine.py:326-399).  A token of -1 means a failed step.
         """
+        if cp_threshold is None:
+            cp_threshold = self.cp_threshold
         g_noncp = g_noncp or self.capture(1, cp=False)
         if self.cp and g_cp is None:
             g_cp = self.capture(1, cp=True)
