@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(512, 1) attn_front_kernel(AttnFrontArgs a) {
 }
 
 // Tensor-core form: one CTA per 16 weight rows, 8 warps split K (see mma_gemv.cuh).
-template <int MP>
+template <int MP, bool LOOP = false>      // LOOP: see gdn_front_mma_kernel
 __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a) {
     constexpr int TERMS = MmaShape<MP>::TERMS, NT = MmaShape<MP>::NT, TILE = MmaShape<MP>::TILE, NB = 8, KS = 8;
     extern __shared__ __align__(16) float smem[];
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(256, 2) attn_front_mma_kernel(AttnFrontArgs a)
             attn_front_row(a, row0 + rl, m0 + m, mma_result<TERMS, NT>(tiles, KS, rl, m, kSplitDescale), C0, interleaved);
         }
     }
-    if constexpr (MP == 1) {
+    if constexpr (MP == 1 && LOOP) {
         // further row groups of this CTA when the grid was capped (wide shards, one row): see gdn_front_mma_kernel
         const int R = (a.nq + a.ngate + 2 * a.kvh) * a.hd;
         for (int rg = row0 + static_cast<int>(gridDim.x) * kRowsPerGroup; rg < R; rg += static_cast<int>(gridDim.x) * kRowsPerGroup) {
@@ -935,7 +935,8 @@ extern "C" int nexrt_attn_front(const void* x, const void* in_ln, const void* w,
         const int mp = M == 1 ? 1 : (M == 2 ? 2 : 4), terms = 3;
         const size_t smem_mma = sizeof(float) * 8 * 256 + static_cast<size_t>(mp) * terms * H + sizeof(float) * H;
         dim3 g(R / 16), b(256);
-        if (mp == 1) return launch(attn_front_mma_kernel<1>, dim3(min(R / 16, 2 * n_cta)), b, smem_mma, st, a);   // capped: the kernel walks the rest
+        if (mp == 1 && R / 16 > 2 * n_cta) return launch(attn_front_mma_kernel<1, true>, dim3(2 * n_cta), b, smem_mma, st, a);   // capped: the kernel walks the rest
+        if (mp == 1) return launch(attn_front_mma_kernel<1>, g, b, smem_mma, st, a);
         if (mp == 2) return launch(attn_front_mma_kernel<2>, g, b, smem_mma, st, a);
         return launch(attn_front_mma_kernel<4>, g, b, smem_mma, st, a);
     }

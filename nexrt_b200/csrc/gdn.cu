@@ -125,7 +125,9 @@ __global__ void __launch_bounds__(512, 1) gdn_front_kernel(GdnFrontArgs a) {
 // activation.  MP token rows per pass (1, 2 or 4).  The first 2*nv CTAs also do one b/a row each.
 #define NEXRT_EVENT(i) do { if (a.events != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.events[i] = globaltimer_ns(); } while (0)
 
-template <int MP>
+// LOOP: the grid is smaller than the number of 16-row groups and a CTA walks several of them (one-row steps on wide shards);
+// a separate instantiation, so that the one-group form the 8-way deployment runs keeps its register allocation.
+template <int MP, bool LOOP = false>
 __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
     constexpr int TERMS = MmaShape<MP>::TERMS, NT = MmaShape<MP>::NT, TILE = MmaShape<MP>::TILE, NB = 8, KS = 8;
     extern __shared__ __align__(16) float smem[];
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(256, 2) gdn_front_mma_kernel(GdnFrontArgs a) {
         }
         NEXRT_EVENT(6);
     }
-    if constexpr (MP == 1) {
+    if constexpr (MP == 1 && LOOP) {
         // One-row steps on wide shards (tensor-parallel 1 or 2: up to 1280 row groups): the grid is capped at the CTAs the
         // machine holds at once and a CTA walks its further groups here - the row is normalised and split once per CTA, not
         // once per group, and only the weight stream repeats.
@@ -426,7 +428,8 @@ extern "C" int nexrt_gdn_front(const void* x, const void* in_ln, const void* fro
                             sizeof(__nv_bfloat16) * H + 16 * sizeof(float4);
         dim3 g(R / 16), b(256);
         // one row: no more CTAs than the machine holds at once (two per SM), but at least the 2 nv that carry a b/a row
-        if (mp == 1) return launch(gdn_front_mma_kernel<1>, dim3(min(R / 16, max(2 * n_cta, 2 * nv))), b, smem, st, a);
+        if (mp == 1 && R / 16 > max(2 * n_cta, 2 * nv)) return launch(gdn_front_mma_kernel<1, true>, dim3(max(2 * n_cta, 2 * nv)), b, smem, st, a);
+        if (mp == 1) return launch(gdn_front_mma_kernel<1>, g, b, smem, st, a);
         if (mp == 2) return launch(gdn_front_mma_kernel<2>, g, b, smem, st, a);
         return launch(gdn_front_mma_kernel<4>, g, b, smem, st, a);
     }

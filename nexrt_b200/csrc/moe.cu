@@ -483,6 +483,7 @@ __global__ void __launch_bounds__(256) moe_topk_rows_kernel(RouterArgs a, int ks
 
 // ---- tensor-core forms (see mma_gemv.cuh) ------------------------------------------------------
 // Expert gate/up: one CTA per 16 virtual rows (slot, i), the 8 warps split K = H.
+template <bool LOOP>      // LOOP: the grid is capped and a CTA walks several groups of 16 virtual rows (see gdn_front_mma_kernel)
 __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
     constexpr int TERMS = 3, NB = 8, KS = 8, KQ = kRouterPartialSplit;
     extern __shared__ __align__(16) float smem[];
@@ -581,7 +582,7 @@ __global__ void __launch_bounds__(256, 2) moe_l1_mma_kernel(MoeL1Args a) {
     // One-row steps on wide shards: the grid is capped at the CTAs the machine holds at once; a CTA walks its further
     // groups of 16 virtual rows here.  The row was normalised and the experts selected once per CTA; only the weight
     // stream repeats.
-    if (a.M == 1) {
+    if (LOOP && a.M == 1) {
         for (int vg = v0 + static_cast<int>(gridDim.x) * kRowsPerGroup; vg < vrows; vg += static_cast<int>(gridDim.x) * kRowsPerGroup) {
             __syncthreads();
             mw.row0 = vg;
@@ -694,7 +695,8 @@ extern "C" int nexrt_moe_l1(const void* x, const void* post_ln, const void* w13,
     const int vrows = S * 2 * I;
     if ((gemv_mode() & 4) && H % 512 == 0 && H <= 4096) {
         const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H;
-        return launch(moe_l1_mma_kernel, dim3(M == 1 ? min(vrows / 16, 2 * sm_count()) : vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
+        return (M == 1 && vrows / 16 > 2 * sm_count()) ? launch(moe_l1_mma_kernel<true>, dim3(2 * sm_count()), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a)
+                                                 : launch(moe_l1_mma_kernel<false>, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
     }
     const size_t smem = sizeof(float) * (static_cast<size_t>(2) * H + gemv_part_floats((vrows + n_cta - 1) / n_cta, 1, gemv_geom(H / 16, gemv_threads())));
     return launch(moe_l1_kernel, dim3(n_cta), dim3(gemv_threads()), smem, static_cast<cudaStream_t>(stream), a);
@@ -741,7 +743,8 @@ extern "C" int nexrt_moe_l1_routed(const void* x, const void* post_ln, const voi
     a.w2 = static_cast<const uint8_t*>(w2); a.pf = pf; a.pf_bytes = pf_bytes;
     const int vrows = S * 2 * I;
     const size_t smem_mma = sizeof(float) * 8 * 128 + static_cast<size_t>(3) * H + sizeof(float) * static_cast<size_t>(M) * (E + 1);
-    return launch(moe_l1_mma_kernel, dim3(M == 1 ? min(vrows / 16, 2 * sm_count()) : vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
+    return (M == 1 && vrows / 16 > 2 * sm_count()) ? launch(moe_l1_mma_kernel<true>, dim3(2 * sm_count()), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a)
+                                                 : launch(moe_l1_mma_kernel<false>, dim3(vrows / 16), dim3(256), smem_mma, static_cast<cudaStream_t>(stream), a);
 }
 
 extern "C" int nexrt_moe_l2_allreduce(const void* gu, const void* ids, const void* wts, const void* w2, const void* w2_s, void* x, int H, int I,
