@@ -31,7 +31,7 @@ int nexrt_version(void);
 int nexrt_set_gemv_threads(int threads);
 int nexrt_set_event_ring(void* ring);  /* 8 x u64 device words: phase timestamps of the GDN front kernel, NULL = off */
 int nexrt_set_attn_event_ring(void* ring);   /* 16 x u64 device words: phase timestamps of the attention decode kernel; null = off */
-int nexrt_set_gemv_mode(int mode);   /* bit mask: 1 fronts, 2 out-proj, 4 expert up, 8 expert down, 16 router, 32 attention key loop on tensor cores; 64 attention decode as thread-block clusters, 128 clusters of 16 CTAs where the device can place them, 256 attention key loop with single-term bf16 Q / P (half the tensor-core instructions, about 1e-3 relative); 255 = default, 0 = CUDA-core kernels */
+int nexrt_set_gemv_mode(int mode);   /* bit mask: 1 fronts, 2 out-proj, 4 expert up, 8 expert down, 16 router, 32 attention key loop on tensor cores; 64 attention decode as thread-block clusters, 128 clusters of 16 CTAs where the device can place them; 255 = everything (default), 0 = CUDA-core kernels */
 
 /* step plumbing */
 int nexrt_embed_gather(const void* embed, const void* ctl, void* x, void* status, int H, int vocab, int M, void* stream);

@@ -170,7 +170,7 @@ struct AttnDecodeArgs {
     float eps;
     // context parallel
     int ldq, ldk;             // row strides of q_raw / k_raw in floats (0: packed)
-    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate; 4: the new k rows are in the cache already; 8: control block readable before the dependency wait; 16: single-term bf16 Q / P in the key loop
+    int flags;                // 1: rows of the step see each other (non-causal block); 2: no output gate; 4: the new k rows are in the cache already; 8: control block readable before the dependency wait
     int window;               // > 0: sliding window, only the last `window` positions are attended
     int cp_size, cp_rank;     // window of the prefix this rank attends
     LLChannel ch;             // partial exchange inside the cp group (world == cp_size)
@@ -704,9 +704,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(AttnDecodeArgs
         const int my_limit = gr < nr ? ((a.flags & 1) ? C0 + a.M - 1 : C0 + (r0 + gr) / G) : -1;
         attn_mma_stage_q<HD>(qf, q_s + static_cast<size_t>(r0) * HD, nr);
         __syncthreads();
-        // bit 16 of the launch flags: bf16 Q and P without their lo terms (see attn_mma_pass)
-        if (a.flags & 16) attn_mma_pass<HD, false>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
-        else attn_mma_pass<HD, true>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
+        attn_mma_pass<HD>(keys, qf, my_limit, warp, NW, lane, part + static_cast<size_t>(warp) * RP * (HD + 2));
         __syncthreads();
     }
     tr.mark(5);
@@ -991,7 +989,6 @@ extern "C" int nexrt_attn_decode(const void* q_raw, const void* gate, const void
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool mma = (gemv_mode() & 32) != 0;
     if (mma && (gemv_mode() & 64) && n_splits >= kClusterCtas) {
-        if (gemv_mode() & 256) a.flags |= 16;      // single-term bf16 operands in the key loop
         // cluster form: whole clusters along x; its shared memory adds this CTA's partial for the DSMEM combine
         const int passes_c = (M * (nq / kvh) + kRowsPerPassMma - 1) / kRowsPerPassMma;
         const size_t rows = static_cast<size_t>(M) * (nq / kvh);

@@ -76,8 +76,9 @@ __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefe
 // Per tile all K pieces are requested at once, the V rows of the tile and the K rows of the next tile are
 // prefetched into L1 at the same moment, so the dependent phases (scores -> softmax -> values) meet warm lines.
 // EXACT = false drops the lo terms of Q and P (bf16 operands, as flash-attention kernels use them: about 1e-3 relative
-// on the output) and with them half of the tensor-core instructions; at long contexts the pass is bound by their issue
-// rate (8 warps share 4 tensor pipes), not by the cache stream.
+// on the output) and with them half of the tensor-core instructions.  Measured at 256K context it buys 6 us of a 69 us
+// layer - the pass waits for one DRAM round trip per tile, not for the tensor pipes - and as a run-time branch in the
+// decode kernel it cost the one-row step 1.9 us per attention layer, so no kernel instantiates it.
 template <int HD, bool EXACT = true>
 __device__ __forceinline__ void attn_mma_pass(const AttnMmaKeys& k, const uint4* qf, int limit_row, int warp, int nwarps, int lane, float* part) {
     constexpr int KS = HD / 16;    // K steps of the score product == output tiles of the value product
