@@ -99,3 +99,34 @@ class RouteAwareCheck:
             self.strict += 1
         elif err >= self.tol:
             self.flipped = True
+
+
+def oracle_state(ref) -> dict:
+    """Per-layer state of a ``RefModel`` in the layout of ``DecodeEngine.export_state`` (whole model)."""
+    out = {}
+    for idx, st in enumerate(ref.states):
+        if st.state is not None:
+            out[idx] = {"conv_state": st.conv, "recurrent_state": st.state}
+        else:
+            out[idx] = {"k_cache": torch.stack(st.k, 1), "v_cache": torch.stack(st.v, 1)}
+    return out
+
+
+def shard_oracle_state(state: dict, cfg: ModelConfig, spec) -> dict:
+    """The slice of ``oracle_state`` one tensor-parallel rank holds: its q | k | v conv channels and value heads of every
+    gated-delta-net layer, its kv heads of every attention layer (``config.ShardSpec``)."""
+    D = cfg.gdn_dim
+    out = {}
+    for idx, st in state.items():
+        if "recurrent_state" in st:
+            ql = spec.gdn_qk * D
+            q0 = spec.rank * ql
+            k0 = cfg.gdn_qk_heads * D + q0
+            v0 = 2 * cfg.gdn_qk_heads * D + spec.rank * spec.gdn_v * D
+            conv = st["conv_state"]
+            out[idx] = {"conv_state": torch.cat([conv[q0 : q0 + ql], conv[k0 : k0 + ql], conv[v0 : v0 + spec.gdn_v * D]]),
+                        "recurrent_state": st["recurrent_state"][spec.rank * spec.gdn_v : (spec.rank + 1) * spec.gdn_v]}
+        else:
+            sl = slice(spec.kv_head0, spec.kv_head0 + spec.kv_heads)
+            out[idx] = {"k_cache": st["k_cache"][sl], "v_cache": st["v_cache"][sl]}
+    return out

@@ -1,0 +1,82 @@
+"""Host-side helpers that the GPU tests lean on, checked on the CPU: the routing-aware tolerance policy, the sharding of
+the oracle's state, the launch-descriptor variants of an LL channel, and the context-parallel threshold policy."""
+
+import torch
+
+from nexrt_b200.config import ShardSpec
+from nexrt_b200.models.reference import RefModel, synthetic_prompt
+from nexrt_b200.testing import RouteAwareCheck, oracle_state, shard_oracle_state, shrunk_checkpoint
+
+
+def test_route_aware_check_policy():
+    c = RouteAwareCheck([0.1, 0.1, 0.005, 0.1, 0.002, 0.1], tol=2e-2, near=0.01, loose=0.3)
+    c.check(0.01, 0)
+    c.check(0.019, 1)
+    assert c.strict == 2 and not c.flipped
+    c.check(0.15, 2)                       # a near tie that did flip
+    assert c.flipped
+    c.check(0.05, 3)                       # clear-gap token after the flip: 4 x tol
+    try:
+        c.check(0.09, 3)
+        raise SystemExit("a clear-gap token 9 % off must fail even after a flip")
+    except AssertionError:
+        pass
+    c.check(0.2, 4)
+    d = RouteAwareCheck([0.1, 0.1])
+    try:
+        d.check(0.03, 0, 1)                # no near tie in the span: the tight bound applies
+        raise SystemExit("must fail")
+    except AssertionError:
+        pass
+
+
+def test_shards_of_the_oracle_state_tile_the_whole():
+    cfg, ckpt = shrunk_checkpoint(0, cp=True)       # the geometry that also splits four ways
+    ref = RefModel(cfg, ckpt)
+    ref.prefill(synthetic_prompt(cfg.vocab, 5))
+    ref_state = oracle_state(ref)
+    for tp in (2, 4):
+        parts = [shard_oracle_state(ref_state, cfg, ShardSpec(cfg, tp, r)) for r in range(tp)]
+        for idx, whole in ref_state.items():
+            if "recurrent_state" in whole:
+                assert torch.equal(torch.cat([p[idx]["recurrent_state"] for p in parts]), whole["recurrent_state"])
+                D, nqk = cfg.gdn_dim, cfg.gdn_qk_heads
+                q = torch.cat([p[idx]["conv_state"][: nqk // tp * D] for p in parts])
+                assert torch.equal(q, whole["conv_state"][: nqk * D])
+                v = torch.cat([p[idx]["conv_state"][2 * (nqk // tp) * D :] for p in parts])
+                assert torch.equal(v, whole["conv_state"][2 * nqk * D :])
+            else:
+                heads = [p[idx]["k_cache"] for p in parts]
+                if tp <= cfg.n_kv_heads:
+                    assert torch.equal(torch.cat(heads), whole["k_cache"])
+                else:      # ranks of one context-parallel group hold the same kv head
+                    assert torch.equal(heads[0], heads[1]) and torch.equal(heads[0], whole["k_cache"][:1])
+
+
+def test_channel_variants_share_the_inbox():
+    from nexrt_b200.parallel.channel import LLChannel
+
+    ch = LLChannel(torch.device("cpu"), 1, 0, 64)
+    v = ch.variant(multicast=False, budget_ms=50)
+    assert v.local == ch.struct.local and v.seq == ch.struct.seq and v.status == ch.struct.status
+    assert v.budget_ns == 50_000_000 and ch.struct.budget_ns != v.budget_ns and not v.mc
+    v.world = 7
+    assert ch.struct.world == 1            # a copy, not a view
+
+
+def test_cp_threshold_depends_on_the_group_size(monkeypatch):
+    import nexrt_b200.decode_engine as de
+
+    class Fake:
+        cp_threshold = de.DecodeEngine.cp_threshold
+
+    monkeypatch.delenv("NEXRT_CP_THRESHOLD", raising=False)
+    cfg, _ = shrunk_checkpoint(0)
+    f = Fake()
+    f.spec = type("S", (), {"cp_size": 2})()
+    assert f.cp_threshold == 1 << 30                      # groups of two never win: off unless asked for
+    f.spec = type("S", (), {"cp_size": 4})()
+    assert f.cp_threshold == de.CP_THRESHOLD == 96 * 1024
+    monkeypatch.setenv("NEXRT_CP_THRESHOLD", "1000")
+    f.spec = type("S", (), {"cp_size": 2})()
+    assert f.cp_threshold == de.CP_THRESHOLD              # an explicit setting applies to every group size

@@ -133,15 +133,7 @@ def test_glue_kernels_against_pytorch():
     assert int((hs != 0).sum()) == T * S
 
 
-def _oracle_state(ref):
-    """Per-layer state of a RefModel in the layout of DecodeEngine.export_state."""
-    out = {}
-    for idx, st in enumerate(ref.states):
-        if st.state is not None:
-            out[idx] = {"conv_state": st.conv, "recurrent_state": st.state}
-        else:
-            out[idx] = {"k_cache": torch.stack(st.k, 1), "v_cache": torch.stack(st.v, 1)}
-    return out
+from nexrt_b200.testing import oracle_state as _oracle_state  # noqa: E402
 
 
 @pytest.mark.parametrize("length,wide", [(53, 16), (150, 64)])

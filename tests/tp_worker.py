@@ -10,7 +10,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from nexrt_b200.models.reference import RefModel, robust_prompt, synthetic_prompt  # noqa: E402
-from nexrt_b200.testing import make_engine, shrunk_checkpoint  # noqa: E402
+from nexrt_b200.testing import make_engine, oracle_state, shard_oracle_state, shrunk_checkpoint  # noqa: E402
 
 
 def rel_l2(a, b):
@@ -97,6 +97,26 @@ def main():
     dist.all_gather(allt, t)
     assert all(torch.equal(allt[0], u) for u in allt), allt
     assert len(eng.generate(max_new=4)) == 4 and eng.status_max() == 0
+
+    # the same wide path against the CPU oracle with the SAME arithmetic (one e4m3 plane per FP8 projection input), held to
+    # the tolerance of the step kernels on this rank's shard of every layer's state: a lost block of the chunk all-reduce,
+    # a wrong row of an attention sub-step or a mis-masked expert shows as an error of order one
+    ref8 = RefModel(cfg, ckpt, fp8_activations=True)
+    wprompt, _ = robust_prompt(ref8, cfg.vocab, 53, seeds=range(1, 9))
+    ref8.reset()
+    ref8.prefill(wprompt)
+    want_w = shard_oracle_state(oracle_state(ref8), cfg, eng.spec)
+    eng.prefill(wprompt, chunk=8, wide=16)
+    got_w = eng.export_state()
+    assert eng.status_max() == 0 and got_w["L"] == 53
+    n_wide = (53 - 1) // 16 * 16
+    for idx, st in want_w.items():
+        for key, w_ in st.items():
+            have = got_w["layers"][idx][key].float().cpu()
+            assert rel_l2(have, w_.float()) < 4e-2, ("wide vs matched oracle", idx, key, rel_l2(have, w_.float()))
+            if key in ("k_cache", "v_cache"):
+                per_pos = (have - w_.float()).norm(dim=-1) / w_.float().norm(dim=-1).clamp_min(1e-6)
+                assert float(per_pos[:, :n_wide].max()) < 0.1, (idx, key, float(per_pos[:, :n_wide].max()))
     dist.barrier()
     if rank == 0:
         print("TP_WORKER_OK", flush=True)
