@@ -59,7 +59,7 @@ def test_dflash_draft_matches_the_oracle():
         want_k, want_v = oracle.kv(l, L)
         assert rel_l2(block.k_cache[l][:, :L].float().cpu(), want_k) < 2e-2, l
         assert rel_l2(block.v_cache[l][:, :L].float().cpu(), want_v) < 2e-2, l
-    # round 1: the block at base position L
+    # first draft round: the block at base position L
     ids, dev_logits = _draft_on_device(block)
     _, want_logits = oracle.draft(first, L)
     _check_block(ids, dev_logits, want_logits, first)
@@ -76,7 +76,7 @@ def test_dflash_draft_matches_the_oracle():
     for j in range(n):
         ref.step(ids[j])
         oracle.context(L + j, ref.last_taps)
-    # round 2
+    # second draft round
     ids2, dev_logits2 = _draft_on_device(block)
     _, want2 = oracle.draft(ctl["pending"], L + n)
     _check_block(ids2, dev_logits2, want2, ctl["pending"])
