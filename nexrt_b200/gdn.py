@@ -60,8 +60,6 @@ class Gdn:
             )
         else:
             self._front_fused(M)
-            if os.environ.get("NEXRT_DUP") == "front":      # timing experiment: the same kernel again, with warm instruction caches
-                self._front_fused(M)
         self._rest(M)
 
     def _front_fused(self, M: int) -> None:

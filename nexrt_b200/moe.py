@@ -84,9 +84,6 @@ class Moe:
         cfg, spec, st = c.cfg, c.spec, c.stream()
         check(lib.nexrt_moe_router_partial(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_partial), self.rows_pad, cfg.hidden,
                                            cfg.n_experts, cfg.top_k, M, cfg.rms_eps, None, st), "moe_router_partial")
-        if os.environ.get("NEXRT_DUP") == "router":     # timing experiment: the same kernel again, with warm instruction caches
-            check(lib.nexrt_moe_router_partial(ptr(c.x), ptr(w["post_ln"]), ptr(w["router_w_pad"]), ptr(c.moe_partial), self.rows_pad, cfg.hidden,
-                                               cfg.n_experts, cfg.top_k, M, cfg.rms_eps, None, st), "moe_router_partial")
         pf, pf_bytes = self.prefetch if (self.prefetch is not None and M == 1) else (None, 0)
         check(lib.nexrt_moe_l1_routed(ptr(c.x), ptr(w["post_ln"]), ptr(w["w13"]), ptr(w["w13_s"]), ptr(c.moe_partial), self.rows_pad, ptr(c.moe_ids),
                                       ptr(c.moe_wts), ptr(c.moe_logits), ptr(c.moe_gu), ptr(w["w2"]) if self.prefetch_w2 else None, pf, pf_bytes,
