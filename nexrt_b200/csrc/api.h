@@ -144,16 +144,16 @@ int nexrt_tc_gemm_fp8_ex(const void* wq, const float* sw, int64_t ldw, const voi
 int nexrt_tc_gemm_bf16_ex(const void* w, int64_t ldw, const void* x, int64_t ldx, void* y, int T, int R, int K, int ldy, int ksplit, int* status,
                           void* stream);   /* K / 64 must divide into ksplit non-empty ranges of at most 64 blocks */
 // Optional RMSNorm (gamma != null, stored as the full multiplier) then per-row, per-128-column e4m3 quantisation.
-int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream);
+int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, int terms, void* stream);   /* xq / sx: terms planes of T rows */
 
 // ---- glue kernels of the wide prefill path (prefill.cu) ---------------------------------------------------------
 int nexrt_prefill_embed(const void* embed, const void* ids, void* x, void* status, int H, int vocab, int T, void* stream);
 int nexrt_prefill_ctl(const void* ctl, void* table, int n_sub, int rows, void* stream);   /* table[j] = ctl with committed length + j * rows */
 int nexrt_prefill_advance(void* ctl, int rows, void* seq, unsigned int n_sites, void* stream);   /* committed length += rows, LL sequence base += n_sites */
 int nexrt_planes_allreduce_residual(void* x, const void* y, int64_t n, int ksplit, const NexrtLLChannel* ch, unsigned int site, void* stream);
-int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, void* stream);
-int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream);
-int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, int ksplit, void* stream);   /* gu: [ksplit][T][n_total * 2I] */
+int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, int terms, void* stream);
+int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, int terms, void* stream);
+int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, int ksplit, int terms, void* stream);   /* gu: [ksplit][T][n_total * 2I] */
 int nexrt_moe_mark_used(const void* ids, void* used, int n_ids, int n_total, void* stream);   /* used[e] = 1 for every routed expert id */
 int nexrt_planes_residual(void* x, const void* y, void* sum_out, int64_t n, int ksplit, void* stream);
 int nexrt_gdn_chunk(const void* pre, const void* xn, const void* ba_w, const void* conv_w, const void* a_log, const void* dt_bias, const void* ctl,

@@ -11,6 +11,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "ll.cuh"
+#include "mma_gemv.cuh"
 
 namespace nexrt {
 namespace {
@@ -53,20 +54,31 @@ __global__ void prefill_advance_kernel(int* ctl, int rows, unsigned int* seq, un
     }
 }
 
-__device__ __forceinline__ void quant_block4(const float v[4], __nv_fp8_storage_t* dst, float* scale_out, int lane) {
+// One 128-column block (4 values per lane) to P e4m3 planes: plane 0 = e4m3(v / scale) with scale = amax / 448, plane p the
+// residual of the planes before it at 16 times finer a scale (the step kernels' exact split, mma_gemv.cuh: split4), so that
+// v = sum_p scale / 16^p * plane_p to 2^-4, 2^-8, 2^-12 of each value for P = 1, 2, 3.  Plane p of the values lies
+// q_stride bytes and of the scales s_stride floats behind plane p - 1: the planes are extra token rows of the GEMM that
+// follows, and its consumer adds their products like K-split partial sums.
+template <int P>
+__device__ __forceinline__ void quant_block4(const float v[4], __nv_fp8_storage_t* dst, float* scale_out, int lane, size_t q_stride, size_t s_stride) {
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
     amax = warp_max(amax);
-    const float scale = fmaxf(amax, 1e-12f) / 448.f;
+    float scale = fmaxf(amax, 1e-12f) / 448.f;
     const float inv = 1.f / scale;
-    uint32_t packed = 0;
+    float r[4] = {v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv};
+    uint32_t out[P];
+    split4<P>(r, out);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-    reinterpret_cast<uint32_t*>(dst)[lane] = packed;
-    if (lane == 0) *scale_out = scale;
+    for (int p = 0; p < P; ++p) {
+        reinterpret_cast<uint32_t*>(dst + p * q_stride)[lane] = out[p];
+        if (lane == 0) scale_out[p * s_stride] = scale;
+        scale *= kTermInv;
+    }
 }
 
 // GDN output gate: per 128-wide head rmsnorm(o) * gnorm_w * silu(z), then e4m3 with one scale per head (= per 128-wide
 // K block of the out-projection).  One warp per (row, head).
+template <int P>
 __global__ void __launch_bounds__(256) gdn_gate_quant_kernel(const float* __restrict__ o, const float* __restrict__ z, const float* __restrict__ gnorm_w,
                                                              __nv_fp8_storage_t* __restrict__ xq, float* __restrict__ sx, int K, int T, float eps) {
     pdl_launch_dependents();
@@ -82,7 +94,8 @@ __global__ void __launch_bounds__(256) gdn_gate_quant_kernel(const float* __rest
     const float4 gw = *reinterpret_cast<const float4*>(gnorm_w + lane * 4);
     const float inv = rsqrtf(warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / 128.f + eps);
     const float v[4] = {gw.x * ov.x * inv * silu_f(zz.x), gw.y * ov.y * inv * silu_f(zz.y), gw.z * ov.z * inv * silu_f(zz.z), gw.w * ov.w * inv * silu_f(zz.w)};
-    quant_block4(v, xq + static_cast<size_t>(m) * K + h * 128, sx + static_cast<size_t>(m) * heads + h, lane);
+    quant_block4<P>(v, xq + static_cast<size_t>(m) * K + h * 128, sx + static_cast<size_t>(m) * heads + h, lane, static_cast<size_t>(T) * K,
+                    static_cast<size_t>(T) * heads);
 }
 
 // Expert activation of the dense expert product.  gu [T][n_total * 2I] holds gate|up of EVERY expert for every row (the
@@ -90,6 +103,7 @@ __global__ void __launch_bounds__(256) gdn_gate_quant_kernel(const float* __rest
 // are what costs); only the S routed (row, expert) pairs are turned into h = silu(gate) * up * route weight, quantised
 // per 128 columns into hq [T][n_total * I] with scales hs [T][n_total * I / 128].  Both were zeroed before: a zero scale
 // removes an unrouted block from the down product.  One warp per (row, slot, 128-column block).
+template <int P>
 __global__ void __launch_bounds__(256) moe_dense_act_kernel(const float* __restrict__ gu, const int* __restrict__ ids, const float* __restrict__ wts,
                                                             __nv_fp8_storage_t* __restrict__ hq, float* __restrict__ hs, int I, int S, int T, int n_total,
                                                             int ksplit) {
@@ -111,7 +125,8 @@ __global__ void __launch_bounds__(256) moe_dense_act_kernel(const float* __restr
         up.x += u2.x; up.y += u2.y; up.z += u2.z; up.w += u2.w;
     }
     const float v[4] = {silu_f(gt.x) * up.x * wt, silu_f(gt.y) * up.y * wt, silu_f(gt.z) * up.z * wt, silu_f(gt.w) * up.w * wt};
-    quant_block4(v, hq + (static_cast<size_t>(m) * n_total + e) * I + b * 128, hs + (static_cast<size_t>(m) * n_total + e) * nb + b, lane);
+    quant_block4<P>(v, hq + (static_cast<size_t>(m) * n_total + e) * I + b * 128, hs + (static_cast<size_t>(m) * n_total + e) * nb + b, lane,
+                    static_cast<size_t>(T) * n_total * I, static_cast<size_t>(T) * n_total * nb);
 }
 
 __global__ void moe_mark_used_kernel(const int* __restrict__ ids, int* __restrict__ used, int n_ids, int n_total) {
@@ -247,6 +262,7 @@ __global__ void __launch_bounds__(256) planes_allreduce_residual_kernel(__nv_bfl
 //   xq / sx : e4m3 with one scale per 128 columns (FP8 projections, expert gate/up),
 //   xn      : fp32 (the bf16 b/a rows of the GDN front are projected from it),
 //   planes  : bf16 hi + lo per token, [T][2][K] (the router: x = hi + lo to about 2^-17, two accumulating GEMMs).
+template <int P>
 __global__ void __launch_bounds__(256) norm_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, __nv_fp8_storage_t* __restrict__ xq,
                                                         float* __restrict__ sx, float* __restrict__ xn, __nv_bfloat16* __restrict__ planes, int K, float eps) {
     // thread t owns columns [8t, 8t + 8) of every 2048-column slab (K <= 8192): one 16-byte load per slab, the row stays in
@@ -309,15 +325,20 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const __nv_bfloat16* __r
             // the 16 lanes of a 128-column block share one scale (all 32 lanes take part in the shuffles)
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            const float scale = fmaxf(amax, 1e-12f) / 448.f, inv = 1.f / scale;
-            uint32_t w0 = 0, w1 = 0;
+            float scale = fmaxf(amax, 1e-12f) / 448.f;
+            const float inv = 1.f / scale;
+            float r0[4] = {v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv}, r1[4] = {v[i][4] * inv, v[i][5] * inv, v[i][6] * inv, v[i][7] * inv};
+            uint32_t w0[P], w1[P];
+            split4<P>(r0, w0);
+            split4<P>(r1, w1);
+            // plane p = rows [p * T, (p + 1) * T) of xq / sx (T = gridDim.x): extra token rows of the GEMM that follows
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                w0 |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i][j] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
-                w1 |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i][4 + j] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+            for (int p = 0; p < P; ++p) {
+                const size_t row = static_cast<size_t>(p) * gridDim.x + t;
+                *reinterpret_cast<uint2*>(xq + row * K + k0) = make_uint2(w0[p], w1[p]);
+                if ((lane & 15) == 0) sx[row * KB + k0 / 128] = scale;
+                scale *= kTermInv;
             }
-            *reinterpret_cast<uint2*>(xq + static_cast<size_t>(t) * K + k0) = make_uint2(w0, w1);
-            if ((lane & 15) == 0) sx[static_cast<size_t>(t) * KB + k0 / 128] = scale;
         }
     }
 }
@@ -506,19 +527,28 @@ int nexrt_planes_allreduce_residual(void* x, const void* y, int64_t n, int kspli
                   static_cast<__nv_bfloat16*>(x), static_cast<const float*>(y), static_cast<size_t>(n), ksplit, *ch, site);
 }
 
-int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, void* stream) {
-    if (T < 1 || K % 128) return cudaErrorInvalidValue;
+// `terms` (1..3) = number of e4m3 planes the quantisers write: plane p occupies rows [p * T, (p + 1) * T) of xq / sx.
+int nexrt_gdn_gate_quant(const void* o, const void* z, const void* gnorm_w, void* xq, void* sx, int K, int T, float eps, int terms, void* stream) {
+    if (T < 1 || K % 128 || terms < 1 || terms > 3) return cudaErrorInvalidValue;
     const int items = T * (K / 128);
-    return launch(gdn_gate_quant_kernel, dim3((items + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(o),
-                  static_cast<const float*>(z), static_cast<const float*>(gnorm_w), static_cast<__nv_fp8_storage_t*>(xq), static_cast<float*>(sx), K, T, eps);
+    auto go = [&](auto kern) {
+        return launch(kern, dim3((items + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(o), static_cast<const float*>(z),
+                      static_cast<const float*>(gnorm_w), static_cast<__nv_fp8_storage_t*>(xq), static_cast<float*>(sx), K, T, eps);
+    };
+    return terms == 1 ? go(gdn_gate_quant_kernel<1>) : terms == 2 ? go(gdn_gate_quant_kernel<2>) : go(gdn_gate_quant_kernel<3>);
 }
 
-int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, int ksplit, void* stream) {
-    if (T < 1 || I % 128 || S < 1 || ksplit < 1) return cudaErrorInvalidValue;
+int nexrt_moe_dense_act(const void* gu, const void* ids, const void* wts, void* hq, void* hs, int I, int S, int T, int n_total, int ksplit, int terms,
+                        void* stream) {
+    if (T < 1 || I % 128 || S < 1 || ksplit < 1 || terms < 1 || terms > 3) return cudaErrorInvalidValue;
     const int items = T * S * (I / 128);
-    return launch(moe_dense_act_kernel, dim3((items + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(gu),
-                  static_cast<const int*>(ids), static_cast<const float*>(wts), static_cast<__nv_fp8_storage_t*>(hq), static_cast<float*>(hs), I, S, T, n_total, ksplit);
+    auto go = [&](auto kern) {
+        return launch(kern, dim3((items + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(gu), static_cast<const int*>(ids),
+                      static_cast<const float*>(wts), static_cast<__nv_fp8_storage_t*>(hq), static_cast<float*>(hs), I, S, T, n_total, ksplit);
+    };
+    return terms == 1 ? go(moe_dense_act_kernel<1>) : terms == 2 ? go(moe_dense_act_kernel<2>) : go(moe_dense_act_kernel<3>);
 }
+
 
 int nexrt_moe_mark_used(const void* ids, void* used, int n_ids, int n_total, void* stream) {
     if (n_ids < 1 || n_total < 1) return cudaErrorInvalidValue;
@@ -535,10 +565,13 @@ int nexrt_planes_residual(void* x, const void* y, void* sum_out, int64_t n, int 
                   static_cast<__nv_bfloat16*>(x), static_cast<const float*>(y), static_cast<float*>(sum_out), static_cast<size_t>(n), ksplit);
 }
 
-int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, void* stream) {
-    if (T < 1 || K < 256 || K % 256 || K > 8192) return cudaErrorInvalidValue;
-    return launch(norm_rows_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(gamma),
-                  static_cast<__nv_fp8_storage_t*>(xq), static_cast<float*>(sx), static_cast<float*>(xn), static_cast<__nv_bfloat16*>(planes), K, eps);
+int nexrt_norm_rows(const void* x, const void* gamma, void* xq, void* sx, void* xn, void* planes, int K, int T, float eps, int terms, void* stream) {
+    if (T < 1 || K < 256 || K % 256 || K > 8192 || terms < 1 || terms > 3) return cudaErrorInvalidValue;
+    auto go = [&](auto kern) {
+        return launch(kern, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(gamma),
+                      static_cast<__nv_fp8_storage_t*>(xq), static_cast<float*>(sx), static_cast<float*>(xn), static_cast<__nv_bfloat16*>(planes), K, eps);
+    };
+    return terms == 1 ? go(norm_rows_kernel<1>) : terms == 2 ? go(norm_rows_kernel<2>) : go(norm_rows_kernel<3>);
 }
 
 // GDN layer of a chunk after its q|k|v|z projection (pre: ksplit partial planes [ksplit][T][R]): conv + gates (front) and

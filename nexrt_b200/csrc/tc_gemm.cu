@@ -26,6 +26,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "mma_gemv.cuh"
 #include "tc_common.cuh"
 
 namespace {
@@ -248,7 +249,10 @@ __global__ void __launch_bounds__(kThreads, 2) tc_gemm_kernel(const __grid_const
 }
 
 // ---- row-wise activation quantisation: optional RMSNorm, then e4m3 with one scale per 128 columns ---------
-// x [T, ldx] bf16 (or fp32 when x_fp32), gamma [K] fp32 or null, xq [T, K] e4m3, sx [T, K/128] fp32.
+// x [T, ldx] bf16 (or fp32 when x_fp32), gamma [K] fp32 or null, xq [P * T, K] e4m3, sx [P * T, K/128] fp32: P planes of T
+// rows each, plane p the residual of the planes before it at a 16 times finer scale (the step kernels' exact split), so
+// that a GEMM over all P * T rows followed by a sum of its row blocks multiplies by x to 2^-4, 2^-8 or 2^-12 of each value.
+template <int P>
 __global__ void act_quant_kernel(const void* __restrict__ x, int x_fp32, int ldx, const float* __restrict__ gamma, float eps,
                                  __nv_fp8_storage_t* __restrict__ xq, float* __restrict__ sx, int K) {
     pdl_launch_dependents();
@@ -290,14 +294,18 @@ __global__ void act_quant_kernel(const void* __restrict__ x, int x_fp32, int ldx
             amax = fmaxf(amax, fabsf(v[i]));
         }
         amax = warp_max(amax);
-        const float scale = fmaxf(amax, 1e-12f) / 448.f;
+        float scale = fmaxf(amax, 1e-12f) / 448.f;
         const float inv = 1.f / scale;
-        uint32_t packed = 0;
+        float r[4] = {v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv};
+        uint32_t out[P];
+        split4<P>(r, out);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-        reinterpret_cast<uint32_t*>(xq + static_cast<size_t>(t) * K + kb * 128)[threadIdx.x & 31] = packed;
-        if ((threadIdx.x & 31) == 0) sx[static_cast<size_t>(t) * KB + kb] = scale;
+        for (int p = 0; p < P; ++p) {
+            const size_t row = static_cast<size_t>(p) * gridDim.x + t;
+            reinterpret_cast<uint32_t*>(xq + row * K + kb * 128)[threadIdx.x & 31] = out[p];
+            if ((threadIdx.x & 31) == 0) sx[row * KB + kb] = scale;
+            scale *= kTermInv;
+        }
     }
 }
 
@@ -449,10 +457,13 @@ int nexrt_tc_gemm_bf16_ex(const void* w, int64_t ldw, const void* x, int64_t ldx
     return launch_tc<false, 64>(mw, mx, a, s);
 }
 
-// Optional RMSNorm (gamma != null) followed by per-row, per-128-column e4m3 quantisation.
-int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, void* stream) {
-    if (T <= 0 || K <= 0 || K % 128) return cudaErrorInvalidValue;
-    return launch(act_quant_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), x, x_fp32, ldx, gamma, eps, static_cast<__nv_fp8_storage_t*>(xq), sx, K);
+// Optional RMSNorm (gamma != null) followed by per-row, per-128-column e4m3 quantisation into `terms` (1..3) planes.
+int nexrt_act_quant(const void* x, int x_fp32, int ldx, const float* gamma, float eps, void* xq, float* sx, int T, int K, int terms, void* stream) {
+    if (T <= 0 || K <= 0 || K % 128 || terms < 1 || terms > 3) return cudaErrorInvalidValue;
+    auto go = [&](auto kern) {
+        return launch(kern, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), x, x_fp32, ldx, gamma, eps, static_cast<__nv_fp8_storage_t*>(xq), sx, K);
+    };
+    return terms == 1 ? go(act_quant_kernel<1>) : terms == 2 ? go(act_quant_kernel<2>) : go(act_quant_kernel<3>);
 }
 
 }  // extern "C"

@@ -93,7 +93,8 @@ class DecodeEngine:
         self.embed = ext["head"]["embed"]
         self.mirror = CtlMirror(self.dev, CTL_WORDS)
         self.graphs: Dict = {}
-        self._wide: Dict = {}     # wide prefill paths by chunk size
+        self._wide: Dict = {}     # wide prefill paths by (chunk size, activation terms, feature taps)
+        self.wide_terms = 0       # activation terms of the wide prefill: 0 = NEXRT_WIDE_TERMS or 3 (the step kernels' exact split); 1 = one e4m3 plane
         self._n_sites: Dict = {}
         # DFlash feature taps: residual rows after the MoE of chosen layers, concatenated per row
         self.tap_layers: Dict[int, int] = {}
@@ -330,7 +331,9 @@ class DecodeEngine:
         evaluates the suffix; ``on_chunk(start, end)`` is called after each chunk is queued.  ``wide`` (default: the
         ``NEXRT_WIDE_PREFILL`` environment variable, 0 = off) is the row count of the wide path
         (``prefill_wide.WidePrefill``): whole chunks of that many tokens go through one tcgen05 GEMM per projection,
-        the rest of the prompt (at least its last token) through the 8-row steps."""
+        the rest of the prompt (at least its last token) through the 8-row steps.  Its activations carry the decode
+        kernels' exact three-term split unless ``self.wide_terms`` (or ``NEXRT_WIDE_TERMS``) is 2 or 1 (one e4m3 plane:
+        1.65 times the throughput, states equal to the 8-row path's only to FP8 rounding)."""
         if self.max_rows < min(chunk, len(ids)) and len(ids) > 1:
             chunk = self.max_rows
         ids = list(int(t) for t in ids)
@@ -374,10 +377,11 @@ class DecodeEngine:
 
         if not prefill_wide.supported(self):
             return None
-        key = rows if self.taps is None else (rows, tuple(sorted(self.tap_layers)))
+        terms = int(self.wide_terms or os.environ.get("NEXRT_WIDE_TERMS", "3"))
+        key = (rows, terms, None if self.taps is None else tuple(sorted(self.tap_layers)))
         wp = self._wide.get(key)
         if wp is None:
-            wp = self._wide[key] = prefill_wide.WidePrefill(self, rows)
+            wp = self._wide[key] = prefill_wide.WidePrefill(self, rows, terms=terms)
         return wp
 
     def load_prefill(self, state: Dict) -> None:

@@ -77,7 +77,7 @@ _PROTOTYPES = {
     "nexrt_kv_publish": [vp, ci, ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp],
     "nexrt_tc_gemm_fp8": [vp, vp, c_int64, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
     "nexrt_tc_gemm_bf16": [vp, c_int64, vp, c_int64, vp, ci, ci, ci, ci, ci, vp, vp],
-    "nexrt_act_quant": [vp, ci, ci, vp, cf, vp, vp, ci, ci, vp],
+    "nexrt_act_quant": [vp, ci, ci, vp, cf, vp, vp, ci, ci, ci, vp],
     "nexrt_tc_gemm_bf16_ex": [vp, c_int64, vp, c_int64, vp, ci, ci, ci, ci, ci, vp, vp],
     "nexrt_tc_gemm_fp8_ex": [vp, vp, c_int64, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp, ci, vp, vp],
     "nexrt_moe_mark_used": [vp, vp, ci, ci, vp],
@@ -88,9 +88,9 @@ _PROTOTYPES = {
     "nexrt_ll_allreduce_bench": [vp, vp, ci, ci, CH, cu, vp, vp],
     "nexrt_ll_seq_advance": [vp, cu, vp],
     "nexrt_ll_pingpong": [CH, ci, ci, cu, ci, ci, vp, vp],
-    "nexrt_norm_rows": [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp],
-    "nexrt_gdn_gate_quant": [vp, vp, vp, vp, vp, ci, ci, cf, vp],
-    "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
+    "nexrt_norm_rows": [vp, vp, vp, vp, vp, vp, ci, ci, cf, ci, vp],
+    "nexrt_gdn_gate_quant": [vp, vp, vp, vp, vp, ci, ci, cf, ci, vp],
+    "nexrt_moe_dense_act": [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
     "nexrt_planes_residual": [vp, vp, vp, c_int64, ci, vp],
     "nexrt_gdn_chunk": [vp] * 14 + [ci] * 9 + [vp],
     "nexrt_rows_norm_split": [vp, vp, vp, vp, ci, ci, cf, vp],

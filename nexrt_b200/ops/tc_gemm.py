@@ -18,15 +18,19 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def act_quant(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``x [T, K]`` (bf16 or fp32, last dim contiguous) -> (e4m3 ``[T, K]``, fp32 scales ``[T, K/128]``);
-    with ``gamma`` (the full RMSNorm multiplier, fp32 ``[K]``) the rows are normalised first."""
+def act_quant(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 1e-6, terms: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x [T, K]`` (bf16 or fp32, last dim contiguous) -> (e4m3 ``[terms * T, K]``, fp32 scales ``[terms * T, K/128]``);
+    with ``gamma`` (the full RMSNorm multiplier, fp32 ``[K]``) the rows are normalised first.  ``terms`` > 1 writes the
+    step kernels' exact split as further row blocks: block ``p`` holds the residual of the blocks before it at a 16 times
+    finer scale, so ``sum_p fp8_gemm(...)[p * T : (p + 1) * T]`` multiplies by ``x`` to 2^-8 (two terms) or 2^-12 (three)."""
     if x.dim() != 2 or x.stride(1) != 1 or x.dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("act_quant expects a 2-D bf16/fp32 tensor with contiguous rows")
+    if terms not in (1, 2, 3):
+        raise ValueError("act_quant: terms must be 1, 2 or 3")
     T, K = x.shape
-    xq = torch.empty(T, K, dtype=FP8, device=x.device)
-    sx = torch.empty(T, K // 128, dtype=torch.float32, device=x.device)
-    check(lib().nexrt_act_quant(ptr(x), int(x.dtype == torch.float32), x.stride(0), ptr(gamma), eps, ptr(xq), ptr(sx), T, K, _stream()), "act_quant")
+    xq = torch.empty(terms * T, K, dtype=FP8, device=x.device)
+    sx = torch.empty(terms * T, K // 128, dtype=torch.float32, device=x.device)
+    check(lib().nexrt_act_quant(ptr(x), int(x.dtype == torch.float32), x.stride(0), ptr(gamma), eps, ptr(xq), ptr(sx), T, K, terms, _stream()), "act_quant")
     return xq, sx
 
 

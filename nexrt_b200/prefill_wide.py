@@ -22,9 +22,14 @@ tokens.  Here a chunk of ``T`` rows goes through each layer in one pass:
   chunk on every rank.
 
 The state it leaves (conv / state rings, KV cache, committed length) is the decode path's own, so decode - or the
-8-row prefill of the prompt's tail - continues from it.  Activations are quantised to one e4m3 plane here (the
-decode kernels use an exact three-term split), so hidden states agree with the 8-row path to FP8 rounding, not
-bit for bit; the same holds between the reference's SGLang prefill and its decode kernels.
+8-row prefill of the prompt's tail - continues from it.
+
+Activation precision (``terms``).  With one term the activations of every FP8 product are one e4m3 plane (a scale per row
+and 128 columns), so hidden states agree with the 8-row path to FP8 rounding only; the same holds between the reference's
+SGLang prefill and its decode kernels.  With two or three terms the quantisers write the step kernels' split
+(``x = s (t1 + t2 / 16 + t3 / 256)``) as further row blocks of the activation matrix: the GEMM runs over ``terms * T``
+token rows against the same weight tiles (which it still streams from memory once), and whoever consumes its output adds
+the row blocks like K-split partial sums.  Three terms reproduce the decode arithmetic to 2^-12 per activation.
 """
 
 from __future__ import annotations
@@ -70,25 +75,29 @@ def down_split(k_blocks: int, tiles: int, n_cta: int, max_blocks: int = 64, max_
 
 
 class WidePrefill:
-    def __init__(self, eng, chunk: int = 64, graph: bool = True):
+    def __init__(self, eng, chunk: int = 64, graph: bool = True, terms: int = 3):
         if chunk % SUB or chunk < 2 * SUB or chunk > 128:
             raise ValueError("chunk must be a multiple of 8 between 16 and 128")
+        if terms not in (1, 2, 3):
+            raise ValueError("terms must be 1, 2 or 3")
         if not supported(eng):
             raise ValueError("model shapes outside the wide prefill path")
         self.eng, self.T, self.use_graph = weakref.proxy(eng), chunk, graph     # the engine owns this object: no reference cycle
         c, cfg, spec, dev = eng.ctx, eng.cfg, eng.spec, eng.dev
         T, H = chunk, cfg.hidden
+        P = self.P = terms            # e4m3 planes per activation = row blocks of every FP8 product's token side
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
         z = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=dev)
         self.n_sub = T // SUB
         self.ids = z(T, dtype=i32)
         self.x = z(T, H, dtype=bf)
-        self.xq, self.sx = torch.zeros(T, H, dtype=FP8, device=dev), z(T, H // 128)
+        self.xq, self.sx = torch.zeros(P * T, H, dtype=FP8, device=dev), z(P * T, H // 128)
         self.xn = z(T, H)
         self.planes = z(T, 2 * H, dtype=bf)
         kb = H // 128
         self.front_ksplit = next(k for k in (4, 2, 1) if kb % k == 0)     # K split of the GDN front projection (few row tiles)
-        self.pre = z(T * max(self.front_ksplit * spec.gdn_front_rows, spec.attn_front_rows))
+        self.pre = z(P * T * max(self.front_ksplit * spec.gdn_front_rows, spec.attn_front_rows))
+        self.pre_sum = z(T, spec.attn_front_rows) if P > 1 else None
         self.ctl_tab = z(self.n_sub, CTL_WORDS, dtype=i32)
         self.gdn_qkv, self.gdn_z = z(T, spec.gdn_qkv_rows), z(T, spec.gdn_local)
         self.gdn_beta, self.gdn_g, self.gdn_out = z(T, spec.gdn_v), z(T, spec.gdn_v), z(T, spec.gdn_local)
@@ -100,7 +109,7 @@ class WidePrefill:
         self.attn_ticket = z(self.n_sub, spec.kv_heads, dtype=i32)
         self.side = [torch.cuda.Stream(dev) for _ in range(self.n_sub)]
         kmax = max(spec.gdn_local, spec.attn_local)
-        self.oq, self.os = torch.zeros(T * kmax, dtype=FP8, device=dev), z(T * (kmax // 128))
+        self.oq, self.os = torch.zeros(P * T * kmax, dtype=FP8, device=dev), z(P * T * (kmax // 128))
         self.S, self.n_total = cfg.top_k + 1, cfg.n_experts + 1
         self.rows_pad = eng.moes[0].rows_pad
         kb64 = H // 64
@@ -112,11 +121,11 @@ class WidePrefill:
         # K split of the gate/up product: 1 (two half-length CTAs per tile fill the last wave better but write and re-read a
         # second 34 MB plane: measured 4 % slower per chunk at 64 rows)
         self.up_ksplit = 1
-        self.gu = z(self.up_ksplit, T, self.n_total * 2 * I)
-        self.hq, self.hs = torch.zeros(T, self.n_total * I, dtype=FP8, device=dev), z(T, self.n_total * I // 128)
+        self.gu = z(self.up_ksplit, P * T, self.n_total * 2 * I)
+        self.hq, self.hs = torch.zeros(P * T, self.n_total * I, dtype=FP8, device=dev), z(P * T, self.n_total * I // 128)
         # K split of the expert down product: at most 64 K blocks per CTA, and about two CTAs per SM over the grid
-        self.down_ksplit = down_split(self.n_total * I // 128, (H // 128) * ((T + 63) // 64), c.n_cta)
-        self.y = z(max(self.down_ksplit, 1), T, H)
+        self.down_ksplit = down_split(self.n_total * I // 128, (H // 128) * ((P * T + 63) // 64), c.n_cta)
+        self.y = z(max(self.down_ksplit, 1), P * T, H)
         # tensor parallel: the chunk's partial sums are all-reduced inside the residual kernel over a symmetric inbox of its
         # own (8 bytes per value of the chunk and half: data vectors, then one flag word per CTA); it shares the engine's
         # sequence word and status, so its tags never collide with the decode steps' and a failure stops both
@@ -135,9 +144,10 @@ class WidePrefill:
 
     # ---- one chunk ---------------------------------------------------------------------------------------------
     def _finish(self, ksplit: int) -> None:
-        """x += (all-reduced) sum of the projection's K-split planes."""
+        """x += (all-reduced) sum of the projection's K-split planes, each of which holds one row block per activation term."""
         c, lib, st = self.eng.ctx, self.eng.ctx.lib, self.eng.ctx.stream()
         n = self.T * self.eng.cfg.hidden
+        ksplit *= self.P
         if self.channel is None:
             check(lib.nexrt_planes_residual(ptr(self.x), ptr(self.y), None, n, ksplit, st), "planes_residual")
             return
@@ -149,19 +159,20 @@ class WidePrefill:
         c, lib, cfg, spec = eng.ctx, eng.ctx.lib, eng.cfg, eng.spec
         st, w, H = c.stream(), m.w, cfg.hidden
         R, C, nv, K = spec.gdn_front_rows, spec.gdn_qkv_rows, spec.gdn_v, spec.gdn_local
-        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), ptr(self.xn), None, H, T, cfg.rms_eps, st), "norm_rows")
+        P = self.P
+        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), ptr(self.xn), None, H, T, cfg.rms_eps, P, st), "norm_rows")
         ks = self.front_ksplit
-        pre = self.pre[: ks * T * R]
+        pre = self.pre[: ks * P * T * R]         # [ks][P][T][R]: ks * P planes of T rows for the chunk kernel
         fp8_gemm_split(w["front_w"], w["front_s"], self.xq, self.sx, pre, ksplit=ks, status=c.status)
         # conv ring + gates and the delta rule for all T rows: two kernels, the state carried in registers along the chunk
         check(
             lib.nexrt_gdn_chunk(ptr(pre), ptr(self.xn), ptr(w["ba_w_pad"]), ptr(w["conv_w"]), ptr(w["a_log"]), ptr(w["dt_bias"]), ptr(self.ctl_tab[0]),
                                 ptr(m.conv_ring), ptr(self.gdn_qkv), ptr(self.gdn_z), ptr(self.gdn_beta), ptr(self.gdn_g), ptr(m.state_ring), ptr(self.gdn_out),
-                                H, R, C, nv, spec.gdn_qk, T, m.conv_ring_len, m.state_ring_len, ks, st),
+                                H, R, C, nv, spec.gdn_qk, T, m.conv_ring_len, m.state_ring_len, ks * P, st),
             "gdn_chunk",
         )
-        oq, os_ = self.oq[: T * K].view(T, K), self.os[: T * (K // 128)].view(T, K // 128)
-        check(lib.nexrt_gdn_gate_quant(ptr(self.gdn_out), ptr(self.gdn_z), ptr(w["gnorm_w"]), ptr(oq), ptr(os_), K, T, cfg.rms_eps, st), "gdn_gate_quant")
+        oq, os_ = self.oq[: P * T * K].view(P * T, K), self.os[: P * T * (K // 128)].view(P * T, K // 128)
+        check(lib.nexrt_gdn_gate_quant(ptr(self.gdn_out), ptr(self.gdn_z), ptr(w["gnorm_w"]), ptr(oq), ptr(os_), K, T, cfg.rms_eps, P, st), "gdn_gate_quant")
         fp8_gemm(w["out_w"], w["out_s"], oq, os_, out=self.y[0], status=c.status)
         self._finish(1)
 
@@ -171,9 +182,13 @@ class WidePrefill:
         st, w, H, hd = c.stream(), m.w, cfg.hidden, cfg.head_dim
         nq, kvh, K = spec.q_heads, spec.kv_heads, spec.attn_local
         R = spec.attn_front_rows
-        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), None, None, H, T, cfg.rms_eps, st), "norm_rows")
-        pre = self.pre[: T * R].view(T, R)
+        P = self.P
+        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["in_ln"]), ptr(self.xq), ptr(self.sx), None, None, H, T, cfg.rms_eps, P, st), "norm_rows")
+        pre = self.pre[: P * T * R].view(P * T, R)
         fp8_gemm(w["front_w"], w["front_s"], self.xq, self.sx, out=pre, status=c.status)
+        if P > 1:                               # the scatter kernels below read one plane: add the terms' row blocks first
+            check(lib.nexrt_planes_residual(None, ptr(pre), ptr(self.pre_sum), T * R, P, st), "planes_sum")
+            pre = self.pre_sum
         rope = c.rope_table(m.cache_len)
         base = self.ctl_tab[0]
         # q / gate / k rows to scratch and v rows to the cache for the whole chunk, then the chunk's k rows (norm + RoPE) to
@@ -197,8 +212,8 @@ class WidePrefill:
                 )
         for j in range(self.n_sub):
             cur.wait_stream(self.side[j])
-        oq, os_ = self.oq[: T * K].view(T, K), self.os[: T * (K // 128)].view(T, K // 128)
-        check(lib.nexrt_act_quant(ptr(self.attn_out), 1, K, None, cfg.rms_eps, ptr(oq), ptr(os_), T, K, st), "act_quant")
+        oq, os_ = self.oq[: P * T * K].view(P * T, K), self.os[: P * T * (K // 128)].view(P * T, K // 128)
+        check(lib.nexrt_act_quant(ptr(self.attn_out), 1, K, None, cfg.rms_eps, ptr(oq), ptr(os_), T, K, P, st), "act_quant")
         fp8_gemm(w["out_w"], w["out_s"], oq, os_, out=self.y[0], status=c.status)
         self._finish(1)
 
@@ -206,7 +221,8 @@ class WidePrefill:
         eng, T = self.eng, self.T
         c, lib, cfg, spec = eng.ctx, eng.ctx.lib, eng.cfg, eng.spec
         st, w, H, I, S, n_total = c.stream(), moe.w, cfg.hidden, spec.inter, self.S, self.n_total
-        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["post_ln"]), ptr(self.xq), ptr(self.sx), None, ptr(self.planes), H, T, cfg.rms_eps, st), "norm_rows")
+        P = self.P
+        check(lib.nexrt_norm_rows(ptr(self.x), ptr(w["post_ln"]), ptr(self.xq), ptr(self.sx), None, ptr(self.planes), H, T, cfg.rms_eps, P, st), "norm_rows")
         # router: bf16 weights, activations as hi + lo bf16 planes, each product split over K; the top-k kernel adds the
         # 2 * ksplit partial planes in a fixed order (one CTA per eight rows)
         ks = self.router_ksplit
@@ -221,7 +237,8 @@ class WidePrefill:
                        status=c.status)
         self.hq.view(torch.uint8).zero_()
         self.hs.zero_()
-        check(lib.nexrt_moe_dense_act(ptr(self.gu), ptr(self.moe_ids), ptr(self.moe_wts), ptr(self.hq), ptr(self.hs), I, S, T, n_total, self.up_ksplit, st), "moe_dense_act")
+        check(lib.nexrt_moe_dense_act(ptr(self.gu), ptr(self.moe_ids), ptr(self.moe_wts), ptr(self.hq), ptr(self.hs), I, S, T, n_total, self.up_ksplit * P, P, st),
+              "moe_dense_act")
         fp8_gemm_split(w["w2"].view(n_total * H, I), w["w2_s"], self.hq, self.hs, self.y, ksplit=self.down_ksplit, group_k=I, group_rows=H, used=self.used, status=c.status)
         self._finish(self.down_ksplit)
 

@@ -93,6 +93,7 @@ def main(argv=None) -> int:
     ap.add_argument("--tp", type=int, default=8)
     ap.add_argument("--length", type=int, default=1024)
     ap.add_argument("--wide", default="64", help="comma list of wide chunk sizes to time (the 8-row path is always timed)")
+    ap.add_argument("--terms", default="1", help="comma list of activation term counts of the wide path (1 = one e4m3 plane, 3 = the exact split)")
     ap.add_argument("--shrunk", action="store_true")
     ap.add_argument("--no-rows", action="store_true", help="skip the 8-row path")
     ap.add_argument("--stages", type=int, default=0, help="chunk size whose stages are timed by leaving one out at a time")
@@ -143,10 +144,11 @@ def main(argv=None) -> int:
         return float(ms.item())
 
     out = {"layers": cfg.n_layers, "tp_shapes": a.tp, "ranks": world, "length": a.length, "paths": {}}
-    cases = ([] if a.no_rows else [0]) + [int(w) for w in a.wide.split(",") if w]
-    for wide in cases:
+    cases = ([] if a.no_rows else [(0, 1)]) + [(int(w), int(t)) for t in a.terms.split(",") if t for w in a.wide.split(",") if w]
+    for wide, terms in cases:
+        eng.wide_terms = terms
         ms = timed(wide)
-        name = "rows8" if wide == 0 else f"wide{wide}"
+        name = "rows8" if wide == 0 else (f"wide{wide}" if terms == 1 else f"wide{wide}x{terms}")
         out["paths"][name] = {"ms": round(ms, 2), "tok_s": round(a.length / ms * 1e3, 1), "us_per_layer_per_token": round(ms * 1e3 / a.length / cfg.n_layers, 2)}
     out["status"] = eng.status_max()
     if rank == 0:

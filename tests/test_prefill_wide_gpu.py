@@ -96,7 +96,7 @@ def test_glue_kernels_against_pytorch():
     gamma = 1.0 + 0.1 * torch.randn(K, device="cuda", generator=g)
     xq, sx = torch.zeros(T, K, dtype=FP8, device="cuda"), torch.zeros(T, K // 128, device="cuda")
     xn, planes = torch.zeros(T, K, device="cuda"), torch.zeros(T, 2 * K, dtype=torch.bfloat16, device="cuda")
-    check(lib.nexrt_norm_rows(ptr(x), ptr(gamma), ptr(xq), ptr(sx), ptr(xn), ptr(planes), K, T, 1e-6, _stream()), "norm_rows")
+    check(lib.nexrt_norm_rows(ptr(x), ptr(gamma), ptr(xq), ptr(sx), ptr(xn), ptr(planes), K, T, 1e-6, 1, _stream()), "norm_rows")
     xf = x.float()
     want = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * gamma
     assert rel(xn, want) < 1e-5
@@ -105,7 +105,7 @@ def test_glue_kernels_against_pytorch():
     # GDN output gate
     o, z = torch.randn(T, K, device="cuda", generator=g), torch.randn(T, K, device="cuda", generator=g)
     gw = 1.0 + 0.1 * torch.randn(128, device="cuda", generator=g)
-    check(lib.nexrt_gdn_gate_quant(ptr(o), ptr(z), ptr(gw), ptr(xq), ptr(sx), K, T, 1e-6, _stream()), "gdn_gate_quant")
+    check(lib.nexrt_gdn_gate_quant(ptr(o), ptr(z), ptr(gw), ptr(xq), ptr(sx), K, T, 1e-6, 1, _stream()), "gdn_gate_quant")
     oh = o.reshape(T, K // 128, 128)
     want = (oh * torch.rsqrt((oh * oh).mean(-1, keepdim=True) + 1e-6) * gw).reshape(T, K) * torch.nn.functional.silu(z)
     assert rel(_deq_act(xq, sx), want) < 0.04
@@ -121,7 +121,7 @@ def test_glue_kernels_against_pytorch():
     ids = torch.stack([torch.randperm(n_total, device="cuda", generator=g)[:S] for _ in range(T)]).to(torch.int32)
     wts = torch.rand(T, S, device="cuda", generator=g)
     hq, hs = torch.zeros(T, n_total * I, dtype=FP8, device="cuda"), torch.zeros(T, n_total * I // 128, device="cuda")
-    check(lib.nexrt_moe_dense_act(ptr(gu), ptr(ids), ptr(wts), ptr(hq), ptr(hs), I, S, T, n_total, 1, _stream()), "moe_dense_act")
+    check(lib.nexrt_moe_dense_act(ptr(gu), ptr(ids), ptr(wts), ptr(hq), ptr(hs), I, S, T, n_total, 1, 1, _stream()), "moe_dense_act")
     want = torch.zeros(T, n_total, I, device="cuda")
     gv = gu.reshape(T, n_total, 2, I)
     for t in range(T):
@@ -133,13 +133,83 @@ def test_glue_kernels_against_pytorch():
     assert int((hs != 0).sum()) == T * S
 
 
+def _sum_terms(xq, sx, terms):
+    """Dequantised value of an activation written as ``terms`` row blocks."""
+    T = xq.shape[0] // terms
+    return sum(_deq_act(xq[p * T : (p + 1) * T], sx[p * T : (p + 1) * T]) for p in range(terms))
+
+
+@pytest.mark.parametrize("terms,tol", [(1, 0.04), (2, 3e-3), (3, 2e-4)])
+def test_quantisers_write_the_exact_split_as_row_blocks(terms, tol):
+    """Every quantiser of the wide path with 1, 2 and 3 e4m3 terms: the row blocks add up to the fp32 value to 2^-4, 2^-8,
+    2^-12 per element, and block p's scales are block 0's divided by 16^p."""
+    lib = load()
+    g = torch.Generator(device="cuda").manual_seed(11 + terms)
+    T, K = 24, 512
+    x = (torch.randn(T, K, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    gamma = 1.0 + 0.1 * torch.randn(K, device="cuda", generator=g)
+    xf = x.float()
+    want = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * gamma
+    xq, sx = torch.zeros(terms * T, K, dtype=FP8, device="cuda"), torch.zeros(terms * T, K // 128, device="cuda")
+    check(lib.nexrt_norm_rows(ptr(x), ptr(gamma), ptr(xq), ptr(sx), None, None, K, T, 1e-6, terms, _stream()), "norm_rows")
+    assert rel(_sum_terms(xq, sx, terms), want) < tol
+    for p in range(1, terms):
+        assert torch.allclose(sx[p * T : (p + 1) * T] * 16.0 ** p, sx[:T], rtol=1e-6)
+    # the stand-alone quantiser (attention output rows), with and without its norm
+    q2, s2 = act_quant(x, gamma, 1e-6, terms=terms)
+    assert rel(_sum_terms(q2, s2, terms), want) < tol
+    q3, s3 = act_quant(want, terms=terms)
+    assert rel(_sum_terms(q3, s3, terms), want) < tol
+    # GDN output gate
+    o, z = torch.randn(T, K, device="cuda", generator=g), torch.randn(T, K, device="cuda", generator=g)
+    gw = 1.0 + 0.1 * torch.randn(128, device="cuda", generator=g)
+    xq.view(torch.uint8).zero_()
+    check(lib.nexrt_gdn_gate_quant(ptr(o), ptr(z), ptr(gw), ptr(xq), ptr(sx), K, T, 1e-6, terms, _stream()), "gdn_gate_quant")
+    oh = o.reshape(T, K // 128, 128)
+    want = (oh * torch.rsqrt((oh * oh).mean(-1, keepdim=True) + 1e-6) * gw).reshape(T, K) * torch.nn.functional.silu(z)
+    assert rel(_sum_terms(xq, sx, terms), want) < tol
+    # dense expert activation from K-split x term planes of the gate/up product
+    I, S, n_total, ks = 128, 3, 7, 2
+    gu = torch.randn(ks * terms, T, n_total * 2 * I, device="cuda", generator=g)
+    ids = torch.stack([torch.randperm(n_total, device="cuda", generator=g)[:S] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, S, device="cuda", generator=g)
+    hq, hs = torch.zeros(terms * T, n_total * I, dtype=FP8, device="cuda"), torch.zeros(terms * T, n_total * I // 128, device="cuda")
+    check(lib.nexrt_moe_dense_act(ptr(gu), ptr(ids), ptr(wts), ptr(hq), ptr(hs), I, S, T, n_total, ks * terms, terms, _stream()), "moe_dense_act")
+    gv = gu.sum(0).reshape(T, n_total, 2, I)
+    want = torch.zeros(T, n_total, I, device="cuda")
+    for t in range(T):
+        for s in range(S):
+            e = int(ids[t, s])
+            want[t, e] = torch.nn.functional.silu(gv[t, e, 0]) * gv[t, e, 1] * wts[t, s]
+    torch.cuda.synchronize()
+    assert rel(_sum_terms(hq, hs, terms), want.reshape(T, -1)) < tol
+    assert int((hs != 0).sum()) == terms * T * S
+
+
+@pytest.mark.parametrize("T,R,K", [(16, 256, 1024), (64, 384, 4096)])
+def test_three_term_rows_make_the_fp8_product_exact_in_the_activation(T, R, K):
+    """One GEMM over 3 T token rows, row blocks added: the product with the UNQUANTISED activation to 1e-3 (the weights are
+    FP8 on both sides of the comparison)."""
+    g = torch.Generator(device="cuda").manual_seed(K + T)
+    wq, sw = quantize_blockwise(torch.randn(R, K, device="cuda", generator=g) * 0.05)
+    x = torch.randn(T, K, device="cuda", generator=g) * 2
+    xq, sx = act_quant(x, terms=3)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((2, 3 * T, R), float("nan"), device="cuda")
+    fp8_gemm_split(wq, sw, xq, sx, out, ksplit=2, status=status)
+    torch.cuda.synchronize()
+    want = x.double() @ dequantize_blockwise(wq, sw).double().T
+    got = out.reshape(2 * 3, T, R).sum(0)
+    assert int(status.item()) == 0 and rel(got, want) < 1e-3
+
+
 from nexrt_b200.testing import oracle_state as _oracle_state  # noqa: E402
 
 
 @pytest.mark.parametrize("length,wide", [(53, 16), (150, 64)])
 def test_wide_prefill_matches_the_oracle_with_the_same_arithmetic(length, wide):
-    """The wide path rounds the input of every FP8 projection to one e4m3 plane; ``RefModel(fp8_activations=True)`` does the
-    same on the CPU.  Against THAT oracle the state the wide prefill leaves (GDN state and conv history, every K/V row) is
+    """With one activation term the wide path rounds the input of every FP8 projection to one e4m3 plane;
+    ``RefModel(fp8_activations=True)`` does the same on the CPU.  Against THAT oracle the state the wide prefill leaves (GDN state and conv history, every K/V row) is
     held to the tolerance of the step kernels, so a lost block of the chunk all-reduce, a wrong row of one attention
     sub-step or a mis-masked expert cannot pass.  The prompt is the one whose oracle run stays furthest from routing
     near ties (a tie broken the other way is a property of random weights, not of the kernels)."""
@@ -151,6 +221,7 @@ def test_wide_prefill_matches_the_oracle_with_the_same_arithmetic(length, wide):
     logits = ref.prefill(prompt)
     want = _oracle_state(ref)
     eng = make_engine(cfg, ckpt, max_rows=8)
+    eng.wide_terms = 1
     first = eng.prefill(prompt, chunk=8, wide=wide)
     assert eng.status_max() == 0
     got = eng.export_state()
@@ -183,6 +254,7 @@ def test_wide_prefill_stays_close_to_the_exact_row_steps(length, wide):
     prompt = synthetic_prompt(cfg.vocab, length, seed=5)
     eng.prefill(prompt, chunk=8, wide=0)
     ref = eng.export_state()
+    eng.wide_terms = 1
     eng.prefill(prompt, chunk=8, wide=wide)
     assert eng.status_max() == 0
     got = eng.export_state()
@@ -190,3 +262,39 @@ def test_wide_prefill_stays_close_to_the_exact_row_steps(length, wide):
         for key, want in st.items():
             if key != "kind":
                 assert rel(got["layers"][idx][key].float(), want.float()) < 0.3, (idx, key)
+
+
+@pytest.mark.parametrize("length,wide,terms", [(53, 16, 3), (150, 64, 3), (150, 64, 2)])
+def test_wide_prefill_with_split_activations_matches_the_exact_oracle(length, wide, terms):
+    """With the step kernels' activation split written as extra token rows of every FP8 product, the wide path is held to
+    the EXACT fp32 oracle at the step kernels' tolerance, and to the 8-row path (the same arithmetic in another order)."""
+    from nexrt_b200.models.reference import RefModel, robust_prompt
+
+    cfg, ckpt = shrunk_checkpoint(0)
+    ref = RefModel(cfg, ckpt)
+    prompt, margin = robust_prompt(ref, cfg.vocab, length, seeds=range(1, 9))
+    logits = ref.prefill(prompt)
+    want = _oracle_state(ref)
+    eng = make_engine(cfg, ckpt, max_rows=8)
+    eng.prefill(prompt, chunk=8, wide=0)
+    rows = eng.export_state()
+    eng.wide_terms = terms
+    first = eng.prefill(prompt, chunk=8, wide=wide)
+    assert eng.status_max() == 0 and eng.wide_path(wide).P == terms
+    got = eng.export_state()
+    assert got["L"] == length
+    tol = 2e-2 if terms == 3 else 3e-2
+    for idx, st in want.items():
+        for key, w in st.items():
+            have = got["layers"][idx][key].float().cpu()
+            assert rel(have, w.float()) < tol, (idx, key, rel(have, w.float()), margin)
+            assert rel(have, rows["layers"][idx][key].float().cpu()) < tol, (idx, key)
+            if key in ("k_cache", "v_cache"):
+                per_pos = (have - w.float()).norm(dim=-1) / w.float().norm(dim=-1).clamp_min(1e-6)
+                if terms == 3:
+                    assert float(per_pos.max()) < 5e-2, (idx, key, int(per_pos.argmax()), float(per_pos.max()))
+                else:   # 2^-8 per activation is enough to turn a routing near tie at a position or two of the prompt
+                    assert float((per_pos > 5e-2).float().mean()) < 0.02 and float(per_pos.median()) < 1e-2, (idx, key, float(per_pos.max()))
+    top = int(logits.argmax())
+    assert first == top or float(logits.max() - logits[first]) < 0.05
+    assert eng.prefill(prompt, chunk=8, wide=wide) == first and eng.status_max() == 0

@@ -85,27 +85,43 @@ def main():
     long_prompt = synthetic_prompt(cfg.vocab, 53, seed=9)
     eng.prefill(long_prompt, chunk=8, wide=0)
     want_state = eng.export_state()
-    first_w = eng.prefill(long_prompt, chunk=8, wide=16)
+    first_w = eng.prefill(long_prompt, chunk=8, wide=16)          # default: the exact three-term activation split
     got_state = eng.export_state()
-    assert eng.status_max() == 0 and got_state["L"] == 53
+    assert eng.status_max() == 0 and got_state["L"] == 53 and eng.wide_path(16).P == 3
     for idx, st in want_state["layers"].items():
         for key, w_ in st.items():
             if key != "kind":
-                assert rel_l2(got_state["layers"][idx][key].float(), w_.float()) < 0.3, (idx, key)
+                # an order of magnitude under a lost row or block; a routing near tie of this arbitrary prompt may still turn
+                assert rel_l2(got_state["layers"][idx][key].float(), w_.float()) < 0.1, (idx, key, rel_l2(got_state["layers"][idx][key].float(), w_.float()))
     t = torch.tensor([first_w], device=dev)
     allt = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(allt, t)
     assert all(torch.equal(allt[0], u) for u in allt), allt
     assert len(eng.generate(max_new=4)) == 4 and eng.status_max() == 0
 
-    # the same wide path against the CPU oracle with the SAME arithmetic (one e4m3 plane per FP8 projection input), held to
-    # the tolerance of the step kernels on this rank's shard of every layer's state: a lost block of the chunk all-reduce,
-    # a wrong row of an attention sub-step or a mis-masked expert shows as an error of order one
+    # the wide path with the exact activation split against the exact CPU oracle at the tolerance of the step kernels, on a
+    # prompt that stays clear of routing near ties
+    xprompt, _ = robust_prompt(ref, cfg.vocab, 53, seeds=range(1, 9))
+    ref.reset()
+    ref.prefill(xprompt)
+    want_x = shard_oracle_state(oracle_state(ref), cfg, eng.spec)
+    eng.prefill(xprompt, chunk=8, wide=16)
+    got_x = eng.export_state()
+    assert eng.status_max() == 0 and got_x["L"] == 53
+    for idx, st in want_x.items():
+        for key, w_ in st.items():
+            have = got_x["layers"][idx][key].float().cpu()
+            assert rel_l2(have, w_.float()) < 2e-2, ("wide, three terms, vs exact oracle", idx, key, rel_l2(have, w_.float()))
+
+    # the wide path with ONE activation term against the CPU oracle with the SAME arithmetic (one e4m3 plane per FP8
+    # projection input), held to the tolerance of the step kernels on this rank's shard of every layer's state: a lost block
+    # of the chunk all-reduce, a wrong row of an attention sub-step or a mis-masked expert shows as an error of order one
     ref8 = RefModel(cfg, ckpt, fp8_activations=True)
     wprompt, _ = robust_prompt(ref8, cfg.vocab, 53, seeds=range(1, 9))
     ref8.reset()
     ref8.prefill(wprompt)
     want_w = shard_oracle_state(oracle_state(ref8), cfg, eng.spec)
+    eng.wide_terms = 1
     eng.prefill(wprompt, chunk=8, wide=16)
     got_w = eng.export_state()
     assert eng.status_max() == 0 and got_w["L"] == 53
