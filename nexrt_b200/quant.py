@@ -66,6 +66,33 @@ def act_quant(x: torch.Tensor):
     return q.reshape(rows, K), scale.reshape(rows, K // BLOCK).contiguous()
 
 
+def act_quant_terms(x: torch.Tensor, terms: int = 3):
+    """The wide prefill path's activation split, in the layout and the arithmetic of its quantiser kernels
+    (``csrc/prefill.cu: quant_block4``, ``csrc/tc_gemm.cu: act_quant_kernel``).
+
+    ``x [rows, K]`` -> (``q`` fp8 ``[terms * rows, K]``, ``scale [terms * rows, K/128]``): row block 0 is
+    ``e4m3(x / s)`` with ``s = max(amax, 1e-12) / 448`` per row and 128 columns; row block ``p`` is the e4m3 rounding of what
+    the blocks before it left over, at the scale ``s / 16^p`` (the residual is multiplied by 16 before it is rounded, so that
+    every term uses e4m3's normal range).  ``sum_p q_p * s_p`` equals ``x`` to 2^-4, 2^-8, 2^-12 of each value for 1, 2, 3
+    terms, and a GEMM over all ``terms * rows`` rows followed by the sum of its row blocks multiplies by that sum.
+    """
+    if terms not in (1, 2, 3):
+        raise ValueError("terms must be 1, 2 or 3")
+    rows, K = x.shape
+    if K % BLOCK:
+        raise ValueError("activation width must be a multiple of 128")
+    blocks = x.float().reshape(rows, K // BLOCK, BLOCK)
+    scale = blocks.abs().amax(-1, keepdim=True).clamp_min(1e-12) / FP8_MAX
+    r = blocks * (1.0 / scale)
+    qs, ss = [], []
+    for p in range(terms):
+        q = r.clamp(-FP8_MAX, FP8_MAX).to(FP8)
+        qs.append(q.reshape(rows, K))
+        ss.append((scale / 16.0 ** p).reshape(rows, K // BLOCK))
+        r = (r - q.float()) * 16.0
+    return torch.cat(qs), torch.cat(ss).contiguous()
+
+
 def act_quant_dequant(x: torch.Tensor) -> torch.Tensor:
     q, s = act_quant(x)
     return (q.float().reshape(x.shape[0], -1, BLOCK) * s[..., None]).reshape(x.shape)

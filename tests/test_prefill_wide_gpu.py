@@ -160,6 +160,13 @@ def test_quantisers_write_the_exact_split_as_row_blocks(terms, tol):
     assert rel(_sum_terms(q2, s2, terms), want) < tol
     q3, s3 = act_quant(want, terms=terms)
     assert rel(_sum_terms(q3, s3, terms), want) < tol
+    # ... and it is the arithmetic that quant.act_quant_terms states on the CPU: the same bytes, up to the last bit of a
+    # scale (the two divisions need not round alike), which may move a value that sits on a rounding boundary
+    from nexrt_b200.quant import act_quant_terms
+
+    qc, sc = act_quant_terms(want.cpu(), terms)
+    assert torch.allclose(s3.cpu(), sc, rtol=3e-7, atol=0)
+    assert float((q3.cpu().view(torch.uint8) != qc.view(torch.uint8)).float().mean()) < 2e-3
     # GDN output gate
     o, z = torch.randn(T, K, device="cuda", generator=g), torch.randn(T, K, device="cuda", generator=g)
     gw = 1.0 + 0.1 * torch.randn(128, device="cuda", generator=g)

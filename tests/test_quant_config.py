@@ -141,3 +141,28 @@ def test_wide_prefill_covers_every_tensor_parallel_degree_of_the_full_model():
             assert supported(eng), (cfg.name, tp)
     # the sequential parts run eight rows at a time on the step kernels' rings: an engine built for fewer rows is out
     assert not supported(SimpleNamespace(cfg=full_config(), spec=ShardSpec(full_config(), 8, 0), max_rows=4))
+
+
+def test_activation_split_terms_add_up():
+    """CPU statement of the wide prefill's quantisers: one, two and three e4m3 terms reproduce the value to 2^-4, 2^-8 and
+    2^-12 per element, each term's scale is the first one's divided by 16^p, and one term is the plain quantiser."""
+    from nexrt_b200.quant import act_quant_terms
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(6, 384, generator=g) * torch.logspace(-3, 2, 6)[:, None]
+    x[2, 128:256] = 0.0                                   # an all-zero block keeps a finite scale and zero terms
+    deq = lambda q, s, terms: sum(
+        (q[p * 6 : (p + 1) * 6].float().reshape(6, -1, 128) * s[p * 6 : (p + 1) * 6, :, None]).reshape(6, -1) for p in range(terms))
+    q1, s1 = act_quant_terms(x, 1)
+    q0, s0 = act_quant(x)
+    assert torch.equal(s1[x.abs().reshape(6, 3, 128).amax(-1) > 0], s0[x.abs().reshape(6, 3, 128).amax(-1) > 0])
+    for terms, bound in ((1, 2.0 ** -4), (2, 2.0 ** -8), (3, 2.0 ** -12)):
+        q, s = act_quant_terms(x, terms)
+        assert q.shape == (terms * 6, 384) and s.shape == (terms * 6, 3)
+        err = (deq(q, s, terms) - x).abs()
+        # relative to each value, except below e4m3's subnormal step of the LAST term's scale
+        floor = (s[(terms - 1) * 6 :, :, None] * 2.0 ** -10).expand(6, 3, 128).reshape(6, -1)
+        assert bool((err <= bound * x.abs() + floor).all()), (terms, float((err / x.abs().clamp_min(1e-30)).max()))
+        for p in range(1, terms):
+            assert torch.equal(s[p * 6 : (p + 1) * 6] * 16.0 ** p, s[:6])
+    assert bool((deq(*act_quant_terms(x, 3), 3)[2, 128:256] == 0).all())
