@@ -166,7 +166,9 @@ __global__ void __launch_bounds__(256) planes_residual_kernel(__nv_bfloat16* x, 
 // its flag word of each peer region (bounded like every LL wait, status latched on expiry), then adds the world's
 // vectors in rank order: every rank gets the same bits.  Region layout: n floats of data, then one u32 flag per CTA.
 // Halves alternate with the global call sequence as in ll.cuh: a peer can publish call k + 2 into a half only after this
-// rank has left the kernel of call k.
+// rank has left the kernel of call k.  CTA b waits for CTA b of every peer, so progress needs the CTAs of a call to be
+// resident together or dispatched in the same order on every rank: the grid is n / 1024 <= 1024 CTAs, dispatched in
+// index order (parallel/ll_model.py: BlockModel states the protocol on CPU threads, tests/test_ll_protocol_model.py).
 __device__ __forceinline__ void st_sys_v4(float* p, const float4& v) {
     asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }

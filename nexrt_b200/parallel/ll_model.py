@@ -119,3 +119,77 @@ class LLModel:
         if errors:
             raise errors[0]
         return out  # type: ignore[return-value]
+
+
+class BlockModel(LLModel):
+    """Host model of the block protocol of the wide prefill's all-reduce (``csrc/prefill.cu:
+    planes_allreduce_residual_kernel``) over the same inbox, sequence word and status as the packet protocol.
+
+    A region ``[half][src]`` holds ``ctas * width`` data values followed by one flag word per CTA.  CTA ``b`` of a rank
+    stores its ``width`` values untagged into region ``[half][own rank]`` of every peer, then the call's tag into flag
+    ``b`` of that region (the device orders the two with a system fence and a barrier; here the flag is simply written
+    last); it polls flag ``b`` of every peer region of its own inbox and only then reads that region's values.  Data
+    carries no tag, so nothing but the ordering of calls keeps a region from being overwritten before it was read:
+
+    * the CTAs of one call of one rank may run in any order and side by side, but call ``k + 1`` of a rank starts only
+      after ALL its CTAs of call ``k`` have finished (stream order; programmatic launches wait for the whole grid);
+    * CTA ``b`` of call ``k + 1`` finishes only once it saw every peer's flag ``b`` of call ``k + 1``, so a rank that is
+      through call ``k + 1`` proves every peer through call ``k``; its stores of call ``k + 2`` (the same half as ``k``)
+      then land in regions nobody reads any more.
+
+    Because CTA ``b`` waits for CTA ``b`` of every peer, the CTAs of a call must either all be resident or be dispatched
+    in the same (index) order on every rank; both hold on the device (grids of at most 1024 CTAs, dispatched in order).
+
+    ``stale_data`` counts values a CTA read that were not the ones its peer wrote for the awaited call (the payload of
+    the model encodes (call, rank, cta, lane), which the device's data does not need to)."""
+
+    def __init__(self, world: int, ctas: int, width: int, budget_s: float = 2.0, silent: Sequence[int] = ()):
+        super().__init__(world, ctas * width + ctas, budget_s, silent)
+        self.ctas, self.width = ctas, width
+        self.stale_data = [0] * world
+
+    def cta(self, me: RankState, site: int, b: int, own: List[float], expect: Optional[Callable[[int], List[float]]] = None) -> List[float]:
+        """One CTA of one call: returns the rank-ordered sums of its ``width`` values (missing peers count as zero)."""
+        tag, half = self.begin(me, site)
+        lo, flag = b * self.width, self.ctas * self.width + b
+        if me.rank not in self.silent:
+            for peer in self.ranks:
+                if peer.rank != me.rank:
+                    region = peer.inbox[half][me.rank]
+                    for j, v in enumerate(own):
+                        region[lo + j] = (0, v)                  # plain data: no tag travels with it
+                    region[flag] = (tag, 0.0)                    # published after the data
+        total = [0.0] * self.width
+        for src in range(self.world):
+            if src == me.rank:
+                vals: Optional[List[float]] = own
+            elif self.wait(me, tag, half, src, flag) is None:
+                vals = None
+            else:
+                vals = [me.inbox[half][src][lo + j][1] for j in range(self.width)]
+                if expect is not None and vals != expect(src):
+                    self.stale_data[me.rank] += 1
+            if vals is not None:
+                total = [t + v for t, v in zip(total, vals)]
+        return total
+
+    def call(self, me: RankState, site: int, own_of: Callable[[int], List[float]], expect_of=None, order: Optional[Sequence[int]] = None,
+             parallel: bool = False) -> List[List[float]]:
+        """All CTAs of one call of rank ``me``: in ``order`` one after the other, or side by side on threads; the call
+        returns when every CTA has finished (the kernel boundary)."""
+        order = list(range(self.ctas)) if order is None else list(order)
+        out: List[Optional[List[float]]] = [None] * self.ctas
+
+        def one(b: int) -> None:
+            out[b] = self.cta(me, site, b, own_of(b), None if expect_of is None else (lambda src: expect_of(src, b)))
+
+        if parallel:
+            ts = [threading.Thread(target=one, args=(b,), daemon=True) for b in order]
+            for t in ts:
+                t.start()
+            for t in ts:
+                t.join(60)
+        else:
+            for b in order:
+                one(b)
+        return out  # type: ignore[return-value]

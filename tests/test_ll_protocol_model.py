@@ -136,3 +136,96 @@ def test_zeroed_inbox_never_matches_and_stale_packets_are_never_consumed():
     me.inbox[half][1][0] = (old_tag, 99.0)
     assert model.wait(me, tag, half, 1, 0) is None
     assert me.stale_reads > 0 and me.status == STATUS_REDUCE_TIMEOUT
+
+
+# ---- block protocol of the wide prefill's all-reduce (csrc/prefill.cu: planes_allreduce_residual_kernel) --------------
+from nexrt_b200.parallel.ll_model import BlockModel  # noqa: E402
+
+
+def _block_value(call, rank, cta, lane):
+    return float(((call * 8 + rank) * 64 + cta) * 16 + lane)
+
+
+@pytest.mark.parametrize("world,parallel", [(2, False), (4, True), (8, False)])
+def test_block_protocol_never_reads_data_of_another_call(world, parallel):
+    """Untagged data vectors + one tagged flag per CTA: over a mix of graphs with different site counts, CTAs of a call
+    side by side in a random start order (a resident grid) or one after the other in index order (a grid larger than the
+    machine, dispatched in order), ranks at different speeds: every CTA reads exactly what its peers wrote for that
+    call, and all ranks get the same sums."""
+    import random
+
+    ctas, width = 5, 3
+    graphs = [2, 3, 1, 3, 2, 2]
+
+    def program(model, me):
+        rng = random.Random(me.rank * 7 + 1)
+        results, call = [], 0
+        for n_sites in graphs:
+            for site in range(n_sites):
+                me._sleep()
+                order = list(range(ctas))
+                if parallel:
+                    rng.shuffle(order)
+                c = call
+                sums = model.call(me, site, lambda b: [_block_value(c, me.rank, b, j) for j in range(width)],
+                                  lambda src, b: [_block_value(c, src, b, j) for j in range(width)], order=order, parallel=parallel)
+                results.append(sums)
+                call += 1
+            model.end_graph(me, n_sites)
+        return results
+
+    model = BlockModel(world, ctas, width, budget_s=20.0)
+    out = model.run(program, jitter_s=0.0005, seed=world)
+    assert all(r.status == STATUS_OK for r in model.ranks) and model.stale_data == [0] * world
+    assert all(o == out[0] for o in out)
+    call = 0
+    for sums in out[0]:
+        for b in range(ctas):
+            assert sums[b] == [sum(_block_value(call, r, b, j) for r in range(world)) for j in range(width)]
+        call += 1
+
+
+def test_block_protocol_breaks_without_the_kernel_boundary():
+    """The model is sharp enough to show why the boundary matters: if a rank starts the next-but-one call (same half)
+    before a peer's CTA has read the data of the current one, that CTA reads the wrong call's values."""
+    model = BlockModel(2, 1, 2, budget_s=5.0)
+    a, b = model.ranks
+    val = lambda call, rank: [_block_value(call, rank, 0, j) for j in range(2)]
+    # rank 1 publishes call 0 and - ignoring every wait - call 2 (site 2: the same half) before rank 0 has run call 0
+    for site in (0, 2):
+        tag, half = model.begin(b, site)
+        for j, v in enumerate(val(site, 1)):
+            a.inbox[half][1][j] = (0, v)
+        if site == 0:
+            a.inbox[half][1][2] = (tag, 0.0)
+    got = model.cta(a, 0, 0, val(0, 0), expect=lambda src: val(0, src))
+    assert model.stale_data[0] == 1 and got != [x + y for x, y in zip(val(0, 0), val(0, 1))]
+
+
+def test_block_protocol_needs_resident_or_in_order_ctas():
+    """CTA b waits for CTA b of every peer.  If the CTAs of a call ran one at a time in DIFFERENT orders on two ranks,
+    each rank would sit in a CTA whose partner has not started: the waits run out.  The device never does that (a grid
+    is dispatched in index order and the launcher's grids fit the machine); the model shows what the kernel relies on."""
+    model = BlockModel(2, 2, 1, budget_s=0.3)
+
+    def program(m, me):
+        out = m.call(me, 0, lambda b: [1.0], order=[0, 1] if me.rank == 0 else [1, 0])
+        m.end_graph(me, 1)
+        return out
+
+    model.run(program)
+    # the rank whose wait runs out first moves on and publishes what the other one is waiting for
+    assert any(r.status == STATUS_REDUCE_TIMEOUT for r in model.ranks)
+
+
+def test_block_protocol_silent_peer_times_out_and_counts_as_zero():
+    model = BlockModel(2, 2, 2, budget_s=0.2, silent=(1,))
+
+    def program(m, me):
+        out = m.call(me, 0, lambda b: [1.0 + me.rank, 2.0])
+        m.end_graph(me, 1)
+        return out
+
+    out = model.run(program)
+    assert model.ranks[0].status == STATUS_REDUCE_TIMEOUT and out[0] == [[1.0, 2.0], [1.0, 2.0]]
+    assert model.ranks[1].status == STATUS_OK and out[1] == [[3.0, 4.0], [3.0, 4.0]]
