@@ -540,10 +540,13 @@ def main(argv=None) -> int:
     p.add_argument("--no-listen", action="store_true", help="exit after the queued work")
     p.add_argument("--wide-prefill", type=int, default=int(os.environ.get("NEXRT_WIDE_PREFILL", "0") or 0),
                    help="rows per wide prefill chunk (16..128, a multiple of 8; every decode mode); 0 = 8-row steps")
+    p.add_argument("--wide-terms", type=int, choices=(1, 2, 3), default=int(os.environ.get("NEXRT_WIDE_TERMS", "3") or 3),
+                   help="e4m3 terms per activation of the wide prefill: 3 = the decode kernels' exact split, 1 = one plane (faster, FP8-rounded)")
     args = p.parse_args(argv)
     if args.wide_prefill and (args.wide_prefill % 8 or not 16 <= args.wide_prefill <= 128):
         p.error("--wide-prefill must be 0 or a multiple of 8 between 16 and 128")
     os.environ["NEXRT_WIDE_PREFILL"] = str(args.wide_prefill)      # read by DecodeEngine.prefill
+    os.environ["NEXRT_WIDE_TERMS"] = str(args.wide_terms)          # read by DecodeEngine.wide_path
     import torch
     import torch.distributed as dist
 
