@@ -95,6 +95,40 @@ def test_forced_commit_and_seeded_schedule(setup):
     eng.set_forced_commit(0)
 
 
+def test_m4_verify_view_drives_the_same_step(setup):
+    """``M4Verify`` (the reference's verifier API, m4_verify.py:155-1227) is a view of the engine: load + run verify four
+    rows, accept the true continuation, and the forced-commit property and schedule reach the control block."""
+    from nexrt_b200.m4_verify import M4Verify, M4VerifyCp
+
+    cfg, ref, eng, mtp = setup
+    prompt, _ = robust_prompt(ref, cfg.vocab, 24, n_new=6, seeds=range(1, 17))
+    toks_ref, _ = ref.greedy(prompt, 6)
+    first = eng.prefill(prompt, chunk=8)
+    v = M4Verify(eng)
+    assert v.eng is eng and first == toks_ref[0]
+    v.load(toks_ref[0:4])
+    v.run(end=True, begin=True)
+    ctl = eng.read_ctl()
+    assert ctl["status"] == 0 and 1 <= ctl["commit_count"] <= 4
+    assert ctl["emitted"][: ctl["commit_count"]] == toks_ref[1 : 1 + ctl["commit_count"]]
+    assert ctl["committed_len"] == len(prompt) + ctl["commit_count"]
+    before = ctl["committed_len"]
+    v.forced_commit = 2
+    assert v.forced_commit == 2
+    v.run(end=True, begin=True)
+    ctl = eng.read_ctl()
+    assert ctl["commit_count"] == 2 and ctl["committed_len"] == before + 2
+    v.set_forced_schedule(seed=7, mean_accept=3.0)
+    counts = []
+    for _ in range(20):
+        v.run(end=True, begin=True)
+        counts.append(eng.read_ctl()["commit_count"])
+    assert all(1 <= c <= 4 for c in counts) and 2.0 <= sum(counts) / len(counts) <= 4.0
+    v.forced_commit = 0
+    with pytest.raises(ValueError):
+        M4VerifyCp(eng)                  # a single-rank engine has no context-parallel arm
+
+
 def test_upstream_status_fails_closed(setup):
     cfg, ref, eng, mtp = setup
     eng.prefill(synthetic_prompt(cfg.vocab, 16, seed=15), chunk=8)
