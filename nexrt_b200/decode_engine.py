@@ -28,6 +28,7 @@ from .moe import Moe
 from .ops.lib import check, ptr
 from .runtime.context import StepContext
 from .runtime.control import CTL_WORDS, Ctl, decode_ctl
+from .runtime.rounds import Stops, stop_set
 
 # Context length from which generate() switches to the context-parallel graph.  The reference crosses over at 48K on
 # H100 (decode_engine.py:63-66).  On 8 x B200 (groups of four ranks per kv head, full model) the context-parallel arm
@@ -269,7 +270,7 @@ class DecodeEngine:
         g_noncp=None,
         g_cp=None,
         max_new: int = 16,
-        eos: Optional[int] = None,
+        eos: Stops = None,
         cp_threshold: Optional[int] = None,
         on_tokens: Optional[Callable[[List[int]], None]] = None,
         host_inputs: Optional[torch.Tensor] = None,
@@ -278,8 +279,10 @@ class DecodeEngine:
 
         Step k+1 is queued before step k's token is read from the host mirror, so the GPU never
         idles on the host; EOS is therefore learned one step late and the extra replay is simply
-        not reported (reference decode_engine.py:326-399).  A token of -1 means a failed step.
+        not reported (reference decode_engine.py:326-399).  ``eos`` is one stop token id or any
+        iterable of them.  A token of -1 means a failed step.
         """
+        stops = stop_set(eos)
         if cp_threshold is None:
             cp_threshold = self.cp_threshold
         g_noncp = g_noncp or self.capture(1, cp=False)
@@ -311,7 +314,7 @@ class DecodeEngine:
             out.append(tok)
             if on_tokens:
                 on_tokens([tok])
-            if eos is not None and tok == eos:
+            if tok in stops:
                 for gen in pending:
                     self.mirror.wait(gen)
                 break

@@ -9,7 +9,7 @@ import torch
 from ..runtime.capture import graph_capture
 import torch.distributed as dist
 
-from ..runtime.control import Ctl
+from ..runtime.rounds import Stops, consume_rounds
 from .block import M8, DFlashBlock
 
 
@@ -40,44 +40,7 @@ def capture_request(block: DFlashBlock, cp: bool = False, warmup: int = 3):
     return g
 
 
-def generate_dflash(block: DFlashBlock, graph=None, max_new: int = 16, eos: Optional[int] = None,
+def generate_dflash(block: DFlashBlock, graph=None, max_new: int = 16, eos: Stops = None,
                     on_tokens: Optional[Callable[[List[int]], None]] = None, stats: Optional[dict] = None) -> List[int]:
-    eng = block.eng
-    graph = graph or capture_request(block)
-    eng.mirror.resync()
-    out: List[int] = []
-    budget = eng._kv_budget() - 2 * M8
-    rounds = accepted = 0
-    pending = [_launch(eng, graph)]
-    while pending:
-        if len(pending) < 2 and len(out) + len(pending) < max_new:
-            pending.append(_launch(eng, graph))
-        words = eng.mirror.wait(pending.pop(0))
-        if words[Ctl.STATUS] != 0 or words[Ctl.COMMIT_COUNT] <= 0:
-            for gen in pending:
-                eng.mirror.wait(gen)
-            raise RuntimeError(f"DFlash round failed: status {words[Ctl.STATUS]}")
-        n = words[Ctl.COMMIT_COUNT]
-        toks = words[Ctl.EMITTED : Ctl.EMITTED + n]
-        rounds += 1
-        accepted += n
-        stop = False
-        for t in toks:
-            out.append(t)
-            if (eos is not None and t == eos) or len(out) >= max_new:
-                stop = True
-                break
-        if on_tokens:
-            on_tokens(toks)
-        if stop or words[Ctl.COMMITTED_LEN] >= budget:
-            for gen in pending:
-                eng.mirror.wait(gen)
-            break
-    if stats is not None:
-        stats.update(rounds=rounds, accept_mean=accepted / max(rounds, 1))
-    return out[:max_new]
-
-
-def _launch(eng, graph) -> int:
-    graph.replay()
-    return eng.mirror.next_gen()
+    """Decode up to ``max_new`` tokens by replaying the request's round graph (``eos``: a stop token id or several)."""
+    return consume_rounds(block.eng, graph or capture_request(block), max_new, eos, on_tokens, stats, reserve=2 * M8, what="DFlash round")

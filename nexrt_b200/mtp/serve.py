@@ -14,7 +14,7 @@ import torch
 from ..runtime.capture import graph_capture
 import torch.distributed as dist
 
-from ..runtime.control import Ctl
+from ..runtime.rounds import Stops, consume_rounds
 from .block import M_VERIFY, MtpDraft
 
 
@@ -45,47 +45,9 @@ def capture_round(mtp: MtpDraft, cp: bool = False, warmup: int = 3):
     return g
 
 
-def generate_mtp(mtp: MtpDraft, graph=None, max_new: int = 16, eos: Optional[int] = None,
+def generate_mtp(mtp: MtpDraft, graph=None, max_new: int = 16, eos: Stops = None,
                  on_tokens: Optional[Callable[[List[int]], None]] = None, stats: Optional[dict] = None) -> List[int]:
     """Decode up to ``max_new`` tokens by replaying the round graph.  Returns the emitted tokens
     (the sequence is exactly what plain greedy / sampled decode would emit: drafts only decide how
-    many tokens a round commits).  ``stats`` receives ``rounds`` and ``accept_mean``."""
-    eng = mtp.eng
-    graph = graph or capture_round(mtp)
-    eng.mirror.resync()
-    out: List[int] = []
-    budget = eng._kv_budget() - 2 * M_VERIFY
-    rounds, accepted = 0, 0
-    pending = [_launch(eng, graph)]
-    while pending:
-        if len(pending) < 2 and len(out) + len(pending) < max_new:   # every round commits at least one token
-            pending.append(_launch(eng, graph))
-        words = eng.mirror.wait(pending.pop(0))
-        if words[Ctl.STATUS] != 0 or words[Ctl.COMMIT_COUNT] <= 0:
-            for gen in pending:
-                eng.mirror.wait(gen)
-            raise RuntimeError(f"MTP round failed: status {words[Ctl.STATUS]}")
-        n = words[Ctl.COMMIT_COUNT]
-        toks = words[Ctl.EMITTED : Ctl.EMITTED + n]
-        rounds += 1
-        accepted += n
-        stop = False
-        for t in toks:
-            out.append(t)
-            if (eos is not None and t == eos) or len(out) >= max_new:
-                stop = True
-                break
-        if on_tokens:
-            on_tokens(toks[: len(toks) if not stop else None])
-        if stop or words[Ctl.COMMITTED_LEN] >= budget:
-            for gen in pending:
-                eng.mirror.wait(gen)
-            break
-    if stats is not None:
-        stats.update(rounds=rounds, accept_mean=accepted / max(rounds, 1))
-    return out[:max_new]
-
-
-def _launch(eng, graph) -> int:
-    graph.replay()
-    return eng.mirror.next_gen()
+    many tokens a round commits).  ``eos``: a stop token id or several; ``stats`` receives ``rounds`` and ``accept_mean``."""
+    return consume_rounds(mtp.eng, graph or capture_round(mtp), max_new, eos, on_tokens, stats, reserve=2 * M_VERIFY, what="MTP round")

@@ -28,7 +28,7 @@ import socket
 import sys
 import time
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 from ..sampling import DEFAULT_SAMPLING, checked_sampling_config, resolve_sampling_config
 from .bridge import PrefillSession, chunked_prefill
@@ -68,6 +68,45 @@ def load_tokenizer(path: Optional[str]):
     from transformers import AutoTokenizer
 
     return AutoTokenizer.from_pretrained(path)
+
+
+# ---- stop tokens --------------------------------------------------------------------------------------------
+# a turn also ends where the model opens a tool call: the client, not the server, continues from there
+TOOL_CALL_OPENERS = ("<tool_call>", "<|tool_call_begin|>", "<|tool_calls_begin|>", "<function_call>", "<|action_start|>")
+
+
+def resolve_stop_ids(tokenizer, model_dir: Optional[str] = None, openers: Sequence[str] = TOOL_CALL_OPENERS) -> Tuple[int, ...]:
+    """Every token id that ends a generation, sorted: the tokenizer's ``eos_token_id`` (one id or a list), the
+    ``eos_token_id`` of ``generation_config.json`` in ``model_dir`` (one id, a list, null or no file), and the ids of the
+    tool-call opener strings the tokenizer knows as single tokens (an id equal to ``unk_token_id``, negative or missing
+    means it does not).  Same sources as the reference's server (sglang_prefill/bridge_serve.py:140-165)."""
+    def as_ids(value) -> List[int]:
+        if value is None or isinstance(value, bool):
+            return []
+        if isinstance(value, int):
+            return [value]
+        return [int(v) for v in value if v is not None and not isinstance(v, bool)]
+
+    ids = set(as_ids(getattr(tokenizer, "eos_token_id", None)))
+    if model_dir:
+        path = os.path.join(model_dir, "generation_config.json")
+        if os.path.isfile(path):
+            try:
+                with open(path, "r", encoding="utf-8") as fh:
+                    ids.update(as_ids(json.load(fh).get("eos_token_id")))
+            except (OSError, ValueError, AttributeError, TypeError):
+                pass        # an unreadable generation config adds no stop ids; the tokenizer's still hold
+    convert = getattr(tokenizer, "convert_tokens_to_ids", None)
+    unk = getattr(tokenizer, "unk_token_id", None)
+    if callable(convert):
+        for text in openers:
+            try:
+                tid = convert(text)
+            except Exception:  # noqa: BLE001 - tokenizers differ in what they raise for an unknown string
+                tid = None
+            if isinstance(tid, int) and not isinstance(tid, bool) and tid >= 0 and tid != unk:
+                ids.add(tid)
+    return tuple(sorted(i for i in ids if i >= 0))
 
 
 # ---- request validation -------------------------------------------------------------------------------
@@ -147,7 +186,7 @@ class EngineBackend:
         return self.boundary()
 
     def decode(self, max_new: int, eos_ids, on_tokens) -> Dict:
-        eos = next(iter(eos_ids), None) if eos_ids else None
+        eos = tuple(eos_ids or ())          # every stop id ends the request, not only the first
         stats: Dict = {}
         if self.mode == "mtp":
             from ..mtp import generate_mtp
@@ -199,15 +238,14 @@ class BridgeServer:
 
     def __init__(self, backend, tokenizer, rank: int = 0, world: int = 1, control_group=None, mode: str = "bs1",
                  report_path: Optional[str] = None, gather: Optional[Callable] = None, log: Callable[[str], None] = print,
-                 consensus_fault_rank: Optional[int] = None, verify: bool = False):
+                 consensus_fault_rank: Optional[int] = None, verify: bool = False, model_dir: Optional[str] = None):
         self.backend, self.tok, self.rank, self.world, self.group, self.mode = backend, tokenizer, rank, world, control_group, mode
         self.state = ServerState(CachedSession(backend.capacity, backend.model_epoch))
         self.report_path = report_path or os.environ.get("NEXRT_SERVE_REPORT")
         self.report: List[Dict] = []
         self._gather = gather or (lambda rec: all_gather_records(rec, group=self.group))
         self.log = log if rank == 0 else (lambda *_: None)
-        eos = getattr(tokenizer, "eos_token_id", None)
-        self.stop_ids = tuple(i for i in ([eos] if isinstance(eos, int) else (eos or [])) if i is not None)
+        self.stop_ids = resolve_stop_ids(tokenizer, model_dir)
         # test-only host-side fault injection: this rank reports its READY boundary as lost on the next reuse,
         # which must turn the request into a collective PREFILL on every rank
         self.consensus_fault_rank = consensus_fault_rank
@@ -559,7 +597,8 @@ def main(argv=None) -> int:
         ctl_group = dist.new_group(backend="gloo")
     backend = build_backend(args, rank, world, dev, None)
     server = BridgeServer(backend, load_tokenizer(args.tokenizer), rank, world, ctl_group, args.mode,
-                          consensus_fault_rank=args.cache_consensus_fault_rank, verify=args.verify)
+                          consensus_fault_rank=args.cache_consensus_fault_rank, verify=args.verify,
+                          model_dir=args.tokenizer if args.tokenizer and os.path.isdir(args.tokenizer) else None)
     queue = queued_requests(args, backend.vocab)
     if queue:
         server.run_queue(queue)
