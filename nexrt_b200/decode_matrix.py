@@ -90,7 +90,7 @@ def main(argv=None) -> int:
     from .decode_engine import DecodeEngine
     from .sampling import GREEDY
     from .serve.process_supervisor import launch_geometry
-    from .weights import load_checkpoint, random_rank_model, shard_model
+    from .weights import load_rank_model, random_rank_model
 
     rank, world, local = launch_geometry()
     torch.cuda.set_device(local)
@@ -99,7 +99,7 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=dev)
     lengths = [int(x) for x in a.lengths.split(",") if x]
     cfg = full_config().truncated(a.layers)
-    model = (shard_model(load_checkpoint(cfg, a.layers_dir), cfg, world, rank, dev, cp=a.cp) if a.layers_dir
+    model = (load_rank_model(cfg, a.layers_dir, world, rank, dev, cp=a.cp) if a.layers_dir
              else random_rank_model(cfg, world, rank, dev))
     eng = DecodeEngine(rank, world, dev, cp=a.cp, ext=model, cfg=cfg, max_rows=8, cache_len=max(lengths) + a.reps * (a.trials + 1) + a.warmup + 1024)
     eng.head.set_sampling_config(0, *GREEDY)

@@ -76,3 +76,50 @@ def load_dflash_shard(ckpt: Dict[str, torch.Tensor], dc: DFlashConfig, tp: int, 
         "fc": d(ckpt["fc.weight"][:, rank * win : (rank + 1) * win]),
         "hidden_ln": g1(ckpt["hidden_norm.weight"]), "final_ln": g1(ckpt["norm.weight"]),
     }
+
+
+def expected_shapes(dc: DFlashConfig) -> Dict[str, tuple]:
+    """Every tensor of a DFlash draft checkpoint with the shape the kernels' geometry requires."""
+    H, hd = dc.hidden, dc.head_dim
+    out = {"fc.weight": (H, dc.n_taps * H), "hidden_norm.weight": (H,), "norm.weight": (H,)}
+    for l in range(dc.n_layers):
+        p = f"layers.{l}."
+        out.update({
+            p + "input_layernorm.weight": (H,), p + "post_attention_layernorm.weight": (H,),
+            p + "self_attn.q_proj.weight": (dc.n_q_heads * hd, H), p + "self_attn.k_proj.weight": (dc.n_kv_heads * hd, H),
+            p + "self_attn.v_proj.weight": (dc.n_kv_heads * hd, H), p + "self_attn.o_proj.weight": (H, dc.n_q_heads * hd),
+            p + "self_attn.q_norm.weight": (hd,), p + "self_attn.k_norm.weight": (hd,),
+            p + "mlp.gate_proj.weight": (dc.mlp_inter, H), p + "mlp.up_proj.weight": (dc.mlp_inter, H),
+            p + "mlp.down_proj.weight": (H, dc.mlp_inter),
+        })
+    return out
+
+
+def check_dflash_checkpoint(ckpt, dc: DFlashConfig) -> None:
+    """The draft geometry is fixed: a checkpoint with a missing tensor or another shape is refused before anything is
+    copied (reference ``_require_shape`` at boot, dflash/weights.py:117-142).  ``ckpt`` is a dict of tensors or a
+    ``weights.TensorFiles`` mapping, whose shapes come from the file header."""
+    shape_of = ckpt.shape if hasattr(ckpt, "shape") and callable(ckpt.shape) else (lambda k: tuple(ckpt[k].shape))
+    problems = []
+    for key, want in expected_shapes(dc).items():
+        if key not in ckpt:
+            problems.append(f"{key}: missing")
+        elif tuple(shape_of(key)) != want:
+            problems.append(f"{key}: shape {tuple(shape_of(key))}, expected {want}")
+    if problems:
+        more = f" (+{len(problems) - 6} more)" if len(problems) > 6 else ""
+        raise ValueError("DFlash checkpoint does not match the draft geometry: " + "; ".join(problems[:6]) + more)
+
+
+def load_dflash_files(dc: DFlashConfig, tp: int, rank: int, device, weights_path=None) -> Dict:
+    """This rank's shard straight from the draft's ``model.safetensors`` (default: ``NEXRT_DFLASH_WEIGHTS`` /
+    ``NEXRT_DFLASH_DIR``), one tensor on the host at a time, after the geometry check."""
+    from ..weights import TensorFiles
+    from .config import DFLASH_WEIGHTS
+
+    files = TensorFiles([weights_path or DFLASH_WEIGHTS], prefault=False)
+    try:
+        check_dflash_checkpoint(files, dc)
+        return load_dflash_shard(files, dc, tp, rank, device)
+    finally:
+        files.close()

@@ -41,7 +41,11 @@ def random_mtp_checkpoint(cfg: ModelConfig, seed: int = 7, device="cpu") -> Dict
 
 def shard_mtp(ckpt: Dict[str, torch.Tensor], cfg: ModelConfig, tp: int, rank: int, device, target_head: Dict) -> Dict:
     """Kernel-layout MTP tensors of one rank.  ``target_head`` is the target's ``head`` dict (shared
-    embedding, LM head shard and final norm)."""
+    embedding, LM head shard and final norm): the draft owns no copy of them, so they must still be resident
+    (reference mtp/weights.py: the draft reuses the target's head and refuses a released one)."""
+    missing = [k for k in ("embed", "lm_head", "final_ln") if not isinstance((target_head or {}).get(k), torch.Tensor)]
+    if missing:
+        raise ValueError(f"the MTP draft shares the target's head tensors, which are not resident: {missing}")
     spec = ShardSpec(cfg, tp, rank)
     H = cfg.hidden
     win = 2 * H // tp
@@ -59,3 +63,20 @@ def shard_mtp(ckpt: Dict[str, torch.Tensor], cfg: ModelConfig, tp: int, rank: in
         "moe": shard_moe(ckpt, cfg, 0, spec, device, base=MTP_BASE),
         "head": {"final_ln": d(_gamma(ckpt["mtp.norm.weight"])), "lm_head": target_head["lm_head"], "embed": target_head["embed"]},
     }
+
+
+def load_mtp_files(cfg: ModelConfig, layers_dir, tp: int, rank: int, device, target_head: Dict) -> Dict:
+    """This rank's MTP tensors straight from ``mtp.safetensors`` of a layer directory, one tensor on the host at a time.
+    Nothing of the target is read again: the embedding, the LM head shard and the final norm are the resident ones."""
+    from pathlib import Path
+
+    from ..weights import TensorFiles
+
+    path = Path(layers_dir) / "mtp.safetensors"
+    if not path.is_file():
+        raise FileNotFoundError(f"{path}: the layer directory holds no MTP weights")
+    files = TensorFiles([path], prefault=False)
+    try:
+        return shard_mtp(files, cfg, tp, rank, device, target_head)
+    finally:
+        files.close()

@@ -501,13 +501,13 @@ def build_backend(args, rank: int, world: int, dev, group):
     """Random-init (or checkpoint) model, engine and speculative block for this rank."""
     from ..config import full_config
     from ..decode_engine import DecodeEngine
-    from ..weights import load_checkpoint, random_rank_model, shard_model
+    from ..weights import load_rank_model, random_rank_model
 
     cfg = full_config()
     if args.layers and args.layers < cfg.n_layers:
         cfg = cfg.truncated(args.layers)
     if args.layers_dir:
-        model = shard_model(load_checkpoint(cfg, args.layers_dir), cfg, world, rank, dev, cp=args.cp)
+        model = load_rank_model(cfg, args.layers_dir, world, rank, dev, cp=args.cp)      # streams the directory: one tensor on the host at a time
         epoch = f"ckpt:{os.path.abspath(args.layers_dir)}"
     else:
         model = random_rank_model(cfg, world, rank, dev, seed=args.seed)
@@ -516,21 +516,35 @@ def build_backend(args, rank: int, world: int, dev, group):
     block = None
     if args.mode == "mtp":
         from ..mtp import MtpDraft
-        from ..mtp.weights import random_mtp_checkpoint, shard_mtp
+        from ..mtp.weights import load_mtp_files, random_mtp_checkpoint, shard_mtp
 
-        block = MtpDraft(eng, shard_mtp(random_mtp_checkpoint(cfg, seed=args.seed + 7, device=dev), cfg, world, rank, dev, model["head"]))
+        if args.layers_dir and os.path.isfile(os.path.join(args.layers_dir, "mtp.safetensors")):
+            draft = load_mtp_files(cfg, args.layers_dir, world, rank, dev, model["head"])
+            epoch += "+mtp"
+        else:                               # no draft weights: a random draft still yields the target's stream, at acceptance ~1
+            draft = shard_mtp(random_mtp_checkpoint(cfg, seed=args.seed + 7, device=dev), cfg, world, rank, dev, model["head"])
+            epoch += f"+mtp-random:{args.seed + 7}"
+        block = MtpDraft(eng, draft)
     elif args.mode == "dflash":
         from dataclasses import replace
 
         from ..dflash import DFlashBlock, DFlashConfig
-        from ..dflash.weights import load_dflash_shard, random_dflash_checkpoint
+        from ..dflash.config import DFLASH_CONFIG, DFLASH_WEIGHTS
+        from ..dflash.weights import load_dflash_files, load_dflash_shard, random_dflash_checkpoint
 
-        dc = DFlashConfig()
+        real = DFLASH_CONFIG.is_file() and DFLASH_WEIGHTS.is_file()       # NEXRT_DFLASH_DIR / _CONFIG / _WEIGHTS
+        dc = DFlashConfig.from_json(DFLASH_CONFIG) if real else DFlashConfig()
         if cfg.n_layers <= max(dc.target_layer_ids):      # truncated stack: tap the layers that exist
             step = max(cfg.n_layers // dc.n_taps, 1)
             dc = replace(dc, target_layer_ids=tuple(min(i * step, cfg.n_layers - 1) for i in range(dc.n_taps)))
         dc.validate_kernel_contract(cfg, world)
-        block = DFlashBlock(eng, dc, load_dflash_shard(random_dflash_checkpoint(dc, seed=args.seed + 11, device=dev), dc, world, rank, dev))
+        if real:
+            draft = load_dflash_files(dc, world, rank, dev, DFLASH_WEIGHTS)
+            epoch += f"+dflash:{DFLASH_WEIGHTS}"
+        else:
+            draft = load_dflash_shard(random_dflash_checkpoint(dc, seed=args.seed + 11, device=dev), dc, world, rank, dev)
+            epoch += f"+dflash-random:{args.seed + 11}"
+        block = DFlashBlock(eng, dc, draft)
     return EngineBackend(eng, args.mode, block, model_epoch=epoch)
 
 

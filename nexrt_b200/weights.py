@@ -23,7 +23,7 @@ kernels, so no weight is re-quantised at load (the reference folds them into the
 from __future__ import annotations
 
 from pathlib import Path
-from typing import Dict, Optional
+from typing import Dict, Mapping, Optional
 
 import torch
 
@@ -145,6 +145,128 @@ def load_checkpoint(cfg: ModelConfig, layers_dir, device="cpu") -> Dict[str, tor
             for k in f.keys():
                 out[k] = f.get_tensor(k)
     return out
+
+
+def prefault_file(path) -> int:
+    """Read ``path`` once, front to back, so that the page cache holds it when the loader maps it (a cold 7 GB layer file
+    otherwise faults in 4 KB at a time under the tensor copies).  Strictly read-only: the file is opened ``O_RDONLY``,
+    nothing is written beside it, and its times are left alone where the platform allows (``O_NOATIME`` when permitted).
+    Returns the number of bytes read.  The reference warms checkpoint files the same way before SGLang maps them
+    (``sglang_prefill/weight_loading.py``: ``_prefault_checkpoint_file``)."""
+    import os
+
+    flags = os.O_RDONLY | getattr(os, "O_CLOEXEC", 0)
+    try:
+        fd = os.open(str(path), flags | getattr(os, "O_NOATIME", 0))
+    except PermissionError:          # O_NOATIME needs ownership of the file
+        fd = os.open(str(path), flags)
+    total = 0
+    try:
+        if hasattr(os, "posix_fadvise"):
+            os.posix_fadvise(fd, 0, 0, os.POSIX_FADV_SEQUENTIAL)
+        while True:
+            chunk = os.read(fd, 16 << 20)
+            if not chunk:
+                break
+            total += len(chunk)
+    finally:
+        os.close(fd)
+    return total
+
+
+class TensorFiles(Mapping):
+    """A list of safetensors files as a read-only mapping ``key -> tensor`` that never holds more than one tensor on the host.
+
+    The files' headers are indexed at construction (names only, no data); a tensor is read when it is asked for and no
+    reference to it is kept; the file that was read last stays open, and while it is in use a background thread warms the
+    page cache with the next file of the list (``prefault=True``).  ``shape(key)`` answers from the header alone."""
+
+    def __init__(self, paths, device="cpu", prefault: bool = True):
+        from safetensors import safe_open
+
+        self.files = [Path(p) for p in paths]
+        self.device, self.prefault = str(device), prefault
+        self.index: Dict[str, int] = {}
+        for i, path in enumerate(self.files):
+            with safe_open(str(path), framework="pt", device="cpu") as f:
+                for k in f.keys():
+                    self.index[k] = i
+        self._open_idx, self._open, self._ctx = -1, None, None
+        self._warm = None                   # thread warming the page cache with file self._warmed
+        self._warmed = -1
+        self.reads = 0                      # tensors read so far
+
+    # ---- Mapping ----
+    def __len__(self) -> int:
+        return len(self.index)
+
+    def __iter__(self):
+        return iter(self.index)
+
+    def __contains__(self, key) -> bool:
+        return key in self.index
+
+    def __getitem__(self, key: str) -> torch.Tensor:
+        self._use(self.index[key])          # KeyError for an unknown name, like a dict
+        self.reads += 1
+        return self._open.get_tensor(key)
+
+    def shape(self, key: str):
+        """Shape of ``key`` from its file's header (no tensor data is read)."""
+        self._use(self.index[key])
+        return tuple(self._open.get_slice(key).get_shape())
+
+    # ---- files ----
+    def _use(self, i: int) -> None:
+        if i == self._open_idx:
+            return
+        from safetensors import safe_open
+
+        self.close()
+        if self._warm is not None and self._warmed == i:
+            self._warm.join()               # the file being opened is the one being warmed: let the read finish
+        self._ctx = safe_open(str(self.files[i]), framework="pt", device=self.device)
+        self._open = self._ctx.__enter__()
+        self._open_idx = i
+        nxt = i + 1
+        if self.prefault and nxt < len(self.files) and nxt > self._warmed:
+            import threading
+
+            self._warmed = nxt
+            self._warm = threading.Thread(target=prefault_file, args=(self.files[nxt],), daemon=True)
+            self._warm.start()
+
+    def close(self) -> None:
+        if self._ctx is not None:
+            self._ctx.__exit__(None, None, None)
+        self._ctx, self._open, self._open_idx = None, None, -1
+
+
+class LayerFiles(TensorFiles):
+    """A layer directory (``embed_tokens``, ``norm``, ``lm_head``, ``layer.{L}``, optionally ``mtp``) as one mapping.
+
+    ``load_checkpoint`` materialises every file of the directory in one dict, which for the full model is the whole
+    checkpoint in host memory on every rank.  The sharding functions only ever ask for one key at a time (and for
+    ``keys()`` when a scale goes by either of its two names), so ``shard_model(LayerFiles(cfg, dir), ...)`` streams the
+    directory once, in file order, with a host footprint of one tensor and the next layer's file warming behind it
+    (reference: per-layer files read one layer at a time, ``weights.py:166-199``)."""
+
+    def __init__(self, cfg: ModelConfig, layers_dir, device="cpu", prefault: bool = True):
+        root = Path(layers_dir)
+        names = ["embed_tokens", "norm", "lm_head"] + [f"layer.{l}" for l in range(cfg.n_layers)]
+        if (root / "mtp.safetensors").is_file():
+            names.append("mtp")
+        super().__init__([root / f"{n}.safetensors" for n in names], device=device, prefault=prefault)
+        self.dir = root
+
+
+def load_rank_model(cfg: ModelConfig, layers_dir, tp: int, rank: int, device, cp: bool = False, prefault: bool = True) -> Dict:
+    """One rank's kernel-layout tensors straight from a layer directory, one tensor on the host at a time."""
+    files = LayerFiles(cfg, layers_dir, prefault=prefault)
+    try:
+        return shard_model(files, cfg, tp, rank, device, cp=cp)
+    finally:
+        files.close()
 
 
 def normalise_scale_names(ckpt: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:

@@ -166,3 +166,98 @@ def test_activation_split_terms_add_up():
         for p in range(1, terms):
             assert torch.equal(s[p * 6 : (p + 1) * 6] * 16.0 ** p, s[:6])
     assert bool((deq(*act_quant_terms(x, 3), 3)[2, 128:256] == 0).all())
+
+
+def _flat(x, prefix=""):
+    if isinstance(x, dict):
+        for k, v in x.items():
+            yield from _flat(v, f"{prefix}.{k}")
+    elif isinstance(x, (list, tuple)):
+        for i, v in enumerate(x):
+            yield from _flat(v, f"{prefix}.{i}")
+    elif isinstance(x, torch.Tensor):
+        yield prefix, x
+
+
+def _same(a, b):
+    fa, fb = dict(_flat(a)), dict(_flat(b))
+    assert fa.keys() == fb.keys()
+    for k in fa:
+        x, y = fa[k], fb[k]
+        assert x.dtype == y.dtype and x.shape == y.shape, k
+        assert torch.equal(x.view(torch.uint8) if x.element_size() == 1 else x, y.view(torch.uint8) if y.element_size() == 1 else y), k
+
+
+def test_streaming_loader_equals_the_eager_one_and_reads_each_tensor_once(tmp_path):
+    """``LayerFiles`` is the layer directory as a lazy mapping: sharding from it gives the eager loader's tensors bit for
+    bit (both scale names), no tensor is read twice, shapes come from the header, unknown names raise ``KeyError``."""
+    from nexrt_b200.weights import LayerFiles, load_rank_model
+
+    cfg = shrunk_config()
+    ck = random_checkpoint(cfg, 3)
+    ck = {(k[: -len("_inv")] if k.endswith("weight_scale_inv") and ".layers.1." in k else k): v for k, v in ck.items()}   # one layer under the other name
+    save_checkpoint(ck, cfg, tmp_path)
+    eager = shard_model(load_checkpoint(cfg, tmp_path), cfg, 2, 1, "cpu", cp=True)
+    _same(load_rank_model(cfg, tmp_path, 2, 1, "cpu", cp=True), eager)
+    files = LayerFiles(cfg, tmp_path, prefault=False)
+    assert len(files) == len(ck) and set(files) == set(ck)
+    key = "model.language_model.embed_tokens.weight"
+    assert files.shape(key) == tuple(ck[key].shape) and files.reads == 0
+    shard_model(files, cfg, 2, 0, "cpu")
+    assert 0 < files.reads <= len(ck)                    # every tensor at most once per rank
+    with pytest.raises(KeyError):
+        files["model.language_model.layers.99.input_layernorm.weight"]
+    files.close()
+
+
+def test_prefault_reads_the_file_and_leaves_it_alone(tmp_path):
+    """Warming the page cache is read-only (reference tests/test_weight_loading.py: test_prefault_preserves_checkpoint)."""
+    from nexrt_b200.weights import prefault_file
+
+    path = tmp_path / "weights.safetensors"
+    contents = b"original checkpoint" * ((20 << 20) // 19 + 1)
+    path.write_bytes(contents)
+    before = path.stat()
+    assert prefault_file(path) == len(contents)
+    assert path.read_bytes() == contents and path.stat().st_mtime_ns == before.st_mtime_ns and path.stat().st_size == before.st_size
+    assert list(tmp_path.iterdir()) == [path]
+
+
+def test_draft_loaders_read_files_and_check_geometry(tmp_path):
+    """MTP weights come from ``mtp.safetensors`` of the layer directory and share the target's resident head; the DFlash
+    draft comes from its own ``model.safetensors`` after a shape check of every tensor against the fixed geometry
+    (reference tests/test_mtp_weight_sharing.py, dflash/weights.py:117-142)."""
+    from safetensors.torch import save_file
+
+    from nexrt_b200.dflash.config import shrunk_dflash_config
+    from nexrt_b200.dflash.weights import check_dflash_checkpoint, load_dflash_files, load_dflash_shard, random_dflash_checkpoint
+    from nexrt_b200.mtp.weights import load_mtp_files, random_mtp_checkpoint, shard_mtp
+
+    cfg = shrunk_config()
+    ck = random_checkpoint(cfg, 1)
+    mtp = random_mtp_checkpoint(cfg, 7)
+    save_checkpoint({**ck, **mtp}, cfg, tmp_path)
+    head = shard_model(ck, cfg, 2, 1, "cpu")["head"]
+    got = load_mtp_files(cfg, tmp_path, 2, 1, "cpu", head)
+    _same(got, shard_mtp(mtp, cfg, 2, 1, "cpu", head))
+    assert got["head"]["lm_head"] is head["lm_head"] and got["head"]["embed"] is head["embed"]      # shared, not copied
+    with pytest.raises(ValueError, match="not resident"):
+        shard_mtp(mtp, cfg, 2, 1, "cpu", {"final_ln": head["final_ln"], "lm_head": None, "embed": head["embed"]})
+    (tmp_path / "mtp.safetensors").unlink()
+    with pytest.raises(FileNotFoundError):
+        load_mtp_files(cfg, tmp_path, 2, 1, "cpu", head)
+
+    dc = shrunk_dflash_config(cfg)
+    dck = random_dflash_checkpoint(dc, 11)
+    path = tmp_path / "model.safetensors"
+    save_file({k: v.contiguous() for k, v in dck.items()}, str(path))
+    _same(load_dflash_files(dc, 2, 0, "cpu", path), load_dflash_shard(dck, dc, 2, 0, "cpu"))
+    check_dflash_checkpoint(dck, dc)
+    bad = dict(dck)
+    bad["layers.0.mlp.up_proj.weight"] = bad["layers.0.mlp.up_proj.weight"][:-1]
+    del bad["norm.weight"]
+    with pytest.raises(ValueError, match=r"norm.weight: missing.*layers.0.mlp.up_proj.weight: shape"):
+        check_dflash_checkpoint(bad, dc)
+    save_file({k: v.contiguous() for k, v in bad.items()}, str(path))
+    with pytest.raises(ValueError, match="draft geometry"):
+        load_dflash_files(dc, 2, 0, "cpu", path)
