@@ -3,6 +3,10 @@
 Counterpart of the reference's ``sglang_prefill/bridge_client.py`` (``BRIDGE.md:28-56``).
 
     python -m nexrt_b200.serve.bridge_client --port 9411 --text "hello" --max-new 64 --stream
+    python -m nexrt_b200.serve.bridge_client --port 9411 --file prompt.txt --chat
+
+A prompt file is read HERE (UTF-8) and travels as inline ``text``: the server takes no paths from the socket, and a file
+that cannot be read ends the client (exit code 2) before it connects.
 """
 
 from __future__ import annotations
@@ -51,6 +55,7 @@ def main(argv=None) -> int:
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=9411)
     p.add_argument("--text")
+    p.add_argument("--file", help="UTF-8 prompt file, read by the client and sent as inline text")
     p.add_argument("--ids", help="comma separated token ids")
     p.add_argument("--chat", action="store_true")
     p.add_argument("--max-new", type=int, default=128)
@@ -62,6 +67,14 @@ def main(argv=None) -> int:
     p.add_argument("--stream", action="store_true")
     p.add_argument("--shutdown", action="store_true")
     a = p.parse_args(argv)
+    if sum(v is not None for v in (a.text, a.file, a.ids)) > 1:
+        p.error("give one of --text, --file, --ids")
+    if a.file is not None:
+        try:
+            with open(a.file, "r", encoding="utf-8") as fh:
+                a.text = fh.read()
+        except (OSError, UnicodeDecodeError) as error:
+            p.error(f"cannot read {a.file}: {error}")          # exits with code 2, nothing was sent
     if a.shutdown:
         print(json.dumps(send_request({"cmd": "shutdown"}, a.host, a.port)))
         return 0

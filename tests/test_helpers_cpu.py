@@ -80,3 +80,35 @@ def test_cp_threshold_depends_on_the_group_size(monkeypatch):
     monkeypatch.setenv("NEXRT_CP_THRESHOLD", "1000")
     f.spec = type("S", (), {"cp_size": 2})()
     assert f.cp_threshold == de.CP_THRESHOLD              # an explicit setting applies to every group size
+
+
+def test_host_side_modules_import_without_torch_from_any_directory(tmp_path):
+    """The serving front ends, the cache / consensus / supervisor logic, the protocol model and the build helper are plain
+    Python: importing them from outside the repository must neither need the working directory nor pull in torch
+    (a front-end box has no GPU stack).  The heavier packages then import too.  Reference: tests/test_package_imports.py."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    light = ("nexrt_b200", "nexrt_b200.serve", "nexrt_b200.parallel", "nexrt_b200.runtime", "nexrt_b200.utils", "nexrt_b200.build",
+             "nexrt_b200.config", "nexrt_b200.sampling", "nexrt_b200.runtime.control", "nexrt_b200.runtime.rounds", "nexrt_b200.parallel.ll_model",
+             "nexrt_b200.serve.cache_lifecycle", "nexrt_b200.serve.cache_consensus", "nexrt_b200.serve.serve_control",
+             "nexrt_b200.serve.process_supervisor", "nexrt_b200.serve.stream_protocol", "nexrt_b200.serve.bridge_client",
+             "nexrt_b200.serve.stream_chat", "nexrt_b200.serve.openai_serve", "nexrt_b200.serve.launch")
+    heavy = ("nexrt_b200.dflash.config", "nexrt_b200.mtp.reference", "nexrt_b200.weights", "nexrt_b200.decode_engine", "nexrt_b200.serve.bridge_serve")
+    repo = Path(__file__).resolve().parents[1]
+    assert repo not in (tmp_path, *tmp_path.parents)
+    script = "\n".join((
+        "import importlib, sys",
+        f"light, heavy = {light!r}, {heavy!r}",
+        "for m in light:",
+        "    importlib.import_module(m)",
+        "    assert 'torch' not in sys.modules, m",
+        "for m in heavy:",
+        "    importlib.import_module(m)",
+        "print('ok')",
+    ))
+    env = dict(os.environ, PYTHONPATH=str(repo), PYTHONDONTWRITEBYTECODE="1")
+    done = subprocess.run([sys.executable, "-c", script], cwd=tmp_path, env=env, text=True, capture_output=True, check=False, timeout=300)
+    assert done.returncode == 0 and done.stdout.strip() == "ok", done.stderr[-2000:]

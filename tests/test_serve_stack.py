@@ -488,3 +488,47 @@ def test_worker_rejects_a_bad_wide_prefill_size(capsys):
         with pytest.raises(SystemExit):
             bridge_serve.main(["--wide-prefill", bad, "--no-listen"])
     assert "--wide-prefill must be 0 or a multiple of 8" in capsys.readouterr().err
+
+
+# ---- client command line (reference tests/test_bridge_client.py) ---------------------------------------------------
+def _run_client(argv, reply=b'{"ok": true}\n'):
+    """``bridge_client.main(argv)`` against a mocked socket: returns (exit code, request sent or None, connect calls)."""
+    import contextlib
+    import io
+    from unittest.mock import MagicMock, patch
+
+    conn = MagicMock()
+    conn.__enter__.return_value = conn
+    conn.recv.return_value = reply
+    code, sent = None, None
+    with patch.object(bridge_client.socket, "create_connection", return_value=conn) as connect, \
+            contextlib.redirect_stdout(io.StringIO()), contextlib.redirect_stderr(io.StringIO()):
+        try:
+            code = bridge_client.main(["--port", "9411", *argv])
+        except SystemExit as e:
+            code = e.code
+    if conn.sendall.call_args is not None:
+        sent = json.loads(conn.sendall.call_args.args[0])
+    return code, sent, connect.call_count
+
+
+def test_client_reads_prompt_files_locally_and_sends_inline_text(tmp_path):
+    path = tmp_path / "prompt.txt"
+    text = "你好，NexRT\nSecond line."
+    path.write_text(text, encoding="utf-8")
+    code, sent, _ = _run_client(["--file", str(path), "--chat", "--max-new", "16", "--seed", "7"])
+    assert code == 0 and sent == {"text": text, "chat": True, "max_new": 16, "seed": 7}
+    code, sent, _ = _run_client(["--text", "hello", "--temperature", "0", "--top-p", "0.95", "--top-k", "28"])
+    assert code == 0 and sent == {"text": "hello", "max_new": 128, "seed": 0, "temperature": 0.0, "top_p": 0.95, "top_k": 28}
+    code, sent, _ = _run_client(["--ids", "5,6,7", "--cache-key", "k"])
+    assert code == 0 and sent == {"ids": [5, 6, 7], "max_new": 128, "seed": 0, "cache_key": "k"}
+    assert _run_client(["--shutdown"])[:2] == (0, {"cmd": "shutdown"})
+
+
+def test_client_fails_before_connecting_when_the_file_cannot_be_read(tmp_path):
+    code, sent, connects = _run_client(["--file", str(tmp_path / "missing.txt")])
+    assert code == 2 and sent is None and connects == 0
+    bad = tmp_path / "latin1.txt"
+    bad.write_bytes(b"caf\xe9")
+    assert _run_client(["--file", str(bad)])[0::2] == (2, 0)
+    assert _run_client(["--file", str(bad), "--text", "x"])[0::2] == (2, 0)
