@@ -123,3 +123,32 @@ def test_stop_ids_come_from_tokenizer_generation_config_and_tool_call_openers(tm
         raise KeyError(text)
 
     assert resolve_stop_ids(SimpleNamespace(eos_token_id=[2, 5], unk_token_id=None, convert_tokens_to_ids=boom)) == (2, 5)
+
+
+def test_stream_deltas_of_a_speculative_request_equal_the_final_text():
+    """Rounds -> ``on_tokens`` -> stream writer: with a stop token in the middle of a round the concatenated deltas are
+    exactly the visible text of the tokens the request returns (reference tests/test_stream_callbacks.py:
+    test_mtp_stop_token_stream_deltas_equal_json_text)."""
+    import socket
+
+    from nexrt_b200.serve.bridge_serve import ByteTokenizer
+    from nexrt_b200.serve.stream_protocol import BridgeStreamWriter, decode_visible_text
+
+    tok = ByteTokenizer()
+    ids = tok.encode("héllo wörld")
+    stop = tok.eos_token_id
+    script = [(ids[:3], 0), (ids[3:7], 0), (ids[7:] + [stop, ids[0], ids[1]], 0), ([ids[2]], 0)]
+    eng, graph = fake_engine(script)
+    a, b = socket.socketpair()
+    try:
+        w = BridgeStreamWriter(a, tok, stop_ids=(stop, 99999))
+        out = consume_rounds(eng, graph, max_new=64, eos=(99999, stop), on_tokens=w.tokens)
+        assert out == ids + [stop]
+        text = decode_visible_text(tok, out, (stop, 99999))
+        assert w.finish({"tokens": out, "generated_text": text, "status": 0}) and w.close()
+        a.close()
+        events = [json.loads(line) for line in b.makefile("rb").read().decode().splitlines()]
+    finally:
+        b.close()
+    assert text == "héllo wörld" and "".join(e["text"] for e in events if e["type"] == "delta") == text
+    assert events[-1]["type"] == "done"
