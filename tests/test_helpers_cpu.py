@@ -112,3 +112,22 @@ def test_host_side_modules_import_without_torch_from_any_directory(tmp_path):
     env = dict(os.environ, PYTHONPATH=str(repo), PYTHONDONTWRITEBYTECODE="1")
     done = subprocess.run([sys.executable, "-c", script], cwd=tmp_path, env=env, text=True, capture_output=True, check=False, timeout=300)
     assert done.returncode == 0 and done.stdout.strip() == "ok", done.stderr[-2000:]
+
+
+def test_no_library_collective_on_the_step_path():
+    """Every all-reduce / exchange of a step happens inside the step's own kernels; the block wrappers and the
+    speculative blocks never call a torch.distributed collective (reference tests/test_dflash_static.py:
+    test_public_kernel_surface, the runtime block holds no collective).  The one library call that exists is the
+    explicitly selected baseline arm of the context (``collective == "nccl"``)."""
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1] / "nexrt_b200"
+    step_path = ["gdn.py", "attn.py", "moe.py", "head.py", "ctl_mirror.py", "prefill_wide.py", "m4_verify.py", "m8_verify.py",
+                 "mtp/block.py", "dflash/block.py", "ops/wide.py", "ops/tc_gemm.py", "runtime/rounds.py"]
+    calls = ("all_reduce(", "all_gather(", "reduce_scatter(", "all_to_all(", "broadcast(")      # (host barriers exist in the reset paths between steps)
+    for name in step_path:
+        text = (root / name).read_text(encoding="utf-8")
+        for call in calls:
+            assert call not in text, (name, call)
+    ctx = (root / "runtime/context.py").read_text(encoding="utf-8")
+    assert ctx.count("dist.all_reduce(") == 1 and 'if self.collective != "nccl":\n            return' in ctx
