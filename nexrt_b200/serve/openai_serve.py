@@ -16,7 +16,6 @@ can be tested without sockets; the HTTP part is a thin ``http.server`` handler.
 from __future__ import annotations
 
 import argparse
-import itertools
 import json
 import threading
 import time
@@ -170,12 +169,32 @@ def primed(events: Iterator[Dict]) -> Iterator[Dict]:
     """Pull the first event now.  ``bridge_client.stream_request`` is a generator, so it connects only when first advanced:
     priming it before the status line goes out turns an unreachable backend into a 502 JSON reply instead of a broken
     200 stream."""
-    source = iter(events)
-    try:
-        first = next(source)
-    except StopIteration:
-        return iter(())
-    return itertools.chain((first,), source)
+    return _Primed(events)
+
+
+class _Primed:
+    """An event stream whose first event has already been pulled; ``close()`` reaches the source (a generator that holds
+    the backend socket), which ``itertools.chain`` would hide."""
+
+    def __init__(self, events: Iterator[Dict]):
+        self.source = iter(events)
+        try:
+            self.head = [next(self.source)]
+        except StopIteration:
+            self.head = []
+
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> Dict:
+        if self.head:
+            return self.head.pop()
+        return next(self.source)
+
+    def close(self) -> None:
+        close = getattr(self.source, "close", None)
+        if close:
+            close()
 
 
 def sse_events(endpoint: str, events: Iterator[Dict], model: str, requested: int, include_usage: bool, request_id: Optional[str] = None) -> Iterator[str]:
@@ -207,6 +226,14 @@ def sse_events(endpoint: str, events: Iterator[Dict], model: str, requested: int
         if kind == "delta":
             yield line(stream_chunk(endpoint, base, text=ev.get("text", "")))
         elif kind == "done":
+            try:
+                device_status = int(ev.get("status", 0))
+            except (TypeError, ValueError):
+                device_status = -1
+            if device_status != 0:     # a step latched a failure: what was streamed is not a completion, and it must not end like one
+                yield line({"error": {"message": f"backend reported device status {ev.get('status')}", "type": "backend_error", "param": None, "code": None}})
+                yield "data: [DONE]\n\n"
+                return
             final = ev
             break
         elif kind == "error" or "error" in ev:
@@ -230,6 +257,7 @@ class FacadeState:
     backend_port: int = 9411
     backend_timeout: float = 1800.0
     queue_timeout: float = 30.0
+    write_timeout: float = 30.0      # a streaming client that takes nothing for this long loses its stream (and frees the engine slot)
     forward_sampling: bool = False
     call: Callable = bridge_client.send_request
     stream: Callable = bridge_client.stream_request
@@ -319,14 +347,17 @@ class Handler(BaseHTTPRequestHandler):
         self.send_header("Access-Control-Allow-Origin", "*")
         self.end_headers()
         self.close_connection = True
+        # the engine slot is held while the stream runs: a reader that stalls must not hold it forever, so every write is
+        # bounded, and whichever way the stream ends the backend connection is closed with it
+        self.connection.settimeout(self.st.write_timeout)
         try:
             for chunk in sse_events(endpoint, events, self.st.model_name, req["max_new"], include_usage):
                 self.wfile.write(chunk.encode())
                 self.wfile.flush()
-        except (BrokenPipeError, ConnectionResetError):
-            close = getattr(events, "close", None)
-            if close:
-                close()
+        except (BrokenPipeError, ConnectionResetError, TimeoutError, OSError):
+            pass                      # the client went away or stopped reading: nothing more can be told to it
+        finally:
+            events.close()
 
 
 class OpenAIServer(ThreadingHTTPServer):
@@ -346,10 +377,11 @@ def main(argv=None) -> int:
     p.add_argument("--backend-port", type=int, default=9411)
     p.add_argument("--backend-timeout", type=float, default=1800.0)
     p.add_argument("--queue-timeout", type=float, default=30.0)
+    p.add_argument("--write-timeout", type=float, default=30.0, help="seconds a streaming client may stall before its stream is dropped")
     p.add_argument("--model-name", default="Nex-N2.5-Pro")
     p.add_argument("--forward-sampling", action="store_true")
     a = p.parse_args(argv)
-    state = FacadeState(a.model_name, a.backend_host, a.backend_port, a.backend_timeout, a.queue_timeout, a.forward_sampling)
+    state = FacadeState(a.model_name, a.backend_host, a.backend_port, a.backend_timeout, a.queue_timeout, a.write_timeout, a.forward_sampling)
     with OpenAIServer((a.host, a.port), state) as srv:
         print(f"@@ OPENAI facade on http://{a.host}:{srv.server_address[1]} -> bridge {a.backend_host}:{a.backend_port}", flush=True)
         try:

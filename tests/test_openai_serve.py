@@ -142,3 +142,68 @@ def test_http_round_trip(facade):
     finally:
         state.slot.release()
     assert _http(port, "POST", "/v1/completions", {"prompt": "hi"})[0] == 200
+
+
+@pytest.mark.parametrize("body", ["[]", '"text"', "5", "null", "true"])
+def test_non_object_body_is_a_400_and_never_reaches_the_backend(facade, body):
+    port, calls, _ = facade
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
+    c.request("POST", "/v1/chat/completions", body=body, headers={"Content-Type": "application/json"})
+    r = c.getresponse()
+    data = json.loads(r.read().decode())
+    c.close()
+    assert r.status == 400 and data["error"]["type"] == "invalid_request_error" and calls == []
+
+
+def test_backend_device_status_is_an_error_in_json_and_in_the_stream():
+    """A reply whose device status word is not zero is never presented as a completion (reference
+    tests/test_openai_serve.py: test_json_and_sse_surface_nonzero_backend_status_as_errors)."""
+    bad = dict(RESULT, status=3)
+    state = FacadeState(model_name="m", call=lambda *a: dict(bad), stream=lambda *a: iter([{"type": "delta", "text": "ab"}, dict(bad, type="done")]))
+    srv = OpenAIServer(("127.0.0.1", 0), state)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        port = srv.server_address[1]
+        status, data = _http(port, "POST", "/v1/completions", {"prompt": "hi"})
+        assert status == 502 and "device status 3" in json.loads(data)["error"]["message"]
+        status, data = _http(port, "POST", "/v1/completions", {"prompt": "hi", "stream": True})
+        chunks = [json.loads(l[6:]) for l in data.splitlines() if l.startswith("data: {")]
+        assert status == 200 and data.strip().endswith("data: [DONE]")
+        assert any("error" in c for c in chunks) and not any(c.get("choices") and c["choices"][0].get("finish_reason") for c in chunks if "choices" in c)
+    finally:
+        srv.shutdown()
+        srv.server_close()
+
+
+def test_a_stalled_stream_reader_gives_the_engine_slot_back():
+    """The slot is held while a stream runs.  A client that connects, asks for a stream and then reads nothing must lose it
+    after the write timeout, the backend stream must be closed, and the next request must be served (reference
+    tests/test_openai_serve.py: test_stalled_sse_reader_releases_backend_lock_for_next_request)."""
+    import socket
+    import time
+
+    closed = threading.Event()
+
+    def stream(req, host, port, timeout):
+        try:
+            for _ in range(1 << 20):
+                yield {"type": "delta", "text": "x" * 65536}
+        finally:
+            closed.set()
+
+    state = FacadeState(model_name="m", call=lambda *a: dict(RESULT), stream=stream, queue_timeout=5.0, write_timeout=0.3)
+    srv = OpenAIServer(("127.0.0.1", 0), state)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    s = socket.create_connection(("127.0.0.1", srv.server_address[1]))
+    try:
+        s.setsockopt(socket.SOL_SOCKET, socket.SO_RCVBUF, 4096)
+        body = json.dumps({"prompt": "hi", "stream": True}).encode()
+        s.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: " + str(len(body)).encode() + b"\r\n\r\n" + body)
+        t0 = time.monotonic()
+        assert closed.wait(20.0), "the stalled stream was never given up"
+        status, data = _http(srv.server_address[1], "POST", "/v1/completions", {"prompt": "hi"})
+        assert status == 200 and json.loads(data)["choices"][0]["text"] == "abc" and time.monotonic() - t0 < 25.0
+    finally:
+        s.close()
+        srv.shutdown()
+        srv.server_close()
