@@ -146,6 +146,16 @@ def test_request_consensus_rules():
         resolve_request([request_record(True, hit, fp), request_record(True, hit, fp, recoverable_failure=True)])
     with pytest.raises(RecoverableRequestError):
         resolve_request([request_record(True, hit, fp, recoverable_failure=True)] * 2)
+    # a rank without a live boundary turns the request into a collective PREFILL, but it cannot hide a disagreement about
+    # the generation, the target length or the request itself, nor a malformed proposal of a rank that claims to be valid
+    with pytest.raises(FatalTPInvariantError):
+        resolve_request([request_record(True, hit, fp), request_record(False, CachePlan(4, CacheDecision.PREFILL, 0, 5), fp)])
+    with pytest.raises(FatalTPInvariantError):
+        resolve_request([request_record(True, hit, fp), request_record(False, CachePlan(3, CacheDecision.PREFILL, 0, 6), fp)])
+    with pytest.raises(FatalTPInvariantError):
+        resolve_request([request_record(True, hit, fp), request_record(False, pre, fp + 1)])
+    with pytest.raises(FatalTPInvariantError):
+        resolve_request([request_record(True, CachePlan(3, CacheDecision.APPEND, 9, 5), fp), request_record(False, pre, fp)])   # base beyond the target
     with pytest.raises(CacheConsensusError):
         resolve_request([])
     with pytest.raises(CacheConsensusError):
