@@ -98,10 +98,10 @@ def _generation_config(directory: Optional[str]) -> Mapping[str, Any]:
     return json.loads(path.read_text()) if path.is_file() else {}
 
 
-def sampling_defaults() -> Tuple[float, float, int]:
-    """Server defaults: ``DEFAULT_SAMPLING`` overridden by the checkpoint's ``generation_config.json`` (looked up under
-    ``NEXRT_MODEL_DIR``, else ``NEXRT_LAYERS_DIR``); ``do_sample: false`` means greedy."""
-    gen = _generation_config(os.environ.get("NEXRT_MODEL_DIR") or os.environ.get("NEXRT_LAYERS_DIR"))
+def sampling_defaults(model_dir: Optional[str] = None) -> Tuple[float, float, int]:
+    """Server defaults: ``DEFAULT_SAMPLING`` overridden by the checkpoint's ``generation_config.json`` (looked up in
+    ``model_dir``, else under ``NEXRT_MODEL_DIR``, else ``NEXRT_LAYERS_DIR``); ``do_sample: false`` means greedy."""
+    gen = _generation_config(model_dir or os.environ.get("NEXRT_MODEL_DIR") or os.environ.get("NEXRT_LAYERS_DIR"))
     if gen.get("do_sample") is False:
         return SamplingConfig.make(GREEDY[0], gen.get("top_p", DEFAULT_SAMPLING[1]), GREEDY[2]).as_tuple()
     picked = [gen.get(key, default) for key, default in zip(("temperature", "top_p", "top_k"), DEFAULT_SAMPLING)]

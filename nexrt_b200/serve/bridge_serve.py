@@ -30,7 +30,7 @@ import time
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
-from ..sampling import DEFAULT_SAMPLING, checked_sampling_config, resolve_sampling_config
+from ..sampling import DEFAULT_SAMPLING, checked_sampling_config, resolve_sampling_config, sampling_defaults
 from .bridge import PrefillSession, chunked_prefill
 from .cache_consensus import (all_gather_records, boundary_record, request_fingerprint, request_record, resolve_boundary,
                               resolve_request, resolve_retain, retain_record)
@@ -246,6 +246,7 @@ class BridgeServer:
         self._gather = gather or (lambda rec: all_gather_records(rec, group=self.group))
         self.log = log if rank == 0 else (lambda *_: None)
         self.stop_ids = resolve_stop_ids(tokenizer, model_dir)
+        self.sampling = sampling_defaults(model_dir)        # the model's generation_config.json over the built-in defaults
         # test-only host-side fault injection: this rank reports its READY boundary as lost on the next reuse,
         # which must turn the request into a collective PREFILL on every rank
         self.consensus_fault_rank = consensus_fault_rank
@@ -367,7 +368,7 @@ class BridgeServer:
         a collective reset is reported and the queue goes on."""
         out = []
         for i, raw in enumerate(requests):
-            req = validate_request(raw, self.backend.capacity, self.mode)
+            req = validate_request(raw, self.backend.capacity, self.mode, self.sampling)
             ids = self.tokenize(req)
             try:
                 res = self.run_request(req, ids)
@@ -397,7 +398,7 @@ class BridgeServer:
             steps = [("prefill", base, key), ("hit", base, key), ("append", target, key), ("oracle-base", base, None), ("oracle-target", target, None)]
             got = {}
             for name, ids, owner in steps:
-                req = validate_request({"ids": ids, "max_new": gen, "temperature": 0.0, "cache_key": owner}, self.backend.capacity, self.mode)
+                req = validate_request({"ids": ids, "max_new": gen, "temperature": 0.0, "cache_key": owner}, self.backend.capacity, self.mode, self.sampling)
                 res = self.run_request(req, ids)
                 got[name] = res
                 rows.append({"rep": rep, "step": name, "cache": res["cache"], "prefill_s": res["prefill_s"], "ttft_s": res["ttft_s"]})
@@ -483,7 +484,7 @@ class BridgeServer:
                 if not part:
                     break
                 buf += part
-            req = validate_request(json.loads(buf.decode("utf-8")), self.backend.capacity, self.mode)
+            req = validate_request(json.loads(buf.decode("utf-8")), self.backend.capacity, self.mode, self.sampling)
             if req.get("cmd") == "shutdown":
                 return conn, req
             ids = self.tokenize(req)

@@ -44,3 +44,40 @@ def test_reference_sampler_greedy_and_ties():
     assert tok == 1 and kept == [1]
     tok, kept, probs = sample_reference(logits, 1, 0, 1.0, 1.0, 3)
     assert kept[:2] == [1, 2] and abs(sum(probs) - 1.0) < 1e-9 and tok in kept
+
+
+def test_model_generation_config_sets_the_server_defaults(tmp_path, monkeypatch):
+    """``generation_config.json`` of the model directory over the built-in defaults, request values over both;
+    ``do_sample: false`` means greedy whatever else the file says (reference tests/test_sampling.py:
+    test_model_defaults_and_request_overrides)."""
+    import json
+
+    from nexrt_b200.sampling import DEFAULT_SAMPLING, resolve_sampling_config, sampling_defaults
+
+    for var in ("NEXRT_MODEL_DIR", "NEXRT_LAYERS_DIR"):
+        monkeypatch.delenv(var, raising=False)
+    assert sampling_defaults() == pytest.approx(DEFAULT_SAMPLING) and sampling_defaults(str(tmp_path)) == pytest.approx(DEFAULT_SAMPLING)    # float32-rounded
+    path = tmp_path / "generation_config.json"
+    path.write_text(json.dumps(dict(temperature=0.7, top_p=0.9, top_k=28)))
+    defaults = sampling_defaults(str(tmp_path))
+    assert defaults == pytest.approx((0.7, 0.9, 28))
+    monkeypatch.setenv("NEXRT_MODEL_DIR", str(tmp_path))
+    assert sampling_defaults() == defaults
+    assert resolve_sampling_config(defaults, temperature=0) == (0, defaults[1], 28) and resolve_sampling_config(defaults) == defaults
+    path.write_text(json.dumps(dict(do_sample=False, temperature=1, top_k=50)))
+    assert sampling_defaults()[::2] == (0, 1)
+
+
+def test_server_applies_the_model_defaults_to_requests(tmp_path):
+    import json
+
+    from nexrt_b200.serve.bridge_serve import BridgeServer, ByteTokenizer, validate_request
+
+    (tmp_path / "generation_config.json").write_text(json.dumps(dict(temperature=0.3, top_p=0.8, top_k=7, eos_token_id=[2, 9])))
+    backend = type("B", (), {"capacity": 64, "model_epoch": "m", "vocab": 300})()
+    srv = BridgeServer(backend, ByteTokenizer(), log=lambda *_: None, model_dir=str(tmp_path))
+    assert srv.sampling == pytest.approx((0.3, 0.8, 7)) and srv.stop_ids == (2, 9)
+    req = validate_request({"text": "a"}, 64, "bs1", srv.sampling)
+    assert (req["temperature"], req["top_p"], req["top_k"]) == pytest.approx((0.3, 0.8, 7))
+    req = validate_request({"text": "a", "temperature": 0.0, "top_k": 3}, 64, "bs1", srv.sampling)
+    assert (req["temperature"], req["top_p"], req["top_k"]) == pytest.approx((0.0, 0.8, 3))
