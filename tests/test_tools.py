@@ -16,6 +16,17 @@ from nexrt_b200.serve.stream_chat import completion_url, parse_sse, payload
 from nexrt_b200.weights import PFX
 
 
+def _no_mtp(tmp_path):
+    """A sharded checkpoint directory without any mtp.* tensor."""
+    from safetensors.torch import save_file
+
+    d = tmp_path / "no-mtp"
+    d.mkdir()
+    save_file({"x.weight": torch.zeros(1)}, str(d / "s.safetensors"))
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"x.weight": "s.safetensors"}}))
+    return d
+
+
 def test_extract_layers_splits_and_normalises_scale_names(tmp_path):
     from safetensors.torch import load_file, save_file
 
@@ -35,6 +46,19 @@ def test_extract_layers_splits_and_normalises_scale_names(tmp_path):
     key = f"{PFX}layers.0.self_attn.q_proj.weight_scale_inv"
     assert key in l0 and l0[key].dtype == torch.float32 and canonical_key("x.weight_scale") == "x.weight_scale_inv"
     assert not list(dst.glob("*.tmp"))
+    # the MTP head from a checkpoint of its own: only its mtp.* tensors are taken, under canonical names
+    msrc = tmp_path / "mtp-src"
+    msrc.mkdir()
+    m = {"mtp.fc.weight": torch.full((2, 4), 5.0), "mtp.fc.weight_scale": torch.ones(1, 1, dtype=torch.bfloat16), "ignored.weight": torch.zeros(1)}
+    save_file(m, str(msrc / "mtp-00001.safetensors"))
+    (msrc / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {k: "mtp-00001.safetensors" for k in m}}))
+    written = extract(str(src), str(dst), layers=[0], with_globals=False, log=lambda *_: None, mtp_src=str(msrc))
+    assert set(written) == {"layer.0.safetensors", "mtp.safetensors"} and written["mtp.safetensors"] == 2
+    got = load_file(str(dst / "mtp.safetensors"))
+    assert set(got) == {"mtp.fc.weight", "mtp.fc.weight_scale_inv"} and float(got["mtp.fc.weight"][0, 0]) == 5.0 and got["mtp.fc.weight_scale_inv"].dtype == torch.float32
+    assert set(extract(None, str(dst), log=lambda *_: None, mtp_src=str(msrc))) == {"mtp.safetensors"}
+    with pytest.raises(KeyError):
+        extract(None, str(dst), log=lambda *_: None, mtp_src=str(_no_mtp(tmp_path)))
     with pytest.raises(KeyError):
         plan_outputs(wm, [5])
     with pytest.raises(KeyError):
