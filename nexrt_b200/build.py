@@ -153,7 +153,14 @@ def build_library(force: bool = False, jobs: int = 0) -> Path:
     return lib
 
 
-if __name__ == "__main__":
+def main(argv=None) -> int:
+    """``python -m nexrt_b200.build [--force]``: build (or reuse) the library and print its path."""
     import sys
 
-    print(build_library(force="--force" in sys.argv))
+    args = sys.argv[1:] if argv is None else list(argv)
+    print(build_library(force="--force" in args))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

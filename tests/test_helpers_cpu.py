@@ -131,3 +131,23 @@ def test_no_library_collective_on_the_step_path():
             assert call not in text, (name, call)
     ctx = (root / "runtime/context.py").read_text(encoding="utf-8")
     assert ctx.count("dist.all_reduce(") == 1 and 'if self.collective != "nccl":\n            return' in ctx
+
+
+def test_packaging_metadata_names_real_entry_points():
+    """pyproject.toml: every console script resolves to a callable of the package, the package data covers the CUDA
+    sources the in-place build needs, and the gpu marker stays registered by conftest (no second registry)."""
+    import importlib
+    import tomllib
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    meta = tomllib.loads((root / "pyproject.toml").read_text(encoding="utf-8"))
+    scripts = meta["project"]["scripts"]
+    assert {"nexrt-serve", "nexrt-openai", "nexrt-client", "nexrt-build", "nexrt-extract-layers"} <= set(scripts)
+    for name, target in scripts.items():
+        module, func = target.split(":")
+        assert callable(getattr(importlib.import_module(module), func)), name
+    patterns = meta["tool"]["setuptools"]["package-data"]["nexrt_b200"]
+    csrc = root / "nexrt_b200" / "csrc"
+    covered = {p.name for pat in patterns for p in (root / "nexrt_b200").glob(pat)}
+    assert {p.name for p in csrc.iterdir() if p.suffix in (".cu", ".cuh", ".h")} <= covered
