@@ -74,18 +74,38 @@ class IncrementalDetokenizer:
         out, self.sent = text[self.sent : end], end
         return out
 
-    def _compact(self) -> None:
+    def _compact(self) -> str:
+        """Bound the window.  A cut is exact when decoding the two parts separately gives the joint text: then the cut lies
+        between two characters (or invalid sequences) and nothing that follows can change the head.  Preferred: an exact
+        cut whose head is already out.  Otherwise an exact cut whose head still holds unsent characters - trailing
+        replacement characters of bytes that turned out to be final - which are returned for emission.  A tokenizer with
+        no exact cut inside the tail at all (one character spread over more tokens than the tail keeps) gets its window
+        flushed as it decodes now: a stream never fails over its own bookkeeping."""
         if len(self.window) <= self.max_tail_tokens:
-            return
+            return ""
         full = _decode(self.tokenizer, self.window)
+        forced = None
         for keep in range(min(self.max_tail_tokens, len(self.window) - 1), 0, -1):
             cut = len(self.window) - keep
             head, tail = _decode(self.tokenizer, self.window[:cut]), _decode(self.tokenizer, self.window[cut:])
-            if head + tail == full and not head.endswith(REPLACEMENT) and len(head) <= self.sent:
+            if head + tail != full:
+                continue
+            if len(head) <= self.sent:
                 del self.window[:cut]
                 self.sent -= len(head)
-                return
-        raise RuntimeError(f"tokenizer has no exact incremental split within {self.max_tail_tokens} retained tokens")
+                return ""
+            if forced is None:
+                forced = (cut, head)
+        if forced is not None:
+            cut, head = forced
+            out = head[self.sent :]
+            del self.window[:cut]
+            self.sent = 0
+            return out
+        out = full[self.sent :]
+        self.window.clear()
+        self.sent = 0
+        return out
 
     def push(self, token_ids: Iterable[int]) -> str:
         if self.stop_seen:
@@ -100,7 +120,9 @@ class IncrementalDetokenizer:
             piece = self._stable_text()
             if piece:
                 parts.append(piece)
-            self._compact()
+            piece = self._compact()
+            if piece:
+                parts.append(piece)
         return "".join(parts)
 
     def finish(self) -> str:

@@ -532,3 +532,36 @@ def test_client_fails_before_connecting_when_the_file_cannot_be_read(tmp_path):
     bad.write_bytes(b"caf\xe9")
     assert _run_client(["--file", str(bad)])[0::2] == (2, 0)
     assert _run_client(["--file", str(bad), "--text", "x"])[0::2] == (2, 0)
+
+
+def test_incremental_detokenizer_equals_one_shot_decode_on_any_byte_stream():
+    """Streamed text == one-shot text for valid UTF-8 and for arbitrary bytes (a model can emit any byte-fallback token),
+    in any grouping, with a bounded window; a run of invalid bytes longer than the window never raises (reference
+    tests/test_openai_serve.py: test_incremental_detokenizer_matches_one_shot_with_bounded_state)."""
+    import random
+
+    tok = ByteTokenizer()
+    rng = random.Random(0)
+    for trial in range(600):
+        n = rng.randint(0, 120)
+        mode = rng.random()
+        if mode < 0.4:
+            ids = tok.encode("".join(rng.choice("aé✓😀\n z中") for _ in range(n)))
+        elif mode < 0.7:
+            ids = [3 + rng.randrange(256) for _ in range(n)]
+        else:
+            ids = [3 + rng.choice([0x80, 0xBF, 0xE2, 0xF0, 0x41]) for _ in range(n)]
+        tail = rng.choice([4, 5, 8, 32])
+        det = IncrementalDetokenizer(tok, max_tail_tokens=tail)
+        out, i = "", 0
+        while i < len(ids):
+            g = rng.randint(1, 5)
+            out += det.push(ids[i : i + g])
+            i += g
+            assert det.retained_tokens <= tail
+        out += det.finish()
+        assert out == decode_visible_text(tok, ids, ()), (trial, tail, ids[:24])
+    # a character spread over more tokens than the window keeps: the window is flushed as it decodes, nothing raises
+    det = IncrementalDetokenizer(tok, max_tail_tokens=1)
+    text = "".join(det.push([t]) for t in tok.encode("a😀b")) + det.finish()
+    assert text.startswith("a") and text.endswith("b")
