@@ -130,6 +130,14 @@ def validate_request(req: Dict, capacity: int, mode: str, defaults=DEFAULT_SAMPL
         raise BadRequest("text must be a string")
     if "ids" in req and not (isinstance(req["ids"], list) and req["ids"] and all(isinstance(t, int) and not isinstance(t, bool) and t >= 0 for t in req["ids"])):
         raise BadRequest("ids must be a non-empty list of non-negative integers")
+    if "messages" in req:
+        msgs = req["messages"]
+        if not (isinstance(msgs, list) and msgs and all(isinstance(m, dict) and isinstance(m.get("role"), str) and isinstance(m.get("content"), str)
+                                                        for m in msgs)):
+            raise BadRequest("messages must be a non-empty list of {role: string, content: string}")
+    for flag in ("chat", "stream"):
+        if flag in req and not isinstance(req[flag], bool):
+            raise BadRequest(f"{flag} must be a boolean")
     max_new = req.get("max_new", 128)
     if isinstance(max_new, bool) or not isinstance(max_new, int) or not 1 <= max_new <= MAX_NEW_LIMIT:
         raise BadRequest(f"max_new must be an integer in [1, {MAX_NEW_LIMIT}]")
@@ -254,17 +262,23 @@ class BridgeServer:
 
     # ---- one request, every rank ---------------------------------------------------------------------
     def tokenize(self, req: Dict) -> List[int]:
-        if req.get("ids") is not None:
-            ids = list(req["ids"])
-        elif req.get("messages") is not None:
-            ids = list(self.tok.apply_chat_template(req["messages"], tokenize=True, add_generation_prompt=True))
-        elif req.get("chat"):
-            ids = list(self.tok.apply_chat_template([{"role": "user", "content": req["text"]}], tokenize=True, add_generation_prompt=True))
-        else:
-            ids = list(self.tok.encode(req["text"], add_special_tokens=False))
+        try:
+            if req.get("ids") is not None:
+                ids = list(req["ids"])
+            elif req.get("messages") is not None:
+                ids = list(self.tok.apply_chat_template(req["messages"], tokenize=True, add_generation_prompt=True))
+            elif req.get("chat"):
+                ids = list(self.tok.apply_chat_template([{"role": "user", "content": req["text"]}], tokenize=True, add_generation_prompt=True))
+            else:
+                ids = list(self.tok.encode(req["text"], add_special_tokens=False))
+            ids = [int(t) for t in ids]
+        except BadRequest:
+            raise
+        except Exception as error:  # noqa: BLE001 - whatever a tokenizer or its chat template raises is the request's fault, not the server's
+            raise BadRequest(f"the tokenizer rejected the prompt: {type(error).__name__}: {error}") from error
         if not ids:
             raise BadRequest("empty prompt")
-        if any(t >= self.backend.vocab for t in ids):
+        if any(t < 0 or t >= self.backend.vocab for t in ids):
             raise BadRequest("token id outside the vocabulary")
         if len(ids) + req["max_new"] > self.backend.capacity:
             raise BadRequest(f"prompt of {len(ids)} tokens + max_new {req['max_new']} exceeds the context capacity {self.backend.capacity}")
@@ -489,9 +503,13 @@ class BridgeServer:
                 return conn, req
             ids = self.tokenize(req)
             return conn, {"cmd": "request", "req": req, "ids": ids}
-        except (BadRequest, json.JSONDecodeError, UnicodeDecodeError, socket.timeout) as error:
+        except Exception as error:  # noqa: BLE001
+            # nothing a client sends may take the server down: malformed JSON, a wrong field, a prompt the tokenizer refuses,
+            # a socket that times out or resets - the request is answered (if the socket still takes it) and dropped
             try:
                 conn.sendall((json.dumps({"error": f"bad request: {error}"}) + "\n").encode())
+            except OSError:
+                pass
             finally:
                 conn.close()
             return None, {"cmd": "heartbeat"}

@@ -371,6 +371,12 @@ def test_socket_server_end_to_end_with_client_and_stream():
     assert "bad request" in bad["error"]
     too_long = bridge_client.send_request({"ids": [5] * 200}, port=port, timeout=10)
     assert "exceeds" in too_long["error"]
+    # nothing a client sends takes the server down: malformed fields, a prompt the chat template cannot take, raw garbage
+    for junk in ({"messages": 5}, {"messages": [{"role": "user"}]}, {"messages": [None]}, {"text": "a", "chat": [1]}, {"ids": [1 << 70]}, [1, 2], "x", None):
+        assert "bad request" in bridge_client.send_request(junk, port=port, timeout=10)["error"], junk
+    with socket.create_connection(("127.0.0.1", port), timeout=10) as raw:
+        raw.sendall(b"\xff\xfe not json at all\n")
+        assert b"bad request" in raw.recv(1 << 16)
     events = list(bridge_client.stream_request({"text": "ping", "max_new": 5, "cache_key": "c"}, port=port, timeout=10))
     assert events[-1]["type"] == "done" and events[-1]["cache"] == "hit" and events[-1]["tokens"] == r["tokens"]
     assert "".join(e["text"] for e in events if e["type"] == "delta") == decode_visible_text(ByteTokenizer(), r["tokens"], (2,))
@@ -565,3 +571,60 @@ def test_incremental_detokenizer_equals_one_shot_decode_on_any_byte_stream():
     det = IncrementalDetokenizer(tok, max_tail_tokens=1)
     text = "".join(det.push([t]) for t in tok.encode("a😀b")) + det.finish()
     assert text.startswith("a") and text.endswith("b")
+
+
+def test_request_validation_survives_arbitrary_json():
+    """Random request objects through ``validate_request`` and ``BridgeServer.tokenize``: the outcome is a normalised
+    request with in-vocabulary ids, or ``BadRequest`` - never another exception (the accept loop would have to guess)."""
+    import random
+
+    rng = random.Random(1)
+    srv = BridgeServer(FakeBackend(), ByteTokenizer(), log=lambda *_: None)
+
+    def value(depth=0):
+        c = rng.randrange(12)
+        if c == 0:
+            return None
+        if c == 1:
+            return rng.choice([True, False])
+        if c == 2:
+            return rng.choice([0, 1, -1, 5, 1 << 70, 255, 258, 259])
+        if c == 3:
+            return rng.choice([0.0, 1.5, float("nan"), float("inf"), -2.0, 1e40])
+        if c == 4:
+            return rng.choice(["", "a", "héllo", "x" * 200])
+        if c == 5 and depth < 2:
+            return [value(depth + 1) for _ in range(rng.randrange(4))]
+        if c == 6 and depth < 2:
+            return {rng.choice(["role", "content", "x"]): value(depth + 1) for _ in range(rng.randrange(3))}
+        if c == 7:
+            return [{"role": "user", "content": "hi"}]
+        if c == 8:
+            return [5, 6, 7]
+        return rng.choice(["a", 3, 0.5])
+
+    keys = ["text", "ids", "chat", "messages", "max_new", "seed", "cache_key", "temperature", "top_p", "top_k", "stream", "cmd", "bogus"]
+    accepted = 0
+    for _ in range(4000):
+        roll = rng.random()
+        if roll < 0.1:
+            req = value()
+        elif roll < 0.5:      # a valid request with one field replaced by something arbitrary
+            req = dict(rng.choice([{"text": "héllo"}, {"ids": [5, 6, 7]}, {"messages": [{"role": "user", "content": "hi"}]}, {"text": "q", "chat": True}]),
+                       max_new=4, seed=3)
+            if rng.random() < 0.7:
+                req[rng.choice(keys)] = value()
+        else:
+            req = {k: value() for k in rng.sample(keys, rng.randrange(0, 6))}
+        for mode in ("bs1", "mtp"):
+            try:
+                r = validate_request(req, srv.backend.capacity, mode, srv.sampling)
+                if r.get("cmd") == "shutdown":
+                    continue
+                ids = srv.tokenize(r)
+            except BadRequest:
+                continue
+            accepted += 1
+            assert ids and all(isinstance(t, int) and 0 <= t < srv.backend.vocab for t in ids)
+            json.dumps(r)
+    assert accepted > 20          # the generator does produce valid requests too
