@@ -131,10 +131,15 @@ def check_bridge_result(result) -> Dict:
         bad = str(result["error"]).startswith("bad request")
         raise ApiError(str(result["error"]), status=HTTPStatus.BAD_REQUEST if bad else HTTPStatus.BAD_GATEWAY,
                        kind="invalid_request_error" if bad else "backend_error")
-    if int(result.get("status", 0)) != 0:
-        raise ApiError(f"backend reported device status {result['status']}", status=HTTPStatus.BAD_GATEWAY, kind="backend_error")
+    status = result.get("status", 0)
+    if isinstance(status, bool) or not isinstance(status, int):
+        raise ApiError("malformed backend reply: status is not an integer", status=HTTPStatus.BAD_GATEWAY, kind="backend_error")
+    if status != 0:
+        raise ApiError(f"backend reported device status {status}", status=HTTPStatus.BAD_GATEWAY, kind="backend_error")
     if not isinstance(result.get("tokens"), list):
         raise ApiError("backend reply has no tokens", status=HTTPStatus.BAD_GATEWAY, kind="backend_error")
+    if not isinstance(result.get("generated_text", ""), str) or not isinstance(result.get("prompt_tokens", 0), int):
+        raise ApiError("malformed backend reply: text / prompt_tokens", status=HTTPStatus.BAD_GATEWAY, kind="backend_error")
     return result
 
 

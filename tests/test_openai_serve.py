@@ -207,3 +207,55 @@ def test_a_stalled_stream_reader_gives_the_engine_slot_back():
         s.close()
         srv.shutdown()
         srv.server_close()
+
+
+def test_translation_and_reply_checks_survive_arbitrary_json():
+    """Random request bodies and random backend replies: the facade answers with ``ApiError`` (400 / 502) or a valid
+    object, never with another exception."""
+    import random
+
+    rng = random.Random(2)
+
+    def value(depth=0):
+        c = rng.randrange(13)
+        if c == 0:
+            return None
+        if c == 1:
+            return rng.choice([True, False])
+        if c == 2:
+            return rng.choice([0, 1, -1, 5, 1 << 70])
+        if c == 3:
+            return rng.choice([0.0, 1.5, float("nan"), -2.0])
+        if c == 4:
+            return rng.choice(["", "a", "héllo"])
+        if c == 5 and depth < 2:
+            return [value(depth + 1) for _ in range(rng.randrange(4))]
+        if c == 6 and depth < 2:
+            return {rng.choice(["role", "content", "include_usage", "type", "x"]): value(depth + 1) for _ in range(rng.randrange(3))}
+        if c == 7:
+            return [{"role": "user", "content": "hi"}]
+        return rng.choice(["a", 3, 0.5])
+
+    keys = ["model", "prompt", "messages", "max_tokens", "max_completion_tokens", "stream", "stream_options", "n", "stop", "seed", "cache_key", "temperature",
+            "top_p", "top_k", "tools", "tool_choice", "logprobs", "logit_bias", "presence_penalty", "frequency_penalty", "response_format", "user", "echo"]
+    ok = 0
+    for _ in range(3000):
+        body = value() if rng.random() < 0.05 else {k: value() for k in rng.sample(keys, rng.randrange(0, 5))}
+        if isinstance(body, dict) and rng.random() < 0.6:
+            body.setdefault(*rng.choice([("prompt", "hello"), ("messages", [{"role": "user", "content": "x"}])]))
+        for endpoint in ("chat", "text"):
+            try:
+                json.dumps(to_bridge_request(body, endpoint, forward_sampling=rng.random() < 0.5))
+                ok += 1
+            except ApiError as error:
+                assert error.status in (400, 404)
+    assert ok > 50
+    fields = ["tokens", "generated_text", "status", "stop_reason", "prompt_tokens", "error", "cache"]
+    for _ in range(3000):
+        res = value() if rng.random() < 0.2 else {k: value() for k in rng.sample(fields, rng.randrange(0, 6))}
+        try:
+            to_openai_reply(rng.choice(["chat", "text"]), check_bridge_result(res), "m", 5)
+        except ApiError as error:
+            assert error.status in (400, 502)
+        events = [res if isinstance(res, dict) else {"type": "delta", "text": "a"}, {"type": "done", "tokens": [1], "status": 0}]
+        assert list(sse_events("chat", iter(events), "m", 5, True))[-1] == "data: [DONE]\n\n"
