@@ -185,3 +185,50 @@ def test_boundary_retain_and_outcome_rules():
         resolve_request_outcome([failure_record(False, 3, 2, 3)] * 2)
     with pytest.raises(FatalTPInvariantError):
         resolve_request_outcome([ok, failure_record(None, 4, 2, 3)])
+
+
+def test_random_operation_sequences_keep_the_cache_consistent():
+    """Any order of lifecycle calls with any arguments either works or raises one of the documented errors, and the
+    snapshot stays sane: the valid length never leaves [0, capacity] and an empty cache holds nothing."""
+    import random
+
+    from nexrt_b200.serve.cache_lifecycle import CacheBusyError, CacheLeaseError
+
+    rng = random.Random(3)
+    for _ in range(400):
+        c = CachedSession(32, "m")
+        leases = []
+        for step in range(40):
+            op = rng.randrange(10)
+            lease = rng.choice(leases) if leases else None
+            toks = [rng.randrange(4) for _ in range(rng.randrange(0, 40))]
+            owner = rng.choice([None, "a", "b", ""])
+            b = CacheBoundary(rng.randrange(0, 34), rng.randrange(-1, 5), 0)
+            try:
+                if op == 0:
+                    c.plan_request(owner, toks, live_boundary=rng.choice([None, b]))
+                elif op == 1:
+                    leases.append(c.begin_request(owner, toks, f"r{step}", live_boundary=rng.choice([None, b]), force_prefill=rng.random() < 0.2))
+                elif lease is None:
+                    continue
+                elif op == 2:
+                    c.record_append(lease, rng.randrange(0, 34), rng.randrange(0, 34))
+                elif op == 3:
+                    c.commit_fill(lease, b)
+                elif op == 4:
+                    c.abort_fill(lease, "x")
+                elif op == 5:
+                    c.begin_decode(lease)
+                elif op == 6:
+                    c.finish_decode(lease, b)
+                elif op == 7:
+                    c.abort_decode(lease, "x")
+                elif op == 8:
+                    c.invalidate("x", force=rng.random() < 0.5)
+                else:
+                    c.validate_decode_boundary(lease, b)
+                    c.validate_fill_boundary(lease, b)
+            except (CacheLeaseError, CacheBusyError, ValueError):
+                pass
+            s = c.snapshot()
+            assert 0 <= s.valid_kv_length <= 32 and (s.phase != CachePhase.EMPTY or s.valid_kv_length == 0), s
