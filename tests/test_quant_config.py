@@ -261,3 +261,103 @@ def test_draft_loaders_read_files_and_check_geometry(tmp_path):
     save_file({k: v.contiguous() for k, v in bad.items()}, str(path))
     with pytest.raises(ValueError, match="draft geometry"):
         load_dflash_files(dc, 2, 0, "cpu", path)
+
+
+def _deq(wq, ws):
+    """Dequantise a block-scaled FP8 matrix [R, K] with scales [ceil(R/128), K/128] in float64."""
+    R, K = wq.shape
+    s = ws.double().repeat_interleave(128, 0)[:R].repeat_interleave(128, 1)[:, :K]
+    return wq.view(torch.float8_e4m3fn).double() * s
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_rank_shards_compute_what_the_checkpoint_computes(tp):
+    """Sharding as a function, for every tensor-parallel degree including the 8-way deployment split: the rank-local
+    tensors (rows AND their block scales), put through the layer's algebra and summed / concatenated over the ranks, give
+    the full checkpoint's result.  Checks the pairing the kernels rely on - a rank's v / z rows with its out-projection
+    columns, its q heads with the kv head GQA assigns them, an expert's gate / up rows with its down columns, the vocab
+    rows - which a random-weight benchmark cannot see."""
+    from nexrt_b200.config import ShardSpec, shrunk_tp8_config
+    from nexrt_b200.weights import PFX
+
+    cfg = shrunk_tp8_config() if tp == 8 else shrunk_config()
+    if tp == 4:
+        from nexrt_b200.config import shrunk_cp_config
+
+        cfg = shrunk_cp_config()
+    ck = random_checkpoint(cfg, 5)
+    shards = [shard_model(ck, cfg, tp, r, "cpu") for r in range(tp)]
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(cfg.hidden, generator=g, dtype=torch.float64)
+    W = lambda key: _deq(ck[key], ck[key + "_scale_inv"])
+    rel = lambda a, b: float((a - b).norm() / b.norm().clamp_min(1e-30))
+    lin = next(l for l in range(cfg.n_layers) if cfg.layer_types[l] == "linear")
+    att = next(l for l in range(cfg.n_layers) if cfg.layer_types[l] != "linear")
+
+    # gated delta net: sum_r out_r @ (v_r * z_r) == out @ (v * z), with v, z the projections of x
+    a = f"{PFX}layers.{lin}.linear_attn."
+    kd, vd = cfg.gdn_key_dim, cfg.gdn_value_dim
+    qkv, z = W(a + "in_proj_qkv.weight") @ x, W(a + "in_proj_z.weight") @ x
+    want = W(a + "out_proj.weight") @ (qkv[2 * kd :] * z)
+    got = torch.zeros_like(want)
+    for r, sh in enumerate(shards):
+        m = sh["layers"][lin]["mixer"]
+        pre = _deq(m["front_w"].view(torch.uint8), m["front_s"]) @ x
+        kr, vr = kd // tp, vd // tp
+        assert rel(pre[:kr], qkv[r * kr : (r + 1) * kr]) < 1e-9 and rel(pre[kr : 2 * kr], qkv[kd + r * kr : kd + (r + 1) * kr]) < 1e-9
+        got += _deq(m["out_w"].view(torch.uint8), m["out_s"]) @ (pre[2 * kr : 2 * kr + vr] * pre[2 * kr + vr :])
+        nv = cfg.gdn_v_heads // tp
+        assert torch.equal(m["a_log"], ck[a + "A_log"].float()[r * nv : (r + 1) * nv])
+        assert torch.equal(m["ba_w"][:nv].float(), ck[a + "in_proj_b.weight"][r * nv : (r + 1) * nv].to(torch.bfloat16).float())
+    assert rel(got, want) < 1e-9
+
+    # attention: every q head of a rank is paired with the kv head GQA gives it, and sum_r o_r @ (q_r * gate_r) == o @ (q * gate)
+    a = f"{PFX}layers.{att}.self_attn."
+    hd, nq, nkv = cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads
+    qg, k, v = W(a + "q_proj.weight") @ x, W(a + "k_proj.weight") @ x, W(a + "v_proj.weight") @ x
+    qg_h = qg.reshape(nq, 2, hd)
+    want = W(a + "o_proj.weight") @ (qg_h[:, 0] * qg_h[:, 1]).reshape(-1)
+    got = torch.zeros_like(want)
+    for r, sh in enumerate(shards):
+        spec = ShardSpec(cfg, tp, r)
+        m = sh["layers"][att]["mixer"]
+        pre = _deq(m["front_w"].view(torch.uint8), m["front_s"]) @ x
+        ql, kl = spec.q_heads, spec.kv_heads
+        q_r = pre[: ql * 2 * hd].reshape(ql, 2, hd)
+        assert rel(q_r, qg_h[r * ql : (r + 1) * ql]) < 1e-9
+        for j in range(ql):                                   # GQA: global q head h reads kv head h // (nq / nkv)
+            kv_global = (r * ql + j) // (nq // nkv)
+            assert spec.kv_head0 <= kv_global < spec.kv_head0 + kl
+        k_r = pre[ql * 2 * hd : ql * 2 * hd + kl * hd]
+        v_r = pre[ql * 2 * hd + kl * hd :]
+        assert rel(k_r, k[spec.kv_head0 * hd : (spec.kv_head0 + kl) * hd]) < 1e-9 and rel(v_r, v[spec.kv_head0 * hd : (spec.kv_head0 + kl) * hd]) < 1e-9
+        got += _deq(m["out_w"].view(torch.uint8), m["out_s"]) @ (q_r[:, 0] * q_r[:, 1]).reshape(-1)
+        if spec.cp_size > 1:
+            # context-parallel front: the query halves of every head that shares this rank's kv head (global head order),
+            # then the rank's own gate halves, then k and v
+            mc = shard_model(ck, cfg, tp, r, "cpu", cp=True)["layers"][att]["mixer_cp"]
+            pc = _deq(mc["front_w"].view(torch.uint8), mc["front_s"]) @ x
+            n_all = ql * spec.cp_size
+            g0 = spec.cp_group[0] * ql
+            assert list(spec.cp_group) == [rr for rr in range(tp) if ShardSpec(cfg, tp, rr).kv_head0 == spec.kv_head0]
+            assert rel(pc[: n_all * hd].reshape(n_all, hd), qg_h[g0 : g0 + n_all, 0]) < 1e-9
+            assert rel(pc[n_all * hd : (n_all + ql) * hd].reshape(ql, hd), qg_h[r * ql : (r + 1) * ql, 1]) < 1e-9
+            assert rel(pc[(n_all + ql) * hd :], torch.cat([k_r, v_r])) < 1e-9
+    assert rel(got, want) < 1e-9
+
+    # experts (a routed one and the shared one): sum_r down_r @ (silu(gate_r x) * up_r x) == the expert
+    mbase = f"{PFX}layers.{lin}.mlp."
+    for e, ep in ((3, mbase + "experts.3."), (cfg.n_experts, mbase + "shared_expert.")):
+        want = W(ep + "down_proj.weight") @ (torch.nn.functional.silu(W(ep + "gate_proj.weight") @ x) * (W(ep + "up_proj.weight") @ x))
+        got = torch.zeros_like(want)
+        for sh in shards:
+            m = sh["layers"][lin]["moe"]
+            gu = _deq(m["w13"][e].view(torch.uint8), m["w13_s"][e]) @ x
+            Il = gu.numel() // 2
+            got += _deq(m["w2"][e].view(torch.uint8), m["w2_s"][e]) @ (torch.nn.functional.silu(gu[:Il]) * gu[Il:])
+        assert rel(got, want) < 1e-9
+    router = torch.cat([ck[mbase + "gate.weight"], ck[mbase + "shared_expert_gate.weight"].reshape(1, -1)], 0).to(torch.bfloat16)
+    assert all(torch.equal(sh["layers"][lin]["moe"]["router_w"], router) for sh in shards)
+
+    # vocabulary rows
+    assert torch.equal(torch.cat([sh["head"]["lm_head"] for sh in shards], 0), ck["lm_head.weight"].to(torch.bfloat16))
