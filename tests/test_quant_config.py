@@ -361,3 +361,61 @@ def test_rank_shards_compute_what_the_checkpoint_computes(tp):
 
     # vocabulary rows
     assert torch.equal(torch.cat([sh["head"]["lm_head"] for sh in shards], 0), ck["lm_head.weight"].to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_draft_shards_compute_what_the_draft_checkpoints_compute(tp):
+    """The same functional check for the two draft models: DFlash (bf16 rows / columns, the fc window over the
+    concatenated target features, the kv head a rank's q heads attend to) and MTP (the re-quantised fc window)."""
+    from nexrt_b200.config import shrunk_tp8_config
+    from nexrt_b200.dflash.config import shrunk_dflash_config
+    from nexrt_b200.dflash.weights import load_dflash_shard, random_dflash_checkpoint
+    from nexrt_b200.mtp.weights import random_mtp_checkpoint, shard_mtp
+
+    from nexrt_b200.config import shrunk_cp_config
+
+    cfg = shrunk_tp8_config() if tp == 8 else (shrunk_cp_config() if tp == 4 else shrunk_config())
+    dc = shrunk_dflash_config(cfg)
+    dc.validate_kernel_contract(cfg, tp)
+    ck = random_dflash_checkpoint(dc, 11)
+    shards = [load_dflash_shard(ck, dc, tp, r, "cpu") for r in range(tp)]
+    g = torch.Generator().manual_seed(2)
+    H, hd = dc.hidden, dc.head_dim
+    x = torch.randn(H, generator=g, dtype=torch.float64)
+    taps = torch.randn(dc.n_taps * H, generator=g, dtype=torch.float64)
+    rel = lambda a, b: float((a - b).norm() / b.norm().clamp_min(1e-30))
+    f = lambda k: ck[k].double()
+    assert rel(sum(sh["fc"].double() @ taps[sh["win0"] : sh["win0"] + sh["win"]] for sh in shards), f("fc.weight") @ taps) < 1e-12
+    p = "layers.0."
+    q, k, v = f(p + "self_attn.q_proj.weight") @ x, f(p + "self_attn.k_proj.weight") @ x, f(p + "self_attn.v_proj.weight") @ x
+    want_o = f(p + "self_attn.o_proj.weight") @ q
+    want_m = f(p + "mlp.down_proj.weight") @ (torch.nn.functional.silu(f(p + "mlp.gate_proj.weight") @ x) * (f(p + "mlp.up_proj.weight") @ x))
+    got_o, got_m = torch.zeros_like(want_o), torch.zeros_like(want_m)
+    group = dc.n_q_heads // dc.n_kv_heads
+    for r, sh in enumerate(shards):
+        lw = sh["layers"][0]
+        ql, kl = sh["q_local"], sh["kv_local"]
+        pre = lw["wqkv"].double() @ x
+        q_r, k_r, v_r = pre[: ql * hd], pre[ql * hd : (ql + kl) * hd], pre[(ql + kl) * hd :]
+        assert rel(q_r, q[r * ql * hd : (r + 1) * ql * hd]) < 1e-12
+        kv0 = (r * ql) // group                               # the kv head of the rank's first q head
+        assert all((r * ql + j) // group in range(kv0, kv0 + kl) for j in range(ql))
+        assert rel(k_r, k[kv0 * hd : (kv0 + kl) * hd]) < 1e-12 and rel(v_r, v[kv0 * hd : (kv0 + kl) * hd]) < 1e-12
+        assert torch.equal(lw["wkv"], lw["wqkv"][ql * hd :])
+        got_o += lw["wo"].double() @ q_r
+        gu = lw["wgu"].double() @ x
+        Il = sh["I_local"]
+        got_m += lw["wdown"].double() @ (torch.nn.functional.silu(gu[:Il]) * gu[Il:])
+    assert rel(got_o, want_o) < 1e-12 and rel(got_m, want_m) < 1e-12
+
+    # MTP: the fc over [embedding | hidden] is re-quantised once and split by input window
+    tck = random_checkpoint(cfg, 1)
+    mck = random_mtp_checkpoint(cfg, 7)
+    cat = torch.randn(2 * cfg.hidden, generator=g, dtype=torch.float64)
+    got = torch.zeros(cfg.hidden, dtype=torch.float64)
+    for r in range(tp):
+        head = shard_model(tck, cfg, tp, r, "cpu")["head"] if r == 0 else head
+        sh = shard_mtp(mck, cfg, tp, r, "cpu", head)
+        got += _deq(sh["fc_w"].view(torch.uint8), sh["fc_s"]) @ cat[sh["win0"] : sh["win0"] + sh["win"]]
+    fq, fs = quantize_blockwise(mck["mtp.fc.weight"].float())
+    assert rel(got, _deq(fq.view(torch.uint8), fs) @ cat) < 1e-9
