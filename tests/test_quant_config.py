@@ -419,3 +419,18 @@ def test_draft_shards_compute_what_the_draft_checkpoints_compute(tp):
         got += _deq(sh["fc_w"].view(torch.uint8), sh["fc_s"]) @ cat[sh["win0"] : sh["win0"] + sh["win"]]
     fq, fs = quantize_blockwise(mck["mtp.fc.weight"].float())
     assert rel(got, _deq(fq.view(torch.uint8), fs) @ cat) < 1e-9
+
+
+@pytest.mark.parametrize("tp,cp", [(1, False), (2, False), (8, True)])
+def test_direct_rank_initialisation_has_the_layout_of_a_sharded_checkpoint(tp, cp):
+    """``random_rank_model`` (what the benchmarks build at full geometry, where no global tensor may exist) must hand the
+    engine exactly the structure ``shard_model`` makes from a checkpoint: same keys, shapes and dtypes on every level."""
+    from nexrt_b200.config import shrunk_tp8_config
+    from nexrt_b200.weights import random_rank_model
+
+    cfg = shrunk_tp8_config() if tp == 8 else shrunk_config()
+    a = dict(_flat(random_rank_model(cfg, tp, tp - 1, "cpu", cp=cp)))
+    b = dict(_flat(shard_model(random_checkpoint(cfg, 0), cfg, tp, tp - 1, "cpu", cp=cp)))
+    assert set(a) == set(b), sorted(set(a) ^ set(b))
+    for k in b:
+        assert a[k].shape == b[k].shape and a[k].dtype == b[k].dtype, (k, a[k].shape, b[k].shape, a[k].dtype, b[k].dtype)
