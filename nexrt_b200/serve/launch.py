@@ -22,8 +22,10 @@ from pathlib import Path
 from typing import Dict, List
 
 
-def preflight(tp: int, layers_dir=None, probe_gpu: bool = True) -> List[Dict]:
-    """Return ``[{check, ok, detail}]``.  Reads state only: nothing on the GPUs is changed."""
+def preflight(tp: int, layers_dir=None, probe_gpu: bool = True, mode: str = "bs1", n_layers: int = 0) -> List[Dict]:
+    """Return ``[{check, ok, detail}]``.  Reads state only: nothing on the GPUs is changed.  ``n_layers`` (0 = the full
+    model) is how many ``layer.<L>`` files the directory must hold; ``mode`` adds the draft weights of a speculative mode
+    (their absence is reported but is not a failure: the server then runs a random draft)."""
     out: List[Dict] = []
 
     def add(check, ok, detail=""):
@@ -35,9 +37,21 @@ def preflight(tp: int, layers_dir=None, probe_gpu: bool = True) -> List[Dict]:
     add("kernel library built", lib.is_file(), lib)
     if layers_dir:
         d = Path(layers_dir)
-        need = ["embed_tokens.safetensors", "norm.safetensors", "lm_head.safetensors", "layer.0.safetensors"]
+        if not n_layers:
+            from ..config import full_config
+
+            n_layers = full_config().n_layers
+        need = ["embed_tokens.safetensors", "norm.safetensors", "lm_head.safetensors"] + [f"layer.{l}.safetensors" for l in range(n_layers)]
         missing = [n for n in need if not (d / n).is_file()]
-        add("layer directory", not missing, f"missing {missing}" if missing else d)
+        add("layer directory", not missing, f"missing {missing[:4]}{' ...' if len(missing) > 4 else ''} ({len(missing)} of {len(need)} files)" if missing else d)
+        if mode == "mtp":
+            have = (d / "mtp.safetensors").is_file()
+            add("MTP draft weights", True, d / "mtp.safetensors" if have else "mtp.safetensors not found: the server will run a RANDOM draft (acceptance ~1)")
+    if mode == "dflash":
+        from ..dflash.config import DFLASH_CONFIG, DFLASH_WEIGHTS
+
+        have = DFLASH_CONFIG.is_file() and DFLASH_WEIGHTS.is_file()
+        add("DFlash draft weights", True, DFLASH_WEIGHTS if have else f"{DFLASH_CONFIG} / {DFLASH_WEIGHTS} not found (NEXRT_DFLASH_DIR): the server will run a RANDOM draft")
     if probe_gpu:
         try:
             import torch
@@ -104,6 +118,8 @@ def main(argv=None) -> int:
     p = sub.add_parser("preflight")
     p.add_argument("--tp", type=int, default=8)
     p.add_argument("--layers-dir", default=None)
+    p.add_argument("--mode", default="bs1", choices=["bs1", "mtp", "dflash"])
+    p.add_argument("--layers", type=int, default=0, help="layer files the directory must hold (0 = the full model)")
     s = sub.add_parser("serve")
     s.add_argument("--tp", type=int, default=8)
     s.add_argument("--mode", default="bs1", choices=["bs1", "mtp", "dflash"])
@@ -125,7 +141,7 @@ def main(argv=None) -> int:
     k.add_argument("--timeout", type=float, default=600.0)
     a = ap.parse_args(argv)
     if a.cmd == "preflight":
-        rows = preflight(a.tp, a.layers_dir)
+        rows = preflight(a.tp, a.layers_dir, mode=a.mode, n_layers=a.layers)
         for r in rows:
             print(f"[{'ok' if r['ok'] else 'FAIL'}] {r['check']}: {r['detail']}")
         return 0 if all(r["ok"] for r in rows) else 1

@@ -99,6 +99,18 @@ def test_state_dir_prompt_and_preflight(tmp_path):
     rows = {r["check"]: r for r in preflight(3, layers_dir=str(tmp_path), probe_gpu=False)}
     assert not rows["tp degree"]["ok"] and not rows["layer directory"]["ok"] and "embed_tokens" in rows["layer directory"]["detail"]
     assert {r["check"]: r["ok"] for r in preflight(8, probe_gpu=False)}["tp degree"]
+    # every layer file is looked for, and a speculative mode reports (without failing) that its draft would be random
+    for name in ("embed_tokens", "norm", "lm_head", "layer.0", "layer.1"):
+        (tmp_path / f"{name}.safetensors").write_bytes(b"")
+    rows = {r["check"]: r for r in preflight(2, layers_dir=str(tmp_path), probe_gpu=False, mode="mtp", n_layers=3)}
+    assert not rows["layer directory"]["ok"] and "layer.2" in rows["layer directory"]["detail"] and "1 of 6" in rows["layer directory"]["detail"]
+    (tmp_path / "layer.2.safetensors").write_bytes(b"")
+    rows = {r["check"]: r for r in preflight(2, layers_dir=str(tmp_path), probe_gpu=False, mode="mtp", n_layers=3)}
+    assert rows["layer directory"]["ok"] and rows["MTP draft weights"]["ok"] and "RANDOM" in rows["MTP draft weights"]["detail"]
+    (tmp_path / "mtp.safetensors").write_bytes(b"")
+    rows = {r["check"]: r for r in preflight(2, layers_dir=str(tmp_path), probe_gpu=False, mode="mtp", n_layers=3)}
+    assert "RANDOM" not in rows["MTP draft weights"]["detail"]
+    assert "RANDOM" in {r["check"]: r for r in preflight(2, probe_gpu=False, mode="dflash")}["DFlash draft weights"]["detail"]
 
 
 def test_timeline_collector_groups_launches_of_mixed_grids():
