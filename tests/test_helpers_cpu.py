@@ -151,3 +151,45 @@ def test_packaging_metadata_names_real_entry_points():
     csrc = root / "nexrt_b200" / "csrc"
     covered = {p.name for pat in patterns for p in (root / "nexrt_b200").glob(pat)}
     assert {p.name for p in csrc.iterdir() if p.suffix in (".cu", ".cuh", ".h")} <= covered
+
+
+def test_bench_clock_sampler_against_a_fake_nvml(monkeypatch):
+    """``bench.NvmlClocks`` only READS: SM clock, maximum clock and throttle reasons.  With a fake ``pynvml`` the summary is
+    the median clock, the named reasons that were active in any sample, and at least the two samples taken at the
+    start and the end of the region; without NVML it reports no samples rather than failing the benchmark."""
+    import sys
+    import time
+    import types
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    import bench
+
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlClocksThrottleReasonHwSlowdown, fake.nvmlClocksThrottleReasonSwPowerCap = 0x8, 0x4
+    fake.nvmlClocksThrottleReasonHwThermalSlowdown, fake.nvmlClocksThrottleReasonSwThermalSlowdown = 0x40, 0x20
+    calls = {"n": 0, "writes": 0}
+    clocks = [1965, 1965, 1310, 1965, 1965]
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("gpu", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, kind: 1965
+
+    def clock(h, kind):
+        calls["n"] += 1
+        return clocks[min(calls["n"] - 1, len(clocks) - 1)]
+
+    fake.nvmlDeviceGetClockInfo = clock
+    fake.nvmlDeviceGetCurrentClocksThrottleReasons = lambda h: 0x4 if calls["n"] == 3 else 0
+    for setter in ("nvmlDeviceSetApplicationsClocks", "nvmlDeviceSetGpuLockedClocks", "nvmlDeviceResetGpuLockedClocks", "nvmlDeviceSetPowerManagementLimit"):
+        setattr(fake, setter, lambda *a, **k: calls.__setitem__("writes", calls["writes"] + 1))
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    s = bench.NvmlClocks(0, period_s=0.002).start()
+    time.sleep(0.05)
+    out = s.stop()
+    assert out["sm_max_mhz"] == 1965.0 and out["sm_mhz"] == 1965.0 and out["samples"] >= 3 and out["reasons"] == ["sw_power_cap"]
+    assert calls["writes"] == 0                       # nothing that changes a GPU setting was called
+    broken = types.ModuleType("pynvml")
+    broken.nvmlInit = lambda: (_ for _ in ()).throw(RuntimeError("no driver"))
+    monkeypatch.setitem(sys.modules, "pynvml", broken)
+    assert bench.NvmlClocks(0).start().stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
