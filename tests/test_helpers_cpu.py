@@ -193,3 +193,19 @@ def test_bench_clock_sampler_against_a_fake_nvml(monkeypatch):
     broken.nvmlInit = lambda: (_ for _ in ()).throw(RuntimeError("no driver"))
     monkeypatch.setitem(sys.modules, "pynvml", broken)
     assert bench.NvmlClocks(0).start().stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+
+
+def test_reference_arm_reports_one_unavailable_line_and_exits_zero():
+    """``bench.py --impl reference`` where the reference cannot run: exactly one JSON line with ``impl`` and a one-line
+    reason, exit code 0."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    done = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference"], capture_output=True, text=True, timeout=300, cwd=root)
+    lines = [l for l in done.stdout.splitlines() if l.strip()]
+    assert done.returncode == 0 and len(lines) == 1, (done.returncode, done.stdout[-500:], done.stderr[-500:])
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and isinstance(rec["unavailable"], str) and rec["unavailable"] and "\n" not in rec["unavailable"]
