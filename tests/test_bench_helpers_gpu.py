@@ -35,9 +35,9 @@ def test_bench_graph_times_known_nodes():
     plain = bench_graph(g, reps=20, warmup=3, device=dev, trials=3)
     assert len(plain["trials_ms"]) == 3 and plain["total_ms"] == pytest.approx(plain["ms_per_replay"] * 20)
     us = plain["ms_per_replay"] * 1e3
-    assert 100.0 <= us < 130.0, us
+    assert 100.0 <= us < 160.0, us              # three kernel boundaries on top of the 100 us of spinning; slack for a busy host
     flushed = bench_graph(g, reps=10, warmup=2, device=dev, flush_l2=True)["ms_per_replay"] * 1e3
-    assert 100.0 <= flushed < 160.0, flushed
+    assert 100.0 <= flushed < 220.0, flushed
 
 
 def test_profile_pipeline_attributes_each_stage():
@@ -56,7 +56,7 @@ def test_profile_pipeline_attributes_each_stage():
     rows = profile_pipeline(made, list(spins), reps=20, warmup=3, device=dev)
     assert [r["stage"] for r in rows] == list(spins)
     for r, ns in zip(rows, spins.values()):
-        assert abs(r["increment_us"] - ns / 1e3) < 8.0, (r, ns)
+        assert abs(r["increment_us"] - ns / 1e3) < 15.0, (r, ns)
     assert rows[-1]["cumulative_us"] == pytest.approx(sum(r["increment_us"] for r in rows), rel=1e-6)
 
 
