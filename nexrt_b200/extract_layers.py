@@ -103,8 +103,10 @@ def extract(src: Optional[str], dst: str, layers: Optional[Iterable[int]] = None
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--src", help="sharded target checkpoint (omit with --mtp-src to write mtp.safetensors only)")
-    ap.add_argument("--mtp-src", help="sharded checkpoint whose mtp.* tensors become mtp.safetensors")
+    ap.add_argument("--src", default=os.environ.get("NEXRT_MODEL_DIR"),
+                    help="sharded target checkpoint (default NEXRT_MODEL_DIR; omit both to write mtp.safetensors only)")
+    ap.add_argument("--mtp-src", default=os.environ.get("NEXRT_MTP_MODEL_DIR"),
+                    help="sharded checkpoint whose mtp.* tensors become mtp.safetensors (default NEXRT_MTP_MODEL_DIR; may be the target checkpoint itself)")
     ap.add_argument("--dst", default=os.environ.get("NEXRT_LAYERS_DIR"))
     ap.add_argument("--layers", type=int, nargs="*", default=None)
     ap.add_argument("--no-globals", action="store_true")
