@@ -143,8 +143,9 @@ class BridgeStreamWriter:
     """Owns the client socket of a streaming request.
 
     Producers (the decode loop's token callback) append to a bounded deque under a condition variable and return at
-    once; one writer thread pops, detokenises and sends.  A backlog that reaches its limit means the client cannot keep
-    up: the stream is dropped, never the decode loop.  Exactly one terminal event (``done`` or ``error``) can be
+    once; one writer thread pops, detokenises and sends.  Consecutive token events that wait behind a send are merged
+    into one.  A backlog that still reaches its limit means the client cannot keep up: the stream is dropped, never the
+    decode loop.  Exactly one terminal event (``done`` or ``error``) can be
     queued; ``close()`` waits a bounded time for the thread and shuts the socket down under it if it is stuck in a send.
     """
 
@@ -185,6 +186,11 @@ class BridgeStreamWriter:
         with self._cv:
             if self._state is not WriterState.OPEN:
                 return False
+            if kind == "tokens" and self._pending and self._pending[-1][0] == "tokens":
+                # tokens that queue up behind a slow send travel as one longer delta: a client that is slow but alive
+                # costs no backlog slots (a dead one is found by the write timeout), and the decode loop still never waits
+                self._pending[-1] = ("tokens", self._pending[-1][1] + payload)
+                return True
             if len(self._pending) >= self.max_backlog:
                 self._state = WriterState.DROPPED
                 self._pending.clear()

@@ -628,3 +628,48 @@ def test_request_validation_survives_arbitrary_json():
             assert ids and all(isinstance(t, int) and 0 <= t < srv.backend.vocab for t in ids)
             json.dumps(r)
     assert accepted > 20          # the generator does produce valid requests too
+
+
+class _PausedConnection:
+    """A connection whose first send blocks until released (a client that is slow, not gone)."""
+
+    def __init__(self):
+        self.started, self.release, self.writes = threading.Event(), threading.Event(), []
+
+    def settimeout(self, t):
+        pass
+
+    def sendall(self, data):
+        self.started.set()
+        assert self.release.wait(10.0)
+        self.writes.append(data)
+
+    def shutdown(self, how):
+        self.release.set()
+
+
+def test_stream_writer_merges_tokens_behind_a_slow_send_and_keeps_the_terminal_event():
+    """While one send is stuck, token events merge into one queued delta (no backlog slots), the terminal event still
+    fits (reference tests/test_openai_serve.py: test_stream_writer_terminal_event_uses_one_backlog_slot), and the client
+    gets the whole text once it reads again."""
+    conn = _PausedConnection()
+    tok = ByteTokenizer()
+    w = BridgeStreamWriter(conn, tok, stop_ids=(2,), max_backlog=2, shutdown_timeout=2.0)
+    assert w.event({"type": "start"})
+    assert conn.started.wait(2.0)
+    ids = tok.encode("slow but alive: " + "é✓" * 200)
+    assert all(w.tokens([t]) for t in ids)                    # hundreds of callbacks, none refused, none blocking
+    assert w.finish({"tokens": ids, "generated_text": "x", "status": 0})
+    assert not w.tokens([5])
+    conn.release.set()
+    assert w.close() and not w.disconnected
+    events = [json.loads(line) for data in conn.writes for line in data.decode().splitlines()]
+    assert [e["type"] for e in events] == ["start", "delta", "done"]
+    assert events[1]["text"] == decode_visible_text(tok, ids, (2,))
+    # different kinds do not merge: two raw events behind a stuck send fill a backlog of two, the third offer drops the stream
+    conn2 = _PausedConnection()
+    w2 = BridgeStreamWriter(conn2, tok, max_backlog=2, shutdown_timeout=0.2)
+    assert w2.event({"type": "start"}) and conn2.started.wait(2.0)
+    assert w2.event({"a": 1}) and w2.event({"a": 2}) and not w2.event({"a": 3}) and w2.disconnected
+    conn2.release.set()
+    w2.close()
